@@ -1,0 +1,102 @@
+// Shared helpers for the sm_100a decode kernels and their C ABI.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/ironmill_cuda.h"
+
+#define IM_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace im {
+
+// Thread-local error text behind im_cuda_last_error().
+std::string &last_error();
+int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define IM_CUDA_CHECK(expr)                                                                   \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess)                                                                \
+            return im::fail(_e == cudaErrorMemoryAllocation ? IM_ERR_ALLOC : IM_ERR_CUDA,     \
+                            "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, \
+                            __LINE__);                                                        \
+    } while (0)
+
+#define IM_REQUIRE(cond, ...)                               \
+    do {                                                    \
+        if (!(cond)) return im::fail(IM_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+// Wrap an entry point body so that no C++ exception crosses the C boundary.
+#define IM_GUARD_BEGIN try {
+#define IM_GUARD_END                                                        \
+    }                                                                       \
+    catch (const std::bad_alloc &) { return im::fail(IM_ERR_ALLOC, "host allocation failed"); } \
+    catch (const std::exception &e) { return im::fail(IM_ERR_CUDA, "exception: %s", e.what()); } \
+    catch (...) { return im::fail(IM_ERR_CUDA, "unknown exception"); }
+
+struct Device {
+    int ordinal = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    cudaDeviceProp prop{};
+    size_t allocated = 0;  // bytes handed out through this handle
+};
+
+// Allocation bookkeeping shared by buffers, weights and models.
+int dev_malloc(Device *dev, void **ptr, size_t bytes);
+void dev_free(Device *dev, void *ptr, size_t bytes);
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// GPU-resident affine weight after the load-time repack.
+struct AffineWeight {
+    Device *dev = nullptr;
+    int N = 0, K = 0, group_size = 0, bits = 0, G = 0;
+    uint8_t *codes = nullptr;  // [N, K/2] (4-bit) or [N, K] (8-bit), row-major, 16-byte aligned rows
+    __half2 *sz = nullptr;     // [N, G] interleaved (scale, zero) fp16
+    __half *awq = nullptr;     // [K] or nullptr
+    size_t bytes = 0;
+};
+
+// ---- device helpers -------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Streaming 128-bit load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
+    uint4 r;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+// 4-way byte dot products: unsigned codes against signed / unsigned activation bytes.
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b_signed, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b_signed), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
+    unsigned d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"((unsigned)c));
+    return (int)d;
+}
+
+}  // namespace im
+
+// The opaque handle types of the C ABI are thin tags over the internal structs.
+struct im_device : im::Device {};
+struct im_affine_weight : im::AffineWeight {};

@@ -1,0 +1,207 @@
+"""Kernel-level entry points of the C ABI, called with torch CUDA tensors.
+
+torch supplies device memory and streams only; every computation below is a call into
+libironmill_cuda.so.  Names follow the reference's kernels
+(crates/ironmill-inference/src/metal/shaders/**) and quantizer
+(crates/mil-rs/src/ir/passes/affine_quantize.rs).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ._lib import IM_DTYPE_F16, IM_DTYPE_F32, check, lib, vp
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Device:
+    """MetalDevice counterpart (crates/ironmill-metal-sys/src/device.rs:74-260)."""
+
+    def __init__(self, ordinal: int = 0):
+        self.handle = C.c_void_p()
+        check(lib().im_cuda_device_open(C.c_int(ordinal), C.byref(self.handle)))
+        self.ordinal = ordinal
+
+    @property
+    def name(self) -> str:
+        buf = C.create_string_buffer(256)
+        check(lib().im_cuda_device_name(self.handle, buf, C.c_size_t(256)))
+        return buf.value.decode()
+
+    @property
+    def sm_count(self) -> int:
+        return int(lib().im_cuda_device_sm_count(self.handle))
+
+    def allocated_bytes(self) -> int:
+        return int(lib().im_cuda_device_allocated_bytes(self.handle))
+
+    def synchronize(self) -> None:
+        check(lib().im_cuda_device_synchronize(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            lib().im_cuda_device_free(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Buffer:
+    """MetalBuffer counterpart (crates/ironmill-metal-sys/src/buffer.rs:42-158)."""
+
+    def __init__(self, dev: Device, nbytes: int, data: bytes | None = None):
+        self.handle = C.c_void_p()
+        if data is None:
+            check(lib().im_cuda_buffer_alloc(dev.handle, C.c_size_t(nbytes), C.byref(self.handle)))
+        else:
+            check(lib().im_cuda_buffer_alloc_with_data(dev.handle, data, C.c_size_t(len(data)), C.byref(self.handle)))
+
+    def __len__(self):
+        return int(lib().im_cuda_buffer_length(self.handle))
+
+    @property
+    def ptr(self) -> int:
+        return int(lib().im_cuda_buffer_ptr(self.handle) or 0)
+
+    def write_bytes(self, data: bytes, offset: int = 0) -> None:
+        check(lib().im_cuda_buffer_upload(self.handle, C.c_size_t(offset), data, C.c_size_t(len(data))))
+
+    def read_bytes(self, nbytes: int, offset: int = 0) -> bytes:
+        out = C.create_string_buffer(nbytes)
+        check(lib().im_cuda_buffer_download(self.handle, C.c_size_t(offset), out, C.c_size_t(nbytes)))
+        return out.raw
+
+    def free(self):
+        if self.handle:
+            lib().im_cuda_buffer_free(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def quantize_affine(w: torch.Tensor, group_size: int, bit_width: int, awq: torch.Tensor | None = None):
+    """GPU quantize + pack.  w fp16 [rows, K] -> (packed u8, scales f32 [rows,G], zps f32 [rows,G])."""
+    assert w.is_cuda and w.dtype == torch.float16 and w.is_contiguous()
+    rows = int(np.prod(w.shape[:-1])) if w.dim() > 1 else 1
+    K = w.shape[-1] if w.dim() else 0
+    G = -(-K // group_size) if K else 0
+    total = rows * K
+    nbytes = (total + 1) // 2 if bit_width == 4 else total
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+    scales = torch.empty((rows, G), dtype=torch.float32, device=w.device)
+    zps = torch.empty((rows, G), dtype=torch.float32, device=w.device)
+    check(lib().im_cuda_quantize_affine(vp(w), vp(awq), C.c_size_t(rows), C.c_size_t(K), C.c_int(group_size),
+                                        C.c_int(bit_width), vp(packed), vp(scales), vp(zps), _stream()))
+    return packed, scales, zps
+
+
+class AffineWeight:
+    """GPU-resident affine-quantized weight (AffineQuantizedWeight,
+    crates/ironmill-inference/src/metal/weights.rs:129-147)."""
+
+    def __init__(self, dev: Device, qdata, scales, zeros, N: int, K: int, group_size: int, bit_width: int, awq=None):
+        self.dev = dev
+        self.N, self.K, self.group_size, self.bit_width = N, K, group_size, bit_width
+        self.handle = C.c_void_p()
+        if isinstance(qdata, torch.Tensor):
+            assert qdata.is_cuda and scales.is_cuda and zeros.is_cuda
+            pd = IM_DTYPE_F32 if scales.dtype == torch.float32 else IM_DTYPE_F16
+            assert scales.dtype == zeros.dtype and scales.is_contiguous() and zeros.is_contiguous()
+            check(lib().im_cuda_affine_weight_create_dev(dev.handle, vp(qdata), vp(scales), vp(zeros), C.c_int(pd),
+                                                         vp(awq), C.c_int(N), C.c_int(K), C.c_int(group_size),
+                                                         C.c_int(bit_width), _stream(), C.byref(self.handle)))
+            torch.cuda.current_stream().synchronize()
+        else:
+            qdata = np.ascontiguousarray(qdata)
+            scales = np.ascontiguousarray(scales)
+            zeros = np.ascontiguousarray(zeros)
+            assert scales.dtype == zeros.dtype and scales.dtype in (np.float32, np.float16)
+            pd = IM_DTYPE_F32 if scales.dtype == np.float32 else IM_DTYPE_F16
+            if awq is not None:
+                awq = np.ascontiguousarray(awq)
+                assert awq.dtype == np.float16
+            check(lib().im_cuda_affine_weight_create(dev.handle, vp(qdata), vp(scales), vp(zeros), C.c_int(pd), vp(awq),
+                                                     C.c_int(N), C.c_int(K), C.c_int(group_size), C.c_int(bit_width),
+                                                     C.byref(self.handle)))
+
+    def nbytes(self) -> int:
+        return int(lib().im_cuda_affine_weight_bytes(self.handle))
+
+    def dequant(self) -> torch.Tensor:
+        out = torch.empty((self.N, self.K), dtype=torch.float16, device=f"cuda:{self.dev.ordinal}")
+        check(lib().im_cuda_affine_weight_dequant(self.handle, vp(out), _stream()))
+        return out
+
+    def free(self):
+        if self.handle:
+            lib().im_cuda_affine_weight_free(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _rows(x: torch.Tensor, K: int) -> int:
+    assert x.is_cuda and x.dtype == torch.float16 and x.is_contiguous()
+    assert x.shape[-1] == K, (x.shape, K)
+    return x.numel() // K
+
+
+def matvec_affine(w: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    B = _rows(x, w.K)
+    y = out if out is not None else torch.empty((B, w.N), dtype=torch.float16, device=x.device)
+    check(lib().im_cuda_matvec_affine(w.handle, vp(x), vp(y), C.c_int(B), _stream()))
+    return y
+
+
+def matvec_affine_host(w: AffineWeight, x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    assert x.dtype == np.float16
+    B = x.size // w.K
+    y = np.empty((B, w.N), dtype=np.float16)
+    check(lib().im_cuda_matvec_affine_host(w.handle, vp(x), vp(y), C.c_int(B)))
+    return y
+
+
+def ffn_gate_up_act(gate: AffineWeight, up: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = None):
+    B = _rows(x, gate.K)
+    y = out if out is not None else torch.empty((B, gate.N), dtype=torch.float16, device=x.device)
+    check(lib().im_cuda_ffn_gate_up_act(gate.handle, up.handle, vp(x), vp(y), C.c_int(B), _stream()))
+    return y
+
+
+def fused_residual_norm_matvec(w: AffineWeight, a: torch.Tensor, b: torch.Tensor, gamma: torch.Tensor, eps: float,
+                               want_residual: bool = True, want_normed: bool = True):
+    B = _rows(a, w.K)
+    assert b.shape == a.shape and b.dtype == torch.float16 and gamma.dtype == torch.float16
+    y = torch.empty((B, w.N), dtype=torch.float16, device=a.device)
+    res = torch.empty_like(a) if want_residual else None
+    nrm = torch.empty_like(a) if want_normed else None
+    check(lib().im_cuda_fused_residual_norm_matvec(w.handle, vp(a), vp(b), vp(gamma), C.c_float(eps), vp(y), vp(res),
+                                                   vp(nrm), C.c_int(B), _stream()))
+    return y, res, nrm
+
+
+def matvec_f16(w: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    assert w.is_cuda and w.dtype == torch.float16 and w.is_contiguous() and w.dim() == 2
+    N, K = w.shape
+    B = _rows(x, K)
+    y = torch.empty((B, N), dtype=torch.float16, device=x.device)
+    check(lib().im_cuda_matvec_f16(vp(w), vp(x), vp(y), C.c_int(N), C.c_int(K), C.c_int(B), _stream()))
+    return y
