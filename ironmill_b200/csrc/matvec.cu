@@ -63,11 +63,14 @@ __device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {
 template <int BITS, int MODE>
 __device__ __forceinline__ float stage_activations(const MatvecParams &p, int b, uint4 *xq, float2 *meta) {
     const int K = p.K;
-    const int lane = threadIdx.x & 31, hl = lane & 15;
-    const int hw = threadIdx.x >> 4, nhw = kThreads >> 4;
+    const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
     float sq = 0.0f;
-    for (int g = hw; g < p.G; g += nhw) {
-        const int k = g * kGroup + hl * 8;
+    // Two groups per warp pass; the trip count is uniform across the warp because the
+    // half-warp shuffles below are issued with a full mask.
+    for (int g0 = warp * 2; g0 < p.G; g0 += kWarps * 2) {
+        const int g = g0 + (lane >> 4);
+        const bool live = g < p.G;
+        const int k = (live ? g : g0) * kGroup + hl * 8;
         float v[8];
         {
             uint4 raw = *reinterpret_cast<const uint4 *>(p.x + (size_t)b * K + k);
@@ -88,7 +91,7 @@ __device__ __forceinline__ float stage_activations(const MatvecParams &p, int b,
             for (int i = 0; i < 4; i++) {
                 float2 fb = __half22float2(hb[i]), fg = __half22float2(hg[i]);
                 float r0 = v[2 * i] + fb.x, r1 = v[2 * i + 1] + fb.y;
-                sq += r0 * r0 + r1 * r1;
+                if (live) sq += r0 * r0 + r1 * r1;
                 v[2 * i] = r0 * fg.x;
                 v[2 * i + 1] = r1 * fg.y;
             }
@@ -123,19 +126,19 @@ __device__ __forceinline__ float stage_activations(const MatvecParams &p, int b,
         const int c = k / kChunk, kl = k % kChunk, ldst = kl / kEpl;
         if (BITS == 4) {
             const int j = (kl % kEpl) / 8;
-            xq[(c * kXV + j) * 32 + ldst] =
+            if (live) xq[(c * kXV + j) * 32 + ldst] =
                 make_uint4(pack4(hi[0], hi[2], hi[4], hi[6]), pack4(hi[1], hi[3], hi[5], hi[7]),
                            pack4(lo[0], lo[2], lo[4], lo[6]), pack4(lo[1], lo[3], lo[5], lo[7]));
             lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
             lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-            if ((hl & 3) == 0) meta[c * 32 + ldst] = make_float2(sx, (float)lsum);
+            if (live && (hl & 3) == 0) meta[c * 32 + ldst] = make_float2(sx, (float)lsum);
         } else {
             const int j = (kl % kEpl) / 8;
-            xq[(c * kXV + j) * 32 + ldst] =
+            if (live) xq[(c * kXV + j) * 32 + ldst] =
                 make_uint4(pack4(hi[0], hi[1], hi[2], hi[3]), pack4(lo[0], lo[1], lo[2], lo[3]),
                            pack4(hi[4], hi[5], hi[6], hi[7]), pack4(lo[4], lo[5], lo[6], lo[7]));
             lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-            if ((hl & 1) == 0) meta[c * 32 + ldst] = make_float2(sx, (float)lsum);
+            if (live && (hl & 1) == 0) meta[c * 32 + ldst] = make_float2(sx, (float)lsum);
         }
     }
     return sq;
