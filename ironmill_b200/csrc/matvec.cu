@@ -187,6 +187,33 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
     const int rgs = kWarps / ksplit;
     const size_t row_bytes = (size_t)K * BITS / 8;
 
+    // One work item = one 16-byte weight load per row stream (plus its scale/zero pair).
+    struct Item {
+        uint4 wv[RS];
+        __half2 szv[RS];
+    };
+    const int rows_per_tile = rgs * R;
+    const int ntiles = (N + rows_per_tile - 1) / rows_per_tile;
+    auto load_item = [&](int tile, int c, Item &it) {
+        const int k0 = c * kChunk + lane * kEpl;
+        if (k0 < K) {
+            const int n0 = tile * rows_per_tile + rg * R;
+#pragma unroll
+            for (int t = 0; t < RS; t++) {
+                const int n = min(n0 + (t % R), N - 1);  // clamped rows compute but never store
+                const bool second = MODE == kGateUpAct && t >= R;
+                it.wv[t] = ldg_stream_v4((second ? p.codes1 : p.codes0) + (size_t)n * row_bytes + (size_t)k0 * BITS / 8);
+                it.szv[t] = (second ? p.sz1 : p.sz0)[(size_t)n * G + k0 / kGroup];
+            }
+        }
+    };
+
+    // The first weight loads are issued before the activations are staged, so that the HBM
+    // pipe fills while the CTA quantises x.
+    Item cur, nxt;
+    int tile = blockIdx.x, c = kw;
+    if (tile < ntiles && c < nchunks) load_item(tile, c, cur);
+
     // ---- stage activations (once per CTA) ----
     float sq_tot[NB];
 #pragma unroll
@@ -211,7 +238,8 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
 #pragma unroll
     for (int b = 0; b < NB; b++) rms_inv[b] = MODE == kResidualNorm ? rsqrtf(sq_tot[b] / (float)K + p.eps) : 1.0f;
 
-    // Side outputs of the fused residual+norm form, written by CTA 0 only.
+    // Side outputs of the fused residual+norm form, written by CTA 0 only
+    // (they must not alias a or b: other CTAs are still reading those).
     if (MODE == kResidualNorm && blockIdx.x == 0) {
         for (int b = 0; b < NB; b++)
             for (int k = threadIdx.x; k < K; k += kThreads) {
@@ -221,9 +249,7 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
             }
     }
 
-    const int rows_per_tile = rgs * R;
-    const int ntiles = (N + rows_per_tile - 1) / rows_per_tile;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    for (; tile < ntiles; tile += gridDim.x) {
         const int n0 = tile * rows_per_tile + rg * R;
         float res[RS][NB];
 #pragma unroll
@@ -231,27 +257,17 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
 #pragma unroll
             for (int b = 0; b < NB; b++) res[t][b] = 0.0f;
 
-        const uint8_t *cptr[RS];
-        const __half2 *sptr[RS];
-#pragma unroll
-        for (int t = 0; t < RS; t++) {
-            const int n = min(n0 + (t % R), N - 1);  // clamped rows compute but never store
-            const bool second = MODE == kGateUpAct && t >= R;
-            cptr[t] = (second ? p.codes1 : p.codes0) + (size_t)n * row_bytes;
-            sptr[t] = (second ? p.sz1 : p.sz0) + (size_t)n * G;
-        }
+        for (c = kw; c < nchunks; c += ksplit) {
+            // prefetch the next item of this warp (next chunk, or first chunk of the next tile)
+            int c2 = c + ksplit, tile2 = tile;
+            if (c2 >= nchunks) {
+                c2 = kw;
+                tile2 = tile + gridDim.x;
+            }
+            if (tile2 < ntiles) load_item(tile2, c2, nxt);
 
-#pragma unroll 2
-        for (int c = kw; c < nchunks; c += ksplit) {
             const int k0 = c * kChunk + lane * kEpl;
             if (k0 < K) {
-                uint4 wv[RS];
-                __half2 szv[RS];
-#pragma unroll
-                for (int t = 0; t < RS; t++) {
-                    wv[t] = ldg_stream_v4(cptr[t] + (size_t)k0 * BITS / 8);
-                    szv[t] = sptr[t][k0 / kGroup];
-                }
 #pragma unroll
                 for (int b = 0; b < NB; b++) {
                     const uint4 *xb = xq + ((size_t)b * nchunks + c) * kXV * 32 + lane;
@@ -261,12 +277,13 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(const MatvecParams p) 
                     const float2 m = meta[((size_t)b * nchunks + c) * 32 + lane];
 #pragma unroll
                     for (int t = 0; t < RS; t++) {
-                        const float f = (float)dot_lane<BITS>(wv[t], xv);
-                        const float2 s_z = __half22float2(szv[t]);
+                        const float f = (float)dot_lane<BITS>(cur.wv[t], xv);
+                        const float2 s_z = __half22float2(cur.szv[t]);
                         res[t][b] = fmaf(s_z.x * m.x, fmaf(-s_z.y, m.y, f), res[t][b]);
                     }
                 }
             }
+            cur = nxt;
         }
 
 #pragma unroll

@@ -66,11 +66,35 @@ __global__ void quantize_params_kernel(const __half *__restrict__ w, const __hal
     }
 }
 
+// A group without any finite value quantizes to all zeros (the CPU routine returns early with
+// a zero vector); a non-finite element of any other group saturates through the clamp.  Only
+// non-finite elements take the rescan, so the common path stays one pass.
+__device__ __noinline__ bool group_has_finite(const __half *w, const __half *awq, size_t row_base, size_t c0, size_t c1) {
+    for (size_t c = c0; c < c1; c++)
+        if (isfinite(load_weight(w, awq, row_base + c, c))) return true;
+    return false;
+}
+
+__device__ __forceinline__ unsigned quantize_elem(const __half *w, const __half *awq, size_t i, size_t K, int gs, int G,
+                                                  const float *scales, const float *zps, float qmax);
+
 __device__ __forceinline__ unsigned quantize_one(float x, float scale, float zp, float qmax) {
     float t = roundf(__fadd_rn(__fdiv_rn(x, scale), zp));
     if (t != t) return 0u;  // NaN saturates to 0 like Rust's `as u8`
     t = fminf(fmaxf(t, 0.0f), qmax);
     return (unsigned)t;
+}
+
+__device__ __forceinline__ unsigned quantize_elem(const __half *w, const __half *awq, size_t i, size_t K, int gs, int G,
+                                                  const float *scales, const float *zps, float qmax) {
+    const size_t r = i / K, c = i % K;
+    const size_t g = c / gs, pi = r * G + g;
+    const float x = load_weight(w, awq, i, c);
+    if (!isfinite(x)) {
+        const size_t c0 = g * gs, c1 = c0 + gs < K ? c0 + gs : K;
+        if (!group_has_finite(w, awq, r * K, c0, c1)) return 0u;
+    }
+    return quantize_one(x, scales[pi], zps[pi], qmax);
 }
 
 // 4-bit: one thread per output byte = flat element pair (2p, 2p+1); the pair may straddle
@@ -87,9 +111,7 @@ __global__ void quantize_codes_int4_kernel(const __half *__restrict__ w, const _
     for (int h = 0; h < 2; h++) {
         size_t i = 2 * p + h;
         if (i < total) {
-            size_t r = i / K, c = i % K;
-            size_t pi = r * G + c / gs;
-            unsigned q = quantize_one(load_weight(w, awq, i, c), scales[pi], zps[pi], 15.0f);
+            unsigned q = quantize_elem(w, awq, i, K, gs, G, scales, zps, 15.0f);
             byte |= (q & 0xFu) << (4 * h);
         }
     }
@@ -102,9 +124,7 @@ __global__ void quantize_codes_int8_kernel(const __half *__restrict__ w, const _
                                            uint8_t *__restrict__ out) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    size_t r = i / K, c = i % K;
-    size_t pi = r * G + c / gs;
-    out[i] = (uint8_t)quantize_one(load_weight(w, awq, i, c), scales[pi], zps[pi], 255.0f);
+    out[i] = (uint8_t)quantize_elem(w, awq, i, K, gs, G, scales, zps, 255.0f);
 }
 
 }  // namespace im
