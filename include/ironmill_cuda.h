@@ -145,6 +145,67 @@ int im_cuda_fused_residual_norm_matvec(const im_affine_weight *w, const void *a_
  * w_dev fp16 [N,K] row-major, x_dev fp16 [B,K], y_dev fp16 [B,N]. */
 int im_cuda_matvec_f16(const void *w_dev, const void *x_dev, void *y_dev, int N, int K, int B, void *stream);
 
+/* ------------------------------------------------------------------ norms, embedding, RoPE
+ * rms_norm (crates/ironmill-inference/src/metal/shaders/norm/normalization.metal:19-57):
+ * out = f16(x * rsqrt(mean(x^2) + eps) * gamma), x fp16 [T,H]. */
+int im_cuda_rms_norm(const void *x_dev, const void *gamma_dev, void *out_dev, int H, int T, float eps, void *stream);
+/* fused_residual_rms_norm (.../shaders/norm/fused_residual_norm.metal:33-75):
+ * residual = f16(a + b); normed from the unrounded f32 sum. */
+int im_cuda_fused_residual_rms_norm(const void *a_dev, const void *b_dev, const void *gamma_dev, void *normed_dev,
+                                    void *residual_dev, int H, int T, float eps, void *stream);
+/* residual_add (.../shaders/elementwise/elementwise.metal:14-23). */
+int im_cuda_residual_add(const void *a_dev, const void *b_dev, void *out_dev, size_t n, void *stream);
+/* fused_embedding_norm (.../shaders/norm/fused_embedding_norm.metal:29-72): gather fp16 row * embed_scale
+ * (zeros when token >= vocab) -> raw; RMSNorm * gamma -> normed.  tokens_dev u32 [T]. */
+int im_cuda_embedding_norm(const uint32_t *tokens_dev, const void *table_dev, const void *gamma_dev, void *normed_dev,
+                           void *raw_dev, int H, int T, uint32_t vocab, float eps, float embed_scale, void *stream);
+/* fused_qk_norm_rope (.../shaders/norm/fused_qk_norm_rope.metal:43-124): per head RMSNorm with a [head_dim]
+ * weight, then half-split RoPE over the first rotary_dim dims, in place.  q [T,nh,hd], k [T,nkv,hd];
+ * cos/sin fp16 [max_pos, hd/2]; position of token t = seq_offset + t. */
+int im_cuda_qk_norm_rope(void *q_dev, void *k_dev, const void *q_norm_w_dev, const void *k_norm_w_dev, const void *cos_dev,
+                         const void *sin_dev, int nh, int nkv, int head_dim, int rotary_dim, int seq_offset, int T, float eps,
+                         void *stream);
+/* rope (.../shaders/rope/rope.metal:21-60): RoPE only (models without QK-norm), in place on qk [T,heads,hd]. */
+int im_cuda_rope(void *qk_dev, const void *cos_dev, const void *sin_dev, int heads, int head_dim, int seq_offset, int T,
+                 void *stream);
+/* precompute_rope_cache (crates/ironmill-core/src/rope.rs:22-49): f64 on the host, rounded to fp16,
+ * uploaded to cos_dev / sin_dev [max_pos, head_dim/2].  rotary_dim 0 = head_dim. */
+int im_cuda_rope_table(int head_dim, int max_pos, double theta, int rotary_dim, void *cos_dev, void *sin_dev);
+
+/* ------------------------------------------------------------------ TurboQuant 8-bit KV cache
+ * Constants of MetalTurboQuantModel::new (crates/ironmill-inference/src/metal/turboquant/mod.rs:221-287):
+ * rotation signs [hd] (+-1), QJL matrix [hd,hd] N(0,1), K codebook with 2^(bits-1) levels, V codebook with
+ * 2^bits levels (lloyd_max_gaussian, crates/ironmill-inference/src/turboquant/codebook.rs:20-52). */
+typedef struct im_tq im_tq;
+/* Host computation of the Lloyd-Max codebook: levels[2^n_bits], bounds[2^n_bits - 1]. */
+int im_cuda_tq_lloyd_max(int dim, int n_bits, float *levels_out_host, float *bounds_out_host);
+/* Seeded sign vector and QJL matrix (stand-in for generate_rotation_signs / generate_qjl_matrix,
+ * crates/ironmill-inference/src/turboquant/rotation.rs:13-49, whose values depend on the rand crate). */
+int im_cuda_tq_generate(int head_dim, uint64_t seed, float *signs_out_host, float *qjl_out_host);
+/* Codebook pointers may be NULL: they are then computed with im_cuda_tq_lloyd_max. */
+int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const float *signs_host, const float *qjl_host,
+                      const float *k_levels_host, const float *k_bounds_host, const float *v_levels_host,
+                      const float *v_bounds_host, im_tq **out);
+void im_cuda_tq_free(im_tq *tq);
+/* turboquant_cache_write (.../shaders/turboquant/turboquant.metal:52-170).  kv fp16 [nseq, T, nkv, hd];
+ * cache u8 [nseq, nkv, max_seq, hd]; scale / r_norms f32 [nseq, nkv, max_seq]; write position of token t of
+ * sequence s = (base_pos + pos_dev[s] + t) % max_seq (pos_dev may be NULL).  is_k selects the K form
+ * (7-bit index | QJL sign, residual norm) or the V form (8-bit index). */
+int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, void *cache_dev, float *scale_dev, float *r_norms_dev,
+                      int nseq, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, void *stream);
+/* turboquant_attention in split mode + fused_sdpa_reduce (.../turboquant/turboquant.metal:202-462,
+ * .../attention/flash_decode.metal:163-215; dispatch crates/ironmill-inference/src/metal/attention.rs:394-489).
+ * q, out fp16 [nseq, T, nh, hd]; causal length of token t = base_pos + pos_dev[s] + t + 1.
+ * num_splits 0 = chosen from the device size and the sequence length.  The split partials live in
+ * scratch memory owned by the handle (grown on demand; reserve it up front to keep this call
+ * allocation-free). */
+int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                         const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,
+                         void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
+                         int num_splits, void *stream);
+size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
+int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,630 @@
+// TurboQuant 8-bit KV cache: encoder and split-K decode attention.
+//   constants   crates/ironmill-inference/src/turboquant/codebook.rs:20-200 (Lloyd-Max codebooks),
+//               crates/ironmill-inference/src/turboquant/rotation.rs:13-49 (signs, QJL matrix),
+//               crates/ironmill-inference/src/metal/turboquant/mod.rs:221-287
+//   encode      crates/ironmill-inference/src/metal/shaders/turboquant/turboquant.metal:52-170
+//               (turboquant_cache_write) + src/shaders/turboquant_helpers.metal:128-157
+//   attention   .../turboquant/turboquant.metal:202-462 (turboquant_attention, split mode),
+//               .../attention/flash_decode.metal:163-215 (fused_sdpa_reduce)
+//
+// Storage (per sequence): K and V caches [nkv, max_seq, hd] bytes, K = 7-bit codebook index |
+// QJL sign in bit 7, V = 8-bit codebook index; f32 scale (L2 norm) per (head, position) for K
+// and V and an f32 residual norm for K: 268 bytes per (kv head, position) at hd = 128.
+//
+// The encoder reproduces the reference arithmetic operation by operation (explicit
+// round-to-nearest intrinsics, the same butterfly and tree-reduction order, sequential QJL dot
+// product), so its bytes and norms are bit-identical to the CPU restatement.
+// The attention kernel streams each K/V tile once per KV head for all query heads of its GQA
+// group, splits the sequence across CTAs and combines the splits in a reduce kernel.
+#include <math.h>
+
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+namespace im {
+
+struct Tq {
+    Device *dev = nullptr;
+    int hd = 0, n_bits = 0, k_levels = 0, v_levels = 0;
+    float *signs = nullptr, *qjl = nullptr, *k_cb = nullptr, *k_bd = nullptr, *v_cb = nullptr, *v_bd = nullptr;
+    float *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    size_t const_bytes = 0;
+};
+
+// ---------------------------------------------------------------- host: Lloyd-Max codebook
+namespace lm {
+static double poly(const double *c, int n, double x) {
+    double r = c[0];
+    for (int i = 1; i < n; i++) r = r * x + c[i];
+    return r;
+}
+static double erf_as(double x) {  // codebook.rs:187-200
+    static const double a[5] = {1.061405429, -1.453152027, 1.421413741, -0.284496736, 0.254829592};
+    const double sign = x < 0.0 ? -1.0 : 1.0;
+    x = fabs(x);
+    const double t = 1.0 / (1.0 + 0.3275911 * x);
+    const double y = 1.0 - (poly(a, 5, t) * t) * exp(-x * x);
+    return sign * y;
+}
+static double pdf(double x) { return exp(-0.5 * x * x) / sqrt(2.0 * M_PI); }
+static double cdf(double x) { return 0.5 * (1.0 + erf_as(x * M_SQRT1_2)); }
+static double quantile(double p) {  // codebook.rs:114-184
+    if (p <= 0.0) return -INFINITY;
+    if (p >= 1.0) return INFINITY;
+    const double t = p - 0.5;
+    if (fabs(t) <= 0.42) {
+        static const double n[4] = {2.5066282746310002, 18.6150006252966, 41.39119773534996, 25.44106049637689};
+        static const double d[5] = {14.382029373388, 63.690613, 84.681, 40.304, 1.0};
+        const double r = t * t;
+        return t * poly(n, 4, r) / poly(d, 5, r);
+    }
+    const double r = t < 0.0 ? p : 1.0 - p;
+    const double s = sqrt(-log(r));
+    double v;
+    if (s <= 5.0) {
+        static const double n[8] = {0.000124818987, 0.0227061845, 0.2728688, 1.3058437, 2.7580128, 2.2311569, 0.6462025, 0.001612};
+        static const double d[8] = {0.000038746, 0.00745102, 0.09234118, 0.4710441, 1.0507501, 1.0, 0.2127601, 1.0};
+        v = poly(n, 8, s - 1.6) / poly(d, 8, s - 1.6);
+    } else {
+        static const double n[8] = {0.0000000271, 0.00000342556, 0.000170717, 0.004531901, 0.06871337, 0.56419917, 1.9715909, 2.1538256};
+        static const double d[8] = {0.0000000393, 0.00000489649, 0.000230147, 0.005492439, 0.06353648, 0.3445453, 0.73741429, 1.0};
+        v = poly(n, 8, s - 5.0) / poly(d, 8, s - 5.0);
+    }
+    return t < 0.0 ? -v : v;
+}
+static double cell_mean(double sigma, double lo, double hi) {  // codebook.rs:84-104
+    const double lz = lo / sigma, hz = hi / sigma;
+    const double prob = cdf(hz) - cdf(lz);
+    if (prob < 1e-30) return isinf(lo) ? hi : (isinf(hi) ? lo : (lo + hi) / 2.0);
+    return sigma * (pdf(lz) - pdf(hz)) / prob;
+}
+static void lloyd_max(int dim, int bits, std::vector<float> &levels, std::vector<float> &bounds) {  // codebook.rs:20-52
+    const double sigma = 1.0 / sqrt((double)dim);
+    const int n = 1 << bits;
+    std::vector<double> lv(n), nl(n), bd(n > 1 ? n - 1 : 0);
+    for (int i = 0; i < n; i++) lv[i] = sigma * quantile(((double)i + 0.5) / (double)n);
+    for (int it = 0; it < 200; it++) {
+        for (int i = 0; i + 1 < n; i++) bd[i] = (lv[i] + lv[i + 1]) / 2.0;
+        double delta = 0.0;
+        for (int i = 0; i < n; i++) {
+            nl[i] = cell_mean(sigma, i == 0 ? -INFINITY : bd[i - 1], i == n - 1 ? INFINITY : bd[i]);
+            delta = fmax(delta, fabs(lv[i] - nl[i]));
+        }
+        lv = nl;
+        if (delta < 1e-10) break;
+    }
+    levels.resize(n);
+    bounds.resize(n - 1);
+    for (int i = 0; i < n; i++) levels[i] = (float)lv[i];
+    for (int i = 0; i + 1 < n; i++) bounds[i] = (float)((lv[i] + lv[i + 1]) / 2.0);
+}
+}  // namespace lm
+
+// ---------------------------------------------------------------- device helpers
+// In-place randomized Hadamard rotation of NV vectors of length hd held in shared memory
+// (x[v * pitch + d]); all threads of the CTA must call it.  Plain float arithmetic.
+template <int NV>
+__device__ __forceinline__ void hadamard_block(float *x, int pitch, const float *__restrict__ signs, int hd) {
+    for (int i = threadIdx.x; i < NV * hd; i += blockDim.x) {
+        const int v = i / hd, d = i % hd;
+        x[v * pitch + d] *= signs[d];
+    }
+    __syncthreads();
+    for (int step = 1; step < hd; step <<= 1) {
+        for (int i = threadIdx.x; i < NV * (hd / 2); i += blockDim.x) {
+            const int v = i / (hd / 2), e = i % (hd / 2);
+            const int j = (e / step) * (2 * step) + (e % step);
+            float *p = x + v * pitch;
+            const float a = p[j], b = p[j + step];
+            p[j] = a + b;
+            p[j + step] = a - b;
+        }
+        __syncthreads();
+    }
+    const float scale = 1.0f / sqrtf((float)hd);
+    for (int i = threadIdx.x; i < NV * hd; i += blockDim.x) {
+        const int v = i / hd, d = i % hd;
+        x[v * pitch + d] *= signs[d] * scale;
+    }
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------- encode (bit-exact)
+// grid (nkv, nseq*T), hd threads.
+__global__ void tq_encode_kernel(const __half *__restrict__ kv, const float *__restrict__ signs, const float *__restrict__ cb,
+                                 const float *__restrict__ bounds, const float *__restrict__ qjl, int is_k, int n_levels,
+                                 uint8_t *__restrict__ cache, float *__restrict__ scale_buf, float *__restrict__ r_norms, int nkv, int hd,
+                                 int max_seq, int base_pos, const int *__restrict__ pos_dev, int T) {
+    extern __shared__ float sh[];
+    float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
+    const int d = threadIdx.x, h = blockIdx.x, st = blockIdx.y;
+    const int seq = st / T, t = st % T;
+    const int pos = (base_pos + (pos_dev ? pos_dev[seq] : 0) + t) % max_seq;
+    const float sg = signs[d];
+    xs[d] = __fmul_rn(__half2float(kv[((size_t)st * nkv + h) * hd + d]), sg);
+    __syncthreads();
+    for (int step = 1; step < hd; step <<= 1) {
+        if (d < hd / 2) {
+            const int j = (d / step) * (2 * step) + (d % step);
+            const float a = xs[j], b = xs[j + step];
+            xs[j] = __fadd_rn(a, b);
+            xs[j + step] = __fsub_rn(a, b);
+        }
+        __syncthreads();
+    }
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    const float x = __fmul_rn(xs[d], __fmul_rn(sg, scale));
+    red[d] = __fmul_rn(x, x);
+    __syncthreads();
+    for (int s = hd / 2; s > 0; s >>= 1) {
+        if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
+        __syncthreads();
+    }
+    const float norm = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+    const size_t row = ((size_t)seq * nkv + h) * max_seq + pos;
+    if (d == 0) scale_buf[row] = norm;
+    const float inv = __fdiv_rn(1.0f, fmaxf(norm, 1e-10f));
+    const float u = __fmul_rn(x, inv);
+    // index = number of boundaries <= u (boundaries ascending): binary search
+    int lo = 0, hi = n_levels - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (u >= bounds[mid]) lo = mid + 1; else hi = mid;
+    }
+    unsigned byte = (unsigned)lo;
+    if (is_k) {
+        const float r = __fsub_rn(u, cb[lo]);
+        __syncthreads();  // everyone has read red[0]
+        res[d] = r;
+        red[d] = __fmul_rn(r, r);
+        __syncthreads();
+        for (int s = hd / 2; s > 0; s >>= 1) {
+            if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
+            __syncthreads();
+        }
+        if (d == 0) r_norms[row] = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+        float proj = 0.0f;
+        const float *srow = qjl + (size_t)d * hd;
+        for (int k = 0; k < hd; k++) proj = __fadd_rn(proj, __fmul_rn(srow[k], res[k]));
+        if (proj >= 0.0f) byte |= 0x80u;
+    }
+    cache[row * hd + d] = (uint8_t)byte;
+}
+
+// ---------------------------------------------------------------- attention
+constexpr int kTile = 32;         // positions per tile
+constexpr int kAttnThreads = 128;  // 4 warps; thread d owns output dim d (hd = 128)
+constexpr int kHd = 128;
+constexpr int kPitchB = 132;      // bytes per tile row: 33 words -> conflict-free 32-bit reads
+constexpr int kQPitch = 132;      // floats per query vector: +1 word per 32 -> conflict-free
+
+struct AttnParams {
+    const __half *q;         // [nseq*T, nh, hd]
+    const uint8_t *kc, *vc;  // [nseq, nkv, max_seq, hd]
+    const float *ks, *vs, *krn;  // [nseq, nkv, max_seq]
+    const float *signs, *qjl, *k_cb, *v_cb;
+    float *po, *pm, *pl;     // partials [nseq*T, nh, splits] x (hd | 1 | 1)
+    float attn_scale, qjl_factor;
+    int nh, nkv, max_seq, base_pos, T, splits;
+    const int *pos_dev;
+};
+
+__device__ __forceinline__ int qidx(int d) { return d + (d >> 5); }
+
+template <int GQ>
+__global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnParams p) {
+    __shared__ float qr[GQ * kQPitch];
+    __shared__ float sq[GQ * kQPitch];
+    __shared__ float cbk[128];
+    __shared__ float cbv[256];
+    __shared__ __align__(16) uint8_t ktile[kTile * kPitchB];
+    __shared__ __align__(16) uint8_t vtile[kTile * kPitchB];
+    __shared__ float t_ks[kTile], t_rw[kTile], t_vs[kTile];
+    __shared__ float sc[GQ * kTile];
+    __shared__ float s_m[GQ], s_l[GQ], s_corr[GQ];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.x, st = blockIdx.y, split = blockIdx.z;
+    const int seq = st / p.T, t = st % p.T;
+    const int seq_len = p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1;
+    const int chunk = (seq_len + p.splits - 1) / p.splits;
+    const int r0 = split * chunk, r1 = min(r0 + chunk, seq_len);
+    const int h0 = kvh * GQ;
+
+    if (r0 >= r1) {  // empty split: neutral partial
+        for (int g = 0; g < GQ; g++) {
+            const size_t pi = ((size_t)st * p.nh + h0 + g) * p.splits + split;
+            p.po[pi * kHd + tid] = 0.0f;
+            if (tid == 0) {
+                p.pm[pi] = -INFINITY;
+                p.pl[pi] = 0.0f;
+            }
+        }
+        return;
+    }
+
+    // codebooks, rotated queries, S * q
+    cbk[tid] = p.k_cb[tid];
+    cbv[tid] = p.v_cb[tid];
+    cbv[tid + 128] = p.v_cb[tid + 128];
+#pragma unroll
+    for (int g = 0; g < GQ; g++) qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
+    if (tid < GQ) {
+        s_m[tid] = -INFINITY;
+        s_l[tid] = 0.0f;
+    }
+    __syncthreads();
+    hadamard_block<GQ>(qr, kQPitch, p.signs, kHd);
+    {
+        float acc[GQ];
+#pragma unroll
+        for (int g = 0; g < GQ; g++) acc[g] = 0.0f;
+        const float4 *srow = reinterpret_cast<const float4 *>(p.qjl + (size_t)tid * kHd);
+        for (int k4 = 0; k4 < kHd / 4; k4++) {
+            const float4 s4 = srow[k4];
+#pragma unroll
+            for (int g = 0; g < GQ; g++) {
+                const float *qv = qr + g * kQPitch + k4 * 4;
+                acc[g] += s4.x * qv[0] + s4.y * qv[1] + s4.z * qv[2] + s4.w * qv[3];
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < GQ; g++) sq[g * kQPitch + qidx(tid)] = acc[g];
+        // move the rotated queries to the padded layout as well
+        float tmp[GQ];
+#pragma unroll
+        for (int g = 0; g < GQ; g++) tmp[g] = qr[g * kQPitch + tid];
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < GQ; g++) qr[g * kQPitch + qidx(tid)] = tmp[g];
+    }
+    __syncthreads();
+
+    float o[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; g++) o[g] = 0.0f;
+
+    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    for (int ts = r0; ts < r1; ts += kTile) {
+        const int nt = min(kTile, r1 - ts);
+        // ---- load K and V tiles: 32 rows x 128 bytes each, 32 bytes per thread ----
+        {
+            const int pr = tid >> 2, part = tid & 3;
+            uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
+            if (pr < nt) {
+                const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
+                const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
+                k0 = ldg_stream_v4(ksrc);
+                k1 = ldg_stream_v4(ksrc + 1);
+                v0 = ldg_stream_v4(vsrc);
+                v1 = ldg_stream_v4(vsrc + 1);
+            }
+            uint32_t *kd = reinterpret_cast<uint32_t *>(ktile + pr * kPitchB + part * 32);
+            uint32_t *vd = reinterpret_cast<uint32_t *>(vtile + pr * kPitchB + part * 32);
+            kd[0] = k0.x; kd[1] = k0.y; kd[2] = k0.z; kd[3] = k0.w; kd[4] = k1.x; kd[5] = k1.y; kd[6] = k1.z; kd[7] = k1.w;
+            vd[0] = v0.x; vd[1] = v0.y; vd[2] = v0.z; vd[3] = v0.w; vd[4] = v1.x; vd[5] = v1.y; vd[6] = v1.z; vd[7] = v1.w;
+            if (tid < kTile) {
+                const bool ok = tid < nt;
+                const float ksv = ok ? p.ks[head_base + ts + tid] : 0.0f;
+                t_ks[tid] = ksv;
+                t_rw[tid] = ok ? p.krn[head_base + ts + tid] * p.qjl_factor : 0.0f;
+                t_vs[tid] = ok ? p.vs[head_base + ts + tid] : 0.0f;
+            }
+        }
+        __syncthreads();
+
+        // ---- scores: warp w owns positions 8w..8w+7, 4 lanes per position (32 dims each) ----
+        {
+            const int pl = lane >> 2, dq = lane & 3, pp = warp * 8 + pl;
+            float a1[GQ], a2[GQ];
+#pragma unroll
+            for (int g = 0; g < GQ; g++) a1[g] = a2[g] = 0.0f;
+            const uint32_t *krow = reinterpret_cast<const uint32_t *>(ktile + pp * kPitchB + dq * 32);
+#pragma unroll
+            for (int jw = 0; jw < 8; jw++) {
+                const uint32_t w4 = krow[jw];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t b = (w4 >> (8 * e)) & 0xffu;
+                    const float kc = cbk[b & 0x7fu];
+                    const float sgn = (b & 0x80u) ? 1.0f : -1.0f;
+                    const int di = dq * 33 + jw * 4 + e;  // padded index of dim dq*32 + jw*4 + e
+#pragma unroll
+                    for (int g = 0; g < GQ; g++) {
+                        a1[g] = fmaf(qr[g * kQPitch + di], kc, a1[g]);
+                        a2[g] = fmaf(sq[g * kQPitch + di], sgn, a2[g]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < GQ; g++) {
+                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 1);
+                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 2);
+                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 1);
+                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 2);
+            }
+            if (dq == 0) {
+                const float ksv = t_ks[pp], rw = t_rw[pp];
+#pragma unroll
+                for (int g = 0; g < GQ; g++)
+                    sc[g * kTile + pp] = pp < nt ? p.attn_scale * (ksv * (a1[g] + rw * a2[g])) : -INFINITY;
+            }
+        }
+        __syncthreads();
+
+        // ---- online softmax: one warp per query head, lane = position ----
+        for (int g = warp; g < GQ; g += kAttnThreads / 32) {
+            const float s = sc[g * kTile + lane];
+            const float tm = warp_max(s);
+            const float m_old = s_m[g];
+            const float m_new = fmaxf(m_old, tm);
+            const float w = lane < nt ? __expf(s - m_new) : 0.0f;
+            const float tsum = warp_sum(w);
+            sc[g * kTile + lane] = w * t_vs[lane];
+            if (lane == 0) {
+                const float corr = __expf(m_old - m_new);
+                s_corr[g] = corr;
+                s_m[g] = m_new;
+                s_l[g] = s_l[g] * corr + tsum;
+            }
+        }
+        __syncthreads();
+
+        // ---- weighted V: thread d accumulates output dim d for every head of the group ----
+#pragma unroll
+        for (int g = 0; g < GQ; g++) o[g] *= s_corr[g];
+        for (int pp = 0; pp < nt; pp++) {
+            const float v = cbv[vtile[pp * kPitchB + tid]];
+#pragma unroll
+            for (int g = 0; g < GQ; g++) o[g] = fmaf(sc[g * kTile + pp], v, o[g]);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int g = 0; g < GQ; g++) {
+        const size_t pi = ((size_t)st * p.nh + h0 + g) * p.splits + split;
+        p.po[pi * kHd + tid] = o[g];
+        if (tid == 0) {
+            p.pm[pi] = s_m[g];
+            p.pl[pi] = s_l[g];
+        }
+    }
+}
+
+// Combine the splits of one (token, head), normalise, rotate back, write fp16.
+// The inverse rotation is linear, so applying it once after the combination equals the
+// reference's per-split rotation up to float rounding.  grid (nh, nseq*T), hd threads.
+__global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict__ po, const float *__restrict__ pm,
+                                                        const float *__restrict__ pl, const float *__restrict__ signs,
+                                                        __half *__restrict__ out, int nh, int splits) {
+    __shared__ float x[kHd];
+    const int d = threadIdx.x;
+    const size_t base = ((size_t)blockIdx.y * nh + blockIdx.x) * splits;
+    float gm = -INFINITY;
+    for (int s = 0; s < splits; s++) gm = fmaxf(gm, pm[base + s]);
+    float acc = 0.0f, lsum = 0.0f;
+    for (int s = 0; s < splits; s++) {
+        const float m = pm[base + s];
+        const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
+        lsum += pl[base + s] * corr;
+        acc += po[(base + s) * kHd + d] * corr;
+    }
+    x[d] = acc / fmaxf(lsum, 1e-10f);
+    __syncthreads();
+    hadamard_block<1>(x, kHd, signs, kHd);
+    out[((size_t)blockIdx.y * nh + blockIdx.x) * kHd + d] = __float2half_rn(x[d]);
+}
+
+}  // namespace im
+
+using namespace im;
+struct im_tq : im::Tq {};
+
+IM_EXPORT int im_cuda_tq_lloyd_max(int dim, int n_bits, float *levels_out_host, float *bounds_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(dim > 0 && n_bits >= 1 && n_bits <= 8 && levels_out_host && bounds_out_host, "bad argument");
+    std::vector<float> lv, bd;
+    lm::lloyd_max(dim, n_bits, lv, bd);
+    for (size_t i = 0; i < lv.size(); i++) levels_out_host[i] = lv[i];
+    for (size_t i = 0; i < bd.size(); i++) bounds_out_host[i] = bd[i];
+    return IM_OK;
+    IM_GUARD_END
+}
+
+// Seeded stand-in for the reference's StdRng draws (rotation.rs:13-49): a +-1 sign vector and an
+// N(0,1) matrix by Box-Muller over a splitmix64 stream.  Any such pair is algorithmically valid;
+// the reference's own values depend on the `rand` crate's generator.
+IM_EXPORT int im_cuda_tq_generate(int head_dim, uint64_t seed, float *signs_out_host, float *qjl_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(head_dim > 0 && signs_out_host && qjl_out_host, "bad argument");
+    auto next = [](uint64_t &s) {
+        s += 0x9E3779B97F4A7C15ull;
+        uint64_t z = s;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        return z ^ (z >> 31);
+    };
+    uint64_t s1 = seed;
+    for (int i = 0; i < head_dim; i++) signs_out_host[i] = (next(s1) >> 63) ? 1.0f : -1.0f;
+    uint64_t s2 = seed + 1;
+    const size_t n = (size_t)head_dim * head_dim;
+    for (size_t i = 0; i < n;) {
+        double u1 = (double)(next(s2) >> 11) * (1.0 / 9007199254740992.0);
+        const double u2 = (double)(next(s2) >> 11) * (1.0 / 9007199254740992.0);
+        if (u1 < 1e-300) u1 = 1e-300;
+        const double r = sqrt(-2.0 * log(u1)), th = 2.0 * M_PI * u2;
+        qjl_out_host[i++] = (float)(r * cos(th));
+        if (i < n) qjl_out_host[i++] = (float)(r * sin(th));
+    }
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT void im_cuda_tq_free(im_tq *tq) {
+    if (!tq) return;
+    const size_t hd = tq->hd;
+    dev_free(tq->dev, tq->signs, hd * 4);
+    dev_free(tq->dev, tq->qjl, hd * hd * 4);
+    dev_free(tq->dev, tq->k_cb, (size_t)tq->k_levels * 4);
+    dev_free(tq->dev, tq->k_bd, (size_t)tq->k_levels * 4);
+    dev_free(tq->dev, tq->v_cb, (size_t)tq->v_levels * 4);
+    dev_free(tq->dev, tq->v_bd, (size_t)tq->v_levels * 4);
+    dev_free(tq->dev, tq->scratch, tq->scratch_bytes);
+    delete tq;
+}
+
+IM_EXPORT int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const float *signs_host, const float *qjl_host,
+                                const float *k_levels_host, const float *k_bounds_host, const float *v_levels_host,
+                                const float *v_bounds_host, im_tq **out) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(dev && out, "bad argument");
+    *out = nullptr;
+    IM_REQUIRE(n_bits == 8, "only the 8-bit TurboQuant cache is built (n_bits = %d)", n_bits);
+    IM_REQUIRE(head_dim >= 32 && head_dim <= 1024 && (head_dim & (head_dim - 1)) == 0, "head_dim must be a power of two in 32..1024");
+    IM_REQUIRE(signs_host && qjl_host, "signs and QJL matrix are required");
+    IM_CUDA_CHECK(cudaSetDevice(dev->ordinal));
+    std::vector<float> kl, kb, vl, vb;
+    if (!k_levels_host || !k_bounds_host) {
+        lm::lloyd_max(head_dim, n_bits - 1, kl, kb);
+        k_levels_host = kl.data();
+        k_bounds_host = kb.data();
+    }
+    if (!v_levels_host || !v_bounds_host) {
+        lm::lloyd_max(head_dim, n_bits, vl, vb);
+        v_levels_host = vl.data();
+        v_bounds_host = vb.data();
+    }
+    im_tq *tq = new im_tq();
+    tq->dev = dev;
+    tq->hd = head_dim;
+    tq->n_bits = n_bits;
+    tq->k_levels = 1 << (n_bits - 1);
+    tq->v_levels = 1 << n_bits;
+    const size_t hd = head_dim;
+    struct Up { float **dst; const float *src; size_t n, alloc; };
+    Up ups[] = {{&tq->signs, signs_host, hd, hd}, {&tq->qjl, qjl_host, hd * hd, hd * hd},
+                {&tq->k_cb, k_levels_host, (size_t)tq->k_levels, (size_t)tq->k_levels},
+                {&tq->k_bd, k_bounds_host, (size_t)tq->k_levels - 1, (size_t)tq->k_levels},
+                {&tq->v_cb, v_levels_host, (size_t)tq->v_levels, (size_t)tq->v_levels},
+                {&tq->v_bd, v_bounds_host, (size_t)tq->v_levels - 1, (size_t)tq->v_levels}};
+    for (auto &u : ups) {
+        int rc = dev_malloc(dev, (void **)u.dst, u.alloc * 4);
+        if (rc == IM_OK && cudaMemcpy(*u.dst, u.src, u.n * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            rc = fail(IM_ERR_CUDA, "constant upload failed");
+        if (rc != IM_OK) {
+            im_cuda_tq_free(tq);
+            return rc;
+        }
+        tq->const_bytes += u.alloc * 4;
+    }
+    *out = tq;
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, void *cache_dev, float *scale_dev, float *r_norms_dev,
+                                int nseq, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(tq && kv_dev && cache_dev && scale_dev, "bad argument");
+    IM_REQUIRE(!is_k || r_norms_dev, "the K cache needs a residual-norm buffer");
+    IM_REQUIRE(nseq >= 0 && nkv > 0 && max_seq > 0 && base_pos >= 0 && T >= 0, "bad shape");
+    if (nseq == 0 || T == 0) return IM_OK;
+    dim3 grid(nkv, nseq * T);
+    const int hd = tq->hd;
+    tq_encode_kernel<<<grid, hd, 3 * hd * sizeof(float), as_stream(stream)>>>(
+        static_cast<const __half *>(kv_dev), tq->signs, is_k ? tq->k_cb : tq->v_cb, is_k ? tq->k_bd : tq->v_bd, tq->qjl, is_k,
+        is_k ? tq->k_levels : tq->v_levels, static_cast<uint8_t *>(cache_dev), scale_dev, r_norms_dev, nkv, hd, max_seq, base_pos,
+        pos_dev, T);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits) {
+    return (size_t)nseq * T * nh * splits * (head_dim + 2) * sizeof(float);
+}
+
+IM_EXPORT int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(tq, "bad argument");
+    if (bytes <= tq->scratch_bytes) return IM_OK;
+    IM_CUDA_CHECK(cudaSetDevice(tq->dev->ordinal));
+    IM_CUDA_CHECK(cudaDeviceSynchronize());  // earlier launches may still use the old buffer
+    dev_free(tq->dev, tq->scratch, tq->scratch_bytes);
+    tq->scratch = nullptr;
+    tq->scratch_bytes = 0;
+    int rc = dev_malloc(tq->dev, (void **)&tq->scratch, bytes);
+    if (rc != IM_OK) return rc;
+    tq->scratch_bytes = bytes;
+    return IM_OK;
+    IM_GUARD_END
+}
+
+namespace im {
+int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
+    const int ctas = nseq * T * nkv;
+    int s = (2 * dev->sm_count + ctas - 1) / ctas;
+    const int by_len = (seq_len + 2 * kTile - 1) / (2 * kTile);  // at least two tiles per split
+    if (s > by_len) s = by_len;
+    if (s > 128) s = 128;
+    return s < 1 ? 1 : s;
+}
+
+int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,
+                        const float *vs, const float *krn, float attn_scale, __half *out, int nseq, int nh, int nkv, int max_seq,
+                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st) {
+    AttnParams p{};
+    p.q = q; p.kc = kc; p.vc = vc; p.ks = ks; p.vs = vs; p.krn = krn;
+    p.signs = tq->signs; p.qjl = tq->qjl; p.k_cb = tq->k_cb; p.v_cb = tq->v_cb;
+    const size_t rows = (size_t)nseq * T * nh * splits;
+    p.po = scratch;
+    p.pm = scratch + rows * kHd;
+    p.pl = p.pm + rows;
+    p.attn_scale = attn_scale;
+    p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)tq->hd;
+    p.nh = nh; p.nkv = nkv; p.max_seq = max_seq; p.base_pos = base_pos; p.T = T; p.splits = splits; p.pos_dev = pos_dev;
+    dim3 grid(nkv, nseq * T, splits);
+    switch (nh / nkv) {
+        case 1: tq_attention_kernel<1><<<grid, kAttnThreads, 0, st>>>(p); break;
+        case 2: tq_attention_kernel<2><<<grid, kAttnThreads, 0, st>>>(p); break;
+        case 4: tq_attention_kernel<4><<<grid, kAttnThreads, 0, st>>>(p); break;
+        case 8: tq_attention_kernel<8><<<grid, kAttnThreads, 0, st>>>(p); break;
+        default: return fail(IM_ERR_INVALID, "query heads per KV head must be 1, 2, 4 or 8 (got %d/%d)", nh, nkv);
+    }
+    IM_CUDA_CHECK(cudaGetLastError());
+    dim3 rgrid(nh, nseq * T);
+    tq_reduce_kernel<<<rgrid, kHd, 0, st>>>(p.po, p.pm, p.pl, tq->signs, out, nh, splits);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+}
+}  // namespace im
+
+IM_EXPORT int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                   const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,
+                                   void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
+                                   int num_splits, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(tq && q_dev && k_cache_dev && v_cache_dev && k_scale_dev && v_scale_dev && k_rnorm_dev && out_dev, "bad argument");
+    IM_REQUIRE(tq->hd == kHd, "the attention kernel is built for head_dim 128 (got %d)", tq->hd);
+    IM_REQUIRE(nkv > 0 && nh % nkv == 0, "nh must be a multiple of nkv");
+    IM_REQUIRE(nseq >= 0 && T >= 0 && max_seq > 0 && base_pos >= 0, "bad shape");
+    if (nseq == 0 || T == 0) return IM_OK;
+    if (!pos_dev && base_pos + T > max_seq)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", base_pos, T, max_seq);
+    int splits = num_splits > 0 ? num_splits : tq_auto_splits(tq->dev, nseq, T, nkv, base_pos + T);
+    IM_REQUIRE(splits <= 1024, "too many splits");
+    const size_t need = im_cuda_tq_scratch_bytes(nseq, T, nh, kHd, splits);
+    if (need > tq->scratch_bytes) {
+        int rc = im_cuda_tq_reserve_scratch(tq, need);
+        if (rc != IM_OK) return rc;
+    }
+    return tq_attention_launch(tq, tq->scratch, static_cast<const __half *>(q_dev), static_cast<const uint8_t *>(k_cache_dev),
+                               static_cast<const uint8_t *>(v_cache_dev), k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale,
+                               static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream));
+    IM_GUARD_END
+}

@@ -205,3 +205,113 @@ def matvec_f16(w: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     y = torch.empty((B, N), dtype=torch.float16, device=x.device)
     check(lib().im_cuda_matvec_f16(vp(w), vp(x), vp(y), C.c_int(N), C.c_int(K), C.c_int(B), _stream()))
     return y
+
+
+# ---------------------------------------------------------------- norms / embedding / RoPE
+def _h16(x):
+    assert x.is_cuda and x.dtype == torch.float16 and x.is_contiguous()
+    return x
+
+
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    H = x.shape[-1]
+    out = torch.empty_like(_h16(x))
+    check(lib().im_cuda_rms_norm(vp(x), vp(_h16(gamma)), vp(out), C.c_int(H), C.c_int(x.numel() // H), C.c_float(eps), _stream()))
+    return out
+
+
+def fused_residual_rms_norm(a, b, gamma, eps):
+    H = a.shape[-1]
+    normed, residual = torch.empty_like(_h16(a)), torch.empty_like(a)
+    check(lib().im_cuda_fused_residual_rms_norm(vp(a), vp(_h16(b)), vp(_h16(gamma)), vp(normed), vp(residual), C.c_int(H),
+                                                C.c_int(a.numel() // H), C.c_float(eps), _stream()))
+    return normed, residual
+
+
+def residual_add(a, b):
+    out = torch.empty_like(_h16(a))
+    check(lib().im_cuda_residual_add(vp(a), vp(_h16(b)), vp(out), C.c_size_t(a.numel()), _stream()))
+    return out
+
+
+def embedding_norm(tokens: torch.Tensor, table: torch.Tensor, gamma: torch.Tensor, eps: float, embed_scale: float = 1.0):
+    assert tokens.is_cuda and tokens.dtype in (torch.int32, torch.uint32) and tokens.is_contiguous()
+    vocab, H = _h16(table).shape
+    T = tokens.numel()
+    normed = torch.empty((T, H), dtype=torch.float16, device=table.device)
+    raw = torch.empty_like(normed)
+    check(lib().im_cuda_embedding_norm(vp(tokens), vp(table), vp(_h16(gamma)), vp(normed), vp(raw), C.c_int(H), C.c_int(T),
+                                       C.c_uint32(vocab), C.c_float(eps), C.c_float(embed_scale), _stream()))
+    return normed, raw
+
+
+def rope_table(head_dim: int, max_pos: int, theta: float, rotary_dim: int | None = None, device="cuda"):
+    cos = torch.empty((max_pos, head_dim // 2), dtype=torch.float16, device=device)
+    sin = torch.empty_like(cos)
+    check(lib().im_cuda_rope_table(C.c_int(head_dim), C.c_int(max_pos), C.c_double(theta), C.c_int(rotary_dim or 0), vp(cos), vp(sin)))
+    return cos, sin
+
+
+def qk_norm_rope_(q, k, qw, kw, cos, sin, nh, nkv, hd, seq_offset, eps, rotary_dim=None):
+    """In place on q [T,nh,hd] and k [T,nkv,hd]."""
+    T = _h16(q).numel() // (nh * hd)
+    check(lib().im_cuda_qk_norm_rope(vp(q), vp(_h16(k)), vp(_h16(qw)), vp(_h16(kw)), vp(cos), vp(sin), C.c_int(nh), C.c_int(nkv),
+                                     C.c_int(hd), C.c_int(rotary_dim or hd), C.c_int(seq_offset), C.c_int(T), C.c_float(eps), _stream()))
+
+
+def rope_(qk, cos, sin, heads, hd, seq_offset):
+    T = _h16(qk).numel() // (heads * hd)
+    check(lib().im_cuda_rope(vp(qk), vp(cos), vp(sin), C.c_int(heads), C.c_int(hd), C.c_int(seq_offset), C.c_int(T), _stream()))
+
+
+# ---------------------------------------------------------------- TurboQuant
+def tq_lloyd_max(dim: int, n_bits: int):
+    levels = np.zeros(1 << n_bits, dtype=np.float32)
+    bounds = np.zeros((1 << n_bits) - 1, dtype=np.float32)
+    check(lib().im_cuda_tq_lloyd_max(C.c_int(dim), C.c_int(n_bits), vp(levels), vp(bounds)))
+    return levels, bounds
+
+
+def tq_generate(head_dim: int, seed: int):
+    signs = np.zeros(head_dim, dtype=np.float32)
+    qjl = np.zeros((head_dim, head_dim), dtype=np.float32)
+    check(lib().im_cuda_tq_generate(C.c_int(head_dim), C.c_uint64(seed), vp(signs), vp(qjl)))
+    return signs, qjl
+
+
+class TurboQuant:
+    """MetalTurboQuantModel counterpart (crates/ironmill-inference/src/metal/turboquant/mod.rs:221-287)."""
+
+    def __init__(self, dev: Device, head_dim: int, n_bits: int, signs: np.ndarray, qjl: np.ndarray,
+                 k_levels=None, k_bounds=None, v_levels=None, v_bounds=None):
+        self.dev, self.head_dim, self.n_bits = dev, head_dim, n_bits
+        self.handle = C.c_void_p()
+        f = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float32)  # noqa: E731
+        self._keep = [f(signs), f(qjl), f(k_levels), f(k_bounds), f(v_levels), f(v_bounds)]
+        check(lib().im_cuda_tq_create(dev.handle, C.c_int(head_dim), C.c_int(n_bits), *[vp(a) for a in self._keep],
+                                      C.byref(self.handle)))
+
+    def encode(self, kv, is_k, cache, scale, r_norms, nkv, max_seq, base_pos, nseq=1, pos_dev=None):
+        T = _h16(kv).numel() // (nseq * nkv * self.head_dim)
+        check(lib().im_cuda_tq_encode(self.handle, vp(kv), C.c_int(int(is_k)), vp(cache), vp(scale), vp(r_norms), C.c_int(nseq),
+                                      C.c_int(nkv), C.c_int(max_seq), C.c_int(base_pos), vp(pos_dev), C.c_int(T), _stream()))
+
+    def attention(self, q, k_cache, v_cache, k_scale, v_scale, k_rnorm, attn_scale, nh, nkv, max_seq, base_pos, nseq=1,
+                  pos_dev=None, num_splits=0):
+        T = _h16(q).numel() // (nseq * nh * self.head_dim)
+        out = torch.empty_like(q)
+        check(lib().im_cuda_tq_attention(self.handle, vp(q), vp(k_cache), vp(v_cache), vp(k_scale), vp(v_scale), vp(k_rnorm),
+                                         C.c_float(attn_scale), vp(out), C.c_int(nseq), C.c_int(nh), C.c_int(nkv), C.c_int(max_seq),
+                                         C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_int(num_splits), _stream()))
+        return out
+
+    def free(self):
+        if self.handle:
+            lib().im_cuda_tq_free(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

@@ -1,0 +1,155 @@
+"""TurboQuant 8-bit KV: encoder bit-exact against the CPU oracle, decode attention within
+tolerance (fp16 output, max abs error <= 2e-3 of the largest reference magnitude)."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests import helpers as H
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def _c(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from ironmill_b200 import ops
+    return ops.Device(0)
+
+
+@pytest.fixture(scope="module")
+def tqc():
+    return orc.TqConstants(128, 8, seed=42)
+
+
+@pytest.fixture(scope="module")
+def tq(dev, tqc):
+    from ironmill_b200 import ops
+    return ops.TurboQuant(dev, 128, 8, tqc.signs, tqc.qjl, tqc.k_levels, tqc.k_bounds, tqc.v_levels, tqc.v_bounds)
+
+
+def test_library_codebook_equals_oracle():
+    from ironmill_b200 import ops
+    for bits in (3, 4, 7, 8):
+        lv, bd = ops.tq_lloyd_max(128, bits)
+        rl, rb = orc.lloyd_max_gaussian(128, bits)
+        assert (lv.view(np.uint32) == rl.view(np.uint32)).all() and (bd.view(np.uint32) == rb.view(np.uint32)).all()
+    signs, qjl = ops.tq_generate(128, 42)
+    assert set(np.unique(signs)) <= {-1.0, 1.0} and abs(float(qjl.mean())) < 0.05 and abs(float(qjl.std()) - 1) < 0.05
+
+
+def _encode_both(tq, tqc, kv, is_k, nkv, max_seq, base, nseq=1):
+    T = kv.size // (nseq * nkv * 128)
+    cache = np.zeros((nseq, nkv, max_seq, 128), dtype=np.uint8)
+    scale = np.zeros((nseq, nkv, max_seq), dtype=np.float32)
+    rn = np.zeros((nseq, nkv, max_seq), dtype=np.float32)
+    for s in range(nseq):
+        orc.tq_encode(kv.reshape(nseq, T, nkv, 128)[s], tqc, is_k, cache[s], scale[s], rn[s], nkv, max_seq, base)
+    cd, sd, rd = _c(np.zeros_like(cache)), _c(np.zeros_like(scale)), _c(np.zeros_like(rn))
+    tq.encode(_c(kv), is_k, cd, sd, rd, nkv, max_seq, base, nseq=nseq)
+    return (cache, scale, rn), (cd.cpu().numpy(), sd.cpu().numpy(), rd.cpu().numpy())
+
+
+@pytest.mark.parametrize("is_k", [True, False])
+@pytest.mark.parametrize("T,base,max_seq,nseq", [(1, 0, 64, 1), (5, 3, 64, 1), (33, 60, 64, 1), (2, 10, 32, 3)])
+def test_encode_bit_exact(tq, tqc, is_k, T, base, max_seq, nseq):
+    nkv = 8
+    kv = H.make_x(nseq * T, nkv * 128, seed=T + base, name="kv")
+    (c, s, r), (gc, gs, gr) = _encode_both(tq, tqc, kv, is_k, nkv, max_seq, base, nseq)
+    assert (gc == c).all(), "cache bytes differ"
+    assert (gs.view(np.uint32) == s.view(np.uint32)).all(), "scales differ"
+    if is_k:
+        assert (gr.view(np.uint32) == r.view(np.uint32)).all(), "residual norms differ"
+
+
+def test_encode_edge_values(tq, tqc):
+    kv = np.zeros((4, 8 * 128), dtype=np.float16)
+    kv[1] = 1.0
+    kv[2, ::7] = np.float16(65504.0)
+    kv[3] = H.make_x(1, 8 * 128, 3)[0] * np.float16(1e-4)
+    for is_k in (True, False):
+        (c, s, r), (gc, gs, gr) = _encode_both(tq, tqc, kv, is_k, 8, 16, 0)
+        assert (gc == c).all() and (gs.view(np.uint32) == s.view(np.uint32)).all() and (gr.view(np.uint32) == r.view(np.uint32)).all()
+
+
+def _fill_cache(tq, tqc, nkv, max_seq, n, seed, nseq=1):
+    k = H.make_x(nseq * n, nkv * 128, seed, "K")
+    v = H.make_x(nseq * n, nkv * 128, seed, "V")
+    kc, ks, kr = [_c(np.zeros(s, dtype=d)) for s, d in (((nseq, nkv, max_seq, 128), np.uint8), ((nseq, nkv, max_seq), np.float32), ((nseq, nkv, max_seq), np.float32))]
+    vc, vs, vr = [_c(np.zeros(s, dtype=d)) for s, d in (((nseq, nkv, max_seq, 128), np.uint8), ((nseq, nkv, max_seq), np.float32), ((nseq, nkv, max_seq), np.float32))]
+    tq.encode(_c(k), True, kc, ks, kr, nkv, max_seq, 0, nseq=nseq)
+    tq.encode(_c(v), False, vc, vs, vr, nkv, max_seq, 0, nseq=nseq)
+    return kc, ks, kr, vc, vs
+
+
+@pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 8), (8, 8)])
+@pytest.mark.parametrize("ctx", [1, 31, 32, 33, 255, 256, 257, 1024])
+def test_decode_attention(tq, tqc, nh, nkv, ctx):
+    max_seq = 1100
+    kc, ks, kr, vc, vs = _fill_cache(tq, tqc, nkv, max_seq, ctx, seed=ctx)
+    q = H.make_x(1, nh * 128, seed=ctx, name="q")
+    scale = 1.0 / np.sqrt(128.0)
+    ref = orc.tq_attention(q, kc.cpu().numpy(), vc.cpu().numpy(), tqc, ks.cpu().numpy(), vs.cpu().numpy(), kr.cpu().numpy(),
+                           scale, nh, nkv, max_seq, ctx - 1, num_splits=0)
+    for splits in (0, 1, 3):
+        out = tq.attention(_c(q), kc, vc, ks, vs, kr, scale, nh, nkv, max_seq, ctx - 1, num_splits=splits)
+        assert H.rel_err(out.cpu().numpy().reshape(ref.shape), ref) <= 2e-3, f"splits={splits}"
+
+
+def test_oracle_split_mode_equals_single_pass(tq, tqc):
+    """The reference's split + reduce path against its single-pass path (CPU oracle both sides)."""
+    nh, nkv, max_seq, ctx = 16, 8, 600, 513
+    kc, ks, kr, vc, vs = [a.cpu().numpy() for a in _fill_cache(tq, tqc, nkv, max_seq, ctx, seed=9)]
+    q = H.make_x(1, nh * 128, seed=1, name="q")
+    a = orc.tq_attention(q, kc, vc, tqc, ks, vs, kr, 0.088, nh, nkv, max_seq, ctx - 1, num_splits=0)
+    b = orc.tq_attention(q, kc, vc, tqc, ks, vs, kr, 0.088, nh, nkv, max_seq, ctx - 1, num_splits=5)
+    assert H.rel_err(b, a) <= 2e-3
+
+
+def test_prefill_attention_causal_and_batched(tq, tqc):
+    """T > 1 (prefill over the quantized cache, causal length base+t+1) and nseq > 1."""
+    nh, nkv, max_seq, base, T, nseq = 32, 8, 128, 20, 6, 2
+    kc, ks, kr, vc, vs = _fill_cache(tq, tqc, nkv, max_seq, base + T, seed=5, nseq=nseq)
+    q = H.make_x(nseq * T, nh * 128, seed=8, name="q")
+    out = tq.attention(_c(q), kc, vc, ks, vs, kr, 0.0884, nh, nkv, max_seq, base, nseq=nseq).cpu().numpy()
+    out = out.reshape(nseq, T, nh, 128)
+    for s in range(nseq):
+        ref = orc.tq_attention(q.reshape(nseq, T, -1)[s], kc[s].cpu().numpy(), vc[s].cpu().numpy(), tqc, ks[s].cpu().numpy(),
+                               vs[s].cpu().numpy(), kr[s].cpu().numpy(), 0.0884, nh, nkv, max_seq, base)
+        assert H.rel_err(out[s], ref) <= 2e-3
+
+
+def test_attention_full_context_property(tq, tqc):
+    """32k context (the oracle is not run): the output with every V row equal to one vector
+    reproduces that vector's quantize-dequantize image, whatever the scores are."""
+    nh, nkv, max_seq, ctx = 32, 8, 32768, 32768
+    g = torch.Generator(device="cuda").manual_seed(1)
+    k = torch.randn((ctx, nkv * 128), generator=g, device="cuda").half()
+    v1 = torch.randn((1, nkv * 128), generator=g, device="cuda").half()
+    v = v1.expand(ctx, -1).contiguous()
+    kc = torch.zeros((1, nkv, max_seq, 128), dtype=torch.uint8, device="cuda")
+    vc = torch.zeros_like(kc)
+    ks, kr, vs, vr = [torch.zeros((1, nkv, max_seq), dtype=torch.float32, device="cuda") for _ in range(4)]
+    tq.encode(k, True, kc, ks, kr, nkv, max_seq, 0)
+    tq.encode(v, False, vc, vs, vr, nkv, max_seq, 0)
+    q = torch.randn((1, nh * 128), generator=g, device="cuda").half()
+    out = tq.attention(q, kc, vc, ks, vs, kr, 0.0884, nh, nkv, max_seq, ctx - 1).float().reshape(nh, 128)
+    # expected: dequantised V row 0 rotated back = signs-Hadamard of codebook[v bytes] * scale
+    lv = torch.from_numpy(tqc.v_levels).cuda()
+    for h in (0, 5, 31):
+        kvh = h // (nh // nkv)
+        vrot = lv[vc[0, kvh, 0].long()] * vs[0, kvh, 0]
+        ref = torch.from_numpy(orc.hadamard_rotate(vrot.cpu().numpy(), tqc.signs)).cuda()
+        assert float((out[h] - ref).abs().max()) <= 2e-3 * float(ref.abs().max()) + 1e-3
+
+
+def test_sequence_overflow_is_reported(tq):
+    from ironmill_b200 import CudaSysError
+    z8 = torch.zeros((1, 8, 16, 128), dtype=torch.uint8, device="cuda")
+    zf = torch.zeros((1, 8, 16), dtype=torch.float32, device="cuda")
+    q = torch.zeros((1, 8 * 128), dtype=torch.float16, device="cuda")
+    with pytest.raises(CudaSysError):
+        tq.attention(q, z8, z8, zf, zf, zf, 1.0, 8, 8, 16, 16)
