@@ -168,7 +168,10 @@ __global__ void tq_encode_kernel(const __half *__restrict__ kv, const float *__r
     if (d == 0) scale_buf[row] = norm;
     const float inv = __fdiv_rn(1.0f, fmaxf(norm, 1e-10f));
     const float u = __fmul_rn(x, inv);
-    // index = number of boundaries <= u (boundaries ascending): binary search
+    // The reference scans all boundaries and keeps the LAST b with u >= boundaries[b]
+    // (index b + 1).  Its 7- and 8-bit tables are not monotone, so that is not a plain
+    // upper bound; `bounds` holds the suffix minima of the table, which are monotone and
+    // give the same answer: max{b : boundaries[b] <= u} = max{b : min(boundaries[b..]) <= u}.
     int lo = 0, hi = n_levels - 1;
     while (lo < hi) {
         const int mid = (lo + hi) >> 1;
@@ -499,6 +502,12 @@ IM_EXPORT int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const 
         v_levels_host = vl.data();
         v_bounds_host = vb.data();
     }
+    // suffix minima of the boundary tables (see tq_encode_kernel)
+    std::vector<float> ksm(k_bounds_host, k_bounds_host + (1 << (n_bits - 1)) - 1), vsm(v_bounds_host, v_bounds_host + (1 << n_bits) - 1);
+    for (int i = (int)ksm.size() - 2; i >= 0; i--) ksm[i] = fminf(ksm[i], ksm[i + 1]);
+    for (int i = (int)vsm.size() - 2; i >= 0; i--) vsm[i] = fminf(vsm[i], vsm[i + 1]);
+    k_bounds_host = ksm.data();
+    v_bounds_host = vsm.data();
     im_tq *tq = new im_tq();
     tq->dev = dev;
     tq->hd = head_dim;
