@@ -206,6 +206,71 @@ int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, 
 size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
 int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
 
+/* ------------------------------------------------------------------ model-level engine
+ * The CUDA counterpart of MetalInference behind the InferenceEngine trait
+ * (crates/ironmill-inference/src/engine.rs:72-114; crates/ironmill-inference/src/metal/engine.rs:122-270,
+ *  loading.rs:483-518, pipeline.rs:228-1313).  One call = one whole token (or prompt chunk): the decode
+ * step is captured once per batch size into a CUDA graph and replayed.
+ *
+ * Config mirrors ModelConfig (crates/mil-rs/src/weights.rs:57-97) + MetalConfig
+ * (crates/ironmill-inference/src/metal/config.rs:270-299).  Zero in an optional field selects the default
+ * named beside it. */
+typedef struct im_model im_model;
+typedef struct im_model_config {
+    int num_layers, hidden_size, intermediate_size, num_heads, num_kv_heads, head_dim, vocab_size;
+    int max_seq_len;          /* MetalConfig.max_seq_len (default 2048) */
+    int max_batch;            /* sequences decoded in lockstep (default 1) */
+    float rms_eps;
+    float attn_scale;         /* 0 = 1/sqrt(head_dim) (crates/mil-rs/src/weights.rs:210-217) */
+    float embed_scale;        /* 0 = 1.0 */
+    double rope_theta;
+    int rotary_dim;           /* 0 = head_dim */
+    int qk_norm;              /* 1: q_norm / k_norm weights present (Qwen3) */
+    int tie_word_embeddings;  /* 1: lm_head = embedding table */
+    int tq_bits;              /* TurboQuant KV bits (0 = 8; only 8 is built) */
+    uint64_t rotation_seed;   /* MetalConfig.rotation_seed (default 42) */
+    int tp_world, tp_rank;    /* tensor parallel group (0/0 = single GPU) */
+} im_model_config;
+
+int im_cuda_model_create(im_device *dev, const im_model_config *cfg, im_model **out);
+void im_cuda_model_free(im_model *m);
+/* Tensors arrive under their Hugging Face names (crates/ironmill-inference/src/weight_loading.rs:163-426):
+ * model.embed_tokens.weight, model.layers.{i}.input_layernorm.weight, .self_attn.{q,k,v,o}_proj.weight,
+ * .self_attn.{q,k}_norm.weight, .post_attention_layernorm.weight, .mlp.{gate,up,down}_proj.weight,
+ * model.norm.weight, lm_head.weight.  Each rank is handed the FULL tensor and keeps its shard. */
+int im_cuda_model_load_dense(im_model *m, const char *name, const void *data_f16_host, size_t num_elements);
+int im_cuda_model_load_affine(im_model *m, const char *name, const void *qdata_host, const void *scales_host,
+                              const void *zeros_host, int param_dtype, const void *awq_f16_host, int N, int K,
+                              int group_size, int bit_width);
+/* Optional: rotation signs [hd] and QJL matrix [hd,hd]; otherwise generated from rotation_seed. */
+int im_cuda_model_set_tq_constants(im_model *m, const float *signs_host, const float *qjl_host);
+/* Tensor parallel: rank 0 makes an id (128 bytes), every rank passes the same bytes. */
+int im_cuda_tp_unique_id(void *id_out_128_bytes);
+int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes);
+/* Checks that every tensor arrived, repacks, allocates KV caches / RoPE tables / TurboQuant constants
+ * (init_model_state, crates/ironmill-inference/src/metal/loading.rs:32-65). */
+int im_cuda_model_finalize(im_model *m);
+/* InferenceEngine::prefill / decode_step: logits_out_host f32 [vocab] (prefill: last token) or
+ * [batch, vocab] (decode).  Tokens are host u32.  Sequence overflow returns IM_ERR_BOUNDS
+ * (crates/ironmill-inference/src/metal/pipeline.rs:270-279). */
+int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, int n_tokens, float *logits_out_host);
+int im_cuda_model_decode_step(im_model *m, const uint32_t *tokens_host, int batch, float *logits_out_host);
+/* Greedy decoding kept on the device: n_steps graph replays, each feeding the arg-max token (last
+ * maximal index, crates/ironmill-inference/src/sampling.rs:331-339) of the previous one.  first_tokens_host
+ * [batch]; tokens_out_host u32 [n_steps, batch] (may be NULL); elapsed_ms_out = CUDA-event time of the loop. */
+int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tokens_host, int batch, int n_steps,
+                                uint32_t *tokens_out_host, float *elapsed_ms_out);
+int im_cuda_model_reset(im_model *m);
+int im_cuda_model_truncate(im_model *m, int pos);
+int im_cuda_model_seq_pos(const im_model *m);
+int im_cuda_model_max_seq_len(const im_model *m);
+size_t im_cuda_model_memory_bytes(const im_model *m);
+/* Algorithmic bytes one decode step of this rank reads from HBM at context length ctx and the given batch:
+ * packed codes + scales/zeros + AWQ vectors + fp16 lm_head rows + norm weights + batch * KV bytes. */
+size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
+/* Number of kernel launches in one captured decode step. */
+int im_cuda_model_step_launches(const im_model *m);
+
 #ifdef __cplusplus
 }
 #endif

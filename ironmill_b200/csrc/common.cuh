@@ -95,6 +95,36 @@ __device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
     return (int)d;
 }
 
+// Arguments of the fused (QK-norm +) RoPE kernel (norm.cu), shared with the model engine.
+struct QkRopeArgs {
+    const __half *q_in, *k_in, *v_in;
+    int q_stride, k_stride, v_stride;  // elements between consecutive tokens of the inputs
+    __half *q_out, *k_out, *v_out;
+    const __half *qw, *kw, *cosc, *sinc;
+    int nh, nkv, hd, rotary_dim, seq_offset;
+    const int *pos_dev;  // per-sequence base positions (tokens_per_seq tokens each) or nullptr
+    int tokens_per_seq;
+    float eps;
+    int with_norm;
+};
+
+int launch_qk_rope(const QkRopeArgs &a, int T, cudaStream_t st);
+
+// TurboQuant constants + scratch (turboquant.cu)
+struct Tq {
+    Device *dev = nullptr;
+    int hd = 0, n_bits = 0, k_levels = 0, v_levels = 0;
+    float *signs = nullptr, *qjl = nullptr, *k_cb = nullptr, *k_bd = nullptr, *v_cb = nullptr, *v_bd = nullptr;
+    float *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    size_t const_bytes = 0;
+};
+
+int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len);
+int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,
+                        const float *vs, const float *krn, float attn_scale, __half *out, int nseq, int nh, int nkv, int max_seq,
+                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st);
+
 }  // namespace im
 
 // The opaque handle types of the C ABI are thin tags over the internal structs.

@@ -1,0 +1,852 @@
+// Model-level decode engine: the CUDA counterpart of MetalInference
+// (crates/ironmill-inference/src/metal/engine.rs:122-270, loading.rs:32-518, pipeline.rs:228-1313).
+//
+// Schedule of one token (pipeline.rs:424-1313, decode DAG metal/graph.rs:98-201):
+//   fused_embedding_norm -> per layer { QKV projection (layer 0; later layers get it from the
+//   end-of-layer fused kernel), (QK-norm +) RoPE, TurboQuant write of K and V, TurboQuant split
+//   attention + reduce, o_proj, fused residual+RMSNorm, fused gate+up+SiLU, down_proj, fused
+//   residual+RMSNorm+next-layer QKV projection } -> final RMSNorm -> fp16 lm_head.
+// The whole step is captured once per batch size into a CUDA graph; the sequence position lives
+// in device memory so that the graph replays unchanged as the sequence grows.
+//
+// Tensor parallelism (not present in the reference): QKV / gate / up are split by output rows
+// (heads), o / down by input columns, KV heads and their caches by rank, lm_head by vocabulary
+// rows; one NCCL all-reduce follows each row-split projection and one all-gather the lm_head.
+#include <dlfcn.h>
+#include <math.h>
+#include <string.h>
+
+#include <map>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+#if __has_include(<nccl.h>)
+#include <nccl.h>
+#define IM_HAVE_NCCL_H 1
+#else
+#define IM_HAVE_NCCL_H 0
+#endif
+
+// entry points of other translation units used here
+extern "C" {
+struct im_tq;
+int im_cuda_tq_generate(int head_dim, uint64_t seed, float *signs_out_host, float *qjl_out_host);
+int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const float *signs_host, const float *qjl_host,
+                      const float *k_levels_host, const float *k_bounds_host, const float *v_levels_host,
+                      const float *v_bounds_host, im_tq **out);
+void im_cuda_tq_free(im_tq *tq);
+int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, void *cache_dev, float *scale_dev, float *r_norms_dev,
+                      int nseq, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, void *stream);
+size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
+int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
+}
+
+namespace im {
+
+// ---- NCCL through dlopen: the library works without NCCL until tensor parallelism is asked for
+#if IM_HAVE_NCCL_H
+struct Nccl {
+    void *lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+static Nccl *nccl() {
+    static Nccl n;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        for (const char *name : {"libnccl.so.2", "libnccl.so"}) {
+            n.lib = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+            if (n.lib) break;
+        }
+        if (n.lib) {
+#define IM_SYM(field, sym) n.field = reinterpret_cast<decltype(n.field)>(dlsym(n.lib, sym))
+            IM_SYM(GetUniqueId, "ncclGetUniqueId");
+            IM_SYM(CommInitRank, "ncclCommInitRank");
+            IM_SYM(AllReduce, "ncclAllReduce");
+            IM_SYM(AllGather, "ncclAllGather");
+            IM_SYM(CommDestroy, "ncclCommDestroy");
+            IM_SYM(GetErrorString, "ncclGetErrorString");
+#undef IM_SYM
+        }
+    }
+    return (n.lib && n.GetUniqueId && n.CommInitRank && n.AllReduce && n.AllGather) ? &n : nullptr;
+}
+#define IM_NCCL_CHECK(expr)                                                                              \
+    do {                                                                                                 \
+        ncclResult_t _r = (expr);                                                                        \
+        if (_r != ncclSuccess)                                                                           \
+            return fail(IM_ERR_NCCL, "%s failed: %s", #expr, nccl()->GetErrorString ? nccl()->GetErrorString(_r) : "?"); \
+    } while (0)
+#endif
+
+struct HostAffine {  // one projection as handed to load_affine, already cut to this rank's shard
+    std::vector<uint8_t> q;
+    std::vector<float> s, z;  // kept as f32 or widened fp16 bit patterns, see param_f32
+    std::vector<uint16_t> s16, z16, awq;
+    bool param_f32 = true, have = false;
+    int N = 0, K = 0, gs = 0, bits = 0;
+};
+
+struct Layer {
+    HostAffine hq, hk, hv;           // staged until finalize concatenates them
+    AffineWeight *qkv = nullptr;     // rows [q | k | v] of this rank
+    AffineWeight *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+    __half *input_ln = nullptr, *post_ln = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    uint8_t *kc = nullptr, *vc = nullptr;
+    float *ks = nullptr, *vs = nullptr, *krn = nullptr;
+};
+
+struct Model {
+    Device *dev = nullptr;
+    im_model_config cfg{};
+    int nh_l = 0, nkv_l = 0, I_l = 0, vocab_l = 0, world = 1, rank = 0;
+    int q_dim = 0, kv_dim = 0, qkv_dim = 0;
+    std::vector<Layer> layers;
+    __half *embed = nullptr, *lm_head = nullptr, *final_norm = nullptr;
+    bool lm_head_owned = false;
+    im_tq *tq = nullptr;
+    std::vector<float> signs_host, qjl_host;
+    __half *cosc = nullptr, *sinc = nullptr;
+    // activations, MT = max tokens per forward
+    int MT = 0;
+    __half *hidden = nullptr, *norm_out = nullptr, *residual = nullptr, *qkv = nullptr, *q_d = nullptr, *k_d = nullptr, *v_d = nullptr,
+           *attn_out = nullptr, *ffn_down = nullptr, *ffn_gate = nullptr, *logits = nullptr, *logits_all = nullptr;
+    uint32_t *tokens_dev = nullptr, *tok_hist = nullptr;
+    int *pos_dev = nullptr, *step_dev = nullptr;
+    uint32_t *tokens_pin = nullptr;
+    __half *logits_pin = nullptr;
+    cudaStream_t stream = nullptr;
+    std::map<int, cudaGraphExec_t> graphs;
+    int seq_pos = 0;
+    bool finalized = false;
+    size_t bytes = 0;
+    int launches_per_step = 0;
+    float *scratch_ref = nullptr;
+#if IM_HAVE_NCCL_H
+    ncclComm_t comm = nullptr;
+#endif
+    std::vector<std::pair<void *, size_t>> allocs;
+
+    int alloc(void **p, size_t n) {
+        int rc = dev_malloc(dev, p, n);
+        if (rc == IM_OK && n) {
+            allocs.push_back({*p, n});
+            bytes += n;
+        }
+        return rc;
+    }
+};
+
+static const int kPrefillChunk = 64;
+
+__global__ void advance_pos_kernel(int *pos, int n, int by) {
+    if ((int)threadIdx.x < n) pos[threadIdx.x] += by;
+}
+__global__ void set_pos_kernel(int *pos, int n, int v) {
+    if ((int)threadIdx.x < n) pos[threadIdx.x] = v;
+}
+
+// Greedy pick per sequence: LAST maximal index (Iterator::max_by keeps the last of equal maxima,
+// crates/ironmill-inference/src/sampling.rs:331-339).  logits are laid out [parts][nseq][vocab_part].
+__global__ void argmax_kernel(const __half *__restrict__ logits, int vocab_part, int parts, int nseq, uint32_t *__restrict__ tokens,
+                              uint32_t *__restrict__ hist, const int *__restrict__ step, int hist_stride, int hist_rows) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int seq = blockIdx.x;
+    float best = -INFINITY;
+    int bi = -1;
+    const int vocab = vocab_part * parts;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const int part = i / vocab_part, j = i % vocab_part;
+        const float v = __half2float(logits[((size_t)part * nseq + seq) * vocab_part + j]);
+        if (!(v < best) || bi < 0) {  // ascending i per thread: ties move to the later index
+            best = v;
+            bi = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (si[w] >= 0 && (bi < 0 || sv[w] > best || (sv[w] == best && si[w] > bi))) {
+                best = sv[w];
+                bi = si[w];
+            }
+        tokens[seq] = (uint32_t)bi;
+        if (hist) hist[(size_t)(*step % hist_rows) * hist_stride + seq] = (uint32_t)bi;
+    }
+}
+__global__ void bump_kernel(int *step) { *step += 1; }
+
+static bool parse_layer_name(const char *name, int *layer, std::string *suffix) {
+    const char *pfx = "model.layers.";
+    if (strncmp(name, pfx, strlen(pfx)) != 0) return false;
+    const char *p = name + strlen(pfx);
+    char *end = nullptr;
+    long l = strtol(p, &end, 10);
+    if (end == p || *end != '.') return false;
+    *layer = (int)l;
+    *suffix = end + 1;
+    return true;
+}
+
+static int upload_f16(Model *m, __half **dst, const void *src, size_t n) {
+    int rc = m->alloc((void **)dst, n * sizeof(__half));
+    if (rc != IM_OK) return rc;
+    IM_CUDA_CHECK(cudaMemcpy(*dst, src, n * sizeof(__half), cudaMemcpyHostToDevice));
+    return IM_OK;
+}
+
+// Cut rows [r0, r0+nr) and columns [c0, c0+nc) out of a full affine tensor.
+static int slice_affine(HostAffine *out, const void *qdata, const void *scales, const void *zeros, int param_dtype, const void *awq,
+                        int N, int K, int gs, int bits, int r0, int nr, int c0, int nc) {
+    if (r0 < 0 || nr <= 0 || r0 + nr > N || c0 < 0 || nc <= 0 || c0 + nc > K) return fail(IM_ERR_INVALID, "shard out of range");
+    if ((c0 % gs) != 0 || (nc % gs != 0 && c0 + nc != K) || (bits == 4 && ((c0 | nc | K) & 1)))
+        return fail(IM_ERR_INVALID, "column shard [%d,%d) of K=%d is not aligned to group size %d", c0, c0 + nc, K, gs);
+    const int G = (K + gs - 1) / gs, g0 = c0 / gs, ng = (nc + gs - 1) / gs;
+    const size_t rb = (size_t)K * bits / 8, cb0 = (size_t)c0 * bits / 8, cbn = (size_t)nc * bits / 8;
+    out->N = nr; out->K = nc; out->gs = gs; out->bits = bits; out->have = true;
+    out->param_f32 = param_dtype == IM_DTYPE_F32;
+    out->q.resize((size_t)nr * cbn);
+    const uint8_t *q = static_cast<const uint8_t *>(qdata);
+    for (int r = 0; r < nr; r++) memcpy(out->q.data() + (size_t)r * cbn, q + (size_t)(r0 + r) * rb + cb0, cbn);
+    if (out->param_f32) {
+        out->s.resize((size_t)nr * ng);
+        out->z.resize((size_t)nr * ng);
+        for (int r = 0; r < nr; r++) {
+            memcpy(out->s.data() + (size_t)r * ng, static_cast<const float *>(scales) + (size_t)(r0 + r) * G + g0, ng * 4);
+            memcpy(out->z.data() + (size_t)r * ng, static_cast<const float *>(zeros) + (size_t)(r0 + r) * G + g0, ng * 4);
+        }
+    } else {
+        out->s16.resize((size_t)nr * ng);
+        out->z16.resize((size_t)nr * ng);
+        for (int r = 0; r < nr; r++) {
+            memcpy(out->s16.data() + (size_t)r * ng, static_cast<const uint16_t *>(scales) + (size_t)(r0 + r) * G + g0, ng * 2);
+            memcpy(out->z16.data() + (size_t)r * ng, static_cast<const uint16_t *>(zeros) + (size_t)(r0 + r) * G + g0, ng * 2);
+        }
+    }
+    out->awq.clear();
+    if (awq) out->awq.assign(static_cast<const uint16_t *>(awq) + c0, static_cast<const uint16_t *>(awq) + c0 + nc);
+    return IM_OK;
+}
+
+static int make_weight(Model *m, const HostAffine &h, AffineWeight **out) {
+    im_affine_weight *w = nullptr;
+    int rc = im_cuda_affine_weight_create(static_cast<im_device *>(m->dev), h.q.data(), h.param_f32 ? (const void *)h.s.data() : (const void *)h.s16.data(),
+                                          h.param_f32 ? (const void *)h.z.data() : (const void *)h.z16.data(),
+                                          h.param_f32 ? IM_DTYPE_F32 : IM_DTYPE_F16, h.awq.empty() ? nullptr : h.awq.data(), h.N, h.K, h.gs,
+                                          h.bits, &w);
+    if (rc != IM_OK) return rc;
+    *out = w;
+    m->bytes += w->bytes;
+    return IM_OK;
+}
+
+static int tp_allreduce(Model *m, __half *buf, size_t count, cudaStream_t st) {
+    if (m->world <= 1) return IM_OK;
+#if IM_HAVE_NCCL_H
+    if (!m->comm) return fail(IM_ERR_STATE, "tensor parallel group not initialised (im_cuda_model_tp_init)");
+    IM_NCCL_CHECK(nccl()->AllReduce(buf, buf, count, ncclHalf, ncclSum, m->comm, st));
+    return IM_OK;
+#else
+    (void)buf; (void)count; (void)st;
+    return fail(IM_ERR_NCCL, "built without nccl.h");
+#endif
+}
+
+#define IM_TRY(expr)                  \
+    do {                              \
+        int _rc = (expr);             \
+        if (_rc != IM_OK) return _rc; \
+    } while (0)
+
+// One forward pass over nseq sequences x T tokens each (decode: T = 1; prefill: nseq = 1).
+// Logits are produced for the last token of every sequence.
+static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches) {
+    const im_model_config &c = m->cfg;
+    const int H = c.hidden_size, hd = c.head_dim, MT = nseq * T;
+    const float eps = c.rms_eps;
+    const float attn_scale = c.attn_scale != 0.0f ? c.attn_scale : 1.0f / sqrtf((float)hd);
+    int nl = 0;
+    IM_TRY(im_cuda_embedding_norm(m->tokens_dev, m->embed, m->layers[0].input_ln, m->norm_out, m->hidden, H, MT, (uint32_t)c.vocab_size, eps,
+                                  c.embed_scale != 0.0f ? c.embed_scale : 1.0f, st));
+    nl++;
+    for (int l = 0; l < c.num_layers; l++) {
+        Layer &L = m->layers[l];
+        if (l == 0) {
+            IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.qkv), m->norm_out, m->qkv, MT, st));
+            nl += (MT + 3) / 4;
+        }
+        QkRopeArgs a{};
+        a.q_in = m->qkv; a.k_in = m->qkv + m->q_dim; a.v_in = m->qkv + m->q_dim + m->kv_dim;
+        a.q_stride = a.k_stride = a.v_stride = m->qkv_dim;
+        a.q_out = m->q_d; a.k_out = m->k_d; a.v_out = m->v_d;
+        a.qw = L.q_norm; a.kw = L.k_norm; a.cosc = m->cosc; a.sinc = m->sinc;
+        a.nh = m->nh_l; a.nkv = m->nkv_l; a.hd = hd; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd;
+        a.seq_offset = 0; a.pos_dev = m->pos_dev; a.tokens_per_seq = T; a.eps = eps; a.with_norm = c.qk_norm ? 1 : 0;
+        IM_TRY(launch_qk_rope(a, MT, st));
+        IM_TRY(im_cuda_tq_encode(m->tq, m->k_d, 1, L.kc, L.ks, L.krn, nseq, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, st));
+        IM_TRY(im_cuda_tq_encode(m->tq, m->v_d, 0, L.vc, L.vs, L.krn /*unused*/, nseq, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, st));
+        IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, m->q_d, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
+                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st));
+        nl += 5;
+        IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.o), m->attn_out, m->ffn_down, MT, st));
+        IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
+        IM_TRY(im_cuda_fused_residual_rms_norm(m->hidden, m->ffn_down, L.post_ln, m->norm_out, m->residual, H, MT, eps, st));
+        IM_TRY(im_cuda_ffn_gate_up_act(static_cast<im_affine_weight *>(L.gate), static_cast<im_affine_weight *>(L.up), m->norm_out,
+                                       m->ffn_gate, MT, st));
+        IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.down), m->ffn_gate, m->ffn_down, MT, st));
+        IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
+        nl += 1 + 3 * ((MT + 3) / 4) + (m->world > 1 ? 2 : 0);
+        if (l + 1 < c.num_layers) {
+            Layer &Nx = m->layers[l + 1];
+            IM_TRY(im_cuda_fused_residual_norm_matvec(static_cast<im_affine_weight *>(Nx.qkv), m->residual, m->ffn_down, Nx.input_ln, eps,
+                                                      m->qkv, m->hidden, m->norm_out, MT, st));
+            nl += (MT + 3) / 4;
+        } else {
+            IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)MT * H, st));
+            nl++;
+        }
+    }
+    // final norm + lm_head on the last token of each sequence
+    for (int s = 0; s < nseq; s++) {
+        const __half *last = m->hidden + ((size_t)s * T + (T - 1)) * H;
+        IM_TRY(im_cuda_rms_norm(last, m->final_norm, m->norm_out + (size_t)s * H, H, 1, eps, st));
+        nl++;
+    }
+    IM_TRY(im_cuda_matvec_f16(m->lm_head, m->norm_out, m->logits, m->vocab_l, H, nseq, st));
+    nl += (nseq + 3) / 4;
+    if (m->world > 1) {
+#if IM_HAVE_NCCL_H
+        IM_NCCL_CHECK(nccl()->AllGather(m->logits, m->logits_all, (size_t)nseq * m->vocab_l, ncclHalf, m->comm, st));
+        nl++;
+#endif
+    }
+    if (launches) *launches = nl;
+    return IM_OK;
+}
+
+static int decode_splits(const Model *m, int batch) {
+    return tq_auto_splits(m->dev, batch, 1, m->nkv_l, m->cfg.max_seq_len);
+}
+
+static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
+    auto it = m->graphs.find(batch);
+    if (it != m->graphs.end()) {
+        *out = it->second;
+        return IM_OK;
+    }
+    cudaStream_t st = m->stream;
+    // one eager pass first: sets function attributes and warms NCCL outside the capture
+    const int splits = decode_splits(m, batch);
+    int saved_pos = m->seq_pos;
+    IM_TRY(forward(m, batch, 1, splits, st, nullptr));
+    IM_CUDA_CHECK(cudaStreamSynchronize(st));
+    (void)saved_pos;
+    cudaGraph_t g = nullptr;
+    IM_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    int nl = 0;
+    int rc = forward(m, batch, 1, splits, st, &nl);
+    if (rc == IM_OK) {
+        const __half *lg = m->world > 1 ? m->logits_all : m->logits;
+        argmax_kernel<<<batch, 1024, 0, st>>>(lg, m->vocab_l, m->world, batch, m->tokens_dev, m->tok_hist, m->step_dev, m->cfg.max_batch, m->cfg.max_seq_len);
+        bump_kernel<<<1, 1, 0, st>>>(m->step_dev);
+        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, batch, 1);
+        nl += 3;
+    }
+    cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (rc != IM_OK) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (e != cudaSuccess) return fail(IM_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+    cudaGraphExec_t ge = nullptr;
+    e = cudaGraphInstantiate(&ge, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(IM_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    m->graphs[batch] = ge;
+    m->launches_per_step = nl;
+    *out = ge;
+    return IM_OK;
+}
+
+static int set_positions(Model *m, int pos) {
+    set_pos_kernel<<<1, 64, 0, m->stream>>>(m->pos_dev, m->cfg.max_batch, pos);
+    IM_CUDA_CHECK(cudaGetLastError());
+    m->seq_pos = pos;
+    return IM_OK;
+}
+
+static void logits_to_host(const Model *m, const __half *pin, int nseq, float *out) {
+    const int vl = m->vocab_l, parts = m->world, V = m->cfg.vocab_size;
+    for (int p = 0; p < parts; p++)
+        for (int s = 0; s < nseq; s++) {
+            const __half *src = pin + ((size_t)p * nseq + s) * vl;
+            float *dst = out + (size_t)s * V + (size_t)p * vl;
+            for (int j = 0; j < vl; j++) dst[j] = __half2float(src[j]);
+        }
+}
+
+}  // namespace im
+
+using namespace im;
+struct im_model : im::Model {};
+
+IM_EXPORT int im_cuda_tp_unique_id(void *id_out_128_bytes) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(id_out_128_bytes, "bad argument");
+#if IM_HAVE_NCCL_H
+    if (!nccl()) return fail(IM_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId size");
+    ncclUniqueId id;
+    IM_NCCL_CHECK(nccl()->GetUniqueId(&id));
+    memcpy(id_out_128_bytes, &id, 128);
+    return IM_OK;
+#else
+    return fail(IM_ERR_NCCL, "built without nccl.h");
+#endif
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && id_128_bytes, "bad argument");
+    if (m->world <= 1) return IM_OK;
+#if IM_HAVE_NCCL_H
+    if (!nccl()) return fail(IM_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    ncclUniqueId id;
+    memcpy(&id, id_128_bytes, 128);
+    IM_NCCL_CHECK(nccl()->CommInitRank(&m->comm, m->world, id, m->rank));
+    return IM_OK;
+#else
+    return fail(IM_ERR_NCCL, "built without nccl.h");
+#endif
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_create(im_device *dev, const im_model_config *cfg, im_model **out) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(dev && cfg && out, "bad argument");
+    *out = nullptr;
+    im_model_config c = *cfg;
+    if (c.max_seq_len == 0) c.max_seq_len = 2048;
+    if (c.max_batch == 0) c.max_batch = 1;
+    if (c.tq_bits == 0) c.tq_bits = 8;
+    if (c.rotation_seed == 0) c.rotation_seed = 42;
+    if (c.tp_world == 0) c.tp_world = 1;
+    // MetalConfig::validate (crates/ironmill-inference/src/metal/config.rs:364-384)
+    IM_REQUIRE(c.max_seq_len > 0, "max_seq_len must be > 0");
+    IM_REQUIRE(c.tq_bits == 4 || c.tq_bits == 8, "n_bits must be 4 or 8, got %d", c.tq_bits);
+    IM_REQUIRE(c.tq_bits == 8, "only the 8-bit TurboQuant cache is built (n_bits = %d)", c.tq_bits);
+    IM_REQUIRE(c.num_layers > 0 && c.hidden_size > 0 && c.intermediate_size > 0 && c.num_heads > 0 && c.num_kv_heads > 0 &&
+                   c.head_dim > 0 && c.vocab_size > 0, "model dimensions must be positive");
+    IM_REQUIRE(c.head_dim == 128, "head_dim %d is not built (128 only)", c.head_dim);
+    IM_REQUIRE(c.num_heads % c.num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads");
+    IM_REQUIRE(c.max_batch >= 1 && c.max_batch <= 64, "max_batch must be in 1..64");
+    IM_REQUIRE(c.tp_world >= 1 && c.tp_rank >= 0 && c.tp_rank < c.tp_world, "bad tensor-parallel rank %d of %d", c.tp_rank, c.tp_world);
+    IM_REQUIRE(c.num_kv_heads % c.tp_world == 0 && c.intermediate_size % (c.tp_world * 128) == 0 && c.vocab_size % c.tp_world == 0,
+               "tensor-parallel size %d must divide num_kv_heads, intermediate_size/128 and vocab_size", c.tp_world);
+    IM_REQUIRE(c.rms_eps > 0.0f && c.rope_theta > 0.0, "rms_eps and rope_theta must be positive");
+    IM_CUDA_CHECK(cudaSetDevice(dev->ordinal));
+    im_model *m = new im_model();
+    m->dev = dev;
+    m->cfg = c;
+    m->world = c.tp_world;
+    m->rank = c.tp_rank;
+    m->nh_l = c.num_heads / m->world;
+    m->nkv_l = c.num_kv_heads / m->world;
+    m->I_l = c.intermediate_size / m->world;
+    m->vocab_l = c.vocab_size / m->world;
+    m->q_dim = m->nh_l * c.head_dim;
+    m->kv_dim = m->nkv_l * c.head_dim;
+    m->qkv_dim = m->q_dim + 2 * m->kv_dim;
+    m->layers.resize(c.num_layers);
+    cudaError_t e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete m;
+        return fail(IM_ERR_CUDA, "stream creation failed: %s", cudaGetErrorString(e));
+    }
+    *out = m;
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT void im_cuda_model_free(im_model *m) {
+    if (!m) return;
+    cudaSetDevice(m->dev->ordinal);
+    if (m->stream) cudaStreamSynchronize(m->stream);
+    for (auto &g : m->graphs) cudaGraphExecDestroy(g.second);
+#if IM_HAVE_NCCL_H
+    if (m->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(m->comm);
+#endif
+    for (auto &L : m->layers) {
+        im_cuda_affine_weight_free(static_cast<im_affine_weight *>(L.qkv));
+        im_cuda_affine_weight_free(static_cast<im_affine_weight *>(L.o));
+        im_cuda_affine_weight_free(static_cast<im_affine_weight *>(L.gate));
+        im_cuda_affine_weight_free(static_cast<im_affine_weight *>(L.up));
+        im_cuda_affine_weight_free(static_cast<im_affine_weight *>(L.down));
+    }
+    if (m->tq) im_cuda_tq_free(m->tq);
+    for (auto &a : m->allocs) dev_free(m->dev, a.first, a.second);
+    if (m->tokens_pin) cudaFreeHost(m->tokens_pin);
+    if (m->logits_pin) cudaFreeHost(m->logits_pin);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+IM_EXPORT int im_cuda_model_load_dense(im_model *m, const char *name, const void *data_f16_host, size_t n) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && name && data_f16_host, "bad argument");
+    if (m->finalized) return fail(IM_ERR_STATE, "model already finalized");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    const im_model_config &c = m->cfg;
+    const size_t H = c.hidden_size;
+    std::string nm(name), suffix;
+    int l = -1;
+    if (nm == "model.embed_tokens.weight") {
+        IM_REQUIRE(n == (size_t)c.vocab_size * H, "%s: expected %zu elements, got %zu", name, (size_t)c.vocab_size * H, n);
+        return upload_f16(m, &m->embed, data_f16_host, n);
+    }
+    if (nm == "model.norm.weight") {
+        IM_REQUIRE(n == H, "%s: expected %zu elements, got %zu", name, H, n);
+        return upload_f16(m, &m->final_norm, data_f16_host, n);
+    }
+    if (nm == "lm_head.weight") {
+        IM_REQUIRE(n == (size_t)c.vocab_size * H, "%s: expected %zu elements, got %zu", name, (size_t)c.vocab_size * H, n);
+        const __half *src = static_cast<const __half *>(data_f16_host) + (size_t)m->rank * m->vocab_l * H;
+        m->lm_head_owned = true;
+        return upload_f16(m, &m->lm_head, src, (size_t)m->vocab_l * H);
+    }
+    if (parse_layer_name(name, &l, &suffix)) {
+        IM_REQUIRE(l >= 0 && l < c.num_layers, "%s: layer index out of range", name);
+        Layer &L = m->layers[l];
+        if (suffix == "input_layernorm.weight") { IM_REQUIRE(n == H, "%s: bad size", name); return upload_f16(m, &L.input_ln, data_f16_host, n); }
+        if (suffix == "post_attention_layernorm.weight") { IM_REQUIRE(n == H, "%s: bad size", name); return upload_f16(m, &L.post_ln, data_f16_host, n); }
+        if (suffix == "self_attn.q_norm.weight") { IM_REQUIRE(n == (size_t)c.head_dim, "%s: bad size", name); return upload_f16(m, &L.q_norm, data_f16_host, n); }
+        if (suffix == "self_attn.k_norm.weight") { IM_REQUIRE(n == (size_t)c.head_dim, "%s: bad size", name); return upload_f16(m, &L.k_norm, data_f16_host, n); }
+    }
+    return fail(IM_ERR_INVALID, "unknown dense tensor '%s'", name);
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_load_affine(im_model *m, const char *name, const void *qdata_host, const void *scales_host,
+                                        const void *zeros_host, int param_dtype, const void *awq_f16_host, int N, int K,
+                                        int group_size, int bit_width) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && name && qdata_host && scales_host && zeros_host, "bad argument");
+    if (m->finalized) return fail(IM_ERR_STATE, "model already finalized");
+    IM_REQUIRE(bit_width == 4 || bit_width == 8, "bit_width must be 4 or 8");
+    IM_REQUIRE(group_size > 0, "group_size must be positive");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    const im_model_config &c = m->cfg;
+    const int H = c.hidden_size, hd = c.head_dim, r = m->rank;
+    std::string suffix;
+    int l = -1;
+    if (!parse_layer_name(name, &l, &suffix) || l < 0 || l >= c.num_layers) return fail(IM_ERR_INVALID, "unknown quantized tensor '%s'", name);
+    Layer &L = m->layers[l];
+    HostAffine h;
+    auto expect = [&](int en, int ek) -> int {
+        if (N != en || K != ek) return fail(IM_ERR_INVALID, "%s: expected shape [%d,%d], got [%d,%d]", name, en, ek, N, K);
+        return IM_OK;
+    };
+#define SLICE(r0, nr, c0, nc) slice_affine(&h, qdata_host, scales_host, zeros_host, param_dtype, awq_f16_host, N, K, group_size, bit_width, r0, nr, c0, nc)
+    if (suffix == "self_attn.q_proj.weight") {
+        IM_TRY(expect(c.num_heads * hd, H));
+        IM_TRY(SLICE(r * m->q_dim, m->q_dim, 0, K));
+        L.hq = std::move(h);
+        return IM_OK;
+    }
+    if (suffix == "self_attn.k_proj.weight" || suffix == "self_attn.v_proj.weight") {
+        IM_TRY(expect(c.num_kv_heads * hd, H));
+        IM_TRY(SLICE(r * m->kv_dim, m->kv_dim, 0, K));
+        (suffix[10] == 'k' ? L.hk : L.hv) = std::move(h);
+        return IM_OK;
+    }
+    AffineWeight **dst = nullptr;
+    if (suffix == "self_attn.o_proj.weight") {
+        IM_TRY(expect(H, c.num_heads * hd));
+        IM_TRY(SLICE(0, N, r * m->q_dim, m->q_dim));
+        dst = &L.o;
+    } else if (suffix == "mlp.gate_proj.weight" || suffix == "mlp.up_proj.weight") {
+        IM_TRY(expect(c.intermediate_size, H));
+        IM_TRY(SLICE(r * m->I_l, m->I_l, 0, K));
+        dst = suffix[4] == 'g' ? &L.gate : &L.up;
+    } else if (suffix == "mlp.down_proj.weight") {
+        IM_TRY(expect(H, c.intermediate_size));
+        IM_TRY(SLICE(0, N, r * m->I_l, m->I_l));
+        dst = &L.down;
+    } else {
+        return fail(IM_ERR_INVALID, "unknown quantized tensor '%s'", name);
+    }
+#undef SLICE
+    if (*dst) return fail(IM_ERR_STATE, "%s loaded twice", name);
+    return make_weight(m, h, dst);
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_set_tq_constants(im_model *m, const float *signs_host, const float *qjl_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && signs_host && qjl_host, "bad argument");
+    if (m->finalized) return fail(IM_ERR_STATE, "model already finalized");
+    const size_t hd = m->cfg.head_dim;
+    m->signs_host.assign(signs_host, signs_host + hd);
+    m->qjl_host.assign(qjl_host, qjl_host + hd * hd);
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_finalize(im_model *m) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m, "bad argument");
+    if (m->finalized) return IM_OK;
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    const im_model_config &c = m->cfg;
+    const int H = c.hidden_size, hd = c.head_dim;
+    if (!m->embed) return fail(IM_ERR_STATE, "missing tensor model.embed_tokens.weight");
+    if (!m->final_norm) return fail(IM_ERR_STATE, "missing tensor model.norm.weight");
+    if (!m->lm_head) {
+        if (!c.tie_word_embeddings) return fail(IM_ERR_STATE, "missing tensor lm_head.weight (and tie_word_embeddings is off)");
+        m->lm_head = m->embed + (size_t)m->rank * m->vocab_l * H;  // tied: this rank's rows of the embedding table
+    }
+    for (int l = 0; l < c.num_layers; l++) {
+        Layer &L = m->layers[l];
+        if (!L.hq.have || !L.hk.have || !L.hv.have || !L.o || !L.gate || !L.up || !L.down || !L.input_ln || !L.post_ln)
+            return fail(IM_ERR_STATE, "layer %d is missing tensors", l);
+        if (c.qk_norm && (!L.q_norm || !L.k_norm)) return fail(IM_ERR_STATE, "layer %d is missing q_norm / k_norm", l);
+        // concatenate q | k | v rows: they read the same input, so one launch serves all three
+        const HostAffine &q = L.hq, &k = L.hk, &v = L.hv;
+        if (q.K != k.K || q.K != v.K || q.gs != k.gs || q.gs != v.gs || q.bits != k.bits || q.bits != v.bits ||
+            q.param_f32 != k.param_f32 || q.param_f32 != v.param_f32 || q.awq != k.awq || q.awq != v.awq)
+            return fail(IM_ERR_INVALID, "layer %d: q/k/v projections must share K, group size, bit width, parameter dtype and AWQ scales", l);
+        HostAffine f;
+        f.N = q.N + k.N + v.N; f.K = q.K; f.gs = q.gs; f.bits = q.bits; f.param_f32 = q.param_f32; f.have = true; f.awq = q.awq;
+        for (const HostAffine *p : {&q, &k, &v}) {
+            f.q.insert(f.q.end(), p->q.begin(), p->q.end());
+            f.s.insert(f.s.end(), p->s.begin(), p->s.end());
+            f.z.insert(f.z.end(), p->z.begin(), p->z.end());
+            f.s16.insert(f.s16.end(), p->s16.begin(), p->s16.end());
+            f.z16.insert(f.z16.end(), p->z16.begin(), p->z16.end());
+        }
+        IM_TRY(make_weight(m, f, &L.qkv));
+        L.hq = HostAffine(); L.hk = HostAffine(); L.hv = HostAffine();
+        // KV cache of this rank's heads (MetalKvCache, crates/ironmill-inference/src/metal/turboquant/cache.rs:104-354)
+        const size_t rows = (size_t)c.max_batch * m->nkv_l * c.max_seq_len;
+        IM_TRY(m->alloc((void **)&L.kc, rows * hd));
+        IM_TRY(m->alloc((void **)&L.vc, rows * hd));
+        IM_TRY(m->alloc((void **)&L.ks, rows * 4));
+        IM_TRY(m->alloc((void **)&L.vs, rows * 4));
+        IM_TRY(m->alloc((void **)&L.krn, rows * 4));
+        IM_CUDA_CHECK(cudaMemset(L.ks, 0, rows * 4));
+        IM_CUDA_CHECK(cudaMemset(L.vs, 0, rows * 4));
+        IM_CUDA_CHECK(cudaMemset(L.krn, 0, rows * 4));
+        IM_CUDA_CHECK(cudaMemset(L.kc, 0, rows * hd));
+        IM_CUDA_CHECK(cudaMemset(L.vc, 0, rows * hd));
+    }
+    // TurboQuant constants
+    if (m->signs_host.empty()) {
+        m->signs_host.resize(hd);
+        m->qjl_host.resize((size_t)hd * hd);
+        IM_TRY(im_cuda_tq_generate(hd, c.rotation_seed, m->signs_host.data(), m->qjl_host.data()));
+    }
+    IM_TRY(im_cuda_tq_create(static_cast<im_device *>(m->dev), hd, c.tq_bits, m->signs_host.data(), m->qjl_host.data(), nullptr, nullptr, nullptr,
+                             nullptr, &m->tq));
+    // RoPE tables
+    IM_TRY(m->alloc((void **)&m->cosc, (size_t)c.max_seq_len * (hd / 2) * 2));
+    IM_TRY(m->alloc((void **)&m->sinc, (size_t)c.max_seq_len * (hd / 2) * 2));
+    IM_TRY(im_cuda_rope_table(hd, c.max_seq_len, c.rope_theta, c.rotary_dim, m->cosc, m->sinc));
+    // activations
+    m->MT = c.max_batch > kPrefillChunk ? c.max_batch : kPrefillChunk;
+    const size_t MT = m->MT;
+    IM_TRY(m->alloc((void **)&m->hidden, MT * H * 2));
+    IM_TRY(m->alloc((void **)&m->norm_out, MT * H * 2));
+    IM_TRY(m->alloc((void **)&m->residual, MT * H * 2));
+    IM_TRY(m->alloc((void **)&m->qkv, MT * m->qkv_dim * 2));
+    IM_TRY(m->alloc((void **)&m->q_d, MT * m->q_dim * 2));
+    IM_TRY(m->alloc((void **)&m->k_d, MT * m->kv_dim * 2));
+    IM_TRY(m->alloc((void **)&m->v_d, MT * m->kv_dim * 2));
+    IM_TRY(m->alloc((void **)&m->attn_out, MT * m->q_dim * 2));
+    IM_TRY(m->alloc((void **)&m->ffn_down, MT * H * 2));
+    IM_TRY(m->alloc((void **)&m->ffn_gate, MT * m->I_l * 2));
+    IM_TRY(m->alloc((void **)&m->logits, (size_t)c.max_batch * m->vocab_l * 2));
+    if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_all, (size_t)c.max_batch * c.vocab_size * 2));
+    IM_TRY(m->alloc((void **)&m->tokens_dev, MT * 4));
+    IM_TRY(m->alloc((void **)&m->tok_hist, (size_t)c.max_seq_len * c.max_batch * 4));
+    IM_TRY(m->alloc((void **)&m->pos_dev, 64 * 4));
+    IM_TRY(m->alloc((void **)&m->step_dev, 4));
+    IM_CUDA_CHECK(cudaMemset(m->pos_dev, 0, 64 * 4));
+    IM_CUDA_CHECK(cudaMemset(m->step_dev, 0, 4));
+    IM_CUDA_CHECK(cudaMallocHost((void **)&m->tokens_pin, MT * 4));
+    IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_pin, (size_t)c.max_batch * c.vocab_size * 2));
+    // attention scratch for the largest launch: decode at max_batch, or a prefill chunk
+    size_t need = 0;
+    for (int b = 1; b <= c.max_batch; b++) {
+        const size_t s = im_cuda_tq_scratch_bytes(b, 1, m->nh_l, hd, decode_splits(m, b));
+        if (s > need) need = s;
+    }
+    for (int t = 1; t <= kPrefillChunk; t++) {
+        const size_t s = im_cuda_tq_scratch_bytes(1, t, m->nh_l, hd, tq_auto_splits(m->dev, 1, t, m->nkv_l, c.max_seq_len));
+        if (s > need) need = s;
+    }
+    IM_TRY(im_cuda_tq_reserve_scratch(m->tq, need));
+    m->scratch_ref = reinterpret_cast<Tq *>(m->tq)->scratch;
+    m->bytes += need + reinterpret_cast<Tq *>(m->tq)->const_bytes;
+    IM_CUDA_CHECK(cudaDeviceSynchronize());
+    m->finalized = true;
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_reset(im_model *m) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    return set_positions(m, 0);
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_truncate(im_model *m, int pos) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    if (pos < 0 || pos > m->seq_pos) return fail(IM_ERR_BOUNDS, "truncate_to(%d) is outside the current sequence of %d tokens", pos, m->seq_pos);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    return set_positions(m, pos);
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_seq_pos(const im_model *m) { return m ? m->seq_pos : 0; }
+IM_EXPORT int im_cuda_model_max_seq_len(const im_model *m) { return m ? m->cfg.max_seq_len : 0; }
+IM_EXPORT size_t im_cuda_model_memory_bytes(const im_model *m) { return m ? m->bytes : 0; }
+IM_EXPORT int im_cuda_model_step_launches(const im_model *m) { return m ? m->launches_per_step : 0; }
+
+IM_EXPORT size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch) {
+    if (!m || !m->finalized) return 0;
+    const im_model_config &c = m->cfg;
+    size_t b = 0;
+    for (const Layer &L : m->layers) {
+        for (const AffineWeight *w : {L.qkv, L.o, L.gate, L.up, L.down}) {
+            b += (size_t)w->N * w->K * w->bits / 8 + (size_t)w->N * w->G * 4 + (w->awq ? (size_t)w->K * 2 : 0);
+        }
+        b += 2 * (size_t)c.hidden_size * 2;
+        b += (size_t)batch * m->nkv_l * ctx * (2 * c.head_dim + 12);
+    }
+    b += (size_t)m->vocab_l * c.hidden_size * 2 + (size_t)c.hidden_size * 2;
+    return b;
+}
+
+IM_EXPORT int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, int n, float *logits_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && tokens_host && logits_out_host, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(n > 0, "prefill needs at least one token");
+    if (m->seq_pos + n > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->seq_pos, n, m->cfg.max_seq_len);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    cudaStream_t st = m->stream;
+    for (int done = 0; done < n; done += kPrefillChunk) {
+        const int T = n - done < kPrefillChunk ? n - done : kPrefillChunk;
+        memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
+        const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->seq_pos + T);
+        IM_TRY(forward(m, 1, T, splits, st, nullptr));
+        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, 1, T);
+        IM_CUDA_CHECK(cudaGetLastError());
+        IM_CUDA_CHECK(cudaStreamSynchronize(st));  // tokens_pin is reused by the next chunk
+        m->seq_pos += T;
+    }
+    const __half *lg = m->world > 1 ? m->logits_all : m->logits;
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, st));
+    IM_CUDA_CHECK(cudaStreamSynchronize(st));
+    logits_to_host(m, m->logits_pin, 1, logits_out_host);
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_decode_step(im_model *m, const uint32_t *tokens_host, int batch, float *logits_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && tokens_host && logits_out_host, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", batch, m->cfg.max_batch);
+    if (m->seq_pos + 1 > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + 1 exceeds max_seq_len %d", m->seq_pos, m->cfg.max_seq_len);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    cudaStream_t st = m->stream;
+    cudaGraphExec_t g = nullptr;
+    IM_TRY(get_graph(m, batch, &g));
+    memcpy(m->tokens_pin, tokens_host, (size_t)batch * 4);
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)batch * 4, cudaMemcpyHostToDevice, st));
+    IM_CUDA_CHECK(cudaGraphLaunch(g, st));
+    const __half *lg = m->world > 1 ? m->logits_all : m->logits;
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, (size_t)batch * m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, st));
+    IM_CUDA_CHECK(cudaStreamSynchronize(st));
+    m->seq_pos += 1;
+    logits_to_host(m, m->logits_pin, batch, logits_out_host);
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tokens_host, int batch, int n_steps,
+                                          uint32_t *tokens_out_host, float *elapsed_ms_out) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && first_tokens_host, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", batch, m->cfg.max_batch);
+    IM_REQUIRE(n_steps >= 0, "n_steps must be >= 0");
+    if (m->seq_pos + n_steps > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d steps exceeds max_seq_len %d", m->seq_pos, n_steps, m->cfg.max_seq_len);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    cudaStream_t st = m->stream;
+    cudaGraphExec_t g = nullptr;
+    IM_TRY(get_graph(m, batch, &g));
+    memcpy(m->tokens_pin, first_tokens_host, (size_t)batch * 4);
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)batch * 4, cudaMemcpyHostToDevice, st));
+    IM_CUDA_CHECK(cudaMemsetAsync(m->step_dev, 0, 4, st));
+    cudaEvent_t e0, e1;
+    IM_CUDA_CHECK(cudaEventCreate(&e0));
+    IM_CUDA_CHECK(cudaEventCreate(&e1));
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < n_steps; i++) {
+        cudaError_t e = cudaGraphLaunch(g, st);
+        if (e != cudaSuccess) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            return fail(IM_ERR_CUDA, "graph launch failed: %s", cudaGetErrorString(e));
+        }
+    }
+    cudaEventRecord(e1, st);
+    cudaError_t e = cudaStreamSynchronize(st);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e != cudaSuccess) return fail(IM_ERR_CUDA, "decode loop failed: %s", cudaGetErrorString(e));
+    m->seq_pos += n_steps;
+    if (elapsed_ms_out) *elapsed_ms_out = ms;
+    if (tokens_out_host && n_steps > 0)
+        IM_CUDA_CHECK(cudaMemcpy2D(tokens_out_host, (size_t)batch * 4, m->tok_hist, (size_t)m->cfg.max_batch * 4, (size_t)batch * 4, n_steps,
+                                   cudaMemcpyDeviceToHost));
+    return IM_OK;
+    IM_GUARD_END
+}

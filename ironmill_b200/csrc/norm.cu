@@ -82,42 +82,64 @@ __global__ void __launch_bounds__(kNormThreads) embedding_norm_kernel(const uint
     }
 }
 
-// grid (nh + nkv, T), one warp-multiple CTA per head.  with_norm = 0 gives plain RoPE (Llama).
-__global__ void qk_norm_rope_kernel(__half *__restrict__ q, __half *__restrict__ k, const __half *__restrict__ qw,
-                                    const __half *__restrict__ kw, const __half *__restrict__ cosc, const __half *__restrict__ sinc,
-                                    int nh, int nkv, int hd, int rotary_dim, int seq_offset, const int *__restrict__ pos_dev,
-                                    float eps, int with_norm) {
+// grid (nh + nkv [+ nkv], T), one CTA per head.  with_norm = 0 gives plain RoPE (Llama).
+// Reads q/k (and optionally v) with a per-token stride, writes dense [T, heads, hd] outputs;
+// input and output may be the same buffer.  The optional third group of CTAs copies V heads
+// so that a fused QKV projection row can be split into dense Q, K and V in this one launch.
+__global__ void qk_norm_rope_kernel(const QkRopeArgs a) {
     __shared__ float sh[32];
     const int slot = blockIdx.x, t = blockIdx.y;
-    const bool is_q = slot < nh;
-    const int h = is_q ? slot : slot - nh, heads = is_q ? nh : nkv;
-    __half *p = (is_q ? q : k) + ((size_t)t * heads + h) * hd;
-    const __half *w = is_q ? qw : kw;
+    const int hd = a.hd;
+    if (slot >= a.nh + a.nkv) {  // V copy
+        const int h = slot - a.nh - a.nkv;
+        const __half *src = a.v_in + (size_t)t * a.v_stride + (size_t)h * hd;
+        __half *dst = a.v_out + ((size_t)t * a.nkv + h) * hd;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
+        return;
+    }
+    const bool is_q = slot < a.nh;
+    const int h = is_q ? slot : slot - a.nh, heads = is_q ? a.nh : a.nkv;
+    const __half *src = (is_q ? a.q_in + (size_t)t * a.q_stride : a.k_in + (size_t)t * a.k_stride) + (size_t)h * hd;
+    __half *dst = (is_q ? a.q_out : a.k_out) + ((size_t)t * heads + h) * hd;
+    const __half *w = is_q ? a.qw : a.kw;
     float rms_inv = 1.0f;
-    if (with_norm) {
+    if (a.with_norm) {
         float ss = 0.0f;
         for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-            const float v = __half2float(p[d]);
+            const float v = __half2float(src[d]);
             ss += v * v;
         }
         const float tot = block_sum(ss, sh);
-        rms_inv = rsqrtf(tot / (float)hd + eps);
+        rms_inv = rsqrtf(tot / (float)hd + a.eps);
     }
-    const int half_rot = rotary_dim / 2, half_dim = hd / 2;
-    const int pos = seq_offset + (pos_dev ? *pos_dev : 0) + t;
+    const int half_rot = a.rotary_dim / 2, half_dim = hd / 2;
+    const int seq = t / a.tokens_per_seq, tt = t % a.tokens_per_seq;
+    const int pos = a.seq_offset + (a.pos_dev ? a.pos_dev[seq] : 0) + tt;
     for (int d = threadIdx.x; d < half_rot; d += blockDim.x) {
-        float lo = __half2float(p[d]), hi = __half2float(p[d + half_rot]);
-        if (with_norm) {
+        float lo = __half2float(src[d]), hi = __half2float(src[d + half_rot]);
+        if (a.with_norm) {
             lo = lo * rms_inv * __half2float(w[d]);
             hi = hi * rms_inv * __half2float(w[d + half_rot]);
         }
-        const float c = __half2float(cosc[(size_t)pos * half_dim + d]), s = __half2float(sinc[(size_t)pos * half_dim + d]);
-        p[d] = __float2half_rn(lo * c - hi * s);
-        p[d + half_rot] = __float2half_rn(lo * s + hi * c);
+        const float c = __half2float(a.cosc[(size_t)pos * half_dim + d]), s = __half2float(a.sinc[(size_t)pos * half_dim + d]);
+        dst[d] = __float2half_rn(lo * c - hi * s);
+        dst[d + half_rot] = __float2half_rn(lo * s + hi * c);
     }
-    if (with_norm)
-        for (int d = threadIdx.x + rotary_dim; d < hd; d += blockDim.x)
-            p[d] = __float2half_rn(__half2float(p[d]) * rms_inv * __half2float(w[d]));
+    for (int d = threadIdx.x + a.rotary_dim; d < hd; d += blockDim.x) {
+        float v = __half2float(src[d]);
+        if (a.with_norm) v = v * rms_inv * __half2float(w[d]);
+        dst[d] = __float2half_rn(v);
+    }
+}
+
+int launch_qk_rope(const QkRopeArgs &a, int T, cudaStream_t st) {
+    const int slots = a.nh + a.nkv + (a.v_in ? a.nkv : 0);
+    if (T == 0 || slots == 0) return IM_OK;
+    const int threads = a.hd >= 256 ? 128 : (a.hd / 2 >= 32 ? (a.hd / 2 + 31) / 32 * 32 : 32);
+    dim3 grid(slots, T);
+    qk_norm_rope_kernel<<<grid, threads, 0, st>>>(a);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
 }
 
 }  // namespace im
@@ -178,29 +200,24 @@ IM_EXPORT int im_cuda_embedding_norm(const uint32_t *tokens_dev, const void *tab
     IM_GUARD_END
 }
 
-namespace im {
-int launch_qk_norm_rope(__half *q, __half *k, const __half *qw, const __half *kw, const __half *cosc, const __half *sinc, int nh,
-                        int nkv, int hd, int rotary_dim, int seq_offset, const int *pos_dev, int T, float eps, int with_norm,
-                        cudaStream_t st) {
-    if (T == 0 || nh + nkv == 0) return IM_OK;
-    int threads = hd >= 256 ? 128 : (hd / 2 >= 32 ? (hd / 2 + 31) / 32 * 32 : 32);
-    dim3 grid(nh + nkv, T);
-    qk_norm_rope_kernel<<<grid, threads, 0, st>>>(q, k, qw, kw, cosc, sinc, nh, nkv, hd, rotary_dim, seq_offset, pos_dev, eps, with_norm);
-    IM_CUDA_CHECK(cudaGetLastError());
-    return IM_OK;
-}
-}  // namespace im
-
 IM_EXPORT int im_cuda_qk_norm_rope(void *q_dev, void *k_dev, const void *q_norm_w_dev, const void *k_norm_w_dev, const void *cos_dev,
                                    const void *sin_dev, int nh, int nkv, int head_dim, int rotary_dim, int seq_offset, int T, float eps,
                                    void *stream) {
     IM_GUARD_BEGIN
     IM_REQUIRE(q_dev && k_dev && q_norm_w_dev && k_norm_w_dev && cos_dev && sin_dev, "bad argument");
     IM_REQUIRE(head_dim > 0 && head_dim % 2 == 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim, "bad head_dim / rotary_dim");
-    return launch_qk_norm_rope(static_cast<__half *>(q_dev), static_cast<__half *>(k_dev), static_cast<const __half *>(q_norm_w_dev),
-                               static_cast<const __half *>(k_norm_w_dev), static_cast<const __half *>(cos_dev),
-                               static_cast<const __half *>(sin_dev), nh, nkv, head_dim, rotary_dim ? rotary_dim : head_dim, seq_offset,
-                               nullptr, T, eps, 1, as_stream(stream));
+    QkRopeArgs a{};
+    a.q_in = a.q_out = static_cast<__half *>(q_dev);
+    a.k_in = a.k_out = static_cast<__half *>(k_dev);
+    a.q_stride = nh * head_dim;
+    a.k_stride = nkv * head_dim;
+    a.qw = static_cast<const __half *>(q_norm_w_dev);
+    a.kw = static_cast<const __half *>(k_norm_w_dev);
+    a.cosc = static_cast<const __half *>(cos_dev);
+    a.sinc = static_cast<const __half *>(sin_dev);
+    a.nh = nh; a.nkv = nkv; a.hd = head_dim; a.rotary_dim = rotary_dim ? rotary_dim : head_dim;
+    a.seq_offset = seq_offset; a.tokens_per_seq = T > 0 ? T : 1; a.eps = eps; a.with_norm = 1;
+    return launch_qk_rope(a, T, as_stream(stream));
     IM_GUARD_END
 }
 
@@ -209,9 +226,14 @@ IM_EXPORT int im_cuda_rope(void *qk_dev, const void *cos_dev, const void *sin_de
     IM_GUARD_BEGIN
     IM_REQUIRE(qk_dev && cos_dev && sin_dev, "bad argument");
     IM_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "bad head_dim");
-    return launch_qk_norm_rope(static_cast<__half *>(qk_dev), nullptr, nullptr, nullptr, static_cast<const __half *>(cos_dev),
-                               static_cast<const __half *>(sin_dev), heads, 0, head_dim, head_dim, seq_offset, nullptr, T, 0.0f, 0,
-                               as_stream(stream));
+    QkRopeArgs a{};
+    a.q_in = a.q_out = static_cast<__half *>(qk_dev);
+    a.q_stride = heads * head_dim;
+    a.cosc = static_cast<const __half *>(cos_dev);
+    a.sinc = static_cast<const __half *>(sin_dev);
+    a.nh = heads; a.nkv = 0; a.hd = head_dim; a.rotary_dim = head_dim;
+    a.seq_offset = seq_offset; a.tokens_per_seq = T > 0 ? T : 1; a.with_norm = 0;
+    return launch_qk_rope(a, T, as_stream(stream));
     IM_GUARD_END
 }
 

@@ -25,15 +25,6 @@
 
 namespace im {
 
-struct Tq {
-    Device *dev = nullptr;
-    int hd = 0, n_bits = 0, k_levels = 0, v_levels = 0;
-    float *signs = nullptr, *qjl = nullptr, *k_cb = nullptr, *k_bd = nullptr, *v_cb = nullptr, *v_bd = nullptr;
-    float *scratch = nullptr;
-    size_t scratch_bytes = 0;
-    size_t const_bytes = 0;
-};
-
 // ---------------------------------------------------------------- host: Lloyd-Max codebook
 namespace lm {
 static double poly(const double *c, int n, double x) {
