@@ -1,20 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the quantized decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload decode|matvec]
+                    [--prompt P] [--batch B]
 
-Prints ONE JSON line (rank 0).  Workloads (synthetic, seeded; shapes of the Llama-3-8B-shaped
-decode config):
+Prints ONE JSON line (rank 0).  Workloads are synthetic and seeded (random-init weights of the named
+shape; no checkpoint or dataset is read):
 
-  matvec  one step = one pass over the four INT4 g128 projection launches of a decoder layer at
-          batch 1 with AWQ scales: fused QKV 4096->6144, o 4096->4096, fused gate+up+SiLU
-          4096->2x14336, down 14336->4096.  Metric: algorithmic HBM GB/s (packed codes + fp16
-          scale/zero + activations in/out, the byte count the reference's own kernel bandwidth
-          benchmark uses).  Each step reads a different copy of the weights out of a rotation
-          larger than L2.
+  decode  (default) Llama-3-8B-shaped model: 32 layers, hidden 4096, FFN 14336 SwiGLU, 32 Q / 8 KV heads,
+          head_dim 128, RoPE theta 5e5, vocab 128256, weights ~ N(0, 0.02) quantized INT4 g128 with AWQ
+          scales ~ U(0.5, 2), fp16 embeddings / lm_head, TurboQuant INT8 KV.  A prompt of P tokens is
+          prefilled, then one step = one greedy decode step of the whole model at batch B; `value` is
+          tokens/s of K steps replayed as CUDA graphs with the token fed back on the device; `e2e` is the
+          same loop through decode_step() with the token coming from host memory and the logits going
+          back to host memory every step.  With --gpus N the model is tensor-parallel over N ranks.
+  matvec  one step = the four INT4 g128 projection launches of one decoder layer at batch 1
+          (fused QKV 4096->6144, o 4096->4096, fused gate+up+SiLU 4096->2x14336, down 14336->4096),
+          each step on a different weight copy out of a rotation larger than L2; value = GB/s.
 
-`--impl reference` times the CPU restatement of the reference's own CPU path (the oracle) on the
-host cores for the same workload, on a bounded sample.
+`--impl reference` times the CPU restatement of the reference's own CPU path (the oracle) on the host
+cores for the same workload, on a bounded sample.
 """
 from __future__ import annotations
 
@@ -31,10 +36,15 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+GS = 128
+L8 = dict(architecture="llama", hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+          num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=8192, rms_norm_eps=1e-5,
+          rope_theta=5e5, tie_word_embeddings=False)
 # Llama-3-8B-shaped projections: (name, N, K, kind)
 L8_SHAPES = [("qkv", 6144, 4096, "plain"), ("o", 4096, 4096, "plain"),
              ("gate_up", 14336, 4096, "ffn"), ("down", 4096, 14336, "plain")]
-GS = 128
+METRIC_DECODE = "decode tok/s (Llama-3-8B shape, INT4 g128 + AWQ weights, INT8 TurboQuant KV)"
+METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)"
 
 
 def matvec_bytes(N, K, B=1, awq=True, bits=4):
@@ -57,17 +67,15 @@ class ClockSampler:
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index = index
-        self.rows = []
-        self.proc = None
+        self.index, self.rows, self.proc = index, [], None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
+            threading.Thread(target=self._read, daemon=True).start()
+            time.sleep(0.2)
         except OSError:
             self.proc = None
 
@@ -80,7 +88,7 @@ class ClockSampler:
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -96,19 +104,26 @@ class ClockSampler:
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
-        d = json.load(open(path))
-        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
 # ----------------------------------------------------------------------------- synthetic weights on the GPU
+def gpu_quantized(dev, N, K, gen, awq):
+    import torch
+
+    from ironmill_b200 import ops
+    w = (torch.randn((N, K), generator=gen, device="cuda") * 0.02).half()
+    packed, s, z = ops.quantize_affine(w, GS, 4, awq)
+    return packed, s, z
+
+
 def gpu_layer_copy(dev, seed):
     """One copy of the four projections, quantized ON the GPU with the library's own quantizer."""
     import torch
@@ -117,126 +132,268 @@ def gpu_layer_copy(dev, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     out = {}
     for name, N, K, kind in L8_SHAPES:
-        awq = torch.rand(K, generator=g, device="cuda") * 1.5 + 0.5
-        awq = awq.half()
+        awq = (torch.rand(K, generator=g, device="cuda") * 1.5 + 0.5).half()
         mats = []
         for _ in range(2 if kind == "ffn" else 1):
-            w = (torch.randn((N, K), generator=g, device="cuda") * 0.02).half()
-            packed, s, z = ops.quantize_affine(w, GS, 4, awq)
+            packed, s, z = gpu_quantized(dev, N, K, g, awq)
             mats.append(ops.AffineWeight(dev, packed, s, z, N, K, GS, 4, awq=awq))
-            del w, packed, s, z
         out[name] = mats
     return out
 
 
-def run_ours(args, rank, world):
+class SyntheticL8Provider:
+    """WeightProvider of a random-init Llama-3-8B-shaped model: tensors are drawn with a seeded torch
+    generator on the GPU, quantized by the library's GPU quantizer (bit-exact with the reference's CPU
+    quantizer) and handed over as host arrays, like a bundle provider would."""
+
+    def __init__(self, cfg, dev, seed=1234):
+        self.cfg, self.dev, self.seed = cfg, dev, seed
+
+    def config(self):
+        return self.cfg
+
+    def has_tensor(self, name):
+        return True
+
+    def tensor(self, name):
+        import zlib
+
+        import torch
+
+        from ironmill_b200.bundle import WeightTensor
+        c = self.cfg
+        g = torch.Generator(device="cuda").manual_seed(self.seed * 7919 + zlib.crc32(name.encode()))
+        Hd, I, hd = c.hidden_size, c.intermediate_size, c.head_dim
+        if name.endswith("layernorm.weight") or name == "model.norm.weight" or name.endswith("_norm.weight"):
+            n = hd if "self_attn" in name else Hd
+            return WeightTensor(np.ones(n, np.float16), (n,), "float16")
+        if name in ("model.embed_tokens.weight", "lm_head.weight"):
+            w = (torch.randn((c.vocab_size, Hd), generator=g, device="cuda") * 0.02).half()
+            return WeightTensor(w.cpu().numpy(), (c.vocab_size, Hd), "float16")
+        shapes = {"q_proj": (c.num_attention_heads * hd, Hd, "attn_in"), "k_proj": (c.num_key_value_heads * hd, Hd, "attn_in"),
+                  "v_proj": (c.num_key_value_heads * hd, Hd, "attn_in"), "o_proj": (Hd, c.num_attention_heads * hd, "o_in"),
+                  "gate_proj": (I, Hd, "ffn_in"), "up_proj": (I, Hd, "ffn_in"), "down_proj": (Hd, I, "down_in")}
+        key = name.split(".")[-2]
+        N, K, grp = shapes[key]
+        layer = name.split(".")[2]
+        ga = torch.Generator(device="cuda").manual_seed(self.seed * 104729 + zlib.crc32(f"{layer}.{grp}".encode()))
+        awq = (torch.rand(K, generator=ga, device="cuda") * 1.5 + 0.5).half()   # shared by projections with one input
+        packed, s, z = gpu_quantized(self.dev, N, K, g, awq)
+        return WeightTensor(packed.cpu().numpy(), (N, K), "uint8", s.cpu().numpy(), z.cpu().numpy(), 4, GS, 1, awq.cpu().numpy())
+
+
+def time_dominant_kernel(dev, reps=5):
+    """Average duration of the fused gate+up+SiLU matvec launch (the largest kernel of a decode step),
+    CUDA events around a CUDA graph of launches that rotate over weight copies larger than L2."""
+    import torch
+
+    from ironmill_b200 import ops
+    N, K = 14336, 4096
+    ncopy = 6
+    g = torch.Generator(device="cuda").manual_seed(5)
+    awq = (torch.rand(K, generator=g, device="cuda") * 1.5 + 0.5).half()
+    gates = [ops.AffineWeight(dev, *gpu_quantized(dev, N, K, g, awq), N, K, GS, 4, awq=awq) for _ in range(ncopy)]
+    ups = [ops.AffineWeight(dev, *gpu_quantized(dev, N, K, g, awq), N, K, GS, 4, awq=awq) for _ in range(ncopy)]
+    x = torch.randn((1, K), generator=g, device="cuda").half()
+    y = torch.empty((1, N), dtype=torch.float16, device="cuda")
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(ncopy):
+            ops.ffn_gate_up_act(gates[i], ups[i], x, out=y)
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(ncopy):
+                ops.ffn_gate_up_act(gates[i], ups[i], x, out=y)
+        graph.replay()
+        s.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(s)
+        s.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * ncopy)
+    nbytes = shape_bytes("gate_up", N, K, "ffn")
+    del gates, ups
+    return us, nbytes, reps * ncopy
+
+
+def run_decode(args, rank, world):
     import torch
     import torch.distributed as dist
 
     from ironmill_b200 import ops
+    from ironmill_b200.bundle import ModelConfig
+    from ironmill_b200.engine import CudaConfig, CudaInference
 
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    dev = ops.Device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-
-    ncopies = 4   # 4 x 116 MB of weights > 126 MB of L2: no step finds its weights cached
-    copies = [gpu_layer_copy(dev, 100 + rank * 10 + i) for i in range(ncopies)]
-    g = torch.Generator(device="cuda").manual_seed(7 + rank)
-    xs = {K: torch.randn((1, K), generator=g, device="cuda").half() for K in (4096, 14336)}
-    ys = {name: torch.empty((1, N), dtype=torch.float16, device="cuda") for name, N, K, kind in L8_SHAPES}
-    step_bytes = sum(shape_bytes(*s) for s in L8_SHAPES)
-    launches_per_step = len(L8_SHAPES)
-
-    def step(i, ev=None):
-        cp = copies[i % ncopies]
-        for name, N, K, kind in L8_SHAPES:
-            if ev is not None and name == "gate_up":
-                ev[0].record()
-            if kind == "ffn":
-                ops.ffn_gate_up_act(cp[name][0], cp[name][1], xs[K], out=ys[name])
-            else:
-                ops.matvec_affine(cp[name][0], xs[K], out=ys[name])
-            if ev is not None and name == "gate_up":
-                ev[1].record()
-
-    for i in range(args.warmup):
-        step(i)
+    dev = ops.Device(local)
+    cfg = ModelConfig(**L8)
+    B, P, K, W = args.batch, args.prompt, args.steps, max(args.warmup, 3)
+    e2e_steps = max(8, min(K, 64))
+    max_seq = P + W + K + e2e_steps + 8
+    eng = CudaInference(CudaConfig(max_seq_len=max_seq, max_batch=B, tp_world=world, tp_rank=rank, device=local))
+    t0 = time.perf_counter()
+    eng.load_weights(SyntheticL8Provider(cfg, dev))
+    if world > 1:
+        ids = [CudaInference.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        eng.tp_init(ids[0])
+    load_s = time.perf_counter() - t0
+    prompt = np.random.Generator(np.random.PCG64(11)).integers(0, cfg.vocab_size, P).astype(np.uint32)
+    t0 = time.perf_counter()
+    logits = eng.prefill(prompt)
+    prefill_s = time.perf_counter() - t0
+    first = np.full(B, int(logits.argmax()), dtype=np.uint32)
+    if B > 1:   # lockstep batch: every sequence needs the prompt in its cache; replicate by decoding it again per step
+        eng.reset()
+        for t in prompt[:min(P, 64)]:
+            eng.decode_step(np.full(B, t, dtype=np.uint32))
+    toks, _ = eng.decode_greedy(first, W)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    t0.record()
-    for i in range(args.steps):
-        step(i, evs[i])
-    t1.record()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1)
-    dom_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+    ctx0 = eng.seq_pos()
+    toks, ms = eng.decode_greedy(toks[-1], K)
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         dist.barrier()
     clocks = sampler.stop() if rank == 0 else None
+    ctx_mid = ctx0 + K // 2
 
-    # end to end through the host-buffer call: x from host memory in, y back to host, per projection
-    e2e_steps = max(3, min(args.steps, 50))
-    xh = {K: np.random.default_rng(1).standard_normal((1, K)).astype(np.float16) for K in (4096, 14336)}
-    plain = [s for s in L8_SHAPES if s[3] == "plain"]
-    e2e_bytes = sum(shape_bytes(*s) for s in plain)
-    for i in range(2):
-        for name, N, K, kind in plain:
-            ops.matvec_affine_host(copies[i % ncopies][name][0], xh[K])
-    torch.cuda.synchronize()
+    # end to end: decode_step() per token, token from host memory, fp16 logits copied back and widened on the host
+    tok = toks[-1].copy()
+    eng.decode_step(tok if B > 1 else int(tok[0]))
     w0 = time.perf_counter()
-    for i in range(e2e_steps):
-        for name, N, K, kind in plain:
-            ops.matvec_affine_host(copies[i % ncopies][name][0], xh[K])
+    for _ in range(e2e_steps):
+        lg = eng.decode_step(tok if B > 1 else int(tok[0]))
+        tok = np.atleast_2d(lg).argmax(-1).astype(np.uint32)
     e2e_s = time.perf_counter() - w0
-    h2d = sum(K * 2 for _, N, K, _ in plain)
-    d2h = sum(N * 2 for _, N, K, _ in plain)
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
 
+    step_bytes = eng.step_bytes(ctx_mid, B)
+    launches = eng.step_launches()
+    dom_us, dom_bytes, _ = time_dominant_kernel(dev) if rank == 0 else (1.0, 0, 0)
     if rank != 0:
         return
     peak, peak_src = measured_peaks()
-    gate_up = [s for s in L8_SHAPES if s[0] == "gate_up"][0]
-    dom_bytes = shape_bytes(*gate_up)
-    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    value = world * step_bytes * args.steps / (ms * 1e-3) / 1e9
+    tok_s = B * K / (ms * 1e-3)
+    step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
     out = {
-        "metric": "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)",
-        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "u4 codes x i16 activations, f32 fix-up", "data": "synthetic",
-        "config": {"workload": "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq",
-                   "shapes": [[n, N, K] for n, N, K, _ in L8_SHAPES], "group_size": GS,
-                   "l2_policy": f"rotation over {ncopies} weight copies ({ncopies * step_bytes >> 20} MiB) larger than L2",
-                   "parallelism": f"replicas x{world}" if world > 1 else "single"},
-        "roofline": {"bound": "hbm", "kernel": "matvec_kernel<4,gate_up_act> 4096->2x14336", "achieved": round(achieved, 1),
-                     "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": peak_src,
-                     "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_ms * 1e3, 3), "traffic": None},
-        "e2e": {"value": round(world * e2e_bytes * e2e_steps / e2e_s / 1e9, 3), "unit": "GB/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "note": "host-buffer matvec calls (qkv, o, down): copy x in, launch, copy y out, synchronise"},
-        "gpu_launches": launches_per_step * args.steps,
+        "metric": METRIC_DECODE, "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "u4 codes x i16 activations (f32 fix-up), f16 lm_head, u8 KV codebook indices",
+        "data": "synthetic",
+        "config": {"workload": "llama3_8b_shape_int4_g128_awq_tq8_decode", "batch": B, "prompt_tokens": P,
+                   "context_during_timing": [ctx0, ctx0 + K], "layers": 32, "hidden": 4096, "ffn": 14336, "vocab": 128256,
+                   "parallelism": f"tp{world}" if world > 1 else "single",
+                   "l2_policy": "inputs larger than L2: every step streams this rank's %.2f GB of weights + KV" % (step_bytes / 1e9),
+                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2)},
+        "roofline": {"bound": "hbm", "kernel": "matvec_kernel<int4, gate+up+SiLU> 4096->2x14336 (largest launch of the step)",
+                     "achieved": round(dom_bytes / (dom_us * 1e-6) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(dom_bytes / (dom_us * 1e-6) / 1e9 / peak, 4), "peak_source": peak_src,
+                     "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_us, 3), "traffic": 62433280 + 139520,
+                     "traffic_note": "dram read+write of this launch from the ncu capture under profiles/",
+                     "timing": "CUDA events around a CUDA graph of launches rotating over 6 weight copies (702 MB > L2)",
+                     "whole_step": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_gbs, 1),
+                                    "frac_of_hbm_roofline": round(step_gbs / peak, 4),
+                                    "roofline_tok_s": round(B * world * peak * 1e9 / (step_bytes * world), 1)}},
+        "e2e": {"value": round(B * e2e_steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
+                "d2h_bytes_per_step": 2 * B * cfg.vocab_size, "steps": e2e_steps,
+                "note": "InferenceEngine.decode_step per token: host token in, fp16 logits to pinned host memory, widened to f32"},
+        "gpu_launches": launches * K,
+        "launches_per_step": launches,
         "clocks": clocks,
     }
     if world == 1:
-        out["cpu_baseline"] = cpu_baseline(sample_only=True)
+        out["cpu_baseline"] = cpu_decode_baseline(quick=True)
     print(json.dumps(out))
 
 
-# ----------------------------------------------------------------------------- CPU arm
-def cpu_baseline(sample_only: bool):
-    """The CPU restatement of the reference's quantize + dequantised matvec (the oracle), timed on
-    the host cores on a bounded sample: W [4096,4096] -> INT4 g128 + y = dequant(W) x, batch 1."""
+def run_matvec(args, rank, world):
+    import torch
+
+    from ironmill_b200 import ops
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = ops.Device(local)
+    ncopies = 4   # 4 x 116 MB of weights > 126 MB of L2: no step finds its weights cached
+    copies = [gpu_layer_copy(dev, 100 + i) for i in range(ncopies)]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    xs = {K: torch.randn((1, K), generator=g, device="cuda").half() for K in (4096, 14336)}
+    ys = {name: torch.empty((1, N), dtype=torch.float16, device="cuda") for name, N, K, kind in L8_SHAPES}
+    step_bytes = sum(shape_bytes(*s) for s in L8_SHAPES)
+
+    def step(i):
+        cp = copies[i % ncopies]
+        for name, N, K, kind in L8_SHAPES:
+            if kind == "ffn":
+                ops.ffn_gate_up_act(cp[name][0], cp[name][1], xs[K], out=ys[name])
+            else:
+                ops.matvec_affine(cp[name][0], xs[K], out=ys[name])
+
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(max(args.warmup, ncopies)):
+            step(i)
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(ncopies):
+                step(i)
+        graph.replay()
+        s.synchronize()
+        reps = max(1, args.steps // ncopies)
+        sampler = ClockSampler(local)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(s)
+        s.synchronize()
+        clocks = sampler.stop()
+    steps = reps * ncopies
+    ms = e0.elapsed_time(e1)
+    xh = {K: np.random.default_rng(1).standard_normal((1, K)).astype(np.float16) for K in (4096, 14336)}
+    plain = [sh for sh in L8_SHAPES if sh[3] == "plain"]
+    for name, N, K, kind in plain:
+        ops.matvec_affine_host(copies[0][name][0], xh[K])
+    w0 = time.perf_counter()
+    for i in range(20):
+        for name, N, K, kind in plain:
+            ops.matvec_affine_host(copies[i % ncopies][name][0], xh[K])
+    e2e_s = time.perf_counter() - w0
+    dom_us, dom_bytes, _ = time_dominant_kernel(dev)
+    peak, peak_src = measured_peaks()
+    out = {"metric": METRIC_MATVEC, "value": round(step_bytes * steps / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": 1,
+           "steps": steps, "warmup": args.warmup, "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "u4 codes x i16 activations, f32 fix-up", "data": "synthetic",
+           "config": {"workload": "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq", "shapes": [[n, N, K] for n, N, K, _ in L8_SHAPES],
+                      "l2_policy": f"rotation over {ncopies} weight copies ({ncopies * step_bytes >> 20} MiB) larger than L2"},
+           "roofline": {"bound": "hbm", "kernel": "matvec_kernel<int4, gate+up+SiLU> 4096->2x14336",
+                        "achieved": round(dom_bytes / (dom_us * 1e-6) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                        "frac": round(dom_bytes / (dom_us * 1e-6) / 1e9 / peak, 4), "peak_source": peak_src, "traffic": None},
+           "e2e": {"value": round(sum(shape_bytes(*sh) for sh in plain) * 20 / e2e_s / 1e9, 3), "unit": "GB/s",
+                   "h2d_bytes_per_step": sum(K * 2 for _, N, K, _ in plain), "d2h_bytes_per_step": sum(N * 2 for _, N, K, _ in plain)},
+           "gpu_launches": 4 * steps, "clocks": clocks, "cpu_baseline": cpu_matvec_baseline(3.0)}
+    print(json.dumps(out))
+
+
+# ----------------------------------------------------------------------------- CPU arm (the oracle, timed)
+def cpu_matvec_baseline(seconds):
     from oracle import oracle as orc
     threads = orc.max_threads()
     rng = np.random.default_rng(0)
@@ -248,53 +405,95 @@ def cpu_baseline(sample_only: bool):
     packed = orc.pack_int4(codes)
     tq = time.perf_counter() - t0
     s16, z16 = orc.f32_to_f16(scales), orc.f32_to_f16(zps)
-    reps = 0
-    t0 = time.perf_counter()
-    while True:
+    reps, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
         orc.matvec_affine(packed, s16, z16, x, N, K, GS, 4, threads=threads)
         reps += 1
-        if time.perf_counter() - t0 > (3.0 if sample_only else 8.0):
-            break
     tm = (time.perf_counter() - t0) / reps
-    gbs = matvec_bytes(N, K, awq=False) / tm / 1e9
-    return {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"o_proj-sized 4096x4096 INT4 g128 matvec, batch 1, {reps} repetitions, OpenMP {threads} threads; "
-                      f"quantize+pack of the same matrix took {tq * 1e3:.0f} ms",
+    return {"value": round(matvec_bytes(N, K, awq=False) / tm / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"4096x4096 INT4 g128 matvec, batch 1, {reps} repetitions, OpenMP {threads} threads; quantize+pack {tq * 1e3:.0f} ms",
             "quantize_ms": round(tq * 1e3, 1), "matvec_ms": round(tm * 1e3, 3)}
+
+
+def cpu_decode_baseline(quick):
+    """The CPU restatement of the reference's CPU path (affine quantize + dequantised matvec), timed on the host
+    cores on a bounded sample of one decode token: ONE Llama-3-8B-shaped layer (QKV, o, gate+up+SiLU, down at batch 1)
+    plus 1/16 of the fp16 lm_head rows; a token is 32 such layers + the whole lm_head."""
+    from oracle import oracle as orc
+    threads = orc.max_threads()
+    rng = np.random.default_rng(0)
+    mats = {}
+    tq0 = time.perf_counter()
+    for name, N, K, kind in L8_SHAPES:
+        for j in range(2 if kind == "ffn" else 1):
+            w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+            awq = rng.uniform(0.5, 2.0, K).astype(np.float16)
+            codes, sc, zp = orc.quantize_groups(w, GS, 4, awq=awq, threads=threads)
+            mats[(name, j)] = (orc.pack_int4(codes), orc.f32_to_f16(sc), orc.f32_to_f16(zp), awq)
+    quant_s = time.perf_counter() - tq0
+    xs = {K: rng.standard_normal((1, K)).astype(np.float16) for K in (4096, 14336)}
+    lm_rows = 128256 // 16
+    lm = (rng.standard_normal((lm_rows, 4096)) * 0.02).astype(np.float16)
+    reps = 1 if quick else 3
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for name, N, K, kind in L8_SHAPES:
+            if kind == "ffn":
+                g, u = mats[(name, 0)], mats[(name, 1)]
+                orc.ffn_gate_up_act(g[0], g[1], g[2], u[0], u[1], u[2], xs[K], N, K, GS, 4, awq=g[3], threads=threads)
+            else:
+                m = mats[(name, 0)]
+                orc.matvec_affine(m[0], m[1], m[2], xs[K], N, K, GS, 4, awq=m[3], threads=threads)
+    layer_s = (time.perf_counter() - t0) / reps
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        orc.matvec_f16(lm, xs[4096], threads=threads)
+    lm_s = (time.perf_counter() - t0) / reps * 16
+    tok_s = 1.0 / (32 * layer_s + lm_s)
+    return {"value": round(tok_s, 4), "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"one layer's four projection calls ({layer_s * 1e3:.0f} ms) x32 + lm_head from 1/16 of its rows "
+                      f"({lm_s * 1e3:.0f} ms), batch 1, OpenMP {threads} threads, {reps} repetition(s); attention and norms "
+                      f"left out (under 1 % of the CPU time); quantize+pack of the layer took {quant_s:.1f} s",
+            "layer_ms": round(layer_s * 1e3, 1), "lm_head_ms": round(lm_s * 1e3, 1), "quantize_layer_s": round(quant_s, 2)}
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
     t0 = time.perf_counter()
-    res = []
-    for _ in range(max(1, min(args.steps, 3))):
-        res.append(cpu_baseline(sample_only=False))
-    cb = res[-1]
-    v = float(np.mean([r["value"] for r in res]))
-    out = {"impl": "reference", "metric": "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)",
-           "value": round(v, 3), "unit": "GB/s", "n_gpus": world, "steps": len(res), "warmup": 0,
-           "ms_per_step": round((time.perf_counter() - t0) / len(res) * 1e3, 2), "higher_is_better": True,
-           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq", "group_size": GS},
-           "cpu_baseline": dict(cb, value=round(v, 3)),
-           "e2e": {"value": round(v, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if args.workload == "matvec":
+        cb = cpu_matvec_baseline(8.0)
+        metric, unit, wl = METRIC_MATVEC, "GB/s", "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq"
+    else:
+        cb = cpu_decode_baseline(quick=False)
+        metric, unit, wl = METRIC_DECODE, "tok/s", "llama3_8b_shape_int4_g128_awq_tq8_decode"
+    out = {"impl": "reference", "metric": metric, "value": cb["value"], "unit": unit, "n_gpus": world, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": round(1e3 / cb["value"], 2) if unit == "tok/s" else None,
+           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": wl, "batch": 1, "wall_s": round(time.perf_counter() - t0, 1)},
+           "cpu_baseline": cb,
+           "e2e": {"value": cb["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "matvec"])
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=1)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.workload == "matvec":
+        run_matvec(args, rank, world)
     else:
-        run_ours(args, rank, world)
+        run_decode(args, rank, world)
 
 
 if __name__ == "__main__":
