@@ -283,6 +283,7 @@ def run_decode(args, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
+    prof = eng.profile_step(B)
     step_bytes = eng.step_bytes(ctx_mid, B)
     launches = eng.step_launches()
     dom_us, dom_bytes, _ = time_dominant_kernel(dev) if rank == 0 else (1.0, 0, 0)
@@ -315,6 +316,7 @@ def run_decode(args, rank, world):
                 "note": "InferenceEngine.decode_step per token: host token in, fp16 logits to pinned host memory, widened to f32"},
         "gpu_launches": launches * K,
         "launches_per_step": launches,
+        "step_profile_ms": {k: round(v, 4) for k, v in prof.items()},
         "clocks": clocks,
     }
     if world == 1:

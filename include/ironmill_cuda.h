@@ -270,6 +270,11 @@ size_t im_cuda_model_memory_bytes(const im_model *m);
 size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
 /* Number of kernel launches in one captured decode step. */
 int im_cuda_model_step_launches(const im_model *m);
+/* Per-category GPU time of one eager decode step at the current position, which is not advanced
+ * (MetalConfig.kernel_timing, crates/ironmill-inference/src/metal/pipeline.rs:353-422,1215-1234).
+ * ms_by_category[11]: embed, qkv projection, rope, kv write, attention, o projection, residual+norm,
+ * gate+up+act, down projection, collectives, final norm + lm_head. */
+int im_cuda_model_profile_step(im_model *m, int batch, float *ms_by_category, int n_categories);
 
 #ifdef __cplusplus
 }

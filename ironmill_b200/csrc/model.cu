@@ -274,6 +274,24 @@ static int tp_allreduce(Model *m, __half *buf, size_t count, cudaStream_t st) {
 #endif
 }
 
+// Per-category GPU timing of one eager step (the counterpart of MetalConfig.kernel_timing /
+// the profile-metal feature, crates/ironmill-inference/src/metal/pipeline.rs:353-422,1215-1234):
+// an event is recorded after each group of launches and the interval is charged to its category.
+enum ProfCat { kCatEmbed = 0, kCatQkv, kCatRope, kCatKvWrite, kCatAttn, kCatOProj, kCatResNorm, kCatFfn, kCatDown, kCatComm, kCatHead, kCatCount };
+struct Prof {
+    cudaStream_t st;
+    std::vector<cudaEvent_t> ev;
+    std::vector<int> cat;
+    void mark(int c) {
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        cudaEventRecord(e, st);
+        ev.push_back(e);
+        cat.push_back(c);
+    }
+};
+#define IM_MARK(c) do { if (prof) prof->mark(c); } while (0)
+
 #define IM_TRY(expr)                  \
     do {                              \
         int _rc = (expr);             \
@@ -282,7 +300,7 @@ static int tp_allreduce(Model *m, __half *buf, size_t count, cudaStream_t st) {
 
 // One forward pass over nseq sequences x T tokens each (decode: T = 1; prefill: nseq = 1).
 // Logits are produced for the last token of every sequence.
-static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches) {
+static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches, Prof *prof = nullptr) {
     const im_model_config &c = m->cfg;
     const int H = c.hidden_size, hd = c.head_dim, MT = nseq * T;
     const float eps = c.rms_eps;
@@ -291,11 +309,13 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
     IM_TRY(im_cuda_embedding_norm(m->tokens_dev, m->embed, m->layers[0].input_ln, m->norm_out, m->hidden, H, MT, (uint32_t)c.vocab_size, eps,
                                   c.embed_scale != 0.0f ? c.embed_scale : 1.0f, st));
     nl++;
+    IM_MARK(kCatEmbed);
     for (int l = 0; l < c.num_layers; l++) {
         Layer &L = m->layers[l];
         if (l == 0) {
             IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.qkv), m->norm_out, m->qkv, MT, st));
             nl += (MT + 3) / 4;
+            IM_MARK(kCatQkv);
         }
         QkRopeArgs a{};
         a.q_in = m->qkv; a.k_in = m->qkv + m->q_dim; a.v_in = m->qkv + m->q_dim + m->kv_dim;
@@ -305,27 +325,38 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         a.nh = m->nh_l; a.nkv = m->nkv_l; a.hd = hd; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd;
         a.seq_offset = 0; a.pos_dev = m->pos_dev; a.tokens_per_seq = T; a.eps = eps; a.with_norm = c.qk_norm ? 1 : 0;
         IM_TRY(launch_qk_rope(a, MT, st));
+        IM_MARK(kCatRope);
         IM_TRY(im_cuda_tq_encode(m->tq, m->k_d, 1, L.kc, L.ks, L.krn, nseq, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, st));
         IM_TRY(im_cuda_tq_encode(m->tq, m->v_d, 0, L.vc, L.vs, L.krn /*unused*/, nseq, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, st));
+        IM_MARK(kCatKvWrite);
         IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, m->q_d, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
                                    m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st));
         nl += 5;
+        IM_MARK(kCatAttn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.o), m->attn_out, m->ffn_down, MT, st));
+        IM_MARK(kCatOProj);
         IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
+        if (m->world > 1) IM_MARK(kCatComm);
         IM_TRY(im_cuda_fused_residual_rms_norm(m->hidden, m->ffn_down, L.post_ln, m->norm_out, m->residual, H, MT, eps, st));
+        IM_MARK(kCatResNorm);
         IM_TRY(im_cuda_ffn_gate_up_act(static_cast<im_affine_weight *>(L.gate), static_cast<im_affine_weight *>(L.up), m->norm_out,
                                        m->ffn_gate, MT, st));
+        IM_MARK(kCatFfn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.down), m->ffn_gate, m->ffn_down, MT, st));
+        IM_MARK(kCatDown);
         IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
+        if (m->world > 1) IM_MARK(kCatComm);
         nl += 1 + 3 * ((MT + 3) / 4) + (m->world > 1 ? 2 : 0);
         if (l + 1 < c.num_layers) {
             Layer &Nx = m->layers[l + 1];
             IM_TRY(im_cuda_fused_residual_norm_matvec(static_cast<im_affine_weight *>(Nx.qkv), m->residual, m->ffn_down, Nx.input_ln, eps,
                                                       m->qkv, m->hidden, m->norm_out, MT, st));
             nl += (MT + 3) / 4;
+            IM_MARK(kCatQkv);
         } else {
             IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)MT * H, st));
             nl++;
+            IM_MARK(kCatResNorm);
         }
     }
     // final norm + lm_head on the last token of each sequence
@@ -342,6 +373,7 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         nl++;
 #endif
     }
+    IM_MARK(kCatHead);
     if (launches) *launches = nl;
     return IM_OK;
 }
@@ -847,6 +879,35 @@ IM_EXPORT int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tok
     if (tokens_out_host && n_steps > 0)
         IM_CUDA_CHECK(cudaMemcpy2D(tokens_out_host, (size_t)batch * 4, m->tok_hist, (size_t)m->cfg.max_batch * 4, (size_t)batch * 4, n_steps,
                                    cudaMemcpyDeviceToHost));
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_profile_step(im_model *m, int batch, float *ms_by_category, int n_categories) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && ms_by_category && n_categories >= kCatCount, "bad argument (need %d categories)", (int)kCatCount);
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", batch, m->cfg.max_batch);
+    if (m->seq_pos + 1 > m->cfg.max_seq_len) return fail(IM_ERR_BOUNDS, "no room for one more position");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    cudaStream_t st = m->stream;
+    const int splits = decode_splits(m, batch);
+    IM_TRY(forward(m, batch, 1, splits, st, nullptr));  // warm
+    Prof prof;
+    prof.st = st;
+    prof.mark(-1);
+    int rc = forward(m, batch, 1, splits, st, nullptr, &prof);
+    cudaError_t e = cudaStreamSynchronize(st);
+    for (int i = 0; i < n_categories; i++) ms_by_category[i] = 0.0f;
+    if (rc == IM_OK && e == cudaSuccess)
+        for (size_t i = 1; i < prof.ev.size(); i++) {
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, prof.ev[i - 1], prof.ev[i]);
+            ms_by_category[prof.cat[i]] += ms;
+        }
+    for (cudaEvent_t ev : prof.ev) cudaEventDestroy(ev);
+    if (rc != IM_OK) return rc;
+    if (e != cudaSuccess) return fail(IM_ERR_CUDA, "profile step failed: %s", cudaGetErrorString(e));
     return IM_OK;
     IM_GUARD_END
 }

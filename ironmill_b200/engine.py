@@ -233,6 +233,17 @@ class CudaInference:
     def step_launches(self) -> int:
         return int(lib().im_cuda_model_step_launches(self._model))
 
+    PROFILE_CATEGORIES = ("embed", "qkv_proj", "rope", "kv_write", "attention", "o_proj", "residual_norm", "ffn_gate_up",
+                          "down_proj", "collectives", "lm_head")
+
+    @_wrap
+    def profile_step(self, batch: int = 1) -> dict:
+        """Per-category GPU milliseconds of one decode step (kernel_timing of the Metal backend)."""
+        self._need_model()
+        ms = (C.c_float * 11)()
+        check(lib().im_cuda_model_profile_step(self._model, C.c_int(batch), ms, C.c_int(11)))
+        return dict(zip(self.PROFILE_CATEGORIES, [float(v) for v in ms]))
+
     def close(self) -> None:
         if self._model:
             lib().im_cuda_model_free(self._model)

@@ -87,8 +87,11 @@ def _deq(t):
 
 
 class OracleModel:
-    def __init__(self, cfg, tensors, tqc, max_seq):
+    def __init__(self, cfg, tensors, tqc, max_seq, flip_rate=0.0):
+        """flip_rate > 0 flips the lowest fp16 bit of that fraction of the activations entering every layer:
+        a stand-in for "another correct implementation" used to measure how far last-bit differences grow."""
         self.cfg, self.tq, self.max_seq = cfg, tqc, max_seq
+        self.flip_rate, self._flip_rng = flip_rate, np.random.default_rng(12345)
         g = lambda n: tensors[n].data.astype(np.float16)  # noqa: E731
         self.embed = g("model.embed_tokens.weight")
         self.lm = (self.embed if cfg.tie_word_embeddings else g("lm_head.weight")).astype(np.float32)
@@ -113,6 +116,11 @@ class OracleModel:
         self.cos, self.sin = orc.rope_table(hd, max_seq, cfg.rope_theta, cfg.extra.get("rotary_dim"))
         self.pos = 0
 
+    def _flip(self, a16):
+        v = np.ascontiguousarray(a16).view(np.uint16).copy()
+        v[self._flip_rng.random(v.shape) < self.flip_rate] ^= 1
+        return v.view(np.float16)
+
     @staticmethod
     def _mv(w, awq, x16):
         x = x16.astype(np.float32)
@@ -129,6 +137,8 @@ class OracleModel:
         for li, d in enumerate(self.L):
             if li == 0:
                 qkv = self._mv(d["qkv"], d["qkv_awq"], norm_out)
+            if self.flip_rate:
+                qkv, hidden = self._flip(qkv), self._flip(hidden)
             q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
             if c.has_qk_norm:
                 q, k = orc.qk_norm_rope(q, k, d["qn"], d["kn"], self.cos, self.sin, nh, nkv, hd, self.pos, float(eps))
