@@ -61,6 +61,10 @@ int im_cuda_device_sm_count(const im_device *dev);
 /* Bytes currently allocated through this device handle (buffers, weights, models). */
 size_t im_cuda_device_allocated_bytes(const im_device *dev);
 int im_cuda_device_synchronize(im_device *dev);
+/* Synchronises and reports IM_ERR_TIMEOUT if a kernel gave up a bounded device-side wait since the last
+ * check (the counterpart of the command-buffer status check,
+ * crates/ironmill-inference/src/metal/pipeline.rs:1209-1213). */
+int im_cuda_device_check_error(im_device *dev);
 
 /* MetalBuffer::{length, write_bytes, read_bytes} with bounds checks
  * (crates/ironmill-metal-sys/src/buffer.rs:42-158).  Buffers are device-private:

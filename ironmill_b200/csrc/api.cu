@@ -88,12 +88,41 @@ IM_EXPORT int im_cuda_device_open(int ordinal, im_device **out) {
         delete d;
         return im::fail(IM_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", ordinal, major, minor);
     }
+    // scratch of the tiled matvec (see common.cuh) and the device-side error word
+    rc = im::dev_malloc(d, (void **)&d->sk_partial, (size_t)d->sm_count * 2 * 64 * sizeof(float));
+    if (rc == IM_OK) rc = im::dev_malloc(d, (void **)&d->sk_counters, (size_t)im::kSkMaxBlocks * sizeof(int));
+    if (rc == IM_OK) rc = im::dev_malloc(d, (void **)&d->err_flag, sizeof(int));
+    if (rc == IM_OK && (cudaMemset(d->sk_counters, 0, (size_t)im::kSkMaxBlocks * sizeof(int)) != cudaSuccess ||
+                        cudaMemset(d->err_flag, 0, sizeof(int)) != cudaSuccess))
+        rc = im::fail(IM_ERR_CUDA, "scratch initialisation failed");
+    if (rc != IM_OK) {
+        im_cuda_device_free(d);
+        return rc;
+    }
     *out = d;
     return IM_OK;
     IM_GUARD_END
 }
 
-IM_EXPORT void im_cuda_device_free(im_device *dev) { delete dev; }
+IM_EXPORT void im_cuda_device_free(im_device *dev) {
+    if (!dev) return;
+    cudaFree(dev->sk_partial);
+    cudaFree(dev->sk_counters);
+    cudaFree(dev->err_flag);
+    delete dev;
+}
+
+IM_EXPORT int im_cuda_device_check_error(im_device *dev) {
+    IM_REQUIRE(dev, "dev is NULL");
+    int flag = 0;
+    IM_CUDA_CHECK(cudaMemcpy(&flag, dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(dev->err_flag, 0, sizeof(int));
+        cudaMemset(dev->sk_counters, 0, (size_t)im::kSkMaxBlocks * sizeof(int));
+        return im::fail(IM_ERR_TIMEOUT, "a device-side bounded wait ran out; the results of the affected launch are invalid");
+    }
+    return IM_OK;
+}
 IM_EXPORT int im_cuda_device_ordinal(const im_device *dev) { return dev ? dev->ordinal : -1; }
 IM_EXPORT int im_cuda_device_sm_count(const im_device *dev) { return dev ? dev->sm_count : 0; }
 IM_EXPORT size_t im_cuda_device_allocated_bytes(const im_device *dev) { return dev ? dev->allocated : 0; }

@@ -508,10 +508,67 @@ static int pick_ksplit(const Device *dev, int N, int K, int R, int chunk) {
     return ks;
 }
 
+// Gate/up pair as one tile stream (8 gate rows + 8 up rows per tile), built the first time the pair is used.
+static int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaStream_t st) {
+    AffineWeight *gate = const_cast<AffineWeight *>(gate_c);
+    if (gate->pair_with == up && gate->pair_tiles) return IM_OK;
+    dev_free(gate->dev, gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1024);
+    dev_free(gate->dev, gate->pair_tsz, (size_t)gate->pair_nblk * gate->G * 16 * sizeof(__half2));
+    gate->pair_tiles = nullptr;
+    gate->pair_tsz = nullptr;
+    gate->pair_with = nullptr;
+    gate->pair_nblk = (gate->N + 7) / 8;
+    int rc = dev_malloc(gate->dev, (void **)&gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1024);
+    if (rc == IM_OK) rc = dev_malloc(gate->dev, (void **)&gate->pair_tsz, (size_t)gate->pair_nblk * gate->G * 16 * sizeof(__half2));
+    if (rc != IM_OK) return rc;
+    gate->bytes += (size_t)gate->pair_nblk * gate->G * (1024 + 64);
+    rc = v2_repack(gate->codes, gate->sz, up->codes, up->sz, gate->N, gate->K, gate->G, gate->pair_nblk, 8, gate->pair_tiles,
+                   gate->pair_tsz, st);
+    if (rc == IM_OK) gate->pair_with = up;
+    return rc;
+}
+
 template <int MODE>
-static int run_matvec(MatvecParams p, const AffineWeight *w, int B, cudaStream_t st) {
+static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const AffineWeight *up, int B, cudaStream_t st) {
+    V2Params q{};
+    if (MODE == kGateUpAct) {
+        if ((w->N + 7) / 8 > kSkMaxBlocks) return IM_ERR_BOUNDS;
+        int rc = ensure_pair(w, up, st);
+        if (rc != IM_OK) return rc;
+        q.tiles = w->pair_tiles;
+        q.tsz = reinterpret_cast<const uint8_t *>(w->pair_tsz);
+        q.nblk = w->pair_nblk;
+    } else {
+        q.tiles = w->tiles;
+        q.tsz = reinterpret_cast<const uint8_t *>(w->tsz);
+        q.nblk = w->nblk;
+    }
+    q.awq = p.awq; q.gamma = p.gamma; q.eps = p.eps;
+    q.N = p.N; q.K = p.K; q.G = p.G;
+    q.partial = w->dev->sk_partial; q.counters = w->dev->sk_counters; q.err = w->dev->err_flag;
+    int done = 0;
+    while (done < B) {
+        const int nb = B - done >= 4 ? 4 : (B - done >= 2 ? 2 : 1);
+        q.x = p.x + (size_t)done * p.K;
+        q.b = p.b ? p.b + (size_t)done * p.K : nullptr;
+        q.y = p.y + (size_t)done * p.N;
+        q.residual_out = p.residual_out ? p.residual_out + (size_t)done * p.K : nullptr;
+        q.normed_out = p.normed_out ? p.normed_out + (size_t)done * p.K : nullptr;
+        int rc = v2_run(MODE, nb, q, w->dev, st);
+        if (rc != IM_OK) return rc;  // IM_ERR_BOUNDS on the first chunk: caller falls back
+        done += nb;
+    }
+    return IM_OK;
+}
+
+template <int MODE>
+static int run_matvec(MatvecParams p, const AffineWeight *w, int B, cudaStream_t st, const AffineWeight *up = nullptr) {
     const Device *dev = w->dev;
     const size_t xstride = (size_t)p.K, ystride = (size_t)p.N;
+    if (w->tiles && (MODE != kGateUpAct || (up && up->tiles))) {
+        const int rc = run_matvec_v2<MODE>(p, w, up, B, st);
+        if (rc != IM_ERR_BOUNDS) return rc;  // shapes whose activations do not fit beside the ring use the kernel below
+    }
     if (!fast_path(w)) {
         const int wpb = 8;
         matvec_generic_kernel<MODE><<<(p.N + wpb - 1) / wpb, wpb * 32, 0, st>>>(p, w->bits, w->group_size, B);
@@ -619,6 +676,18 @@ static int weight_create_common(im_device *dev, const void *qdata, const void *s
     if (e == cudaSuccess && host_src) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return bail(fail(IM_ERR_CUDA, "weight repack failed: %s", cudaGetErrorString(e)));
     cleanup();
+    if (bit_width == 4 && group_size == kGroup && K % kGroup == 0 && (N + 15) / 16 <= kSkMaxBlocks) {
+        // tile-major copy for the bulk-staged kernel
+        w->nblk = (N + 15) / 16;
+        const size_t tb = (size_t)w->nblk * w->G * 1024, sb = (size_t)w->nblk * w->G * 16 * sizeof(__half2);
+        if ((rc = dev_malloc(dev, (void **)&w->tiles, tb)) != IM_OK) return bail(rc);
+        w->bytes += tb;
+        if ((rc = dev_malloc(dev, (void **)&w->tsz, sb)) != IM_OK) return bail(rc);
+        w->bytes += sb;
+        rc = v2_repack(w->codes, w->sz, nullptr, nullptr, N, K, w->G, w->nblk, 16, w->tiles, w->tsz, st);
+        if (rc == IM_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(IM_ERR_CUDA, "tile repack failed");
+        if (rc != IM_OK) return bail(rc);
+    }
     *out = w;
     return IM_OK;
 }
@@ -648,6 +717,10 @@ IM_EXPORT void im_cuda_affine_weight_free(im_affine_weight *w) {
     im::dev_free(w->dev, w->codes, (code_bytes + 15) / 16 * 16);
     im::dev_free(w->dev, w->sz, (size_t)w->N * w->G * sizeof(__half2));
     im::dev_free(w->dev, w->awq, (size_t)w->K * sizeof(__half));
+    im::dev_free(w->dev, w->tiles, (size_t)w->nblk * w->G * 1024);
+    im::dev_free(w->dev, w->tsz, (size_t)w->nblk * w->G * 16 * sizeof(__half2));
+    im::dev_free(w->dev, w->pair_tiles, (size_t)w->pair_nblk * w->G * 1024);
+    im::dev_free(w->dev, w->pair_tsz, (size_t)w->pair_nblk * w->G * 16 * sizeof(__half2));
     delete w;
 }
 
@@ -709,7 +782,7 @@ IM_EXPORT int im_cuda_ffn_gate_up_act(const im_affine_weight *gate, const im_aff
     p.sz1 = up->sz;
     p.x = static_cast<const __half *>(x_dev);
     p.y = static_cast<__half *>(out_dev);
-    return im::run_matvec<im::kGateUpAct>(p, gate, B, im::as_stream(stream));
+    return im::run_matvec<im::kGateUpAct>(p, gate, B, im::as_stream(stream), up);
     IM_GUARD_END
 }
 

@@ -1,0 +1,419 @@
+// INT4 group-128 matvec, second generation: bulk-async staged, tensor-core dot products,
+// stream-K work split.  Same arithmetic contract as matvec.cu (the (q - z) * s dequant of
+// crates/ironmill-core/src/dequant.rs:129-139 applied to the decode projections
+// crates/ironmill-inference/src/metal/shaders/quantized/affine_matvec.metal:16-111,
+// affine_fused.metal:9-108, norm/superblock_fused_norm.metal:21-124).
+//
+// Layout (built once at load time): the matrix is cut into tiles of 16 rows x 128 columns
+// (one quantization group): 16 x 64 bytes of nibbles = 1 KB, stored tile after tile in
+// [row block][group] order, with the 16 (scale, zero) fp16 pairs of each tile in a parallel
+// array.  A run of consecutive tiles is therefore one contiguous byte range, which one thread
+// moves into shared memory with cp.async.bulk, completion counted on an mbarrier.
+//
+// Kernel: one persistent CTA per SM = 1 producer warp + 8 consumer warps around a ring of
+// shared-memory stages (8 tiles each), so the bytes in flight do not depend on how fast the
+// consumers compute.  A consumer warp handles one tile per stage: two 128-bit shared loads give
+// each thread the 8 nibble words of its two rows, three logic operations per word split them
+// into byte lanes, and four mma.sync m16n8k32 (u8 x s8 -> s32) multiply them with the
+// activations, which were block-quantised once per CTA to 16 bits per value (signed high byte
+// in one B column, signed low byte in the next; up to four batch rows share one instruction).
+// Integer sums are exact inside a group; one float fix-up per tile applies
+//   s * sx * (sum_k xi_k q_k - z * sum_k xi_k).
+// Work is split stream-K fashion: every CTA gets the same number of stages (+-1) out of the
+// flattened [row block][stage] list; a row block cut by a CTA boundary is completed by whichever
+// of its CTAs arrives last (an atomic counter; nobody waits), summing the partials in CTA order
+// so the result does not depend on arrival order.
+#include "common.cuh"
+
+namespace im {
+
+constexpr int kV2Consumers = 8;
+constexpr int kV2Threads = (kV2Consumers + 1) * 32;
+constexpr int kTileBytes = 1024;
+constexpr int kTileSzBytes = 64;
+constexpr unsigned long long kWaitLimitNs = 400ull * 1000 * 1000;  // bounded mbarrier waits: give up, flag, carry on without computing
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false (and the error word set) if the barrier never completed.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned i = 1;; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) break;
+    }
+    atomicExch(err, 1);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kV2Consumers * 32) : "memory"); }
+
+__device__ __forceinline__ unsigned pack4s(int a, int b, int c, int d) {
+    return (unsigned)(a & 0xff) | ((unsigned)(b & 0xff) << 8) | ((unsigned)(c & 0xff) << 16) | ((unsigned)(d & 0xff) << 24);
+}
+
+// Activation staging.  xq words: index (((grp*2NB + col)*4 + t)*4 + j)*2 + eo, col = 2b (high bytes) or
+// 2b+1 (low bytes); the word holds elements (4t+j)*8 + {0,2,4,6} (eo = 0) or {1,3,5,7} (eo = 1) of the group.
+// meta[grp*NB + b] = (group scale, sum of the 128 integers).  Returns this thread's share of sum r^2.
+template <int MODE, int NB>
+__device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *xq, float2 *meta, int nthreads_warps) {
+    const int K = p.K, lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
+    float sq = 0.0f;
+    for (int g0 = warp * 2; g0 < p.G; g0 += nthreads_warps * 2) {
+        const int grp = g0 + (lane >> 4);
+        const bool live = grp < p.G;
+        const int k = (live ? grp : g0) * 128 + hl * 8;
+        float v[8];
+        {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + (size_t)b * K + k);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(h[i]);
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            }
+        }
+        if (MODE == 2) {
+            const uint4 rb = *reinterpret_cast<const uint4 *>(p.b + (size_t)b * K + k);
+            const uint4 rg = *reinterpret_cast<const uint4 *>(p.gamma + k);
+            const __half2 *hb = reinterpret_cast<const __half2 *>(&rb), *hg = reinterpret_cast<const __half2 *>(&rg);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 fb = __half22float2(hb[i]), fg = __half22float2(hg[i]);
+                const float r0 = v[2 * i] + fb.x, r1 = v[2 * i + 1] + fb.y;
+                if (live) sq += r0 * r0 + r1 * r1;
+                v[2 * i] = r0 * fg.x;
+                v[2 * i + 1] = r1 * fg.y;
+            }
+        }
+        if (p.awq) {
+            const uint4 ra = *reinterpret_cast<const uint4 *>(p.awq + k);
+            const __half2 *ha = reinterpret_cast<const __half2 *>(&ra);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 fa = __half22float2(ha[i]);
+                v[2 * i] = v[2 * i] / fa.x;
+                v[2 * i + 1] = v[2 * i + 1] / fa.y;
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        // 32639 = 127 * 256 + 127: both bytes of the split below stay inside a signed byte
+        const float sx = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f;
+        const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
+        int hi[8], lo[8], lsum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int xi = __float2int_rn(v[i] * inv);
+            xi = max(-32639, min(32639, xi));
+            lsum += xi;
+            hi[i] = (xi + 128) >> 8;
+            lo[i] = xi - hi[i] * 256;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        if (live) {
+            const int t = hl >> 2, j = hl & 3;
+            uint2 *dh = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 * NB + 2 * b) * 4 + t) * 4 + j) * 2);
+            uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 * NB + 2 * b + 1) * 4 + t) * 4 + j) * 2);
+            *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
+            *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
+            if (hl == 0) meta[grp * NB + b] = make_float2(sx, (float)lsum);
+        }
+    }
+    return sq;
+}
+
+// MODE 0 plain, 1 gate+up+SiLU (tile rows 0-7 = gate rows, 8-15 = up rows of the same outputs), 2 residual+norm.
+template <int MODE, int NB>
+__global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int G = p.G, tps = p.tps, nring = p.nring;
+    const int stage_bytes = tps * (kTileBytes + kTileSzBytes);
+    unsigned char *ring = smem;                                             // nring * stage_bytes (weights then sz per stage)
+    uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);  // G * 2NB * 32 words
+    float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 2 * NB * 32);          // G * NB
+    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // 8 warps * 64 + 64 + 16
+    uint64_t *full = reinterpret_cast<uint64_t *>(red + kV2Consumers * 64 + 64 + 16);  // nring
+    uint64_t *empty = full + nring;
+    int *flag = reinterpret_cast<int *>(empty + nring);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int spb = G / tps;  // stages per row block
+    const long long total = (long long)p.nblk * spb;
+    const int s_begin = (int)(total * blockIdx.x / gridDim.x), s_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+
+    if (tid == 0) {
+        for (int i = 0; i < nring; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], kV2Consumers);
+        }
+        *flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kV2Consumers) {
+        // ------------------------------------------------ producer: one lane streams the stages
+        if (lane == 0) {
+            for (int s = s_begin; s < s_end; s++) {
+                const int it = s - s_begin, slot = it % nring;
+                if (!mbar_wait(&empty[slot], ((it / nring) & 1) ^ 1, p.err)) break;
+                unsigned char *dst = ring + (size_t)slot * stage_bytes;
+                const size_t tile0 = (size_t)s * tps;  // flattened [row block][group] index of the stage's first tile
+                mbar_expect_tx(&full[slot], (uint32_t)stage_bytes);
+                bulk_g2s(dst, p.tiles + tile0 * kTileBytes, (uint32_t)(tps * kTileBytes), &full[slot]);
+                bulk_g2s(dst + tps * kTileBytes, p.tsz + tile0 * kTileSzBytes, (uint32_t)(tps * kTileSzBytes), &full[slot]);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------- consumers
+    float sq_tot[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+        float sq = v2_stage_x<MODE, NB>(p, b, xq, meta, kV2Consumers);
+        sq_tot[b] = 0.0f;
+        if (MODE == 2) {
+            sq = warp_sum(sq);
+            if (lane == 0) red[kV2Consumers * 64 + 64 + warp] = sq;
+            consumer_sync();
+            float t = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kV2Consumers; w++) t += red[kV2Consumers * 64 + 64 + w];
+            sq_tot[b] = t;
+            consumer_sync();
+        }
+    }
+    consumer_sync();
+    float rms_inv[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) rms_inv[b] = MODE == 2 ? rsqrtf(sq_tot[b] / (float)p.K + p.eps) : 1.0f;
+    if (MODE == 2 && blockIdx.x == 0) {  // side outputs (must not alias a or b)
+        for (int b = 0; b < NB; b++)
+            for (int k = tid; k < p.K; k += kV2Consumers * 32) {
+                const float r = __half2float(p.x[(size_t)b * p.K + k]) + __half2float(p.b[(size_t)b * p.K + k]);
+                if (p.residual_out) p.residual_out[(size_t)b * p.K + k] = __float2half_rn(r);
+                if (p.normed_out) p.normed_out[(size_t)b * p.K + k] = __float2half_rn(r * rms_inv[b] * __half2float(p.gamma[k]));
+            }
+    }
+
+    const int g = lane >> 2, t = lane & 3;  // fragment coordinates: rows g and g+8, batch column pair t
+    float acc0 = 0.0f, acc1 = 0.0f;          // rows g, g+8 for batch t
+    int cur_rb = s_begin < s_end ? s_begin / spb : -1;
+    bool dead = false;
+
+    // Finish row block rb: reduce the 8 warps, then either write the outputs (block fully inside this CTA's
+    // range) or publish a partial and let the last contributing CTA combine them in CTA order.
+    auto flush = [&](int rb) {
+        if (t < NB) {
+            red[warp * 64 + g * 4 + t] = acc0;
+            red[warp * 64 + (g + 8) * 4 + t] = acc1;
+        }
+        acc0 = acc1 = 0.0f;
+        consumer_sync();
+        const int row = tid >> 2, bb = tid & 3;  // threads 0..63: (row, batch)
+        float v = 0.0f;
+        if (tid < 64 && bb < NB) {
+#pragma unroll
+            for (int w = 0; w < kV2Consumers; w++) v += red[w * 64 + tid];
+        }
+        const long long b0 = (long long)rb * spb, b1 = b0 + spb;
+        const bool complete = b0 >= s_begin && b1 <= s_end;
+        bool finalize = complete;
+        if (!complete) {
+            const int slot = (rb == s_begin / spb) ? 0 : 1;
+            if (tid < 64) p.partial[((size_t)blockIdx.x * 2 + slot) * 64 + tid] = v;
+            __threadfence();
+            consumer_sync();
+            const int c_first = (int)(((b0 + 1) * gridDim.x + total - 1) / total) - 1;
+            const int c_last = (int)((b1 * gridDim.x + total - 1) / total) - 1;
+            if (tid == 0) {
+                const int old = atomicAdd(&p.counters[rb], 1);
+                *flag = (old == c_last - c_first) ? 1 : 0;
+            }
+            consumer_sync();
+            finalize = *flag != 0;
+            if (finalize) {
+                __threadfence();
+                v = 0.0f;
+                if (tid < 64) {
+                    for (int c = c_first; c <= c_last; c++) {
+                        const int cb = (int)(total * c / gridDim.x);
+                        const int cslot = (rb == cb / spb) ? 0 : 1;
+                        v += __ldcg(&p.partial[((size_t)c * 2 + cslot) * 64 + tid]);
+                    }
+                }
+                if (tid == 0) p.counters[rb] = 0;  // ready for the next launch
+            }
+        }
+        if (finalize) {
+            if (MODE == 1) {
+                if (tid < 64) red[kV2Consumers * 64 + tid] = v;
+                consumer_sync();
+                if (tid < 32 && bb < NB) {  // rows 0..7: gate, partner row + 8: up
+                    const float gv = v, uv = red[kV2Consumers * 64 + tid + 32];
+                    const int n = rb * 8 + row;
+                    if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
+                }
+            } else if (tid < 64 && bb < NB) {
+                const int n = rb * 16 + row;
+                float ri = rms_inv[0];
+#pragma unroll
+                for (int b = 1; b < NB; b++) ri = bb == b ? rms_inv[b] : ri;
+                if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn(v * ri);
+            }
+        }
+        consumer_sync();  // red / flag are reused by the next flush
+    };
+
+    // A warp whose wait ran out stops computing but keeps every barrier of the schedule, so that
+    // the other warps and the producer still run to the end; the host sees the error word.
+    for (int s = s_begin; s < s_end; s++) {
+        const int it = s - s_begin, slot = it % nring;
+        const int rb = s / spb, part = s % spb;
+        if (rb != cur_rb) {
+            flush(cur_rb);
+            cur_rb = rb;
+        }
+        if (!dead && !mbar_wait(&full[slot], (it / nring) & 1, p.err)) dead = true;
+        const unsigned char *st = ring + (size_t)slot * stage_bytes;
+        for (int ti = warp; ti < tps && !dead; ti += kV2Consumers) {
+            const int grp = part * tps + ti;
+            const uint4 w0 = *reinterpret_cast<const uint4 *>(st + ti * kTileBytes + lane * 16);        // row g
+            const uint4 w1 = *reinterpret_cast<const uint4 *>(st + ti * kTileBytes + 512 + lane * 16);  // row g+8
+            uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = xb0;
+            if (g < 2 * NB) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp * 2 * NB + g) * 4 + t) * 8);
+                xb0 = xp[0];  // (even, odd) words of j = 0, 1
+                xb1 = xp[1];  // j = 2, 3
+            }
+            int c[4] = {0, 0, 0, 0};
+            constexpr unsigned M = 0x0F0F0F0Fu;
+            mma_u8s8(c, w0.x & M, w1.x & M, (w0.x >> 4) & M, (w1.x >> 4) & M, xb0.x, xb0.y);
+            mma_u8s8(c, w0.y & M, w1.y & M, (w0.y >> 4) & M, (w1.y >> 4) & M, xb0.z, xb0.w);
+            mma_u8s8(c, w0.z & M, w1.z & M, (w0.z >> 4) & M, (w1.z >> 4) & M, xb1.x, xb1.y);
+            mma_u8s8(c, w0.w & M, w1.w & M, (w0.w >> 4) & M, (w1.w >> 4) & M, xb1.z, xb1.w);
+            if (t < NB) {
+                const float2 m = meta[grp * NB + t];
+                const __half2 *szp = reinterpret_cast<const __half2 *>(st + tps * kTileBytes + ti * kTileSzBytes);
+                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                const float f0 = (float)(c[0] * 256 + c[1]), f1 = (float)(c[2] * 256 + c[3]);
+                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+    }
+    if (cur_rb >= 0) flush(cur_rb);
+}
+
+// ---- load-time repack -------------------------------------------------------
+// Row-major codes [N][K/2] + interleaved (s, z) [N][G]  ->  tiles.  One thread per 16-byte chunk.
+// rows_per_blk = 16 (plain) or 8 (gate/up pair: tile rows 0-7 from matrix 0, 8-15 from matrix 1).
+__global__ void v2_repack_kernel(const uint8_t *__restrict__ codes0, const __half2 *__restrict__ sz0, const uint8_t *__restrict__ codes1,
+                                 const __half2 *__restrict__ sz1, int N, int K, int G, int nblk, int rows_per_blk,
+                                 uint8_t *__restrict__ tiles, __half2 *__restrict__ tsz) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // chunk index: ((rb*G + grp)*16 + r)*4 + c
+    const size_t nchunks = (size_t)nblk * G * 64;
+    if (i >= nchunks) return;
+    const int c = i & 3, r = (i >> 2) & 15;
+    const size_t tile = i >> 6;
+    const int grp = (int)(tile % G), rb = (int)(tile / G);
+    const bool second = rows_per_blk == 8 && r >= 8;
+    const int row = rb * rows_per_blk + (rows_per_blk == 8 ? (r & 7) : r);
+    const uint8_t *codes = second ? codes1 : codes0;
+    const __half2 *sz = second ? sz1 : sz0;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < N) v = *reinterpret_cast<const uint4 *>(codes + (size_t)row * (K / 2) + grp * 64 + c * 16);
+    reinterpret_cast<uint4 *>(tiles)[i] = v;
+    if (c == 0) tsz[tile * 16 + r] = row < N ? sz[(size_t)row * G + grp] : __halves2half2(__float2half(0.0f), __float2half(0.0f));
+}
+
+int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, const __half2 *sz1, int N, int K, int G, int nblk,
+              int rows_per_blk, uint8_t *tiles, __half2 *tsz, cudaStream_t st) {
+    const size_t nchunks = (size_t)nblk * G * 64;
+    v2_repack_kernel<<<(unsigned)((nchunks + 255) / 256), 256, 0, st>>>(codes0, sz0, codes1, sz1, N, K, G, nblk, rows_per_blk, tiles, tsz);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+}
+
+static int pick_tps(int G) {
+    for (int t = 8; t >= 1; t--)
+        if (G % t == 0) return t;
+    return 1;
+}
+
+template <int MODE, int NB>
+static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
+    p.tps = pick_tps(p.G);
+    const size_t stage_bytes = (size_t)p.tps * (kTileBytes + kTileSzBytes);
+    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + (kV2Consumers * 64 + 64 + 16) * 4 + 64;
+    const size_t budget = dev->smem_optin > 8192 ? dev->smem_optin - 2048 : 0;
+    if (fixed + 2 * stage_bytes + 64 > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel
+    int nring = (int)((budget - fixed - 64) / (stage_bytes + 16));
+    if (nring > 24) nring = 24;
+    p.nring = nring;
+    const size_t smem = (size_t)nring * stage_bytes + fixed + (size_t)nring * 16;
+    auto kern = matvec_v2_kernel<MODE, NB>;
+    static thread_local bool configured = false;
+    if (!configured) {
+        IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
+        configured = true;
+    }
+    const long long total = (long long)p.nblk * (p.G / p.tps);
+    int grid = dev->sm_count;
+    if (grid > total) grid = (int)total;
+    kern<<<grid, kV2Threads, smem, st>>>(p);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+}
+
+// mode: 0 plain, 1 gate+up (fused tiles), 2 residual+norm.  Returns IM_ERR_BOUNDS if the shape does not fit.
+int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st) {
+#define V2_CASE(M, B) \
+    if (mode == M && nb == B) return v2_launch<M, B>(p, dev, st);
+    V2_CASE(0, 1) V2_CASE(0, 2) V2_CASE(0, 4) V2_CASE(1, 1) V2_CASE(1, 2) V2_CASE(1, 4) V2_CASE(2, 1) V2_CASE(2, 2) V2_CASE(2, 4)
+#undef V2_CASE
+    return fail(IM_ERR_INVALID, "unsupported v2 matvec mode %d / batch %d", mode, nb);
+}
+
+}  // namespace im
