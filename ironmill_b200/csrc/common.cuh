@@ -68,25 +68,21 @@ struct AffineWeight {
     // 4-bit, group 128: tiles of 16 rows x 128 columns (1 KB of nibbles) in [row block][group] order and
     // the 16 (scale, zero) pairs of each tile; see matvec_v2.cu
     uint8_t *tiles = nullptr;
-    __half2 *tsz = nullptr;
     int nblk = 0;
     // gate+up pair in one tile stream (tile rows 0-7 from this matrix, 8-15 from `pair_with`), built on first use
     uint8_t *pair_tiles = nullptr;
-    __half2 *pair_tsz = nullptr;
     const AffineWeight *pair_with = nullptr;
     int pair_nblk = 0;
     size_t bytes = 0;
 };
 
 struct V2Params {
-    const uint8_t *tiles;  // [nblk][G][1024]
-    const uint8_t *tsz;    // [nblk][G][16] half2
+    const uint8_t *tiles;  // [nblk][G][1088]: 1024 bytes of nibbles + 16 (scale, zero) pairs per tile
     const __half *awq, *x, *b, *gamma;
     __half *y, *residual_out, *normed_out;
     float eps;
     int N;       // logical outputs per batch row
     int K, G, nblk;
-    int tps;     // tiles per stage, divides G
     int nring;   // stages in the shared-memory ring
     float *partial;  // [grid][2][64]
     int *counters;   // [nblk], zero between launches
@@ -95,7 +91,7 @@ struct V2Params {
 
 int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st);
 int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, const __half2 *sz1, int N, int K, int G, int nblk,
-              int rows_per_blk, uint8_t *tiles, __half2 *tsz, cudaStream_t st);
+              int rows_per_blk, uint8_t *tiles, cudaStream_t st);
 
 // ---- device helpers -------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

@@ -512,18 +512,14 @@ static int pick_ksplit(const Device *dev, int N, int K, int R, int chunk) {
 static int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaStream_t st) {
     AffineWeight *gate = const_cast<AffineWeight *>(gate_c);
     if (gate->pair_with == up && gate->pair_tiles) return IM_OK;
-    dev_free(gate->dev, gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1024);
-    dev_free(gate->dev, gate->pair_tsz, (size_t)gate->pair_nblk * gate->G * 16 * sizeof(__half2));
+    dev_free(gate->dev, gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1088);
     gate->pair_tiles = nullptr;
-    gate->pair_tsz = nullptr;
     gate->pair_with = nullptr;
     gate->pair_nblk = (gate->N + 7) / 8;
-    int rc = dev_malloc(gate->dev, (void **)&gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1024);
-    if (rc == IM_OK) rc = dev_malloc(gate->dev, (void **)&gate->pair_tsz, (size_t)gate->pair_nblk * gate->G * 16 * sizeof(__half2));
+    int rc = dev_malloc(gate->dev, (void **)&gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1088);
     if (rc != IM_OK) return rc;
-    gate->bytes += (size_t)gate->pair_nblk * gate->G * (1024 + 64);
-    rc = v2_repack(gate->codes, gate->sz, up->codes, up->sz, gate->N, gate->K, gate->G, gate->pair_nblk, 8, gate->pair_tiles,
-                   gate->pair_tsz, st);
+    gate->bytes += (size_t)gate->pair_nblk * gate->G * 1088;
+    rc = v2_repack(gate->codes, gate->sz, up->codes, up->sz, gate->N, gate->K, gate->G, gate->pair_nblk, 8, gate->pair_tiles, st);
     if (rc == IM_OK) gate->pair_with = up;
     return rc;
 }
@@ -536,11 +532,9 @@ static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const Aff
         int rc = ensure_pair(w, up, st);
         if (rc != IM_OK) return rc;
         q.tiles = w->pair_tiles;
-        q.tsz = reinterpret_cast<const uint8_t *>(w->pair_tsz);
         q.nblk = w->pair_nblk;
     } else {
         q.tiles = w->tiles;
-        q.tsz = reinterpret_cast<const uint8_t *>(w->tsz);
         q.nblk = w->nblk;
     }
     q.awq = p.awq; q.gamma = p.gamma; q.eps = p.eps;
@@ -679,12 +673,10 @@ static int weight_create_common(im_device *dev, const void *qdata, const void *s
     if (bit_width == 4 && group_size == kGroup && K % kGroup == 0 && (N + 15) / 16 <= kSkMaxBlocks) {
         // tile-major copy for the bulk-staged kernel
         w->nblk = (N + 15) / 16;
-        const size_t tb = (size_t)w->nblk * w->G * 1024, sb = (size_t)w->nblk * w->G * 16 * sizeof(__half2);
+        const size_t tb = (size_t)w->nblk * w->G * 1088;
         if ((rc = dev_malloc(dev, (void **)&w->tiles, tb)) != IM_OK) return bail(rc);
         w->bytes += tb;
-        if ((rc = dev_malloc(dev, (void **)&w->tsz, sb)) != IM_OK) return bail(rc);
-        w->bytes += sb;
-        rc = v2_repack(w->codes, w->sz, nullptr, nullptr, N, K, w->G, w->nblk, 16, w->tiles, w->tsz, st);
+        rc = v2_repack(w->codes, w->sz, nullptr, nullptr, N, K, w->G, w->nblk, 16, w->tiles, st);
         if (rc == IM_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(IM_ERR_CUDA, "tile repack failed");
         if (rc != IM_OK) return bail(rc);
     }
@@ -717,10 +709,8 @@ IM_EXPORT void im_cuda_affine_weight_free(im_affine_weight *w) {
     im::dev_free(w->dev, w->codes, (code_bytes + 15) / 16 * 16);
     im::dev_free(w->dev, w->sz, (size_t)w->N * w->G * sizeof(__half2));
     im::dev_free(w->dev, w->awq, (size_t)w->K * sizeof(__half));
-    im::dev_free(w->dev, w->tiles, (size_t)w->nblk * w->G * 1024);
-    im::dev_free(w->dev, w->tsz, (size_t)w->nblk * w->G * 16 * sizeof(__half2));
-    im::dev_free(w->dev, w->pair_tiles, (size_t)w->pair_nblk * w->G * 1024);
-    im::dev_free(w->dev, w->pair_tsz, (size_t)w->pair_nblk * w->G * 16 * sizeof(__half2));
+    im::dev_free(w->dev, w->tiles, (size_t)w->nblk * w->G * 1088);
+    im::dev_free(w->dev, w->pair_tiles, (size_t)w->pair_nblk * w->G * 1088);
     delete w;
 }
 

@@ -8,29 +8,31 @@
 // (one quantization group): 16 x 64 bytes of nibbles = 1 KB, stored tile after tile in
 // [row block][group] order, with the 16 (scale, zero) fp16 pairs of each tile in a parallel
 // array.  A run of consecutive tiles is therefore one contiguous byte range, which one thread
-// moves into shared memory with cp.async.bulk, completion counted on an mbarrier.
+// moves into shared memory with cp.async.bulk, completion counted on an mbarrier.  (A producer
+// lane turns out one bulk copy per ~0.3 us whatever its size, so a stage is made large, 32 tiles = 34 KB.)
 //
-// Kernel: one persistent CTA per SM = 1 producer warp + 8 consumer warps around a ring of
-// shared-memory stages (8 tiles each), so the bytes in flight do not depend on how fast the
-// consumers compute.  A consumer warp handles one tile per stage: two 128-bit shared loads give
+// Kernel: one persistent CTA per SM = 1 producer warp + 16 consumer warps around a ring of
+// shared-memory stages (up to 32 tiles each), so the bytes in flight do not depend on how fast the
+// consumers compute.  A consumer warp handles two tiles per stage: two 128-bit shared loads give
 // each thread the 8 nibble words of its two rows, three logic operations per word split them
 // into byte lanes, and four mma.sync m16n8k32 (u8 x s8 -> s32) multiply them with the
 // activations, which were block-quantised once per CTA to 16 bits per value (signed high byte
 // in one B column, signed low byte in the next; up to four batch rows share one instruction).
 // Integer sums are exact inside a group; one float fix-up per tile applies
 //   s * sx * (sum_k xi_k q_k - z * sum_k xi_k).
-// Work is split stream-K fashion: every CTA gets the same number of stages (+-1) out of the
-// flattened [row block][stage] list; a row block cut by a CTA boundary is completed by whichever
+// Work is split stream-K fashion: every CTA gets the same number of tiles (+-1) out of the
+// flattened [row block][group] list; a row block cut by a CTA boundary is completed by whichever
 // of its CTAs arrives last (an atomic counter; nobody waits), summing the partials in CTA order
 // so the result does not depend on arrival order.
 #include "common.cuh"
 
 namespace im {
 
-constexpr int kV2Consumers = 8;
+constexpr int kV2Consumers = 16;
 constexpr int kV2Threads = (kV2Consumers + 1) * 32;
-constexpr int kTileBytes = 1024;
-constexpr int kTileSzBytes = 64;
+constexpr int kTileCodeBytes = 1024;
+constexpr int kTileBytes = 1088;     // 1024 bytes of nibbles + 16 (scale, zero) fp16 pairs, contiguous
+constexpr int kStageTiles = 32;      // tiles per stage: two per consumer warp
 constexpr unsigned long long kWaitLimitNs = 400ull * 1000 * 1000;  // bounded mbarrier waits: give up, flag, carry on without computing
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -161,23 +163,42 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
 }
 
 // MODE 0 plain, 1 gate+up+SiLU (tile rows 0-7 = gate rows, 8-15 = up rows of the same outputs), 2 residual+norm.
+//
+// Stage schedule (the producer lane and every consumer warp walk the same list): the CTA owns the
+// flattened tile range [t_begin, t_end); a stage is the next run of at most kStageTiles tiles that
+// stays inside one row block.
+struct StageIter {
+    long long t, t_end;
+    int G;
+    __device__ bool next(long long &t0, int &n) {
+        if (t >= t_end) return false;
+        const long long rb_end = (t / G + 1) * G;
+        long long e = t + kStageTiles;
+        if (e > rb_end) e = rb_end;
+        if (e > t_end) e = t_end;
+        t0 = t;
+        n = (int)(e - t);
+        t = e;
+        return true;
+    }
+};
+
 template <int MODE, int NB>
 __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    const int G = p.G, tps = p.tps, nring = p.nring;
-    const int stage_bytes = tps * (kTileBytes + kTileSzBytes);
-    unsigned char *ring = smem;                                             // nring * stage_bytes (weights then sz per stage)
-    uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);  // G * 2NB * 32 words
-    float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 2 * NB * 32);          // G * NB
-    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // 8 warps * 64 + 64 + 16
-    uint64_t *full = reinterpret_cast<uint64_t *>(red + kV2Consumers * 64 + 64 + 16);  // nring
+    const int G = p.G, nring = p.nring;
+    constexpr int stage_bytes = kStageTiles * kTileBytes;
+    unsigned char *ring = smem;                                                        // nring * stage_bytes
+    uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);   // G * 2NB * 32 words
+    float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 2 * NB * 32);           // G * NB
+    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // warps * 64 + 64 + warps
+    uint64_t *full = reinterpret_cast<uint64_t *>(red + kV2Consumers * 64 + 64 + kV2Consumers);
     uint64_t *empty = full + nring;
     int *flag = reinterpret_cast<int *>(empty + nring);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int spb = G / tps;  // stages per row block
-    const long long total = (long long)p.nblk * spb;
-    const int s_begin = (int)(total * blockIdx.x / gridDim.x), s_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+    const long long total = (long long)p.nblk * G;  // tiles
+    const long long t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
 
     if (tid == 0) {
         for (int i = 0; i < nring; i++) {
@@ -192,14 +213,14 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     if (warp == kV2Consumers) {
         // ------------------------------------------------ producer: one lane streams the stages
         if (lane == 0) {
-            for (int s = s_begin; s < s_end; s++) {
-                const int it = s - s_begin, slot = it % nring;
-                if (!mbar_wait(&empty[slot], ((it / nring) & 1) ^ 1, p.err)) break;
-                unsigned char *dst = ring + (size_t)slot * stage_bytes;
-                const size_t tile0 = (size_t)s * tps;  // flattened [row block][group] index of the stage's first tile
-                mbar_expect_tx(&full[slot], (uint32_t)stage_bytes);
-                bulk_g2s(dst, p.tiles + tile0 * kTileBytes, (uint32_t)(tps * kTileBytes), &full[slot]);
-                bulk_g2s(dst + tps * kTileBytes, p.tsz + tile0 * kTileSzBytes, (uint32_t)(tps * kTileSzBytes), &full[slot]);
+            StageIter it{t_begin, t_end, G};
+            long long t0;
+            int n;
+            for (int i = 0; it.next(t0, n); i++) {
+                const int slot = i % nring;
+                if (!mbar_wait(&empty[slot], ((i / nring) & 1) ^ 1, p.err)) break;
+                mbar_expect_tx(&full[slot], (uint32_t)(n * kTileBytes));
+                bulk_g2s(ring + (size_t)slot * stage_bytes, p.tiles + (size_t)t0 * kTileBytes, (uint32_t)(n * kTileBytes), &full[slot]);
             }
         }
         return;
@@ -237,10 +258,10 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 
     const int g = lane >> 2, t = lane & 3;  // fragment coordinates: rows g and g+8, batch column pair t
     float acc0 = 0.0f, acc1 = 0.0f;          // rows g, g+8 for batch t
-    int cur_rb = s_begin < s_end ? s_begin / spb : -1;
+    int cur_rb = t_begin < t_end ? (int)(t_begin / G) : -1;
     bool dead = false;
 
-    // Finish row block rb: reduce the 8 warps, then either write the outputs (block fully inside this CTA's
+    // Finish row block rb: reduce the warps, then either write the outputs (block fully inside this CTA's
     // range) or publish a partial and let the last contributing CTA combine them in CTA order.
     auto flush = [&](int rb) {
         if (t < NB) {
@@ -255,11 +276,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 #pragma unroll
             for (int w = 0; w < kV2Consumers; w++) v += red[w * 64 + tid];
         }
-        const long long b0 = (long long)rb * spb, b1 = b0 + spb;
-        const bool complete = b0 >= s_begin && b1 <= s_end;
+        const long long b0 = (long long)rb * G, b1 = b0 + G;
+        const bool complete = b0 >= t_begin && b1 <= t_end;
         bool finalize = complete;
         if (!complete) {
-            const int slot = (rb == s_begin / spb) ? 0 : 1;
+            const int slot = (rb == (int)(t_begin / G)) ? 0 : 1;
             if (tid < 64) p.partial[((size_t)blockIdx.x * 2 + slot) * 64 + tid] = v;
             __threadfence();
             consumer_sync();
@@ -276,8 +297,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
                 v = 0.0f;
                 if (tid < 64) {
                     for (int c = c_first; c <= c_last; c++) {
-                        const int cb = (int)(total * c / gridDim.x);
-                        const int cslot = (rb == cb / spb) ? 0 : 1;
+                        const long long cb = total * c / gridDim.x;
+                        const int cslot = (rb == (int)(cb / G)) ? 0 : 1;
                         v += __ldcg(&p.partial[((size_t)c * 2 + cslot) * 64 + tid]);
                     }
                 }
@@ -304,41 +325,53 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         consumer_sync();  // red / flag are reused by the next flush
     };
 
+    // One tile: 16 rows x 128 columns against the staged activations.
+    auto tile_dot = [&](const unsigned char *tile, int grp) {
+        const uint4 w0 = *reinterpret_cast<const uint4 *>(tile + lane * 16);        // row g
+        const uint4 w1 = *reinterpret_cast<const uint4 *>(tile + 512 + lane * 16);  // row g+8
+        uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = xb0;
+        if (g < 2 * NB) {
+            const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp * 2 * NB + g) * 4 + t) * 8);
+            xb0 = xp[0];  // (even, odd) words of j = 0, 1
+            xb1 = xp[1];  // j = 2, 3
+        }
+        // four independent accumulator sets: the mma latencies overlap instead of chaining
+        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0}, c3[4] = {0, 0, 0, 0};
+        constexpr unsigned M = 0x0F0F0F0Fu;
+        mma_u8s8(c0, w0.x & M, w1.x & M, (w0.x >> 4) & M, (w1.x >> 4) & M, xb0.x, xb0.y);
+        mma_u8s8(c1, w0.y & M, w1.y & M, (w0.y >> 4) & M, (w1.y >> 4) & M, xb0.z, xb0.w);
+        mma_u8s8(c2, w0.z & M, w1.z & M, (w0.z >> 4) & M, (w1.z >> 4) & M, xb1.x, xb1.y);
+        mma_u8s8(c3, w0.w & M, w1.w & M, (w0.w >> 4) & M, (w1.w >> 4) & M, xb1.z, xb1.w);
+        if (t < NB) {
+            const float2 m = meta[grp * NB + t];
+            const __half2 *szp = reinterpret_cast<const __half2 *>(tile + kTileCodeBytes);
+            const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+            const int hi0 = c0[0] + c1[0] + c2[0] + c3[0], lo0 = c0[1] + c1[1] + c2[1] + c3[1];
+            const int hi1 = c0[2] + c1[2] + c2[2] + c3[2], lo1 = c0[3] + c1[3] + c2[3] + c3[3];
+            const float f0 = (float)(hi0 * 256 + lo0), f1 = (float)(hi1 * 256 + lo1);
+            acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+            acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+        }
+    };
+
     // A warp whose wait ran out stops computing but keeps every barrier of the schedule, so that
     // the other warps and the producer still run to the end; the host sees the error word.
-    for (int s = s_begin; s < s_end; s++) {
-        const int it = s - s_begin, slot = it % nring;
-        const int rb = s / spb, part = s % spb;
+    StageIter it{t_begin, t_end, G};
+    long long t0;
+    int n;
+    for (int i = 0; it.next(t0, n); i++) {
+        const int slot = i % nring;
+        const int rb = (int)(t0 / G), grp0 = (int)(t0 % G);
         if (rb != cur_rb) {
             flush(cur_rb);
             cur_rb = rb;
         }
-        if (!dead && !mbar_wait(&full[slot], (it / nring) & 1, p.err)) dead = true;
+        if (!dead && !mbar_wait(&full[slot], (i / nring) & 1, p.err)) dead = true;
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
-        for (int ti = warp; ti < tps && !dead; ti += kV2Consumers) {
-            const int grp = part * tps + ti;
-            const uint4 w0 = *reinterpret_cast<const uint4 *>(st + ti * kTileBytes + lane * 16);        // row g
-            const uint4 w1 = *reinterpret_cast<const uint4 *>(st + ti * kTileBytes + 512 + lane * 16);  // row g+8
-            uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = xb0;
-            if (g < 2 * NB) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp * 2 * NB + g) * 4 + t) * 8);
-                xb0 = xp[0];  // (even, odd) words of j = 0, 1
-                xb1 = xp[1];  // j = 2, 3
-            }
-            int c[4] = {0, 0, 0, 0};
-            constexpr unsigned M = 0x0F0F0F0Fu;
-            mma_u8s8(c, w0.x & M, w1.x & M, (w0.x >> 4) & M, (w1.x >> 4) & M, xb0.x, xb0.y);
-            mma_u8s8(c, w0.y & M, w1.y & M, (w0.y >> 4) & M, (w1.y >> 4) & M, xb0.z, xb0.w);
-            mma_u8s8(c, w0.z & M, w1.z & M, (w0.z >> 4) & M, (w1.z >> 4) & M, xb1.x, xb1.y);
-            mma_u8s8(c, w0.w & M, w1.w & M, (w0.w >> 4) & M, (w1.w >> 4) & M, xb1.z, xb1.w);
-            if (t < NB) {
-                const float2 m = meta[grp * NB + t];
-                const __half2 *szp = reinterpret_cast<const __half2 *>(st + tps * kTileBytes + ti * kTileSzBytes);
-                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)(c[0] * 256 + c[1]), f1 = (float)(c[2] * 256 + c[3]);
-                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-            }
+        if (!dead) {
+            const int ta = warp, tb = warp + kV2Consumers;
+            if (ta < n) tile_dot(st + (size_t)ta * kTileBytes, grp0 + ta);
+            if (tb < n) tile_dot(st + (size_t)tb * kTileBytes, grp0 + tb);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
@@ -347,11 +380,12 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 }
 
 // ---- load-time repack -------------------------------------------------------
-// Row-major codes [N][K/2] + interleaved (s, z) [N][G]  ->  tiles.  One thread per 16-byte chunk.
+// Row-major codes [N][K/2] + interleaved (s, z) [N][G]  ->  tiles of 1088 bytes (1024 of nibbles: 16 rows x
+// 64 bytes, then the 16 (scale, zero) pairs).  One thread per 16-byte chunk of nibbles.
 // rows_per_blk = 16 (plain) or 8 (gate/up pair: tile rows 0-7 from matrix 0, 8-15 from matrix 1).
 __global__ void v2_repack_kernel(const uint8_t *__restrict__ codes0, const __half2 *__restrict__ sz0, const uint8_t *__restrict__ codes1,
                                  const __half2 *__restrict__ sz1, int N, int K, int G, int nblk, int rows_per_blk,
-                                 uint8_t *__restrict__ tiles, __half2 *__restrict__ tsz) {
+                                 uint8_t *__restrict__ tiles) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // chunk index: ((rb*G + grp)*16 + r)*4 + c
     const size_t nchunks = (size_t)nblk * G * 64;
     if (i >= nchunks) return;
@@ -364,33 +398,29 @@ __global__ void v2_repack_kernel(const uint8_t *__restrict__ codes0, const __hal
     const __half2 *sz = second ? sz1 : sz0;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < N) v = *reinterpret_cast<const uint4 *>(codes + (size_t)row * (K / 2) + grp * 64 + c * 16);
-    reinterpret_cast<uint4 *>(tiles)[i] = v;
-    if (c == 0) tsz[tile * 16 + r] = row < N ? sz[(size_t)row * G + grp] : __halves2half2(__float2half(0.0f), __float2half(0.0f));
+    uint8_t *dst = tiles + tile * kTileBytes;
+    *reinterpret_cast<uint4 *>(dst + r * 64 + c * 16) = v;
+    if (c == 0)
+        reinterpret_cast<__half2 *>(dst + kTileCodeBytes)[r] =
+            row < N ? sz[(size_t)row * G + grp] : __halves2half2(__float2half(0.0f), __float2half(0.0f));
 }
 
 int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, const __half2 *sz1, int N, int K, int G, int nblk,
-              int rows_per_blk, uint8_t *tiles, __half2 *tsz, cudaStream_t st) {
+              int rows_per_blk, uint8_t *tiles, cudaStream_t st) {
     const size_t nchunks = (size_t)nblk * G * 64;
-    v2_repack_kernel<<<(unsigned)((nchunks + 255) / 256), 256, 0, st>>>(codes0, sz0, codes1, sz1, N, K, G, nblk, rows_per_blk, tiles, tsz);
+    v2_repack_kernel<<<(unsigned)((nchunks + 255) / 256), 256, 0, st>>>(codes0, sz0, codes1, sz1, N, K, G, nblk, rows_per_blk, tiles);
     IM_CUDA_CHECK(cudaGetLastError());
     return IM_OK;
 }
 
-static int pick_tps(int G) {
-    for (int t = 8; t >= 1; t--)
-        if (G % t == 0) return t;
-    return 1;
-}
-
 template <int MODE, int NB>
 static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
-    p.tps = pick_tps(p.G);
-    const size_t stage_bytes = (size_t)p.tps * (kTileBytes + kTileSzBytes);
-    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + (kV2Consumers * 64 + 64 + 16) * 4 + 64;
+    const size_t stage_bytes = (size_t)kStageTiles * kTileBytes;
+    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + (kV2Consumers * 64 + 64 + kV2Consumers) * 4 + 64;
     const size_t budget = dev->smem_optin > 8192 ? dev->smem_optin - 2048 : 0;
-    if (fixed + 2 * stage_bytes + 64 > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel
+    if (fixed + 3 * stage_bytes + 64 > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel
     int nring = (int)((budget - fixed - 64) / (stage_bytes + 16));
-    if (nring > 24) nring = 24;
+    if (nring > 8) nring = 8;
     p.nring = nring;
     const size_t smem = (size_t)nring * stage_bytes + fixed + (size_t)nring * 16;
     auto kern = matvec_v2_kernel<MODE, NB>;
@@ -399,7 +429,7 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
         IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
         configured = true;
     }
-    const long long total = (long long)p.nblk * (p.G / p.tps);
+    const long long total = (long long)p.nblk * p.G;
     int grid = dev->sm_count;
     if (grid > total) grid = (int)total;
     kern<<<grid, kV2Threads, smem, st>>>(p);
