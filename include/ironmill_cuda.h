@@ -144,6 +144,16 @@ int im_cuda_fused_residual_norm_matvec(const im_affine_weight *w, const void *a_
                                        const void *gamma_dev, float eps, void *y_dev,
                                        void *residual_out_dev, void *normed_out_dev, int B, void *stream);
 
+/* fused_residual_rms_norm followed by the fused gate+up+SiLU projection in one launch:
+ * r = a + b; out[n] = f16( silu(rms_inv * gate[n].(r gamma / awq)) * (rms_inv * up[n].(r gamma / awq)) );
+ * residual_out = f16(r), normed_out = f16(r * rms_inv * gamma) (either may be NULL for tiled INT4 weights).
+ * Stands for the pair (.../shaders/norm/fused_residual_norm.metal:33-75, .../quantized/affine_fused.metal:9-108)
+ * that the reference encodes back to back (crates/ironmill-inference/src/metal/pipeline.rs:887-905, ffn.rs:25-54);
+ * the projection reads the unrounded normalised vector instead of its fp16 copy. */
+int im_cuda_fused_residual_norm_ffn(const im_affine_weight *gate, const im_affine_weight *up, const void *a_dev,
+                                    const void *b_dev, const void *gamma_dev, float eps, void *out_dev,
+                                    void *residual_out_dev, void *normed_out_dev, int B, void *stream);
+
 /* Dense fp16 matvec y = W x (lm_head): matvec
  * (.../shaders/linear/matvec.metal:30-84; crates/ironmill-inference/src/metal/pipeline.rs:1159-1174).
  * w_dev fp16 [N,K] row-major, x_dev fp16 [B,K], y_dev fp16 [B,N]. */

@@ -28,7 +28,7 @@ constexpr int kGroup = 128;     // fast-path group size
 constexpr int kWarps = 8;       // warps per CTA
 constexpr int kThreads = kWarps * 32;
 
-enum MatvecMode { kPlain = 0, kGateUpAct = 1, kResidualNorm = 2 };
+enum MatvecMode { kPlain = 0, kGateUpAct = 1, kResidualNorm = 2, kResNormGateUp = 3 };
 
 struct MatvecParams {
     const uint8_t *codes0;  // plain / gate rows
@@ -527,7 +527,7 @@ static int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaS
 template <int MODE>
 static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const AffineWeight *up, int B, cudaStream_t st) {
     V2Params q{};
-    if (MODE == kGateUpAct) {
+    if (MODE & 1) {
         if ((w->N + 7) / 8 > kSkMaxBlocks) return IM_ERR_BOUNDS;
         int rc = ensure_pair(w, up, st);
         if (rc != IM_OK) return rc;
@@ -791,6 +791,35 @@ IM_EXPORT int im_cuda_fused_residual_norm_matvec(const im_affine_weight *w, cons
     p.residual_out = static_cast<__half *>(residual_out_dev);
     p.normed_out = static_cast<__half *>(normed_out_dev);
     return im::run_matvec<im::kResidualNorm>(p, w, B, im::as_stream(stream));
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_fused_residual_norm_ffn(const im_affine_weight *gate, const im_affine_weight *up, const void *a_dev,
+                                              const void *b_dev, const void *gamma_dev, float eps, void *out_dev,
+                                              void *residual_out_dev, void *normed_out_dev, int B, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(gate && up && a_dev && b_dev && gamma_dev && out_dev, "bad argument");
+    IM_REQUIRE(B >= 1 && B <= 64, "batch must be in 1..64, got %d", B);
+    IM_REQUIRE(gate->N == up->N && gate->K == up->K && gate->bits == up->bits && gate->group_size == up->group_size,
+               "gate [%d,%d] and up [%d,%d] must have the same shape and format", gate->N, gate->K, up->N, up->K);
+    cudaStream_t st = im::as_stream(stream);
+    if (gate->tiles && up->tiles) {
+        im::MatvecParams p = im::base_params(gate);
+        p.x = static_cast<const __half *>(a_dev);
+        p.b = static_cast<const __half *>(b_dev);
+        p.gamma = static_cast<const __half *>(gamma_dev);
+        p.eps = eps;
+        p.y = static_cast<__half *>(out_dev);
+        p.residual_out = static_cast<__half *>(residual_out_dev);
+        p.normed_out = static_cast<__half *>(normed_out_dev);
+        const int rc = im::run_matvec_v2<im::kResNormGateUp>(p, gate, up, B, st);
+        if (rc != IM_ERR_BOUNDS) return rc;
+    }
+    // formats without the tiled layout: the two-step form
+    IM_REQUIRE(residual_out_dev && normed_out_dev, "this weight format needs residual_out and normed_out buffers");
+    int rc = im_cuda_fused_residual_rms_norm(a_dev, b_dev, gamma_dev, normed_out_dev, residual_out_dev, gate->K, B, eps, stream);
+    if (rc != IM_OK) return rc;
+    return im_cuda_ffn_gate_up_act(gate, up, normed_out_dev, out_dev, B, stream);
     IM_GUARD_END
 }
 

@@ -108,7 +108,7 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
                 v[2 * i + 1] = f.y;
             }
         }
-        if (MODE == 2) {
+        if (MODE & 2) {
             const uint4 rb = *reinterpret_cast<const uint4 *>(p.b + (size_t)b * K + k);
             const uint4 rg = *reinterpret_cast<const uint4 *>(p.gamma + k);
             const __half2 *hb = reinterpret_cast<const __half2 *>(&rb), *hg = reinterpret_cast<const __half2 *>(&rg);
@@ -162,7 +162,8 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
     return sq;
 }
 
-// MODE 0 plain, 1 gate+up+SiLU (tile rows 0-7 = gate rows, 8-15 = up rows of the same outputs), 2 residual+norm.
+// MODE bit 0: gate+up+SiLU epilogue (tile rows 0-7 = gate rows, 8-15 = up rows of the same outputs);
+// MODE bit 1: residual + RMSNorm prologue (x = (a + b) * gamma, outputs scaled by rms_inv).
 //
 // Stage schedule (the producer lane and every consumer warp walk the same list): the CTA owns the
 // flattened tile range [t_begin, t_end); a stage is the next run of at most kStageTiles tiles that
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     for (int b = 0; b < NB; b++) {
         float sq = v2_stage_x<MODE, NB>(p, b, xq, meta, kV2Consumers);
         sq_tot[b] = 0.0f;
-        if (MODE == 2) {
+        if (MODE & 2) {
             sq = warp_sum(sq);
             if (lane == 0) red[kV2Consumers * 64 + 64 + warp] = sq;
             consumer_sync();
@@ -246,8 +247,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     consumer_sync();
     float rms_inv[NB];
 #pragma unroll
-    for (int b = 0; b < NB; b++) rms_inv[b] = MODE == 2 ? rsqrtf(sq_tot[b] / (float)p.K + p.eps) : 1.0f;
-    if (MODE == 2 && blockIdx.x == 0) {  // side outputs (must not alias a or b)
+    for (int b = 0; b < NB; b++) rms_inv[b] = (MODE & 2) ? rsqrtf(sq_tot[b] / (float)p.K + p.eps) : 1.0f;
+    if ((MODE & 2) && blockIdx.x == 0) {  // side outputs (must not alias a or b)
         for (int b = 0; b < NB; b++)
             for (int k = tid; k < p.K; k += kV2Consumers * 32) {
                 const float r = __half2float(p.x[(size_t)b * p.K + k]) + __half2float(p.b[(size_t)b * p.K + k]);
@@ -306,19 +307,19 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             }
         }
         if (finalize) {
-            if (MODE == 1) {
-                if (tid < 64) red[kV2Consumers * 64 + tid] = v;
+            float ri = rms_inv[0];
+#pragma unroll
+            for (int b = 1; b < NB; b++) ri = bb == b ? rms_inv[b] : ri;
+            if (MODE & 1) {
+                if (tid < 64) red[kV2Consumers * 64 + tid] = v * ri;
                 consumer_sync();
                 if (tid < 32 && bb < NB) {  // rows 0..7: gate, partner row + 8: up
-                    const float gv = v, uv = red[kV2Consumers * 64 + tid + 32];
+                    const float gv = v * ri, uv = red[kV2Consumers * 64 + tid + 32];
                     const int n = rb * 8 + row;
                     if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
                 }
             } else if (tid < 64 && bb < NB) {
                 const int n = rb * 16 + row;
-                float ri = rms_inv[0];
-#pragma unroll
-                for (int b = 1; b < NB; b++) ri = bb == b ? rms_inv[b] : ri;
                 if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn(v * ri);
             }
         }
@@ -437,11 +438,11 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     return IM_OK;
 }
 
-// mode: 0 plain, 1 gate+up (fused tiles), 2 residual+norm.  Returns IM_ERR_BOUNDS if the shape does not fit.
+// mode: bit 0 gate+up epilogue (paired tiles), bit 1 residual+norm prologue.  IM_ERR_BOUNDS if the shape does not fit.
 int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st) {
 #define V2_CASE(M, B) \
     if (mode == M && nb == B) return v2_launch<M, B>(p, dev, st);
-    V2_CASE(0, 1) V2_CASE(0, 2) V2_CASE(0, 4) V2_CASE(1, 1) V2_CASE(1, 2) V2_CASE(1, 4) V2_CASE(2, 1) V2_CASE(2, 2) V2_CASE(2, 4)
+    V2_CASE(0, 1) V2_CASE(0, 2) V2_CASE(0, 4) V2_CASE(1, 1) V2_CASE(1, 2) V2_CASE(1, 4) V2_CASE(2, 1) V2_CASE(2, 2) V2_CASE(2, 4) V2_CASE(3, 1) V2_CASE(3, 2) V2_CASE(3, 4)
 #undef V2_CASE
     return fail(IM_ERR_INVALID, "unsupported v2 matvec mode %d / batch %d", mode, nb);
 }
