@@ -217,6 +217,17 @@ int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, 
                          const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,
                          void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
                          int num_splits, void *stream);
+/* One call for the whole attention block of a decode step, two launches + reduce instead of five:
+ * (fused_qk_norm_rope | rope) on the q and k parts of a fused QKV row, turboquant_cache_write of K and V, the query
+ * rotation that turboquant_attention starts with (done once per head here), then the split attention.
+ * qkv_dev fp16 [nseq*T, qkv_stride] with q at 0, k at k_offset, v at v_offset (elements); norm weights NULL = plain
+ * RoPE (Llama); qrot_dev f32 scratch [nseq*T, nh, 2, head_dim].  Same references as the separate entry points. */
+int im_cuda_tq_fused_attention(im_tq *tq, const void *qkv_dev, int qkv_stride, int k_offset, int v_offset,
+                               const void *q_norm_w_dev, const void *k_norm_w_dev, const void *cos_dev, const void *sin_dev,
+                               int rotary_dim, float eps, void *k_cache_dev, void *v_cache_dev, float *k_scale_dev,
+                               float *v_scale_dev, float *k_rnorm_dev, float attn_scale, float *qrot_dev, void *out_dev,
+                               int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
+                               int num_splits, void *stream);
 size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
 int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
 

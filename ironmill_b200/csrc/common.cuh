@@ -87,6 +87,7 @@ struct V2Params {
     float *partial;  // [grid][2][64]
     int *counters;   // [nblk], zero between launches
     int *err;
+    unsigned long long *trace;  // optional: 8 timer stamps from CTA 0 (development aid), else nullptr
 };
 
 int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st);
@@ -145,16 +146,30 @@ int launch_qk_rope(const QkRopeArgs &a, int T, cudaStream_t st);
 struct Tq {
     Device *dev = nullptr;
     int hd = 0, n_bits = 0, k_levels = 0, v_levels = 0;
-    float *signs = nullptr, *qjl = nullptr, *k_cb = nullptr, *k_bd = nullptr, *v_cb = nullptr, *v_bd = nullptr;
+    float *signs = nullptr, *qjl = nullptr, *qjl_t = nullptr, *k_cb = nullptr, *k_bd = nullptr, *v_cb = nullptr, *v_bd = nullptr;
     float *scratch = nullptr;
     size_t scratch_bytes = 0;
     size_t const_bytes = 0;
 };
 
 int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len);
+// Inputs of the fused RoPE + cache write + query rotation launch (turboquant.cu).
+struct TqPrep {
+    const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
+    int stride, k_off, v_off;
+    const __half *qw, *kw, *cosc, *sinc;
+    int nh, nkv, rotary_dim, with_norm, T, nseq, max_seq, base_pos;
+    float eps;
+    const int *pos_dev;
+    float *qrot;    // out [nseq*T, nh, 2, hd]
+    __half *q_out;  // optional out [nseq*T, nh, hd]
+    uint8_t *kc, *vc;
+    float *ks, *vs, *krn;
+};
+int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st);
 int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,
                         const float *vs, const float *krn, float attn_scale, __half *out, int nseq, int nh, int nkv, int max_seq,
-                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st);
+                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot = nullptr);
 
 }  // namespace im
 

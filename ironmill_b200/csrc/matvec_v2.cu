@@ -201,6 +201,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     const long long total = (long long)p.nblk * G;  // tiles
     const long long t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
 
+#define IM_STAMP(i) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[i] = global_ns(); } while (0)
+    IM_STAMP(0);
     if (tid == 0) {
         for (int i = 0; i < nring; i++) {
             mbar_init(&full[i], 1);
@@ -245,6 +247,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         }
     }
     consumer_sync();
+    IM_STAMP(1);
     float rms_inv[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) rms_inv[b] = (MODE & 2) ? rsqrtf(sq_tot[b] / (float)p.K + p.eps) : 1.0f;
@@ -368,6 +371,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             cur_rb = rb;
         }
         if (!dead && !mbar_wait(&full[slot], (i / nring) & 1, p.err)) dead = true;
+        if (i == 0) IM_STAMP(2);
+        if (i == 1) IM_STAMP(3);
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
         if (!dead) {
             const int ta = warp, tb = warp + kV2Consumers;
@@ -377,7 +382,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
     }
+    IM_STAMP(4);
     if (cur_rb >= 0) flush(cur_rb);
+    IM_STAMP(5);
 }
 
 // ---- load-time repack -------------------------------------------------------

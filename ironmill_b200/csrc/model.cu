@@ -119,6 +119,7 @@ struct Model {
     int MT = 0;
     __half *hidden = nullptr, *norm_out = nullptr, *residual = nullptr, *qkv = nullptr, *q_d = nullptr, *k_d = nullptr, *v_d = nullptr,
            *attn_out = nullptr, *ffn_down = nullptr, *ffn_gate = nullptr, *logits = nullptr, *logits_all = nullptr;
+    float *qrot = nullptr;  // [MT, nh_l, 2, hd] rotated queries
     uint32_t *tokens_dev = nullptr, *tok_hist = nullptr;
     int *pos_dev = nullptr, *step_dev = nullptr;
     uint32_t *tokens_pin = nullptr;
@@ -317,36 +318,33 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
             nl += (MT + 3) / 4;
             IM_MARK(kCatQkv);
         }
-        QkRopeArgs a{};
-        a.q_in = m->qkv; a.k_in = m->qkv + m->q_dim; a.v_in = m->qkv + m->q_dim + m->kv_dim;
-        a.q_stride = a.k_stride = a.v_stride = m->qkv_dim;
-        a.q_out = m->q_d; a.k_out = m->k_d; a.v_out = m->v_d;
+        // (QK-norm +) RoPE, K/V cache write and query rotation in one launch, then split attention + reduce
+        TqPrep a{};
+        a.qkv = m->qkv; a.stride = m->qkv_dim; a.k_off = m->q_dim; a.v_off = m->q_dim + m->kv_dim;
         a.qw = L.q_norm; a.kw = L.k_norm; a.cosc = m->cosc; a.sinc = m->sinc;
-        a.nh = m->nh_l; a.nkv = m->nkv_l; a.hd = hd; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd;
-        a.seq_offset = 0; a.pos_dev = m->pos_dev; a.tokens_per_seq = T; a.eps = eps; a.with_norm = c.qk_norm ? 1 : 0;
-        IM_TRY(launch_qk_rope(a, MT, st));
-        IM_MARK(kCatRope);
-        IM_TRY(im_cuda_tq_encode(m->tq, m->k_d, 1, L.kc, L.ks, L.krn, nseq, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, st));
-        IM_TRY(im_cuda_tq_encode(m->tq, m->v_d, 0, L.vc, L.vs, L.krn /*unused*/, nseq, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, st));
+        a.nh = m->nh_l; a.nkv = m->nkv_l; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd; a.with_norm = c.qk_norm ? 1 : 0;
+        a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev;
+        a.qrot = m->qrot; a.q_out = nullptr;
+        a.kc = L.kc; a.vc = L.vc; a.ks = L.ks; a.vs = L.vs; a.krn = L.krn;
+        IM_TRY(tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st));
         IM_MARK(kCatKvWrite);
-        IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, m->q_d, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
-                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st));
-        nl += 5;
+        IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
+                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot));
+        nl += 3;
         IM_MARK(kCatAttn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.o), m->attn_out, m->ffn_down, MT, st));
         IM_MARK(kCatOProj);
         IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
         if (m->world > 1) IM_MARK(kCatComm);
-        IM_TRY(im_cuda_fused_residual_rms_norm(m->hidden, m->ffn_down, L.post_ln, m->norm_out, m->residual, H, MT, eps, st));
-        IM_MARK(kCatResNorm);
-        IM_TRY(im_cuda_ffn_gate_up_act(static_cast<im_affine_weight *>(L.gate), static_cast<im_affine_weight *>(L.up), m->norm_out,
-                                       m->ffn_gate, MT, st));
+        // residual + RMSNorm folded into the gate/up projection (the projection reads the unrounded normalised vector)
+        IM_TRY(im_cuda_fused_residual_norm_ffn(static_cast<im_affine_weight *>(L.gate), static_cast<im_affine_weight *>(L.up), m->hidden,
+                                               m->ffn_down, L.post_ln, eps, m->ffn_gate, m->residual, m->norm_out, MT, st));
         IM_MARK(kCatFfn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.down), m->ffn_gate, m->ffn_down, MT, st));
         IM_MARK(kCatDown);
         IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
         if (m->world > 1) IM_MARK(kCatComm);
-        nl += 1 + 3 * ((MT + 3) / 4) + (m->world > 1 ? 2 : 0);
+        nl += 3 * ((MT + 3) / 4) + (m->world > 1 ? 2 : 0);
         if (l + 1 < c.num_layers) {
             Layer &Nx = m->layers[l + 1];
             IM_TRY(im_cuda_fused_residual_norm_matvec(static_cast<im_affine_weight *>(Nx.qkv), m->residual, m->ffn_down, Nx.input_ln, eps,
@@ -391,10 +389,8 @@ static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
     cudaStream_t st = m->stream;
     // one eager pass first: sets function attributes and warms NCCL outside the capture
     const int splits = decode_splits(m, batch);
-    int saved_pos = m->seq_pos;
     IM_TRY(forward(m, batch, 1, splits, st, nullptr));
     IM_CUDA_CHECK(cudaStreamSynchronize(st));
-    (void)saved_pos;
     cudaGraph_t g = nullptr;
     IM_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     int nl = 0;
@@ -718,6 +714,7 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_TRY(m->alloc((void **)&m->k_d, MT * m->kv_dim * 2));
     IM_TRY(m->alloc((void **)&m->v_d, MT * m->kv_dim * 2));
     IM_TRY(m->alloc((void **)&m->attn_out, MT * m->q_dim * 2));
+    IM_TRY(m->alloc((void **)&m->qrot, MT * m->q_dim * 2 * sizeof(float)));
     IM_TRY(m->alloc((void **)&m->ffn_down, MT * H * 2));
     IM_TRY(m->alloc((void **)&m->ffn_gate, MT * m->I_l * 2));
     IM_TRY(m->alloc((void **)&m->logits, (size_t)c.max_batch * m->vocab_l * 2));

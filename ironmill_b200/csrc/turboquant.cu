@@ -124,18 +124,20 @@ __device__ __forceinline__ void hadamard_block(float *x, int pitch, const float 
 }
 
 // ---------------------------------------------------------------- encode (bit-exact)
-// grid (nkv, nseq*T), hd threads.
-__global__ void tq_encode_kernel(const __half *__restrict__ kv, const float *__restrict__ signs, const float *__restrict__ cb,
-                                 const float *__restrict__ bounds, const float *__restrict__ qjl, int is_k, int n_levels,
-                                 uint8_t *__restrict__ cache, float *__restrict__ scale_buf, float *__restrict__ r_norms, int nkv, int hd,
-                                 int max_seq, int base_pos, const int *__restrict__ pos_dev, int T) {
-    extern __shared__ float sh[];
+struct EncodeTables {
+    const float *signs, *cb, *bounds, *qjl_t;  // bounds = suffix minima; qjl_t = transposed QJL matrix [k][d]
+    int n_levels, is_k;
+};
+
+// Encodes one head vector; thread d holds element d (already widened from fp16).  sh = 3*hd floats.
+// Every operation and its order follow turboquant_cache_write; the QJL dot product walks k upwards
+// with separate multiply and add, reading the transposed matrix so that the warp's loads coalesce.
+__device__ __forceinline__ void tq_encode_body(float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
+                                               float *scale_out, float *rnorm_out) {
     float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
-    const int d = threadIdx.x, h = blockIdx.x, st = blockIdx.y;
-    const int seq = st / T, t = st % T;
-    const int pos = (base_pos + (pos_dev ? pos_dev[seq] : 0) + t) % max_seq;
-    const float sg = signs[d];
-    xs[d] = __fmul_rn(__half2float(kv[((size_t)st * nkv + h) * hd + d]), sg);
+    const int d = threadIdx.x;
+    const float sg = tb.signs[d];
+    xs[d] = __fmul_rn(xin, sg);
     __syncthreads();
     for (int step = 1; step < hd; step <<= 1) {
         if (d < hd / 2) {
@@ -155,22 +157,21 @@ __global__ void tq_encode_kernel(const __half *__restrict__ kv, const float *__r
         __syncthreads();
     }
     const float norm = __fsqrt_rn(fmaxf(red[0], 1e-20f));
-    const size_t row = ((size_t)seq * nkv + h) * max_seq + pos;
-    if (d == 0) scale_buf[row] = norm;
+    if (d == 0) *scale_out = norm;
     const float inv = __fdiv_rn(1.0f, fmaxf(norm, 1e-10f));
     const float u = __fmul_rn(x, inv);
     // The reference scans all boundaries and keeps the LAST b with u >= boundaries[b]
     // (index b + 1).  Its 7- and 8-bit tables are not monotone, so that is not a plain
     // upper bound; `bounds` holds the suffix minima of the table, which are monotone and
     // give the same answer: max{b : boundaries[b] <= u} = max{b : min(boundaries[b..]) <= u}.
-    int lo = 0, hi = n_levels - 1;
+    int lo = 0, hi = tb.n_levels - 1;
     while (lo < hi) {
         const int mid = (lo + hi) >> 1;
-        if (u >= bounds[mid]) lo = mid + 1; else hi = mid;
+        if (u >= tb.bounds[mid]) lo = mid + 1; else hi = mid;
     }
     unsigned byte = (unsigned)lo;
-    if (is_k) {
-        const float r = __fsub_rn(u, cb[lo]);
+    if (tb.is_k) {
+        const float r = __fsub_rn(u, tb.cb[lo]);
         __syncthreads();  // everyone has read red[0]
         res[d] = r;
         red[d] = __fmul_rn(r, r);
@@ -179,13 +180,26 @@ __global__ void tq_encode_kernel(const __half *__restrict__ kv, const float *__r
             if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
             __syncthreads();
         }
-        if (d == 0) r_norms[row] = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+        if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(red[0], 1e-20f));
         float proj = 0.0f;
-        const float *srow = qjl + (size_t)d * hd;
-        for (int k = 0; k < hd; k++) proj = __fadd_rn(proj, __fmul_rn(srow[k], res[k]));
+        for (int k = 0; k < hd; k++) proj = __fadd_rn(proj, __fmul_rn(tb.qjl_t[(size_t)k * hd + d], res[k]));
         if (proj >= 0.0f) byte |= 0x80u;
     }
-    cache[row * hd + d] = (uint8_t)byte;
+    cache_row[d] = (uint8_t)byte;
+    __syncthreads();  // sh may be reused by the caller
+}
+
+// grid (nkv, nseq*T), hd threads.
+__global__ void tq_encode_kernel(const __half *__restrict__ kv, const EncodeTables tb, uint8_t *__restrict__ cache,
+                                 float *__restrict__ scale_buf, float *__restrict__ r_norms, int nkv, int hd, int max_seq, int base_pos,
+                                 const int *__restrict__ pos_dev, int T) {
+    extern __shared__ float sh[];
+    const int d = threadIdx.x, h = blockIdx.x, st = blockIdx.y;
+    const int seq = st / T, t = st % T;
+    const int pos = (base_pos + (pos_dev ? pos_dev[seq] : 0) + t) % max_seq;
+    const size_t row = ((size_t)seq * nkv + h) * max_seq + pos;
+    tq_encode_body(__half2float(kv[((size_t)st * nkv + h) * hd + d]), tb, sh, hd, cache + row * hd, scale_buf + row,
+                   r_norms ? r_norms + row : nullptr);
 }
 
 // ---------------------------------------------------------------- attention
@@ -199,7 +213,8 @@ struct AttnParams {
     const __half *q;         // [nseq*T, nh, hd]
     const uint8_t *kc, *vc;  // [nseq, nkv, max_seq, hd]
     const float *ks, *vs, *krn;  // [nseq, nkv, max_seq]
-    const float *signs, *qjl, *k_cb, *v_cb;
+    const float *signs, *qjl, *k_cb, *v_cb;  // qjl: TRANSPOSED matrix [k][d]
+    const float *qrot;       // optional [nseq*T, nh, 2, hd]: rotated query and S * rotated query, computed upstream
     float *po, *pm, *pl;     // partials [nseq*T, nh, splits] x (hd | 1 | 1)
     float attn_scale, qjl_factor;
     int nh, nkv, max_seq, base_pos, T, splits;
@@ -244,26 +259,29 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
     cbk[tid] = p.k_cb[tid];
     cbv[tid] = p.v_cb[tid];
     cbv[tid + 128] = p.v_cb[tid + 128];
-#pragma unroll
-    for (int g = 0; g < GQ; g++) qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
     if (tid < GQ) {
         s_m[tid] = -INFINITY;
         s_l[tid] = 0.0f;
     }
-    __syncthreads();
-    hadamard_block<GQ>(qr, kQPitch, p.signs, kHd);
-    {
+    if (p.qrot) {
+#pragma unroll
+        for (int g = 0; g < GQ; g++) {
+            const float *src = p.qrot + ((size_t)st * p.nh + h0 + g) * 2 * kHd;
+            qr[g * kQPitch + qidx(tid)] = src[tid];
+            sq[g * kQPitch + qidx(tid)] = src[kHd + tid];
+        }
+    } else {
+#pragma unroll
+        for (int g = 0; g < GQ; g++) qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
+        __syncthreads();
+        hadamard_block<GQ>(qr, kQPitch, p.signs, kHd);
         float acc[GQ];
 #pragma unroll
         for (int g = 0; g < GQ; g++) acc[g] = 0.0f;
-        const float4 *srow = reinterpret_cast<const float4 *>(p.qjl + (size_t)tid * kHd);
-        for (int k4 = 0; k4 < kHd / 4; k4++) {
-            const float4 s4 = srow[k4];
+        for (int k = 0; k < kHd; k++) {  // transposed matrix: the warp reads consecutive floats
+            const float sv = p.qjl[(size_t)k * kHd + tid];
 #pragma unroll
-            for (int g = 0; g < GQ; g++) {
-                const float *qv = qr + g * kQPitch + k4 * 4;
-                acc[g] += s4.x * qv[0] + s4.y * qv[1] + s4.z * qv[2] + s4.w * qv[3];
-            }
+            for (int g = 0; g < GQ; g++) acc[g] = fmaf(sv, qr[g * kQPitch + k], acc[g]);
         }
         __syncthreads();
 #pragma unroll
@@ -390,6 +408,79 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
     }
 }
 
+// ---------------------------------------------------------------- fused (QK-norm +) RoPE + cache write + query rotation
+// One launch between the QKV projection and the attention: grid (nh + 2 nkv, nseq*T), hd = 128 threads.
+//   query heads : (RMSNorm,) RoPE as fused_qk_norm_rope / rope, rounded to fp16 like the reference's q buffer,
+//                 then the rotation R q and S (R q) that every attention CTA of the head would otherwise redo
+//   key heads   : (RMSNorm,) RoPE, rounded to fp16, then the bit-exact cache write
+//   value heads : the bit-exact cache write
+struct PrepArgs {
+    const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
+    int stride, k_off, v_off;
+    const __half *qw, *kw, *cosc, *sinc;
+    int nh, nkv, rotary_dim, with_norm, T, max_seq, base_pos;
+    float eps;
+    const int *pos_dev;
+    float *qrot;    // [nseq*T, nh, 2, hd]
+    __half *q_out;  // optional dense roped q [nseq*T, nh, hd]
+    EncodeTables ktab, vtab;
+    uint8_t *kc, *vc;
+    float *ks, *vs, *krn;
+};
+
+__global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a) {
+    __shared__ float sh[3 * kHd];
+    __shared__ float red[4];
+    const int d = threadIdx.x, slot = blockIdx.x, st = blockIdx.y;
+    const int seq = st / a.T, t = st % a.T;
+    const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
+    const __half *tok = a.qkv + (size_t)st * a.stride;
+    if (slot >= a.nh + a.nkv) {  // value head
+        const int h = slot - a.nh - a.nkv;
+        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
+        tq_encode_body(__half2float(tok[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, nullptr);
+        return;
+    }
+    const bool is_q = slot < a.nh;
+    const int h = is_q ? slot : slot - a.nh;
+    const __half *src = tok + (is_q ? 0 : a.k_off) + h * kHd;
+    const __half *w = is_q ? a.qw : a.kw;
+    float x = __half2float(src[d]);
+    if (a.with_norm) {
+        float ss = warp_sum(x * x);
+        if ((d & 31) == 0) red[d >> 5] = ss;
+        __syncthreads();
+        const float tot = red[0] + red[1] + red[2] + red[3];
+        x = x * rsqrtf(tot / (float)kHd + a.eps) * __half2float(w[d]);
+    }
+    sh[d] = x;
+    __syncthreads();
+    const int half_rot = a.rotary_dim / 2;
+    float y = x;
+    if (d < a.rotary_dim) {
+        const int i = d < half_rot ? d : d - half_rot;
+        const float lo = sh[i], hi = sh[i + half_rot];
+        const float c = __half2float(a.cosc[(size_t)pos_abs * (kHd / 2) + i]), sn = __half2float(a.sinc[(size_t)pos_abs * (kHd / 2) + i]);
+        y = d < half_rot ? lo * c - hi * sn : lo * sn + hi * c;
+    }
+    const __half yh = __float2half_rn(y);
+    __syncthreads();
+    if (!is_q) {
+        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
+        tq_encode_body(__half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row);
+        return;
+    }
+    if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;
+    sh[d] = __half2float(yh);
+    __syncthreads();
+    hadamard_block<1>(sh, kHd, a.ktab.signs, kHd);
+    float acc = 0.0f;
+    for (int k = 0; k < kHd; k++) acc = fmaf(a.ktab.qjl_t[(size_t)k * kHd + d], sh[k], acc);
+    float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
+    dst[d] = sh[d];
+    dst[kHd + d] = acc;
+}
+
 // Combine the splits of one (token, head), normalise, rotate back, write fp16.
 // The inverse rotation is linear, so applying it once after the combination equals the
 // reference's per-split rotation up to float rounding.  grid (nh, nseq*T), hd threads.
@@ -464,6 +555,7 @@ IM_EXPORT void im_cuda_tq_free(im_tq *tq) {
     const size_t hd = tq->hd;
     dev_free(tq->dev, tq->signs, hd * 4);
     dev_free(tq->dev, tq->qjl, hd * hd * 4);
+    dev_free(tq->dev, tq->qjl_t, hd * hd * 4);
     dev_free(tq->dev, tq->k_cb, (size_t)tq->k_levels * 4);
     dev_free(tq->dev, tq->k_bd, (size_t)tq->k_levels * 4);
     dev_free(tq->dev, tq->v_cb, (size_t)tq->v_levels * 4);
@@ -506,8 +598,12 @@ IM_EXPORT int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const 
     tq->k_levels = 1 << (n_bits - 1);
     tq->v_levels = 1 << n_bits;
     const size_t hd = head_dim;
+    const size_t hd_sz = head_dim;
+    std::vector<float> qt(hd_sz * hd_sz);
+    for (size_t r = 0; r < hd_sz; r++)
+        for (size_t c2 = 0; c2 < hd_sz; c2++) qt[c2 * hd_sz + r] = qjl_host[r * hd_sz + c2];
     struct Up { float **dst; const float *src; size_t n, alloc; };
-    Up ups[] = {{&tq->signs, signs_host, hd, hd}, {&tq->qjl, qjl_host, hd * hd, hd * hd},
+    Up ups[] = {{&tq->signs, signs_host, hd, hd}, {&tq->qjl, qjl_host, hd * hd, hd * hd}, {&tq->qjl_t, qt.data(), hd * hd, hd * hd},
                 {&tq->k_cb, k_levels_host, (size_t)tq->k_levels, (size_t)tq->k_levels},
                 {&tq->k_bd, k_bounds_host, (size_t)tq->k_levels - 1, (size_t)tq->k_levels},
                 {&tq->v_cb, v_levels_host, (size_t)tq->v_levels, (size_t)tq->v_levels},
@@ -536,10 +632,9 @@ IM_EXPORT int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, v
     if (nseq == 0 || T == 0) return IM_OK;
     dim3 grid(nkv, nseq * T);
     const int hd = tq->hd;
+    EncodeTables tb{tq->signs, is_k ? tq->k_cb : tq->v_cb, is_k ? tq->k_bd : tq->v_bd, tq->qjl_t, is_k ? tq->k_levels : tq->v_levels, is_k};
     tq_encode_kernel<<<grid, hd, 3 * hd * sizeof(float), as_stream(stream)>>>(
-        static_cast<const __half *>(kv_dev), tq->signs, is_k ? tq->k_cb : tq->v_cb, is_k ? tq->k_bd : tq->v_bd, tq->qjl, is_k,
-        is_k ? tq->k_levels : tq->v_levels, static_cast<uint8_t *>(cache_dev), scale_dev, r_norms_dev, nkv, hd, max_seq, base_pos,
-        pos_dev, T);
+        static_cast<const __half *>(kv_dev), tb, static_cast<uint8_t *>(cache_dev), scale_dev, r_norms_dev, nkv, hd, max_seq, base_pos, pos_dev, T);
     IM_CUDA_CHECK(cudaGetLastError());
     return IM_OK;
     IM_GUARD_END
@@ -566,6 +661,24 @@ IM_EXPORT int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes) {
 }
 
 namespace im {
+int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
+    if (tq->hd != kHd) return fail(IM_ERR_INVALID, "the fused cache-write kernel is built for head_dim 128 (got %d)", tq->hd);
+    if (a.nseq == 0 || a.T == 0) return IM_OK;
+    PrepArgs k{};
+    k.qkv = a.qkv; k.stride = a.stride; k.k_off = a.k_off; k.v_off = a.v_off;
+    k.qw = a.qw; k.kw = a.kw; k.cosc = a.cosc; k.sinc = a.sinc;
+    k.nh = a.nh; k.nkv = a.nkv; k.rotary_dim = a.rotary_dim ? a.rotary_dim : kHd; k.with_norm = a.with_norm;
+    k.T = a.T; k.max_seq = a.max_seq; k.base_pos = a.base_pos; k.eps = a.eps; k.pos_dev = a.pos_dev;
+    k.qrot = a.qrot; k.q_out = a.q_out;
+    k.ktab = EncodeTables{tq->signs, tq->k_cb, tq->k_bd, tq->qjl_t, tq->k_levels, 1};
+    k.vtab = EncodeTables{tq->signs, tq->v_cb, tq->v_bd, tq->qjl_t, tq->v_levels, 0};
+    k.kc = a.kc; k.vc = a.vc; k.ks = a.ks; k.vs = a.vs; k.krn = a.krn;
+    dim3 grid(a.nh + 2 * a.nkv, a.nseq * a.T);
+    tq_qkv_prep_kernel<<<grid, kHd, 0, st>>>(k);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+}
+
 int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
     const int ctas = nseq * T * nkv;
     int s = (2 * dev->sm_count + ctas - 1) / ctas;
@@ -577,10 +690,11 @@ int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
 
 int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,
                         const float *vs, const float *krn, float attn_scale, __half *out, int nseq, int nh, int nkv, int max_seq,
-                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st) {
+                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot) {
     AttnParams p{};
+    p.qrot = qrot;
     p.q = q; p.kc = kc; p.vc = vc; p.ks = ks; p.vs = vs; p.krn = krn;
-    p.signs = tq->signs; p.qjl = tq->qjl; p.k_cb = tq->k_cb; p.v_cb = tq->v_cb;
+    p.signs = tq->signs; p.qjl = tq->qjl_t; p.k_cb = tq->k_cb; p.v_cb = tq->v_cb;
     const size_t rows = (size_t)nseq * T * nh * splits;
     p.po = scratch;
     p.pm = scratch + rows * kHd;
@@ -626,5 +740,44 @@ IM_EXPORT int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_c
     return tq_attention_launch(tq, tq->scratch, static_cast<const __half *>(q_dev), static_cast<const uint8_t *>(k_cache_dev),
                                static_cast<const uint8_t *>(v_cache_dev), k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale,
                                static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream));
+    IM_GUARD_END
+}
+
+// Fused form of (fused_qk_norm_rope | rope) + turboquant_cache_write(K) + turboquant_cache_write(V) + the query
+// rotation of turboquant_attention, followed by the attention itself; one call for the engine and the tests.
+IM_EXPORT int im_cuda_tq_fused_attention(im_tq *tq, const void *qkv_dev, int qkv_stride, int k_offset, int v_offset,
+                                         const void *q_norm_w_dev, const void *k_norm_w_dev, const void *cos_dev, const void *sin_dev,
+                                         int rotary_dim, float eps, void *k_cache_dev, void *v_cache_dev, float *k_scale_dev,
+                                         float *v_scale_dev, float *k_rnorm_dev, float attn_scale, float *qrot_dev, void *out_dev,
+                                         int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
+                                         int num_splits, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(tq && qkv_dev && cos_dev && sin_dev && k_cache_dev && v_cache_dev && k_scale_dev && v_scale_dev && k_rnorm_dev &&
+                   qrot_dev && out_dev, "bad argument");
+    IM_REQUIRE(tq->hd == kHd, "built for head_dim 128 (got %d)", tq->hd);
+    IM_REQUIRE(nkv > 0 && nh % nkv == 0, "nh must be a multiple of nkv");
+    IM_REQUIRE((q_norm_w_dev == nullptr) == (k_norm_w_dev == nullptr), "give both norm weights or neither");
+    if (nseq == 0 || T == 0) return IM_OK;
+    if (!pos_dev && base_pos + T > max_seq)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", base_pos, T, max_seq);
+    const int splits = num_splits > 0 ? num_splits : tq_auto_splits(tq->dev, nseq, T, nkv, base_pos + T);
+    const size_t need = im_cuda_tq_scratch_bytes(nseq, T, nh, kHd, splits);
+    if (need > tq->scratch_bytes) {
+        int rc = im_cuda_tq_reserve_scratch(tq, need);
+        if (rc != IM_OK) return rc;
+    }
+    TqPrep a{};
+    a.qkv = static_cast<const __half *>(qkv_dev); a.stride = qkv_stride; a.k_off = k_offset; a.v_off = v_offset;
+    a.qw = static_cast<const __half *>(q_norm_w_dev); a.kw = static_cast<const __half *>(k_norm_w_dev);
+    a.cosc = static_cast<const __half *>(cos_dev); a.sinc = static_cast<const __half *>(sin_dev);
+    a.nh = nh; a.nkv = nkv; a.rotary_dim = rotary_dim; a.with_norm = q_norm_w_dev != nullptr; a.T = T; a.nseq = nseq;
+    a.max_seq = max_seq; a.base_pos = base_pos; a.eps = eps; a.pos_dev = pos_dev; a.qrot = qrot_dev;
+    a.kc = static_cast<uint8_t *>(k_cache_dev); a.vc = static_cast<uint8_t *>(v_cache_dev);
+    a.ks = k_scale_dev; a.vs = v_scale_dev; a.krn = k_rnorm_dev;
+    cudaStream_t st = as_stream(stream);
+    int rc = tq_prep_launch(tq, a, st);
+    if (rc != IM_OK) return rc;
+    return tq_attention_launch(tq, tq->scratch, nullptr, a.kc, a.vc, a.ks, a.vs, a.krn, attn_scale, static_cast<__half *>(out_dev), nseq,
+                               nh, nkv, max_seq, base_pos, pos_dev, T, splits, st, qrot_dev);
     IM_GUARD_END
 }

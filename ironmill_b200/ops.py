@@ -315,3 +315,30 @@ class TurboQuant:
             self.free()
         except Exception:
             pass
+
+
+def fused_residual_norm_ffn(gate: AffineWeight, up: AffineWeight, a, b, gamma, eps: float):
+    """residual + RMSNorm + gate/up + SiLU in one launch -> (out [B, I], residual, normed)."""
+    B = _rows(a, gate.K)
+    out = torch.empty((B, gate.N), dtype=torch.float16, device=a.device)
+    res, nrm = torch.empty_like(a), torch.empty_like(a)
+    check(lib().im_cuda_fused_residual_norm_ffn(gate.handle, up.handle, vp(a), vp(_h16(b)), vp(_h16(gamma)), C.c_float(eps), vp(out),
+                                                vp(res), vp(nrm), C.c_int(B), _stream()))
+    return out, res, nrm
+
+
+def tq_fused_attention(tq: "TurboQuant", qkv, nh, nkv, cos, sin, k_cache, v_cache, k_scale, v_scale, k_rnorm, attn_scale, max_seq,
+                       base_pos, eps=1e-6, qw=None, kw=None, nseq=1, pos_dev=None, num_splits=0, rotary_dim=0):
+    """(QK-norm +) RoPE + K/V cache write + attention from a fused QKV row [nseq*T, (nh + 2 nkv) * hd]."""
+    hd = tq.head_dim
+    stride = (nh + 2 * nkv) * hd
+    MT = _h16(qkv).numel() // stride
+    T = MT // nseq
+    out = torch.empty((MT, nh * hd), dtype=torch.float16, device=qkv.device)
+    qrot = torch.empty((MT, nh, 2, hd), dtype=torch.float32, device=qkv.device)
+    check(lib().im_cuda_tq_fused_attention(tq.handle, vp(qkv), C.c_int(stride), C.c_int(nh * hd), C.c_int((nh + nkv) * hd), vp(qw), vp(kw),
+                                           vp(cos), vp(sin), C.c_int(rotary_dim), C.c_float(eps), vp(k_cache), vp(v_cache), vp(k_scale),
+                                           vp(v_scale), vp(k_rnorm), C.c_float(attn_scale), vp(qrot), vp(out), C.c_int(nseq), C.c_int(nh),
+                                           C.c_int(nkv), C.c_int(max_seq), C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_int(num_splits),
+                                           _stream()))
+    return out

@@ -139,3 +139,20 @@ def test_invalid_arguments_are_reported(dev):
         ops.matvec_affine(w, x)
     with pytest.raises(CudaSysError):
         ops.AffineWeight(dev, qw.packed, qw.scales, qw.zps, 8, 128, 128, 3)
+
+
+@pytest.mark.parametrize("I,K", [(64, 128), (3072, 1024), (1000, 4096)])
+@pytest.mark.parametrize("B", [1, 3])
+def test_fused_residual_norm_ffn(dev, I, K, B):
+    """residual + RMSNorm + gate/up + SiLU in one launch against the two oracle steps."""
+    from ironmill_b200 import ops
+    g = H.QWeight(I, K, awq=True, seed=41, name="gate")
+    u = H.QWeight(I, K, seed=41, name="up", awq_vec=g.awq)
+    a, b = H.make_x(B, K, seed=6, name="a"), H.make_x(B, K, seed=6, name="b")
+    gamma = (1.0 + 0.1 * H.rng_for("gamma2").standard_normal(K)).astype(np.float16)
+    nrm, res = orc.fused_residual_rms_norm(a, b, gamma, 1e-5)
+    ref = orc.ffn_gate_up_act(g.packed, g.scales_f16, g.zps_f16, u.packed, u.scales_f16, u.zps_f16, nrm, I, K, 128, 4, awq=g.awq, threads=8)
+    out, gres, gnrm = ops.fused_residual_norm_ffn(g.gpu(dev), u.gpu(dev), _cuda(a), _cuda(b), _cuda(gamma), 1e-5)
+    assert (gres.cpu().numpy().view(np.uint16) == res.view(np.uint16)).all()
+    assert H.rel_err(gnrm.cpu().numpy(), nrm) <= 2e-3
+    assert H.rel_err(out.cpu().numpy(), ref) <= 5e-3
