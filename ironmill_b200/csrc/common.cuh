@@ -84,6 +84,7 @@ struct V2Params {
     int N;       // logical outputs per batch row
     int K, G, nblk;
     int nring;   // stages in the shared-memory ring
+    int split_tiles;  // 1: CTAs split the flattened tile list (stream-K); 0: whole row blocks per CTA
     float *partial;  // [grid][2][64]
     int *counters;   // [nblk], zero between launches
     int *err;

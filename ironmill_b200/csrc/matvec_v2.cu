@@ -93,6 +93,7 @@ template <int MODE, int NB>
 __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *xq, float2 *meta, int nthreads_warps) {
     const int K = p.K, lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
     float sq = 0.0f;
+#pragma unroll 2
     for (int g0 = warp * 2; g0 < p.G; g0 += nthreads_warps * 2) {
         const int grp = g0 + (lane >> 4);
         const bool live = grp < p.G;
@@ -199,7 +200,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long total = (long long)p.nblk * G;  // tiles
-    const long long t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
+    // Work split.  With enough row blocks each CTA takes whole row blocks: the kernel is HBM-bound, a CTA with
+    // one block more than its neighbour simply keeps streaming while the others have left the bus, and no fix-up
+    // is needed.  With few row blocks (short matrices) the split is by tiles, stream-K fashion (see flush()).
+    const long long t_begin = p.split_tiles ? total * blockIdx.x / gridDim.x : ((long long)p.nblk * blockIdx.x / gridDim.x) * G;
+    const long long t_end = p.split_tiles ? total * (blockIdx.x + 1) / gridDim.x : ((long long)p.nblk * (blockIdx.x + 1) / gridDim.x) * G;
 
 #define IM_STAMP(i) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[i] = global_ns(); } while (0)
     IM_STAMP(0);
@@ -439,6 +444,7 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     }
     const long long total = (long long)p.nblk * p.G;
     int grid = dev->sm_count;
+    p.split_tiles = p.nblk < grid ? 1 : 0;
     if (grid > total) grid = (int)total;
     kern<<<grid, kV2Threads, smem, st>>>(p);
     IM_CUDA_CHECK(cudaGetLastError());
