@@ -64,11 +64,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (unsigned i = 1;; i++) {
+        __nanosleep(32);  // back off: a tight poll from many threads competes with the bulk copies for shared memory
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) break;
     }
     atomicExch(err, 1);
     return false;
+}
+// One lane polls for the warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *err) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, err) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
@@ -193,10 +200,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     unsigned char *ring = smem;                                                        // nring * stage_bytes
     uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);   // G * 2NB * 32 words
     float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 2 * NB * 32);           // G * NB
-    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // warps * 64 + 64 + warps
-    uint64_t *full = reinterpret_cast<uint64_t *>(red + kV2Consumers * 64 + 64 + kV2Consumers);
+    const int nbuf = nring + 1;
+    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // nbuf * warps * 64 partial sums
+    uint64_t *full = reinterpret_cast<uint64_t *>(red + (size_t)nbuf * kV2Consumers * 64);
     uint64_t *empty = full + nring;
-    int *flag = reinterpret_cast<int *>(empty + nring);
+    int *cnts = reinterpret_cast<int *>(empty + nring);                                // nbuf arrival counters
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long total = (long long)p.nblk * G;  // tiles
@@ -213,7 +221,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], kV2Consumers);
         }
-        *flag = 0;
+        for (int i = 0; i < nbuf; i++) cnts[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -242,11 +250,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         sq_tot[b] = 0.0f;
         if (MODE & 2) {
             sq = warp_sum(sq);
-            if (lane == 0) red[kV2Consumers * 64 + 64 + warp] = sq;
+            if (lane == 0) red[warp] = sq;
             consumer_sync();
             float t = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kV2Consumers; w++) t += red[kV2Consumers * 64 + 64 + w];
+            for (int w = 0; w < kV2Consumers; w++) t += red[w];
             sq_tot[b] = t;
             consumer_sync();
         }
@@ -267,99 +275,130 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 
     const int g = lane >> 2, t = lane & 3;  // fragment coordinates: rows g and g+8, batch column pair t
     float acc0 = 0.0f, acc1 = 0.0f;          // rows g, g+8 for batch t
-    int cur_rb = t_begin < t_end ? (int)(t_begin / G) : -1;
     bool dead = false;
 
-    // Finish row block rb: reduce the warps, then either write the outputs (block fully inside this CTA's
-    // range) or publish a partial and let the last contributing CTA combine them in CTA order.
-    auto flush = [&](int rb) {
+    // Finish row block rb (the seq-th of this CTA) without a CTA-wide barrier: every warp drops its partial sums
+    // into one of nbuf shared buffers and bumps a shared counter; the warp that arrives last adds the sixteen
+    // partials in warp order (so the result does not depend on arrival order) and writes the outputs, or, for a
+    // row block cut by a CTA boundary, publishes the CTA's partial and lets the last CTA combine them in CTA order.
+    // A buffer is reused nbuf row blocks later; the ring keeps every warp within nring stages of the slowest one
+    // and a warp releases a stage only after its flush, so nbuf = nring + 1 buffers cannot collide.
+    auto flush = [&](int rb, int seq) {
+        float *buf = red + (size_t)(seq % nbuf) * (kV2Consumers * 64);
+        int *cnt = cnts + (seq % nbuf);
         if (t < NB) {
-            red[warp * 64 + g * 4 + t] = acc0;
-            red[warp * 64 + (g + 8) * 4 + t] = acc1;
+            buf[warp * 64 + g * 4 + t] = acc0;
+            buf[warp * 64 + (g + 8) * 4 + t] = acc1;
         }
         acc0 = acc1 = 0.0f;
-        consumer_sync();
-        const int row = tid >> 2, bb = tid & 3;  // threads 0..63: (row, batch)
-        float v = 0.0f;
-        if (tid < 64 && bb < NB) {
+        __threadfence_block();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(cnt, 1) == kV2Consumers - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence_block();
+        if (lane == 0) *cnt = 0;
+        // lane owns entries e = lane (rows 0..7) and lane + 32 (rows 8..15): row = e >> 2, batch = e & 3
+        const int bb = lane & 3, row = lane >> 2;
+        float v0 = 0.0f, v1 = 0.0f;
+        if (bb < NB) {
 #pragma unroll
-            for (int w = 0; w < kV2Consumers; w++) v += red[w * 64 + tid];
+            for (int w = 0; w < kV2Consumers; w++) {
+                v0 += buf[w * 64 + lane];
+                v1 += buf[w * 64 + lane + 32];
+            }
         }
         const long long b0 = (long long)rb * G, b1 = b0 + G;
-        const bool complete = b0 >= t_begin && b1 <= t_end;
-        bool finalize = complete;
-        if (!complete) {
+        bool finalize = b0 >= t_begin && b1 <= t_end;
+        if (!finalize) {
             const int slot = (rb == (int)(t_begin / G)) ? 0 : 1;
-            if (tid < 64) p.partial[((size_t)blockIdx.x * 2 + slot) * 64 + tid] = v;
+            float *mine = p.partial + ((size_t)blockIdx.x * 2 + slot) * 64;
+            mine[lane] = v0;
+            mine[lane + 32] = v1;
             __threadfence();
-            consumer_sync();
+            __syncwarp();
             const int c_first = (int)(((b0 + 1) * gridDim.x + total - 1) / total) - 1;
             const int c_last = (int)((b1 * gridDim.x + total - 1) / total) - 1;
-            if (tid == 0) {
-                const int old = atomicAdd(&p.counters[rb], 1);
-                *flag = (old == c_last - c_first) ? 1 : 0;
-            }
-            consumer_sync();
-            finalize = *flag != 0;
+            int fin = 0;
+            if (lane == 0) fin = atomicAdd(&p.counters[rb], 1) == c_last - c_first;
+            finalize = __shfl_sync(0xffffffffu, fin, 0) != 0;
             if (finalize) {
                 __threadfence();
-                v = 0.0f;
-                if (tid < 64) {
-                    for (int c = c_first; c <= c_last; c++) {
-                        const long long cb = total * c / gridDim.x;
-                        const int cslot = (rb == (int)(cb / G)) ? 0 : 1;
-                        v += __ldcg(&p.partial[((size_t)c * 2 + cslot) * 64 + tid]);
-                    }
+                v0 = v1 = 0.0f;
+                for (int c = c_first; c <= c_last; c++) {
+                    const long long cb = total * c / gridDim.x;
+                    const float *theirs = p.partial + ((size_t)c * 2 + ((rb == (int)(cb / G)) ? 0 : 1)) * 64;
+                    v0 += __ldcg(theirs + lane);
+                    v1 += __ldcg(theirs + lane + 32);
                 }
-                if (tid == 0) p.counters[rb] = 0;  // ready for the next launch
+                if (lane == 0) p.counters[rb] = 0;  // ready for the next launch
             }
         }
-        if (finalize) {
+        if (finalize && bb < NB) {
             float ri = rms_inv[0];
 #pragma unroll
             for (int b = 1; b < NB; b++) ri = bb == b ? rms_inv[b] : ri;
-            if (MODE & 1) {
-                if (tid < 64) red[kV2Consumers * 64 + tid] = v * ri;
-                consumer_sync();
-                if (tid < 32 && bb < NB) {  // rows 0..7: gate, partner row + 8: up
-                    const float gv = v * ri, uv = red[kV2Consumers * 64 + tid + 32];
-                    const int n = rb * 8 + row;
-                    if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
-                }
-            } else if (tid < 64 && bb < NB) {
+            if (MODE & 1) {  // rows 0..7 gate, rows 8..15 up of the same eight outputs
+                const float gv = v0 * ri, uv = v1 * ri;
+                const int n = rb * 8 + row;
+                if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
+            } else {
                 const int n = rb * 16 + row;
-                if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn(v * ri);
+                if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn(v0 * ri);
+                if (n + 8 < p.N) p.y[(size_t)bb * p.N + n + 8] = __float2half_rn(v1 * ri);
             }
         }
-        consumer_sync();  // red / flag are reused by the next flush
     };
 
-    // One tile: 16 rows x 128 columns against the staged activations.
-    auto tile_dot = [&](const unsigned char *tile, int grp) {
-        const uint4 w0 = *reinterpret_cast<const uint4 *>(tile + lane * 16);        // row g
-        const uint4 w1 = *reinterpret_cast<const uint4 *>(tile + 512 + lane * 16);  // row g+8
-        uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = xb0;
-        if (g < 2 * NB) {
-            const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp * 2 * NB + g) * 4 + t) * 8);
-            xb0 = xp[0];  // (even, odd) words of j = 0, 1
-            xb1 = xp[1];  // j = 2, 3
+    // Two tiles (16 rows x 128 columns each) against the staged activations, interleaved so that the shared
+    // loads, the unpacking and the tensor-core latencies of one overlap the other.
+    auto tile_pair = [&](const unsigned char *tile_a, int grp_a, const unsigned char *tile_b, int grp_b, bool have_b) {
+        const uint4 a0 = *reinterpret_cast<const uint4 *>(tile_a + lane * 16);        // row g
+        const uint4 a1 = *reinterpret_cast<const uint4 *>(tile_a + 512 + lane * 16);  // row g+8
+        uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
+        if (have_b) {
+            b0 = *reinterpret_cast<const uint4 *>(tile_b + lane * 16);
+            b1 = *reinterpret_cast<const uint4 *>(tile_b + 512 + lane * 16);
         }
-        // four independent accumulator sets: the mma latencies overlap instead of chaining
-        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0}, c3[4] = {0, 0, 0, 0};
+        uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
+        if (g < 2 * NB) {
+            const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_a * 2 * NB + g) * 4 + t) * 8);
+            xa0 = xp[0];  // (even, odd) words of j = 0, 1
+            xa1 = xp[1];  // j = 2, 3
+            if (have_b) {
+                const uint4 *xr = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_b * 2 * NB + g) * 4 + t) * 8);
+                xb0 = xr[0];
+                xb1 = xr[1];
+            }
+        }
+        int ca0[4] = {0, 0, 0, 0}, ca1[4] = {0, 0, 0, 0}, cb0[4] = {0, 0, 0, 0}, cb1[4] = {0, 0, 0, 0};
         constexpr unsigned M = 0x0F0F0F0Fu;
-        mma_u8s8(c0, w0.x & M, w1.x & M, (w0.x >> 4) & M, (w1.x >> 4) & M, xb0.x, xb0.y);
-        mma_u8s8(c1, w0.y & M, w1.y & M, (w0.y >> 4) & M, (w1.y >> 4) & M, xb0.z, xb0.w);
-        mma_u8s8(c2, w0.z & M, w1.z & M, (w0.z >> 4) & M, (w1.z >> 4) & M, xb1.x, xb1.y);
-        mma_u8s8(c3, w0.w & M, w1.w & M, (w0.w >> 4) & M, (w1.w >> 4) & M, xb1.z, xb1.w);
+        mma_u8s8(ca0, a0.x & M, a1.x & M, (a0.x >> 4) & M, (a1.x >> 4) & M, xa0.x, xa0.y);
+        mma_u8s8(cb0, b0.x & M, b1.x & M, (b0.x >> 4) & M, (b1.x >> 4) & M, xb0.x, xb0.y);
+        mma_u8s8(ca1, a0.y & M, a1.y & M, (a0.y >> 4) & M, (a1.y >> 4) & M, xa0.z, xa0.w);
+        mma_u8s8(cb1, b0.y & M, b1.y & M, (b0.y >> 4) & M, (b1.y >> 4) & M, xb0.z, xb0.w);
+        mma_u8s8(ca0, a0.z & M, a1.z & M, (a0.z >> 4) & M, (a1.z >> 4) & M, xa1.x, xa1.y);
+        mma_u8s8(cb0, b0.z & M, b1.z & M, (b0.z >> 4) & M, (b1.z >> 4) & M, xb1.x, xb1.y);
+        mma_u8s8(ca1, a0.w & M, a1.w & M, (a0.w >> 4) & M, (a1.w >> 4) & M, xa1.z, xa1.w);
+        mma_u8s8(cb1, b0.w & M, b1.w & M, (b0.w >> 4) & M, (b1.w >> 4) & M, xb1.z, xb1.w);
         if (t < NB) {
-            const float2 m = meta[grp * NB + t];
-            const __half2 *szp = reinterpret_cast<const __half2 *>(tile + kTileCodeBytes);
-            const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-            const int hi0 = c0[0] + c1[0] + c2[0] + c3[0], lo0 = c0[1] + c1[1] + c2[1] + c3[1];
-            const int hi1 = c0[2] + c1[2] + c2[2] + c3[2], lo1 = c0[3] + c1[3] + c2[3] + c3[3];
-            const float f0 = (float)(hi0 * 256 + lo0), f1 = (float)(hi1 * 256 + lo1);
-            acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-            acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+            {
+                const float2 m = meta[grp_a * NB + t];
+                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
+                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                const float f0 = (float)((ca0[0] + ca1[0]) * 256 + ca0[1] + ca1[1]), f1 = (float)((ca0[2] + ca1[2]) * 256 + ca0[3] + ca1[3]);
+                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+            }
+            if (have_b) {
+                const float2 m = meta[grp_b * NB + t];
+                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
+                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                const float f0 = (float)((cb0[0] + cb1[0]) * 256 + cb0[1] + cb1[1]), f1 = (float)((cb0[2] + cb1[2]) * 256 + cb0[3] + cb1[3]);
+                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+            }
         }
     };
 
@@ -367,29 +406,24 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     // the other warps and the producer still run to the end; the host sees the error word.
     StageIter it{t_begin, t_end, G};
     long long t0;
-    int n;
+    int n, seq = 0;
     for (int i = 0; it.next(t0, n); i++) {
         const int slot = i % nring;
         const int rb = (int)(t0 / G), grp0 = (int)(t0 % G);
-        if (rb != cur_rb) {
-            flush(cur_rb);
-            cur_rb = rb;
-        }
-        if (!dead && !mbar_wait(&full[slot], (i / nring) & 1, p.err)) dead = true;
+        if (!dead && !mbar_wait_warp(&full[slot], (i / nring) & 1, p.err)) dead = true;
         if (i == 0) IM_STAMP(2);
         if (i == 1) IM_STAMP(3);
+        if (i < 24) IM_STAMP(8 + i);
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
-        if (!dead) {
-            const int ta = warp, tb = warp + kV2Consumers;
-            if (ta < n) tile_dot(st + (size_t)ta * kTileBytes, grp0 + ta);
-            if (tb < n) tile_dot(st + (size_t)tb * kTileBytes, grp0 + tb);
+        if (!dead && warp < n) {
+            const int tb = warp + kV2Consumers;
+            tile_pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n);
         }
+        if (grp0 + n == G || t0 + n == t_end) flush(rb, seq++);  // last stage of this row block inside the CTA's range
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
     }
     IM_STAMP(4);
-    if (cur_rb >= 0) flush(cur_rb);
-    IM_STAMP(5);
 }
 
 // ---- load-time repack -------------------------------------------------------
@@ -429,13 +463,15 @@ int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, 
 template <int MODE, int NB>
 static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     const size_t stage_bytes = (size_t)kStageTiles * kTileBytes;
-    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + (kV2Consumers * 64 + 64 + kV2Consumers) * 4 + 64;
+    const size_t red_buf = (size_t)kV2Consumers * 64 * 4 + 4;  // one partial-sum buffer + its counter
+    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + red_buf + 64;
+    const size_t per_slot = stage_bytes + 16 + red_buf;
     const size_t budget = dev->smem_optin > 8192 ? dev->smem_optin - 2048 : 0;
-    if (fixed + 3 * stage_bytes + 64 > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel
-    int nring = (int)((budget - fixed - 64) / (stage_bytes + 16));
+    if (fixed + 3 * per_slot > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel
+    int nring = (int)((budget - fixed) / per_slot);
     if (nring > 8) nring = 8;
     p.nring = nring;
-    const size_t smem = (size_t)nring * stage_bytes + fixed + (size_t)nring * 16;
+    const size_t smem = fixed + (size_t)nring * per_slot;
     auto kern = matvec_v2_kernel<MODE, NB>;
     static thread_local bool configured = false;
     if (!configured) {
