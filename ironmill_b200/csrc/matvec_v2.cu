@@ -176,18 +176,21 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
 // Stage schedule (the producer lane and every consumer warp walk the same list): the CTA owns the
 // flattened tile range [t_begin, t_end); a stage is the next run of at most kStageTiles tiles that
 // stays inside one row block.
-struct StageIter {
-    long long t, t_end;
-    int G;
-    __device__ bool next(long long &t0, int &n) {
+struct StageIter {  // 32-bit and division-free in the loop: a 64-bit divide costs more than a tile
+    int t, t_end, G, rb, grp;
+    __device__ StageIter(int t_begin, int t_end_, int G_) : t(t_begin), t_end(t_end_), G(G_), rb(t_begin / G_), grp(t_begin % G_) {}
+    __device__ bool next(int &t0, int &n, int &rb0, int &grp0) {
         if (t >= t_end) return false;
-        const long long rb_end = (t / G + 1) * G;
-        long long e = t + kStageTiles;
-        if (e > rb_end) e = rb_end;
-        if (e > t_end) e = t_end;
+        n = min(min(kStageTiles, G - grp), t_end - t);
         t0 = t;
-        n = (int)(e - t);
-        t = e;
+        rb0 = rb;
+        grp0 = grp;
+        t += n;
+        grp += n;
+        if (grp == G) {
+            grp = 0;
+            rb++;
+        }
         return true;
     }
 };
@@ -207,12 +210,12 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     int *cnts = reinterpret_cast<int *>(empty + nring);                                // nbuf arrival counters
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const long long total = (long long)p.nblk * G;  // tiles
+    const int total = p.nblk * G;  // tiles (fits 32 bits: checked on the host)
     // Work split.  With enough row blocks each CTA takes whole row blocks: the kernel is HBM-bound, a CTA with
     // one block more than its neighbour simply keeps streaming while the others have left the bus, and no fix-up
     // is needed.  With few row blocks (short matrices) the split is by tiles, stream-K fashion (see flush()).
-    const long long t_begin = p.split_tiles ? total * blockIdx.x / gridDim.x : ((long long)p.nblk * blockIdx.x / gridDim.x) * G;
-    const long long t_end = p.split_tiles ? total * (blockIdx.x + 1) / gridDim.x : ((long long)p.nblk * (blockIdx.x + 1) / gridDim.x) * G;
+    const int t_begin = p.split_tiles ? (int)((long long)total * blockIdx.x / gridDim.x) : (int)((long long)p.nblk * blockIdx.x / gridDim.x) * G;
+    const int t_end = p.split_tiles ? (int)((long long)total * (blockIdx.x + 1) / gridDim.x) : (int)((long long)p.nblk * (blockIdx.x + 1) / gridDim.x) * G;
 
 #define IM_STAMP(i) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[i] = global_ns(); } while (0)
     IM_STAMP(0);
@@ -229,12 +232,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     if (warp == kV2Consumers) {
         // ------------------------------------------------ producer: one lane streams the stages
         if (lane == 0) {
-            StageIter it{t_begin, t_end, G};
-            long long t0;
-            int n;
-            for (int i = 0; it.next(t0, n); i++) {
+            StageIter it(t_begin, t_end, G);
+            int t0, n, rb0, grp0;
+            for (int i = 0; it.next(t0, n, rb0, grp0); i++) {
                 const int slot = i % nring;
-                if (!mbar_wait(&empty[slot], ((i / nring) & 1) ^ 1, p.err)) break;
+                if (!mbar_wait(&empty[slot], ((i / nring) & 1) ^ 1, p.err)) break;  // one lane, once per 34 KB: the divide is harmless here
                 mbar_expect_tx(&full[slot], (uint32_t)(n * kTileBytes));
                 bulk_g2s(ring + (size_t)slot * stage_bytes, p.tiles + (size_t)t0 * kTileBytes, (uint32_t)(n * kTileBytes), &full[slot]);
             }
@@ -283,9 +285,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     // row block cut by a CTA boundary, publishes the CTA's partial and lets the last CTA combine them in CTA order.
     // A buffer is reused nbuf row blocks later; the ring keeps every warp within nring stages of the slowest one
     // and a warp releases a stage only after its flush, so nbuf = nring + 1 buffers cannot collide.
-    auto flush = [&](int rb, int seq) {
-        float *buf = red + (size_t)(seq % nbuf) * (kV2Consumers * 64);
-        int *cnt = cnts + (seq % nbuf);
+    auto flush = [&](int rb, int bi) {
+        float *buf = red + bi * (kV2Consumers * 64);
+        int *cnt = cnts + bi;
         if (t < NB) {
             buf[warp * 64 + g * 4 + t] = acc0;
             buf[warp * 64 + (g + 8) * 4 + t] = acc1;
@@ -309,17 +311,17 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
                 v1 += buf[w * 64 + lane + 32];
             }
         }
-        const long long b0 = (long long)rb * G, b1 = b0 + G;
+        const int b0 = rb * G, b1 = b0 + G;
         bool finalize = b0 >= t_begin && b1 <= t_end;
         if (!finalize) {
-            const int slot = (rb == (int)(t_begin / G)) ? 0 : 1;
-            float *mine = p.partial + ((size_t)blockIdx.x * 2 + slot) * 64;
+            const int pslot = (rb == t_begin / G) ? 0 : 1;
+            float *mine = p.partial + ((size_t)blockIdx.x * 2 + pslot) * 64;
             mine[lane] = v0;
             mine[lane + 32] = v1;
             __threadfence();
             __syncwarp();
-            const int c_first = (int)(((b0 + 1) * gridDim.x + total - 1) / total) - 1;
-            const int c_last = (int)((b1 * gridDim.x + total - 1) / total) - 1;
+            const int c_first = (int)((((long long)b0 + 1) * gridDim.x + total - 1) / total) - 1;
+            const int c_last = (int)(((long long)b1 * gridDim.x + total - 1) / total) - 1;
             int fin = 0;
             if (lane == 0) fin = atomicAdd(&p.counters[rb], 1) == c_last - c_first;
             finalize = __shfl_sync(0xffffffffu, fin, 0) != 0;
@@ -327,8 +329,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
                 __threadfence();
                 v0 = v1 = 0.0f;
                 for (int c = c_first; c <= c_last; c++) {
-                    const long long cb = total * c / gridDim.x;
-                    const float *theirs = p.partial + ((size_t)c * 2 + ((rb == (int)(cb / G)) ? 0 : 1)) * 64;
+                    const int cb = (int)((long long)total * c / gridDim.x);
+                    const float *theirs = p.partial + ((size_t)c * 2 + ((rb == cb / G) ? 0 : 1)) * 64;
                     v0 += __ldcg(theirs + lane);
                     v1 += __ldcg(theirs + lane + 32);
                 }
@@ -404,25 +406,32 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 
     // A warp whose wait ran out stops computing but keeps every barrier of the schedule, so that
     // the other warps and the producer still run to the end; the host sees the error word.
-    StageIter it{t_begin, t_end, G};
-    long long t0;
-    int n, seq = 0;
-    for (int i = 0; it.next(t0, n); i++) {
-        const int slot = i % nring;
-        const int rb = (int)(t0 / G), grp0 = (int)(t0 % G);
-        if (!dead && !mbar_wait_warp(&full[slot], (i / nring) & 1, p.err)) dead = true;
+    StageIter it(t_begin, t_end, G);
+    int t0, n, rb, grp0, seq = 0, slot = 0, phase = 0, bufi = 0;
+    for (int i = 0; it.next(t0, n, rb, grp0); i++) {
+        if (i < 12) IM_STAMP(8 + 2 * i);
+        if (!dead && !mbar_wait_warp(&full[slot], phase, p.err)) dead = true;
         if (i == 0) IM_STAMP(2);
         if (i == 1) IM_STAMP(3);
-        if (i < 24) IM_STAMP(8 + i);
+        if (i < 12) IM_STAMP(9 + 2 * i);
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
         if (!dead && warp < n) {
             const int tb = warp + kV2Consumers;
             tile_pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n);
         }
-        if (grp0 + n == G || t0 + n == t_end) flush(rb, seq++);  // last stage of this row block inside the CTA's range
+        if (grp0 + n == G || t0 + n == t_end) {  // last stage of this row block inside the CTA's range
+            flush(rb, bufi);
+            if (++bufi == nbuf) bufi = 0;
+            seq++;
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
+        if (++slot == nring) {
+            slot = 0;
+            phase ^= 1;
+        }
     }
+    (void)seq;
     IM_STAMP(4);
 }
 
@@ -479,6 +488,7 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
         configured = true;
     }
     const long long total = (long long)p.nblk * p.G;
+    if (total > 0x7fffffffLL) return IM_ERR_BOUNDS;
     int grid = dev->sm_count;
     p.split_tiles = p.nblk < grid ? 1 : 0;
     if (grid > total) grid = (int)total;
