@@ -203,11 +203,10 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     unsigned char *ring = smem;                                                        // nring * stage_bytes
     uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);   // G * 2NB * 32 words
     float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 2 * NB * 32);           // G * NB
-    const int nbuf = nring + 1;
-    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // nbuf * warps * 64 partial sums
-    uint64_t *full = reinterpret_cast<uint64_t *>(red + (size_t)nbuf * kV2Consumers * 64);
+    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // nring * warps * 64 partial sums
+    float *misc = red + (size_t)nring * kV2Consumers * 64;                             // 16 floats: rms_inv per batch row, reduction scratch
+    uint64_t *full = reinterpret_cast<uint64_t *>(misc + 32);
     uint64_t *empty = full + nring;
-    int *cnts = reinterpret_cast<int *>(empty + nring);                                // nbuf arrival counters
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int total = p.nblk * G;  // tiles (fits 32 bits: checked on the host)
@@ -224,21 +223,98 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], kV2Consumers);
         }
-        for (int i = 0; i < nbuf; i++) cnts[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     if (warp == kV2Consumers) {
-        // ------------------------------------------------ producer: one lane streams the stages
-        if (lane == 0) {
-            StageIter it(t_begin, t_end, G);
-            int t0, n, rb0, grp0;
-            for (int i = 0; it.next(t0, n, rb0, grp0); i++) {
-                const int slot = i % nring;
-                if (!mbar_wait(&empty[slot], ((i / nring) & 1) ^ 1, p.err)) break;  // one lane, once per 34 KB: the divide is harmless here
+        // ------------------------------------------------ producer warp
+        // Lane 0 streams the stages.  Before a ring slot is refilled the warp waits for the sixteen consumer warps
+        // to release it; if the stage that lived there ended a row block, the consumers left their partial sums in
+        // the slot's buffer and this otherwise idle warp adds them in warp order (so the result does not depend on
+        // timing) and writes the outputs.  Consumers thus never wait for each other.
+        // A row block cut by a CTA boundary (tile-granular split) is published as a partial instead; the last CTA
+        // to arrive at its counter combines the partials in CTA order.
+        const int bb = lane & 3, row = lane >> 2;  // lane owns entries e = lane (rows 0..7) and lane + 32 (rows 8..15)
+        auto drain = [&](int slot, int rb) {
+            const float *buf = red + slot * (kV2Consumers * 64);
+            float v0 = 0.0f, v1 = 0.0f;
+            if (bb < NB) {
+#pragma unroll
+                for (int w = 0; w < kV2Consumers; w++) {
+                    v0 += buf[w * 64 + lane];
+                    v1 += buf[w * 64 + lane + 32];
+                }
+            }
+            const int b0 = rb * G, b1 = b0 + G;
+            bool finalize = b0 >= t_begin && b1 <= t_end;
+            if (!finalize) {
+                const int pslot = (rb == t_begin / G) ? 0 : 1;
+                float *mine = p.partial + ((size_t)blockIdx.x * 2 + pslot) * 64;
+                mine[lane] = v0;
+                mine[lane + 32] = v1;
+                __threadfence();
+                __syncwarp();
+                const int c_first = (int)((((long long)b0 + 1) * gridDim.x + total - 1) / total) - 1;
+                const int c_last = (int)(((long long)b1 * gridDim.x + total - 1) / total) - 1;
+                int fin = 0;
+                if (lane == 0) fin = atomicAdd(&p.counters[rb], 1) == c_last - c_first;
+                finalize = __shfl_sync(0xffffffffu, fin, 0) != 0;
+                if (finalize) {
+                    __threadfence();
+                    v0 = v1 = 0.0f;
+                    for (int c = c_first; c <= c_last; c++) {
+                        const int cb = (int)((long long)total * c / gridDim.x);
+                        const float *theirs = p.partial + ((size_t)c * 2 + ((rb == cb / G) ? 0 : 1)) * 64;
+                        v0 += __ldcg(theirs + lane);
+                        v1 += __ldcg(theirs + lane + 32);
+                    }
+                    if (lane == 0) p.counters[rb] = 0;  // ready for the next launch
+                }
+            }
+            if (finalize && bb < NB) {
+                const float ri = (MODE & 2) ? misc[bb] : 1.0f;  // rms_inv, left by the consumers before their first release
+                if (MODE & 1) {  // rows 0..7 gate, rows 8..15 up of the same eight outputs
+                    const float gv = v0 * ri, uv = v1 * ri;
+                    const int n = rb * 8 + row;
+                    if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
+                } else {
+                    const int n = rb * 16 + row;
+                    if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn(v0 * ri);
+                    if (n + 8 < p.N) p.y[(size_t)bb * p.N + n + 8] = __float2half_rn(v1 * ri);
+                }
+            }
+        };
+        StageIter issue(t_begin, t_end, G), done(t_begin, t_end, G);
+        int t0, n, rb0, grp0, dt0, dn, drb, dgrp;
+        int slot = 0, phase = 0;  // slot of the stage being issued; phase = parity of the ring pass that last used it
+        bool ok = true;
+        int nstages = 0;
+        for (; issue.next(t0, n, rb0, grp0); nstages++) {
+            if (nstages >= nring) {  // reclaim: stage (nstages - nring) lived in this slot
+                if (ok && !mbar_wait_warp(&empty[slot], phase ^ 1, p.err)) ok = false;
+                done.next(dt0, dn, drb, dgrp);
+                if (ok && (dgrp + dn == G || dt0 + dn == t_end)) drain(slot, drb);
+            }
+            if (lane == 0 && ok) {
                 mbar_expect_tx(&full[slot], (uint32_t)(n * kTileBytes));
                 bulk_g2s(ring + (size_t)slot * stage_bytes, p.tiles + (size_t)t0 * kTileBytes, (uint32_t)(n * kTileBytes), &full[slot]);
+            }
+            if (++slot == nring) {
+                slot = 0;
+                phase ^= 1;
+            }
+        }
+        // the last min(nring, nstages) stages are still in the ring
+        int left = nstages < nring ? nstages : nring;
+        int dslot = nstages < nring ? 0 : slot, dphase = nstages < nring ? 0 : (phase ^ 1);
+        for (; left > 0; left--) {
+            if (ok && !mbar_wait_warp(&empty[dslot], dphase, p.err)) ok = false;
+            done.next(dt0, dn, drb, dgrp);
+            if (ok && (dgrp + dn == G || dt0 + dn == t_end)) drain(dslot, drb);
+            if (++dslot == nring) {
+                dslot = 0;
+                dphase ^= 1;
             }
         }
         return;
@@ -252,11 +328,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         sq_tot[b] = 0.0f;
         if (MODE & 2) {
             sq = warp_sum(sq);
-            if (lane == 0) red[warp] = sq;
+            if (lane == 0) misc[8 + warp] = sq;
             consumer_sync();
             float t = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kV2Consumers; w++) t += red[w];
+            for (int w = 0; w < kV2Consumers; w++) t += misc[8 + w];
             sq_tot[b] = t;
             consumer_sync();
         }
@@ -266,6 +342,10 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     float rms_inv[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) rms_inv[b] = (MODE & 2) ? rsqrtf(sq_tot[b] / (float)p.K + p.eps) : 1.0f;
+    if ((MODE & 2) && tid == 0) {
+#pragma unroll
+        for (int b = 0; b < NB; b++) misc[b] = rms_inv[b];  // visible to the producer warp through the slot-release barrier
+    }
     if ((MODE & 2) && blockIdx.x == 0) {  // side outputs (must not alias a or b)
         for (int b = 0; b < NB; b++)
             for (int k = tid; k < p.K; k += kV2Consumers * 32) {
@@ -278,80 +358,6 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     const int g = lane >> 2, t = lane & 3;  // fragment coordinates: rows g and g+8, batch column pair t
     float acc0 = 0.0f, acc1 = 0.0f;          // rows g, g+8 for batch t
     bool dead = false;
-
-    // Finish row block rb (the seq-th of this CTA) without a CTA-wide barrier: every warp drops its partial sums
-    // into one of nbuf shared buffers and bumps a shared counter; the warp that arrives last adds the sixteen
-    // partials in warp order (so the result does not depend on arrival order) and writes the outputs, or, for a
-    // row block cut by a CTA boundary, publishes the CTA's partial and lets the last CTA combine them in CTA order.
-    // A buffer is reused nbuf row blocks later; the ring keeps every warp within nring stages of the slowest one
-    // and a warp releases a stage only after its flush, so nbuf = nring + 1 buffers cannot collide.
-    auto flush = [&](int rb, int bi) {
-        float *buf = red + bi * (kV2Consumers * 64);
-        int *cnt = cnts + bi;
-        if (t < NB) {
-            buf[warp * 64 + g * 4 + t] = acc0;
-            buf[warp * 64 + (g + 8) * 4 + t] = acc1;
-        }
-        acc0 = acc1 = 0.0f;
-        __threadfence_block();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) last = atomicAdd(cnt, 1) == kV2Consumers - 1;
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) return;
-        __threadfence_block();
-        if (lane == 0) *cnt = 0;
-        // lane owns entries e = lane (rows 0..7) and lane + 32 (rows 8..15): row = e >> 2, batch = e & 3
-        const int bb = lane & 3, row = lane >> 2;
-        float v0 = 0.0f, v1 = 0.0f;
-        if (bb < NB) {
-#pragma unroll
-            for (int w = 0; w < kV2Consumers; w++) {
-                v0 += buf[w * 64 + lane];
-                v1 += buf[w * 64 + lane + 32];
-            }
-        }
-        const int b0 = rb * G, b1 = b0 + G;
-        bool finalize = b0 >= t_begin && b1 <= t_end;
-        if (!finalize) {
-            const int pslot = (rb == t_begin / G) ? 0 : 1;
-            float *mine = p.partial + ((size_t)blockIdx.x * 2 + pslot) * 64;
-            mine[lane] = v0;
-            mine[lane + 32] = v1;
-            __threadfence();
-            __syncwarp();
-            const int c_first = (int)((((long long)b0 + 1) * gridDim.x + total - 1) / total) - 1;
-            const int c_last = (int)(((long long)b1 * gridDim.x + total - 1) / total) - 1;
-            int fin = 0;
-            if (lane == 0) fin = atomicAdd(&p.counters[rb], 1) == c_last - c_first;
-            finalize = __shfl_sync(0xffffffffu, fin, 0) != 0;
-            if (finalize) {
-                __threadfence();
-                v0 = v1 = 0.0f;
-                for (int c = c_first; c <= c_last; c++) {
-                    const int cb = (int)((long long)total * c / gridDim.x);
-                    const float *theirs = p.partial + ((size_t)c * 2 + ((rb == cb / G) ? 0 : 1)) * 64;
-                    v0 += __ldcg(theirs + lane);
-                    v1 += __ldcg(theirs + lane + 32);
-                }
-                if (lane == 0) p.counters[rb] = 0;  // ready for the next launch
-            }
-        }
-        if (finalize && bb < NB) {
-            float ri = rms_inv[0];
-#pragma unroll
-            for (int b = 1; b < NB; b++) ri = bb == b ? rms_inv[b] : ri;
-            if (MODE & 1) {  // rows 0..7 gate, rows 8..15 up of the same eight outputs
-                const float gv = v0 * ri, uv = v1 * ri;
-                const int n = rb * 8 + row;
-                if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
-            } else {
-                const int n = rb * 16 + row;
-                if (n < p.N) p.y[(size_t)bb * p.N + n] = __float2half_rn(v0 * ri);
-                if (n + 8 < p.N) p.y[(size_t)bb * p.N + n + 8] = __float2half_rn(v1 * ri);
-            }
-        }
-    };
 
     // Two tiles (16 rows x 128 columns each) against the staged activations, interleaved so that the shared
     // loads, the unpacking and the tensor-core latencies of one overlap the other.
@@ -407,7 +413,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     // A warp whose wait ran out stops computing but keeps every barrier of the schedule, so that
     // the other warps and the producer still run to the end; the host sees the error word.
     StageIter it(t_begin, t_end, G);
-    int t0, n, rb, grp0, seq = 0, slot = 0, phase = 0, bufi = 0;
+    int t0, n, rb, grp0, slot = 0, phase = 0;
     for (int i = 0; it.next(t0, n, rb, grp0); i++) {
         if (i < 12) IM_STAMP(8 + 2 * i);
         if (!dead && !mbar_wait_warp(&full[slot], phase, p.err)) dead = true;
@@ -419,10 +425,13 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             const int tb = warp + kV2Consumers;
             tile_pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n);
         }
-        if (grp0 + n == G || t0 + n == t_end) {  // last stage of this row block inside the CTA's range
-            flush(rb, bufi);
-            if (++bufi == nbuf) bufi = 0;
-            seq++;
+        if (grp0 + n == G || t0 + n == t_end) {  // last stage of this row block inside the CTA's range:
+            float *buf = red + slot * (kV2Consumers * 64);  // hand the partial sums to the producer warp
+            if (t < NB) {
+                buf[warp * 64 + g * 4 + t] = acc0;
+                buf[warp * 64 + (g + 8) * 4 + t] = acc1;
+            }
+            acc0 = acc1 = 0.0f;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
@@ -431,7 +440,6 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             phase ^= 1;
         }
     }
-    (void)seq;
     IM_STAMP(4);
 }
 
@@ -472,8 +480,8 @@ int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, 
 template <int MODE, int NB>
 static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     const size_t stage_bytes = (size_t)kStageTiles * kTileBytes;
-    const size_t red_buf = (size_t)kV2Consumers * 64 * 4 + 4;  // one partial-sum buffer + its counter
-    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + red_buf + 64;
+    const size_t red_buf = (size_t)kV2Consumers * 64 * 4;  // one partial-sum buffer per ring slot
+    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + 32 * 4 + 64;
     const size_t per_slot = stage_bytes + 16 + red_buf;
     const size_t budget = dev->smem_optin > 8192 ? dev->smem_optin - 2048 : 0;
     if (fixed + 3 * per_slot > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel
