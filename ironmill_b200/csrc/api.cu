@@ -1,6 +1,7 @@
 // Device / buffer handles and error plumbing of the C ABI
 // (the part of the boundary that mirrors ironmill-metal-sys device.rs / buffer.rs).
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include <new>
 
@@ -21,6 +22,14 @@ int fail(int code, const char *fmt, ...) {
     va_end(ap);
     last_error() = buf;
     return code;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("IM_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 int dev_malloc(Device *dev, void **ptr, size_t bytes) {

@@ -95,6 +95,35 @@ int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t 
 int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, const __half2 *sz1, int N, int K, int G, int nblk,
               int rows_per_blk, uint8_t *tiles, cudaStream_t st);
 
+// ---- programmatic dependent launch ------------------------------------------
+// Decode is a chain of ~230 short kernels per token.  Launched with the programmatic-serialization
+// attribute, a kernel may start while its predecessor is still draining: everything it does before
+// pdl_wait() (barrier set-up, streaming constant weights into shared memory) overlaps the predecessor's
+// tail; pdl_wait() returns once the predecessor has completed and its writes are visible.  Every kernel
+// launched through launch_k() must therefore call pdl_wait() before it reads anything a predecessor wrote
+// and before its first global write.  IM_PDL=0 in the environment turns the attribute off.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // ---- device helpers -------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

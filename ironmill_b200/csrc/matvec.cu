@@ -389,6 +389,8 @@ __global__ void __launch_bounds__(kThreads) matvec_f16_kernel(const __half *__re
     uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [NB][K/8] blocks of 8 halves
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kb = K / 8;
+    pdl_trigger();
+    pdl_wait();
     for (int b = 0; b < NB; b++)
         for (int i = threadIdx.x; i < kb; i += kThreads) xs[b * kb + i] = reinterpret_cast<const uint4 *>(x + (size_t)b * K)[i];
     __syncthreads();
@@ -853,8 +855,7 @@ IM_EXPORT int im_cuda_matvec_f16(const void *w_dev, const void *x_dev, void *y_d
         int grid = sms * cps < ntiles ? sms * cps : ntiles;
         auto launch = [&](auto kern) -> int {
             if (smem > 48 * 1024) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<grid, kThreads, smem, st>>>(w, x + (size_t)done * K, y + (size_t)done * N, N, K);
-            IM_CUDA_CHECK(cudaGetLastError());
+            IM_CUDA_CHECK(launch_k(kern, dim3(grid), dim3(kThreads), smem, st, w, x + (size_t)done * K, y + (size_t)done * N, N, K));
             return IM_OK;
         };
         int rc = nb == 4 ? launch(matvec_f16_kernel<4>) : nb == 2 ? launch(matvec_f16_kernel<2>) : launch(matvec_f16_kernel<1>);

@@ -217,6 +217,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     const int t_end = p.split_tiles ? (int)((long long)total * (blockIdx.x + 1) / gridDim.x) : (int)((long long)p.nblk * (blockIdx.x + 1) / gridDim.x) * G;
 
 #define IM_STAMP(i) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[i] = global_ns(); } while (0)
+    pdl_trigger();
     IM_STAMP(0);
     if (tid == 0) {
         for (int i = 0; i < nring; i++) {
@@ -321,6 +322,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     }
 
     // ---------------------------------------------------- consumers
+    // The weights are constants, so the producer above streams them without waiting; the activations come
+    // from the preceding kernel.  (The producer's output writes follow consumer releases, hence this wait.)
+    pdl_wait();
     float sq_tot[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) {
@@ -500,8 +504,7 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     int grid = dev->sm_count;
     p.split_tiles = p.nblk < grid ? 1 : 0;
     if (grid > total) grid = (int)total;
-    kern<<<grid, kV2Threads, smem, st>>>(p);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(kern, dim3(grid), dim3(kV2Threads), smem, st, p));
     return IM_OK;
 }
 

@@ -149,6 +149,8 @@ struct Model {
 static const int kPrefillChunk = 64;
 
 __global__ void advance_pos_kernel(int *pos, int n, int by) {
+    pdl_trigger();
+    pdl_wait();
     if ((int)threadIdx.x < n) pos[threadIdx.x] += by;
 }
 __global__ void set_pos_kernel(int *pos, int n, int v) {
@@ -161,6 +163,8 @@ __global__ void argmax_kernel(const __half *__restrict__ logits, int vocab_part,
                               uint32_t *__restrict__ hist, const int *__restrict__ step, int hist_stride, int hist_rows) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.x;
     float best = -INFINITY;
     int bi = -1;
@@ -197,7 +201,11 @@ __global__ void argmax_kernel(const __half *__restrict__ logits, int vocab_part,
         if (hist) hist[(size_t)(*step % hist_rows) * hist_stride + seq] = (uint32_t)bi;
     }
 }
-__global__ void bump_kernel(int *step) { *step += 1; }
+__global__ void bump_kernel(int *step) {
+    pdl_trigger();
+    pdl_wait();
+    *step += 1;
+}
 
 static bool parse_layer_name(const char *name, int *layer, std::string *suffix) {
     const char *pfx = "model.layers.";
@@ -397,9 +405,11 @@ static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
     int rc = forward(m, batch, 1, splits, st, &nl);
     if (rc == IM_OK) {
         const __half *lg = m->world > 1 ? m->logits_all : m->logits;
-        argmax_kernel<<<batch, 1024, 0, st>>>(lg, m->vocab_l, m->world, batch, m->tokens_dev, m->tok_hist, m->step_dev, m->cfg.max_batch, m->cfg.max_seq_len);
-        bump_kernel<<<1, 1, 0, st>>>(m->step_dev);
-        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, batch, 1);
+        cudaError_t le = launch_k(argmax_kernel, dim3(batch), dim3(1024), 0, st, lg, m->vocab_l, m->world, batch, m->tokens_dev, m->tok_hist,
+                                  (const int *)m->step_dev, m->cfg.max_batch, m->cfg.max_seq_len);
+        if (le == cudaSuccess) le = launch_k(bump_kernel, dim3(1), dim3(1), 0, st, m->step_dev);
+        if (le == cudaSuccess) le = launch_k(advance_pos_kernel, dim3(1), dim3(64), 0, st, m->pos_dev, batch, 1);
+        if (le != cudaSuccess) rc = fail(IM_ERR_CUDA, "launch failed: %s", cudaGetErrorString(le));
         nl += 3;
     }
     cudaError_t e = cudaStreamEndCapture(st, &g);

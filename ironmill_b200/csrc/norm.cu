@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const __half *__
                                                                 const __half *__restrict__ gamma, __half *__restrict__ normed,
                                                                 __half *__restrict__ residual, int H, float eps) {
     __shared__ float sh[32];
+    pdl_trigger();
+    pdl_wait();
     const size_t base = (size_t)blockIdx.x * H;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -56,6 +58,8 @@ __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const __half *__
 }
 
 __global__ void residual_add_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2half_rn(__half2float(a[i]) + __half2float(b[i]));
 }
@@ -65,6 +69,8 @@ __global__ void __launch_bounds__(kNormThreads) embedding_norm_kernel(const uint
                                                                       __half *__restrict__ raw, int H, uint32_t vocab, float eps,
                                                                       float embed_scale) {
     __shared__ float sh[32];
+    pdl_trigger();
+    pdl_wait();
     const uint32_t tok = tokens[blockIdx.x];
     const bool valid = tok < vocab;
     const size_t src = (size_t)tok * H, dst = (size_t)blockIdx.x * H;
@@ -151,10 +157,9 @@ IM_EXPORT int im_cuda_rms_norm(const void *x_dev, const void *gamma_dev, void *o
     IM_REQUIRE(x_dev && gamma_dev && out_dev, "bad argument");
     IM_REQUIRE(H > 0 && T >= 0, "bad shape");
     if (T == 0) return IM_OK;
-    rms_norm_kernel<0><<<T, kNormThreads, 0, as_stream(stream)>>>(static_cast<const __half *>(x_dev), nullptr,
-                                                                 static_cast<const __half *>(gamma_dev),
-                                                                 static_cast<__half *>(out_dev), nullptr, H, eps);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(rms_norm_kernel<0>, dim3(T), dim3(kNormThreads), 0, as_stream(stream), static_cast<const __half *>(x_dev),
+                           (const __half *)nullptr, static_cast<const __half *>(gamma_dev), static_cast<__half *>(out_dev),
+                           (__half *)nullptr, H, eps));
     return IM_OK;
     IM_GUARD_END
 }
@@ -165,10 +170,9 @@ IM_EXPORT int im_cuda_fused_residual_rms_norm(const void *a_dev, const void *b_d
     IM_REQUIRE(a_dev && b_dev && gamma_dev && normed_dev && residual_dev, "bad argument");
     IM_REQUIRE(H > 0 && T >= 0, "bad shape");
     if (T == 0) return IM_OK;
-    rms_norm_kernel<1><<<T, kNormThreads, 0, as_stream(stream)>>>(static_cast<const __half *>(a_dev), static_cast<const __half *>(b_dev),
-                                                                 static_cast<const __half *>(gamma_dev), static_cast<__half *>(normed_dev),
-                                                                 static_cast<__half *>(residual_dev), H, eps);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(rms_norm_kernel<1>, dim3(T), dim3(kNormThreads), 0, as_stream(stream), static_cast<const __half *>(a_dev),
+                           static_cast<const __half *>(b_dev), static_cast<const __half *>(gamma_dev), static_cast<__half *>(normed_dev),
+                           static_cast<__half *>(residual_dev), H, eps));
     return IM_OK;
     IM_GUARD_END
 }
@@ -177,10 +181,8 @@ IM_EXPORT int im_cuda_residual_add(const void *a_dev, const void *b_dev, void *o
     IM_GUARD_BEGIN
     IM_REQUIRE(a_dev && b_dev && out_dev, "bad argument");
     if (n == 0) return IM_OK;
-    residual_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(static_cast<const __half *>(a_dev),
-                                                                                   static_cast<const __half *>(b_dev),
-                                                                                   static_cast<__half *>(out_dev), n);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(residual_add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, as_stream(stream),
+                           static_cast<const __half *>(a_dev), static_cast<const __half *>(b_dev), static_cast<__half *>(out_dev), n));
     return IM_OK;
     IM_GUARD_END
 }
@@ -191,11 +193,9 @@ IM_EXPORT int im_cuda_embedding_norm(const uint32_t *tokens_dev, const void *tab
     IM_REQUIRE(tokens_dev && table_dev && gamma_dev && normed_dev && raw_dev, "bad argument");
     IM_REQUIRE(H > 0 && T >= 0, "bad shape");
     if (T == 0) return IM_OK;
-    embedding_norm_kernel<<<T, kNormThreads, 0, as_stream(stream)>>>(tokens_dev, static_cast<const __half *>(table_dev),
-                                                                    static_cast<const __half *>(gamma_dev),
-                                                                    static_cast<__half *>(normed_dev), static_cast<__half *>(raw_dev), H,
-                                                                    vocab, eps, embed_scale);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(embedding_norm_kernel, dim3(T), dim3(kNormThreads), 0, as_stream(stream), tokens_dev,
+                           static_cast<const __half *>(table_dev), static_cast<const __half *>(gamma_dev),
+                           static_cast<__half *>(normed_dev), static_cast<__half *>(raw_dev), H, vocab, eps, embed_scale));
     return IM_OK;
     IM_GUARD_END
 }

@@ -237,6 +237,8 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kvh = blockIdx.x, st = blockIdx.y, split = blockIdx.z;
+    pdl_trigger();
+    pdl_wait();
     const int seq = st / p.T, t = st % p.T;
     const int seq_len = p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1;
     const int chunk = (seq_len + p.splits - 1) / p.splits;
@@ -432,6 +434,8 @@ __global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a) {
     __shared__ float sh[3 * kHd];
     __shared__ float red[4];
     const int d = threadIdx.x, slot = blockIdx.x, st = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     const int seq = st / a.T, t = st % a.T;
     const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
     const __half *tok = a.qkv + (size_t)st * a.stride;
@@ -489,6 +493,8 @@ __global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict_
                                                         __half *__restrict__ out, int nh, int splits) {
     __shared__ float x[kHd];
     const int d = threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const size_t base = ((size_t)blockIdx.y * nh + blockIdx.x) * splits;
     float gm = -INFINITY;
     for (int s = 0; s < splits; s++) gm = fmaxf(gm, pm[base + s]);
@@ -674,8 +680,7 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
     k.vtab = EncodeTables{tq->signs, tq->v_cb, tq->v_bd, tq->qjl_t, tq->v_levels, 0};
     k.kc = a.kc; k.vc = a.vc; k.ks = a.ks; k.vs = a.vs; k.krn = a.krn;
     dim3 grid(a.nh + 2 * a.nkv, a.nseq * a.T);
-    tq_qkv_prep_kernel<<<grid, kHd, 0, st>>>(k);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(tq_qkv_prep_kernel, grid, dim3(kHd), 0, st, k));
     return IM_OK;
 }
 
@@ -704,16 +709,15 @@ int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uin
     p.nh = nh; p.nkv = nkv; p.max_seq = max_seq; p.base_pos = base_pos; p.T = T; p.splits = splits; p.pos_dev = pos_dev;
     dim3 grid(nkv, nseq * T, splits);
     switch (nh / nkv) {
-        case 1: tq_attention_kernel<1><<<grid, kAttnThreads, 0, st>>>(p); break;
-        case 2: tq_attention_kernel<2><<<grid, kAttnThreads, 0, st>>>(p); break;
-        case 4: tq_attention_kernel<4><<<grid, kAttnThreads, 0, st>>>(p); break;
-        case 8: tq_attention_kernel<8><<<grid, kAttnThreads, 0, st>>>(p); break;
+        case 1: IM_CUDA_CHECK(launch_k(tq_attention_kernel<1>, grid, dim3(kAttnThreads), 0, st, p)); break;
+        case 2: IM_CUDA_CHECK(launch_k(tq_attention_kernel<2>, grid, dim3(kAttnThreads), 0, st, p)); break;
+        case 4: IM_CUDA_CHECK(launch_k(tq_attention_kernel<4>, grid, dim3(kAttnThreads), 0, st, p)); break;
+        case 8: IM_CUDA_CHECK(launch_k(tq_attention_kernel<8>, grid, dim3(kAttnThreads), 0, st, p)); break;
         default: return fail(IM_ERR_INVALID, "query heads per KV head must be 1, 2, 4 or 8 (got %d/%d)", nh, nkv);
     }
-    IM_CUDA_CHECK(cudaGetLastError());
     dim3 rgrid(nh, nseq * T);
-    tq_reduce_kernel<<<rgrid, kHd, 0, st>>>(p.po, p.pm, p.pl, tq->signs, out, nh, splits);
-    IM_CUDA_CHECK(cudaGetLastError());
+    IM_CUDA_CHECK(launch_k(tq_reduce_kernel, rgrid, dim3(kHd), 0, st, (const float *)p.po, (const float *)p.pm, (const float *)p.pl,
+                           (const float *)tq->signs, out, nh, splits));
     return IM_OK;
 }
 }  // namespace im
