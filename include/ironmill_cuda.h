@@ -228,6 +228,22 @@ int im_cuda_tq_fused_attention(im_tq *tq, const void *qkv_dev, int qkv_stride, i
                                float *v_scale_dev, float *k_rnorm_dev, float attn_scale, float *qrot_dev, void *out_dev,
                                int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
                                int num_splits, void *stream);
+/* im_cuda_tq_attention for callers that must not allocate.  (No counterpart in the reference: its Metal backend
+ * sizes every buffer up front; this entry point exists for CUDA hosts that cannot call cudaMalloc when they need
+ * attention - an arena-owning server, a plugin whose host forbids allocation after start-up, code that runs between
+ * another component's graph capture and replay.)  It allocates nothing and calls nothing that allocates: the split
+ * partials go into a 4 MiB array inside the library image, which every GPU that loads the library keeps until the
+ * process exits.  Same arguments and results as im_cuda_tq_attention.  Limits and rules:
+ *  - nseq * T * nh * splits * 520 bytes must fit 4 MiB, otherwise IM_ERR_BOUNDS with the numbers in the message;
+ *  - the device of `tq` must be the current device;
+ *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress); make that first call
+ *    before any stream capture;
+ *  - all calls share the one array, which keeps whatever the last call left in it (nothing needs clearing: every
+ *    split writes its whole partial before it is read); two calls whose kernels overlap on the GPU race. */
+int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,
+                                void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
+                                int num_splits, void *stream);
 size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
 int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
 

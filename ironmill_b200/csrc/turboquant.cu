@@ -785,3 +785,48 @@ IM_EXPORT int im_cuda_tq_fused_attention(im_tq *tq, const void *qkv_dev, int qkv
                                nh, nkv, max_seq, base_pos, pos_dev, T, splits, st, qrot_dev);
     IM_GUARD_END
 }
+
+// ---------------------------------------------------------------- attention without any allocation
+// Some hosts cannot allocate device memory at the moment they need attention: a serving loop that has handed
+// all memory to its own arena, code running between the capture and the replay of someone else's CUDA graph, a
+// plugin whose host forbids cudaMalloc after start-up.  For them the split partials live in a fixed array that
+// is part of the library image: every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr size_t kStaticScratchFloats = (size_t)1 << 20;  // 4 MiB
+static __device__ __align__(256) float g_static_attn_scratch[kStaticScratchFloats];
+static float *g_static_attn_ptr[64] = {};  // device address of the array, per device ordinal
+
+IM_EXPORT int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                          const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev,
+                                          float attn_scale, void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos,
+                                          const int *pos_dev, int T, int num_splits, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(tq && q_dev && k_cache_dev && v_cache_dev && k_scale_dev && v_scale_dev && k_rnorm_dev && out_dev, "bad argument");
+    IM_REQUIRE(tq->hd == kHd, "the attention kernel is built for head_dim 128 (got %d)", tq->hd);
+    IM_REQUIRE(nkv > 0 && nh % nkv == 0, "nh must be a multiple of nkv");
+    IM_REQUIRE(nseq >= 0 && T >= 0 && max_seq > 0 && base_pos >= 0, "bad shape");
+    if (nseq == 0 || T == 0) return IM_OK;
+    if (!pos_dev && base_pos + T > max_seq)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", base_pos, T, max_seq);
+    int cur = -1;
+    IM_CUDA_CHECK(cudaGetDevice(&cur));
+    IM_REQUIRE(cur == tq->dev->ordinal, "device %d must be current (device %d is)", tq->dev->ordinal, cur);
+    IM_REQUIRE(cur >= 0 && cur < 64, "device ordinal %d is outside the table", cur);
+    if (!g_static_attn_ptr[cur]) {
+        // The array's name is a host-side stand-in; the kernels need its address on THIS device.
+        float *ptr = nullptr;
+        IM_CUDA_CHECK(cudaGetSymbolAddress((void **)&ptr, g_static_attn_scratch));
+        g_static_attn_ptr[cur] = ptr;
+    }
+    const int splits = num_splits > 0 ? num_splits : tq_auto_splits(tq->dev, nseq, T, nkv, base_pos + T);
+    const size_t need = im_cuda_tq_scratch_bytes(nseq, T, nh, kHd, splits);
+    if (need > kStaticScratchFloats * sizeof(float))
+        return fail(IM_ERR_BOUNDS,
+                    "%d sequence(s) x %d token(s) x %d heads x %d splits need %zu bytes of split partials; the built-in scratch holds %zu "
+                    "(use fewer splits or im_cuda_tq_attention)",
+                    nseq, T, nh, splits, need, kStaticScratchFloats * sizeof(float));
+    // Nothing has to start at zero: every split, empty ones included, writes its whole partial before the reduce reads it.
+    return tq_attention_launch(tq, g_static_attn_ptr[cur], static_cast<const __half *>(q_dev), static_cast<const uint8_t *>(k_cache_dev),
+                               static_cast<const uint8_t *>(v_cache_dev), k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale,
+                               static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream));
+    IM_GUARD_END
+}

@@ -342,3 +342,14 @@ def tq_fused_attention(tq: "TurboQuant", qkv, nh, nkv, cos, sin, k_cache, v_cach
                                            C.c_int(nkv), C.c_int(max_seq), C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_int(num_splits),
                                            _stream()))
     return out
+
+
+def tq_attention_static(tq: "TurboQuant", q, k_cache, v_cache, k_scale, v_scale, k_rnorm, attn_scale, nh, nkv, max_seq, base_pos,
+                        nseq=1, pos_dev=None, num_splits=0):
+    """Attention through the entry point that allocates nothing (split partials in the library's built-in array)."""
+    T = _h16(q).numel() // (nseq * nh * tq.head_dim)
+    out = torch.empty_like(q)
+    check(lib().im_cuda_tq_attention_static(tq.handle, vp(q), vp(k_cache), vp(v_cache), vp(k_scale), vp(v_scale), vp(k_rnorm),
+                                            C.c_float(attn_scale), vp(out), C.c_int(nseq), C.c_int(nh), C.c_int(nkv), C.c_int(max_seq),
+                                            C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_int(num_splits), _stream()))
+    return out
