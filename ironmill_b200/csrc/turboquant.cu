@@ -181,8 +181,17 @@ __device__ __forceinline__ void tq_encode_body(float xin, const EncodeTables &tb
             __syncthreads();
         }
         if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+        // Same sequential sum; the matrix column is fetched 64 values at a time so that the loads are in
+        // flight together instead of one memory latency per term.
         float proj = 0.0f;
-        for (int k = 0; k < hd; k++) proj = __fadd_rn(proj, __fmul_rn(tb.qjl_t[(size_t)k * hd + d], res[k]));
+        for (int k0 = 0; k0 < hd; k0 += 64) {
+            float sv[64];
+#pragma unroll
+            for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? tb.qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 64; j++)
+                if (k0 + j < hd) proj = __fadd_rn(proj, __fmul_rn(sv[j], res[k0 + j]));
+        }
         if (proj >= 0.0f) byte |= 0x80u;
     }
     cache_row[d] = (uint8_t)byte;
@@ -479,6 +488,7 @@ __global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a) {
     __syncthreads();
     hadamard_block<1>(sh, kHd, a.ktab.signs, kHd);
     float acc = 0.0f;
+#pragma unroll 32
     for (int k = 0; k < kHd; k++) acc = fmaf(a.ktab.qjl_t[(size_t)k * kHd + d], sh[k], acc);
     float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
     dst[d] = sh[d];
