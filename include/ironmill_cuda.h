@@ -288,6 +288,13 @@ int im_cuda_model_set_tq_constants(im_model *m, const float *signs_host, const f
 /* Tensor parallel: rank 0 makes an id (128 bytes), every rank passes the same bytes. */
 int im_cuda_tp_unique_id(void *id_out_128_bytes);
 int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes);
+/* Host-only pieces of the tensor-parallel loader (no GPU needed): the rectangle [r0,r0+nr) x [c0,c0+nc) of a full
+ * projection that rank cfg->tp_rank keeps (`suffix` = tensor name after "model.layers.<i>."), and the cut itself
+ * into caller buffers sized for the shard.  (Tensor parallelism has no counterpart in the reference.) */
+int im_cuda_tp_shard_rect(const im_model_config *cfg, const char *suffix, int *r0, int *nr, int *c0, int *nc);
+int im_cuda_tp_shard_affine(const void *qdata_host, const void *scales_host, const void *zeros_host, int param_dtype,
+                            const void *awq_f16_host, int N, int K, int group_size, int bit_width, int r0, int nr, int c0,
+                            int nc, void *q_out, void *scales_out, void *zeros_out, void *awq_out);
 /* Checks that every tensor arrived, repacks, allocates KV caches / RoPE tables / TurboQuant constants
  * (init_model_state, crates/ironmill-inference/src/metal/loading.rs:32-65). */
 int im_cuda_model_finalize(im_model *m);

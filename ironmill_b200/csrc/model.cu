@@ -226,6 +226,20 @@ static int upload_f16(Model *m, __half **dst, const void *src, size_t n) {
     return IM_OK;
 }
 
+// The rectangle of a full projection that a tensor-parallel rank keeps: q/k/v/gate/up are split by output rows
+// (whole heads), o/down by input columns; (en, ek) is the full shape the tensor must have.
+static int shard_rect(const im_model_config &c, const std::string &suffix, int *r0, int *nr, int *c0, int *nc, int *en, int *ek) {
+    const int world = c.tp_world > 0 ? c.tp_world : 1, r = c.tp_rank, H = c.hidden_size, hd = c.head_dim;
+    const int q_dim = c.num_heads / world * hd, kv_dim = c.num_kv_heads / world * hd, I_l = c.intermediate_size / world;
+    if (suffix == "self_attn.q_proj.weight") { *en = c.num_heads * hd; *ek = H; *r0 = r * q_dim; *nr = q_dim; *c0 = 0; *nc = H; }
+    else if (suffix == "self_attn.k_proj.weight" || suffix == "self_attn.v_proj.weight") { *en = c.num_kv_heads * hd; *ek = H; *r0 = r * kv_dim; *nr = kv_dim; *c0 = 0; *nc = H; }
+    else if (suffix == "self_attn.o_proj.weight") { *en = H; *ek = c.num_heads * hd; *r0 = 0; *nr = H; *c0 = r * q_dim; *nc = q_dim; }
+    else if (suffix == "mlp.gate_proj.weight" || suffix == "mlp.up_proj.weight") { *en = c.intermediate_size; *ek = H; *r0 = r * I_l; *nr = I_l; *c0 = 0; *nc = H; }
+    else if (suffix == "mlp.down_proj.weight") { *en = H; *ek = c.intermediate_size; *r0 = 0; *nr = H; *c0 = r * I_l; *nc = I_l; }
+    else return IM_ERR_INVALID;
+    return IM_OK;
+}
+
 // Cut rows [r0, r0+nr) and columns [c0, c0+nc) out of a full affine tensor.
 static int slice_affine(HostAffine *out, const void *qdata, const void *scales, const void *zeros, int param_dtype, const void *awq,
                         int N, int K, int gs, int bits, int r0, int nr, int c0, int nc) {
@@ -608,36 +622,16 @@ IM_EXPORT int im_cuda_model_load_affine(im_model *m, const char *name, const voi
         if (N != en || K != ek) return fail(IM_ERR_INVALID, "%s: expected shape [%d,%d], got [%d,%d]", name, en, ek, N, K);
         return IM_OK;
     };
-#define SLICE(r0, nr, c0, nc) slice_affine(&h, qdata_host, scales_host, zeros_host, param_dtype, awq_f16_host, N, K, group_size, bit_width, r0, nr, c0, nc)
-    if (suffix == "self_attn.q_proj.weight") {
-        IM_TRY(expect(c.num_heads * hd, H));
-        IM_TRY(SLICE(r * m->q_dim, m->q_dim, 0, K));
-        L.hq = std::move(h);
-        return IM_OK;
-    }
-    if (suffix == "self_attn.k_proj.weight" || suffix == "self_attn.v_proj.weight") {
-        IM_TRY(expect(c.num_kv_heads * hd, H));
-        IM_TRY(SLICE(r * m->kv_dim, m->kv_dim, 0, K));
-        (suffix[10] == 'k' ? L.hk : L.hv) = std::move(h);
-        return IM_OK;
-    }
-    AffineWeight **dst = nullptr;
-    if (suffix == "self_attn.o_proj.weight") {
-        IM_TRY(expect(H, c.num_heads * hd));
-        IM_TRY(SLICE(0, N, r * m->q_dim, m->q_dim));
-        dst = &L.o;
-    } else if (suffix == "mlp.gate_proj.weight" || suffix == "mlp.up_proj.weight") {
-        IM_TRY(expect(c.intermediate_size, H));
-        IM_TRY(SLICE(r * m->I_l, m->I_l, 0, K));
-        dst = suffix[4] == 'g' ? &L.gate : &L.up;
-    } else if (suffix == "mlp.down_proj.weight") {
-        IM_TRY(expect(H, c.intermediate_size));
-        IM_TRY(SLICE(0, N, r * m->I_l, m->I_l));
-        dst = &L.down;
-    } else {
-        return fail(IM_ERR_INVALID, "unknown quantized tensor '%s'", name);
-    }
-#undef SLICE
+    int r0, nr, c0, nc, en, ek;
+    if (shard_rect(c, suffix, &r0, &nr, &c0, &nc, &en, &ek) != IM_OK) return fail(IM_ERR_INVALID, "unknown quantized tensor '%s'", name);
+    IM_TRY(expect(en, ek));
+    IM_TRY(slice_affine(&h, qdata_host, scales_host, zeros_host, param_dtype, awq_f16_host, N, K, group_size, bit_width, r0, nr, c0, nc));
+    (void)H; (void)hd; (void)r;
+    if (suffix == "self_attn.q_proj.weight") { L.hq = std::move(h); return IM_OK; }
+    if (suffix == "self_attn.k_proj.weight") { L.hk = std::move(h); return IM_OK; }
+    if (suffix == "self_attn.v_proj.weight") { L.hv = std::move(h); return IM_OK; }
+    AffineWeight **dst = suffix == "self_attn.o_proj.weight" ? &L.o : suffix == "mlp.gate_proj.weight" ? &L.gate
+                         : suffix == "mlp.up_proj.weight" ? &L.up : &L.down;
     if (*dst) return fail(IM_ERR_STATE, "%s loaded twice", name);
     return make_weight(m, h, dst);
     IM_GUARD_END
@@ -915,6 +909,37 @@ IM_EXPORT int im_cuda_model_profile_step(im_model *m, int batch, float *ms_by_ca
     for (cudaEvent_t ev : prof.ev) cudaEventDestroy(ev);
     if (rc != IM_OK) return rc;
     if (e != cudaSuccess) return fail(IM_ERR_CUDA, "profile step failed: %s", cudaGetErrorString(e));
+    return IM_OK;
+    IM_GUARD_END
+}
+
+// Host-only helpers of the tensor-parallel loader, exported so that the shard arithmetic can be checked on a
+// machine without a GPU.  `suffix` is the part of the tensor name after "model.layers.<i>.".
+IM_EXPORT int im_cuda_tp_shard_rect(const im_model_config *cfg, const char *suffix, int *r0, int *nr, int *c0, int *nc) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(cfg && suffix && r0 && nr && c0 && nc, "bad argument");
+    int en, ek;
+    if (shard_rect(*cfg, suffix, r0, nr, c0, nc, &en, &ek) != IM_OK) return fail(IM_ERR_INVALID, "unknown projection '%s'", suffix);
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_tp_shard_affine(const void *qdata_host, const void *scales_host, const void *zeros_host, int param_dtype,
+                                      const void *awq_f16_host, int N, int K, int group_size, int bit_width, int r0, int nr, int c0,
+                                      int nc, void *q_out, void *scales_out, void *zeros_out, void *awq_out) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(qdata_host && scales_host && zeros_host && q_out && scales_out && zeros_out, "bad argument");
+    HostAffine h;
+    IM_TRY(slice_affine(&h, qdata_host, scales_host, zeros_host, param_dtype, awq_f16_host, N, K, group_size, bit_width, r0, nr, c0, nc));
+    memcpy(q_out, h.q.data(), h.q.size());
+    if (h.param_f32) {
+        memcpy(scales_out, h.s.data(), h.s.size() * 4);
+        memcpy(zeros_out, h.z.data(), h.z.size() * 4);
+    } else {
+        memcpy(scales_out, h.s16.data(), h.s16.size() * 2);
+        memcpy(zeros_out, h.z16.data(), h.z16.size() * 2);
+    }
+    if (awq_out && !h.awq.empty()) memcpy(awq_out, h.awq.data(), h.awq.size() * 2);
     return IM_OK;
     IM_GUARD_END
 }

@@ -1,0 +1,63 @@
+"""Tensor-parallel engine on 2 GPUs (NCCL): logits of the sharded model against the single-GPU engine.
+Skipped when fewer than 2 GPUs are visible."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ironmill_b200.bundle import ModelConfig
+        from ironmill_b200.engine import CudaConfig, CudaInference
+        from oracle import oracle as orc
+        from tests.oracle_model import DictProvider, synth_model
+        cfg = ModelConfig(architecture="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                          num_key_value_heads=2, head_dim=128, vocab_size=1000, rms_norm_eps=1e-5, rope_theta=5e5)
+        tensors = synth_model(cfg, seed=9, awq=True)
+        tqc = orc.TqConstants(128, 8, seed=42)
+        eng = CudaInference(CudaConfig(max_seq_len=64, tp_world=world, tp_rank=rank, device=rank))
+        eng.load_weights(DictProvider(cfg, tensors), tq_signs=tqc.signs, tq_qjl=tqc.qjl)
+        ids = [CudaInference.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        eng.tp_init(ids[0])
+        prompt = np.arange(7, dtype=np.uint32) * 13 % 1000
+        outs = [eng.prefill(prompt)]
+        for t in (5, 17, 400):
+            outs.append(eng.decode_step(t))
+        if rank == 0:
+            single = CudaInference(CudaConfig(max_seq_len=64, device=0))
+            single.load_weights(DictProvider(cfg, tensors), tq_signs=tqc.signs, tq_qjl=tqc.qjl)
+            refs = [single.prefill(prompt)] + [single.decode_step(t) for t in (5, 17, 400)]
+            err = max(float(np.abs(a - b).max()) for a, b in zip(outs, refs))
+            ret[0] = err
+        dist.barrier()
+    except Exception as e:  # noqa: BLE001
+        ret[rank] = f"{type(e).__name__}: {e}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert isinstance(ret.get(0), float) and ret[0] <= 5e-2, dict(ret)
+    assert 1 not in ret, dict(ret)
