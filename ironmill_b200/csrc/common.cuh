@@ -91,6 +91,8 @@ struct V2Params {
     unsigned long long *trace;  // optional: 8 timer stamps from CTA 0 (development aid), else nullptr
 };
 
+// Gate/up pair as one tile stream (matvec.cu); built on first use.
+int ensure_pair(const AffineWeight *gate, const AffineWeight *up, cudaStream_t st);
 int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st);
 int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, const __half2 *sz1, int N, int K, int G, int nblk,
               int rows_per_blk, uint8_t *tiles, cudaStream_t st);

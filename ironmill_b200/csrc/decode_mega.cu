@@ -1,0 +1,535 @@
+// Whole-token decode kernel: every decoder layer of one batch-1 decode step in ONE persistent launch.
+//
+// Why: a decode step of a Llama-3-8B-shaped model is ~230 short kernels (7 per layer).  Each of them pays a
+// launch ramp, a pipeline fill and a tail in which HBM idles, and together those fixed costs are several
+// times the time the weight bytes need.  Here one CTA per SM lives for the whole token:
+//   * its producer warp streams this CTA's share of EVERY projection of EVERY layer, in execution order,
+//     through one shared-memory ring with cp.async.bulk.  Weights are constants, so the producer never waits
+//     for activations, only for a free ring slot: while the consumers sit in a grid barrier, rotate a query
+//     or walk the KV cache, the next projection's tiles are already arriving;
+//   * its 16 consumer warps run the phases of the layer (the same arithmetic as the stand-alone kernels:
+//     matvec_v2.cu for the projections, tq_device.cuh for RoPE + cache write, attention and its reduction),
+//     separated by grid-wide barriers (one arrival counter per barrier, bounded polls).
+// Phases of layer l:  [residual+norm ->] QKV | RoPE + TurboQuant cache write + query rotation | split attention
+//                     | split reduction | o | residual+norm -> gate/up+SiLU | down.
+// The launch is cooperative (all CTAs resident).  Semantics per phase:
+//   crates/ironmill-inference/src/metal/pipeline.rs:436-1245 (run_pipeline_inner) and the shader files named in
+//   matvec_v2.cu / turboquant.cu.
+#include "common.cuh"
+#include "tq_device.cuh"
+#include "v2_device.cuh"
+#include "mega.cuh"
+
+namespace im {
+
+namespace {
+
+constexpr int kGroups = kV2Consumers / 4;      // 128-thread groups of consumer warps
+constexpr int kRedFloats = kV2Consumers * 16;  // per ring slot: 16 row sums from each consumer warp
+constexpr int kStageBytes = kStageTiles * kTileBytes;
+
+struct Range {
+    int t_begin, t_end;
+};
+__device__ __forceinline__ Range cta_range(int nblk, int G) {  // whole row blocks per CTA
+    const int b0 = (int)((long long)nblk * blockIdx.x / gridDim.x), b1 = (int)((long long)nblk * (blockIdx.x + 1) / gridDim.x);
+    return Range{b0 * G, b1 * G};
+}
+// barrier index of matvec phase q (4 per layer: qkv, o, gate/up, down); 7 barriers per layer:
+// qkv, prep, attention, reduce, o, gate/up, down
+__device__ __forceinline__ int phase_barrier(int q) {
+    const int j = q & 3;
+    return (q >> 2) * 7 + (j == 0 ? 0 : j + 3);
+}
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_volatile(const int *p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Arrival of this CTA at barrier k: the caller's threads have synchronised among themselves.
+__device__ __forceinline__ void grid_arrive(unsigned *bar, int k) {
+    __threadfence();
+    atomicAdd(bar + k, 1u);
+}
+// One thread polls until every CTA has arrived (or the error word is set / the time limit passes).
+__device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err) {
+    const unsigned want = gridDim.x;
+    if (ld_acquire(bar + k) >= want) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned i = 1;; i++) {
+        __nanosleep(20);
+        if (ld_acquire(bar + k) >= want) return true;
+        if ((i & 127u) == 0) {
+            if (ld_volatile(err) != 0) return false;
+            if (global_ns() - t0 > kWaitLimitNs) break;
+        }
+    }
+    atomicExch(err, 2);
+    return false;
+}
+
+// ---- activation staging for one batch row (the NB = 1 case of matvec_v2.cu's v2_stage_x) ------------------
+// xq words: index ((grp*2 + col)*4 + t)*8 + j*2 + eo, col 0 = high bytes, 1 = low bytes; meta[grp] = (scale, sum).
+template <bool NORM>
+__device__ __forceinline__ float mega_stage_x(const __half *__restrict__ x, const __half *__restrict__ b, const __half *__restrict__ gamma,
+                                              const __half *__restrict__ awq, int G, uint32_t *xq, float2 *meta) {
+    const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
+    float sq = 0.0f;
+#pragma unroll 2
+    for (int g0 = warp * 2; g0 < G; g0 += kV2Consumers * 2) {
+        const int grp = g0 + (lane >> 4);
+        const bool live = grp < G;
+        const int k = (live ? grp : g0) * 128 + hl * 8;
+        float v[8];
+        {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(h[i]);
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            }
+        }
+        if (NORM) {
+            const uint4 rb = *reinterpret_cast<const uint4 *>(b + k);
+            const uint4 rg = *reinterpret_cast<const uint4 *>(gamma + k);
+            const __half2 *hb = reinterpret_cast<const __half2 *>(&rb), *hg = reinterpret_cast<const __half2 *>(&rg);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 fb = __half22float2(hb[i]), fg = __half22float2(hg[i]);
+                const float r0 = v[2 * i] + fb.x, r1 = v[2 * i + 1] + fb.y;
+                if (live) sq += r0 * r0 + r1 * r1;
+                v[2 * i] = r0 * fg.x;
+                v[2 * i + 1] = r1 * fg.y;
+            }
+        }
+        if (awq) {
+            const uint4 ra = *reinterpret_cast<const uint4 *>(awq + k);
+            const __half2 *ha = reinterpret_cast<const __half2 *>(&ra);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 fa = __half22float2(ha[i]);
+                v[2 * i] = v[2 * i] / fa.x;
+                v[2 * i + 1] = v[2 * i + 1] / fa.y;
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float sx = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f;
+        const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
+        int hi[8], lo[8], lsum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int xi = __float2int_rn(v[i] * inv);
+            xi = max(-32639, min(32639, xi));
+            lsum += xi;
+            hi[i] = (xi + 128) >> 8;
+            lo[i] = xi - hi[i] * 256;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        if (live) {
+            const int t = hl >> 2, j = hl & 3;
+            uint2 *dh = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 0) * 4 + t) * 4 + j) * 2);
+            uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 1) * 4 + t) * 4 + j) * 2);
+            *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
+            *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
+            if (hl == 0) meta[grp] = make_float2(sx, (float)lsum);
+        }
+    }
+    return sq;
+}
+
+}  // namespace
+
+template <int GQ>
+__global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int nring = p.nring;
+    unsigned char *ring = smem;
+    float *red = reinterpret_cast<float *>(ring + (size_t)nring * kStageBytes);
+    float *cbk = red + (size_t)nring * kRedFloats;  // K codebook (128), V codebook (256)
+    float *cbv = cbk + 128;
+    float *misc = cbv + 256;                         // [0] rms_inv, [8..23] reduction scratch, [30] wait result
+    uint64_t *full = reinterpret_cast<uint64_t *>(misc + 32);
+    uint64_t *empty = full + nring;
+    unsigned char *U = reinterpret_cast<unsigned char *>(empty + nring);  // phase scratch (16-byte aligned by construction)
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int NP = 4 * p.L;
+
+    if (tid == 0) {
+        for (int i = 0; i < nring; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], kV2Consumers);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (p.trace && blockIdx.x == 0) p.trace[0] = global_ns();
+    }
+    for (int i = tid; i < 128 + 256; i += kV2Threads) cbk[i] = i < 128 ? p.k_cb[i] : p.v_cb[i - 128];
+    __syncthreads();
+
+    if (warp == kV2Consumers) {
+        // =========================================================== producer warp
+        // Lane 0 issues the stages of every phase in order.  Before a slot is refilled the warp waits for the
+        // consumers to release it; if the stage that lived there ended a row block, the warp adds the sixteen
+        // partial sums in warp order, applies the epilogue and writes the outputs; after the last stage of a
+        // phase it arrives at that phase's grid barrier.
+        struct Cursor {
+            int q;          // phase
+            StageIter it;
+            MegaPhase ph;
+        };
+        auto open = [&](Cursor &c, int q) {
+            c.q = q;
+            if (q < NP) {
+                c.ph = p.phases[q];
+                const Range r = cta_range(c.ph.nblk, c.ph.G);
+                c.it = StageIter(r.t_begin, r.t_end, c.ph.G);
+            }
+        };
+        auto arrive = [&](int q) {  // all lanes' output writes precede the arrival
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(p.bar + phase_barrier(q), 1u);
+        };
+        Cursor issue{0, StageIter(0, 0, 1), MegaPhase{}}, done{0, StageIter(0, 0, 1), MegaPhase{}};
+        open(issue, 0);
+        open(done, 0);
+        // phases in which this CTA has no tiles are passed at once
+        auto skip_empty_done = [&]() {
+            while (done.q < NP && done.it.t >= done.it.t_end) {
+                arrive(done.q);
+                open(done, done.q + 1);
+            }
+        };
+        skip_empty_done();
+        bool ok = true;
+        auto reclaim = [&](int slot_, int parity) {  // the oldest stage in flight lives in slot_
+            if (ok && !mbar_wait_warp(&empty[slot_], parity, p.err)) ok = false;
+            int dt0, dn, drb, dgrp;
+            done.it.next(dt0, dn, drb, dgrp);
+            const MegaPhase &ph = done.ph;
+            if (ok && dgrp + dn == ph.G) {  // the stage ended a row block: combine and write
+                const float *buf = red + slot_ * kRedFloats;
+                float v = 0.0f;
+                if (lane < 16) {
+#pragma unroll
+                    for (int w = 0; w < kV2Consumers; w++) v += buf[w * 16 + lane];
+                }
+                const float ri = ph.resid ? misc[0] : 1.0f;
+                const float vu = __shfl_down_sync(0xffffffffu, v, 8);  // lanes 0-7: the up row of the same output
+                if (ph.gate_up) {
+                    const float gv = v * ri, uv = vu * ri;
+                    const int n = drb * 8 + lane;
+                    if (lane < 8 && n < ph.N) ph.y[n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
+                } else {
+                    const int n = drb * 16 + lane;
+                    if (lane < 16 && n < ph.N) ph.y[n] = __float2half_rn(v * ri);
+                }
+            }
+            if (done.it.t >= done.it.t_end) {  // that was this CTA's last stage of the phase
+                arrive(done.q);
+                open(done, done.q + 1);
+                skip_empty_done();
+            }
+        };
+        int slot = 0, phase = 0, nstages = 0;
+        int t0, n, rb0, grp0;
+        while (issue.q < NP) {
+            if (!issue.it.next(t0, n, rb0, grp0)) {
+                open(issue, issue.q + 1);
+                continue;
+            }
+            if (nstages >= nring) reclaim(slot, phase ^ 1);
+            if (lane == 0) {
+                mbar_expect_tx(&full[slot], (uint32_t)(n * kTileBytes));
+                bulk_g2s(ring + (size_t)slot * kStageBytes, issue.ph.tiles + (size_t)t0 * kTileBytes, (uint32_t)(n * kTileBytes), &full[slot]);
+            }
+            nstages++;
+            if (++slot == nring) {
+                slot = 0;
+                phase ^= 1;
+            }
+        }
+        int left = nstages < nring ? nstages : nring;
+        int dslot = nstages < nring ? 0 : slot, dphase = nstages < nring ? 0 : (phase ^ 1);
+        for (; left > 0; left--) {
+            reclaim(dslot, dphase);
+            if (++dslot == nring) {
+                dslot = 0;
+                dphase ^= 1;
+            }
+        }
+    } else {
+        // =========================================================== consumers
+        float2 *meta = reinterpret_cast<float2 *>(U);                                        // [g_max]
+        uint32_t *xq = reinterpret_cast<uint32_t *>(U + (((size_t)p.g_max * 8 + 15) & ~(size_t)15));  // [G][2][32] words
+        const int group = warp >> 2;
+        const GroupScope gs{tid & 127, 128, 2 + group};
+        bool dead = false;
+        int slot = 0, par = 0;
+
+        auto grid_wait = [&](int k) {
+            if (tid == 0) {
+                const bool okw = dead ? false : grid_poll(p.bar, k, p.err);
+                reinterpret_cast<int *>(misc)[30] = okw ? 1 : 0;
+                if (p.trace && blockIdx.x == 0) p.trace[k + 1] = global_ns();
+            }
+            consumer_sync();
+            if (reinterpret_cast<int *>(misc)[30] == 0) dead = true;
+        };
+        auto items_done = [&](int k) {  // every consumer thread has finished its items of the phase
+            consumer_sync();
+            if (tid == 0) grid_arrive(p.bar, k);
+        };
+
+        const int g = lane >> 2, t = lane & 3;
+        float acc0 = 0.0f, acc1 = 0.0f;
+        auto tile_pair = [&](const unsigned char *tile_a, int grp_a, const unsigned char *tile_b, int grp_b, bool have_b) {
+            const uint4 a0 = *reinterpret_cast<const uint4 *>(tile_a + lane * 16);
+            const uint4 a1 = *reinterpret_cast<const uint4 *>(tile_a + 512 + lane * 16);
+            uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
+            if (have_b) {
+                b0 = *reinterpret_cast<const uint4 *>(tile_b + lane * 16);
+                b1 = *reinterpret_cast<const uint4 *>(tile_b + 512 + lane * 16);
+            }
+            uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
+            if (g < 2) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_a * 2 + g) * 4 + t) * 8);
+                xa0 = xp[0];
+                xa1 = xp[1];
+                if (have_b) {
+                    const uint4 *xr = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_b * 2 + g) * 4 + t) * 8);
+                    xb0 = xr[0];
+                    xb1 = xr[1];
+                }
+            }
+            int ca0[4] = {0, 0, 0, 0}, ca1[4] = {0, 0, 0, 0}, cb0[4] = {0, 0, 0, 0}, cb1[4] = {0, 0, 0, 0};
+            constexpr unsigned M = 0x0F0F0F0Fu;
+            mma_u8s8(ca0, a0.x & M, a1.x & M, (a0.x >> 4) & M, (a1.x >> 4) & M, xa0.x, xa0.y);
+            mma_u8s8(cb0, b0.x & M, b1.x & M, (b0.x >> 4) & M, (b1.x >> 4) & M, xb0.x, xb0.y);
+            mma_u8s8(ca1, a0.y & M, a1.y & M, (a0.y >> 4) & M, (a1.y >> 4) & M, xa0.z, xa0.w);
+            mma_u8s8(cb1, b0.y & M, b1.y & M, (b0.y >> 4) & M, (b1.y >> 4) & M, xb0.z, xb0.w);
+            mma_u8s8(ca0, a0.z & M, a1.z & M, (a0.z >> 4) & M, (a1.z >> 4) & M, xa1.x, xa1.y);
+            mma_u8s8(cb0, b0.z & M, b1.z & M, (b0.z >> 4) & M, (b1.z >> 4) & M, xb1.x, xb1.y);
+            mma_u8s8(ca1, a0.w & M, a1.w & M, (a0.w >> 4) & M, (a1.w >> 4) & M, xa1.z, xa1.w);
+            mma_u8s8(cb1, b0.w & M, b1.w & M, (b0.w >> 4) & M, (b1.w >> 4) & M, xb1.z, xb1.w);
+            if (t == 0) {
+                {
+                    const float2 m = meta[grp_a];
+                    const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
+                    const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                    const float f0 = (float)((ca0[0] + ca1[0]) * 256 + ca0[1] + ca1[1]), f1 = (float)((ca0[2] + ca1[2]) * 256 + ca0[3] + ca1[3]);
+                    acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                    acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+                }
+                if (have_b) {
+                    const float2 m = meta[grp_b];
+                    const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
+                    const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                    const float f0 = (float)((cb0[0] + cb1[0]) * 256 + cb0[1] + cb1[1]), f1 = (float)((cb0[2] + cb1[2]) * 256 + cb0[3] + cb1[3]);
+                    acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                    acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+                }
+            }
+        };
+
+        // One projection: stage the activations, then walk this CTA's stages of the phase.
+        auto matvec_phase = [&](const MegaPhase &ph) {
+            const int G = ph.G;
+            if (ph.resid) {
+                float sq = mega_stage_x<true>(ph.x, ph.resid, ph.gamma, ph.awq, G, xq, meta);
+                sq = warp_sum(sq);
+                if (lane == 0) misc[8 + warp] = sq;
+                consumer_sync();
+                float tot = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kV2Consumers; w++) tot += misc[8 + w];
+                if (tid == 0) misc[0] = rsqrtf(tot / (float)(G * 128) + p.eps);  // reaches the producer through the slot release
+                if (blockIdx.x == 0 && ph.resid_out) {
+                    for (int k = tid; k < G * 128; k += kV2Consumers * 32)
+                        ph.resid_out[k] = __float2half_rn(__half2float(ph.x[k]) + __half2float(ph.resid[k]));
+                }
+            } else {
+                mega_stage_x<false>(ph.x, nullptr, nullptr, ph.awq, G, xq, meta);
+            }
+            consumer_sync();
+            const Range r = cta_range(ph.nblk, G);
+            StageIter it(r.t_begin, r.t_end, G);
+            int t0, n, rb, grp0;
+            while (it.next(t0, n, rb, grp0)) {
+                if (!dead && !mbar_wait_warp(&full[slot], par, p.err)) dead = true;
+                const unsigned char *st = ring + (size_t)slot * kStageBytes;
+                if (!dead && warp < n) {
+                    const int tb = warp + kV2Consumers;
+                    tile_pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n);
+                }
+                if (grp0 + n == G) {  // last stage of the row block: hand the partial sums to the producer warp
+                    float *buf = red + slot * kRedFloats;
+                    if (t == 0) {
+                        buf[warp * 16 + g] = acc0;
+                        buf[warp * 16 + g + 8] = acc1;
+                    }
+                    acc0 = acc1 = 0.0f;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+                if (++slot == nring) {
+                    slot = 0;
+                    par ^= 1;
+                }
+            }
+        };
+
+        const int seq_len = p.pos[0] + 1;
+        int chunk = (seq_len + p.splits - 1) / p.splits;
+        chunk = (chunk + kTile - 1) / kTile * kTile;
+        const int used = (seq_len + chunk - 1) / chunk;  // splits that hold positions (<= p.splits)
+
+        for (int l = 0; l < p.L; l++) {
+            const MegaLayer ly = p.layers[l];
+            // ---- QKV (layer 0: plain, on the normalised embedding; later layers: residual + norm prologue)
+            if (l > 0) grid_wait(7 * l - 1);
+            matvec_phase(p.phases[4 * l]);
+            grid_wait(7 * l);
+
+            // ---- (QK-norm,) RoPE, cache write, query rotation: one head per 128-thread group
+            {
+                PrepArgs a;
+                a.qkv = p.qkv; a.stride = p.q_dim + 2 * p.kv_dim; a.k_off = p.q_dim; a.v_off = p.q_dim + p.kv_dim;
+                a.qw = ly.q_norm; a.kw = ly.k_norm; a.cosc = p.cosc; a.sinc = p.sinc;
+                a.nh = p.nh; a.nkv = p.nkv; a.rotary_dim = p.rotary_dim; a.with_norm = p.with_qk_norm; a.T = 1; a.max_seq = p.max_seq;
+                a.base_pos = 0; a.eps = p.eps; a.pos_dev = p.pos; a.qrot = p.qrot; a.q_out = nullptr;
+                a.ktab = EncodeTables{p.signs, p.k_cb, p.k_bd, p.qjl_t, p.k_levels, 1};
+                a.vtab = EncodeTables{p.signs, p.v_cb, p.v_bd, p.qjl_t, p.v_levels, 0};
+                a.kc = ly.kc; a.vc = ly.vc; a.ks = ly.ks; a.vs = ly.vs; a.krn = ly.krn;
+                float *sh = reinterpret_cast<float *>(U) + group * (3 * kHd + 4);
+                if (!dead)
+                    for (int item = blockIdx.x + gridDim.x * group; item < p.nh + 2 * p.nkv; item += gridDim.x * kGroups)
+                        tq_prep_item(gs, a, sh, item, 0);
+            }
+            items_done(7 * l + 1);
+            grid_wait(7 * l + 1);
+
+            // ---- split attention: one (KV head, split) per group
+            {
+                AttnParams ap;
+                ap.q = nullptr; ap.kc = ly.kc; ap.vc = ly.vc; ap.ks = ly.ks; ap.vs = ly.vs; ap.krn = ly.krn;
+                ap.signs = p.signs; ap.qjl = p.qjl_t; ap.k_cb = p.k_cb; ap.v_cb = p.v_cb; ap.qrot = p.qrot;
+                ap.po = p.po; ap.pm = p.pm; ap.pl = p.pl; ap.attn_scale = p.attn_scale; ap.qjl_factor = p.qjl_factor;
+                ap.nh = p.nh; ap.nkv = p.nkv; ap.max_seq = p.max_seq; ap.base_pos = 0; ap.T = 1; ap.splits = p.splits; ap.pos_dev = p.pos;
+                AttnSmem<GQ> &sm = reinterpret_cast<AttnSmem<GQ> *>(U)[group];
+                if (!dead)
+                    for (int item = blockIdx.x + gridDim.x * group; item < p.nkv * used; item += gridDim.x * kGroups) {
+                        const int kvh = item % p.nkv, split = item / p.nkv;
+                        tq_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, 0, split, split * chunk, min(split * chunk + chunk, seq_len));
+                    }
+            }
+            items_done(7 * l + 2);
+            grid_wait(7 * l + 2);
+
+            // ---- combine the splits, rotate back: one query head per group
+            {
+                float *x = reinterpret_cast<float *>(U) + group * kHd;
+                if (!dead)
+                    for (int item = blockIdx.x + gridDim.x * group; item < p.nh; item += gridDim.x * kGroups)
+                        tq_reduce_item(gs, x, p.po, p.pm, p.pl, p.signs, p.attn_out, (size_t)item, p.splits, used);
+            }
+            items_done(7 * l + 3);
+            grid_wait(7 * l + 3);
+
+            matvec_phase(p.phases[4 * l + 1]);  // o
+            grid_wait(7 * l + 4);
+            matvec_phase(p.phases[4 * l + 2]);  // residual + norm -> gate/up + SiLU
+            grid_wait(7 * l + 5);
+            matvec_phase(p.phases[4 * l + 3]);  // down
+        }
+    }
+
+    // ---- exit: the last CTA to leave clears the counters for the next launch
+    __syncthreads();
+    if (tid == 0) {
+        const int nbar = 7 * p.L;
+        __threadfence();
+        if (atomicAdd(p.bar + nbar, 1u) == gridDim.x - 1) {
+            // every CTA has passed every barrier except possibly the very last one (down of the last layer),
+            // whose arrivals all precede the exits counted above
+            for (int i = 0; i <= nbar; i++) p.bar[i] = 0;
+            if (p.trace) p.trace[nbar + 1] = global_ns();
+        }
+    }
+}
+
+size_t mega_smem_bytes(int nring, int u_bytes) {
+    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + (128 + 256 + 32) * 4 + (size_t)u_bytes;
+}
+
+template <int GQ>
+static constexpr int attn_bytes() {
+    return kGroups * (int)sizeof(AttnSmem<GQ>);
+}
+
+int mega_u_bytes(int G_max, int gq) {
+    const int stage = ((G_max * 8 + 15) & ~15) + G_max * 2 * 32 * 4;
+    int attn = 0;
+    switch (gq) {
+        case 1: attn = attn_bytes<1>(); break;
+        case 2: attn = attn_bytes<2>(); break;
+        case 4: attn = attn_bytes<4>(); break;
+        case 8: attn = attn_bytes<8>(); break;
+        default: return -1;
+    }
+    const int prep = kGroups * (3 * kHd + 4) * 4;
+    int u = stage > attn ? stage : attn;
+    if (prep > u) u = prep;
+    return (u + 15) & ~15;
+}
+
+template <int GQ>
+static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st) {
+    const size_t smem = mega_smem_bytes(p.nring, p.u_bytes);
+    if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
+    auto kern = decode_token_kernel<GQ>;
+    static thread_local bool configured = false;
+    if (!configured) {
+        IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(dev->sm_count);
+    cfg.blockDim = dim3(kV2Threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // every CTA resident: the grid barriers need it
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    IM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, p));
+    return IM_OK;
+}
+
+int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st) {
+    if (p.nkv <= 0 || p.nh % p.nkv != 0) return IM_ERR_BOUNDS;
+    switch (p.nh / p.nkv) {
+        case 1: return mega_launch_t<1>(p, dev, st);
+        case 2: return mega_launch_t<2>(p, dev, st);
+        case 4: return mega_launch_t<4>(p, dev, st);
+        case 8: return mega_launch_t<8>(p, dev, st);
+        default: return IM_ERR_BOUNDS;
+    }
+}
+
+}  // namespace im

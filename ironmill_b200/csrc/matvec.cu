@@ -513,7 +513,7 @@ static int pick_ksplit(const Device *dev, int N, int K, int R, int chunk) {
 unsigned long long *g_v2_trace = nullptr;  // development aid, see im_cuda_debug_set_trace
 
 // Gate/up pair as one tile stream (8 gate rows + 8 up rows per tile), built the first time the pair is used.
-static int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaStream_t st) {
+int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaStream_t st) {
     AffineWeight *gate = const_cast<AffineWeight *>(gate_c);
     if (gate->pair_with == up && gate->pair_tiles) return IM_OK;
     dev_free(gate->dev, gate->pair_tiles, (size_t)gate->pair_nblk * gate->G * 1088);

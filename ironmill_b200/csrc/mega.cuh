@@ -1,0 +1,55 @@
+// Parameter blocks of the whole-token decode kernel (decode_mega.cu), filled by the engine (model.cu).
+#pragma once
+#include "common.cuh"
+
+namespace im {
+
+struct MegaPhase {         // one projection of the token; 4 per layer in execution order: qkv, o, gate/up, down
+    const uint8_t *tiles;  // [nblk][G] tiles of 1088 bytes (matvec_v2.cu)
+    const __half *awq;     // [K] activation scales or nullptr
+    const __half *x;       // input vector [K] (plain phases) or the branch output a of (a + residual) (norm phases)
+    const __half *resid;   // norm phases: residual b; nullptr = plain phase
+    const __half *gamma;   // norm phases: RMSNorm weight
+    __half *resid_out;     // norm phases: a + b rounded to fp16 (must not alias x / resid)
+    __half *y;             // outputs [N]
+    int nblk, G, N;
+    int gate_up;           // tile rows 0-7 gate, 8-15 up of the same 8 outputs -> SiLU(gate) * up
+};
+
+struct MegaLayer {
+    const __half *q_norm, *k_norm;  // QK-norm weights or nullptr
+    uint8_t *kc, *vc;               // this layer's TurboQuant caches [nkv, max_seq, 128]
+    float *ks, *vs, *krn;
+};
+
+struct MegaParams {
+    const MegaPhase *phases;  // device, 4 * L
+    const MegaLayer *layers;  // device, L
+    int L, nh, nkv, q_dim, kv_dim;
+    const int *pos;           // device: position of the token being decoded
+    const __half *qkv;        // the QKV phase's output buffer [q | k | v]
+    __half *attn_out;         // [nh * 128]
+    float *qrot;              // [nh, 2, 128]
+    float *po, *pm, *pl;      // split partials [nh, splits] x (128 | 1 | 1)
+    const __half *cosc, *sinc;
+    const float *signs, *qjl_t, *k_cb, *k_bd, *v_cb, *v_bd;
+    int k_levels, v_levels;
+    float eps, attn_scale, qjl_factor;
+    int max_seq, rotary_dim, with_qk_norm;
+    int splits;               // attention items per KV head (capacity of the partial buffers)
+    int nring;                // ring slots
+    int u_bytes;              // shared-memory scratch shared by the phases
+    int g_max;                // largest group count of any phase (sizes the activation staging area)
+    unsigned *bar;            // 7 * L arrival counters + 1 exit counter, zero between launches
+    int *err;
+    unsigned long long *trace;  // optional: CTA 0 stamps %globaltimer when it leaves each barrier (7L + 2 words)
+};
+
+// Shared-memory bytes the kernel needs for `nring` ring slots and `u_bytes` of phase scratch.
+size_t mega_smem_bytes(int nring, int u_bytes);
+// Phase scratch for projections of up to G_max groups and GQ query heads per KV head.
+int mega_u_bytes(int G_max, int gq);
+// Cooperative launch; IM_ERR_BOUNDS if the shapes do not fit the kernel.
+int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st);
+
+}  // namespace im

@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "mega.cuh"
 
 #if __has_include(<nccl.h>)
 #include <nccl.h>
@@ -124,6 +125,7 @@ struct Model {
     int *pos_dev = nullptr, *step_dev = nullptr;
     uint32_t *tokens_pin = nullptr;
     __half *logits_pin = nullptr;
+    int *err_pin = nullptr;  // the device's bounded-wait error word, copied back with every step
     cudaStream_t stream = nullptr;
     std::map<int, cudaGraphExec_t> graphs;
     int seq_pos = 0;
@@ -131,6 +133,10 @@ struct Model {
     size_t bytes = 0;
     int launches_per_step = 0;
     float *scratch_ref = nullptr;
+    // whole-token decode kernel (batch 1, single GPU): tables built by mega_prepare()
+    bool mega_ready = false;
+    MegaParams mega{};
+    int mega_mode = 1;  // 0: never use it (config / IM_MEGA=0)
 #if IM_HAVE_NCCL_H
     ncclComm_t comm = nullptr;
 #endif
@@ -333,7 +339,15 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
                                   c.embed_scale != 0.0f ? c.embed_scale : 1.0f, st));
     nl++;
     IM_MARK(kCatEmbed);
-    for (int l = 0; l < c.num_layers; l++) {
+    const bool mega = MT == 1 && m->mega_ready && !prof;
+    if (mega) {  // every layer in one persistent launch (decode_mega.cu); leaves the same buffers as the loop below
+        int rc = mega_launch(m->mega, m->dev, st);
+        if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "whole-token decode kernel: shapes do not fit");
+        IM_TRY(rc);
+        IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)H, st));
+        nl += 2;
+    }
+    for (int l = 0; l < c.num_layers && !mega; l++) {
         Layer &L = m->layers[l];
         if (l == 0) {
             IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.qkv), m->norm_out, m->qkv, MT, st));
@@ -398,6 +412,91 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
     return IM_OK;
 }
 
+// Tables of the whole-token decode kernel.  Used when one sequence decodes on one GPU and every projection
+// has the tiled INT4 layout; anything else keeps the launch-per-kernel schedule of forward().
+static int mega_prepare(Model *m) {
+    m->mega_ready = false;
+    const char *env = getenv("IM_MEGA");
+    if (m->mega_mode == 0 || (env && env[0] == '0')) return IM_OK;
+    const im_model_config &c = m->cfg;
+    if (m->world != 1 || c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
+    const int gq = m->nh_l / m->nkv_l;
+    if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return IM_OK;
+    int g_max = 0;
+    for (Layer &L : m->layers) {
+        for (AffineWeight *w : {L.qkv, L.o, L.gate, L.up, L.down}) {
+            if (!w || !w->tiles || w->bits != 4 || w->group_size != 128) return IM_OK;
+            if (w->G > g_max) g_max = w->G;
+        }
+        if (L.gate->N != L.up->N || L.gate->K != L.up->K) return IM_OK;
+        if ((L.gate->awq != nullptr) != (L.up->awq != nullptr)) return IM_OK;
+        IM_TRY(ensure_pair(L.gate, L.up, m->stream));
+    }
+    const int u_bytes = mega_u_bytes(g_max, gq);
+    if (u_bytes < 0) return IM_OK;
+    int nring = 8;
+    while (nring >= 3 && mega_smem_bytes(nring, u_bytes) + 1024 > m->dev->smem_optin) nring--;
+    if (nring < 3) return IM_OK;
+    const int L = c.num_layers;
+    std::vector<MegaPhase> ph((size_t)4 * L);
+    std::vector<MegaLayer> ml((size_t)L);
+    for (int l = 0; l < L; l++) {
+        Layer &Ly = m->layers[l];
+        MegaPhase q{}, o{}, gu{}, dn{};
+        q.tiles = Ly.qkv->tiles; q.awq = Ly.qkv->awq; q.nblk = Ly.qkv->nblk; q.G = Ly.qkv->G; q.N = Ly.qkv->N; q.y = m->qkv;
+        if (l == 0) {
+            q.x = m->norm_out;
+        } else {
+            q.x = m->residual; q.resid = m->ffn_down; q.gamma = Ly.input_ln; q.resid_out = m->hidden;
+        }
+        o.tiles = Ly.o->tiles; o.awq = Ly.o->awq; o.nblk = Ly.o->nblk; o.G = Ly.o->G; o.N = Ly.o->N; o.x = m->attn_out; o.y = m->ffn_down;
+        gu.tiles = Ly.gate->pair_tiles; gu.awq = Ly.gate->awq; gu.nblk = Ly.gate->pair_nblk; gu.G = Ly.gate->G; gu.N = Ly.gate->N;
+        gu.x = m->hidden; gu.resid = m->ffn_down; gu.gamma = Ly.post_ln; gu.resid_out = m->residual; gu.y = m->ffn_gate; gu.gate_up = 1;
+        dn.tiles = Ly.down->tiles; dn.awq = Ly.down->awq; dn.nblk = Ly.down->nblk; dn.G = Ly.down->G; dn.N = Ly.down->N;
+        dn.x = m->ffn_gate; dn.y = m->ffn_down;
+        ph[4 * l] = q; ph[4 * l + 1] = o; ph[4 * l + 2] = gu; ph[4 * l + 3] = dn;
+        ml[l] = MegaLayer{Ly.q_norm, Ly.k_norm, Ly.kc, Ly.vc, Ly.ks, Ly.vs, Ly.krn};
+    }
+    MegaParams &p = m->mega;
+    p = MegaParams{};
+    MegaPhase *dph = nullptr;
+    MegaLayer *dml = nullptr;
+    IM_TRY(m->alloc((void **)&dph, ph.size() * sizeof(MegaPhase)));
+    IM_TRY(m->alloc((void **)&dml, ml.size() * sizeof(MegaLayer)));
+    IM_CUDA_CHECK(cudaMemcpy(dph, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
+    IM_CUDA_CHECK(cudaMemcpy(dml, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+    p.phases = dph; p.layers = dml;
+    p.L = L; p.nh = m->nh_l; p.nkv = m->nkv_l; p.q_dim = m->q_dim; p.kv_dim = m->kv_dim;
+    p.pos = m->pos_dev; p.qkv = m->qkv; p.attn_out = m->attn_out; p.qrot = m->qrot;
+    p.splits = m->dev->sm_count * 4 / m->nkv_l;
+    if (p.splits < 1) p.splits = 1;
+    if (p.splits > 256) p.splits = 256;
+    const size_t rows = (size_t)m->nh_l * p.splits;
+    float *part = nullptr;
+    IM_TRY(m->alloc((void **)&part, rows * (128 + 2) * sizeof(float)));
+    p.po = part; p.pm = part + rows * 128; p.pl = p.pm + rows;
+    p.cosc = m->cosc; p.sinc = m->sinc;
+    const Tq *tq = reinterpret_cast<const Tq *>(m->tq);
+    p.signs = tq->signs; p.qjl_t = tq->qjl_t; p.k_cb = tq->k_cb; p.k_bd = tq->k_bd; p.v_cb = tq->v_cb; p.v_bd = tq->v_bd;
+    p.k_levels = tq->k_levels; p.v_levels = tq->v_levels;
+    p.eps = c.rms_eps;
+    p.attn_scale = c.attn_scale != 0.0f ? c.attn_scale : 1.0f / sqrtf((float)c.head_dim);
+    p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)c.head_dim;
+    p.max_seq = c.max_seq_len; p.rotary_dim = c.rotary_dim ? c.rotary_dim : c.head_dim; p.with_qk_norm = c.qk_norm ? 1 : 0;
+    p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max;
+    IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
+    IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
+    p.err = m->dev->err_flag;
+    const char *tr = getenv("IM_MEGA_TRACE");
+    if (tr && tr[0] == '1') {
+        IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2) * sizeof(unsigned long long)));
+        IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2) * sizeof(unsigned long long)));
+    }
+    IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
+    m->mega_ready = true;
+    return IM_OK;
+}
+
 static int decode_splits(const Model *m, int batch) {
     return tq_auto_splits(m->dev, batch, 1, m->nkv_l, m->cfg.max_seq_len);
 }
@@ -457,6 +556,18 @@ static void logits_to_host(const Model *m, const __half *pin, int nseq, float *o
             float *dst = out + (size_t)s * V + (size_t)p * vl;
             for (int j = 0; j < vl; j++) dst[j] = __half2float(src[j]);
         }
+}
+
+// A kernel whose bounded wait ran out leaves a non-zero word; the step's results are then invalid.  Clears the
+// word and the grid-barrier counters so that the next step starts clean.
+static int step_error_check(Model *m) {
+    if (*m->err_pin == 0) return IM_OK;
+    const int code = *m->err_pin;
+    *m->err_pin = 0;
+    cudaMemset(m->dev->err_flag, 0, sizeof(int));
+    cudaMemset(m->dev->sk_counters, 0, (size_t)kSkMaxBlocks * sizeof(int));
+    if (m->mega.bar) cudaMemset(m->mega.bar, 0, (size_t)(7 * m->cfg.num_layers + 1) * sizeof(unsigned));
+    return fail(IM_ERR_TIMEOUT, "a device-side bounded wait ran out (code %d); the results of this step are invalid", code);
 }
 
 }  // namespace im
@@ -563,6 +674,7 @@ IM_EXPORT void im_cuda_model_free(im_model *m) {
     for (auto &a : m->allocs) dev_free(m->dev, a.first, a.second);
     if (m->tokens_pin) cudaFreeHost(m->tokens_pin);
     if (m->logits_pin) cudaFreeHost(m->logits_pin);
+    if (m->err_pin) cudaFreeHost(m->err_pin);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
 }
@@ -731,6 +843,8 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_CUDA_CHECK(cudaMemset(m->step_dev, 0, 4));
     IM_CUDA_CHECK(cudaMallocHost((void **)&m->tokens_pin, MT * 4));
     IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_pin, (size_t)c.max_batch * c.vocab_size * 2));
+    IM_CUDA_CHECK(cudaMallocHost((void **)&m->err_pin, sizeof(int)));
+    *m->err_pin = 0;
     // attention scratch for the largest launch: decode at max_batch, or a prefill chunk
     size_t need = 0;
     for (int b = 1; b <= c.max_batch; b++) {
@@ -745,6 +859,7 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     m->scratch_ref = reinterpret_cast<Tq *>(m->tq)->scratch;
     m->bytes += need + reinterpret_cast<Tq *>(m->tq)->const_bytes;
     IM_CUDA_CHECK(cudaDeviceSynchronize());
+    IM_TRY(mega_prepare(m));
     m->finalized = true;
     return IM_OK;
     IM_GUARD_END
@@ -833,7 +948,9 @@ IM_EXPORT int im_cuda_model_decode_step(im_model *m, const uint32_t *tokens_host
     IM_CUDA_CHECK(cudaGraphLaunch(g, st));
     const __half *lg = m->world > 1 ? m->logits_all : m->logits;
     IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, (size_t)batch * m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, st));
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
     IM_CUDA_CHECK(cudaStreamSynchronize(st));
+    IM_TRY(step_error_check(m));
     m->seq_pos += 1;
     logits_to_host(m, m->logits_pin, batch, logits_out_host);
     return IM_OK;
@@ -869,12 +986,14 @@ IM_EXPORT int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tok
         }
     }
     cudaEventRecord(e1, st);
+    cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st);
     cudaError_t e = cudaStreamSynchronize(st);
     float ms = 0.0f;
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     if (e != cudaSuccess) return fail(IM_ERR_CUDA, "decode loop failed: %s", cudaGetErrorString(e));
+    IM_TRY(step_error_check(m));
     m->seq_pos += n_steps;
     if (elapsed_ms_out) *elapsed_ms_out = ms;
     if (tokens_out_host && n_steps > 0)

@@ -1,0 +1,423 @@
+// Device-side bodies of the TurboQuant kernels, written against a "scope": a set of threads with its own
+// barrier.  The stand-alone kernels run them with one CTA per work item (CtaScope); the whole-token decode
+// kernel runs four items side by side in one CTA, each on a 128-thread group with a named barrier (GroupScope).
+//   encode      crates/ironmill-inference/src/metal/shaders/turboquant/turboquant.metal:52-170
+//   attention   .../turboquant/turboquant.metal:202-462, .../attention/flash_decode.metal:163-215
+#pragma once
+#include "common.cuh"
+
+namespace im {
+
+struct CtaScope {  // the whole CTA; d = threadIdx.x, n = blockDim.x
+    int d, n;
+    __device__ __forceinline__ void sync() const { __syncthreads(); }
+};
+struct GroupScope {  // n consecutive threads (a multiple of 32) of a larger CTA sharing hardware barrier `bar`
+    int d, n, bar;
+    __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory"); }
+};
+
+constexpr int kTile = 32;          // positions per tile
+constexpr int kAttnThreads = 128;  // 4 warps; thread d owns output dim d (hd = 128)
+constexpr int kHd = 128;
+constexpr int kPitchB = 132;       // bytes per tile row: 33 words -> conflict-free 32-bit reads
+constexpr int kQPitch = 132;       // floats per query vector: +1 word per 32 -> conflict-free
+
+// In-place randomized Hadamard rotation of NV vectors of length hd held in shared memory
+// (x[v * pitch + d]); all threads of the scope must call it.  Plain float arithmetic.
+template <int NV, class Scope>
+__device__ __forceinline__ void hadamard_block(const Scope &sc, float *x, int pitch, const float *__restrict__ signs, int hd) {
+    for (int i = sc.d; i < NV * hd; i += sc.n) {
+        const int v = i / hd, d = i % hd;
+        x[v * pitch + d] *= signs[d];
+    }
+    sc.sync();
+    for (int step = 1; step < hd; step <<= 1) {
+        for (int i = sc.d; i < NV * (hd / 2); i += sc.n) {
+            const int v = i / (hd / 2), e = i % (hd / 2);
+            const int j = (e / step) * (2 * step) + (e % step);
+            float *p = x + v * pitch;
+            const float a = p[j], b = p[j + step];
+            p[j] = a + b;
+            p[j + step] = a - b;
+        }
+        sc.sync();
+    }
+    const float scale = 1.0f / sqrtf((float)hd);
+    for (int i = sc.d; i < NV * hd; i += sc.n) {
+        const int v = i / hd, d = i % hd;
+        x[v * pitch + d] *= signs[d] * scale;
+    }
+    sc.sync();
+}
+
+// ---------------------------------------------------------------- encode (bit-exact)
+struct EncodeTables {
+    const float *signs, *cb, *bounds, *qjl_t;  // bounds = suffix minima; qjl_t = transposed QJL matrix [k][d]
+    int n_levels, is_k;
+};
+
+// Encodes one head vector; thread d of the scope (n = hd threads) holds element d (already widened from
+// fp16).  sh = 3*hd floats.  Every operation and its order follow turboquant_cache_write; the QJL dot
+// product walks k upwards with separate multiply and add, reading the transposed matrix so that the
+// warp's loads coalesce.
+template <class Scope>
+__device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
+                                               float *scale_out, float *rnorm_out) {
+    float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
+    const int d = sc.d;
+    const float sg = tb.signs[d];
+    xs[d] = __fmul_rn(xin, sg);
+    sc.sync();
+    for (int step = 1; step < hd; step <<= 1) {
+        if (d < hd / 2) {
+            const int j = (d / step) * (2 * step) + (d % step);
+            const float a = xs[j], b = xs[j + step];
+            xs[j] = __fadd_rn(a, b);
+            xs[j + step] = __fsub_rn(a, b);
+        }
+        sc.sync();
+    }
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    const float x = __fmul_rn(xs[d], __fmul_rn(sg, scale));
+    red[d] = __fmul_rn(x, x);
+    sc.sync();
+    for (int s = hd / 2; s > 0; s >>= 1) {
+        if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
+        sc.sync();
+    }
+    const float norm = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+    if (d == 0) *scale_out = norm;
+    const float inv = __fdiv_rn(1.0f, fmaxf(norm, 1e-10f));
+    const float u = __fmul_rn(x, inv);
+    // The reference scans all boundaries and keeps the LAST b with u >= boundaries[b]
+    // (index b + 1).  Its 7- and 8-bit tables are not monotone, so that is not a plain
+    // upper bound; `bounds` holds the suffix minima of the table, which are monotone and
+    // give the same answer: max{b : boundaries[b] <= u} = max{b : min(boundaries[b..]) <= u}.
+    int lo = 0, hi = tb.n_levels - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (u >= tb.bounds[mid]) lo = mid + 1; else hi = mid;
+    }
+    unsigned byte = (unsigned)lo;
+    if (tb.is_k) {
+        const float r = __fsub_rn(u, tb.cb[lo]);
+        sc.sync();  // everyone has read red[0]
+        res[d] = r;
+        red[d] = __fmul_rn(r, r);
+        sc.sync();
+        for (int s = hd / 2; s > 0; s >>= 1) {
+            if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
+            sc.sync();
+        }
+        if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+        // Same sequential sum; the matrix column is fetched 64 values at a time so that the loads are in
+        // flight together instead of one memory latency per term.
+        float proj = 0.0f;
+        for (int k0 = 0; k0 < hd; k0 += 64) {
+            float sv[64];
+#pragma unroll
+            for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? tb.qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 64; j++)
+                if (k0 + j < hd) proj = __fadd_rn(proj, __fmul_rn(sv[j], res[k0 + j]));
+        }
+        if (proj >= 0.0f) byte |= 0x80u;
+    }
+    cache_row[d] = (uint8_t)byte;
+    sc.sync();  // sh may be reused by the caller
+}
+
+// ---------------------------------------------------------------- attention
+struct AttnParams {
+    const __half *q;         // [nseq*T, nh, hd]
+    const uint8_t *kc, *vc;  // [nseq, nkv, max_seq, hd]
+    const float *ks, *vs, *krn;  // [nseq, nkv, max_seq]
+    const float *signs, *qjl, *k_cb, *v_cb;  // qjl: TRANSPOSED matrix [k][d]
+    const float *qrot;       // optional [nseq*T, nh, 2, hd]: rotated query and S * rotated query, computed upstream
+    float *po, *pm, *pl;     // partials [nseq*T, nh, splits] x (hd | 1 | 1)
+    float attn_scale, qjl_factor;
+    int nh, nkv, max_seq, base_pos, T, splits;
+    const int *pos_dev;
+};
+
+__device__ __forceinline__ int qidx(int d) { return d + (d >> 5); }
+
+template <int GQ>
+struct AttnSmem {  // per work item (128 threads)
+    float qr[GQ * kQPitch];
+    float sq[GQ * kQPitch];
+    alignas(16) uint8_t tile[kTile * kPitchB];  // the K codes of a tile, then the V codes of the same positions
+    float t_ks[kTile], t_rw[kTile], t_vs[kTile];
+    float sc[GQ * kTile];
+    float s_m[GQ], s_l[GQ], s_corr[GQ];
+};
+
+// One (kv head, token, split) item on a 128-thread scope: positions [r0, r1) of the sequence against the GQ
+// query heads of the group.  cbk / cbv: the K (128) and V (256) codebooks in shared memory, filled by the caller.
+template <int GQ, class Scope>
+__device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> &sm, const float *cbk, const float *cbv, const AttnParams &p,
+                                                  int kvh, int st, int split, int r0, int r1) {
+    const int tid = sc.d, lane = tid & 31, warp = tid >> 5;
+    const int seq = st / p.T;
+    const int h0 = kvh * GQ;
+
+    if (r0 >= r1) {  // empty split: neutral partial
+        for (int g = 0; g < GQ; g++) {
+            const size_t pi = ((size_t)st * p.nh + h0 + g) * p.splits + split;
+            p.po[pi * kHd + tid] = 0.0f;
+            if (tid == 0) {
+                p.pm[pi] = -INFINITY;
+                p.pl[pi] = 0.0f;
+            }
+        }
+        return;
+    }
+
+    if (tid < GQ) {
+        sm.s_m[tid] = -INFINITY;
+        sm.s_l[tid] = 0.0f;
+    }
+    if (p.qrot) {
+#pragma unroll
+        for (int g = 0; g < GQ; g++) {
+            const float *src = p.qrot + ((size_t)st * p.nh + h0 + g) * 2 * kHd;
+            sm.qr[g * kQPitch + qidx(tid)] = src[tid];
+            sm.sq[g * kQPitch + qidx(tid)] = src[kHd + tid];
+        }
+    } else {
+#pragma unroll
+        for (int g = 0; g < GQ; g++) sm.qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
+        sc.sync();
+        hadamard_block<GQ>(sc, sm.qr, kQPitch, p.signs, kHd);
+        float acc[GQ];
+#pragma unroll
+        for (int g = 0; g < GQ; g++) acc[g] = 0.0f;
+        for (int k = 0; k < kHd; k++) {  // transposed matrix: the warp reads consecutive floats
+            const float sv = p.qjl[(size_t)k * kHd + tid];
+#pragma unroll
+            for (int g = 0; g < GQ; g++) acc[g] = fmaf(sv, sm.qr[g * kQPitch + k], acc[g]);
+        }
+        sc.sync();
+#pragma unroll
+        for (int g = 0; g < GQ; g++) sm.sq[g * kQPitch + qidx(tid)] = acc[g];
+        // move the rotated queries to the padded layout as well
+        float tmp[GQ];
+#pragma unroll
+        for (int g = 0; g < GQ; g++) tmp[g] = sm.qr[g * kQPitch + tid];
+        sc.sync();
+#pragma unroll
+        for (int g = 0; g < GQ; g++) sm.qr[g * kQPitch + qidx(tid)] = tmp[g];
+    }
+    sc.sync();
+
+    float o[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; g++) o[g] = 0.0f;
+
+    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const int pr = tid >> 2, part = tid & 3;  // loader: 32 rows x 128 bytes, 32 bytes per thread
+    uint32_t *td = reinterpret_cast<uint32_t *>(sm.tile + pr * kPitchB + part * 32);
+    for (int ts = r0; ts < r1; ts += kTile) {
+        const int nt = min(kTile, r1 - ts);
+        // ---- fetch the K and V rows; K goes to the tile buffer now, V waits in registers until the scores are done ----
+        uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
+        if (pr < nt) {
+            const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
+            const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
+            k0 = ldg_stream_v4(ksrc);
+            k1 = ldg_stream_v4(ksrc + 1);
+            v0 = ldg_stream_v4(vsrc);
+            v1 = ldg_stream_v4(vsrc + 1);
+        }
+        td[0] = k0.x; td[1] = k0.y; td[2] = k0.z; td[3] = k0.w; td[4] = k1.x; td[5] = k1.y; td[6] = k1.z; td[7] = k1.w;
+        if (tid < kTile) {
+            const bool ok = tid < nt;
+            sm.t_ks[tid] = ok ? p.ks[head_base + ts + tid] : 0.0f;
+            sm.t_rw[tid] = ok ? p.krn[head_base + ts + tid] * p.qjl_factor : 0.0f;
+            sm.t_vs[tid] = ok ? p.vs[head_base + ts + tid] : 0.0f;
+        }
+        sc.sync();
+
+        // ---- scores: warp w owns positions 8w..8w+7, 4 lanes per position (32 dims each) ----
+        {
+            const int pl = lane >> 2, dq = lane & 3, pp = warp * 8 + pl;
+            float a1[GQ], a2[GQ];
+#pragma unroll
+            for (int g = 0; g < GQ; g++) a1[g] = a2[g] = 0.0f;
+            const uint32_t *krow = reinterpret_cast<const uint32_t *>(sm.tile + pp * kPitchB + dq * 32);
+#pragma unroll
+            for (int jw = 0; jw < 8; jw++) {
+                const uint32_t w4 = krow[jw];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t b = (w4 >> (8 * e)) & 0xffu;
+                    const float kc = cbk[b & 0x7fu];
+                    const float sgn = (b & 0x80u) ? 1.0f : -1.0f;
+                    const int di = dq * 33 + jw * 4 + e;  // padded index of dim dq*32 + jw*4 + e
+#pragma unroll
+                    for (int g = 0; g < GQ; g++) {
+                        a1[g] = fmaf(sm.qr[g * kQPitch + di], kc, a1[g]);
+                        a2[g] = fmaf(sm.sq[g * kQPitch + di], sgn, a2[g]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < GQ; g++) {
+                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 1);
+                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 2);
+                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 1);
+                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 2);
+            }
+            if (dq == 0) {
+                const float ksv = sm.t_ks[pp], rw = sm.t_rw[pp];
+#pragma unroll
+                for (int g = 0; g < GQ; g++)
+                    sm.sc[g * kTile + pp] = pp < nt ? p.attn_scale * (ksv * (a1[g] + rw * a2[g])) : -INFINITY;
+            }
+        }
+        sc.sync();
+
+        // ---- the V codes replace the K codes; online softmax: one warp per query head, lane = position ----
+        td[0] = v0.x; td[1] = v0.y; td[2] = v0.z; td[3] = v0.w; td[4] = v1.x; td[5] = v1.y; td[6] = v1.z; td[7] = v1.w;
+        for (int g = warp; g < GQ; g += kAttnThreads / 32) {
+            const float s = sm.sc[g * kTile + lane];
+            const float tm = warp_max(s);
+            const float m_old = sm.s_m[g];
+            const float m_new = fmaxf(m_old, tm);
+            const float w = lane < nt ? __expf(s - m_new) : 0.0f;
+            const float tsum = warp_sum(w);
+            sm.sc[g * kTile + lane] = w * sm.t_vs[lane];
+            if (lane == 0) {
+                const float corr = __expf(m_old - m_new);
+                sm.s_corr[g] = corr;
+                sm.s_m[g] = m_new;
+                sm.s_l[g] = sm.s_l[g] * corr + tsum;
+            }
+        }
+        sc.sync();
+
+        // ---- weighted V: thread d accumulates output dim d for every head of the group ----
+#pragma unroll
+        for (int g = 0; g < GQ; g++) o[g] *= sm.s_corr[g];
+        for (int pp = 0; pp < nt; pp++) {
+            const float v = cbv[sm.tile[pp * kPitchB + tid]];
+#pragma unroll
+            for (int g = 0; g < GQ; g++) o[g] = fmaf(sm.sc[g * kTile + pp], v, o[g]);
+        }
+        sc.sync();
+    }
+
+#pragma unroll
+    for (int g = 0; g < GQ; g++) {
+        const size_t pi = ((size_t)st * p.nh + h0 + g) * p.splits + split;
+        p.po[pi * kHd + tid] = o[g];
+        if (tid == 0) {
+            p.pm[pi] = sm.s_m[g];
+            p.pl[pi] = sm.s_l[g];
+        }
+    }
+    sc.sync();  // sm may be reused by the caller's next item
+}
+
+// ---------------------------------------------------------------- (QK-norm +) RoPE + cache write + query rotation
+//   query heads : (RMSNorm,) RoPE as fused_qk_norm_rope / rope, rounded to fp16 like the reference's q buffer,
+//                 then the rotation R q and S (R q) that every attention item of the head would otherwise redo
+//   key heads   : (RMSNorm,) RoPE, rounded to fp16, then the bit-exact cache write
+//   value heads : the bit-exact cache write
+struct PrepArgs {
+    const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
+    int stride, k_off, v_off;
+    const __half *qw, *kw, *cosc, *sinc;
+    int nh, nkv, rotary_dim, with_norm, T, max_seq, base_pos;
+    float eps;
+    const int *pos_dev;
+    float *qrot;    // [nseq*T, nh, 2, hd]
+    __half *q_out;  // optional dense roped q [nseq*T, nh, hd]
+    EncodeTables ktab, vtab;
+    uint8_t *kc, *vc;
+    float *ks, *vs, *krn;
+};
+
+// One head (slot in [0, nh + 2 nkv)) of token st on a 128-thread scope.  sh: 3*128 + 4 floats.
+template <class Scope>
+__device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a, float *sh, int slot, int st) {
+    float *red = sh + 3 * kHd;
+    const int d = sc.d;
+    const int seq = st / a.T, t = st % a.T;
+    const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
+    const __half *tok = a.qkv + (size_t)st * a.stride;
+    if (slot >= a.nh + a.nkv) {  // value head
+        const int h = slot - a.nh - a.nkv;
+        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
+        tq_encode_body(sc, __half2float(tok[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, (float *)nullptr);
+        return;
+    }
+    const bool is_q = slot < a.nh;
+    const int h = is_q ? slot : slot - a.nh;
+    const __half *src = tok + (is_q ? 0 : a.k_off) + h * kHd;
+    const __half *w = is_q ? a.qw : a.kw;
+    float x = __half2float(src[d]);
+    if (a.with_norm) {
+        float ss = warp_sum(x * x);
+        if ((d & 31) == 0) red[d >> 5] = ss;
+        sc.sync();
+        const float tot = red[0] + red[1] + red[2] + red[3];
+        x = x * rsqrtf(tot / (float)kHd + a.eps) * __half2float(w[d]);
+    }
+    sh[d] = x;
+    sc.sync();
+    const int half_rot = a.rotary_dim / 2;
+    float y = x;
+    if (d < a.rotary_dim) {
+        const int i = d < half_rot ? d : d - half_rot;
+        const float lo = sh[i], hi = sh[i + half_rot];
+        const float c = __half2float(a.cosc[(size_t)pos_abs * (kHd / 2) + i]), sn = __half2float(a.sinc[(size_t)pos_abs * (kHd / 2) + i]);
+        y = d < half_rot ? lo * c - hi * sn : lo * sn + hi * c;
+    }
+    const __half yh = __float2half_rn(y);
+    sc.sync();
+    if (!is_q) {
+        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
+        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row);
+        return;
+    }
+    if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;
+    sh[d] = __half2float(yh);
+    sc.sync();
+    hadamard_block<1>(sc, sh, kHd, a.ktab.signs, kHd);
+    float acc = 0.0f;
+#pragma unroll 32
+    for (int k = 0; k < kHd; k++) acc = fmaf(a.ktab.qjl_t[(size_t)k * kHd + d], sh[k], acc);
+    float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
+    dst[d] = sh[d];
+    dst[kHd + d] = acc;
+    sc.sync();  // sh may be reused by the caller
+}
+
+// Combine the splits of one (token, head), normalise, rotate back, write fp16.
+// The inverse rotation is linear, so applying it once after the combination equals the
+// reference's per-split rotation up to float rounding.  x: 128 floats of shared memory.
+template <class Scope>
+__device__ __forceinline__ void tq_reduce_item(const Scope &sc, float *x, const float *__restrict__ po, const float *__restrict__ pm,
+                                               const float *__restrict__ pl, const float *__restrict__ signs, __half *__restrict__ out,
+                                               size_t head_index, int splits_stride, int splits_used) {
+    const int d = sc.d;
+    const size_t base = head_index * splits_stride;
+    float gm = -INFINITY;
+    for (int s = 0; s < splits_used; s++) gm = fmaxf(gm, pm[base + s]);
+    float acc = 0.0f, lsum = 0.0f;
+    for (int s = 0; s < splits_used; s++) {
+        const float m = pm[base + s];
+        const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
+        lsum += pl[base + s] * corr;
+        acc += po[(base + s) * kHd + d] * corr;
+    }
+    x[d] = acc / fmaxf(lsum, 1e-10f);
+    sc.sync();
+    hadamard_block<1>(sc, x, kHd, signs, kHd);
+    out[head_index * kHd + d] = __float2half_rn(x[d]);
+    sc.sync();
+}
+
+}  // namespace im

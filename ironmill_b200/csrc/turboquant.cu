@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "tq_device.cuh"
 
 namespace im {
 
@@ -94,109 +95,8 @@ static void lloyd_max(int dim, int bits, std::vector<float> &levels, std::vector
 }
 }  // namespace lm
 
-// ---------------------------------------------------------------- device helpers
-// In-place randomized Hadamard rotation of NV vectors of length hd held in shared memory
-// (x[v * pitch + d]); all threads of the CTA must call it.  Plain float arithmetic.
-template <int NV>
-__device__ __forceinline__ void hadamard_block(float *x, int pitch, const float *__restrict__ signs, int hd) {
-    for (int i = threadIdx.x; i < NV * hd; i += blockDim.x) {
-        const int v = i / hd, d = i % hd;
-        x[v * pitch + d] *= signs[d];
-    }
-    __syncthreads();
-    for (int step = 1; step < hd; step <<= 1) {
-        for (int i = threadIdx.x; i < NV * (hd / 2); i += blockDim.x) {
-            const int v = i / (hd / 2), e = i % (hd / 2);
-            const int j = (e / step) * (2 * step) + (e % step);
-            float *p = x + v * pitch;
-            const float a = p[j], b = p[j + step];
-            p[j] = a + b;
-            p[j + step] = a - b;
-        }
-        __syncthreads();
-    }
-    const float scale = 1.0f / sqrtf((float)hd);
-    for (int i = threadIdx.x; i < NV * hd; i += blockDim.x) {
-        const int v = i / hd, d = i % hd;
-        x[v * pitch + d] *= signs[d] * scale;
-    }
-    __syncthreads();
-}
-
-// ---------------------------------------------------------------- encode (bit-exact)
-struct EncodeTables {
-    const float *signs, *cb, *bounds, *qjl_t;  // bounds = suffix minima; qjl_t = transposed QJL matrix [k][d]
-    int n_levels, is_k;
-};
-
-// Encodes one head vector; thread d holds element d (already widened from fp16).  sh = 3*hd floats.
-// Every operation and its order follow turboquant_cache_write; the QJL dot product walks k upwards
-// with separate multiply and add, reading the transposed matrix so that the warp's loads coalesce.
-__device__ __forceinline__ void tq_encode_body(float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
-                                               float *scale_out, float *rnorm_out) {
-    float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
-    const int d = threadIdx.x;
-    const float sg = tb.signs[d];
-    xs[d] = __fmul_rn(xin, sg);
-    __syncthreads();
-    for (int step = 1; step < hd; step <<= 1) {
-        if (d < hd / 2) {
-            const int j = (d / step) * (2 * step) + (d % step);
-            const float a = xs[j], b = xs[j + step];
-            xs[j] = __fadd_rn(a, b);
-            xs[j + step] = __fsub_rn(a, b);
-        }
-        __syncthreads();
-    }
-    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-    const float x = __fmul_rn(xs[d], __fmul_rn(sg, scale));
-    red[d] = __fmul_rn(x, x);
-    __syncthreads();
-    for (int s = hd / 2; s > 0; s >>= 1) {
-        if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
-        __syncthreads();
-    }
-    const float norm = __fsqrt_rn(fmaxf(red[0], 1e-20f));
-    if (d == 0) *scale_out = norm;
-    const float inv = __fdiv_rn(1.0f, fmaxf(norm, 1e-10f));
-    const float u = __fmul_rn(x, inv);
-    // The reference scans all boundaries and keeps the LAST b with u >= boundaries[b]
-    // (index b + 1).  Its 7- and 8-bit tables are not monotone, so that is not a plain
-    // upper bound; `bounds` holds the suffix minima of the table, which are monotone and
-    // give the same answer: max{b : boundaries[b] <= u} = max{b : min(boundaries[b..]) <= u}.
-    int lo = 0, hi = tb.n_levels - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (u >= tb.bounds[mid]) lo = mid + 1; else hi = mid;
-    }
-    unsigned byte = (unsigned)lo;
-    if (tb.is_k) {
-        const float r = __fsub_rn(u, tb.cb[lo]);
-        __syncthreads();  // everyone has read red[0]
-        res[d] = r;
-        red[d] = __fmul_rn(r, r);
-        __syncthreads();
-        for (int s = hd / 2; s > 0; s >>= 1) {
-            if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
-            __syncthreads();
-        }
-        if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(red[0], 1e-20f));
-        // Same sequential sum; the matrix column is fetched 64 values at a time so that the loads are in
-        // flight together instead of one memory latency per term.
-        float proj = 0.0f;
-        for (int k0 = 0; k0 < hd; k0 += 64) {
-            float sv[64];
-#pragma unroll
-            for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? tb.qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
-#pragma unroll
-            for (int j = 0; j < 64; j++)
-                if (k0 + j < hd) proj = __fadd_rn(proj, __fmul_rn(sv[j], res[k0 + j]));
-        }
-        if (proj >= 0.0f) byte |= 0x80u;
-    }
-    cache_row[d] = (uint8_t)byte;
-    __syncthreads();  // sh may be reused by the caller
-}
+// ---------------------------------------------------------------- kernels: one CTA per work item
+// (the bodies live in tq_device.cuh, shared with the whole-token decode kernel)
 
 // grid (nkv, nseq*T), hd threads.
 __global__ void tq_encode_kernel(const __half *__restrict__ kv, const EncodeTables tb, uint8_t *__restrict__ cache,
@@ -207,44 +107,18 @@ __global__ void tq_encode_kernel(const __half *__restrict__ kv, const EncodeTabl
     const int seq = st / T, t = st % T;
     const int pos = (base_pos + (pos_dev ? pos_dev[seq] : 0) + t) % max_seq;
     const size_t row = ((size_t)seq * nkv + h) * max_seq + pos;
-    tq_encode_body(__half2float(kv[((size_t)st * nkv + h) * hd + d]), tb, sh, hd, cache + row * hd, scale_buf + row,
+    const CtaScope sc{d, (int)blockDim.x};
+    tq_encode_body(sc, __half2float(kv[((size_t)st * nkv + h) * hd + d]), tb, sh, hd, cache + row * hd, scale_buf + row,
                    r_norms ? r_norms + row : nullptr);
 }
 
-// ---------------------------------------------------------------- attention
-constexpr int kTile = 32;         // positions per tile
-constexpr int kAttnThreads = 128;  // 4 warps; thread d owns output dim d (hd = 128)
-constexpr int kHd = 128;
-constexpr int kPitchB = 132;      // bytes per tile row: 33 words -> conflict-free 32-bit reads
-constexpr int kQPitch = 132;      // floats per query vector: +1 word per 32 -> conflict-free
-
-struct AttnParams {
-    const __half *q;         // [nseq*T, nh, hd]
-    const uint8_t *kc, *vc;  // [nseq, nkv, max_seq, hd]
-    const float *ks, *vs, *krn;  // [nseq, nkv, max_seq]
-    const float *signs, *qjl, *k_cb, *v_cb;  // qjl: TRANSPOSED matrix [k][d]
-    const float *qrot;       // optional [nseq*T, nh, 2, hd]: rotated query and S * rotated query, computed upstream
-    float *po, *pm, *pl;     // partials [nseq*T, nh, splits] x (hd | 1 | 1)
-    float attn_scale, qjl_factor;
-    int nh, nkv, max_seq, base_pos, T, splits;
-    const int *pos_dev;
-};
-
-__device__ __forceinline__ int qidx(int d) { return d + (d >> 5); }
-
+// grid (nkv, nseq*T, splits), 128 threads.
 template <int GQ>
 __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnParams p) {
-    __shared__ float qr[GQ * kQPitch];
-    __shared__ float sq[GQ * kQPitch];
+    __shared__ AttnSmem<GQ> sm;
     __shared__ float cbk[128];
     __shared__ float cbv[256];
-    __shared__ __align__(16) uint8_t ktile[kTile * kPitchB];
-    __shared__ __align__(16) uint8_t vtile[kTile * kPitchB];
-    __shared__ float t_ks[kTile], t_rw[kTile], t_vs[kTile];
-    __shared__ float sc[GQ * kTile];
-    __shared__ float s_m[GQ], s_l[GQ], s_corr[GQ];
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int kvh = blockIdx.x, st = blockIdx.y, split = blockIdx.z;
     pdl_trigger();
     pdl_wait();
@@ -252,274 +126,34 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
     const int seq_len = p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1;
     const int chunk = (seq_len + p.splits - 1) / p.splits;
     const int r0 = split * chunk, r1 = min(r0 + chunk, seq_len);
-    const int h0 = kvh * GQ;
-
-    if (r0 >= r1) {  // empty split: neutral partial
-        for (int g = 0; g < GQ; g++) {
-            const size_t pi = ((size_t)st * p.nh + h0 + g) * p.splits + split;
-            p.po[pi * kHd + tid] = 0.0f;
-            if (tid == 0) {
-                p.pm[pi] = -INFINITY;
-                p.pl[pi] = 0.0f;
-            }
-        }
-        return;
-    }
-
-    // codebooks, rotated queries, S * q
     cbk[tid] = p.k_cb[tid];
     cbv[tid] = p.v_cb[tid];
     cbv[tid + 128] = p.v_cb[tid + 128];
-    if (tid < GQ) {
-        s_m[tid] = -INFINITY;
-        s_l[tid] = 0.0f;
-    }
-    if (p.qrot) {
-#pragma unroll
-        for (int g = 0; g < GQ; g++) {
-            const float *src = p.qrot + ((size_t)st * p.nh + h0 + g) * 2 * kHd;
-            qr[g * kQPitch + qidx(tid)] = src[tid];
-            sq[g * kQPitch + qidx(tid)] = src[kHd + tid];
-        }
-    } else {
-#pragma unroll
-        for (int g = 0; g < GQ; g++) qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
-        __syncthreads();
-        hadamard_block<GQ>(qr, kQPitch, p.signs, kHd);
-        float acc[GQ];
-#pragma unroll
-        for (int g = 0; g < GQ; g++) acc[g] = 0.0f;
-        for (int k = 0; k < kHd; k++) {  // transposed matrix: the warp reads consecutive floats
-            const float sv = p.qjl[(size_t)k * kHd + tid];
-#pragma unroll
-            for (int g = 0; g < GQ; g++) acc[g] = fmaf(sv, qr[g * kQPitch + k], acc[g]);
-        }
-        __syncthreads();
-#pragma unroll
-        for (int g = 0; g < GQ; g++) sq[g * kQPitch + qidx(tid)] = acc[g];
-        // move the rotated queries to the padded layout as well
-        float tmp[GQ];
-#pragma unroll
-        for (int g = 0; g < GQ; g++) tmp[g] = qr[g * kQPitch + tid];
-        __syncthreads();
-#pragma unroll
-        for (int g = 0; g < GQ; g++) qr[g * kQPitch + qidx(tid)] = tmp[g];
-    }
     __syncthreads();
-
-    float o[GQ];
-#pragma unroll
-    for (int g = 0; g < GQ; g++) o[g] = 0.0f;
-
-    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
-    for (int ts = r0; ts < r1; ts += kTile) {
-        const int nt = min(kTile, r1 - ts);
-        // ---- load K and V tiles: 32 rows x 128 bytes each, 32 bytes per thread ----
-        {
-            const int pr = tid >> 2, part = tid & 3;
-            uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
-            if (pr < nt) {
-                const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
-                const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
-                k0 = ldg_stream_v4(ksrc);
-                k1 = ldg_stream_v4(ksrc + 1);
-                v0 = ldg_stream_v4(vsrc);
-                v1 = ldg_stream_v4(vsrc + 1);
-            }
-            uint32_t *kd = reinterpret_cast<uint32_t *>(ktile + pr * kPitchB + part * 32);
-            uint32_t *vd = reinterpret_cast<uint32_t *>(vtile + pr * kPitchB + part * 32);
-            kd[0] = k0.x; kd[1] = k0.y; kd[2] = k0.z; kd[3] = k0.w; kd[4] = k1.x; kd[5] = k1.y; kd[6] = k1.z; kd[7] = k1.w;
-            vd[0] = v0.x; vd[1] = v0.y; vd[2] = v0.z; vd[3] = v0.w; vd[4] = v1.x; vd[5] = v1.y; vd[6] = v1.z; vd[7] = v1.w;
-            if (tid < kTile) {
-                const bool ok = tid < nt;
-                const float ksv = ok ? p.ks[head_base + ts + tid] : 0.0f;
-                t_ks[tid] = ksv;
-                t_rw[tid] = ok ? p.krn[head_base + ts + tid] * p.qjl_factor : 0.0f;
-                t_vs[tid] = ok ? p.vs[head_base + ts + tid] : 0.0f;
-            }
-        }
-        __syncthreads();
-
-        // ---- scores: warp w owns positions 8w..8w+7, 4 lanes per position (32 dims each) ----
-        {
-            const int pl = lane >> 2, dq = lane & 3, pp = warp * 8 + pl;
-            float a1[GQ], a2[GQ];
-#pragma unroll
-            for (int g = 0; g < GQ; g++) a1[g] = a2[g] = 0.0f;
-            const uint32_t *krow = reinterpret_cast<const uint32_t *>(ktile + pp * kPitchB + dq * 32);
-#pragma unroll
-            for (int jw = 0; jw < 8; jw++) {
-                const uint32_t w4 = krow[jw];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const uint32_t b = (w4 >> (8 * e)) & 0xffu;
-                    const float kc = cbk[b & 0x7fu];
-                    const float sgn = (b & 0x80u) ? 1.0f : -1.0f;
-                    const int di = dq * 33 + jw * 4 + e;  // padded index of dim dq*32 + jw*4 + e
-#pragma unroll
-                    for (int g = 0; g < GQ; g++) {
-                        a1[g] = fmaf(qr[g * kQPitch + di], kc, a1[g]);
-                        a2[g] = fmaf(sq[g * kQPitch + di], sgn, a2[g]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < GQ; g++) {
-                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 1);
-                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 2);
-                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 1);
-                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 2);
-            }
-            if (dq == 0) {
-                const float ksv = t_ks[pp], rw = t_rw[pp];
-#pragma unroll
-                for (int g = 0; g < GQ; g++)
-                    sc[g * kTile + pp] = pp < nt ? p.attn_scale * (ksv * (a1[g] + rw * a2[g])) : -INFINITY;
-            }
-        }
-        __syncthreads();
-
-        // ---- online softmax: one warp per query head, lane = position ----
-        for (int g = warp; g < GQ; g += kAttnThreads / 32) {
-            const float s = sc[g * kTile + lane];
-            const float tm = warp_max(s);
-            const float m_old = s_m[g];
-            const float m_new = fmaxf(m_old, tm);
-            const float w = lane < nt ? __expf(s - m_new) : 0.0f;
-            const float tsum = warp_sum(w);
-            sc[g * kTile + lane] = w * t_vs[lane];
-            if (lane == 0) {
-                const float corr = __expf(m_old - m_new);
-                s_corr[g] = corr;
-                s_m[g] = m_new;
-                s_l[g] = s_l[g] * corr + tsum;
-            }
-        }
-        __syncthreads();
-
-        // ---- weighted V: thread d accumulates output dim d for every head of the group ----
-#pragma unroll
-        for (int g = 0; g < GQ; g++) o[g] *= s_corr[g];
-        for (int pp = 0; pp < nt; pp++) {
-            const float v = cbv[vtile[pp * kPitchB + tid]];
-#pragma unroll
-            for (int g = 0; g < GQ; g++) o[g] = fmaf(sc[g * kTile + pp], v, o[g]);
-        }
-        __syncthreads();
-    }
-
-#pragma unroll
-    for (int g = 0; g < GQ; g++) {
-        const size_t pi = ((size_t)st * p.nh + h0 + g) * p.splits + split;
-        p.po[pi * kHd + tid] = o[g];
-        if (tid == 0) {
-            p.pm[pi] = s_m[g];
-            p.pl[pi] = s_l[g];
-        }
-    }
+    const CtaScope sc{tid, kAttnThreads};
+    tq_attention_item<GQ>(sc, sm, cbk, cbv, p, kvh, st, split, r0, r1);
 }
 
-// ---------------------------------------------------------------- fused (QK-norm +) RoPE + cache write + query rotation
 // One launch between the QKV projection and the attention: grid (nh + 2 nkv, nseq*T), hd = 128 threads.
-//   query heads : (RMSNorm,) RoPE as fused_qk_norm_rope / rope, rounded to fp16 like the reference's q buffer,
-//                 then the rotation R q and S (R q) that every attention CTA of the head would otherwise redo
-//   key heads   : (RMSNorm,) RoPE, rounded to fp16, then the bit-exact cache write
-//   value heads : the bit-exact cache write
-struct PrepArgs {
-    const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
-    int stride, k_off, v_off;
-    const __half *qw, *kw, *cosc, *sinc;
-    int nh, nkv, rotary_dim, with_norm, T, max_seq, base_pos;
-    float eps;
-    const int *pos_dev;
-    float *qrot;    // [nseq*T, nh, 2, hd]
-    __half *q_out;  // optional dense roped q [nseq*T, nh, hd]
-    EncodeTables ktab, vtab;
-    uint8_t *kc, *vc;
-    float *ks, *vs, *krn;
-};
-
 __global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a) {
-    __shared__ float sh[3 * kHd];
-    __shared__ float red[4];
-    const int d = threadIdx.x, slot = blockIdx.x, st = blockIdx.y;
+    __shared__ float sh[3 * kHd + 4];
     pdl_trigger();
     pdl_wait();
-    const int seq = st / a.T, t = st % a.T;
-    const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
-    const __half *tok = a.qkv + (size_t)st * a.stride;
-    if (slot >= a.nh + a.nkv) {  // value head
-        const int h = slot - a.nh - a.nkv;
-        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(__half2float(tok[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, nullptr);
-        return;
-    }
-    const bool is_q = slot < a.nh;
-    const int h = is_q ? slot : slot - a.nh;
-    const __half *src = tok + (is_q ? 0 : a.k_off) + h * kHd;
-    const __half *w = is_q ? a.qw : a.kw;
-    float x = __half2float(src[d]);
-    if (a.with_norm) {
-        float ss = warp_sum(x * x);
-        if ((d & 31) == 0) red[d >> 5] = ss;
-        __syncthreads();
-        const float tot = red[0] + red[1] + red[2] + red[3];
-        x = x * rsqrtf(tot / (float)kHd + a.eps) * __half2float(w[d]);
-    }
-    sh[d] = x;
-    __syncthreads();
-    const int half_rot = a.rotary_dim / 2;
-    float y = x;
-    if (d < a.rotary_dim) {
-        const int i = d < half_rot ? d : d - half_rot;
-        const float lo = sh[i], hi = sh[i + half_rot];
-        const float c = __half2float(a.cosc[(size_t)pos_abs * (kHd / 2) + i]), sn = __half2float(a.sinc[(size_t)pos_abs * (kHd / 2) + i]);
-        y = d < half_rot ? lo * c - hi * sn : lo * sn + hi * c;
-    }
-    const __half yh = __float2half_rn(y);
-    __syncthreads();
-    if (!is_q) {
-        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(__half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row);
-        return;
-    }
-    if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;
-    sh[d] = __half2float(yh);
-    __syncthreads();
-    hadamard_block<1>(sh, kHd, a.ktab.signs, kHd);
-    float acc = 0.0f;
-#pragma unroll 32
-    for (int k = 0; k < kHd; k++) acc = fmaf(a.ktab.qjl_t[(size_t)k * kHd + d], sh[k], acc);
-    float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
-    dst[d] = sh[d];
-    dst[kHd + d] = acc;
+    const CtaScope sc{(int)threadIdx.x, kHd};
+    tq_prep_item(sc, a, sh, blockIdx.x, blockIdx.y);
 }
 
-// Combine the splits of one (token, head), normalise, rotate back, write fp16.
-// The inverse rotation is linear, so applying it once after the combination equals the
-// reference's per-split rotation up to float rounding.  grid (nh, nseq*T), hd threads.
+// grid (nh, nseq*T), hd threads.
 __global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict__ po, const float *__restrict__ pm,
                                                         const float *__restrict__ pl, const float *__restrict__ signs,
                                                         __half *__restrict__ out, int nh, int splits) {
     __shared__ float x[kHd];
-    const int d = threadIdx.x;
     pdl_trigger();
     pdl_wait();
-    const size_t base = ((size_t)blockIdx.y * nh + blockIdx.x) * splits;
-    float gm = -INFINITY;
-    for (int s = 0; s < splits; s++) gm = fmaxf(gm, pm[base + s]);
-    float acc = 0.0f, lsum = 0.0f;
-    for (int s = 0; s < splits; s++) {
-        const float m = pm[base + s];
-        const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
-        lsum += pl[base + s] * corr;
-        acc += po[(base + s) * kHd + d] * corr;
-    }
-    x[d] = acc / fmaxf(lsum, 1e-10f);
-    __syncthreads();
-    hadamard_block<1>(x, kHd, signs, kHd);
-    out[((size_t)blockIdx.y * nh + blockIdx.x) * kHd + d] = __float2half_rn(x[d]);
+    const CtaScope sc{(int)threadIdx.x, kHd};
+    tq_reduce_item(sc, x, po, pm, pl, signs, out, (size_t)blockIdx.y * nh + blockIdx.x, splits, splits);
 }
+
 
 }  // namespace im
 

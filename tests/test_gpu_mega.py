@@ -1,0 +1,108 @@
+"""The whole-token decode kernel (one persistent launch for all layers of a batch-1 step) against the
+launch-per-kernel schedule of the same engine and against the CPU oracle model."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests import helpers as H
+from tests.oracle_model import DictProvider, OracleModel, synth_model
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def _cfg(L, Hd, I, nh, nkv, vocab, arch="llama", theta=5e5, eps=1e-5):
+    from ironmill_b200.bundle import ModelConfig
+    return ModelConfig(architecture=arch, hidden_size=Hd, intermediate_size=I, num_hidden_layers=L, num_attention_heads=nh,
+                       num_key_value_heads=nkv, head_dim=128, vocab_size=vocab, max_position_embeddings=8192, rms_norm_eps=eps,
+                       rope_theta=theta, tie_word_embeddings=False)
+
+
+def _engine(cfg, tensors, max_seq, mega, tqc):
+    from ironmill_b200.engine import CudaConfig, CudaInference
+    old = os.environ.get("IM_MEGA")
+    os.environ["IM_MEGA"] = "1" if mega else "0"
+    try:
+        eng = CudaInference(CudaConfig(max_seq_len=max_seq))
+        eng.load_weights(DictProvider(cfg, tensors), tq_signs=tqc.signs, tq_qjl=tqc.qjl)
+    finally:
+        if old is None:
+            os.environ.pop("IM_MEGA", None)
+        else:
+            os.environ["IM_MEGA"] = old
+    return eng
+
+
+def _both(cfg, tensors, max_seq, prompt_len, steps):
+    tqc = orc.TqConstants(128, 8, seed=42)
+    a, b = _engine(cfg, tensors, max_seq, True, tqc), _engine(cfg, tensors, max_seq, False, tqc)
+    prompt = H.rng_for("mega-prompt").integers(0, cfg.vocab_size, prompt_len).astype(np.uint32)
+    la, lb = a.prefill(prompt), b.prefill(prompt)
+    assert np.array_equal(la, lb)      # prefill runs the same kernels in both engines
+    errs, agree = [], []
+    tok = int(lb.argmax())
+    for _ in range(steps):
+        la, lb = a.decode_step(tok), b.decode_step(tok)
+        errs.append(float(np.abs(la - lb).max()))
+        agree.append(int(la.argmax() == lb.argmax()))
+        tok = int(lb.argmax())
+    return a, b, max(errs), float(np.mean(agree))
+
+
+def test_launch_counts_show_the_fused_schedule():
+    cfg = _cfg(2, 512, 1024, 8, 2, 500)
+    a, b, err, agree = _both(cfg, synth_model(cfg, seed=3, awq=True, gamma_jitter=0.1), 64, 5, 3)
+    assert a.step_launches() == 8          # embedding, all layers, residual add, final norm, lm_head, argmax, step, position
+    assert b.step_launches() > 8
+    assert err <= 2e-2 and agree == 1.0, (err, agree)
+
+
+def test_small_shapes_with_idle_ctas_and_qk_norm():
+    # 256-wide model: most CTAs own no row block of o / down / QKV; Qwen-style QK-norm, 2 query heads per KV head
+    cfg = _cfg(3, 256, 512, 4, 2, 1000, arch="qwen3", theta=1e6, eps=1e-6)
+    a, b, err, agree = _both(cfg, synth_model(cfg, seed=1, gamma_jitter=0.1), 64, 9, 20)
+    assert err <= 2e-2 and agree >= 0.95, (err, agree)
+
+
+def test_every_cta_busy_shapes():
+    # every projection has at least one row block per SM: the same work split as the stand-alone kernels
+    cfg = _cfg(2, 2560, 2560, 20, 5, 512)
+    a, b, err, agree = _both(cfg, synth_model(cfg, seed=5, awq=True, gamma_jitter=0.1), 48, 7, 8)
+    assert err <= 2e-2 and agree == 1.0, (err, agree)
+
+
+def test_long_context_uses_multi_tile_splits():
+    # 2400 cached positions: every (KV head, split) item walks more than one tile
+    cfg = _cfg(2, 512, 1024, 8, 2, 500)
+    a, b, err, agree = _both(cfg, synth_model(cfg, seed=7, awq=True), 2600, 2400, 6)
+    assert err <= 2e-2 and agree == 1.0, (err, agree)
+
+
+def test_against_the_oracle_model_and_greedy_loop():
+    cfg = _cfg(2, 512, 1024, 8, 2, 777)
+    tensors = synth_model(cfg, seed=2, awq=True, gamma_jitter=0.1)
+    tqc = orc.TqConstants(128, 8, seed=42)
+    eng = _engine(cfg, tensors, 96, True, tqc)
+    ref = OracleModel(cfg, tensors, tqc, 96)
+    prompt = H.rng_for("p2").integers(0, cfg.vocab_size, 11).astype(np.uint32)
+    lg, rl = eng.prefill(prompt), ref.forward(prompt)
+    tok = orc.argmax(rl)
+    errs, agree = [], []
+    for _ in range(16):
+        lg, rl = eng.decode_step(int(tok)), ref.forward([tok])
+        errs.append(float(np.abs(lg - rl).max()))
+        agree.append(int(orc.argmax(lg) == orc.argmax(rl)))
+        tok = orc.argmax(rl)
+    assert max(errs) <= 5e-2 and np.mean(agree) >= 0.99, (max(errs), np.mean(agree))
+    # the on-device greedy loop replays the same graph: its tokens are the arg-max of decode_step's logits
+    eng.truncate_to(11)
+    first = 5
+    toks, ms = eng.decode_greedy([first], 8)
+    eng.truncate_to(11)
+    t = first
+    for i in range(8):
+        t = int(orc.argmax(eng.decode_step(t)))
+        assert t == int(toks[i][0]), (i, t, toks[:, 0])
+    assert ms > 0
