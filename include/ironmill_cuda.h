@@ -318,6 +318,9 @@ size_t im_cuda_model_memory_bytes(const im_model *m);
 size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
 /* Number of kernel launches in one captured decode step. */
 int im_cuda_model_step_launches(const im_model *m);
+/* Development aid (no counterpart in the reference): timer stamps of the whole-token decode kernel, one per grid
+ * barrier, recorded when IM_MEGA_TRACE=1 was set in the environment at load time. IM_ERR_STATE otherwise. */
+int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, int n);
 /* Per-category GPU time of one eager decode step at the current position, which is not advanced
  * (MetalConfig.kernel_timing, crates/ironmill-inference/src/metal/pipeline.rs:353-422,1215-1234).
  * ms_by_category[11]: embed, qkv projection, rope, kv write, attention, o projection, residual+norm,

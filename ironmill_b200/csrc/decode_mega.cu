@@ -20,6 +20,10 @@
 #include "v2_device.cuh"
 #include "mega.cuh"
 
+#ifndef IM_MEGA_ITEM_INLINE
+#define IM_MEGA_ITEM_INLINE __forceinline__
+#endif
+
 namespace im {
 
 namespace {
@@ -77,9 +81,79 @@ __device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err) 
 
 // ---- activation staging for one batch row (the NB = 1 case of matvec_v2.cu's v2_stage_x) ------------------
 // xq words: index ((grp*2 + col)*4 + t)*8 + j*2 + eo, col 0 = high bytes, 1 = low bytes; meta[grp] = (scale, sum).
-template <bool NORM>
-__device__ __forceinline__ float mega_stage_x(const __half *__restrict__ x, const __half *__restrict__ b, const __half *__restrict__ gamma,
-                                              const __half *__restrict__ awq, int G, uint32_t *xq, float2 *meta) {
+// resid_out (NORM only): a + b rounded to fp16; each 8-element chunk is written by one CTA of the grid, from the
+// registers that hold it anyway.
+// One 8-element chunk of a group (16 lanes per group): quantise to 16 bits, write the fragment words and the group's
+// (scale, sum).  v: the 8 values after norm weight and activation scale.
+__device__ __forceinline__ void stage_chunk(float (&v)[8], bool live, int grp, int hl, uint32_t *xq, float2 *meta) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // 32639 = 127 * 256 + 127: both bytes of the split below stay inside a signed byte
+    const float sx = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f;
+    const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
+    int hi[8], lo[8], lsum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        int xi = __float2int_rn(v[i] * inv);
+        xi = max(-32639, min(32639, xi));
+        lsum += xi;
+        hi[i] = (xi + 128) >> 8;
+        lo[i] = xi - hi[i] * 256;
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (live) {
+        const int t = hl >> 2, j = hl & 3;
+        uint2 *dh = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 0) * 4 + t) * 4 + j) * 2);
+        uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 1) * 4 + t) * 4 + j) * 2);
+        *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
+        *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
+        if (hl == 0) meta[grp] = make_float2(sx, (float)lsum);
+    }
+}
+__device__ __forceinline__ void unpack2(unsigned w, float &a, float &b) {  // two fp16 values of a word, no address taken
+    a = __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+    b = __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+}
+__device__ __forceinline__ void unpack8(const uint4 raw, float (&v)[8]) {
+    unpack2(raw.x, v[0], v[1]);
+    unpack2(raw.y, v[2], v[3]);
+    unpack2(raw.z, v[4], v[5]);
+    unpack2(raw.w, v[6], v[7]);
+}
+
+// Plain projection input: x (/ awq).
+__device__ __forceinline__ void mega_stage_plain(const __half *__restrict__ x, const __half *__restrict__ awq, int G, uint32_t *xq,
+                                                 float2 *meta) {
+    const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
+#pragma unroll 2
+    for (int g0 = warp * 2; g0 < G; g0 += kV2Consumers * 2) {
+        const int grp = g0 + (lane >> 4);
+        const bool live = grp < G;
+        const int k = (live ? grp : g0) * 128 + hl * 8;
+        const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
+        uint4 ra = make_uint4(0, 0, 0, 0);
+        if (awq) ra = *reinterpret_cast<const uint4 *>(awq + k);
+        float v[8];
+        unpack8(raw, v);
+        if (awq) {
+            float a[8];
+            unpack8(ra, a);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = __fdividef(v[i], a[i]);  // x / s[k]; 2 ulp, far below the 16-bit rounding that follows
+        }
+        stage_chunk(v, live, grp, hl, xq, meta);
+    }
+}
+
+// Residual + RMSNorm input: r = x + b, staged value r * gamma (/ awq); returns this thread's share of sum r^2.
+// resid_out: r rounded to fp16; each 8-element chunk is written by one CTA of the grid, from registers.
+__device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, const __half *__restrict__ b, const __half *__restrict__ gamma,
+                                                 const __half *__restrict__ awq, __half *__restrict__ resid_out, int G, uint32_t *xq,
+                                                 float2 *meta) {
     const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
     float sq = 0.0f;
 #pragma unroll 2
@@ -87,68 +161,102 @@ __device__ __forceinline__ float mega_stage_x(const __half *__restrict__ x, cons
         const int grp = g0 + (lane >> 4);
         const bool live = grp < G;
         const int k = (live ? grp : g0) * 128 + hl * 8;
-        float v[8];
-        {
-            const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
-            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+        const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
+        const uint4 rb = *reinterpret_cast<const uint4 *>(b + k);
+        const uint4 rg = *reinterpret_cast<const uint4 *>(gamma + k);
+        uint4 ra = make_uint4(0, 0, 0, 0);
+        if (awq) ra = *reinterpret_cast<const uint4 *>(awq + k);
+        float v[8], fb[8], fg[8];
+        unpack8(raw, v);
+        unpack8(rb, fb);
+        unpack8(rg, fg);
+        unsigned hres[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 f = __half22float2(h[i]);
-                v[2 * i] = f.x;
-                v[2 * i + 1] = f.y;
-            }
+        for (int i = 0; i < 8; i += 2) {
+            const float r0 = v[i] + fb[i], r1 = v[i + 1] + fb[i + 1];
+            if (live) sq += r0 * r0 + r1 * r1;
+            v[i] = r0 * fg[i];
+            v[i + 1] = r1 * fg[i + 1];
+            hres[i >> 1] = (unsigned)__half_as_ushort(__float2half_rn(r0)) | ((unsigned)__half_as_ushort(__float2half_rn(r1)) << 16);
         }
-        if (NORM) {
-            const uint4 rb = *reinterpret_cast<const uint4 *>(b + k);
-            const uint4 rg = *reinterpret_cast<const uint4 *>(gamma + k);
-            const __half2 *hb = reinterpret_cast<const __half2 *>(&rb), *hg = reinterpret_cast<const __half2 *>(&rg);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 fb = __half22float2(hb[i]), fg = __half22float2(hg[i]);
-                const float r0 = v[2 * i] + fb.x, r1 = v[2 * i + 1] + fb.y;
-                if (live) sq += r0 * r0 + r1 * r1;
-                v[2 * i] = r0 * fg.x;
-                v[2 * i + 1] = r1 * fg.y;
-            }
-        }
+        if (live && resid_out && (unsigned)(grp * 16 + hl) % gridDim.x == blockIdx.x)
+            *reinterpret_cast<uint4 *>(resid_out + k) = make_uint4(hres[0], hres[1], hres[2], hres[3]);
         if (awq) {
-            const uint4 ra = *reinterpret_cast<const uint4 *>(awq + k);
-            const __half2 *ha = reinterpret_cast<const __half2 *>(&ra);
+            float a[8];
+            unpack8(ra, a);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 fa = __half22float2(ha[i]);
-                v[2 * i] = v[2 * i] / fa.x;
-                v[2 * i + 1] = v[2 * i + 1] / fa.y;
-            }
+            for (int i = 0; i < 8; i++) v[i] = __fdividef(v[i], a[i]);
         }
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float sx = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f;
-        const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
-        int hi[8], lo[8], lsum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            int xi = __float2int_rn(v[i] * inv);
-            xi = max(-32639, min(32639, xi));
-            lsum += xi;
-            hi[i] = (xi + 128) >> 8;
-            lo[i] = xi - hi[i] * 256;
-        }
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-        if (live) {
-            const int t = hl >> 2, j = hl & 3;
-            uint2 *dh = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 0) * 4 + t) * 4 + j) * 2);
-            uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 1) * 4 + t) * 4 + j) * 2);
-            *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
-            *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
-            if (hl == 0) meta[grp] = make_float2(sx, (float)lsum);
-        }
+        stage_chunk(v, live, grp, hl, xq, meta);
     }
     return sq;
+}
+
+// The item phases run out of line: they are cold next to the projection loop, and a call boundary keeps their
+// register appetite (the encoder holds 64 matrix values in flight) from spilling the loop's state.
+__device__ IM_MEGA_ITEM_INLINE void mega_prep_item(const GroupScope &gs, const PrepArgs &a, float *sh, int item) { tq_prep_item(gs, a, sh, item, 0); }
+
+template <int GQ>
+__device__ IM_MEGA_ITEM_INLINE void mega_attention_item(const GroupScope &gs, AttnSmem<GQ> &sm, const float *cbk, const float *cbv, const AttnParams &ap,
+                                                 int kvh, int split, int r0, int r1) {
+    tq_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, 0, split, r0, r1);
+}
+
+// Combine the splits of one query head and rotate back, by all 16 consumer warps: the four groups each combine a
+// quarter of the splits (their loads all in flight together), group 0 merges the four and applies the rotation.
+__device__ IM_MEGA_ITEM_INLINE void mega_reduce_head(const GroupScope &gs, int group, int tid, float *U, const float *__restrict__ po,
+                                              const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ signs,
+                                              __half *__restrict__ attn_out, int head, int splits, int used) {
+    float *sm_m = U, *sm_l = sm_m + 256;  // per split: running max, sum
+    float *part_ml = sm_l + 256;          // [4][2]
+    float *part = part_ml + 8;            // [4][128]
+    float *xs = part + kGroups * kHd;     // 128 floats for the rotation
+    const int d = tid & 127;
+    const size_t base = (size_t)head * splits;
+    for (int i = tid; i < used; i += kV2Consumers * 32) {
+        sm_m[i] = pm[base + i];
+        sm_l[i] = pl[base + i];
+    }
+    consumer_sync();
+    const int per = (used + kGroups - 1) / kGroups, s_lo = group * per, s_hi = min(used, s_lo + per);
+    float gmx = -INFINITY;
+    for (int s = s_lo; s < s_hi; s++) gmx = fmaxf(gmx, sm_m[s]);
+    float acc = 0.0f, lsum = 0.0f;
+    for (int s0 = s_lo; s0 < s_hi; s0 += 10) {
+        float o[10];
+#pragma unroll
+        for (int j = 0; j < 10; j++) o[j] = s0 + j < s_hi ? po[(base + s0 + j) * kHd + d] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 10; j++)
+            if (s0 + j < s_hi) {
+                const float m = sm_m[s0 + j];
+                const float corr = m == -INFINITY ? 0.0f : __expf(m - gmx);
+                lsum += sm_l[s0 + j] * corr;
+                acc += o[j] * corr;
+            }
+    }
+    part[group * kHd + d] = acc;
+    if (d == 0) {
+        part_ml[group * 2] = gmx;
+        part_ml[group * 2 + 1] = lsum;
+    }
+    consumer_sync();
+    if (group == 0) {
+        float gm = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kGroups; i++) gm = fmaxf(gm, part_ml[i * 2]);
+        float a = 0.0f, lt = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kGroups; i++) {
+            const float m = part_ml[i * 2];
+            const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
+            a += part[i * kHd + d] * corr;
+            lt += part_ml[i * 2 + 1] * corr;
+        }
+        const float r = hadamard_thread(gs, a / fmaxf(lt, 1e-10f), signs[d], xs, kHd);
+        attn_out[(size_t)head * kHd + d] = __float2half_rn(r);
+    }
+    consumer_sync();
 }
 
 }  // namespace
@@ -161,7 +269,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
     float *red = reinterpret_cast<float *>(ring + (size_t)nring * kStageBytes);
     float *cbk = red + (size_t)nring * kRedFloats;  // K codebook (128), V codebook (256)
     float *cbv = cbk + 128;
-    float *misc = cbv + 256;                         // [0] rms_inv, [8..23] reduction scratch, [30] wait result
+    float *bdk = cbv + 256;                          // suffix-minimum boundary tables of the encoder: K (127), V (255)
+    float *bdv = bdk + 128;
+    float *misc = bdv + 256;                         // [0] rms_inv, [8..23] reduction scratch, [30] wait result
     uint64_t *full = reinterpret_cast<uint64_t *>(misc + 32);
     uint64_t *empty = full + nring;
     unsigned char *U = reinterpret_cast<unsigned char *>(empty + nring);  // phase scratch (16-byte aligned by construction)
@@ -177,7 +287,10 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (p.trace && blockIdx.x == 0) p.trace[0] = global_ns();
     }
-    for (int i = tid; i < 128 + 256; i += kV2Threads) cbk[i] = i < 128 ? p.k_cb[i] : p.v_cb[i - 128];
+    for (int i = tid; i < 128 + 256; i += kV2Threads) {
+        cbk[i] = i < 128 ? p.k_cb[i] : p.v_cb[i - 128];
+        bdk[i] = i < 128 ? (i < p.k_levels - 1 ? p.k_bd[i] : INFINITY) : (i - 128 < p.v_levels - 1 ? p.v_bd[i - 128] : INFINITY);
+    }
     __syncthreads();
 
     if (warp == kV2Consumers) {
@@ -245,6 +358,24 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 skip_empty_done();
             }
         };
+        // A third cursor runs l2_ahead stages in front of the copies and asks L2 for those tiles: HBM then keeps
+        // streaming while the ring is full and the consumers are busy with attention or a barrier.
+        Cursor pf{0, StageIter(0, 0, 1), MegaPhase{}};
+        open(pf, 0);
+        auto prefetch_one = [&]() {
+            int pt0, pn, prb, pgrp;
+            while (pf.q < NP) {
+                if (!pf.it.next(pt0, pn, prb, pgrp)) {
+                    open(pf, pf.q + 1);
+                    continue;
+                }
+                if (lane == 1)
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ph.tiles + (size_t)pt0 * kTileBytes), "r"(pn * kTileBytes)
+                                 : "memory");
+                return;
+            }
+        };
+        for (int i = 0; i < p.l2_ahead; i++) prefetch_one();
         int slot = 0, phase = 0, nstages = 0;
         int t0, n, rb0, grp0;
         while (issue.q < NP) {
@@ -252,6 +383,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 open(issue, issue.q + 1);
                 continue;
             }
+            if (p.l2_ahead > 0) prefetch_one();
             if (nstages >= nring) reclaim(slot, phase ^ 1);
             if (lane == 0) {
                 mbar_expect_tx(&full[slot], (uint32_t)(n * kTileBytes));
@@ -296,61 +428,17 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         };
 
         const int g = lane >> 2, t = lane & 3;
-        float acc0 = 0.0f, acc1 = 0.0f;
-        auto tile_pair = [&](const unsigned char *tile_a, int grp_a, const unsigned char *tile_b, int grp_b, bool have_b) {
-            const uint4 a0 = *reinterpret_cast<const uint4 *>(tile_a + lane * 16);
-            const uint4 a1 = *reinterpret_cast<const uint4 *>(tile_a + 512 + lane * 16);
-            uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
-            if (have_b) {
-                b0 = *reinterpret_cast<const uint4 *>(tile_b + lane * 16);
-                b1 = *reinterpret_cast<const uint4 *>(tile_b + 512 + lane * 16);
-            }
-            uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
-            if (g < 2) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_a * 2 + g) * 4 + t) * 8);
-                xa0 = xp[0];
-                xa1 = xp[1];
-                if (have_b) {
-                    const uint4 *xr = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_b * 2 + g) * 4 + t) * 8);
-                    xb0 = xr[0];
-                    xb1 = xr[1];
-                }
-            }
-            int ca0[4] = {0, 0, 0, 0}, ca1[4] = {0, 0, 0, 0}, cb0[4] = {0, 0, 0, 0}, cb1[4] = {0, 0, 0, 0};
-            constexpr unsigned M = 0x0F0F0F0Fu;
-            mma_u8s8(ca0, a0.x & M, a1.x & M, (a0.x >> 4) & M, (a1.x >> 4) & M, xa0.x, xa0.y);
-            mma_u8s8(cb0, b0.x & M, b1.x & M, (b0.x >> 4) & M, (b1.x >> 4) & M, xb0.x, xb0.y);
-            mma_u8s8(ca1, a0.y & M, a1.y & M, (a0.y >> 4) & M, (a1.y >> 4) & M, xa0.z, xa0.w);
-            mma_u8s8(cb1, b0.y & M, b1.y & M, (b0.y >> 4) & M, (b1.y >> 4) & M, xb0.z, xb0.w);
-            mma_u8s8(ca0, a0.z & M, a1.z & M, (a0.z >> 4) & M, (a1.z >> 4) & M, xa1.x, xa1.y);
-            mma_u8s8(cb0, b0.z & M, b1.z & M, (b0.z >> 4) & M, (b1.z >> 4) & M, xb1.x, xb1.y);
-            mma_u8s8(ca1, a0.w & M, a1.w & M, (a0.w >> 4) & M, (a1.w >> 4) & M, xa1.z, xa1.w);
-            mma_u8s8(cb1, b0.w & M, b1.w & M, (b0.w >> 4) & M, (b1.w >> 4) & M, xb1.z, xb1.w);
-            if (t == 0) {
-                {
-                    const float2 m = meta[grp_a];
-                    const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
-                    const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                    const float f0 = (float)((ca0[0] + ca1[0]) * 256 + ca0[1] + ca1[1]), f1 = (float)((ca0[2] + ca1[2]) * 256 + ca0[3] + ca1[3]);
-                    acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                    acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-                }
-                if (have_b) {
-                    const float2 m = meta[grp_b];
-                    const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
-                    const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                    const float f0 = (float)((cb0[0] + cb1[0]) * 256 + cb0[1] + cb1[1]), f1 = (float)((cb0[2] + cb1[2]) * 256 + cb0[3] + cb1[3]);
-                    acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                    acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-                }
-            }
-        };
+        TileMath<1> tm;
+        tm.reset();
 
         // One projection: stage the activations, then walk this CTA's stages of the phase.
-        auto matvec_phase = [&](const MegaPhase &ph) {
+        auto matvec_phase = [&](int q, int fine) {  // fine >= 0: CTA 0 records 24 stamps at trace[fine..]
+            const MegaPhase ph = p.phases[q];
             const int G = ph.G;
+            const bool stamp = p.trace && fine >= 0 && blockIdx.x == 0 && tid == 0;
+            if (stamp) p.trace[fine] = global_ns();
             if (ph.resid) {
-                float sq = mega_stage_x<true>(ph.x, ph.resid, ph.gamma, ph.awq, G, xq, meta);
+                float sq = mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, xq, meta);
                 sq = warp_sum(sq);
                 if (lane == 0) misc[8 + warp] = sq;
                 consumer_sync();
@@ -358,31 +446,37 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 #pragma unroll
                 for (int w = 0; w < kV2Consumers; w++) tot += misc[8 + w];
                 if (tid == 0) misc[0] = rsqrtf(tot / (float)(G * 128) + p.eps);  // reaches the producer through the slot release
-                if (blockIdx.x == 0 && ph.resid_out) {
-                    for (int k = tid; k < G * 128; k += kV2Consumers * 32)
-                        ph.resid_out[k] = __float2half_rn(__half2float(ph.x[k]) + __half2float(ph.resid[k]));
-                }
             } else {
-                mega_stage_x<false>(ph.x, nullptr, nullptr, ph.awq, G, xq, meta);
+                mega_stage_plain(ph.x, ph.awq, G, xq, meta);
             }
             consumer_sync();
+            if (q + 1 < NP) {  // the next projection's activation scales and norm weight: one pass through a 4.9 GB weight
+                               // stream evicts them from L2 every token, so ask for them now, one 128-byte line per thread
+                const MegaPhase nx = p.phases[q + 1];
+                for (int i = blockIdx.x + gridDim.x * tid; i < 2 * nx.G; i += gridDim.x * kV2Consumers * 32) {
+                    if (nx.awq) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.awq + i * 64));
+                    if (nx.gamma) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.gamma + i * 64));
+                }
+            }
+            if (stamp) p.trace[fine + 1] = global_ns();
             const Range r = cta_range(ph.nblk, G);
             StageIter it(r.t_begin, r.t_end, G);
             int t0, n, rb, grp0;
+            tm.reset();
             while (it.next(t0, n, rb, grp0)) {
                 if (!dead && !mbar_wait_warp(&full[slot], par, p.err)) dead = true;
                 const unsigned char *st = ring + (size_t)slot * kStageBytes;
                 if (!dead && warp < n) {
                     const int tb = warp + kV2Consumers;
-                    tile_pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n);
+                    tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq, meta, lane);
                 }
                 if (grp0 + n == G) {  // last stage of the row block: hand the partial sums to the producer warp
                     float *buf = red + slot * kRedFloats;
                     if (t == 0) {
-                        buf[warp * 16 + g] = acc0;
-                        buf[warp * 16 + g + 8] = acc1;
+                        buf[warp * 16 + g] = tm.acc0;
+                        buf[warp * 16 + g + 8] = tm.acc1;
                     }
-                    acc0 = acc1 = 0.0f;
+                    tm.acc0 = tm.acc1 = 0.0f;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[slot]);
@@ -391,6 +485,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                     par ^= 1;
                 }
             }
+            if (stamp) p.trace[fine + 22] = global_ns();
         };
 
         const int seq_len = p.pos[0] + 1;
@@ -402,7 +497,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             const MegaLayer ly = p.layers[l];
             // ---- QKV (layer 0: plain, on the normalised embedding; later layers: residual + norm prologue)
             if (l > 0) grid_wait(7 * l - 1);
-            matvec_phase(p.phases[4 * l]);
+            matvec_phase(4 * l, l == 1 ? 7 * p.L + 2 : -1);
             grid_wait(7 * l);
 
             // ---- (QK-norm,) RoPE, cache write, query rotation: one head per 128-thread group
@@ -412,13 +507,13 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 a.qw = ly.q_norm; a.kw = ly.k_norm; a.cosc = p.cosc; a.sinc = p.sinc;
                 a.nh = p.nh; a.nkv = p.nkv; a.rotary_dim = p.rotary_dim; a.with_norm = p.with_qk_norm; a.T = 1; a.max_seq = p.max_seq;
                 a.base_pos = 0; a.eps = p.eps; a.pos_dev = p.pos; a.qrot = p.qrot; a.q_out = nullptr;
-                a.ktab = EncodeTables{p.signs, p.k_cb, p.k_bd, p.qjl_t, p.k_levels, 1};
-                a.vtab = EncodeTables{p.signs, p.v_cb, p.v_bd, p.qjl_t, p.v_levels, 0};
+                a.ktab = EncodeTables{p.signs, cbk, bdk, p.qjl_t, p.k_levels, 1};
+                a.vtab = EncodeTables{p.signs, cbv, bdv, p.qjl_t, p.v_levels, 0};
                 a.kc = ly.kc; a.vc = ly.vc; a.ks = ly.ks; a.vs = ly.vs; a.krn = ly.krn;
                 float *sh = reinterpret_cast<float *>(U) + group * (3 * kHd + 4);
                 if (!dead)
                     for (int item = blockIdx.x + gridDim.x * group; item < p.nh + 2 * p.nkv; item += gridDim.x * kGroups)
-                        tq_prep_item(gs, a, sh, item, 0);
+                        mega_prep_item(gs, a, sh, item);
             }
             items_done(7 * l + 1);
             grid_wait(7 * l + 1);
@@ -434,27 +529,25 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 if (!dead)
                     for (int item = blockIdx.x + gridDim.x * group; item < p.nkv * used; item += gridDim.x * kGroups) {
                         const int kvh = item % p.nkv, split = item / p.nkv;
-                        tq_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, 0, split, split * chunk, min(split * chunk + chunk, seq_len));
+                        mega_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, split, split * chunk, min(split * chunk + chunk, seq_len));
                     }
             }
             items_done(7 * l + 2);
             grid_wait(7 * l + 2);
 
-            // ---- combine the splits, rotate back: one query head per group
-            {
-                float *x = reinterpret_cast<float *>(U) + group * kHd;
-                if (!dead)
-                    for (int item = blockIdx.x + gridDim.x * group; item < p.nh; item += gridDim.x * kGroups)
-                        tq_reduce_item(gs, x, p.po, p.pm, p.pl, p.signs, p.attn_out, (size_t)item, p.splits, used);
-            }
+            // ---- combine the splits, rotate back: one query head per CTA.  The four groups each combine a quarter
+            // of the splits (their loads all in flight together), group 0 merges the four and rotates back.
+            if (!dead)
+                for (int head = blockIdx.x; head < p.nh; head += gridDim.x)
+                    mega_reduce_head(gs, group, tid, reinterpret_cast<float *>(U), p.po, p.pm, p.pl, p.signs, p.attn_out, head, p.splits, used);
             items_done(7 * l + 3);
             grid_wait(7 * l + 3);
 
-            matvec_phase(p.phases[4 * l + 1]);  // o
+            matvec_phase(4 * l + 1, l == 1 ? 7 * p.L + 2 + 24 : -1);  // o
             grid_wait(7 * l + 4);
-            matvec_phase(p.phases[4 * l + 2]);  // residual + norm -> gate/up + SiLU
+            matvec_phase(4 * l + 2, l == 1 ? 7 * p.L + 2 + 48 : -1);  // residual + norm -> gate/up + SiLU
             grid_wait(7 * l + 5);
-            matvec_phase(p.phases[4 * l + 3]);  // down
+            matvec_phase(4 * l + 3, l == 1 ? 7 * p.L + 2 + 72 : -1);  // down
         }
     }
 
@@ -473,7 +566,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 }
 
 size_t mega_smem_bytes(int nring, int u_bytes) {
-    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + (128 + 256 + 32) * 4 + (size_t)u_bytes;
+    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + (2 * (128 + 256) + 32) * 4 + (size_t)u_bytes;
 }
 
 template <int GQ>

@@ -277,82 +277,28 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     }
 
     const int g = lane >> 2, t = lane & 3;  // fragment coordinates: rows g and g+8, batch column pair t
-    float acc0 = 0.0f, acc1 = 0.0f;          // rows g, g+8 for batch t
     bool dead = false;
-
-    // Two tiles (16 rows x 128 columns each) against the staged activations, interleaved so that the shared
-    // loads, the unpacking and the tensor-core latencies of one overlap the other.
-    auto tile_pair = [&](const unsigned char *tile_a, int grp_a, const unsigned char *tile_b, int grp_b, bool have_b) {
-        const uint4 a0 = *reinterpret_cast<const uint4 *>(tile_a + lane * 16);        // row g
-        const uint4 a1 = *reinterpret_cast<const uint4 *>(tile_a + 512 + lane * 16);  // row g+8
-        uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
-        if (have_b) {
-            b0 = *reinterpret_cast<const uint4 *>(tile_b + lane * 16);
-            b1 = *reinterpret_cast<const uint4 *>(tile_b + 512 + lane * 16);
-        }
-        uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
-        if (g < 2 * NB) {
-            const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_a * 2 * NB + g) * 4 + t) * 8);
-            xa0 = xp[0];  // (even, odd) words of j = 0, 1
-            xa1 = xp[1];  // j = 2, 3
-            if (have_b) {
-                const uint4 *xr = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_b * 2 * NB + g) * 4 + t) * 8);
-                xb0 = xr[0];
-                xb1 = xr[1];
-            }
-        }
-        int ca0[4] = {0, 0, 0, 0}, ca1[4] = {0, 0, 0, 0}, cb0[4] = {0, 0, 0, 0}, cb1[4] = {0, 0, 0, 0};
-        constexpr unsigned M = 0x0F0F0F0Fu;
-        mma_u8s8(ca0, a0.x & M, a1.x & M, (a0.x >> 4) & M, (a1.x >> 4) & M, xa0.x, xa0.y);
-        mma_u8s8(cb0, b0.x & M, b1.x & M, (b0.x >> 4) & M, (b1.x >> 4) & M, xb0.x, xb0.y);
-        mma_u8s8(ca1, a0.y & M, a1.y & M, (a0.y >> 4) & M, (a1.y >> 4) & M, xa0.z, xa0.w);
-        mma_u8s8(cb1, b0.y & M, b1.y & M, (b0.y >> 4) & M, (b1.y >> 4) & M, xb0.z, xb0.w);
-        mma_u8s8(ca0, a0.z & M, a1.z & M, (a0.z >> 4) & M, (a1.z >> 4) & M, xa1.x, xa1.y);
-        mma_u8s8(cb0, b0.z & M, b1.z & M, (b0.z >> 4) & M, (b1.z >> 4) & M, xb1.x, xb1.y);
-        mma_u8s8(ca1, a0.w & M, a1.w & M, (a0.w >> 4) & M, (a1.w >> 4) & M, xa1.z, xa1.w);
-        mma_u8s8(cb1, b0.w & M, b1.w & M, (b0.w >> 4) & M, (b1.w >> 4) & M, xb1.z, xb1.w);
-        if (t < NB) {
-            {
-                const float2 m = meta[grp_a * NB + t];
-                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
-                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)((ca0[0] + ca1[0]) * 256 + ca0[1] + ca1[1]), f1 = (float)((ca0[2] + ca1[2]) * 256 + ca0[3] + ca1[3]);
-                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-            }
-            if (have_b) {
-                const float2 m = meta[grp_b * NB + t];
-                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
-                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)((cb0[0] + cb1[0]) * 256 + cb0[1] + cb1[1]), f1 = (float)((cb0[2] + cb1[2]) * 256 + cb0[3] + cb1[3]);
-                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-            }
-        }
-    };
+    TileMath<NB> tm;
+    tm.reset();
 
     // A warp whose wait ran out stops computing but keeps every barrier of the schedule, so that
     // the other warps and the producer still run to the end; the host sees the error word.
     StageIter it(t_begin, t_end, G);
     int t0, n, rb, grp0, slot = 0, phase = 0;
-    for (int i = 0; it.next(t0, n, rb, grp0); i++) {
-        if (i < 12) IM_STAMP(8 + 2 * i);
+    while (it.next(t0, n, rb, grp0)) {
         if (!dead && !mbar_wait_warp(&full[slot], phase, p.err)) dead = true;
-        if (i == 0) IM_STAMP(2);
-        if (i == 1) IM_STAMP(3);
-        if (i < 12) IM_STAMP(9 + 2 * i);
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
         if (!dead && warp < n) {
             const int tb = warp + kV2Consumers;
-            tile_pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n);
+            tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq, meta, lane);
         }
         if (grp0 + n == G || t0 + n == t_end) {  // last stage of this row block inside the CTA's range:
             float *buf = red + slot * (kV2Consumers * 64);  // hand the partial sums to the producer warp
             if (t < NB) {
-                buf[warp * 64 + g * 4 + t] = acc0;
-                buf[warp * 64 + (g + 8) * 4 + t] = acc1;
+                buf[warp * 64 + g * 4 + t] = tm.acc0;
+                buf[warp * 64 + (g + 8) * 4 + t] = tm.acc1;
             }
-            acc0 = acc1 = 0.0f;
+            tm.acc0 = tm.acc1 = 0.0f;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);

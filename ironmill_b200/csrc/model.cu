@@ -484,13 +484,19 @@ static int mega_prepare(Model *m) {
     p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)c.head_dim;
     p.max_seq = c.max_seq_len; p.rotary_dim = c.rotary_dim ? c.rotary_dim : c.head_dim; p.with_qk_norm = c.qk_norm ? 1 : 0;
     p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max;
+    {
+        const char *la = getenv("IM_MEGA_L2AHEAD");
+        p.l2_ahead = la ? atoi(la) : 0;  // measured: asking L2 ahead of the copies slows the stream down; off unless set
+        if (p.l2_ahead < 0) p.l2_ahead = 0;
+        if (p.l2_ahead > 64) p.l2_ahead = 64;
+    }
     IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;
     const char *tr = getenv("IM_MEGA_TRACE");
     if (tr && tr[0] == '1') {
-        IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2) * sizeof(unsigned long long)));
-        IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2) * sizeof(unsigned long long)));
+        IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
+        IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
     }
     IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
     m->mega_ready = true;
@@ -887,6 +893,19 @@ IM_EXPORT int im_cuda_model_truncate(im_model *m, int pos) {
 IM_EXPORT int im_cuda_model_seq_pos(const im_model *m) { return m ? m->seq_pos : 0; }
 IM_EXPORT int im_cuda_model_max_seq_len(const im_model *m) { return m ? m->cfg.max_seq_len : 0; }
 IM_EXPORT size_t im_cuda_model_memory_bytes(const im_model *m) { return m ? m->bytes : 0; }
+// Development aid: with IM_MEGA_TRACE=1 in the environment at load time, CTA 0 of the whole-token kernel stamps the
+// nanosecond timer at its start [0], when it leaves grid barrier k [k + 1] and at exit [7L + 1]; this copies the stamps.
+IM_EXPORT int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, int n) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && out && n >= 0, "bad argument");
+    if (!m->mega.trace) return fail(IM_ERR_STATE, "tracing is off (IM_MEGA_TRACE=1 at load time turns it on)");
+    const int have = 7 * m->cfg.num_layers + 2 + 96;  // + 4 x 24 stamps inside the projections of layer 1
+    IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
+    IM_CUDA_CHECK(cudaMemcpy(out, m->mega.trace, (size_t)(n < have ? n : have) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return IM_OK;
+    IM_GUARD_END
+}
+
 IM_EXPORT int im_cuda_model_step_launches(const im_model *m) { return m ? m->launches_per_step : 0; }
 
 IM_EXPORT size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch) {

@@ -51,6 +51,27 @@ __device__ __forceinline__ void hadamard_block(const Scope &sc, float *x, int pi
     sc.sync();
 }
 
+// The same rotation for ONE vector with thread d of the scope holding element d (scope size = hd >= 32): strides
+// below 32 on warp shuffles, the rest through xs (hd floats).  Same pairs and operations as hadamard_block.
+template <class Scope>
+__device__ __forceinline__ float hadamard_thread(const Scope &sc, float v, float sg, float *xs, int hd) {
+    const int d = sc.d;
+    v *= sg;
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, step);
+        v = (d & step) ? o - v : v + o;
+    }
+    for (int step = 32; step < hd; step <<= 1) {
+        xs[d] = v;
+        sc.sync();
+        const float o = xs[d ^ step];
+        v = (d & step) ? o - v : v + o;
+        sc.sync();
+    }
+    return v * (sg * (1.0f / sqrtf((float)hd)));
+}
+
 // ---------------------------------------------------------------- encode (bit-exact)
 struct EncodeTables {
     const float *signs, *cb, *bounds, *qjl_t;  // bounds = suffix minima; qjl_t = transposed QJL matrix [k][d]
@@ -61,32 +82,66 @@ struct EncodeTables {
 // fp16).  sh = 3*hd floats.  Every operation and its order follow turboquant_cache_write; the QJL dot
 // product walks k upwards with separate multiply and add, reading the transposed matrix so that the
 // warp's loads coalesce.
+// Sum of the scope's hd values in the order of the reference's shared-memory tree (stride hd/2, hd/4, ... 1:
+// r[d] += r[d + s] for d < s), with the strides below 32 done by warp shuffles: lane d < s adds the value of lane
+// d + s, which is exactly r[d + s] of the tree.  buf: hd floats; every thread gets the total.  hd >= 32.
+template <class Scope>
+__device__ __forceinline__ float tq_tree_sum(const Scope &sc, float v, float *buf, int hd) {
+    const int d = sc.d;
+    buf[d] = v;
+    sc.sync();
+    const int l = d & 31;
+    // strides >= 32 straight from shared memory, in the tree's order: width w -> w/2 ... until 32 values remain
+    // r_w[j] = r_2w[j] + r_2w[j + w]; evaluated recursively for j = lane
+    float r;
+    if (hd == 128) {
+        r = __fadd_rn(__fadd_rn(buf[l], buf[l + 64]), __fadd_rn(buf[l + 32], buf[l + 96]));
+    } else {
+        // generic: fold the top halves down one stride at a time (every warp repeats the same reads)
+        for (int s = hd / 2; s >= 32; s >>= 1) {
+            float t = 0.0f;
+            if (d < s) t = __fadd_rn(buf[d], buf[d + s]);
+            sc.sync();
+            if (d < s) buf[d] = t;
+            sc.sync();
+        }
+        r = buf[l];
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) r = __fadd_rn(r, __shfl_down_sync(0xffffffffu, r, s));
+    r = __shfl_sync(0xffffffffu, r, 0);
+    sc.sync();  // buf may be rewritten by the caller
+    return r;
+}
+
+// Encodes one head vector; thread d of the scope (n = hd threads) holds element d (already widened from
+// fp16).  sh = 3*hd floats.  Every operation follows turboquant_cache_write: the same butterfly pairs with the
+// same add / subtract, the same summation trees, the QJL dot product walking k upwards with separate multiply and
+// add (reading the transposed matrix so that the warp's loads coalesce).  Butterfly strides below 32 and the
+// tails of the trees run on warp shuffles instead of shared memory + barriers; the operands are the same.
 template <class Scope>
 __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
                                                float *scale_out, float *rnorm_out) {
     float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
     const int d = sc.d;
     const float sg = tb.signs[d];
-    xs[d] = __fmul_rn(xin, sg);
-    sc.sync();
-    for (int step = 1; step < hd; step <<= 1) {
-        if (d < hd / 2) {
-            const int j = (d / step) * (2 * step) + (d % step);
-            const float a = xs[j], b = xs[j + step];
-            xs[j] = __fadd_rn(a, b);
-            xs[j + step] = __fsub_rn(a, b);
-        }
+    float v = __fmul_rn(xin, sg);
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) {  // pair (j, j + step): lower index gets a + b, upper a - b
+        const float o = __shfl_xor_sync(0xffffffffu, v, step);
+        v = (d & step) ? __fsub_rn(o, v) : __fadd_rn(v, o);
+    }
+    for (int step = 32; step < hd; step <<= 1) {
+        xs[d] = v;
+        sc.sync();
+        const float o = xs[d ^ step];
+        v = (d & step) ? __fsub_rn(o, v) : __fadd_rn(v, o);
         sc.sync();
     }
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-    const float x = __fmul_rn(xs[d], __fmul_rn(sg, scale));
-    red[d] = __fmul_rn(x, x);
-    sc.sync();
-    for (int s = hd / 2; s > 0; s >>= 1) {
-        if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
-        sc.sync();
-    }
-    const float norm = __fsqrt_rn(fmaxf(red[0], 1e-20f));
+    const float x = __fmul_rn(v, __fmul_rn(sg, scale));
+    const float ss = tq_tree_sum(sc, __fmul_rn(x, x), red, hd);
+    const float norm = __fsqrt_rn(fmaxf(ss, 1e-20f));
     if (d == 0) *scale_out = norm;
     const float inv = __fdiv_rn(1.0f, fmaxf(norm, 1e-10f));
     const float u = __fmul_rn(x, inv);
@@ -102,22 +157,19 @@ __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const
     unsigned byte = (unsigned)lo;
     if (tb.is_k) {
         const float r = __fsub_rn(u, tb.cb[lo]);
-        sc.sync();  // everyone has read red[0]
         res[d] = r;
-        red[d] = __fmul_rn(r, r);
-        sc.sync();
-        for (int s = hd / 2; s > 0; s >>= 1) {
-            if (d < s) red[d] = __fadd_rn(red[d], red[d + s]);
-            sc.sync();
-        }
-        if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(red[0], 1e-20f));
-        // Same sequential sum; the matrix column is fetched 64 values at a time so that the loads are in
-        // flight together instead of one memory latency per term.
+        // first half of this thread's matrix column: in flight while the residual norm is reduced
+        float sv[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) sv[j] = j < hd ? tb.qjl_t[(size_t)j * hd + d] : 0.0f;
+        const float rs = tq_tree_sum(sc, __fmul_rn(r, r), red, hd);  // its barriers also publish res[]
+        if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(rs, 1e-20f));
         float proj = 0.0f;
         for (int k0 = 0; k0 < hd; k0 += 64) {
-            float sv[64];
+            if (k0 > 0) {
 #pragma unroll
-            for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? tb.qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
+                for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? tb.qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
+            }
 #pragma unroll
             for (int j = 0; j < 64; j++)
                 if (k0 + j < hd) proj = __fadd_rn(proj, __fmul_rn(sv[j], res[k0 + j]));
@@ -142,11 +194,15 @@ struct AttnParams {
 };
 
 __device__ __forceinline__ int qidx(int d) { return d + (d >> 5); }
+template <int GQ>
+__device__ __forceinline__ int qrow(int d) { return d * 2 * GQ + (d >> 5) * 4; }  // first float of dimension d's row in AttnSmem::qv
 
 template <int GQ>
 struct AttnSmem {  // per work item (128 threads)
-    float qr[GQ * kQPitch];
-    float sq[GQ * kQPitch];
+    // queries, one row of 2 GQ floats per dimension: the GQ rotated queries, then the GQ values of S * q, so that the
+    // score loop fetches all of a dimension's operands with one or two vector loads; 4 floats of padding after
+    // every 32 rows keep the four dimension blocks a warp reads at once on different banks
+    float qv[2 * GQ * kHd + 16];
     alignas(16) uint8_t tile[kTile * kPitchB];  // the K codes of a tile, then the V codes of the same positions
     float t_ks[kTile], t_rw[kTile], t_vs[kTile];
     float sc[GQ * kTile];
@@ -174,6 +230,32 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         return;
     }
 
+    // The K / V rows of a tile travel through registers: the first tile is requested before the queries are set
+    // up, each further tile while its predecessor is being scored, so the cache latency overlaps other work.
+    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const int pr = tid >> 2, part = tid & 3;  // loader: 32 rows x 128 bytes, 32 bytes per thread
+    uint4 nk0, nk1, nv0, nv1;
+    float n_ks = 0.0f, n_rw = 0.0f, n_vs = 0.0f;
+    auto fetch = [&](int ts) {
+        const int nt = min(kTile, r1 - ts);
+        nk0 = nk1 = nv0 = nv1 = make_uint4(0, 0, 0, 0);
+        if (pr < nt) {
+            const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
+            const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
+            nk0 = ldg_stream_v4(ksrc);
+            nk1 = ldg_stream_v4(ksrc + 1);
+            nv0 = ldg_stream_v4(vsrc);
+            nv1 = ldg_stream_v4(vsrc + 1);
+        }
+        if (tid < kTile) {
+            const bool ok = tid < nt;
+            n_ks = ok ? p.ks[head_base + ts + tid] : 0.0f;
+            n_rw = ok ? p.krn[head_base + ts + tid] * p.qjl_factor : 0.0f;
+            n_vs = ok ? p.vs[head_base + ts + tid] : 0.0f;
+        }
+    };
+    fetch(r0);
+
     if (tid < GQ) {
         sm.s_m[tid] = -INFINITY;
         sm.s_l[tid] = 0.0f;
@@ -182,32 +264,31 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 #pragma unroll
         for (int g = 0; g < GQ; g++) {
             const float *src = p.qrot + ((size_t)st * p.nh + h0 + g) * 2 * kHd;
-            sm.qr[g * kQPitch + qidx(tid)] = src[tid];
-            sm.sq[g * kQPitch + qidx(tid)] = src[kHd + tid];
+            sm.qv[qrow<GQ>(tid) + g] = src[tid];
+            sm.qv[qrow<GQ>(tid) + GQ + g] = src[kHd + tid];
         }
     } else {
+        float *qr = sm.qv;  // scratch in the old one-vector-per-head layout, converted below
 #pragma unroll
-        for (int g = 0; g < GQ; g++) sm.qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
+        for (int g = 0; g < GQ; g++) qr[g * kQPitch + tid] = __half2float(p.q[((size_t)st * p.nh + h0 + g) * kHd + tid]);
         sc.sync();
-        hadamard_block<GQ>(sc, sm.qr, kQPitch, p.signs, kHd);
-        float acc[GQ];
+        hadamard_block<GQ>(sc, qr, kQPitch, p.signs, kHd);
+        float acc[GQ], tmp[GQ];
 #pragma unroll
         for (int g = 0; g < GQ; g++) acc[g] = 0.0f;
         for (int k = 0; k < kHd; k++) {  // transposed matrix: the warp reads consecutive floats
             const float sv = p.qjl[(size_t)k * kHd + tid];
 #pragma unroll
-            for (int g = 0; g < GQ; g++) acc[g] = fmaf(sv, sm.qr[g * kQPitch + k], acc[g]);
+            for (int g = 0; g < GQ; g++) acc[g] = fmaf(sv, qr[g * kQPitch + k], acc[g]);
         }
+#pragma unroll
+        for (int g = 0; g < GQ; g++) tmp[g] = qr[g * kQPitch + tid];
         sc.sync();
 #pragma unroll
-        for (int g = 0; g < GQ; g++) sm.sq[g * kQPitch + qidx(tid)] = acc[g];
-        // move the rotated queries to the padded layout as well
-        float tmp[GQ];
-#pragma unroll
-        for (int g = 0; g < GQ; g++) tmp[g] = sm.qr[g * kQPitch + tid];
-        sc.sync();
-#pragma unroll
-        for (int g = 0; g < GQ; g++) sm.qr[g * kQPitch + qidx(tid)] = tmp[g];
+        for (int g = 0; g < GQ; g++) {
+            sm.qv[qrow<GQ>(tid) + g] = tmp[g];
+            sm.qv[qrow<GQ>(tid) + GQ + g] = acc[g];
+        }
     }
     sc.sync();
 
@@ -215,28 +296,18 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 #pragma unroll
     for (int g = 0; g < GQ; g++) o[g] = 0.0f;
 
-    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
-    const int pr = tid >> 2, part = tid & 3;  // loader: 32 rows x 128 bytes, 32 bytes per thread
     uint32_t *td = reinterpret_cast<uint32_t *>(sm.tile + pr * kPitchB + part * 32);
     for (int ts = r0; ts < r1; ts += kTile) {
         const int nt = min(kTile, r1 - ts);
-        // ---- fetch the K and V rows; K goes to the tile buffer now, V waits in registers until the scores are done ----
-        uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
-        if (pr < nt) {
-            const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
-            const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
-            k0 = ldg_stream_v4(ksrc);
-            k1 = ldg_stream_v4(ksrc + 1);
-            v0 = ldg_stream_v4(vsrc);
-            v1 = ldg_stream_v4(vsrc + 1);
-        }
-        td[0] = k0.x; td[1] = k0.y; td[2] = k0.z; td[3] = k0.w; td[4] = k1.x; td[5] = k1.y; td[6] = k1.z; td[7] = k1.w;
+        // ---- K goes to the tile buffer now, V waits in registers until the scores are done ----
+        const uint4 v0 = nv0, v1 = nv1;
+        td[0] = nk0.x; td[1] = nk0.y; td[2] = nk0.z; td[3] = nk0.w; td[4] = nk1.x; td[5] = nk1.y; td[6] = nk1.z; td[7] = nk1.w;
         if (tid < kTile) {
-            const bool ok = tid < nt;
-            sm.t_ks[tid] = ok ? p.ks[head_base + ts + tid] : 0.0f;
-            sm.t_rw[tid] = ok ? p.krn[head_base + ts + tid] * p.qjl_factor : 0.0f;
-            sm.t_vs[tid] = ok ? p.vs[head_base + ts + tid] : 0.0f;
+            sm.t_ks[tid] = n_ks;
+            sm.t_rw[tid] = n_rw;
+            sm.t_vs[tid] = n_vs;
         }
+        if (ts + kTile < r1) fetch(ts + kTile);
         sc.sync();
 
         // ---- scores: warp w owns positions 8w..8w+7, 4 lanes per position (32 dims each) ----
@@ -254,11 +325,24 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
                     const uint32_t b = (w4 >> (8 * e)) & 0xffu;
                     const float kc = cbk[b & 0x7fu];
                     const float sgn = (b & 0x80u) ? 1.0f : -1.0f;
-                    const int di = dq * 33 + jw * 4 + e;  // padded index of dim dq*32 + jw*4 + e
+                    float qd[2 * GQ];  // this dimension's row: vector loads (the row is 8 GQ bytes, 8-byte aligned at least)
+                    {
+                        const float *row = sm.qv + (dq * 32 + jw * 4 + e) * 2 * GQ + dq * 4;
+                        if (GQ == 1) {
+                            const float2 v = *reinterpret_cast<const float2 *>(row);
+                            qd[0] = v.x; qd[1] = v.y;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 2 * GQ; i += 4) {
+                                const float4 v = *reinterpret_cast<const float4 *>(row + i);
+                                qd[i] = v.x; qd[i + 1] = v.y; qd[i + 2] = v.z; qd[i + 3] = v.w;
+                            }
+                        }
+                    }
 #pragma unroll
                     for (int g = 0; g < GQ; g++) {
-                        a1[g] = fmaf(sm.qr[g * kQPitch + di], kc, a1[g]);
-                        a2[g] = fmaf(sm.sq[g * kQPitch + di], sgn, a2[g]);
+                        a1[g] = fmaf(qd[g], kc, a1[g]);
+                        a2[g] = fmaf(qd[GQ + g], sgn, a2[g]);
                     }
                 }
             }
@@ -273,7 +357,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
                 const float ksv = sm.t_ks[pp], rw = sm.t_rw[pp];
 #pragma unroll
                 for (int g = 0; g < GQ; g++)
-                    sm.sc[g * kTile + pp] = pp < nt ? p.attn_scale * (ksv * (a1[g] + rw * a2[g])) : -INFINITY;
+                    sm.sc[pp * GQ + g] = pp < nt ? p.attn_scale * (ksv * (a1[g] + rw * a2[g])) : -INFINITY;
             }
         }
         sc.sync();
@@ -281,13 +365,13 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         // ---- the V codes replace the K codes; online softmax: one warp per query head, lane = position ----
         td[0] = v0.x; td[1] = v0.y; td[2] = v0.z; td[3] = v0.w; td[4] = v1.x; td[5] = v1.y; td[6] = v1.z; td[7] = v1.w;
         for (int g = warp; g < GQ; g += kAttnThreads / 32) {
-            const float s = sm.sc[g * kTile + lane];
+            const float s = sm.sc[lane * GQ + g];
             const float tm = warp_max(s);
             const float m_old = sm.s_m[g];
             const float m_new = fmaxf(m_old, tm);
             const float w = lane < nt ? __expf(s - m_new) : 0.0f;
             const float tsum = warp_sum(w);
-            sm.sc[g * kTile + lane] = w * sm.t_vs[lane];
+            sm.sc[lane * GQ + g] = w * sm.t_vs[lane];
             if (lane == 0) {
                 const float corr = __expf(m_old - m_new);
                 sm.s_corr[g] = corr;
@@ -303,7 +387,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         for (int pp = 0; pp < nt; pp++) {
             const float v = cbv[sm.tile[pp * kPitchB + tid]];
 #pragma unroll
-            for (int g = 0; g < GQ; g++) o[g] = fmaf(sm.sc[g * kTile + pp], v, o[g]);
+            for (int g = 0; g < GQ; g++) o[g] = fmaf(sm.sc[pp * GQ + g], v, o[g]);
         }
         sc.sync();
     }
@@ -383,14 +467,19 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
         return;
     }
     if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;
-    sh[d] = __half2float(yh);
-    sc.sync();
-    hadamard_block<1>(sc, sh, kHd, a.ktab.signs, kHd);
-    float acc = 0.0f;
-#pragma unroll 32
-    for (int k = 0; k < kHd; k++) acc = fmaf(a.ktab.qjl_t[(size_t)k * kHd + d], sh[k], acc);
+    const float rq = hadamard_thread(sc, __half2float(yh), a.ktab.signs[d], sh + kHd, kHd);
+    sh[d] = rq;
     float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
-    dst[d] = sh[d];
+    dst[d] = rq;
+    sc.sync();
+    float acc = 0.0f;
+    for (int k0 = 0; k0 < kHd; k0 += 64) {  // 64 loads of the matrix column in flight at a time
+        float sv[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) sv[j] = a.ktab.qjl_t[(size_t)(k0 + j) * kHd + d];
+#pragma unroll
+        for (int j = 0; j < 64; j++) acc = fmaf(sv[j], sh[k0 + j], acc);
+    }
     dst[kHd + d] = acc;
     sc.sync();  // sh may be reused by the caller
 }
@@ -404,20 +493,34 @@ __device__ __forceinline__ void tq_reduce_item(const Scope &sc, float *x, const 
                                                size_t head_index, int splits_stride, int splits_used) {
     const int d = sc.d;
     const size_t base = head_index * splits_stride;
+    const float sg = signs[d];
     float gm = -INFINITY;
-    for (int s = 0; s < splits_used; s++) gm = fmaxf(gm, pm[base + s]);
-    float acc = 0.0f, lsum = 0.0f;
-    for (int s = 0; s < splits_used; s++) {
-        const float m = pm[base + s];
-        const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
-        lsum += pl[base + s] * corr;
-        acc += po[(base + s) * kHd + d] * corr;
+    for (int s0 = 0; s0 < splits_used; s0 += 8) {  // eight loads in flight at a time; combined in split order
+        float m[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) m[j] = s0 + j < splits_used ? pm[base + s0 + j] : -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; j++) gm = fmaxf(gm, m[j]);
     }
-    x[d] = acc / fmaxf(lsum, 1e-10f);
-    sc.sync();
-    hadamard_block<1>(sc, x, kHd, signs, kHd);
-    out[head_index * kHd + d] = __float2half_rn(x[d]);
-    sc.sync();
+    float acc = 0.0f, lsum = 0.0f;
+    for (int s0 = 0; s0 < splits_used; s0 += 8) {
+        float m[8], l[8], o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool live = s0 + j < splits_used;
+            m[j] = live ? pm[base + s0 + j] : -INFINITY;
+            l[j] = live ? pl[base + s0 + j] : 0.0f;
+            o[j] = live ? po[(base + s0 + j) * kHd + d] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float corr = m[j] == -INFINITY ? 0.0f : __expf(m[j] - gm);
+            lsum += l[j] * corr;
+            acc += o[j] * corr;
+        }
+    }
+    const float r = hadamard_thread(sc, acc / fmaxf(lsum, 1e-10f), sg, x, kHd);
+    out[head_index * kHd + d] = __float2half_rn(r);
 }
 
 }  // namespace im

@@ -64,6 +64,88 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, 
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// First product of an accumulator: C = 0 comes from the zero register, no moves to clear it.
+__device__ __forceinline__ void mma_u8s8_z(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// The arithmetic of the consumer warps: two tiles (16 rows x 128 columns of 4-bit codes each) against the staged
+// activations of their groups, then the per-(row, group) float fix-up  s * sx * (sum_k xi_k q_k - z * sum_k xi_k).
+// Lane (g = lane >> 2, t = lane & 3) holds rows g and g + 8 of batch row t in acc0 / acc1.
+// The activation fragments of a group stay in registers until the warp is handed another group: with K = 4096 a
+// stage is a whole row block, every warp sees the same two groups stage after stage, and the fragments are read
+// from shared memory once per projection.
+template <int NB>
+struct TileMath {
+    uint4 xa0, xa1, xb0, xb1;  // B fragments of the groups ga / gb (words of columns 2b = high bytes, 2b + 1 = low bytes)
+    int ga, gb;
+    float acc0, acc1;
+    __device__ __forceinline__ void reset() {  // new activations were staged
+        ga = gb = -1;
+        acc0 = acc1 = 0.0f;
+        xa0 = xa1 = xb0 = xb1 = make_uint4(0, 0, 0, 0);
+    }
+    // xq words: index ((grp*2NB + col)*4 + t)*8 ..; meta[grp*NB + b] = (scale, sum of the 128 integers)
+    __device__ __forceinline__ void pair(const unsigned char *tile_a, int grp_a, const unsigned char *tile_b, int grp_b, bool have_b,
+                                         const uint32_t *xq, const float2 *meta, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint4 a0 = *reinterpret_cast<const uint4 *>(tile_a + lane * 16);        // row g
+        const uint4 a1 = *reinterpret_cast<const uint4 *>(tile_a + 512 + lane * 16);  // row g + 8
+        uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
+        if (have_b) {
+            b0 = *reinterpret_cast<const uint4 *>(tile_b + lane * 16);
+            b1 = *reinterpret_cast<const uint4 *>(tile_b + 512 + lane * 16);
+        }
+        if (grp_a != ga) {  // warp-uniform
+            ga = grp_a;
+            if (g < 2 * NB) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_a * 2 * NB + g) * 4 + t) * 8);
+                xa0 = xp[0];
+                xa1 = xp[1];
+            }
+        }
+        if (have_b && grp_b != gb) {
+            gb = grp_b;
+            if (g < 2 * NB) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_b * 2 * NB + g) * 4 + t) * 8);
+                xb0 = xp[0];
+                xb1 = xp[1];
+            }
+        }
+        // two independent accumulator chains per tile: the second product of a chain does not wait for four others
+        int ca0[4], ca1[4], cb0[4], cb1[4];
+        constexpr unsigned M = 0x0F0F0F0Fu;
+        mma_u8s8_z(ca0, a0.x & M, a1.x & M, (a0.x >> 4) & M, (a1.x >> 4) & M, xa0.x, xa0.y);
+        mma_u8s8_z(cb0, b0.x & M, b1.x & M, (b0.x >> 4) & M, (b1.x >> 4) & M, xb0.x, xb0.y);
+        mma_u8s8_z(ca1, a0.y & M, a1.y & M, (a0.y >> 4) & M, (a1.y >> 4) & M, xa0.z, xa0.w);
+        mma_u8s8_z(cb1, b0.y & M, b1.y & M, (b0.y >> 4) & M, (b1.y >> 4) & M, xb0.z, xb0.w);
+        mma_u8s8(ca0, a0.z & M, a1.z & M, (a0.z >> 4) & M, (a1.z >> 4) & M, xa1.x, xa1.y);
+        mma_u8s8(cb0, b0.z & M, b1.z & M, (b0.z >> 4) & M, (b1.z >> 4) & M, xb1.x, xb1.y);
+        mma_u8s8(ca1, a0.w & M, a1.w & M, (a0.w >> 4) & M, (a1.w >> 4) & M, xa1.z, xa1.w);
+        mma_u8s8(cb1, b0.w & M, b1.w & M, (b0.w >> 4) & M, (b1.w >> 4) & M, xb1.z, xb1.w);
+        if (t < NB) {
+            {
+                const float2 m = meta[grp_a * NB + t];
+                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
+                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                const float f0 = (float)((ca0[0] + ca1[0]) * 256 + ca0[1] + ca1[1]), f1 = (float)((ca0[2] + ca1[2]) * 256 + ca0[3] + ca1[3]);
+                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+            }
+            if (have_b) {
+                const float2 m = meta[grp_b * NB + t];
+                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
+                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                const float f0 = (float)((cb0[0] + cb1[0]) * 256 + cb0[1] + cb1[1]), f1 = (float)((cb0[2] + cb1[2]) * 256 + cb0[3] + cb1[3]);
+                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+            }
+        }
+    }
+};
+
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kV2Consumers * 32) : "memory"); }
 
 __device__ __forceinline__ unsigned pack4s(int a, int b, int c, int d) {
