@@ -45,6 +45,9 @@ L8_SHAPES = [("qkv", 6144, 4096, "plain"), ("o", 4096, 4096, "plain"),
              ("gate_up", 14336, 4096, "ffn"), ("down", 4096, 14336, "plain")]
 METRIC_DECODE = "decode tok/s (Llama-3-8B shape, INT4 g128 + AWQ weights, INT8 TurboQuant KV)"
 METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)"
+# dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
+PROJ_DRAM_BYTES = 62467840 + 17920          # matvec_v2_kernel<gate+up+SiLU>, one launch
+TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = 0.0     # decode_token_kernel, per decoder layer at ~2k context (filled from the capture)
 
 
 def matvec_bytes(N, K, B=1, awq=True, bits=4):
@@ -232,7 +235,7 @@ def run_decode(args, rank, world):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     dev = ops.Device(local)
-    cfg = ModelConfig(**L8)
+    cfg = ModelConfig(**dict(L8, num_hidden_layers=args.layers))
     B, P, K, W = args.batch, args.prompt, args.steps, max(args.warmup, 3)
     e2e_steps = max(8, min(K, 64))
     max_seq = P + W + K + e2e_steps + 8
@@ -286,37 +289,56 @@ def run_decode(args, rank, world):
     prof = eng.profile_step(B)
     step_bytes = eng.step_bytes(ctx_mid, B)
     launches = eng.step_launches()
+    # dominant kernel: the whole-token decode kernel when the engine uses it (batch 1, one GPU), else the largest projection launch
+    tk = eng.token_kernel_profile(8) if (B == 1 and world == 1) else None
     dom_us, dom_bytes, _ = time_dominant_kernel(dev) if rank == 0 else (1.0, 0, 0)
     if rank != 0:
         return
     peak, peak_src = measured_peaks()
     tok_s = B * K / (ms * 1e-3)
     step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
+    proj = {"kernel": "matvec_v2_kernel<gate+up+SiLU, batch 1> 4096->2x14336 (largest projection, launched alone)",
+            "achieved": round(dom_bytes / (dom_us * 1e-6) / 1e9, 1), "frac": round(dom_bytes / (dom_us * 1e-6) / 1e9 / peak, 4),
+            "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_us, 3),
+            "timing": "CUDA events around a CUDA graph of launches rotating over 6 weight copies (702 MB > L2)"}
+    if tk is not None:
+        tk_ms, phases = tk
+        head_bytes = cfg.vocab_size * cfg.hidden_size * 2 + 2 * cfg.hidden_size * 2 + cfg.vocab_size * 2   # lm_head + embedding row + logits
+        tk_bytes = step_bytes - head_bytes
+        roof = {"bound": "hbm", "kernel": "decode_token_kernel (all %d layers of one token: projections, RoPE + cache write, attention)" % cfg.num_hidden_layers,
+                "achieved": round(tk_bytes / (tk_ms * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(tk_bytes / (tk_ms * 1e-3) / 1e9 / peak, 4), "peak_source": peak_src,
+                "bytes_per_launch": tk_bytes, "us_per_launch": round(tk_ms * 1e3, 1),
+                "traffic": int(TOKEN_KERNEL_DRAM_BYTES_PER_LAYER * cfg.num_hidden_layers),
+                "traffic_note": "dram read+write per launch: ncu capture of an 8-layer model of the same shapes scaled by the layer count (profiles/)",
+                "timing": "CUDA events around 8 back-to-back launches on the engine's stream; every launch streams all weights (> L2)",
+                "phase_us_per_layer": {k: round(v, 2) for k, v in phases.items()},
+                "largest_projection_alone": proj}
+    else:
+        roof = dict(proj, bound="hbm", peak=peak, unit="GB/s", peak_source=peak_src, traffic=PROJ_DRAM_BYTES,
+                    traffic_note="dram read+write of this launch from the ncu capture under profiles/")
+    roof["whole_step"] = {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_gbs, 1),
+                          "frac_of_hbm_roofline": round(step_gbs / peak, 4),
+                          "roofline_tok_s": round(B * peak * 1e9 / step_bytes, 1)}
     out = {
         "metric": METRIC_DECODE, "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u4 codes x i16 activations (f32 fix-up), f16 lm_head, u8 KV codebook indices",
         "data": "synthetic",
         "config": {"workload": "llama3_8b_shape_int4_g128_awq_tq8_decode", "batch": B, "prompt_tokens": P,
-                   "context_during_timing": [ctx0, ctx0 + K], "layers": 32, "hidden": 4096, "ffn": 14336, "vocab": 128256,
+                   "context_during_timing": [ctx0, ctx0 + K], "layers": cfg.num_hidden_layers, "hidden": 4096, "ffn": 14336, "vocab": 128256,
                    "parallelism": f"tp{world}" if world > 1 else "single",
                    "l2_policy": "inputs larger than L2: every step streams this rank's %.2f GB of weights + KV" % (step_bytes / 1e9),
                    "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2)},
-        "roofline": {"bound": "hbm", "kernel": "matvec_kernel<int4, gate+up+SiLU> 4096->2x14336 (largest launch of the step)",
-                     "achieved": round(dom_bytes / (dom_us * 1e-6) / 1e9, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(dom_bytes / (dom_us * 1e-6) / 1e9 / peak, 4), "peak_source": peak_src,
-                     "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_us, 3), "traffic": 62433280 + 139520,
-                     "traffic_note": "dram read+write of this launch from the ncu capture under profiles/",
-                     "timing": "CUDA events around a CUDA graph of launches rotating over 6 weight copies (702 MB > L2)",
-                     "whole_step": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_gbs, 1),
-                                    "frac_of_hbm_roofline": round(step_gbs / peak, 4),
-                                    "roofline_tok_s": round(B * world * peak * 1e9 / (step_bytes * world), 1)}},
+        "roofline": roof,
         "e2e": {"value": round(B * e2e_steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 2 * B * cfg.vocab_size, "steps": e2e_steps,
                 "note": "InferenceEngine.decode_step per token: host token in, fp16 logits to pinned host memory, widened to f32"},
         "gpu_launches": launches * K,
         "launches_per_step": launches,
         "step_profile_ms": {k: round(v, 4) for k, v in prof.items()},
+        "step_profile_note": "per-category timing of the launch-per-kernel schedule run eagerly (the schedule used for batch > 1); "
+                             "the timed steps above run the whole-token kernel when roofline.kernel says so",
         "clocks": clocks,
     }
     if world == 1:
@@ -385,9 +407,10 @@ def run_matvec(args, rank, world):
            "vs_baseline": None, "dtype": "u4 codes x i16 activations, f32 fix-up", "data": "synthetic",
            "config": {"workload": "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq", "shapes": [[n, N, K] for n, N, K, _ in L8_SHAPES],
                       "l2_policy": f"rotation over {ncopies} weight copies ({ncopies * step_bytes >> 20} MiB) larger than L2"},
-           "roofline": {"bound": "hbm", "kernel": "matvec_kernel<int4, gate+up+SiLU> 4096->2x14336",
+           "roofline": {"bound": "hbm", "kernel": "matvec_v2_kernel<gate+up+SiLU, batch 1> 4096->2x14336",
                         "achieved": round(dom_bytes / (dom_us * 1e-6) / 1e9, 1), "peak": peak, "unit": "GB/s",
-                        "frac": round(dom_bytes / (dom_us * 1e-6) / 1e9 / peak, 4), "peak_source": peak_src, "traffic": None},
+                        "frac": round(dom_bytes / (dom_us * 1e-6) / 1e9 / peak, 4), "peak_source": peak_src, "traffic": PROJ_DRAM_BYTES,
+                        "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_us, 3)},
            "e2e": {"value": round(sum(shape_bytes(*sh) for sh in plain) * 20 / e2e_s / 1e9, 3), "unit": "GB/s",
                    "h2d_bytes_per_step": sum(K * 2 for _, N, K, _ in plain), "d2h_bytes_per_step": sum(N * 2 for _, N, K, _ in plain)},
            "gpu_launches": 4 * steps, "clocks": clocks, "cpu_baseline": cpu_matvec_baseline(3.0)}
@@ -487,6 +510,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "matvec"])
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the synthetic model (32 = the named workload; fewer only for profiler captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

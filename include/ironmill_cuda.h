@@ -318,8 +318,14 @@ size_t im_cuda_model_memory_bytes(const im_model *m);
 size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
 /* Number of kernel launches in one captured decode step. */
 int im_cuda_model_step_launches(const im_model *m);
-/* Development aid (no counterpart in the reference): timer stamps of the whole-token decode kernel, one per grid
- * barrier, recorded when IM_MEGA_TRACE=1 was set in the environment at load time. IM_ERR_STATE otherwise. */
+/* Timing of the whole-token decode kernel (all layers of a batch-1 step in one launch) by itself: the counterpart of
+ * MetalConfig.kernel_timing for that kernel (crates/ironmill-inference/src/metal/pipeline.rs:353-422).
+ * ms_per_launch: average of `reps` back-to-back launches between two events on the model's stream;
+ * phase_us_7 (optional, 7 floats): microseconds per layer in QKV, RoPE + cache write, attention, split reduction,
+ * o, gate/up, down.  IM_ERR_STATE when the model does not use that kernel (batch > 1 only, tensor parallel,
+ * non-INT4 weights, IM_MEGA=0). */
+int im_cuda_model_token_kernel_profile(im_model *m, int reps, float *ms_per_launch, float *phase_us_7);
+/* Development aid (no counterpart in the reference): the raw timer stamps behind the call above. */
 int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, int n);
 /* Per-category GPU time of one eager decode step at the current position, which is not advanced
  * (MetalConfig.kernel_timing, crates/ironmill-inference/src/metal/pipeline.rs:353-422,1215-1234).

@@ -493,11 +493,9 @@ static int mega_prepare(Model *m) {
     IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;
-    const char *tr = getenv("IM_MEGA_TRACE");
-    if (tr && tr[0] == '1') {
-        IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
-        IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
-    }
+    // phase stamps of CTA 0 (a store per grid barrier; read back by im_cuda_model_token_kernel_profile)
+    IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
+    IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
     IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
     m->mega_ready = true;
     return IM_OK;
@@ -893,13 +891,63 @@ IM_EXPORT int im_cuda_model_truncate(im_model *m, int pos) {
 IM_EXPORT int im_cuda_model_seq_pos(const im_model *m) { return m ? m->seq_pos : 0; }
 IM_EXPORT int im_cuda_model_max_seq_len(const im_model *m) { return m ? m->cfg.max_seq_len : 0; }
 IM_EXPORT size_t im_cuda_model_memory_bytes(const im_model *m) { return m ? m->bytes : 0; }
-// Development aid: with IM_MEGA_TRACE=1 in the environment at load time, CTA 0 of the whole-token kernel stamps the
-// nanosecond timer at its start [0], when it leaves grid barrier k [k + 1] and at exit [7L + 1]; this copies the stamps.
+// Timing of the whole-token decode kernel alone: `reps` launches back to back on the model's stream between two
+// events (the sequence position is not advanced: every launch rewrites the same cache row), and the time CTA 0
+// spent in each of the seven phases of a layer, averaged over the layers of the last launch, from the
+// nanosecond-timer stamps it leaves at every grid barrier.  IM_ERR_STATE when the model does not use that kernel.
+IM_EXPORT int im_cuda_model_token_kernel_profile(im_model *m, int reps, float *ms_per_launch, float *phase_us_7) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && reps >= 1 && ms_per_launch, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    if (!m->mega_ready) return fail(IM_ERR_STATE, "this model does not run the whole-token decode kernel");
+    if (m->seq_pos + 1 > m->cfg.max_seq_len) return fail(IM_ERR_BOUNDS, "no room for one more position");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    cudaStream_t st = m->stream;
+    const im_model_config &c = m->cfg;
+    IM_TRY(im_cuda_embedding_norm(m->tokens_dev, m->embed, m->layers[0].input_ln, m->norm_out, m->hidden, c.hidden_size, 1,
+                                  (uint32_t)c.vocab_size, c.rms_eps, c.embed_scale != 0.0f ? c.embed_scale : 1.0f, st));
+    IM_TRY(mega_launch(m->mega, m->dev, st));  // warm
+    cudaEvent_t e0, e1;
+    IM_CUDA_CHECK(cudaEventCreate(&e0));
+    IM_CUDA_CHECK(cudaEventCreate(&e1));
+    cudaEventRecord(e0, st);
+    int rc = IM_OK;
+    for (int i = 0; i < reps && rc == IM_OK; i++) rc = mega_launch(m->mega, m->dev, st);
+    cudaEventRecord(e1, st);
+    cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st);
+    cudaError_t e = cudaStreamSynchronize(st);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    IM_TRY(rc);
+    if (e != cudaSuccess) return fail(IM_ERR_CUDA, "whole-token kernel failed: %s", cudaGetErrorString(e));
+    IM_TRY(step_error_check(m));
+    *ms_per_launch = ms / (float)reps;
+    if (phase_us_7) {
+        const int L = c.num_layers, n = 7 * L + 2;
+        std::vector<unsigned long long> t((size_t)n);
+        IM_CUDA_CHECK(cudaMemcpy(t.data(), m->mega.trace, (size_t)n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        // t[0] start, t[k + 1] leaving barrier k (k = 0 .. 7L - 2), t[7L + 1] exit
+        for (int j = 0; j < 7; j++) phase_us_7[j] = 0.0f;
+        for (int l = 0; l < L; l++)
+            for (int j = 0; j < 7; j++) {
+                const int k = 7 * l + j;
+                const unsigned long long end = k + 1 <= 7 * L - 1 ? t[(size_t)k + 1] : t[(size_t)7 * L + 1];
+                const unsigned long long start = t[(size_t)k];
+                phase_us_7[j] += (float)((double)(end - start) * 1e-3) / (float)L;
+            }
+    }
+    return IM_OK;
+    IM_GUARD_END
+}
+
+// Development aid: the raw stamps (7L + 2 phase stamps, then 4 x 24 stamps inside the projections of layer 1).
 IM_EXPORT int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, int n) {
     IM_GUARD_BEGIN
     IM_REQUIRE(m && out && n >= 0, "bad argument");
-    if (!m->mega.trace) return fail(IM_ERR_STATE, "tracing is off (IM_MEGA_TRACE=1 at load time turns it on)");
-    const int have = 7 * m->cfg.num_layers + 2 + 96;  // + 4 x 24 stamps inside the projections of layer 1
+    if (!m->mega.trace) return fail(IM_ERR_STATE, "this model does not run the whole-token decode kernel");
+    const int have = 7 * m->cfg.num_layers + 2 + 96;
     IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
     IM_CUDA_CHECK(cudaMemcpy(out, m->mega.trace, (size_t)(n < have ? n : have) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return IM_OK;

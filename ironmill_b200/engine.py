@@ -244,6 +244,19 @@ class CudaInference:
         check(lib().im_cuda_model_profile_step(self._model, C.c_int(batch), ms, C.c_int(11)))
         return dict(zip(self.PROFILE_CATEGORIES, [float(v) for v in ms]))
 
+    def token_kernel_profile(self, reps: int = 8):
+        """(ms per launch, {phase: microseconds per layer}) of the whole-token decode kernel, or None when the model
+        does not run it (batch > 1 only, tensor parallel, non-INT4 weights)."""
+        self._need_model()
+        ms = C.c_float()
+        ph = (C.c_float * 7)()
+        rc = lib().im_cuda_model_token_kernel_profile(self._model, C.c_int(reps), C.byref(ms), ph)
+        if rc == -7:
+            return None
+        check(rc)
+        names = ("qkv", "rope_cache_write", "attention", "split_reduce", "o", "gate_up", "down")
+        return float(ms.value), {n: float(v) for n, v in zip(names, ph)}
+
     def close(self) -> None:
         if self._model:
             lib().im_cuda_model_free(self._model)
