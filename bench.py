@@ -47,7 +47,7 @@ METRIC_DECODE = "decode tok/s (Llama-3-8B shape, INT4 g128 + AWQ weights, INT8 T
 METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)"
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
 PROJ_DRAM_BYTES = 62467840 + 17920          # matvec_v2_kernel<gate+up+SiLU>, one launch
-TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = 0.0     # decode_token_kernel, per decoder layer at ~2k context (filled from the capture)
+TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = (970164992 + 28496384) / 8   # decode_token_kernel: capture of the 8-layer model at ~2k context
 
 
 def matvec_bytes(N, K, B=1, awq=True, bits=4):

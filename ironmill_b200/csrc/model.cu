@@ -125,6 +125,8 @@ struct Model {
     int *pos_dev = nullptr, *step_dev = nullptr;
     uint32_t *tokens_pin = nullptr;
     __half *logits_pin = nullptr;
+    float2 *argmax_cand = nullptr;  // [max_batch][kArgmaxCtas] candidates of the greedy pick
+    unsigned *argmax_counters = nullptr;
     int *err_pin = nullptr;  // the device's bounded-wait error word, copied back with every step
     cudaStream_t stream = nullptr;
     std::map<int, cudaGraphExec_t> graphs;
@@ -165,17 +167,27 @@ __global__ void set_pos_kernel(int *pos, int n, int v) {
 
 // Greedy pick per sequence: LAST maximal index (Iterator::max_by keeps the last of equal maxima,
 // crates/ironmill-inference/src/sampling.rs:331-339).  logits are laid out [parts][nseq][vocab_part].
-__global__ void argmax_kernel(const __half *__restrict__ logits, int vocab_part, int parts, int nseq, uint32_t *__restrict__ tokens,
-                              uint32_t *__restrict__ hist, const int *__restrict__ step, int hist_stride, int hist_rows) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
+// grid (kArgmaxCtas, nseq): every CTA scans a slice of the vocabulary and leaves its candidate in `cand`; the last
+// CTA of a sequence to arrive combines the candidates, writes the token and clears the counter for the next launch.
+constexpr int kArgmaxCtas = 64, kArgmaxThreads = 256;
+__device__ __forceinline__ bool argmax_better(float ov, int oi, float best, int bi) {  // is (ov, oi) preferred over (best, bi)?
+    return oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi));
+}
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_kernel(const __half *__restrict__ logits, int vocab_part, int parts, int nseq,
+                                                                uint32_t *__restrict__ tokens, uint32_t *__restrict__ hist,
+                                                                const int *__restrict__ step, int hist_stride, int hist_rows,
+                                                                float2 *__restrict__ cand, unsigned *__restrict__ counters) {
+    __shared__ float sv[kArgmaxThreads / 32];
+    __shared__ int si[kArgmaxThreads / 32];
+    __shared__ int s_last;
     pdl_trigger();
     pdl_wait();
-    const int seq = blockIdx.x;
+    const int seq = blockIdx.y;
+    const int vocab = vocab_part * parts;
+    const int per = (vocab + gridDim.x - 1) / gridDim.x, i0 = blockIdx.x * per, i1 = min(vocab, i0 + per);
     float best = -INFINITY;
     int bi = -1;
-    const int vocab = vocab_part * parts;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const int part = i / vocab_part, j = i % vocab_part;
         const float v = __half2float(logits[((size_t)part * nseq + seq) * vocab_part + j]);
         if (!(v < best) || bi < 0) {  // ascending i per thread: ties move to the later index
@@ -183,28 +195,50 @@ __global__ void argmax_kernel(const __half *__restrict__ logits, int vocab_part,
             bi = i;
         }
     }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) {
-            best = ov;
-            bi = oi;
+    auto block_reduce = [&]() {
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (argmax_better(ov, oi, best, bi)) {
+                best = ov;
+                bi = oi;
+            }
         }
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) {
-        sv[warp] = best;
-        si[warp] = bi;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (lane == 0) {
+            sv[warp] = best;
+            si[warp] = bi;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+                if (argmax_better(sv[w], si[w], best, bi)) {
+                    best = sv[w];
+                    bi = si[w];
+                }
+    };
+    block_reduce();
+    if (threadIdx.x == 0) {
+        cand[(size_t)seq * gridDim.x + blockIdx.x] = make_float2(best, __int_as_float(bi));
+        __threadfence();
+        s_last = atomicAdd(&counters[seq], 1u) == gridDim.x - 1;
     }
     __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY;
+    bi = -1;
+    if (threadIdx.x < gridDim.x) {
+        const float2 c = __ldcg(&cand[(size_t)seq * gridDim.x + threadIdx.x]);
+        best = c.x;
+        bi = __float_as_int(c.y);
+    }
+    __syncthreads();
+    block_reduce();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
-            if (si[w] >= 0 && (bi < 0 || sv[w] > best || (sv[w] == best && si[w] > bi))) {
-                best = sv[w];
-                bi = si[w];
-            }
         tokens[seq] = (uint32_t)bi;
         if (hist) hist[(size_t)(*step % hist_rows) * hist_stride + seq] = (uint32_t)bi;
+        counters[seq] = 0;
     }
 }
 __global__ void bump_kernel(int *step) {
@@ -522,8 +556,8 @@ static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
     int rc = forward(m, batch, 1, splits, st, &nl);
     if (rc == IM_OK) {
         const __half *lg = m->world > 1 ? m->logits_all : m->logits;
-        cudaError_t le = launch_k(argmax_kernel, dim3(batch), dim3(1024), 0, st, lg, m->vocab_l, m->world, batch, m->tokens_dev, m->tok_hist,
-                                  (const int *)m->step_dev, m->cfg.max_batch, m->cfg.max_seq_len);
+        cudaError_t le = launch_k(argmax_kernel, dim3(kArgmaxCtas, batch), dim3(kArgmaxThreads), 0, st, lg, m->vocab_l, m->world, batch, m->tokens_dev,
+                                  m->tok_hist, (const int *)m->step_dev, m->cfg.max_batch, m->cfg.max_seq_len, m->argmax_cand, m->argmax_counters);
         if (le == cudaSuccess) le = launch_k(bump_kernel, dim3(1), dim3(1), 0, st, m->step_dev);
         if (le == cudaSuccess) le = launch_k(advance_pos_kernel, dim3(1), dim3(64), 0, st, m->pos_dev, batch, 1);
         if (le != cudaSuccess) rc = fail(IM_ERR_CUDA, "launch failed: %s", cudaGetErrorString(le));
@@ -845,6 +879,9 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_TRY(m->alloc((void **)&m->step_dev, 4));
     IM_CUDA_CHECK(cudaMemset(m->pos_dev, 0, 64 * 4));
     IM_CUDA_CHECK(cudaMemset(m->step_dev, 0, 4));
+    IM_TRY(m->alloc((void **)&m->argmax_cand, (size_t)c.max_batch * kArgmaxCtas * sizeof(float2)));
+    IM_TRY(m->alloc((void **)&m->argmax_counters, (size_t)c.max_batch * sizeof(unsigned)));
+    IM_CUDA_CHECK(cudaMemset(m->argmax_counters, 0, (size_t)c.max_batch * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMallocHost((void **)&m->tokens_pin, MT * 4));
     IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_pin, (size_t)c.max_batch * c.vocab_size * 2));
     IM_CUDA_CHECK(cudaMallocHost((void **)&m->err_pin, sizeof(int)));
