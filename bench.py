@@ -257,12 +257,13 @@ def run_decode(args, rank, world):
         for t in prompt[:min(P, 64)]:
             eng.decode_step(np.full(B, t, dtype=np.uint32))
     toks, _ = eng.decode_greedy(first, W)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()   # before the barrier: its start-up must not delay this rank inside the timed region
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+        torch.cuda.synchronize()
     ctx0 = eng.seq_pos()
     toks, ms = eng.decode_greedy(toks[-1], K)
     if world > 1:
