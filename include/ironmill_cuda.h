@@ -158,6 +158,10 @@ int im_cuda_fused_residual_norm_ffn(const im_affine_weight *gate, const im_affin
  * (.../shaders/linear/matvec.metal:30-84; crates/ironmill-inference/src/metal/pipeline.rs:1159-1174).
  * w_dev fp16 [N,K] row-major, x_dev fp16 [B,K], y_dev fp16 [B,N]. */
 int im_cuda_matvec_f16(const void *w_dev, const void *x_dev, void *y_dev, int N, int K, int B, void *stream);
+/* superblock_matmul_int4 (.../shaders/quantized/affine_matmul.metal:10-152), the dense-contraction case (prefill,
+ * decode batches >= 16): y[M,N] = sum_k f16(x[m,k] / awq[k]) * f16((q - z) * s), f32 accumulation on the tcgen05
+ * tensor cores, fp16 result.  INT4 group-128 weights; scratch_dev holds M*K halves (the scaled activations). */
+int im_cuda_matmul_affine(const im_affine_weight *w, const void *x_dev, void *y_dev, int M, void *scratch_dev, void *stream);
 
 /* ------------------------------------------------------------------ norms, embedding, RoPE
  * rms_norm (crates/ironmill-inference/src/metal/shaders/norm/normalization.metal:19-57):

@@ -91,6 +91,9 @@ struct V2Params {
     unsigned long long *trace;  // optional: 8 timer stamps from CTA 0 (development aid), else nullptr
 };
 
+// INT4 g128 GEMM on tcgen05 / TMEM (gemm_tc.cu): y[M, N] = f16(x / awq) * dequant(w)^T; xs_scratch holds M * K halves.
+// IM_ERR_BOUNDS when the weight is not INT4 group-128.
+int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __half *xs_scratch, cudaStream_t st);
 // Gate/up pair as one tile stream (matvec.cu); built on first use.
 int ensure_pair(const AffineWeight *gate, const AffineWeight *up, cudaStream_t st);
 int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st);

@@ -1,0 +1,288 @@
+// INT4 group-128 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for the dense-contraction cases of the
+// hot path: prefill chunks and decode batches of 16 tokens and more.
+//   crates/ironmill-inference/src/metal/shaders/quantized/affine_matmul.metal:10-152 (superblock_matmul_int4):
+//   C[m, n] = sum_k f16(A[m, k] / awq[k]) * f16((q[n, k] - z) * s), f32 accumulation, fp16 result.
+//
+// Shape of the computation: D[128 weight rows x TN tokens] (f32, in tensor memory) += W[128 x 16] * X[TN x 16]^T, issued
+// by one thread with tcgen05.mma (kind::f16, UMMA M = 128, N = TN, K = 16), eight per stage of one quantisation
+// group (128 columns).  Both operands sit in shared memory, K-major with the 128-byte swizzle:
+//   * A: the weights.  Four warps read the packed 4-bit codes of their rows (64 bytes per row and group) and the
+//     row's (scale, zero), dequantise in packed fp16 arithmetic - (q - z) * s with one rounding, the reference's
+//     f16((q - z) s) - and store fp16 straight into the swizzled operand layout: the dequantisation is fused into
+//     the operand load, HBM carries 4 bits per weight;
+//   * B: the activations, already divided by the AWQ scales and rounded to fp16 (act_scale_kernel), copied by four
+//     warps with 16-byte loads into the same layout.
+// A three-stage ring decouples the producers from the tensor core: full barriers count the eight producer warps,
+// tcgen05.commit releases a stage when its eight MMAs have read it.  After the last group the four producer warps
+// read their 32 TMEM lanes (tcgen05.ld 32x32b), convert and write fp16 outputs.  Every wait is bounded; a wait
+// that runs out sets the device error word, the kernel still frees its tensor memory and returns.
+#include "common.cuh"
+#include "v2_device.cuh"
+
+namespace im {
+
+namespace {
+
+constexpr int kGM = 128;       // weight rows per CTA = UMMA M
+constexpr int kGK = 128;       // columns per stage = one quantisation group = two 64-column swizzle atoms
+constexpr int kGStages = 3;
+constexpr int kGThreads = 9 * 32;  // warps 0-3: weights + epilogue, 4-7: activations, 8: tensor memory + MMA issue
+
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    // shared-memory matrix descriptor, K-major, 128-byte swizzle: start address >> 4 in bits 0-13, leading byte
+    // offset (unused for swizzled K-major) = 1 in bits 16-29, stride byte offset = 1024 B (8 rows of 128 B) >> 4 in
+    // bits 32-45, descriptor version 1 in bits 46-47, layout type 2 (SWIZZLE_128B) in bits 61-63
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+        " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmParams {
+    const uint8_t *codes;  // [N, K/2] row-major 4-bit codes, low nibble first
+    const __half2 *sz;     // [N, G] (scale, zero)
+    const __half *xs;      // [M, K] activations, already divided by the AWQ scales
+    __half *y;             // [M, N]
+    int N, K, G, M;
+    int *err;
+};
+
+// 8 nibbles of a word -> 8 fp16 values (q - z) * s in memory order.  c = 1024 + z, exact for integer z in
+// [-1024, 1023]: 0x6400 | q is the fp16 number 1024 + q, the subtraction is exact, the product is rounded once.
+__device__ __forceinline__ uint4 dequant8_fast(uint32_t w, __half2 c, __half2 s) {
+    constexpr uint32_t M = 0x000F000Fu, E = 0x64006400u;
+    uint32_t h04 = (w & M) | E, h15 = ((w >> 4) & M) | E, h26 = ((w >> 8) & M) | E, h37 = ((w >> 12) & M) | E;
+    __half2 v04 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h04), c), s);
+    __half2 v15 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h15), c), s);
+    __half2 v26 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h26), c), s);
+    __half2 v37 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h37), c), s);
+    const uint32_t a = *reinterpret_cast<uint32_t *>(&v04), b = *reinterpret_cast<uint32_t *>(&v15);
+    const uint32_t cc = *reinterpret_cast<uint32_t *>(&v26), d = *reinterpret_cast<uint32_t *>(&v37);
+    return make_uint4(__byte_perm(a, b, 0x5410), __byte_perm(cc, d, 0x5410), __byte_perm(a, b, 0x7632), __byte_perm(cc, d, 0x7632));
+}
+__device__ __forceinline__ uint4 dequant8_slow(uint32_t w, float z, float s) {  // any zero point: f32, one rounding
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float lo = ((float)((w >> (8 * i)) & 15u) - z) * s, hi = ((float)((w >> (8 * i + 4)) & 15u) - z) * s;
+        o[i] = (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int TN>
+__global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment of every operand buffer: the swizzle is a function of the address bits
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int kABytes = kGM * kGK * 2, kBBytes = TN * kGK * 2;
+    unsigned char *As = smem, *Bs = smem + kGStages * kABytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(Bs + kGStages * kBBytes);
+    uint64_t *empty = full + kGStages;
+    uint64_t *accum = empty + kGStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * kGM, m0 = blockIdx.y * TN;
+    pdl_trigger();
+    if (tid == 0) {
+        for (int i = 0; i < kGStages; i++) {
+            mbar_init(&full[i], 8);
+            mbar_init(&empty[i], 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {  // TN f32 columns of tensor memory for the accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TN < 32 ? 32 : TN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot;
+    pdl_wait();
+
+    const int G = p.G;
+    bool ok = true;
+    if (warp < 4) {
+        // ---------------------------------------------------------------- weights: dequantise into operand A
+        const int r = tid, n = n0 + r;
+        const bool live = n < p.N;
+        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * (p.K / 2);
+        const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * G;
+        const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        for (int kt = 0; kt < G; kt++) {
+            const int s = kt % kGStages, use = kt / kGStages;
+            if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
+            const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)kt * 64);
+            uint4 w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) w[i] = live ? ldg_stream_v4(src + i) : make_uint4(0, 0, 0, 0);
+            const __half2 szv = szrow[kt];
+            const float zf = __high2float(szv), sf = __low2float(szv);
+            const bool fast = zf == rintf(zf) && zf >= -1024.0f && zf <= 1023.0f;
+            const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szv));
+            unsigned char *dst = As + (size_t)s * kABytes + row_off;
+            const uint32_t *ww = reinterpret_cast<const uint32_t *>(w);
+#pragma unroll
+            for (int c = 0; c < 16; c++) {  // chunk c = columns 8c .. 8c+7 of the group
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (live) v = fast ? dequant8_fast(ww[c], c2, s2) : dequant8_slow(ww[c], zf, sf);
+                *reinterpret_cast<uint4 *>(dst + (c >> 3) * (kGM * 128) + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    } else if (warp < 8) {
+        // ---------------------------------------------------------------- activations: copy into operand B
+        const int t2 = tid - 128;
+        constexpr int kPer = TN / 8;                 // 16-byte chunks per thread and stage (TN * 16 chunks / 128 threads)
+        const int trow = t2 % TN, c_lo = (t2 / TN) * kPer;
+        const int m = m0 + trow;
+        const bool live = m < p.M;
+        const __half *xrow = p.xs + (size_t)(live ? m : 0) * p.K;
+        const uint32_t row_off = (uint32_t)((trow >> 3) * 1024 + (trow & 7) * 128);
+        for (int kt = 0; kt < G; kt++) {
+            const int s = kt % kGStages, use = kt / kGStages;
+            if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
+            const uint4 *src = reinterpret_cast<const uint4 *>(xrow + (size_t)kt * kGK);
+            uint4 v[kPer];
+#pragma unroll
+            for (int i = 0; i < kPer; i++) v[i] = live ? src[c_lo + i] : make_uint4(0, 0, 0, 0);
+            unsigned char *dst = Bs + (size_t)s * kBBytes + row_off;
+#pragma unroll
+            for (int i = 0; i < kPer; i++) {
+                const int c = c_lo + i;
+                *reinterpret_cast<uint4 *>(dst + (c >> 3) * (TN * 128) + (((c & 7) ^ (trow & 7)) << 4)) = v[i];
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    } else {
+        // ---------------------------------------------------------------- one thread issues the MMAs
+        // instruction descriptor: f32 accumulator (bit 4), fp16 A and B (formats 0), both K-major, N >> 3 in bits
+        // 17-22, M >> 4 in bits 24-28
+        constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(kGM >> 4) << 24);
+        for (int kt = 0; kt < G; kt++) {
+            const int s = kt % kGStages, use = kt / kGStages;
+            if (ok && !mbar_wait_warp(&full[s], use & 1, p.err)) ok = false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0 && ok) {
+                const uint32_t a0 = smem_u32(As + (size_t)s * kABytes), b0 = smem_u32(Bs + (size_t)s * kBBytes);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {  // K = 16 per instruction: 32 bytes along the swizzled row, second atom after four
+                    const uint64_t ad = umma_desc_sw128(a0 + (j >> 2) * (kGM * 128) + (j & 3) * 32);
+                    const uint64_t bd = umma_desc_sw128(b0 + (j >> 2) * (TN * 128) + (j & 3) * 32);
+                    umma_f16(tmem_d, ad, bd, idesc, (kt > 0 || j > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);              // the stage is free once these MMAs have read it
+                if (kt == G - 1) umma_commit(accum);  // ... and the accumulator is complete after the last one
+            }
+            __syncwarp();
+        }
+    }
+
+    // -------------------------------------------------------------------- epilogue: TMEM -> fp16 outputs
+    if (warp < 4) {
+        if (ok && !mbar_wait_warp(accum, 0, p.err)) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int n = n0 + tid;  // this thread's TMEM lane = weight row
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                if (n < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int m = m0 + c0 + i;
+                        if (m < p.M) p.y[(size_t)m * p.N + n] = __float2half_rn(__uint_as_float(r[i]));
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TN < 32 ? 32 : TN) : "memory");
+    }
+}
+
+// xs[m, k] = f16(x[m, k] / awq[k]) (or a copy when there are no activation scales)
+__global__ void act_scale_kernel(const __half *__restrict__ x, const __half *__restrict__ awq, __half *__restrict__ xs, size_t n, int K) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= n) return;
+    uint4 v = *reinterpret_cast<const uint4 *>(x + i);
+    if (awq) {
+        const uint4 a = *reinterpret_cast<const uint4 *>(awq + (i % (size_t)K));
+        __half2 *hv = reinterpret_cast<__half2 *>(&v);
+        const __half2 *ha = reinterpret_cast<const __half2 *>(&a);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 fx = __half22float2(hv[j]), fa = __half22float2(ha[j]);
+            hv[j] = __floats2half2_rn(fx.x / fa.x, fx.y / fa.y);
+        }
+    }
+    *reinterpret_cast<uint4 *>(xs + i) = v;
+}
+
+template <int TN>
+int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
+    const size_t smem = 1024 + (size_t)kGStages * (kGM * kGK * 2 + TN * kGK * 2) + (2 * kGStages + 1) * 8 + 16;
+    if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
+    auto kern = gemm_int4_tc_kernel<TN>;
+    static thread_local bool configured = false;
+    if (!configured) {
+        IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    dim3 grid((p.N + kGM - 1) / kGM, (p.M + TN - 1) / TN);
+    IM_CUDA_CHECK(launch_k(kern, grid, dim3(kGThreads), smem, st, p));
+    return IM_OK;
+}
+
+}  // namespace
+
+// Y[M, N] = f16(X / awq) * dequant(W)^T for M tokens.  xs_scratch: M * K halves.  IM_ERR_BOUNDS when the weight is not
+// INT4 group-128 with K a multiple of 128 (the caller falls back to the matvec kernels).
+int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __half *xs_scratch, cudaStream_t st) {
+    if (w->bits != 4 || w->group_size != 128 || w->K % 128 != 0 || M < 1) return IM_ERR_BOUNDS;
+    const size_t n = (size_t)M * w->K;
+    IM_CUDA_CHECK(launch_k(act_scale_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, x, (const __half *)w->awq, xs_scratch, n, w->K));
+    GemmParams p{w->codes, w->sz, xs_scratch, y, w->N, w->K, w->G, M, w->dev->err_flag};
+    if (M > 64) return gemm_launch<128>(p, w->dev, st);
+    if (M > 32) return gemm_launch<64>(p, w->dev, st);
+    return gemm_launch<32>(p, w->dev, st);
+}
+
+}  // namespace im

@@ -869,3 +869,19 @@ IM_EXPORT int im_cuda_matvec_f16(const void *w_dev, const void *x_dev, void *y_d
 // Development aid (not part of the documented ABI): device buffer of 8 u64 that CTA 0 of the tiled matvec
 // fills with %globaltimer stamps (start, activations staged, first stage ready, second stage ready, loop end, end).
 IM_EXPORT void im_cuda_debug_set_trace(void *dev_u64x8) { im::g_v2_trace = static_cast<unsigned long long *>(dev_u64x8); }
+
+// superblock_matmul_int4 (crates/ironmill-inference/src/metal/shaders/quantized/affine_matmul.metal:10-152) on the
+// tcgen05 tensor cores (gemm_tc.cu).  INT4 group-128 weights only.
+IM_EXPORT int im_cuda_matmul_affine(const im_affine_weight *w, const void *x_dev, void *y_dev, int M, void *scratch_dev, void *stream) {
+    IM_GUARD_BEGIN
+    using namespace im;
+    IM_REQUIRE(w && x_dev && y_dev && scratch_dev, "bad argument");
+    IM_REQUIRE(M >= 0, "M must be >= 0");
+    if (M == 0) return IM_OK;
+    IM_CUDA_CHECK(cudaSetDevice(w->dev->ordinal));
+    const int rc = gemm_affine_tc(w, static_cast<const __half *>(x_dev), static_cast<__half *>(y_dev), M, static_cast<__half *>(scratch_dev),
+                                  as_stream(stream));
+    if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "the tensor-core GEMM takes INT4 group-128 weights with K a multiple of 128");
+    return rc;
+    IM_GUARD_END
+}

@@ -119,7 +119,9 @@ struct Model {
     // activations, MT = max tokens per forward
     int MT = 0;
     __half *hidden = nullptr, *norm_out = nullptr, *residual = nullptr, *qkv = nullptr, *q_d = nullptr, *k_d = nullptr, *v_d = nullptr,
-           *attn_out = nullptr, *ffn_down = nullptr, *ffn_gate = nullptr, *logits = nullptr, *logits_all = nullptr;
+           *attn_out = nullptr, *ffn_down = nullptr, *ffn_gate = nullptr, *ffn_up = nullptr, *xs_scratch = nullptr, *logits = nullptr,
+           *logits_all = nullptr;
+    bool gemm_ok = false;  // every projection is INT4 group-128: forwards of 16 tokens and more run the tensor-core GEMM
     float *qrot = nullptr;  // [MT, nh_l, 2, hd] rotated queries
     uint32_t *tokens_dev = nullptr, *tok_hist = nullptr;
     int *pos_dev = nullptr, *step_dev = nullptr;
@@ -154,7 +156,8 @@ struct Model {
     }
 };
 
-static const int kPrefillChunk = 64;
+static const int kPrefillChunk = 256;
+static const int kGemmMinTokens = 16;  // from here on the projections are dense contractions: tcgen05 GEMM instead of matvecs
 
 __global__ void advance_pos_kernel(int *pos, int n, int by) {
     pdl_trigger();
@@ -245,6 +248,16 @@ __global__ void bump_kernel(int *step) {
     pdl_trigger();
     pdl_wait();
     *step += 1;
+}
+
+// act[i] = SiLU(gate[i]) * up[i] (crates/ironmill-inference/src/metal/shaders/activation/activation.metal silu_gate), f32 inside
+__global__ void silu_mul_kernel(const __half *__restrict__ gate, const __half *__restrict__ up, __half *__restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(gate + i)), u = __half22float2(*reinterpret_cast<const __half2 *>(up + i));
+    *reinterpret_cast<__half2 *>(out + i) = __floats2half2_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
 }
 
 static bool parse_layer_name(const char *name, int *layer, std::string *suffix) {
@@ -381,7 +394,58 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)H, st));
         nl += 2;
     }
-    for (int l = 0; l < c.num_layers && !mega; l++) {
+    const bool gemm = !mega && m->gemm_ok && m->world == 1 && MT >= kGemmMinTokens;
+    for (int l = 0; l < c.num_layers && gemm; l++) {
+        // Dense contraction (prefill chunks, large decode batches): every projection is one tcgen05 GEMM; norms, SiLU
+        // and the residual adds are separate element-wise launches (their bytes are a rounding error next to the GEMMs).
+        Layer &L = m->layers[l];
+        if (l == 0) {
+            IM_TRY(gemm_affine_tc(L.qkv, m->norm_out, m->qkv, MT, m->xs_scratch, st));
+            nl += 2;
+            IM_MARK(kCatQkv);
+        }
+        TqPrep a{};
+        a.qkv = m->qkv; a.stride = m->qkv_dim; a.k_off = m->q_dim; a.v_off = m->q_dim + m->kv_dim;
+        a.qw = L.q_norm; a.kw = L.k_norm; a.cosc = m->cosc; a.sinc = m->sinc;
+        a.nh = m->nh_l; a.nkv = m->nkv_l; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd; a.with_norm = c.qk_norm ? 1 : 0;
+        a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev;
+        a.qrot = m->qrot; a.q_out = nullptr;
+        a.kc = L.kc; a.vc = L.vc; a.ks = L.ks; a.vs = L.vs; a.krn = L.krn;
+        IM_TRY(tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st));
+        IM_MARK(kCatKvWrite);
+        IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
+                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot));
+        nl += 3;
+        IM_MARK(kCatAttn);
+        IM_TRY(gemm_affine_tc(L.o, m->attn_out, m->ffn_down, MT, m->xs_scratch, st));
+        IM_MARK(kCatOProj);
+        IM_TRY(im_cuda_fused_residual_rms_norm(m->hidden, m->ffn_down, L.post_ln, m->norm_out, m->residual, H, MT, eps, st));
+        IM_MARK(kCatResNorm);
+        IM_TRY(gemm_affine_tc(L.gate, m->norm_out, m->ffn_gate, MT, m->xs_scratch, st));
+        IM_TRY(gemm_affine_tc(L.up, m->norm_out, m->ffn_up, MT, m->xs_scratch, st));
+        {
+            const size_t n = (size_t)MT * m->I_l;
+            cudaError_t le = launch_k(silu_mul_kernel, dim3((unsigned)((n / 2 + 255) / 256)), dim3(256), 0, st, (const __half *)m->ffn_gate,
+                                      (const __half *)m->ffn_up, m->ffn_gate, n);
+            if (le != cudaSuccess) return fail(IM_ERR_CUDA, "launch failed: %s", cudaGetErrorString(le));
+        }
+        IM_MARK(kCatFfn);
+        IM_TRY(gemm_affine_tc(L.down, m->ffn_gate, m->ffn_down, MT, m->xs_scratch, st));
+        IM_MARK(kCatDown);
+        nl += 11;
+        if (l + 1 < c.num_layers) {
+            Layer &Nx = m->layers[l + 1];
+            IM_TRY(im_cuda_fused_residual_rms_norm(m->residual, m->ffn_down, Nx.input_ln, m->norm_out, m->hidden, H, MT, eps, st));
+            IM_TRY(gemm_affine_tc(Nx.qkv, m->norm_out, m->qkv, MT, m->xs_scratch, st));
+            nl += 3;
+            IM_MARK(kCatQkv);
+        } else {
+            IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)MT * H, st));
+            nl++;
+            IM_MARK(kCatResNorm);
+        }
+    }
+    for (int l = 0; l < c.num_layers && !mega && !gemm; l++) {
         Layer &L = m->layers[l];
         if (l == 0) {
             IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.qkv), m->norm_out, m->qkv, MT, st));
@@ -871,6 +935,17 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_TRY(m->alloc((void **)&m->qrot, MT * m->q_dim * 2 * sizeof(float)));
     IM_TRY(m->alloc((void **)&m->ffn_down, MT * H * 2));
     IM_TRY(m->alloc((void **)&m->ffn_gate, MT * m->I_l * 2));
+    IM_TRY(m->alloc((void **)&m->ffn_up, MT * m->I_l * 2));
+    {
+        size_t kmax = (size_t)H;
+        if ((size_t)m->I_l > kmax) kmax = (size_t)m->I_l;
+        if ((size_t)m->q_dim > kmax) kmax = (size_t)m->q_dim;
+        IM_TRY(m->alloc((void **)&m->xs_scratch, MT * kmax * 2));
+    }
+    m->gemm_ok = getenv("IM_GEMM") == nullptr || getenv("IM_GEMM")[0] != '0';
+    for (Layer &L : m->layers)
+        for (AffineWeight *w : {L.qkv, L.o, L.gate, L.up, L.down})
+            if (!w || w->bits != 4 || w->group_size != 128 || w->K % 128 != 0 || w->N % 8 != 0) m->gemm_ok = false;
     IM_TRY(m->alloc((void **)&m->logits, (size_t)c.max_batch * m->vocab_l * 2));
     if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_all, (size_t)c.max_batch * c.vocab_size * 2));
     IM_TRY(m->alloc((void **)&m->tokens_dev, MT * 4));

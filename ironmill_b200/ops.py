@@ -170,6 +170,15 @@ def matvec_affine(w: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = N
     return y
 
 
+def matmul_affine(w: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Dense INT4 g128 GEMM on the tcgen05 tensor cores: y[M, N] = f16(x / awq) @ dequant(w)^T."""
+    M = _rows(x, w.K)
+    y = out if out is not None else torch.empty((M, w.N), dtype=torch.float16, device=x.device)
+    scratch = torch.empty((M, w.K), dtype=torch.float16, device=x.device)
+    check(lib().im_cuda_matmul_affine(w.handle, vp(x), vp(y), C.c_int(M), vp(scratch), _stream()))
+    return y
+
+
 def matvec_affine_host(w: AffineWeight, x: np.ndarray) -> np.ndarray:
     x = np.ascontiguousarray(x)
     assert x.dtype == np.float16
