@@ -6,16 +6,17 @@
 // Shape of the computation: D[128 weight rows x TN tokens] (f32, in tensor memory) += W[128 x 16] * X[TN x 16]^T, issued
 // by one thread with tcgen05.mma (kind::f16, UMMA M = 128, N = TN, K = 16), eight per stage of one quantisation
 // group (128 columns).  Both operands sit in shared memory, K-major with the 128-byte swizzle:
-//   * A: the weights.  Four warps read the packed 4-bit codes of their rows (64 bytes per row and group) and the
-//     row's (scale, zero), dequantise in packed fp16 arithmetic - (q - z) * s with one rounding, the reference's
-//     f16((q - z) s) - and store fp16 straight into the swizzled operand layout: the dequantisation is fused into
-//     the operand load, HBM carries 4 bits per weight;
-//   * B: the activations, already divided by the AWQ scales and rounded to fp16 (act_scale_kernel), copied by four
-//     warps with 16-byte loads into the same layout.
-// A three-stage ring decouples the producers from the tensor core: full barriers count the eight producer warps,
-// tcgen05.commit releases a stage when its eight MMAs have read it.  After the last group the four producer warps
-// read their 32 TMEM lanes (tcgen05.ld 32x32b), convert and write fp16 outputs.  Every wait is bounded; a wait
-// that runs out sets the device error word, the kernel still frees its tensor memory and returns.
+//   * A: the weights.  Eight warps (thread = row and half of the group) read the packed 4-bit codes, 32 bytes per
+//     thread and stage, and the row's (scale, zero), dequantise in packed fp16 arithmetic - (q - z) * s with one
+//     rounding, the reference's f16((q - z) s) - and store fp16 straight into the swizzled operand layout: the
+//     dequantisation is fused into the operand load, HBM carries 4 bits per weight.  The codes of the next stage
+//     are requested before the current one is converted;
+//   * B: the activations, already divided by the AWQ scales and rounded to fp16 (act_scale_kernel), brought in by
+//     two warps with 16-byte cp.async copies into the same layout, two stages in flight.
+// A three-stage ring decouples the producers from the tensor core: full barriers count the ten producer warps,
+// tcgen05.commit releases a stage when its eight MMAs have read it.  After the last group warps 0-3 read their 32
+// TMEM lanes each (tcgen05.ld 32x32b), convert and write fp16 outputs.  Every wait is bounded; a wait that runs
+// out sets the device error word, the kernel still frees its tensor memory and returns.
 #include "common.cuh"
 #include "v2_device.cuh"
 
@@ -25,8 +26,10 @@ namespace {
 
 constexpr int kGM = 128;       // weight rows per CTA = UMMA M
 constexpr int kGK = 128;       // columns per stage = one quantisation group = two 64-column swizzle atoms
-constexpr int kGStages = 3;
-constexpr int kGThreads = 9 * 32;  // warps 0-3: weights + epilogue, 4-7: activations, 8: tensor memory + MMA issue
+constexpr int kGAhead = 4;      // stages of packed codes a weight thread keeps in flight in registers
+constexpr int kGWarpsA = 8, kGWarpsB = 4;       // warps 0-7: weights (0-3 also the epilogue), 8-11: activations, 12: tensor memory + MMA issue
+constexpr int kGThreads = (kGWarpsA + kGWarpsB + 1) * 32;
+constexpr int kGMmaWarp = kGWarpsA + kGWarpsB;
 
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     // shared-memory matrix descriptor, K-major, 128-byte swizzle: start address >> 4 in bits 0-13, leading byte
@@ -92,8 +95,14 @@ __device__ __forceinline__ uint4 dequant8_slow(uint32_t w, float z, float s) {  
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// ring depth by token tile: 96 KB per stage at TN = 256 leaves room for two, 64 KB at TN = 128 for three (deeper rings
+// measured no faster: the weight warps, not the pipeline depth, set the pace)
+template <int TN>
+constexpr int gemm_stages() { return TN >= 256 ? 2 : 3; }
+
 template <int TN>
 __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p) {
+    constexpr int kGStages = gemm_stages<TN>();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of every operand buffer: the swizzle is a function of the address bits
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -109,13 +118,13 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
     pdl_trigger();
     if (tid == 0) {
         for (int i = 0; i < kGStages; i++) {
-            mbar_init(&full[i], 8);
+            mbar_init(&full[i], kGWarpsA + kGWarpsB);
             mbar_init(&empty[i], 1);
         }
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {  // TN f32 columns of tensor memory for the accumulator
+    if (warp == kGMmaWarp) {  // TN f32 columns of tensor memory for the accumulator
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TN < 32 ? 32 : TN)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -128,61 +137,111 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
 
     const int G = p.G;
     bool ok = true;
-    if (warp < 4) {
+    if (warp < kGWarpsA) {
         // ---------------------------------------------------------------- weights: dequantise into operand A
-        const int r = tid, n = n0 + r;
+        // thread = (row r, half h of the group): 64 columns = 32 bytes of codes per stage, one swizzle atom.  The
+        // codes of the next stage are requested before this stage is converted, so the memory latency is paid once.
+        const int r = tid & 127, h = tid >> 7, n = n0 + r;
         const bool live = n < p.N;
-        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * (p.K / 2);
+        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * (p.K / 2) + h * 32;
         const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * G;
-        const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        for (int kt = 0; kt < G; kt++) {
-            const int s = kt % kGStages, use = kt / kGStages;
-            if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
-            const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)kt * 64);
-            uint4 w[4];
+        const uint32_t row_off = (uint32_t)(h * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
+        // register ring of the next kGAhead stages' codes: 32 bytes per stage in flight per thread, enough to cover the
+        // memory latency at one stage per ~0.3 us
+        uint4 wb[kGAhead][2];
+        __half2 szb[kGAhead];
 #pragma unroll
-            for (int i = 0; i < 4; i++) w[i] = live ? ldg_stream_v4(src + i) : make_uint4(0, 0, 0, 0);
-            const __half2 szv = szrow[kt];
-            const float zf = __high2float(szv), sf = __low2float(szv);
-            const bool fast = zf == rintf(zf) && zf >= -1024.0f && zf <= 1023.0f;
-            const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szv));
-            unsigned char *dst = As + (size_t)s * kABytes + row_off;
-            const uint32_t *ww = reinterpret_cast<const uint32_t *>(w);
-#pragma unroll
-            for (int c = 0; c < 16; c++) {  // chunk c = columns 8c .. 8c+7 of the group
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (live) v = fast ? dequant8_fast(ww[c], c2, s2) : dequant8_slow(ww[c], zf, sf);
-                *reinterpret_cast<uint4 *>(dst + (c >> 3) * (kGM * 128) + (((c & 7) ^ (r & 7)) << 4)) = v;
+        for (int u = 0; u < kGAhead; u++) {
+            wb[u][0] = wb[u][1] = make_uint4(0, 0, 0, 0);
+            szb[u] = __floats2half2_rn(0.0f, 0.0f);
+            if (live && u < G) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)u * 64);
+                wb[u][0] = ldg_stream_v4(src);
+                wb[u][1] = ldg_stream_v4(src + 1);
+                szb[u] = szrow[u];
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
         }
-    } else if (warp < 8) {
-        // ---------------------------------------------------------------- activations: copy into operand B
-        const int t2 = tid - 128;
-        constexpr int kPer = TN / 8;                 // 16-byte chunks per thread and stage (TN * 16 chunks / 128 threads)
-        const int trow = t2 % TN, c_lo = (t2 / TN) * kPer;
-        const int m = m0 + trow;
-        const bool live = m < p.M;
-        const __half *xrow = p.xs + (size_t)(live ? m : 0) * p.K;
-        const uint32_t row_off = (uint32_t)((trow >> 3) * 1024 + (trow & 7) * 128);
-        for (int kt = 0; kt < G; kt++) {
-            const int s = kt % kGStages, use = kt / kGStages;
-            if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
-            const uint4 *src = reinterpret_cast<const uint4 *>(xrow + (size_t)kt * kGK);
-            uint4 v[kPer];
+        for (int kt0 = 0; kt0 < G; kt0 += kGAhead) {
 #pragma unroll
-            for (int i = 0; i < kPer; i++) v[i] = live ? src[c_lo + i] : make_uint4(0, 0, 0, 0);
-            unsigned char *dst = Bs + (size_t)s * kBBytes + row_off;
-#pragma unroll
-            for (int i = 0; i < kPer; i++) {
-                const int c = c_lo + i;
-                *reinterpret_cast<uint4 *>(dst + (c >> 3) * (TN * 128) + (((c & 7) ^ (trow & 7)) << 4)) = v[i];
+            for (int u = 0; u < kGAhead; u++) {
+                const int kt = kt0 + u;
+                if (kt < G) {  // warp-uniform
+                    const int s = kt % kGStages, use = kt / kGStages;
+                    const uint32_t w0 = wb[u][0].x, w1 = wb[u][0].y, w2 = wb[u][0].z, w3 = wb[u][0].w;
+                    const uint32_t w4 = wb[u][1].x, w5 = wb[u][1].y, w6 = wb[u][1].z, w7 = wb[u][1].w;
+                    const __half2 szc = szb[u];
+                    if (live && kt + kGAhead < G) {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)(kt + kGAhead) * 64);
+                        wb[u][0] = ldg_stream_v4(src);
+                        wb[u][1] = ldg_stream_v4(src + 1);
+                        szb[u] = szrow[kt + kGAhead];
+                    }
+                    // convert into registers first: only the eight stores wait for the slot to be free
+                    const float zf = __high2float(szc), sf = __low2float(szc);
+                    const bool fast = zf == rintf(zf) && zf >= -1024.0f && zf <= 1023.0f;
+                    uint4 v0, v1, v2, v3, v4, v5, v6, v7;
+                    // Two real branches (not a select): the f32 path costs three times the packed one and almost no group
+                    // needs it.  Rows past N carry zero codes and a zero scale, which dequantise to zero.
+                    if (__builtin_expect(fast, 1)) {
+                        const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szc));
+                        v0 = dequant8_fast(w0, c2, s2); v1 = dequant8_fast(w1, c2, s2); v2 = dequant8_fast(w2, c2, s2); v3 = dequant8_fast(w3, c2, s2);
+                        v4 = dequant8_fast(w4, c2, s2); v5 = dequant8_fast(w5, c2, s2); v6 = dequant8_fast(w6, c2, s2); v7 = dequant8_fast(w7, c2, s2);
+                    } else {
+                        v0 = dequant8_slow(w0, zf, sf); v1 = dequant8_slow(w1, zf, sf); v2 = dequant8_slow(w2, zf, sf); v3 = dequant8_slow(w3, zf, sf);
+                        v4 = dequant8_slow(w4, zf, sf); v5 = dequant8_slow(w5, zf, sf); v6 = dequant8_slow(w6, zf, sf); v7 = dequant8_slow(w7, zf, sf);
+                    }
+                    if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
+                    unsigned char *dst = As + (size_t)s * kABytes + row_off;
+                    const int x = r & 7;  // chunk c = columns 64h + 8c .. + 7 of the group, stored at chunk c ^ (row & 7)
+                    *reinterpret_cast<uint4 *>(dst + ((0 ^ x) << 4)) = v0;
+                    *reinterpret_cast<uint4 *>(dst + ((1 ^ x) << 4)) = v1;
+                    *reinterpret_cast<uint4 *>(dst + ((2 ^ x) << 4)) = v2;
+                    *reinterpret_cast<uint4 *>(dst + ((3 ^ x) << 4)) = v3;
+                    *reinterpret_cast<uint4 *>(dst + ((4 ^ x) << 4)) = v4;
+                    *reinterpret_cast<uint4 *>(dst + ((5 ^ x) << 4)) = v5;
+                    *reinterpret_cast<uint4 *>(dst + ((6 ^ x) << 4)) = v6;
+                    *reinterpret_cast<uint4 *>(dst + ((7 ^ x) << 4)) = v7;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[s]);
+                }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    } else if (warp < kGMmaWarp) {
+        // ---------------------------------------------------------------- activations: cp.async into operand B
+        // 64 threads keep two stages of 16-byte asynchronous copies in flight; a stage is announced once its group of
+        // copies has landed (rows past the last token are zero-filled by a copy of source size 0).
+        // 128 threads: thread = (16-byte chunk c of the 256-byte row segment, row r0 of every group of eight rows), so its
+        // swizzled destination is one constant plus 1024 bytes per step and its source one pointer plus 8 rows per step.
+        const int t2 = tid - kGWarpsA * 32;
+        constexpr int kPer = TN / 8, kAhead = 2;
+        const int c = t2 & 15, r0 = t2 >> 4;
+        const uint32_t off0 = (uint32_t)((c >> 3) * (TN * 128) + r0 * 128 + (((c & 7) ^ r0) << 4));
+        const __half *src0 = p.xs + (size_t)c * 8;
+        for (int it = 0; it < G + kAhead; it++) {
+            // announce the stage whose copies have landed BEFORE waiting for a free slot for the next one: the other
+            // order would make every MMA wait for its predecessor to retire
+            if (it >= kAhead) {
+                asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[(it - kAhead) % kGStages]);
+            }
+            if (it < G) {
+                const int s = it % kGStages, use = it / kGStages;
+                if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
+                const uint32_t d0 = smem_u32(Bs + (size_t)s * kBBytes) + off0;
+                const __half *sk = src0 + (size_t)it * kGK;
+#pragma unroll 8
+                for (int i = 0; i < kPer; i++) {
+                    const int m = m0 + r0 + 8 * i;
+                    const bool in = m < p.M;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d0 + (uint32_t)i * 1024u), "l"(sk + (size_t)(in ? m : 0) * p.K),
+                                 "r"(in ? 16 : 0)
+                                 : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
     } else {
         // ---------------------------------------------------------------- one thread issues the MMAs
@@ -230,7 +289,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
+    if (warp == kGMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TN < 32 ? 32 : TN) : "memory");
     }
@@ -258,6 +317,7 @@ __global__ void act_scale_kernel(const __half *__restrict__ x, const __half *__r
 
 template <int TN>
 int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
+    constexpr int kGStages = gemm_stages<TN>();
     const size_t smem = 1024 + (size_t)kGStages * (kGM * kGK * 2 + TN * kGK * 2) + (2 * kGStages + 1) * 8 + 16;
     if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
     auto kern = gemm_int4_tc_kernel<TN>;
@@ -280,6 +340,10 @@ int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __h
     const size_t n = (size_t)M * w->K;
     IM_CUDA_CHECK(launch_k(act_scale_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, x, (const __half *)w->awq, xs_scratch, n, w->K));
     GemmParams p{w->codes, w->sz, xs_scratch, y, w->N, w->K, w->G, M, w->dev->err_flag};
+    // a 256-token tile shares every dequantised weight tile between twice as many tokens, but halves the CTA count:
+    // worth it only once the grid still covers the GPU
+    const long long ctas256 = (long long)((w->N + kGM - 1) / kGM) * ((M + 255) / 256);
+    if (M > 128 && ctas256 >= w->dev->sm_count) return gemm_launch<256>(p, w->dev, st);
     if (M > 64) return gemm_launch<128>(p, w->dev, st);
     if (M > 32) return gemm_launch<64>(p, w->dev, st);
     return gemm_launch<32>(p, w->dev, st);

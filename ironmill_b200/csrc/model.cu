@@ -1092,8 +1092,10 @@ IM_EXPORT int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, in
         return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->seq_pos, n, m->cfg.max_seq_len);
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
-    for (int done = 0; done < n; done += kPrefillChunk) {
-        const int T = n - done < kPrefillChunk ? n - done : kPrefillChunk;
+    // 256-token chunks when the projections run as tensor-core GEMMs; the matvec kernels take at most 64 rows per call
+    const int chunk = (m->gemm_ok && m->world == 1) ? kPrefillChunk : 64;
+    for (int done = 0; done < n; done += chunk) {
+        const int T = n - done < chunk ? n - done : chunk;
         memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
         IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
         const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->seq_pos + T);
