@@ -88,7 +88,6 @@ struct V2Params {
     float *partial;  // [grid][2][64]
     int *counters;   // [nblk], zero between launches
     int *err;
-    unsigned long long *trace;  // optional: 8 timer stamps from CTA 0 (development aid), else nullptr
 };
 
 // INT4 g128 GEMM on tcgen05 / TMEM (gemm_tc.cu): y[M, N] = f16(x / awq) * dequant(w)^T; xs_scratch holds M * K halves.

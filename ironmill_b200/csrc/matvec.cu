@@ -510,7 +510,6 @@ static int pick_ksplit(const Device *dev, int N, int K, int R, int chunk) {
     return ks;
 }
 
-unsigned long long *g_v2_trace = nullptr;  // development aid, see im_cuda_debug_set_trace
 
 // Gate/up pair as one tile stream (8 gate rows + 8 up rows per tile), built the first time the pair is used.
 int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaStream_t st) {
@@ -543,7 +542,7 @@ static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const Aff
     }
     q.awq = p.awq; q.gamma = p.gamma; q.eps = p.eps;
     q.N = p.N; q.K = p.K; q.G = p.G;
-    q.partial = w->dev->sk_partial; q.counters = w->dev->sk_counters; q.err = w->dev->err_flag; q.trace = g_v2_trace;
+    q.partial = w->dev->sk_partial; q.counters = w->dev->sk_counters; q.err = w->dev->err_flag;
     int done = 0;
     while (done < B) {
         const int nb = B - done >= 4 ? 4 : (B - done >= 2 ? 2 : 1);
@@ -868,7 +867,6 @@ IM_EXPORT int im_cuda_matvec_f16(const void *w_dev, const void *x_dev, void *y_d
 
 // Development aid (not part of the documented ABI): device buffer of 8 u64 that CTA 0 of the tiled matvec
 // fills with %globaltimer stamps (start, activations staged, first stage ready, second stage ready, loop end, end).
-IM_EXPORT void im_cuda_debug_set_trace(void *dev_u64x8) { im::g_v2_trace = static_cast<unsigned long long *>(dev_u64x8); }
 
 // superblock_matmul_int4 (crates/ironmill-inference/src/metal/shaders/quantized/affine_matmul.metal:10-152) on the
 // tcgen05 tensor cores (gemm_tc.cu).  INT4 group-128 weights only.

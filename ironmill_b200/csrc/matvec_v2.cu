@@ -133,9 +133,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     const int t_begin = p.split_tiles ? (int)((long long)total * blockIdx.x / gridDim.x) : (int)((long long)p.nblk * blockIdx.x / gridDim.x) * G;
     const int t_end = p.split_tiles ? (int)((long long)total * (blockIdx.x + 1) / gridDim.x) : (int)((long long)p.nblk * (blockIdx.x + 1) / gridDim.x) * G;
 
-#define IM_STAMP(i) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[i] = global_ns(); } while (0)
     pdl_trigger();
-    IM_STAMP(0);
     if (tid == 0) {
         for (int i = 0; i < nring; i++) {
             mbar_init(&full[i], 1);
@@ -259,7 +257,6 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         }
     }
     consumer_sync();
-    IM_STAMP(1);
     float rms_inv[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) rms_inv[b] = (MODE & 2) ? rsqrtf(sq_tot[b] / (float)p.K + p.eps) : 1.0f;
@@ -307,7 +304,6 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
             phase ^= 1;
         }
     }
-    IM_STAMP(4);
 }
 
 // ---- load-time repack -------------------------------------------------------
