@@ -111,7 +111,7 @@ __device__ __forceinline__ void stage_chunk(float (&v)[8], bool live, int grp, i
         uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 1) * 4 + t) * 4 + j) * 2);
         *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
         *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
-        if (hl == 0) meta[grp] = make_float2(sx, (float)lsum);
+        if (hl == 0) meta[grp] = make_float2(sx * 0.0625f, (float)(lsum * 16));  // TileMath accumulates 16 x the integer dot product
     }
 }
 __device__ __forceinline__ void unpack2(unsigned w, float &a, float &b) {  // two fp16 values of a word, no address taken
@@ -358,24 +358,6 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 skip_empty_done();
             }
         };
-        // A third cursor runs l2_ahead stages in front of the copies and asks L2 for those tiles: HBM then keeps
-        // streaming while the ring is full and the consumers are busy with attention or a barrier.
-        Cursor pf{0, StageIter(0, 0, 1), MegaPhase{}};
-        open(pf, 0);
-        auto prefetch_one = [&]() {
-            int pt0, pn, prb, pgrp;
-            while (pf.q < NP) {
-                if (!pf.it.next(pt0, pn, prb, pgrp)) {
-                    open(pf, pf.q + 1);
-                    continue;
-                }
-                if (lane == 1)
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ph.tiles + (size_t)pt0 * kTileBytes), "r"(pn * kTileBytes)
-                                 : "memory");
-                return;
-            }
-        };
-        for (int i = 0; i < p.l2_ahead; i++) prefetch_one();
         int slot = 0, phase = 0, nstages = 0;
         int t0, n, rb0, grp0;
         while (issue.q < NP) {
@@ -383,7 +365,6 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 open(issue, issue.q + 1);
                 continue;
             }
-            if (p.l2_ahead > 0) prefetch_one();
             if (nstages >= nring) reclaim(slot, phase ^ 1);
             if (lane == 0) {
                 mbar_expect_tx(&full[slot], (uint32_t)(n * kTileBytes));
@@ -516,18 +497,26 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                         mega_prep_item(gs, a, sh, item);
             }
             items_done(7 * l + 1);
+            // This group's first attention item: its cached rows do not depend on this layer's cache write (only the row
+            // of the token being decoded does), so L2 is asked for them before the barrier (no registers held across it).
+            AttnParams ap;
+            ap.q = nullptr; ap.kc = ly.kc; ap.vc = ly.vc; ap.ks = ly.ks; ap.vs = ly.vs; ap.krn = ly.krn;
+            ap.signs = p.signs; ap.qjl = p.qjl_t; ap.k_cb = p.k_cb; ap.v_cb = p.v_cb; ap.qrot = p.qrot;
+            ap.po = p.po; ap.pm = p.pm; ap.pl = p.pl; ap.attn_scale = p.attn_scale; ap.qjl_factor = p.qjl_factor;
+            ap.nh = p.nh; ap.nkv = p.nkv; ap.max_seq = p.max_seq; ap.base_pos = 0; ap.T = 1; ap.splits = p.splits; ap.pos_dev = p.pos;
+            const int item0 = blockIdx.x + gridDim.x * group;
+            const bool have0 = !dead && item0 < p.nkv * used;
+            if (have0) {
+                const int split = item0 / p.nkv;
+                tq_attention_l2_prefetch(gs.d, ap, item0 % p.nkv, 0, split * chunk, min(split * chunk + chunk, seq_len), seq_len - 1);
+            }
             grid_wait(7 * l + 1);
 
             // ---- split attention: one (KV head, split) per group
             {
-                AttnParams ap;
-                ap.q = nullptr; ap.kc = ly.kc; ap.vc = ly.vc; ap.ks = ly.ks; ap.vs = ly.vs; ap.krn = ly.krn;
-                ap.signs = p.signs; ap.qjl = p.qjl_t; ap.k_cb = p.k_cb; ap.v_cb = p.v_cb; ap.qrot = p.qrot;
-                ap.po = p.po; ap.pm = p.pm; ap.pl = p.pl; ap.attn_scale = p.attn_scale; ap.qjl_factor = p.qjl_factor;
-                ap.nh = p.nh; ap.nkv = p.nkv; ap.max_seq = p.max_seq; ap.base_pos = 0; ap.T = 1; ap.splits = p.splits; ap.pos_dev = p.pos;
                 AttnSmem<GQ> &sm = reinterpret_cast<AttnSmem<GQ> *>(U)[group];
                 if (!dead)
-                    for (int item = blockIdx.x + gridDim.x * group; item < p.nkv * used; item += gridDim.x * kGroups) {
+                    for (int item = item0; item < p.nkv * used; item += gridDim.x * kGroups) {
                         const int kvh = item % p.nkv, split = item / p.nkv;
                         mega_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, split, split * chunk, min(split * chunk + chunk, seq_len));
                     }

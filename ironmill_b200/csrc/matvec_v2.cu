@@ -100,7 +100,7 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
             uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 * NB + 2 * b + 1) * 4 + t) * 4 + j) * 2);
             *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
             *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
-            if (hl == 0) meta[grp * NB + b] = make_float2(sx, (float)lsum);
+            if (hl == 0) meta[grp * NB + b] = make_float2(sx * 0.0625f, (float)(lsum * 16));  // TileMath accumulates 16 x the integer dot product
         }
     }
     return sq;

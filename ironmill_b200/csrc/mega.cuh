@@ -38,7 +38,6 @@ struct MegaParams {
     int max_seq, rotary_dim, with_qk_norm;
     int splits;               // attention items per KV head (capacity of the partial buffers)
     int nring;                // ring slots
-    int l2_ahead;             // stages the producer asks L2 for ahead of its copies (0 = none)
     int u_bytes;              // shared-memory scratch shared by the phases
     int g_max;                // largest group count of any phase (sizes the activation staging area)
     unsigned *bar;            // 7 * L arrival counters + 1 exit counter, zero between launches

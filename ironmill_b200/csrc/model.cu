@@ -582,12 +582,6 @@ static int mega_prepare(Model *m) {
     p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)c.head_dim;
     p.max_seq = c.max_seq_len; p.rotary_dim = c.rotary_dim ? c.rotary_dim : c.head_dim; p.with_qk_norm = c.qk_norm ? 1 : 0;
     p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max;
-    {
-        const char *la = getenv("IM_MEGA_L2AHEAD");
-        p.l2_ahead = la ? atoi(la) : 0;  // measured: asking L2 ahead of the copies slows the stream down; off unless set
-        if (p.l2_ahead < 0) p.l2_ahead = 0;
-        if (p.l2_ahead > 64) p.l2_ahead = 64;
-    }
     IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;

@@ -121,10 +121,9 @@ __device__ __forceinline__ float tq_tree_sum(const Scope &sc, float v, float *bu
 // tails of the trees run on warp shuffles instead of shared memory + barriers; the operands are the same.
 template <class Scope>
 __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
-                                               float *scale_out, float *rnorm_out) {
+                                               float *scale_out, float *rnorm_out, float sg) {
     float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
     const int d = sc.d;
-    const float sg = tb.signs[d];
     float v = __fmul_rn(xin, sg);
 #pragma unroll
     for (int step = 1; step < 32; step <<= 1) {  // pair (j, j + step): lower index gets a + b, upper a - b
@@ -180,6 +179,12 @@ __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const
     sc.sync();  // sh may be reused by the caller
 }
 
+template <class Scope>
+__device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
+                                               float *scale_out, float *rnorm_out) {
+    tq_encode_body(sc, xin, tb, sh, hd, cache_row, scale_out, rnorm_out, tb.signs[sc.d]);
+}
+
 // ---------------------------------------------------------------- attention
 struct AttnParams {
     const __half *q;         // [nseq*T, nh, hd]
@@ -208,6 +213,21 @@ struct AttnSmem {  // per work item (128 threads)
     float sc[GQ * kTile];
     float s_m[GQ], s_l[GQ], s_corr[GQ];
 };
+
+// Ask L2 for the first tile of an item (rows of positions below `limit` only) without holding anything in registers:
+// issued before the barrier that publishes the query rotation and the new cache row, it turns the item's first cache
+// reads from HBM misses into L2 hits.
+__device__ __forceinline__ void tq_attention_l2_prefetch(int tid, const AttnParams &p, int kvh, int seq, int r0, int r1, int limit) {
+    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const int nt = min(kTile, min(r1, limit) - r0);
+    if (tid < nt) {  // one 128-byte row of K and of V per thread
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kc + (head_base + r0 + tid) * kHd));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vc + (head_base + r0 + tid) * kHd));
+    } else if (tid >= 32 && tid < 35 && nt > 0) {  // the tile's scales: 32 floats = one line each
+        const float *b = tid == 32 ? p.ks : (tid == 33 ? p.krn : p.vs);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(b + head_base + r0));
+    }
+}
 
 // One (kv head, token, split) item on a 128-thread scope: positions [r0, r1) of the sequence against the GQ
 // query heads of the group.  cbk / cbv: the K (128) and V (256) codebooks in shared memory, filled by the caller.
@@ -431,10 +451,11 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     const int seq = st / a.T, t = st % a.T;
     const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
     const __half *tok = a.qkv + (size_t)st * a.stride;
+    const float sg = a.ktab.signs[d];  // requested together with the head's values, not after the RoPE
     if (slot >= a.nh + a.nkv) {  // value head
         const int h = slot - a.nh - a.nkv;
         const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(sc, __half2float(tok[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, (float *)nullptr);
+        tq_encode_body(sc, __half2float(tok[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, (float *)nullptr, sg);
         return;
     }
     const bool is_q = slot < a.nh;
@@ -463,11 +484,11 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     sc.sync();
     if (!is_q) {
         const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row);
+        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row, sg);
         return;
     }
     if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;
-    const float rq = hadamard_thread(sc, __half2float(yh), a.ktab.signs[d], sh + kHd, kHd);
+    const float rq = hadamard_thread(sc, __half2float(yh), sg, sh + kHd, kHd);
     sh[d] = rq;
     float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
     dst[d] = rq;

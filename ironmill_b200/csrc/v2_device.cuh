@@ -72,7 +72,8 @@ __device__ __forceinline__ void mma_u8s8_z(int (&c)[4], unsigned a0, unsigned a1
 }
 
 // The arithmetic of the consumer warps: two tiles (16 rows x 128 columns of 4-bit codes each) against the staged
-// activations of their groups, then the per-(row, group) float fix-up  s * sx * (sum_k xi_k q_k - z * sum_k xi_k).
+// activations of their groups, then the per-(row, group) float fix-up  s * sx * (sum_k xi_k q_k - z * sum_k xi_k)
+// (with meta = (sx / 16, 16 * sum_k xi_k): the integer dot product arrives multiplied by 16, see pair()).
 // Lane (g = lane >> 2, t = lane & 3) holds rows g and g + 8 of batch row t in acc0 / acc1.
 // The activation fragments of a group stay in registers until the warp is handed another group: with K = 4096 a
 // stage is a whole row block, every warp sees the same two groups stage after stage, and the fragments are read
@@ -114,23 +115,27 @@ struct TileMath {
                 xb1 = xp[1];
             }
         }
-        // two independent accumulator chains per tile: the second product of a chain does not wait for four others
-        int ca0[4], ca1[4], cb0[4], cb1[4];
-        constexpr unsigned M = 0x0F0F0F0Fu;
-        mma_u8s8_z(ca0, a0.x & M, a1.x & M, (a0.x >> 4) & M, (a1.x >> 4) & M, xa0.x, xa0.y);
-        mma_u8s8_z(cb0, b0.x & M, b1.x & M, (b0.x >> 4) & M, (b1.x >> 4) & M, xb0.x, xb0.y);
-        mma_u8s8_z(ca1, a0.y & M, a1.y & M, (a0.y >> 4) & M, (a1.y >> 4) & M, xa0.z, xa0.w);
-        mma_u8s8_z(cb1, b0.y & M, b1.y & M, (b0.y >> 4) & M, (b1.y >> 4) & M, xb0.z, xb0.w);
-        mma_u8s8(ca0, a0.z & M, a1.z & M, (a0.z >> 4) & M, (a1.z >> 4) & M, xa1.x, xa1.y);
-        mma_u8s8(cb0, b0.z & M, b1.z & M, (b0.z >> 4) & M, (b1.z >> 4) & M, xb1.x, xb1.y);
-        mma_u8s8(ca1, a0.w & M, a1.w & M, (a0.w >> 4) & M, (a1.w >> 4) & M, xa1.z, xa1.w);
-        mma_u8s8(cb1, b0.w & M, b1.w & M, (b0.w >> 4) & M, (b1.w >> 4) & M, xb1.z, xb1.w);
+        // Low and high nibbles go to separate accumulators: the low ones masked in place, the high ones masked in place
+        // too (a byte 16 q, still a valid u8), so a word costs two logic operations and no shift.  The two chains are
+        // independent; the fix-up adds them as 16 * low + high16, and the staged activation scale carries the 1/16.
+        // B columns of a group: words (even positions, odd positions) of each 8-byte chunk: the low nibbles of a code
+        // word are the even columns, the high nibbles the odd ones.
+        int cal[4], cah[4], cbl[4], cbh[4];
+        constexpr unsigned ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
+        mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, xa0.x, xa0.z);
+        mma_u8s8_z(cbl, b0.x & ML, b1.x & ML, b0.y & ML, b1.y & ML, xb0.x, xb0.z);
+        mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, xa0.y, xa0.w);
+        mma_u8s8_z(cbh, b0.x & MH, b1.x & MH, b0.y & MH, b1.y & MH, xb0.y, xb0.w);
+        mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, xa1.x, xa1.z);
+        mma_u8s8(cbl, b0.z & ML, b1.z & ML, b0.w & ML, b1.w & ML, xb1.x, xb1.z);
+        mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, xa1.y, xa1.w);
+        mma_u8s8(cbh, b0.z & MH, b1.z & MH, b0.w & MH, b1.w & MH, xb1.y, xb1.w);
         if (t < NB) {
             {
                 const float2 m = meta[grp_a * NB + t];
                 const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
                 const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)((ca0[0] + ca1[0]) * 256 + ca0[1] + ca1[1]), f1 = (float)((ca0[2] + ca1[2]) * 256 + ca0[3] + ca1[3]);
+                const float f0 = (float)(cal[0] * 4096 + (cal[1] * 16 + (cah[0] * 256 + cah[1]))), f1 = (float)(cal[2] * 4096 + (cal[3] * 16 + (cah[2] * 256 + cah[3])));
                 acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
                 acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
             }
@@ -138,7 +143,7 @@ struct TileMath {
                 const float2 m = meta[grp_b * NB + t];
                 const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
                 const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)((cb0[0] + cb1[0]) * 256 + cb0[1] + cb1[1]), f1 = (float)((cb0[2] + cb1[2]) * 256 + cb0[3] + cb1[3]);
+                const float f0 = (float)(cbl[0] * 4096 + (cbl[1] * 16 + (cbh[0] * 256 + cbh[1]))), f1 = (float)(cbl[2] * 4096 + (cbl[3] * 16 + (cbh[2] * 256 + cbh[3])));
                 acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
                 acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
             }
