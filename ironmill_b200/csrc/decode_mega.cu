@@ -31,6 +31,8 @@ namespace {
 constexpr int kGroups = kV2Consumers / 4;      // 128-thread groups of consumer warps
 constexpr int kRedFloats = kV2Consumers * 16;  // per ring slot: 16 row sums from each consumer warp
 constexpr int kStageBytes = kStageTiles * kTileBytes;
+constexpr int kPhaseWords = sizeof(MegaPhase) / 4, kLayerWords = sizeof(MegaLayer) / 4;
+constexpr int kDescWords = (5 * kPhaseWords + kLayerWords + 3) & ~3;  // per layer: phases 4l .. 4l+4, then the layer block
 
 struct Range {
     int t_begin, t_end;
@@ -272,12 +274,25 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
     float *bdk = cbv + 256;                          // suffix-minimum boundary tables of the encoder: K (127), V (255)
     float *bdv = bdk + 128;
     float *misc = bdv + 256;                         // [0] rms_inv, [8..23] reduction scratch, [30] wait result
-    uint64_t *full = reinterpret_cast<uint64_t *>(misc + 32);
+    // descriptors of the current and the next layer (5 phase blocks per layer: the four projections and the next
+    // layer's QKV; plus the layer block), copied one layer ahead so that no phase starts with a global load
+    uint32_t *desc = reinterpret_cast<uint32_t *>(misc + 32);   // [2][kDescWords]
+    uint64_t *full = reinterpret_cast<uint64_t *>(desc + 2 * kDescWords);
     uint64_t *empty = full + nring;
     unsigned char *U = reinterpret_cast<unsigned char *>(empty + nring);  // phase scratch (16-byte aligned by construction)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NP = 4 * p.L;
+    // words of layer l's descriptors -> desc[l & 1]; called by consumer threads one layer ahead (and for layer 0 at start)
+    auto copy_desc = [&](int l, int t, int nthreads) {
+        uint32_t *dst = desc + (l & 1) * kDescWords;
+        const uint32_t *src_ph = reinterpret_cast<const uint32_t *>(p.phases + 4 * l);
+        const int nph = min(5, NP - 4 * l) * kPhaseWords;
+        for (int i = t; i < nph; i += nthreads) dst[i] = src_ph[i];
+        const uint32_t *src_ly = reinterpret_cast<const uint32_t *>(p.layers + l);
+        for (int i = t; i < kLayerWords; i += nthreads) dst[5 * kPhaseWords + i] = src_ly[i];
+    };
+    copy_desc(0, tid, kV2Threads);
 
     if (tid == 0) {
         for (int i = 0; i < nring; i++) {
@@ -414,7 +429,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 
         // One projection: stage the activations, then walk this CTA's stages of the phase.
         auto matvec_phase = [&](int q, int fine) {  // fine >= 0: CTA 0 records 24 stamps at trace[fine..]
-            const MegaPhase ph = p.phases[q];
+            const MegaPhase ph = *reinterpret_cast<const MegaPhase *>(desc + ((q >> 2) & 1) * kDescWords + (q & 3) * kPhaseWords);
             const int G = ph.G;
             const bool stamp = p.trace && fine >= 0 && blockIdx.x == 0 && tid == 0;
             if (stamp) p.trace[fine] = global_ns();
@@ -433,7 +448,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             consumer_sync();
             if (q + 1 < NP) {  // the next projection's activation scales and norm weight: one pass through a 4.9 GB weight
                                // stream evicts them from L2 every token, so ask for them now, one 128-byte line per thread
-                const MegaPhase nx = p.phases[q + 1];
+                const MegaPhase nx = *reinterpret_cast<const MegaPhase *>(desc + ((q >> 2) & 1) * kDescWords + ((q & 3) + 1) * kPhaseWords);
                 for (int i = blockIdx.x + gridDim.x * tid; i < 2 * nx.G; i += gridDim.x * kV2Consumers * 32) {
                     if (nx.awq) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.awq + i * 64));
                     if (nx.gamma) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.gamma + i * 64));
@@ -475,11 +490,14 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         const int used = (seq_len + chunk - 1) / chunk;  // splits that hold positions (<= p.splits)
 
         for (int l = 0; l < p.L; l++) {
-            const MegaLayer ly = p.layers[l];
+            const MegaLayer ly = *reinterpret_cast<const MegaLayer *>(desc + (l & 1) * kDescWords + 5 * kPhaseWords);
             // ---- QKV (layer 0: plain, on the normalised embedding; later layers: residual + norm prologue)
             if (l > 0) grid_wait(7 * l - 1);
             matvec_phase(4 * l, l == 1 ? 7 * p.L + 2 : -1);
             grid_wait(7 * l);
+            // the next layer's descriptors: the buffer's previous tenant (layer l - 1) was last read before the barrier above
+            // (by the threads of groups 1-3: group 0 carries the head items of the phase that starts here)
+            if (l + 1 < p.L && tid >= 128) copy_desc(l + 1, tid - 128, kV2Consumers * 32 - 128);
 
             // ---- (QK-norm,) RoPE, cache write, query rotation: one head per 128-thread group
             {
@@ -555,7 +573,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 }
 
 size_t mega_smem_bytes(int nring, int u_bytes) {
-    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + (2 * (128 + 256) + 32) * 4 + (size_t)u_bytes;
+    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + (2 * (128 + 256) + 32) * 4 + 2 * kDescWords * 4 + (size_t)u_bytes;
 }
 
 template <int GQ>
