@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload decode|matvec]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload decode|matvec|attention]
                     [--prompt P] [--batch B]
 
 Prints ONE JSON line (rank 0).  Workloads are synthetic and seeded (random-init weights of the named
@@ -17,6 +17,8 @@ shape; no checkpoint or dataset is read):
   matvec  one step = the four INT4 g128 projection launches of one decoder layer at batch 1
           (fused QKV 4096->6144, o 4096->4096, fused gate+up+SiLU 4096->2x14336, down 14336->4096),
           each step on a different weight copy out of a rotation larger than L2; value = GB/s.
+
+  attention  TurboQuant INT8-KV decode attention alone at context --prompt and batch --batch (32 Q / 8 KV heads); GB/s of KV bytes.
 
 `--impl reference` times the CPU restatement of the reference's own CPU path (the oracle) on the host
 cores for the same workload, on a bounded sample.
@@ -45,6 +47,7 @@ L8_SHAPES = [("qkv", 6144, 4096, "plain"), ("o", 4096, 4096, "plain"),
              ("gate_up", 14336, 4096, "ffn"), ("down", 4096, 14336, "plain")]
 METRIC_DECODE = "decode tok/s (Llama-3-8B shape, INT4 g128 + AWQ weights, INT8 TurboQuant KV)"
 METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)"
+METRIC_ATTN = "TurboQuant INT8-KV decode attention HBM GB/s (32 Q / 8 KV heads, head_dim 128)"
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
 PROJ_DRAM_BYTES = 62467840 + 17920          # matvec_v2_kernel<gate+up+SiLU>, one launch
 TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = (970164992 + 28496384) / 8   # decode_token_kernel: capture of the 8-layer model at ~2k context
@@ -418,6 +421,83 @@ def run_matvec(args, rank, world):
     print(json.dumps(out))
 
 
+def run_attention(args, rank, world):
+    """TurboQuant INT8 KV decode attention alone (split attention + reduction), one step = one decode token of `batch`
+    sequences at context --prompt: value = KV bytes read (codes + scales + residual norms) / time.  The cache holds
+    random codes and positive scales (the kernel's work does not depend on the values); rotating over enough cache
+    copies keeps every step's KV out of L2."""
+    import torch
+
+    from ironmill_b200 import ops
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = ops.Device(local)
+    nh, nkv, hd, ctx, B = 32, 8, 128, args.prompt, args.batch
+    signs, qjl = ops.tq_generate(hd, 42)
+    tq = ops.TurboQuant(dev, hd, 8, signs, qjl)
+    kv_bytes = B * nkv * ctx * (2 * hd + 12)
+    ncopy = max(2, int(400e6 // kv_bytes) + 1)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    caches = []
+    for _ in range(ncopy):
+        kc = torch.randint(0, 256, (B, nkv, ctx, hd), generator=g, device="cuda", dtype=torch.uint8)
+        vc = torch.randint(0, 256, (B, nkv, ctx, hd), generator=g, device="cuda", dtype=torch.uint8)
+        ks = torch.rand((B, nkv, ctx), generator=g, device="cuda") + 0.5
+        vs = torch.rand((B, nkv, ctx), generator=g, device="cuda") + 0.5
+        kr = torch.rand((B, nkv, ctx), generator=g, device="cuda") * 0.1
+        caches.append((kc, vc, ks, vs, kr))
+    q = torch.randn((B, nh, hd), generator=g, device="cuda").half()
+    scale = 1.0 / np.sqrt(hd)
+
+    def step(i):
+        kc, vc, ks, vs, kr = caches[i % ncopy]
+        return tq.attention(q, kc, vc, ks, vs, kr, scale, nh, nkv, ctx, ctx - 1, nseq=B)
+
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(ncopy):
+                step(i)
+        graph.replay()
+        s.synchronize()
+        reps = max(1, args.steps // ncopy)
+        sampler = ClockSampler(local)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(s)
+        s.synchronize()
+        clocks = sampler.stop()
+    steps = reps * ncopy
+    ms = e0.elapsed_time(e1)
+    peak, peak_src = measured_peaks()
+    gbs = kv_bytes * steps / (ms * 1e-3) / 1e9
+    qh = q.cpu()
+    w0 = time.perf_counter()
+    for i in range(8):
+        step(i).cpu()
+        q.copy_(qh, non_blocking=False)
+    e2e_s = time.perf_counter() - w0
+    out = {"metric": METRIC_ATTN, "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+           "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "u8 codebook indices, f32 accumulation", "data": "synthetic",
+           "config": {"workload": "turboquant_int8_kv_decode_attention", "context": ctx, "batch": B, "q_heads": nh, "kv_heads": nkv,
+                      "l2_policy": f"rotation over {ncopy} cache copies ({ncopy * kv_bytes >> 20} MiB) larger than L2"},
+           "roofline": {"bound": "hbm", "kernel": "tq_attention_kernel<4> + tq_reduce_kernel", "achieved": round(gbs, 1), "peak": peak,
+                        "unit": "GB/s", "frac": round(gbs / peak, 4), "peak_source": peak_src, "bytes_per_launch": kv_bytes,
+                        "us_per_launch": round(ms / steps * 1e3, 2), "traffic": None},
+           "e2e": {"value": round(kv_bytes * 8 / e2e_s / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": B * nh * hd * 2,
+                   "d2h_bytes_per_step": B * nh * hd * 2},
+           "gpu_launches": 2 * steps, "clocks": clocks}
+    print(json.dumps(out))
+
+
 # ----------------------------------------------------------------------------- CPU arm (the oracle, timed)
 def cpu_matvec_baseline(seconds):
     from oracle import oracle as orc
@@ -508,7 +588,7 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "matvec"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "matvec", "attention"])
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the synthetic model (32 = the named workload; fewer only for profiler captures)")
@@ -519,6 +599,8 @@ def main():
         run_reference(args, rank, world)
     elif args.workload == "matvec":
         run_matvec(args, rank, world)
+    elif args.workload == "attention":
+        run_attention(args, rank, world)
     else:
         run_decode(args, rank, world)
 

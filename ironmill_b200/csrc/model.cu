@@ -23,6 +23,9 @@
 
 #include "common.cuh"
 #include "mega.cuh"
+#if defined(__x86_64__)
+#include <immintrin.h>
+#endif
 
 #if __has_include(<nccl.h>)
 #include <nccl.h>
@@ -644,14 +647,25 @@ static int set_positions(Model *m, int pos) {
     return IM_OK;
 }
 
+// fp16 -> f32 on the host: 128 K logits per step.  With F16C (every x86-64-v3 CPU) eight at a time.
+#if defined(__x86_64__)
+__attribute__((target("avx,f16c"))) static void widen_f16c(const __half *src, float *dst, int n) {
+    int j = 0;
+    for (; j + 8 <= n; j += 8) _mm256_storeu_ps(dst + j, _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i *>(src + j))));
+    for (; j < n; j++) dst[j] = __half2float(src[j]);
+}
+#endif
+static void widen(const __half *src, float *dst, int n) {
+#if defined(__x86_64__)
+    static const bool have = __builtin_cpu_supports("f16c") && __builtin_cpu_supports("avx");
+    if (have) return widen_f16c(src, dst, n);
+#endif
+    for (int j = 0; j < n; j++) dst[j] = __half2float(src[j]);
+}
 static void logits_to_host(const Model *m, const __half *pin, int nseq, float *out) {
     const int vl = m->vocab_l, parts = m->world, V = m->cfg.vocab_size;
     for (int p = 0; p < parts; p++)
-        for (int s = 0; s < nseq; s++) {
-            const __half *src = pin + ((size_t)p * nseq + s) * vl;
-            float *dst = out + (size_t)s * V + (size_t)p * vl;
-            for (int j = 0; j < vl; j++) dst[j] = __half2float(src[j]);
-        }
+        for (int s = 0; s < nseq; s++) widen(pin + ((size_t)p * nseq + s) * vl, out + (size_t)s * V + (size_t)p * vl, vl);
 }
 
 // A kernel whose bounded wait ran out leaves a non-zero word; the step's results are then invalid.  Clears the
