@@ -248,6 +248,8 @@ int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, const void *
                                 const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,
                                 void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
                                 int num_splits, void *stream);
+/* Scratch im_cuda_tq_attention needs for a launch: split partials (nseq*T*nh*splits*(head_dim+2) floats) plus the
+ * rotated queries of its pre-pass (nseq*T*nh*2*head_dim floats).  The handle grows its scratch on demand. */
 size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
 int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
 

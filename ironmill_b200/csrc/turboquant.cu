@@ -155,6 +155,31 @@ __global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict_
 }
 
 
+// Rotated query and S * rotated query for every (token, head), computed once instead of once per split:
+// grid (nh, nseq*T), 128 threads.  q fp16 [nseq*T, nh, 128] -> qrot f32 [nseq*T, nh, 2, 128].
+__global__ void __launch_bounds__(kHd) tq_qrot_kernel(const __half *__restrict__ q, const float *__restrict__ signs,
+                                                      const float *__restrict__ qjl_t, float *__restrict__ qrot, int nh) {
+    __shared__ float sh[2 * kHd];
+    pdl_trigger();
+    pdl_wait();
+    const int d = threadIdx.x;
+    const size_t hi = (size_t)blockIdx.y * nh + blockIdx.x;
+    const CtaScope sc{d, kHd};
+    const float rq = hadamard_thread(sc, __half2float(q[hi * kHd + d]), signs[d], sh + kHd, kHd);
+    sh[d] = rq;
+    __syncthreads();
+    float acc = 0.0f;
+    for (int k0 = 0; k0 < kHd; k0 += 64) {
+        float sv[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) sv[j] = qjl_t[(size_t)(k0 + j) * kHd + d];
+#pragma unroll
+        for (int j = 0; j < 64; j++) acc = fmaf(sv[j], sh[k0 + j], acc);
+    }
+    qrot[hi * 2 * kHd + d] = rq;
+    qrot[hi * 2 * kHd + kHd + d] = acc;
+}
+
 }  // namespace im
 
 using namespace im;
@@ -290,8 +315,12 @@ IM_EXPORT int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, v
     IM_GUARD_END
 }
 
-IM_EXPORT size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits) {
+static size_t tq_partial_bytes(int nseq, int T, int nh, int head_dim, int splits) {
     return (size_t)nseq * T * nh * splits * (head_dim + 2) * sizeof(float);
+}
+// split partials, then the rotated queries of im_cuda_tq_attention's pre-pass
+IM_EXPORT size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits) {
+    return tq_partial_bytes(nseq, T, nh, head_dim, splits) + (size_t)nseq * T * nh * 2 * head_dim * sizeof(float);
 }
 
 IM_EXPORT int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes) {
@@ -330,7 +359,7 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
 
 int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
     const int ctas = nseq * T * nkv;
-    int s = (2 * dev->sm_count + ctas - 1) / ctas;
+    int s = (4 * dev->sm_count + ctas - 1) / ctas;  // four 128-thread CTAs per SM: an item is latency-bound, more of them in flight pay
     const int by_len = (seq_len + 2 * kTile - 1) / (2 * kTile);  // at least two tiles per split
     if (s > by_len) s = by_len;
     if (s > 128) s = 128;
@@ -385,9 +414,13 @@ IM_EXPORT int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_c
         int rc = im_cuda_tq_reserve_scratch(tq, need);
         if (rc != IM_OK) return rc;
     }
-    return tq_attention_launch(tq, tq->scratch, static_cast<const __half *>(q_dev), static_cast<const uint8_t *>(k_cache_dev),
+    // rotate the queries once (every split of a head would otherwise redo the rotation and the 128 x 128 projection)
+    float *qrot = tq->scratch + tq_partial_bytes(nseq, T, nh, kHd, splits) / sizeof(float);
+    IM_CUDA_CHECK(launch_k(tq_qrot_kernel, dim3(nh, nseq * T), dim3(kHd), 0, as_stream(stream), static_cast<const __half *>(q_dev),
+                           (const float *)tq->signs, (const float *)tq->qjl_t, qrot, nh));
+    return tq_attention_launch(tq, tq->scratch, nullptr, static_cast<const uint8_t *>(k_cache_dev),
                                static_cast<const uint8_t *>(v_cache_dev), k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale,
-                               static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream));
+                               static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream), qrot);
     IM_GUARD_END
 }
 
@@ -462,7 +495,7 @@ IM_EXPORT int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, co
         g_static_attn_ptr[cur] = ptr;
     }
     const int splits = num_splits > 0 ? num_splits : tq_auto_splits(tq->dev, nseq, T, nkv, base_pos + T);
-    const size_t need = im_cuda_tq_scratch_bytes(nseq, T, nh, kHd, splits);
+    const size_t need = tq_partial_bytes(nseq, T, nh, kHd, splits);
     if (need > kStaticScratchFloats * sizeof(float))
         return fail(IM_ERR_BOUNDS,
                     "%d sequence(s) x %d token(s) x %d heads x %d splits need %zu bytes of split partials; the built-in scratch holds %zu "
