@@ -155,6 +155,259 @@ __global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict_
 }
 
 
+// ---------------------------------------------------------------- tensor-core attention (GQ <= 4, rotated queries given)
+// The split attention above spends its time in shared-memory gathers (one codebook lookup per cached byte, bank
+// conflicts included) and f32 FMAs; at long context it reaches a few per cent of HBM bandwidth.  This kernel keeps
+// the same arithmetic contract and partial format but
+//   * every warp walks its own run of 32-position tiles: the K and V rows go from global memory straight into
+//     registers (a lane owns 32-byte / 16-byte pieces of whole rows, all coalesced), no block barrier in the loop;
+//   * the codebooks are shared-memory tables replicated once per lane (entry b of lane l at word 32 b + l): a
+//     gather never meets a bank conflict.  K entries carry (centroid, QJL sign) as an fp16 pair, V entries the centroid;
+//   * the dot products run on mma.sync m16n8k16 (fp16 operands, f32 accumulation): scores as
+//     [16 positions x 16 dims] x [16 dims x 8] with columns 0-3 = the GQ rotated queries against the centroid
+//     fragment and columns 4-7 = S q against the sign fragment; outputs as [16 dims x 16 positions] x
+//     [16 positions x 8 heads].  The fragment <-> (dimension, position) assignment is chosen so that a fragment
+//     register is built from bytes the lane already holds.
+// The eight warps of a CTA take consecutive runs of one (KV head, token, split) and merge their results in shared
+// memory, so the number of partials per head is the same as with the kernel above.
+constexpr int kTcWarps = 8;
+__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned lut_at(unsigned lane_base, unsigned w, int byte) {  // table word of byte `byte` of w for this lane
+    const unsigned b = __byte_perm(w, 0, 0x4440 + byte);
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(b * 128u + lane_base));
+    return v;
+}
+__device__ __forceinline__ unsigned pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const unsigned *>(&h);
+}
+
+template <int GQ>
+__global__ void __launch_bounds__(kTcWarps * 32) tq_attention_tc_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char tc_smem[];
+    unsigned *lutk = reinterpret_cast<unsigned *>(tc_smem);        // [256][32]: (centroid, sign) fp16 pair
+    unsigned *lutv = lutk + 256 * 32;                               // [256][32]: (centroid, 0)
+    __half *pw = reinterpret_cast<__half *>(lutv + 256 * 32);       // [warps][4 heads][32 positions] softmax weights x v scale
+    float *comb = reinterpret_cast<float *>(pw + kTcWarps * 4 * 32);  // [warps][4 heads][130]: o, m, l of each warp
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int kvh = blockIdx.x, st = blockIdx.y, split = blockIdx.z;
+    pdl_trigger();
+    {   // tables (constants): before the dependency wait
+        const int b = tid;  // 256 threads, one byte value each
+        const __half2 ke = __floats2half2_rn(p.k_cb[b & 127], (b & 0x80) ? 1.0f : -1.0f);
+        const __half2 ve = __floats2half2_rn(p.v_cb[b], 0.0f);
+        const unsigned ku = *reinterpret_cast<const unsigned *>(&ke), vu = *reinterpret_cast<const unsigned *>(&ve);
+        uint4 *dk = reinterpret_cast<uint4 *>(lutk + b * 32), *dv = reinterpret_cast<uint4 *>(lutv + b * 32);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            dk[i] = make_uint4(ku, ku, ku, ku);
+            dv[i] = make_uint4(vu, vu, vu, vu);
+        }
+    }
+    pdl_wait();
+    __syncthreads();
+
+    const int seq = st / p.T, tt = st % p.T;
+    const int seq_len = p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + tt + 1;
+    const int chunk = (seq_len + p.splits - 1) / p.splits;
+    const int c0 = split * chunk, c1 = min(c0 + chunk, seq_len);
+    // this warp's run: whole tiles of the split's range
+    const int tiles = (max(c1 - c0, 0) + kTile - 1) / kTile, per = (tiles + kTcWarps - 1) / kTcWarps;
+    const int r0 = c0 + warp * per * kTile, r1 = min(c1, r0 + per * kTile);
+    const int h0 = kvh * GQ;
+    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const unsigned lk = (unsigned)__cvta_generic_to_shared(lutk) + lane * 4u, lv = (unsigned)__cvta_generic_to_shared(lutv) + lane * 4u;
+
+    // B fragments of the score products: lane (n = g, t) holds dims 32 t + 4 j + {0..3} of column n: the rotated query
+    // of head n (n < GQ, against centroids) or S q of head n - 4 (4 <= n < 4 + GQ, against signs); zero otherwise
+    unsigned bc[16], bs[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) bc[i] = bs[i] = 0u;
+    if (g < GQ || (g >= 4 && g < 4 + GQ)) {
+        const float *src = p.qrot + ((size_t)st * p.nh + h0 + (g < 4 ? g : g - 4)) * 2 * kHd + (g < 4 ? 0 : kHd) + 32 * t;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 v = *reinterpret_cast<const float4 *>(src + 4 * j);
+            const unsigned lo = pack_h2(v.x, v.y), hi = pack_h2(v.z, v.w);
+            if (g < 4) { bc[2 * j] = lo; bc[2 * j + 1] = hi; } else { bs[2 * j] = lo; bs[2 * j + 1] = hi; }
+        }
+    }
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // lanes t < 2: heads 2t, 2t + 1
+    float o[8][4];                                                       // o[mb]: dims 16g + 2mb, +1 (rows) x heads 2t, 2t+1
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    __half *pwarp = pw + warp * 4 * 32;
+
+    for (int ts = r0; ts < r1; ts += kTile) {
+        const int nt = min(kTile, r1 - ts);
+        // ---- K rows g, g+8, g+16, g+24 of the tile: 32 bytes (dims 32t .. 32t+31) each ----
+        uint4 kq[4][2];
+        float ksv[4], rwv[4], vsv[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int pos = g + 8 * r;
+            kq[r][0] = kq[r][1] = make_uint4(0, 0, 0, 0);
+            ksv[r] = rwv[r] = vsv[r] = 0.0f;
+            if (pos < nt) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pos) * kHd + 32 * t);
+                kq[r][0] = ldg_stream_v4(src);
+                kq[r][1] = ldg_stream_v4(src + 1);
+                ksv[r] = p.ks[head_base + ts + pos];
+                rwv[r] = p.krn[head_base + ts + pos] * p.qjl_factor;
+                vsv[r] = p.vs[head_base + ts + pos];
+            }
+        }
+        // ---- V rows 2t, 2t+1, 2t+8, 2t+9 (+16): 16 bytes (dims 16g .. 16g+15) each ----
+        uint4 vq[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            const int pos = 2 * t + (r & 1) + 8 * ((r >> 1) & 1) + 16 * (r >> 2);
+            vq[r] = make_uint4(0, 0, 0, 0);
+            if (pos < nt) vq[r] = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pos) * kHd + 16 * g));
+        }
+
+        // ---- scores: two 16-position row blocks ----
+        float sc[2][4];  // [row block][c0..c3]
+#pragma unroll
+        for (int rb = 0; rb < 2; rb++) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const unsigned *wa = reinterpret_cast<const unsigned *>(&kq[2 * rb][0]);      // row g + 16 rb
+            const unsigned *wb = reinterpret_cast<const unsigned *>(&kq[2 * rb + 1][0]);  // row g + 8 + 16 rb
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const unsigned a = wa[j], b = wb[j];
+                const unsigned la0 = lut_at(lk, a, 0), la1 = lut_at(lk, a, 1), la2 = lut_at(lk, a, 2), la3 = lut_at(lk, a, 3);
+                const unsigned lb0 = lut_at(lk, b, 0), lb1 = lut_at(lk, b, 1), lb2 = lut_at(lk, b, 2), lb3 = lut_at(lk, b, 3);
+                // centroids in the low halves, signs in the high halves
+                mma_f16(c, __byte_perm(la0, la1, 0x5410), __byte_perm(lb0, lb1, 0x5410), __byte_perm(la2, la3, 0x5410),
+                        __byte_perm(lb2, lb3, 0x5410), bc[2 * j], bc[2 * j + 1]);
+                mma_f16(c, __byte_perm(la0, la1, 0x7632), __byte_perm(lb0, lb1, 0x7632), __byte_perm(la2, la3, 0x7632),
+                        __byte_perm(lb2, lb3, 0x7632), bs[2 * j], bs[2 * j + 1]);
+            }
+            sc[rb][0] = c[0]; sc[rb][1] = c[1]; sc[rb][2] = c[2]; sc[rb][3] = c[3];
+        }
+        // lanes t < 2 hold the centroid sums of heads 2t, 2t+1; lanes t + 2 the sign sums of the same heads
+        float s[4][2];  // [position g + 8 r][head 2t + i]
+#pragma unroll
+        for (int rb = 0; rb < 2; rb++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float other = __shfl_xor_sync(0xffffffffu, sc[rb][q], 2);
+                const int r = 2 * rb + (q >> 1), i = q & 1;  // c0,c1: row g ; c2,c3: row g + 8
+                const bool live = t < 2 && g + 8 * r < nt;  // lanes t >= 2 only feed the shuffle above
+                s[r][i] = live ? p.attn_scale * (ksv[r] * (sc[rb][q] + rwv[r] * other)) : -INFINITY;
+            }
+        // ---- online softmax over the tile (meaningful on lanes t < 2; the others carry copies of no use) ----
+        float wgt[4][2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float mx = fmaxf(fmaxf(s[0][i], s[1][i]), fmaxf(s[2][i], s[3][i]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[i], mx);
+            const float corr = m_new == -INFINITY ? 1.0f : __expf(m_run[i] - m_new);
+            float sum = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                wgt[r][i] = s[r][i] == -INFINITY ? 0.0f : __expf(s[r][i] - m_new);
+                sum += wgt[r][i];
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+            l_run[i] = l_run[i] * corr + sum;
+            m_run[i] = m_new;
+#pragma unroll
+            for (int mb = 0; mb < 8; mb++) {  // heads 2t + i live in accumulator columns i (rows d0) and i + 2 (rows d1)
+                o[mb][i] *= corr;
+                o[mb][i + 2] *= corr;
+            }
+        }
+        // weights x V scale, as fp16, to this warp's P[head][position] for the output products
+        __syncwarp();
+        if (t < 2) {
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int i = 0; i < 2; i++)
+                    if (2 * t + i < 4) pwarp[(2 * t + i) * 32 + g + 8 * r] = __float2half_rn(wgt[r][i] * vsv[r]);
+        }
+        __syncwarp();
+        // ---- outputs: O^T[dims][heads] += V^T[dims][positions] P^T[positions][heads] ----
+#pragma unroll
+        for (int kb = 0; kb < 2; kb++) {
+            unsigned b0 = 0u, b1 = 0u;  // lane (n = g): P[head g][16 kb + 2t, +1] and [.. + 8, + 9]
+            if (g < GQ) {
+                b0 = *reinterpret_cast<const unsigned *>(pwarp + g * 32 + 16 * kb + 2 * t);
+                b1 = *reinterpret_cast<const unsigned *>(pwarp + g * 32 + 16 * kb + 2 * t + 8);
+            }
+            const unsigned *v0 = reinterpret_cast<const unsigned *>(&vq[4 * kb + 0]);  // position 16 kb + 2t
+            const unsigned *v1 = reinterpret_cast<const unsigned *>(&vq[4 * kb + 1]);  // + 1
+            const unsigned *v2 = reinterpret_cast<const unsigned *>(&vq[4 * kb + 2]);  // + 8
+            const unsigned *v3 = reinterpret_cast<const unsigned *>(&vq[4 * kb + 3]);  // + 9
+#pragma unroll
+            for (int mb = 0; mb < 8; mb++) {  // rows g, g + 8 of the block: dims 16 g + 2 mb, + 1
+                const int w = mb >> 1, by = 2 * (mb & 1);
+                const unsigned e00 = lut_at(lv, v0[w], by), e01 = lut_at(lv, v1[w], by), e10 = lut_at(lv, v0[w], by + 1), e11 = lut_at(lv, v1[w], by + 1);
+                const unsigned f00 = lut_at(lv, v2[w], by), f01 = lut_at(lv, v3[w], by), f10 = lut_at(lv, v2[w], by + 1), f11 = lut_at(lv, v3[w], by + 1);
+                mma_f16(o[mb], __byte_perm(e00, e01, 0x5410), __byte_perm(e10, e11, 0x5410), __byte_perm(f00, f01, 0x5410),
+                        __byte_perm(f10, f11, 0x5410), b0, b1);
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---- merge the warps: comb[warp][head][130] = o (dims 0..127), m, l ----
+    if (t < 2) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int h = 2 * t + i;
+            if (h < 4) {
+                float *dst = comb + (warp * 4 + h) * 130;
+#pragma unroll
+                for (int mb = 0; mb < 8; mb++) {
+                    dst[16 * g + 2 * mb] = o[mb][i];
+                    dst[16 * g + 2 * mb + 1] = o[mb][i + 2];
+                }
+                if (g == 0) {
+                    dst[128] = m_run[i];
+                    dst[129] = l_run[i];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < GQ * kHd; idx += kTcWarps * 32) {
+        const int h = idx >> 7, d = idx & 127;
+        float gm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kTcWarps; w++) gm = fmaxf(gm, comb[(w * 4 + h) * 130 + 128]);
+        float acc = 0.0f, lsum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kTcWarps; w++) {
+            const float m = comb[(w * 4 + h) * 130 + 128];
+            const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
+            acc += comb[(w * 4 + h) * 130 + d] * corr;
+            lsum += comb[(w * 4 + h) * 130 + 129] * corr;
+        }
+        const size_t pi = ((size_t)st * p.nh + h0 + h) * p.splits + split;
+        p.po[pi * kHd + d] = acc;
+        if (d == 0) {
+            p.pm[pi] = gm;
+            p.pl[pi] = lsum;
+        }
+    }
+}
+constexpr size_t kTcSmem = 2 * 256 * 32 * 4 + kTcWarps * 4 * 32 * 2 + kTcWarps * 4 * 130 * 4;
+
 // Rotated query and S * rotated query for every (token, head), computed once instead of once per split:
 // grid (nh, nseq*T), 128 threads.  q fp16 [nseq*T, nh, 128] -> qrot f32 [nseq*T, nh, 2, 128].
 __global__ void __launch_bounds__(kHd) tq_qrot_kernel(const __half *__restrict__ q, const float *__restrict__ signs,
@@ -381,6 +634,21 @@ int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uin
     p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)tq->hd;
     p.nh = nh; p.nkv = nkv; p.max_seq = max_seq; p.base_pos = base_pos; p.T = T; p.splits = splits; p.pos_dev = pos_dev;
     dim3 grid(nkv, nseq * T, splits);
+    const int gq = nh / nkv;
+    static const bool tc_on = [] { const char *e = getenv("IM_ATTN_TC"); return !(e && e[0] == '0'); }();
+    if (qrot && tc_on && (gq == 1 || gq == 2 || gq == 4) && nh % nkv == 0) {  // tensor-core kernel (needs the rotated queries)
+        static thread_local bool configured = false;
+        if (!configured) {  // the three instantiations share one function-pointer type: set them all once
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            configured = true;
+        }
+        auto kern = gq == 1 ? tq_attention_tc_kernel<1> : (gq == 2 ? tq_attention_tc_kernel<2> : tq_attention_tc_kernel<4>);
+        int rc = IM_OK;
+        IM_CUDA_CHECK(launch_k(kern, grid, dim3(kTcWarps * 32), kTcSmem, st, p));
+        if (rc != IM_OK) return rc;
+    } else
     switch (nh / nkv) {
         case 1: IM_CUDA_CHECK(launch_k(tq_attention_kernel<1>, grid, dim3(kAttnThreads), 0, st, p)); break;
         case 2: IM_CUDA_CHECK(launch_k(tq_attention_kernel<2>, grid, dim3(kAttnThreads), 0, st, p)); break;
