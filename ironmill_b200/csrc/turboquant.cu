@@ -188,7 +188,7 @@ __device__ __forceinline__ unsigned pack_h2(float a, float b) {
 }
 
 template <int GQ>
-__global__ void __launch_bounds__(kTcWarps * 32) tq_attention_tc_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char tc_smem[];
     unsigned *lutk = reinterpret_cast<unsigned *>(tc_smem);        // [256][32]: (centroid, sign) fp16 pair
     unsigned *lutv = lutk + 256 * 32;                               // [256][32]: (centroid, 0)
@@ -226,16 +226,18 @@ __global__ void __launch_bounds__(kTcWarps * 32) tq_attention_tc_kernel(const At
 
     // B fragments of the score products: lane (n = g, t) holds dims 32 t + 4 j + {0..3} of column n: the rotated query
     // of head n (n < GQ, against centroids) or S q of head n - 4 (4 <= n < 4 + GQ, against signs); zero otherwise
-    unsigned bc[16], bs[16];
+    // (one register set: a lane has either query or S q values; the other product of the pair gets zeros)
+    unsigned bx[16];
 #pragma unroll
-    for (int i = 0; i < 16; i++) bc[i] = bs[i] = 0u;
+    for (int i = 0; i < 16; i++) bx[i] = 0u;
+    const bool is_c = g < 4;  // this lane's column belongs to the centroid product
     if (g < GQ || (g >= 4 && g < 4 + GQ)) {
         const float *src = p.qrot + ((size_t)st * p.nh + h0 + (g < 4 ? g : g - 4)) * 2 * kHd + (g < 4 ? 0 : kHd) + 32 * t;
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const float4 v = *reinterpret_cast<const float4 *>(src + 4 * j);
-            const unsigned lo = pack_h2(v.x, v.y), hi = pack_h2(v.z, v.w);
-            if (g < 4) { bc[2 * j] = lo; bc[2 * j + 1] = hi; } else { bs[2 * j] = lo; bs[2 * j + 1] = hi; }
+            bx[2 * j] = pack_h2(v.x, v.y);
+            bx[2 * j + 1] = pack_h2(v.z, v.w);
         }
     }
 
@@ -264,15 +266,6 @@ __global__ void __launch_bounds__(kTcWarps * 32) tq_attention_tc_kernel(const At
                 vsv[r] = p.vs[head_base + ts + pos];
             }
         }
-        // ---- V rows 2t, 2t+1, 2t+8, 2t+9 (+16): 16 bytes (dims 16g .. 16g+15) each ----
-        uint4 vq[8];
-#pragma unroll
-        for (int r = 0; r < 8; r++) {
-            const int pos = 2 * t + (r & 1) + 8 * ((r >> 1) & 1) + 16 * (r >> 2);
-            vq[r] = make_uint4(0, 0, 0, 0);
-            if (pos < nt) vq[r] = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pos) * kHd + 16 * g));
-        }
-
         // ---- scores: two 16-position row blocks ----
         float sc[2][4];  // [row block][c0..c3]
 #pragma unroll
@@ -287,12 +280,21 @@ __global__ void __launch_bounds__(kTcWarps * 32) tq_attention_tc_kernel(const At
                 const unsigned lb0 = lut_at(lk, b, 0), lb1 = lut_at(lk, b, 1), lb2 = lut_at(lk, b, 2), lb3 = lut_at(lk, b, 3);
                 // centroids in the low halves, signs in the high halves
                 mma_f16(c, __byte_perm(la0, la1, 0x5410), __byte_perm(lb0, lb1, 0x5410), __byte_perm(la2, la3, 0x5410),
-                        __byte_perm(lb2, lb3, 0x5410), bc[2 * j], bc[2 * j + 1]);
+                        __byte_perm(lb2, lb3, 0x5410), is_c ? bx[2 * j] : 0u, is_c ? bx[2 * j + 1] : 0u);
                 mma_f16(c, __byte_perm(la0, la1, 0x7632), __byte_perm(lb0, lb1, 0x7632), __byte_perm(la2, la3, 0x7632),
-                        __byte_perm(lb2, lb3, 0x7632), bs[2 * j], bs[2 * j + 1]);
+                        __byte_perm(lb2, lb3, 0x7632), is_c ? 0u : bx[2 * j], is_c ? 0u : bx[2 * j + 1]);
             }
             sc[rb][0] = c[0]; sc[rb][1] = c[1]; sc[rb][2] = c[2]; sc[rb][3] = c[3];
         }
+        // ---- V rows 2t, 2t+1, 2t+8, 2t+9 (+16): 16 bytes (dims 16g .. 16g+15) each ----
+        uint4 vq[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            const int pos = 2 * t + (r & 1) + 8 * ((r >> 1) & 1) + 16 * (r >> 2);
+            vq[r] = make_uint4(0, 0, 0, 0);
+            if (pos < nt) vq[r] = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pos) * kHd + 16 * g));
+        }
+
         // lanes t < 2 hold the centroid sums of heads 2t, 2t+1; lanes t + 2 the sign sums of the same heads
         float s[4][2];  // [position g + 8 r][head 2t + i]
 #pragma unroll
@@ -612,8 +614,8 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
 
 int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
     const int ctas = nseq * T * nkv;
-    int s = (4 * dev->sm_count + ctas - 1) / ctas;  // four 128-thread CTAs per SM: an item is latency-bound, more of them in flight pay
-    const int by_len = (seq_len + 2 * kTile - 1) / (2 * kTile);  // at least two tiles per split
+    int s = (2 * dev->sm_count + ctas - 1) / ctas;                // two 8-warp CTAs per SM
+    const int by_len = (seq_len + 8 * kTile - 1) / (8 * kTile);  // at least one tile per warp of a split
     if (s > by_len) s = by_len;
     if (s > 128) s = 128;
     return s < 1 ? 1 : s;
