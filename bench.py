@@ -332,6 +332,7 @@ def run_decode(args, rank, world):
         "config": {"workload": "llama3_8b_shape_int4_g128_awq_tq8_decode", "batch": B, "prompt_tokens": P,
                    "context_during_timing": [ctx0, ctx0 + K], "layers": cfg.num_hidden_layers, "hidden": 4096, "ffn": 14336, "vocab": 128256,
                    "parallelism": f"tp{world}" if world > 1 else "single",
+                   "allreduce": ("one-shot peer-memory kernel" if eng.tp_peer_allreduce() else "nccl") if world > 1 else None,
                    "l2_policy": "inputs larger than L2: every step streams this rank's %.2f GB of weights + KV" % (step_bytes / 1e9),
                    "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2)},
         "roofline": roof,

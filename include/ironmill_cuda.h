@@ -322,6 +322,10 @@ size_t im_cuda_model_memory_bytes(const im_model *m);
 /* Algorithmic bytes one decode step of this rank reads from HBM at context length ctx and the given batch:
  * packed codes + scales/zeros + AWQ vectors + fp16 lm_head rows + norm weights + batch * KV bytes. */
 size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
+/* 1 when the row-split projections of a tensor-parallel model are summed by the library's one-shot all-reduce over
+ * peer memory (CUDA IPC + NVLink stores, set up by im_cuda_model_tp_init; IM_TP_PEER=0 disables it), 0 when NCCL's
+ * all-reduce does it.  No counterpart in the reference (it has no tensor parallelism). */
+int im_cuda_model_tp_peer_allreduce(const im_model *m);
 /* Number of kernel launches in one captured decode step. */
 int im_cuda_model_step_launches(const im_model *m);
 /* Timing of the whole-token decode kernel (all layers of a batch-1 step in one launch) by itself: the counterpart of

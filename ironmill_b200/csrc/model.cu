@@ -99,6 +99,93 @@ struct HostAffine {  // one projection as handed to load_affine, already cut to 
     int N = 0, K = 0, gs = 0, bits = 0;
 };
 
+// ---- one-shot all-reduce over peer memory (tensor parallel, small vectors) --------------------------------
+// A decode step has two row-split projections per layer, each followed by a sum of a [batch, hidden] fp16 vector over
+// the ranks: 8 KB at batch 1, 65 times per token.  NCCL's all-reduce costs 15-30 us there, more than the projections.
+// Here every rank stores its vector into a slot of EVERY rank's receive buffer (plain stores to peer memory over
+// NVLink), raises a per-source sequence flag on every rank, waits (bounded) until all sources have raised theirs, and
+// sums the world's vectors from its own memory in rank order, in f32, rounding once.  Two buffer halves alternate:
+// a rank can only be one all-reduce ahead of the slowest one.  No multicast, no multimem: plain peer stores.
+constexpr int kXarMaxWorld = 8, kXarThreads = 512;
+struct PeerAllreduce {
+    bool ok = false;
+    unsigned char *base = nullptr;  // this rank's allocation: [flags: kXarMaxWorld u32][seq u32][pad to 256][buf: 2 x world x cap halves]
+    size_t bytes = 0, cap = 0;      // cap: halves per vector
+    unsigned char *peer[kXarMaxWorld] = {};  // every rank's allocation as mapped here (own included)
+};
+struct XarArgs {
+    unsigned *flags, *seq;             // local
+    __half *buf;                       // local receive buffer
+    unsigned *peer_flags[kXarMaxWorld];
+    __half *peer_buf[kXarMaxWorld];
+    int world, rank;
+    size_t cap;
+    int *err;
+};
+__global__ void __launch_bounds__(kXarThreads) peer_allreduce_kernel(const XarArgs x, const __half *__restrict__ in, __half *__restrict__ out,
+                                                                      int count) {
+    __shared__ int s_ok;
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, chunks = count / 8;
+    const unsigned seq = *x.seq + 1u;
+    const size_t slot = (size_t)(seq & 1u) * x.world;
+    for (int c = tid; c < chunks; c += kXarThreads) {
+        const uint4 v = reinterpret_cast<const uint4 *>(in)[c];
+        for (int p = 0; p < x.world; p++) reinterpret_cast<uint4 *>(x.peer_buf[p] + (slot + x.rank) * x.cap)[c] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) s_ok = 1;
+    if (tid < x.world) {
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned *>(x.peer_flags[tid] + x.rank) = seq;  // "my vector number seq is in your buffer"
+    }
+    __syncthreads();
+    if (tid < x.world) {  // one poller per source; sequence numbers only grow
+        const volatile unsigned *f = x.flags + tid;
+        unsigned long long t0 = 0;
+        for (unsigned i = 0;; i++) {
+            if ((int)(*f - seq) >= 0) break;
+            if ((i & 255u) == 255u) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                // ranks are separate processes whose hosts may lag each other by a scheduling hiccup: 5 s before a rank is
+                // given up; once the error word is set no later all-reduce waits at all
+                if (now - t0 > 5000ull * 1000 * 1000 || *reinterpret_cast<volatile int *>(x.err) != 0) {
+                    atomicExch(x.err, 3);
+                    s_ok = 0;
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (s_ok) {
+        for (int c = tid; c < chunks; c += kXarThreads) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int p = 0; p < x.world; p++) {
+                const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x.buf + (slot + p) * x.cap) + c);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(h[i]);
+                    acc[2 * i] += f.x;
+                    acc[2 * i + 1] += f.y;
+                }
+            }
+            uint4 r;
+            __half2 *hr = reinterpret_cast<__half2 *>(&r);
+#pragma unroll
+            for (int i = 0; i < 4; i++) hr[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+            reinterpret_cast<uint4 *>(out)[c] = r;
+        }
+    }
+    if (tid == 0) *x.seq = seq;
+}
+
 struct Layer {
     HostAffine hq, hk, hv;           // staged until finalize concatenates them
     AffineWeight *qkv = nullptr;     // rows [q | k | v] of this rank
@@ -147,6 +234,7 @@ struct Model {
 #if IM_HAVE_NCCL_H
     ncclComm_t comm = nullptr;
 #endif
+    PeerAllreduce xar;
     std::vector<std::pair<void *, size_t>> allocs;
 
     int alloc(void **p, size_t n) {
@@ -345,6 +433,19 @@ static int tp_allreduce(Model *m, __half *buf, size_t count, cudaStream_t st) {
     if (m->world <= 1) return IM_OK;
 #if IM_HAVE_NCCL_H
     if (!m->comm) return fail(IM_ERR_STATE, "tensor parallel group not initialised (im_cuda_model_tp_init)");
+    if (m->xar.ok && count <= m->xar.cap && count % 8 == 0) {
+        XarArgs x{};
+        x.flags = reinterpret_cast<unsigned *>(m->xar.base);
+        x.seq = x.flags + kXarMaxWorld;
+        x.buf = reinterpret_cast<__half *>(m->xar.base + 256);
+        for (int p = 0; p < m->world; p++) {
+            x.peer_flags[p] = reinterpret_cast<unsigned *>(m->xar.peer[p]);
+            x.peer_buf[p] = reinterpret_cast<__half *>(m->xar.peer[p] + 256);
+        }
+        x.world = m->world; x.rank = m->rank; x.cap = m->xar.cap; x.err = m->dev->err_flag;
+        IM_CUDA_CHECK(launch_k(peer_allreduce_kernel, dim3(1), dim3(kXarThreads), 0, st, x, (const __half *)buf, buf, (int)count));
+        return IM_OK;
+    }
     IM_NCCL_CHECK(nccl()->AllReduce(buf, buf, count, ncclHalf, ncclSum, m->comm, st));
     return IM_OK;
 #else
@@ -711,6 +812,49 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
     ncclUniqueId id;
     memcpy(&id, id_128_bytes, 128);
     IM_NCCL_CHECK(nccl()->CommInitRank(&m->comm, m->world, id, m->rank));
+    // Receive buffers of the one-shot all-reduce, mapped into every rank with CUDA IPC (handles exchanged through the
+    // communicator just created).  Any failure here leaves the NCCL all-reduce in charge.
+    const char *env = getenv("IM_TP_PEER");
+    if (m->world <= kXarMaxWorld && !(env && env[0] == '0')) {
+        PeerAllreduce &x = m->xar;
+        x.cap = (size_t)4 * m->cfg.hidden_size;  // up to four batch rows: the decode batches that run one matvec per projection
+        x.bytes = 256 + (size_t)2 * m->world * x.cap * sizeof(__half);
+        cudaIpcMemHandle_t mine{};
+        unsigned char *xchg = nullptr;
+        std::vector<cudaIpcMemHandle_t> all((size_t)m->world);
+        bool good = cudaMalloc((void **)&x.base, x.bytes) == cudaSuccess && cudaMemset(x.base, 0, x.bytes) == cudaSuccess &&
+                    cudaIpcGetMemHandle(&mine, x.base) == cudaSuccess &&
+                    cudaMalloc((void **)&xchg, (size_t)m->world * sizeof(mine)) == cudaSuccess &&
+                    cudaMemcpy(xchg + (size_t)m->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess;
+        // every rank takes part in the exchange whatever happened locally (a rank that failed sends zeros)
+        ncclResult_t nr = nccl()->AllGather(xchg ? xchg + (size_t)m->rank * sizeof(mine) : nullptr, xchg, sizeof(mine), ncclChar, m->comm,
+                                            m->stream);
+        good = good && nr == ncclSuccess && cudaStreamSynchronize(m->stream) == cudaSuccess &&
+               cudaMemcpy(all.data(), xchg, (size_t)m->world * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
+        for (int p = 0; good && p < m->world; p++) {
+            if (p == m->rank) {
+                x.peer[p] = x.base;
+                continue;
+            }
+            void *ptr = nullptr;
+            good = cudaIpcOpenMemHandle(&ptr, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+            x.peer[p] = static_cast<unsigned char *>(ptr);
+        }
+        if (xchg) cudaFree(xchg);
+        (void)cudaGetLastError();
+        // all ranks must agree: one that could not map its peers would wait for flags nobody raises
+        int *agree = nullptr;
+        int flag = good ? 1 : 0, out = 0;
+        if (cudaMalloc((void **)&agree, sizeof(int)) == cudaSuccess) {
+            cudaMemcpy(agree, &flag, sizeof(int), cudaMemcpyHostToDevice);
+            if (nccl()->AllReduce(agree, agree, 1, ncclInt, ncclMin, m->comm, m->stream) == ncclSuccess &&
+                cudaStreamSynchronize(m->stream) == cudaSuccess)
+                cudaMemcpy(&out, agree, sizeof(int), cudaMemcpyDeviceToHost);
+            cudaFree(agree);
+        }
+        x.ok = out == 1;
+        (void)cudaGetLastError();
+    }
     return IM_OK;
 #else
     return fail(IM_ERR_NCCL, "built without nccl.h");
@@ -771,6 +915,9 @@ IM_EXPORT void im_cuda_model_free(im_model *m) {
     if (m->stream) cudaStreamSynchronize(m->stream);
     for (auto &g : m->graphs) cudaGraphExecDestroy(g.second);
 #if IM_HAVE_NCCL_H
+    for (int p = 0; p < kXarMaxWorld; p++)
+        if (m->xar.peer[p] && p != m->rank) cudaIpcCloseMemHandle(m->xar.peer[p]);
+    if (m->xar.base) cudaFree(m->xar.base);
     if (m->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(m->comm);
 #endif
     for (auto &L : m->layers) {
@@ -1074,6 +1221,9 @@ IM_EXPORT int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, in
     IM_GUARD_END
 }
 
+// 1 when the row-split projections of a tensor-parallel model are summed by the one-shot peer-memory all-reduce,
+// 0 when NCCL does it (single GPU: 0).
+IM_EXPORT int im_cuda_model_tp_peer_allreduce(const im_model *m) { return m && m->xar.ok ? 1 : 0; }
 IM_EXPORT int im_cuda_model_step_launches(const im_model *m) { return m ? m->launches_per_step : 0; }
 
 IM_EXPORT size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch) {

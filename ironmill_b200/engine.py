@@ -160,6 +160,10 @@ class CudaInference:
     def tp_init(self, unique_id: bytes) -> None:
         check(lib().im_cuda_model_tp_init(self._model, unique_id))
 
+    def tp_peer_allreduce(self) -> bool:
+        """True when the row-split projections are summed by the one-shot peer-memory all-reduce, False when NCCL does it."""
+        return bool(self._model) and lib().im_cuda_model_tp_peer_allreduce(self._model) == 1
+
     @staticmethod
     def tp_unique_id() -> bytes:
         buf = C.create_string_buffer(128)

@@ -42,6 +42,7 @@ def _worker(rank, world, port, ret):
             refs = [single.prefill(prompt)] + [single.decode_step(t) for t in (5, 17, 400)]
             err = max(float(np.abs(a - b).max()) for a, b in zip(outs, refs))
             ret[0] = err
+            ret['peer'] = eng.tp_peer_allreduce()
         dist.barrier()
     except Exception as e:  # noqa: BLE001
         ret[rank] = f"{type(e).__name__}: {e}"
@@ -60,4 +61,5 @@ def test_tp2_matches_single_gpu():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert isinstance(ret.get(0), float) and ret[0] <= 5e-2, dict(ret)
+    print('one-shot peer all-reduce in use:', ret.get('peer'))
     assert 1 not in ret, dict(ret)
