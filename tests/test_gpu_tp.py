@@ -23,8 +23,9 @@ def _worker(rank, world, port, ret):
         from ironmill_b200.engine import CudaConfig, CudaInference
         from oracle import oracle as orc
         from tests.oracle_model import DictProvider, synth_model
-        cfg = ModelConfig(architecture="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
-                          num_key_value_heads=2, head_dim=128, vocab_size=1000, rms_norm_eps=1e-5, rope_theta=5e5)
+        nkv = max(2, world)   # KV heads are split across the ranks
+        cfg = ModelConfig(architecture="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4 * nkv,
+                          num_key_value_heads=nkv, head_dim=128, vocab_size=1000, rms_norm_eps=1e-5, rope_theta=5e5)
         tensors = synth_model(cfg, seed=9, awq=True)
         tqc = orc.TqConstants(128, 8, seed=42)
         eng = CudaInference(CudaConfig(max_seq_len=64, tp_world=world, tp_rank=rank, device=rank))
@@ -50,16 +51,17 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_tp2_matches_single_gpu():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+def test_tp_matches_single_gpu():
+    world = int(os.environ.get("IM_TEST_TP_WORLD", "2"))   # 2 by default; 4 or 8 when that many GPUs are visible
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert isinstance(ret.get(0), float) and ret[0] <= 5e-2, dict(ret)
     print('one-shot peer all-reduce in use:', ret.get('peer'))
-    assert 1 not in ret, dict(ret)
+    assert all(r not in ret for r in range(1, world)), dict(ret)
