@@ -61,16 +61,15 @@ __device__ __forceinline__ int ld_volatile(const int *p) {
 
 // Arrival of this CTA at barrier k: the caller's threads have synchronised among themselves.
 __device__ __forceinline__ void grid_arrive(unsigned *bar, int k) {
-    __threadfence();
-    atomicAdd(bar + k, 1u);
+    // release: the CTA's writes (ordered before this by its own barrier) are visible to whoever acquires the count
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(bar + k), "r"(1u) : "memory");
 }
 // One thread polls until every CTA has arrived (or the error word is set / the time limit passes).
 __device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err) {
     const unsigned want = gridDim.x;
     if (ld_acquire(bar + k) >= want) return true;
     const unsigned long long t0 = global_ns();
-    for (unsigned i = 1;; i++) {
-        __nanosleep(20);
+    for (unsigned i = 1;; i++) {  // each poll is a trip to L2: that paces the loop
         if (ld_acquire(bar + k) >= want) return true;
         if ((i & 127u) == 0) {
             if (ld_volatile(err) != 0) return false;
@@ -196,7 +195,42 @@ __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, c
 
 // The item phases run out of line: they are cold next to the projection loop, and a call boundary keeps their
 // register appetite (the encoder holds 64 matrix values in flight) from spilling the loop's state.
-__device__ IM_MEGA_ITEM_INLINE void mega_prep_item(const GroupScope &gs, const PrepArgs &a, float *sh, int item) { tq_prep_item(gs, a, sh, item, 0); }
+// ---- the QJL projection of a head item by all four groups ------------------------------------------------------
+// A head item runs on group 0, but its projection reads a 64 KB matrix: alone, a thread brings its column in two
+// waves of 64 loads, two trips to L2 on the phase's critical path.  Here every consumer thread holds 32 values of a
+// column (rows 32 * group ..., loaded before the barrier that opens the phase: the matrix is a constant), and the
+// sum walks k upwards through the four groups in turn, handing the running value on through shared memory, so the
+// additions happen in exactly the encoder's order.
+struct QjlCoop {
+    const float (&sv)[32];
+    float *carry;  // [128]
+    __device__ __forceinline__ void begin(int, int) {}
+    template <bool EXACT>
+    __device__ __forceinline__ float step(float acc, const float *vec, int group) const {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            acc = EXACT ? __fadd_rn(acc, __fmul_rn(sv[j], vec[32 * group + j])) : fmaf(sv[j], vec[32 * group + j], acc);
+        return acc;
+    }
+    // group 0's side: 1 + kGroups CTA-wide barriers, matched by assist() on the other groups
+    template <bool EXACT, class Scope>
+    __device__ __forceinline__ float finish(const Scope &, const float *vec, int d, int) {
+        consumer_sync();  // vec is visible to every group
+        carry[d] = step<EXACT>(0.0f, vec, 0);
+#pragma unroll
+        for (int gi = 0; gi < kGroups; gi++) consumer_sync();
+        return carry[d];
+    }
+    template <bool EXACT>
+    __device__ __forceinline__ void assist(const float *vec, int d, int group) const {
+        consumer_sync();
+#pragma unroll
+        for (int gi = 0; gi < kGroups; gi++) {
+            if (gi == group) carry[d] = step<EXACT>(carry[d], vec, group);
+            consumer_sync();
+        }
+    }
+};
 
 template <int GQ>
 __device__ IM_MEGA_ITEM_INLINE void mega_attention_item(const GroupScope &gs, AttnSmem<GQ> &sm, const float *cbk, const float *cbv, const AttnParams &ap,
@@ -204,56 +238,64 @@ __device__ IM_MEGA_ITEM_INLINE void mega_attention_item(const GroupScope &gs, At
     tq_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, 0, split, r0, r1);
 }
 
-// Combine the splits of one query head and rotate back, by all 16 consumer warps: the four groups each combine a
-// quarter of the splits (their loads all in flight together), group 0 merges the four and applies the rotation.
+// Combine the splits of one query head and rotate back, by all 16 consumer warps.  Warp w takes splits w, w + 16, ...:
+// a lane loads four output dimensions of up to five splits (and their max / sum) in one trip to L2 and folds them
+// under the warp's own running max; group 0 then merges the 16 warp partials and applies the rotation.
 __device__ IM_MEGA_ITEM_INLINE void mega_reduce_head(const GroupScope &gs, int group, int tid, float *U, const float *__restrict__ po,
                                               const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ signs,
                                               __half *__restrict__ attn_out, int head, int splits, int used) {
-    float *sm_m = U, *sm_l = sm_m + 256;  // per split: running max, sum
-    float *part_ml = sm_l + 256;          // [4][2]
-    float *part = part_ml + 8;            // [4][128]
-    float *xs = part + kGroups * kHd;     // 128 floats for the rotation
-    const int d = tid & 127;
+    constexpr int kBatch = 5;
+    float *part = U;                                 // [16][128]
+    float *part_ml = part + kV2Consumers * kHd;      // [16][2]
+    float *xs = part_ml + 2 * kV2Consumers;          // 128 floats for the rotation
+    const int warp = tid >> 5, lane = tid & 31;
     const size_t base = (size_t)head * splits;
-    for (int i = tid; i < used; i += kV2Consumers * 32) {
-        sm_m[i] = pm[base + i];
-        sm_l[i] = pl[base + i];
-    }
-    consumer_sync();
-    const int per = (used + kGroups - 1) / kGroups, s_lo = group * per, s_hi = min(used, s_lo + per);
-    float gmx = -INFINITY;
-    for (int s = s_lo; s < s_hi; s++) gmx = fmaxf(gmx, sm_m[s]);
-    float acc = 0.0f, lsum = 0.0f;
-    for (int s0 = s_lo; s0 < s_hi; s0 += 10) {
-        float o[10];
+    float wm = -INFINITY, wl = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s0 = warp; s0 < used; s0 += kV2Consumers * kBatch) {
+        float4 o[kBatch];
+        float m[kBatch], l[kBatch];
 #pragma unroll
-        for (int j = 0; j < 10; j++) o[j] = s0 + j < s_hi ? po[(base + s0 + j) * kHd + d] : 0.0f;
+        for (int j = 0; j < kBatch; j++) {
+            const int sp = s0 + j * kV2Consumers;
+            const bool live = sp < used;
+            o[j] = live ? __ldcg(reinterpret_cast<const float4 *>(po + (base + sp) * kHd) + lane) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            m[j] = live ? __ldcg(pm + base + sp) : -INFINITY;
+            l[j] = live ? __ldcg(pl + base + sp) : 0.0f;
+        }
+        float bm = wm;
 #pragma unroll
-        for (int j = 0; j < 10; j++)
-            if (s0 + j < s_hi) {
-                const float m = sm_m[s0 + j];
-                const float corr = m == -INFINITY ? 0.0f : __expf(m - gmx);
-                lsum += sm_l[s0 + j] * corr;
-                acc += o[j] * corr;
-            }
+        for (int j = 0; j < kBatch; j++) bm = fmaxf(bm, m[j]);
+        const float c0 = wm == -INFINITY ? 0.0f : __expf(wm - bm);
+        acc.x *= c0; acc.y *= c0; acc.z *= c0; acc.w *= c0;
+        wl *= c0;
+#pragma unroll
+        for (int j = 0; j < kBatch; j++) {
+            const float c = m[j] == -INFINITY ? 0.0f : __expf(m[j] - bm);
+            acc.x = fmaf(o[j].x, c, acc.x); acc.y = fmaf(o[j].y, c, acc.y);
+            acc.z = fmaf(o[j].z, c, acc.z); acc.w = fmaf(o[j].w, c, acc.w);
+            wl = fmaf(l[j], c, wl);
+        }
+        wm = bm;
     }
-    part[group * kHd + d] = acc;
-    if (d == 0) {
-        part_ml[group * 2] = gmx;
-        part_ml[group * 2 + 1] = lsum;
+    reinterpret_cast<float4 *>(part + warp * kHd)[lane] = acc;
+    if (lane == 0) {
+        part_ml[warp * 2] = wm;
+        part_ml[warp * 2 + 1] = wl;
     }
     consumer_sync();
     if (group == 0) {
+        const int d = tid;
         float gm = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < kGroups; i++) gm = fmaxf(gm, part_ml[i * 2]);
+        for (int i = 0; i < kV2Consumers; i++) gm = fmaxf(gm, part_ml[i * 2]);
         float a = 0.0f, lt = 0.0f;
 #pragma unroll
-        for (int i = 0; i < kGroups; i++) {
+        for (int i = 0; i < kV2Consumers; i++) {
             const float m = part_ml[i * 2];
             const float corr = m == -INFINITY ? 0.0f : __expf(m - gm);
-            a += part[i * kHd + d] * corr;
-            lt += part_ml[i * 2 + 1] * corr;
+            a = fmaf(part[i * kHd + d], corr, a);
+            lt = fmaf(part_ml[i * 2 + 1], corr, lt);
         }
         const float r = hadamard_thread(gs, a / fmaxf(lt, 1e-10f), signs[d], xs, kHd);
         attn_out[(size_t)head * kHd + d] = __float2half_rn(r);
@@ -489,11 +531,17 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         chunk = (chunk + kTile - 1) / kTile * kTile;
         const int used = (seq_len + chunk - 1) / chunk;  // splits that hold positions (<= p.splits)
 
+        const int n_heads = p.nh + 2 * p.nkv;
         for (int l = 0; l < p.L; l++) {
             const MegaLayer ly = *reinterpret_cast<const MegaLayer *>(desc + (l & 1) * kDescWords + 5 * kPhaseWords);
             // ---- QKV (layer 0: plain, on the normalised embedding; later layers: residual + norm prologue)
             if (l > 0) grid_wait(7 * l - 1);
             matvec_phase(4 * l, l == 1 ? 7 * p.L + 2 : -1);
+            float sv[32];  // this thread's share of the projection matrix, on its way while the grid gathers
+            if (blockIdx.x < n_heads) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) sv[j] = __ldg(p.qjl_t + (size_t)(32 * group + j) * kHd + gs.d);
+            }
             grid_wait(7 * l);
             // the next layer's descriptors: the buffer's previous tenant (layer l - 1) was last read before the barrier above
             // (by the threads of groups 1-3: group 0 carries the head items of the phase that starts here)
@@ -509,10 +557,17 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 a.ktab = EncodeTables{p.signs, cbk, bdk, p.qjl_t, p.k_levels, 1};
                 a.vtab = EncodeTables{p.signs, cbv, bdv, p.qjl_t, p.v_levels, 0};
                 a.kc = ly.kc; a.vc = ly.vc; a.ks = ly.ks; a.vs = ly.vs; a.krn = ly.krn;
-                float *sh = reinterpret_cast<float *>(U) + group * (3 * kHd + 4);
+                float *sh = reinterpret_cast<float *>(U);
+                QjlCoop pj{sv, sh + 3 * kHd + 4};
                 if (!dead)
-                    for (int item = blockIdx.x + gridDim.x * group; item < p.nh + 2 * p.nkv; item += gridDim.x * kGroups)
-                        mega_prep_item(gs, a, sh, item);
+                    for (int item = blockIdx.x; item < n_heads; item += gridDim.x) {
+                        if (group == 0)
+                            tq_prep_item(gs, a, sh, item, 0, pj);
+                        else if (item < p.nh)
+                            pj.assist<false>(sh, gs.d, group);            // query head: projects the rotated query
+                        else if (item < p.nh + p.nkv)
+                            pj.assist<true>(sh + 2 * kHd, gs.d, group);  // key head: projects the residual
+                    }
             }
             items_done(7 * l + 1);
             // This group's first attention item: its cached rows do not depend on this layer's cache write (only the row

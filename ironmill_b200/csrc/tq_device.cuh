@@ -78,6 +78,33 @@ struct EncodeTables {
     int n_levels, is_k;
 };
 
+// The QJL projection of a 128-vector held in shared memory: thread d computes sum_k S^T[k][d] * vec[k], walking k
+// upwards.  `Direct` reads the thread's matrix column itself, 64 values in flight at a time; begin() may be called
+// early so that the first half travels while the caller still reduces.  EXACT selects the encoder's arithmetic
+// (separate multiply and add, bit-exact with turboquant_cache_write); otherwise fused multiply-adds.
+struct QjlDirect {
+    const float *qjl_t;
+    float sv[64];
+    __device__ __forceinline__ void begin(int d, int hd) {
+#pragma unroll
+        for (int j = 0; j < 64; j++) sv[j] = j < hd ? qjl_t[(size_t)j * hd + d] : 0.0f;
+    }
+    template <bool EXACT, class Scope>
+    __device__ __forceinline__ float finish(const Scope &, const float *vec, int d, int hd) {
+        float proj = 0.0f;
+        for (int k0 = 0; k0 < hd; k0 += 64) {
+            if (k0 > 0) {
+#pragma unroll
+                for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 64; j++)
+                if (k0 + j < hd) proj = EXACT ? __fadd_rn(proj, __fmul_rn(sv[j], vec[k0 + j])) : fmaf(sv[j], vec[k0 + j], proj);
+        }
+        return proj;
+    }
+};
+
 // Encodes one head vector; thread d of the scope (n = hd threads) holds element d (already widened from
 // fp16).  sh = 3*hd floats.  Every operation and its order follow turboquant_cache_write; the QJL dot
 // product walks k upwards with separate multiply and add, reading the transposed matrix so that the
@@ -119,9 +146,9 @@ __device__ __forceinline__ float tq_tree_sum(const Scope &sc, float v, float *bu
 // same add / subtract, the same summation trees, the QJL dot product walking k upwards with separate multiply and
 // add (reading the transposed matrix so that the warp's loads coalesce).  Butterfly strides below 32 and the
 // tails of the trees run on warp shuffles instead of shared memory + barriers; the operands are the same.
-template <class Scope>
+template <class Scope, class Proj>
 __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
-                                               float *scale_out, float *rnorm_out, float sg) {
+                                               float *scale_out, float *rnorm_out, float sg, Proj &pj) {
     float *xs = sh, *red = sh + hd, *res = sh + 2 * hd;
     const int d = sc.d;
     float v = __fmul_rn(xin, sg);
@@ -157,28 +184,22 @@ __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const
     if (tb.is_k) {
         const float r = __fsub_rn(u, tb.cb[lo]);
         res[d] = r;
-        // first half of this thread's matrix column: in flight while the residual norm is reduced
-        float sv[64];
-#pragma unroll
-        for (int j = 0; j < 64; j++) sv[j] = j < hd ? tb.qjl_t[(size_t)j * hd + d] : 0.0f;
+        pj.begin(d, hd);  // a direct projector's first loads travel while the residual norm is reduced
         const float rs = tq_tree_sum(sc, __fmul_rn(r, r), red, hd);  // its barriers also publish res[]
         if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(rs, 1e-20f));
-        float proj = 0.0f;
-        for (int k0 = 0; k0 < hd; k0 += 64) {
-            if (k0 > 0) {
-#pragma unroll
-                for (int j = 0; j < 64; j++) sv[j] = k0 + j < hd ? tb.qjl_t[(size_t)(k0 + j) * hd + d] : 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 64; j++)
-                if (k0 + j < hd) proj = __fadd_rn(proj, __fmul_rn(sv[j], res[k0 + j]));
-        }
+        const float proj = pj.template finish<true>(sc, res, d, hd);
         if (proj >= 0.0f) byte |= 0x80u;
     }
     cache_row[d] = (uint8_t)byte;
     sc.sync();  // sh may be reused by the caller
 }
 
+template <class Scope>
+__device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
+                                               float *scale_out, float *rnorm_out, float sg) {
+    QjlDirect pj{tb.qjl_t};
+    tq_encode_body(sc, xin, tb, sh, hd, cache_row, scale_out, rnorm_out, sg, pj);
+}
 template <class Scope>
 __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const EncodeTables &tb, float *sh, int hd, uint8_t *cache_row,
                                                float *scale_out, float *rnorm_out) {
@@ -200,14 +221,14 @@ struct AttnParams {
 
 __device__ __forceinline__ int qidx(int d) { return d + (d >> 5); }
 template <int GQ>
-__device__ __forceinline__ int qrow(int d) { return d * 2 * GQ + (d >> 5) * 4; }  // first float of dimension d's row in AttnSmem::qv
+__device__ __forceinline__ int qrow(int d) { return d * 2 * GQ + (d >> 4) * 4; }  // first float of dimension d's row in AttnSmem::qv
 
 template <int GQ>
 struct AttnSmem {  // per work item (128 threads)
     // queries, one row of 2 GQ floats per dimension: the GQ rotated queries, then the GQ values of S * q, so that the
     // score loop fetches all of a dimension's operands with one or two vector loads; 4 floats of padding after
-    // every 32 rows keep the four dimension blocks a warp reads at once on different banks
-    float qv[2 * GQ * kHd + 16];
+    // every 16 rows keep the eight dimension slices a warp reads at once on different banks
+    float qv[2 * GQ * kHd + 32];
     alignas(16) uint8_t tile[kTile * kPitchB];  // the K codes of a tile, then the V codes of the same positions
     float t_ks[kTile], t_rw[kTile], t_vs[kTile];
     float sc[GQ * kTile];
@@ -330,54 +351,68 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         if (ts + kTile < r1) fetch(ts + kTile);
         sc.sync();
 
-        // ---- scores: warp w owns positions 8w..8w+7, 4 lanes per position (32 dims each) ----
-        {
-            const int pl = lane >> 2, dq = lane & 3, pp = warp * 8 + pl;
-            float a1[GQ], a2[GQ];
+        // ---- scores: warp w owns positions 8w..8w+7; a lane scores TWO positions over a slice of 16 dimensions, so
+        // every query row it fetches (the loop's dominant shared-memory traffic) serves both ----
+        constexpr int GP = GQ < 4 ? GQ : 4;  // heads per pass: eight heads at once would not fit the register budget
+#pragma unroll 1
+        for (int gb = 0; gb < GQ; gb += GP) {
+            const int ds = lane & 7, p0 = warp * 8 + (lane >> 3) * 2;
+            float s0[GP], s1[GP], t0[GP], t1[GP];  // centroid and sign sums of the two positions
 #pragma unroll
-            for (int g = 0; g < GQ; g++) a1[g] = a2[g] = 0.0f;
-            const uint32_t *krow = reinterpret_cast<const uint32_t *>(sm.tile + pp * kPitchB + dq * 32);
+            for (int g = 0; g < GP; g++) s0[g] = s1[g] = t0[g] = t1[g] = 0.0f;
+            const uint32_t *kr0 = reinterpret_cast<const uint32_t *>(sm.tile + p0 * kPitchB + ds * 16);
+            const uint32_t *kr1 = reinterpret_cast<const uint32_t *>(sm.tile + (p0 + 1) * kPitchB + ds * 16);
 #pragma unroll
-            for (int jw = 0; jw < 8; jw++) {
-                const uint32_t w4 = krow[jw];
+            for (int jw = 0; jw < 4; jw++) {
+                const uint32_t w0 = kr0[jw], w1 = kr1[jw];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const uint32_t b = (w4 >> (8 * e)) & 0xffu;
-                    const float kc = cbk[b & 0x7fu];
-                    const float sgn = (b & 0x80u) ? 1.0f : -1.0f;
-                    float qd[2 * GQ];  // this dimension's row: vector loads (the row is 8 GQ bytes, 8-byte aligned at least)
+                    const uint32_t b0 = (w0 >> (8 * e)) & 0xffu, b1 = (w1 >> (8 * e)) & 0xffu;
+                    const float kc0 = cbk[b0 & 0x7fu], kc1 = cbk[b1 & 0x7fu];
+                    const float sg0 = (b0 & 0x80u) ? 1.0f : -1.0f, sg1 = (b1 & 0x80u) ? 1.0f : -1.0f;
+                    float qa[GP], qb[GP];  // this dimension's row: the rotated queries and S * q of the pass's heads (vector loads)
                     {
-                        const float *row = sm.qv + (dq * 32 + jw * 4 + e) * 2 * GQ + dq * 4;
+                        const float *row = sm.qv + qrow<GQ>(ds * 16 + jw * 4 + e);
                         if (GQ == 1) {
                             const float2 v = *reinterpret_cast<const float2 *>(row);
-                            qd[0] = v.x; qd[1] = v.y;
+                            qa[0] = v.x; qb[0] = v.y;
+                        } else if (GQ == 2) {
+                            const float4 v = *reinterpret_cast<const float4 *>(row);
+                            qa[0] = v.x; qa[1] = v.y; qb[0] = v.z; qb[1] = v.w;
                         } else {
-#pragma unroll
-                            for (int i = 0; i < 2 * GQ; i += 4) {
-                                const float4 v = *reinterpret_cast<const float4 *>(row + i);
-                                qd[i] = v.x; qd[i + 1] = v.y; qd[i + 2] = v.z; qd[i + 3] = v.w;
-                            }
+                            const float4 va = *reinterpret_cast<const float4 *>(row + gb);
+                            const float4 vb = *reinterpret_cast<const float4 *>(row + GQ + gb);
+                            qa[0] = va.x; qa[1] = va.y; qa[2] = va.z; qa[3] = va.w;
+                            qb[0] = vb.x; qb[1] = vb.y; qb[2] = vb.z; qb[3] = vb.w;
                         }
                     }
 #pragma unroll
-                    for (int g = 0; g < GQ; g++) {
-                        a1[g] = fmaf(qd[g], kc, a1[g]);
-                        a2[g] = fmaf(qd[GQ + g], sgn, a2[g]);
+                    for (int g = 0; g < GP; g++) {
+                        s0[g] = fmaf(qa[g], kc0, s0[g]);
+                        t0[g] = fmaf(qb[g], sg0, t0[g]);
+                        s1[g] = fmaf(qa[g], kc1, s1[g]);
+                        t1[g] = fmaf(qb[g], sg1, t1[g]);
                     }
                 }
             }
+            const float rw0 = sm.t_rw[p0], rw1 = sm.t_rw[p0 + 1];
 #pragma unroll
-            for (int g = 0; g < GQ; g++) {
-                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 1);
-                a1[g] += __shfl_xor_sync(0xffffffffu, a1[g], 2);
-                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 1);
-                a2[g] += __shfl_xor_sync(0xffffffffu, a2[g], 2);
+            for (int g = 0; g < GP; g++) {  // the residual weight is per position: fold before the slices are summed
+                s0[g] = fmaf(rw0, t0[g], s0[g]);
+                s1[g] = fmaf(rw1, t1[g], s1[g]);
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    s0[g] += __shfl_xor_sync(0xffffffffu, s0[g], o);
+                    s1[g] += __shfl_xor_sync(0xffffffffu, s1[g], o);
+                }
             }
-            if (dq == 0) {
-                const float ksv = sm.t_ks[pp], rw = sm.t_rw[pp];
+            if (ds == 0) {
+                const float k0 = p.attn_scale * sm.t_ks[p0], k1 = p.attn_scale * sm.t_ks[p0 + 1];
 #pragma unroll
-                for (int g = 0; g < GQ; g++)
-                    sm.sc[pp * GQ + g] = pp < nt ? p.attn_scale * (ksv * (a1[g] + rw * a2[g])) : -INFINITY;
+                for (int g = 0; g < GP; g++) {
+                    sm.sc[p0 * GQ + gb + g] = p0 < nt ? k0 * s0[g] : -INFINITY;
+                    sm.sc[(p0 + 1) * GQ + gb + g] = p0 + 1 < nt ? k1 * s1[g] : -INFINITY;
+                }
             }
         }
         sc.sync();
@@ -443,9 +478,10 @@ struct PrepArgs {
     float *ks, *vs, *krn;
 };
 
-// One head (slot in [0, nh + 2 nkv)) of token st on a 128-thread scope.  sh: 3*128 + 4 floats.
-template <class Scope>
-__device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a, float *sh, int slot, int st) {
+// One head (slot in [0, nh + 2 nkv)) of token st on a 128-thread scope.  sh: 3*128 + 4 floats.  pj: the QJL
+// projector (key heads project sh + 256, query heads sh).
+template <class Scope, class Proj>
+__device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a, float *sh, int slot, int st, Proj &pj) {
     float *red = sh + 3 * kHd;
     const int d = sc.d;
     const int seq = st / a.T, t = st % a.T;
@@ -484,7 +520,7 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     sc.sync();
     if (!is_q) {
         const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row, sg);
+        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row, sg, pj);
         return;
     }
     if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;
@@ -493,16 +529,16 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
     dst[d] = rq;
     sc.sync();
-    float acc = 0.0f;
-    for (int k0 = 0; k0 < kHd; k0 += 64) {  // 64 loads of the matrix column in flight at a time
-        float sv[64];
-#pragma unroll
-        for (int j = 0; j < 64; j++) sv[j] = a.ktab.qjl_t[(size_t)(k0 + j) * kHd + d];
-#pragma unroll
-        for (int j = 0; j < 64; j++) acc = fmaf(sv[j], sh[k0 + j], acc);
-    }
+    pj.begin(d, kHd);
+    const float acc = pj.template finish<false>(sc, sh, d, kHd);
     dst[kHd + d] = acc;
     sc.sync();  // sh may be reused by the caller
+}
+
+template <class Scope>
+__device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a, float *sh, int slot, int st) {
+    QjlDirect pj{a.ktab.qjl_t};
+    tq_prep_item(sc, a, sh, slot, st, pj);
 }
 
 // Combine the splits of one (token, head), normalise, rotate back, write fp16.
