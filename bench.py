@@ -294,7 +294,7 @@ def run_decode(args, rank, world):
     step_bytes = eng.step_bytes(ctx_mid, B)
     launches = eng.step_launches()
     # dominant kernel: the whole-token decode kernel when the engine uses it (batch 1, one GPU), else the largest projection launch
-    tk = eng.token_kernel_profile(8) if (B == 1 and world == 1) else None
+    tk = eng.token_kernel_profile(8) if (B == 1 and eng.token_kernel()) else None   # every rank: the kernels of a tensor-parallel model wait on one another
     dom_us, dom_bytes, _ = time_dominant_kernel(dev) if rank == 0 else (1.0, 0, 0)
     if rank != 0:
         return
@@ -332,7 +332,9 @@ def run_decode(args, rank, world):
         "config": {"workload": "llama3_8b_shape_int4_g128_awq_tq8_decode", "batch": B, "prompt_tokens": P,
                    "context_during_timing": [ctx0, ctx0 + K], "layers": cfg.num_hidden_layers, "hidden": 4096, "ffn": 14336, "vocab": 128256,
                    "parallelism": f"tp{world}" if world > 1 else "single",
-                   "allreduce": ("one-shot peer-memory kernel" if eng.tp_peer_allreduce() else "nccl") if world > 1 else None,
+                   "allreduce": (("inside the whole-token kernel: partial sums stored to every rank's mailbox over NVLink, barrier across ranks"
+                                  if (B == 1 and eng.token_kernel()) else "one-shot peer-memory kernel")
+                                 if eng.tp_peer_allreduce() else "nccl") if world > 1 else None,
                    "l2_policy": "inputs larger than L2: every step streams this rank's %.2f GB of weights + KV" % (step_bytes / 1e9),
                    "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2)},
         "roofline": roof,

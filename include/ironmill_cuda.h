@@ -326,6 +326,11 @@ size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
  * peer memory (CUDA IPC + NVLink stores, set up by im_cuda_model_tp_init; IM_TP_PEER=0 disables it), 0 when NCCL's
  * all-reduce does it.  No counterpart in the reference (it has no tensor parallelism). */
 int im_cuda_model_tp_peer_allreduce(const im_model *m);
+/* 1 when batch-1 decode steps of this model run in the whole-token kernel (all layers in one cooperative launch), 0
+ * when they run as a graph of per-projection kernels.  Under tensor parallelism the kernel of every rank exchanges the
+ * partial sums of the row-split projections through peer memory and its barriers after those projections span all
+ * ranks (IM_TP_MEGA=0 keeps tensor-parallel models on the per-kernel schedule; IM_MEGA=0 every model). */
+int im_cuda_model_token_kernel(const im_model *m);
 /* Number of kernel launches in one captured decode step. */
 int im_cuda_model_step_launches(const im_model *m);
 /* Timing of the whole-token decode kernel (all layers of a batch-1 step in one launch) by itself: the counterpart of

@@ -65,7 +65,7 @@ __device__ __forceinline__ void grid_arrive(unsigned *bar, int k) {
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(bar + k), "r"(1u) : "memory");
 }
 // One thread polls until every CTA has arrived (or the error word is set / the time limit passes).
-__device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err) {
+__device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err, unsigned limit_ms) {
     const unsigned want = gridDim.x;
     if (ld_acquire(bar + k) >= want) return true;
     const unsigned long long t0 = global_ns();
@@ -73,7 +73,28 @@ __device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err) 
         if (ld_acquire(bar + k) >= want) return true;
         if ((i & 127u) == 0) {
             if (ld_volatile(err) != 0) return false;
-            if (global_ns() - t0 > kWaitLimitNs) break;
+            if (global_ns() - t0 > (unsigned long long)limit_ms * 1000000ull) break;
+        }
+    }
+    atomicExch(err, 2);
+    return false;
+}
+
+// Cross-rank barrier: the counter lives in this GPU's memory and every CTA of every rank adds to it over NVLink.  It is
+// never reset; `target` grows with the launch number (wrap-safe compare).  Same bounds as grid_poll.
+__device__ __forceinline__ bool xrank_poll(const unsigned *ctr, unsigned target, int *err, unsigned limit_ms) {
+    auto ld = [&]() {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+        return v;
+    };
+    if ((int)(ld() - target) >= 0) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned i = 1;; i++) {
+        if ((int)(ld() - target) >= 0) return true;
+        if ((i & 127u) == 0) {
+            if (ld_volatile(err) != 0) return false;
+            if (global_ns() - t0 > (unsigned long long)limit_ms * 1000000ull) break;
         }
     }
     atomicExch(err, 2);
@@ -152,9 +173,11 @@ __device__ __forceinline__ void mega_stage_plain(const __half *__restrict__ x, c
 
 // Residual + RMSNorm input: r = x + b, staged value r * gamma (/ awq); returns this thread's share of sum r^2.
 // resid_out: r rounded to fp16; each 8-element chunk is written by one CTA of the grid, from registers.
-__device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, const __half *__restrict__ b, const __half *__restrict__ gamma,
+// nsum > 1 (tensor parallel): b is a mailbox of nsum slots, `slot` halves apart, filled by the ranks; the operand is
+// their sum in f32 in rank order, rounded to fp16 (what the stand-alone all-reduce hands to the next kernel).
+__device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, const __half *b, const __half *__restrict__ gamma,
                                                  const __half *__restrict__ awq, __half *__restrict__ resid_out, int G, uint32_t *xq,
-                                                 float2 *meta) {
+                                                 float2 *meta, int nsum, int slot) {
     const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
     float sq = 0.0f;
 #pragma unroll 2
@@ -163,7 +186,7 @@ __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, c
         const bool live = grp < G;
         const int k = (live ? grp : g0) * 128 + hl * 8;
         const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
-        const uint4 rb = *reinterpret_cast<const uint4 *>(b + k);
+        const uint4 rb = __ldcg(reinterpret_cast<const uint4 *>(b + k));
         const uint4 rg = *reinterpret_cast<const uint4 *>(gamma + k);
         uint4 ra = make_uint4(0, 0, 0, 0);
         if (awq) ra = *reinterpret_cast<const uint4 *>(awq + k);
@@ -171,6 +194,18 @@ __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, c
         unpack8(raw, v);
         unpack8(rb, fb);
         unpack8(rg, fg);
+        if (nsum > 1) {
+#pragma unroll 2
+            for (int r = 1; r < nsum; r++) {
+                const uint4 rr = __ldcg(reinterpret_cast<const uint4 *>(b + (size_t)r * slot + k));
+                float fr[8];
+                unpack8(rr, fr);
+#pragma unroll
+                for (int i = 0; i < 8; i++) fb[i] += fr[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) fb[i] = __half2float(__float2half_rn(fb[i]));
+        }
         unsigned hres[4];
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
@@ -305,7 +340,9 @@ __device__ IM_MEGA_ITEM_INLINE void mega_reduce_head(const GroupScope &gs, int g
 
 }  // namespace
 
-template <int GQ>
+// TP: the tensor-parallel variant (exchange of the row-split projections' partial sums between the ranks' kernels);
+// compiled apart so that the single-GPU kernel carries none of it.
+template <int GQ, bool TP>
 __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int nring = p.nring;
@@ -325,6 +362,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NP = 4 * p.L;
+    // Patience of every wait.  Tensor parallel: a rank may sit behind a peer whose launch came later (host jitter, a
+    // graph being instantiated), and while its consumers wait for that peer its producer waits for them.
+    const unsigned wait_ms = TP ? 5000u : (unsigned)(kWaitLimitNs / 1000000ull);
     // words of layer l's descriptors -> desc[l & 1]; called by consumer threads one layer ahead (and for layer 0 at start)
     auto copy_desc = [&](int l, int t, int nthreads) {
         uint32_t *dst = desc + (l & 1) * kDescWords;
@@ -369,7 +409,14 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 c.it = StageIter(r.t_begin, r.t_end, c.ph.G);
             }
         };
-        auto arrive = [&](int q) {  // all lanes' output writes precede the arrival
+        auto arrive = [&](int q, int xout) {  // all lanes' output writes precede the arrival
+            if (TP && xout) {  // the outputs went to every rank: so does the arrival (counter 2 * layer + mailbox index)
+                __threadfence_system();
+                __syncwarp();
+                if (lane < p.world)
+                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.xbar[lane] + (q >> 2) * 2 + (xout - 1)), "r"(1u) : "memory");
+                return;
+            }
             __threadfence();
             __syncwarp();
             if (lane == 0) atomicAdd(p.bar + phase_barrier(q), 1u);
@@ -380,14 +427,14 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         // phases in which this CTA has no tiles are passed at once
         auto skip_empty_done = [&]() {
             while (done.q < NP && done.it.t >= done.it.t_end) {
-                arrive(done.q);
+                arrive(done.q, done.ph.xout);
                 open(done, done.q + 1);
             }
         };
         skip_empty_done();
         bool ok = true;
         auto reclaim = [&](int slot_, int parity) {  // the oldest stage in flight lives in slot_
-            if (ok && !mbar_wait_warp(&empty[slot_], parity, p.err)) ok = false;
+            if (ok && !mbar_wait_warp(&empty[slot_], parity, p.err, wait_ms)) ok = false;
             int dt0, dn, drb, dgrp;
             done.it.next(dt0, dn, drb, dgrp);
             const MegaPhase &ph = done.ph;
@@ -406,11 +453,19 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                     if (lane < 8 && n < ph.N) ph.y[n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
                 } else {
                     const int n = drb * 16 + lane;
-                    if (lane < 16 && n < ph.N) ph.y[n] = __float2half_rn(v * ri);
+                    if (lane < 16 && n < ph.N) {
+                        const __half h = __float2half_rn(v * ri);
+                        if (TP && ph.xout) {  // this rank's partial sum: one NVLink store per rank (its own included)
+                            const size_t off = ((size_t)(ph.xout - 1) * p.world + p.rank) * p.xH + n;
+                            for (int r = 0; r < p.world; r++) p.xmail[r][off] = h;
+                        } else {
+                            ph.y[n] = h;
+                        }
+                    }
                 }
             }
             if (done.it.t >= done.it.t_end) {  // that was this CTA's last stage of the phase
-                arrive(done.q);
+                arrive(done.q, done.ph.xout);
                 open(done, done.q + 1);
                 skip_empty_done();
             }
@@ -453,7 +508,19 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 
         auto grid_wait = [&](int k) {
             if (tid == 0) {
-                const bool okw = dead ? false : grid_poll(p.bar, k, p.err);
+                const bool okw = dead ? false : grid_poll(p.bar, k, p.err, wait_ms);
+                reinterpret_cast<int *>(misc)[30] = okw ? 1 : 0;
+                if (p.trace && blockIdx.x == 0) p.trace[k + 1] = global_ns();
+            }
+            consumer_sync();
+            if (reinterpret_cast<int *>(misc)[30] == 0) dead = true;
+        };
+        constexpr bool tp = TP;
+        const unsigned xtarget = tp ? (ld_volatile(reinterpret_cast<const int *>(p.xepoch)) + 1u) * (unsigned)p.world * gridDim.x : 0u;
+        // barrier k of a row-split projection under tensor parallelism: counter xi of this rank, fed by all ranks
+        auto xrank_wait = [&](int k, int xi) {
+            if (tid == 0) {
+                const bool okw = dead ? false : xrank_poll(p.xbar[p.rank] + xi, xtarget, p.err, wait_ms);
                 reinterpret_cast<int *>(misc)[30] = okw ? 1 : 0;
                 if (p.trace && blockIdx.x == 0) p.trace[k + 1] = global_ns();
             }
@@ -476,7 +543,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             const bool stamp = p.trace && fine >= 0 && blockIdx.x == 0 && tid == 0;
             if (stamp) p.trace[fine] = global_ns();
             if (ph.resid) {
-                float sq = mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, xq, meta);
+                float sq = mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, xq, meta, (TP && ph.xin) ? p.world : 1, p.xH);
                 sq = warp_sum(sq);
                 if (lane == 0) misc[8 + warp] = sq;
                 consumer_sync();
@@ -502,7 +569,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             int t0, n, rb, grp0;
             tm.reset();
             while (it.next(t0, n, rb, grp0)) {
-                if (!dead && !mbar_wait_warp(&full[slot], par, p.err)) dead = true;
+                if (!dead && !mbar_wait_warp(&full[slot], par, p.err, wait_ms)) dead = true;
                 const unsigned char *st = ring + (size_t)slot * kStageBytes;
                 if (!dead && warp < n) {
                     const int tb = warp + kV2Consumers;
@@ -535,7 +602,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         for (int l = 0; l < p.L; l++) {
             const MegaLayer ly = *reinterpret_cast<const MegaLayer *>(desc + (l & 1) * kDescWords + 5 * kPhaseWords);
             // ---- QKV (layer 0: plain, on the normalised embedding; later layers: residual + norm prologue)
-            if (l > 0) grid_wait(7 * l - 1);
+            if (l > 0) {  // the previous layer's down projection
+                if (tp) xrank_wait(7 * l - 1, 2 * (l - 1) + 1); else grid_wait(7 * l - 1);
+            }
             matvec_phase(4 * l, l == 1 ? 7 * p.L + 2 : -1);
             float sv[32];  // this thread's share of the projection matrix, on its way while the grid gathers
             if (blockIdx.x < n_heads) {
@@ -606,7 +675,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             grid_wait(7 * l + 3);
 
             matvec_phase(4 * l + 1, l == 1 ? 7 * p.L + 2 + 24 : -1);  // o
-            grid_wait(7 * l + 4);
+            if (tp) xrank_wait(7 * l + 4, 2 * l); else grid_wait(7 * l + 4);
             matvec_phase(4 * l + 2, l == 1 ? 7 * p.L + 2 + 48 : -1);  // residual + norm -> gate/up + SiLU
             grid_wait(7 * l + 5);
             matvec_phase(4 * l + 3, l == 1 ? 7 * p.L + 2 + 72 : -1);  // down
@@ -622,6 +691,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             // every CTA has passed every barrier except possibly the very last one (down of the last layer),
             // whose arrivals all precede the exits counted above
             for (int i = 0; i <= nbar; i++) p.bar[i] = 0;
+            if (TP) *p.xepoch = *p.xepoch + 1u;  // every CTA read it at its start, long before the last one leaves
             if (p.trace) p.trace[nbar + 1] = global_ns();
         }
     }
@@ -652,11 +722,11 @@ int mega_u_bytes(int G_max, int gq) {
     return (u + 15) & ~15;
 }
 
-template <int GQ>
+template <int GQ, bool TP>
 static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st) {
     const size_t smem = mega_smem_bytes(p.nring, p.u_bytes);
     if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
-    auto kern = decode_token_kernel<GQ>;
+    auto kern = decode_token_kernel<GQ, TP>;
     static thread_local bool configured = false;
     if (!configured) {
         IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
@@ -678,11 +748,12 @@ static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st
 
 int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st) {
     if (p.nkv <= 0 || p.nh % p.nkv != 0) return IM_ERR_BOUNDS;
+    const bool tp = p.world > 1;
     switch (p.nh / p.nkv) {
-        case 1: return mega_launch_t<1>(p, dev, st);
-        case 2: return mega_launch_t<2>(p, dev, st);
-        case 4: return mega_launch_t<4>(p, dev, st);
-        case 8: return mega_launch_t<8>(p, dev, st);
+        case 1: return tp ? mega_launch_t<1, true>(p, dev, st) : mega_launch_t<1, false>(p, dev, st);
+        case 2: return tp ? mega_launch_t<2, true>(p, dev, st) : mega_launch_t<2, false>(p, dev, st);
+        case 4: return tp ? mega_launch_t<4, true>(p, dev, st) : mega_launch_t<4, false>(p, dev, st);
+        case 8: return tp ? mega_launch_t<8, true>(p, dev, st) : mega_launch_t<8, false>(p, dev, st);
         default: return IM_ERR_BOUNDS;
     }
 }

@@ -14,6 +14,10 @@ struct MegaPhase {         // one projection of the token; 4 per layer in execut
     __half *y;             // outputs [N]
     int nblk, G, N;
     int gate_up;           // tile rows 0-7 gate, 8-15 up of the same 8 outputs -> SiLU(gate) * up
+    // Tensor parallel (MegaParams::world > 1).  xout = 1 + mailbox index: the outputs are this rank's partial sums of
+    // a row-split projection and go to slot `rank` of that mailbox on EVERY rank instead of y; the phase's barrier then
+    // spans all ranks.  xin = 1: resid points at a mailbox here, and b is the fp16-rounded sum of its `world` slots.
+    int xout, xin;
 };
 
 struct MegaLayer {
@@ -43,6 +47,12 @@ struct MegaParams {
     unsigned *bar;            // 7 * L arrival counters + 1 exit counter, zero between launches
     int *err;
     unsigned long long *trace;  // optional: CTA 0 stamps %globaltimer when it leaves each barrier (7L + 2 words)
+    // Tensor parallel: every rank runs this kernel on its shard, on its own GPU, in step with the others.
+    int world, rank;            // world <= 1: single GPU, nothing below is read
+    int xH;                     // mailbox slot length in halves (the hidden size)
+    __half *xmail[8];           // rank r's mailboxes [2][world][xH] as mapped here (peer memory; [rank] is local)
+    unsigned *xbar[8];          // rank r's cross-rank arrival counters [2 * L]; they only grow, one launch adds world * grid to each
+    unsigned *xepoch;           // local: launches completed so far (sets the counters' target)
 };
 
 // Shared-memory bytes the kernel needs for `nring` ring slots and `u_bytes` of phase scratch.

@@ -112,6 +112,8 @@ struct PeerAllreduce {
     unsigned char *base = nullptr;  // this rank's allocation: [flags: kXarMaxWorld u32][seq u32][pad to 256][buf: 2 x world x cap halves]
     size_t bytes = 0, cap = 0;      // cap: halves per vector
     unsigned char *peer[kXarMaxWorld] = {};  // every rank's allocation as mapped here (own included)
+    // appended for the tensor-parallel whole-token kernel: [mailboxes: 2 x world x hidden halves][2 L counters][launch count]
+    size_t mail_off = 0, bar_off = 0, epoch_off = 0;
 };
 struct XarArgs {
     unsigned *flags, *seq;             // local
@@ -495,8 +497,9 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         int rc = mega_launch(m->mega, m->dev, st);
         if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "whole-token decode kernel: shapes do not fit");
         IM_TRY(rc);
+        IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)H, st));  // tensor parallel: the last layer's down projection
         IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)H, st));
-        nl += 2;
+        nl += 2 + (m->world > 1 ? 1 : 0);
     }
     const bool gemm = !mega && m->gemm_ok && m->world == 1 && MT >= kGemmMinTokens;
     for (int l = 0; l < c.num_layers && gemm; l++) {
@@ -621,7 +624,9 @@ static int mega_prepare(Model *m) {
     const char *env = getenv("IM_MEGA");
     if (m->mega_mode == 0 || (env && env[0] == '0')) return IM_OK;
     const im_model_config &c = m->cfg;
-    if (m->world != 1 || c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
+    const bool tp = m->world > 1;
+    if (tp && (!m->xar.ok || m->world > 8 || c.hidden_size % 128 != 0)) return IM_OK;  // needs the peer mapping of tp_init
+    if (c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
     const int gq = m->nh_l / m->nkv_l;
     if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return IM_OK;
     int g_max = 0;
@@ -656,6 +661,14 @@ static int mega_prepare(Model *m) {
         gu.x = m->hidden; gu.resid = m->ffn_down; gu.gamma = Ly.post_ln; gu.resid_out = m->residual; gu.y = m->ffn_gate; gu.gate_up = 1;
         dn.tiles = Ly.down->tiles; dn.awq = Ly.down->awq; dn.nblk = Ly.down->nblk; dn.G = Ly.down->G; dn.N = Ly.down->N;
         dn.x = m->ffn_gate; dn.y = m->ffn_down;
+        if (tp) {  // o and down are row-split: partial sums travel through the mailboxes, the next phase sums them
+            __half *mail = reinterpret_cast<__half *>(m->xar.base + m->xar.mail_off);
+            const size_t box = (size_t)m->world * c.hidden_size;
+            o.xout = 1;
+            gu.resid = mail; gu.xin = 1;
+            if (l > 0) { q.resid = mail + box; q.xin = 1; }
+            if (l + 1 < L) dn.xout = 2;  // the last layer's sum feeds the final norm outside the kernel
+        }
         ph[4 * l] = q; ph[4 * l + 1] = o; ph[4 * l + 2] = gu; ph[4 * l + 3] = dn;
         ml[l] = MegaLayer{Ly.q_norm, Ly.k_norm, Ly.kc, Ly.vc, Ly.ks, Ly.vs, Ly.krn};
     }
@@ -689,6 +702,14 @@ static int mega_prepare(Model *m) {
     IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;
+    if (tp) {
+        p.world = m->world; p.rank = m->rank; p.xH = c.hidden_size;
+        for (int r = 0; r < m->world; r++) {
+            p.xmail[r] = reinterpret_cast<__half *>(m->xar.peer[r] + m->xar.mail_off);
+            p.xbar[r] = reinterpret_cast<unsigned *>(m->xar.peer[r] + m->xar.bar_off);
+        }
+        p.xepoch = reinterpret_cast<unsigned *>(m->xar.base + m->xar.epoch_off);
+    }
     // phase stamps of CTA 0 (a store per grid barrier; read back by im_cuda_model_token_kernel_profile)
     IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
     IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
@@ -819,6 +840,10 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
         PeerAllreduce &x = m->xar;
         x.cap = (size_t)4 * m->cfg.hidden_size;  // up to four batch rows: the decode batches that run one matvec per projection
         x.bytes = 256 + (size_t)2 * m->world * x.cap * sizeof(__half);
+        x.mail_off = (x.bytes + 255) & ~(size_t)255;
+        x.bar_off = (x.mail_off + (size_t)2 * m->world * m->cfg.hidden_size * sizeof(__half) + 255) & ~(size_t)255;
+        x.epoch_off = x.bar_off + (size_t)2 * m->cfg.num_layers * sizeof(unsigned);
+        x.bytes = x.epoch_off + 256;
         cudaIpcMemHandle_t mine{};
         unsigned char *xchg = nullptr;
         std::vector<cudaIpcMemHandle_t> all((size_t)m->world);
@@ -854,6 +879,24 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
         }
         x.ok = out == 1;
         (void)cudaGetLastError();
+        // The whole-token kernel exchanges its row-split partial sums through the same mapping; every rank must run it
+        // or none (a rank on the per-kernel schedule would never feed the others' counters).
+        if (x.ok) {
+            const char *me = getenv("IM_TP_MEGA");
+            int mine_ready = 0;
+            if (!(me && me[0] == '0') && mega_prepare(m) == IM_OK && m->mega_ready) mine_ready = 1;
+            int all_ready = 0;
+            int *ag = nullptr;
+            if (cudaMalloc((void **)&ag, sizeof(int)) == cudaSuccess) {
+                cudaMemcpy(ag, &mine_ready, sizeof(int), cudaMemcpyHostToDevice);
+                if (nccl()->AllReduce(ag, ag, 1, ncclInt, ncclMin, m->comm, m->stream) == ncclSuccess &&
+                    cudaStreamSynchronize(m->stream) == cudaSuccess)
+                    cudaMemcpy(&all_ready, ag, sizeof(int), cudaMemcpyDeviceToHost);
+                cudaFree(ag);
+            }
+            if (all_ready != 1) m->mega_ready = false;
+            (void)cudaGetLastError();
+        }
     }
     return IM_OK;
 #else
@@ -1224,6 +1267,7 @@ IM_EXPORT int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, in
 // 1 when the row-split projections of a tensor-parallel model are summed by the one-shot peer-memory all-reduce,
 // 0 when NCCL does it (single GPU: 0).
 IM_EXPORT int im_cuda_model_tp_peer_allreduce(const im_model *m) { return m && m->xar.ok ? 1 : 0; }
+IM_EXPORT int im_cuda_model_token_kernel(const im_model *m) { return m && m->mega_ready ? 1 : 0; }
 IM_EXPORT int im_cuda_model_step_launches(const im_model *m) { return m ? m->launches_per_step : 0; }
 
 IM_EXPORT size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch) {

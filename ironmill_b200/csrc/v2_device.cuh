@@ -37,21 +37,22 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err) {
+// limit_ms: patience of this wait (default: kWaitLimitNs); a kernel that may legitimately sit behind another GPU passes more
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, unsigned limit_ms = (unsigned)(kWaitLimitNs / 1000000ull)) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (unsigned i = 1;; i++) {
         __nanosleep(32);  // back off: a tight poll from many threads competes with the bulk copies for shared memory
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) break;
+        if ((i & 255u) == 0 && global_ns() - t0 > (unsigned long long)limit_ms * 1000000ull) break;
     }
     atomicExch(err, 1);
     return false;
 }
 // One lane polls for the warp.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *err) {
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *err, unsigned limit_ms = (unsigned)(kWaitLimitNs / 1000000ull)) {
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, err) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, err, limit_ms) ? 1 : 0;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {

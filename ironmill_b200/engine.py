@@ -164,6 +164,10 @@ class CudaInference:
         """True when the row-split projections are summed by the one-shot peer-memory all-reduce, False when NCCL does it."""
         return bool(self._model) and lib().im_cuda_model_tp_peer_allreduce(self._model) == 1
 
+    def token_kernel(self) -> bool:
+        """True when batch-1 decode steps run in the whole-token kernel (one cooperative launch for all layers)."""
+        return bool(self._model) and lib().im_cuda_model_token_kernel(self._model) == 1
+
     @staticmethod
     def tp_unique_id() -> bytes:
         buf = C.create_string_buffer(128)

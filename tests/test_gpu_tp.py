@@ -35,15 +35,17 @@ def _worker(rank, world, port, ret):
         eng.tp_init(ids[0])
         prompt = np.arange(7, dtype=np.uint32) * 13 % 1000
         outs = [eng.prefill(prompt)]
-        for t in (5, 17, 400):
+        steps = (5, 17, 400, 3, 999, 12, 77, 250)   # batch-1 steps: the whole-token kernel with its cross-rank barriers when enabled
+        for t in steps:
             outs.append(eng.decode_step(t))
         if rank == 0:
             single = CudaInference(CudaConfig(max_seq_len=64, device=0))
             single.load_weights(DictProvider(cfg, tensors), tq_signs=tqc.signs, tq_qjl=tqc.qjl)
-            refs = [single.prefill(prompt)] + [single.decode_step(t) for t in (5, 17, 400)]
+            refs = [single.prefill(prompt)] + [single.decode_step(t) for t in steps]
             err = max(float(np.abs(a - b).max()) for a, b in zip(outs, refs))
             ret[0] = err
             ret['peer'] = eng.tp_peer_allreduce()
+            ret['token_kernel'] = eng.token_kernel()
         dist.barrier()
     except Exception as e:  # noqa: BLE001
         ret[rank] = f"{type(e).__name__}: {e}"
@@ -63,5 +65,5 @@ def test_tp_matches_single_gpu():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert isinstance(ret.get(0), float) and ret[0] <= 5e-2, dict(ret)
-    print('one-shot peer all-reduce in use:', ret.get('peer'))
+    print('one-shot peer all-reduce in use:', ret.get('peer'), '| whole-token kernel across ranks:', ret.get('token_kernel'))
     assert all(r not in ret for r in range(1, world)), dict(ret)
