@@ -80,25 +80,27 @@ __device__ __forceinline__ bool grid_poll(const unsigned *bar, int k, int *err, 
     return false;
 }
 
-// Cross-rank barrier: the counter lives in this GPU's memory and every CTA of every rank adds to it over NVLink.  It is
-// never reset; `target` grows with the launch number (wrap-safe compare).  Same bounds as grid_poll.
-__device__ __forceinline__ bool xrank_poll(const unsigned *ctr, unsigned target, int *err, unsigned limit_ms) {
-    auto ld = [&]() {
-        unsigned v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
-        return v;
-    };
-    if ((int)(ld() - target) >= 0) return true;
+// 16 bytes of a mailbox (two {data, tag} pairs), past every cache
+__device__ __forceinline__ uint4 ld_mail(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Re-reads one 8-element chunk of a mailbox slot until its four tags match (the writer is another GPU).  Bounded like
+// every wait of the kernel: gives up after limit_ms or when the error word is set, and sets it.
+__device__ __forceinline__ void mail_settle(const uint4 *src, uint4 &a, uint4 &c, unsigned tag, int *err, unsigned limit_ms) {
+    if (a.y == tag && a.w == tag && c.y == tag && c.w == tag) return;
     const unsigned long long t0 = global_ns();
     for (unsigned i = 1;; i++) {
-        if ((int)(ld() - target) >= 0) return true;
+        a = ld_mail(src);
+        c = ld_mail(src + 1);
+        if (a.y == tag && a.w == tag && c.y == tag && c.w == tag) return;
         if ((i & 127u) == 0) {
-            if (ld_volatile(err) != 0) return false;
+            if (ld_volatile(err) != 0) return;
             if (global_ns() - t0 > (unsigned long long)limit_ms * 1000000ull) break;
         }
     }
     atomicExch(err, 2);
-    return false;
 }
 
 // ---- activation staging for one batch row (the NB = 1 case of matvec_v2.cu's v2_stage_x) ------------------
@@ -173,11 +175,13 @@ __device__ __forceinline__ void mega_stage_plain(const __half *__restrict__ x, c
 
 // Residual + RMSNorm input: r = x + b, staged value r * gamma (/ awq); returns this thread's share of sum r^2.
 // resid_out: r rounded to fp16; each 8-element chunk is written by one CTA of the grid, from registers.
-// nsum > 1 (tensor parallel): b is a mailbox of nsum slots, `slot` halves apart, filled by the ranks; the operand is
-// their sum in f32 in rank order, rounded to fp16 (what the stand-alone all-reduce hands to the next kernel).
+// mail != nullptr (tensor parallel): operand b is the sum of a mailbox's nsum slots (`slot` pairs apart, one per rank,
+// written over NVLink with `tag` beside every pair of values): f32 in rank order, rounded to fp16 (what the
+// stand-alone all-reduce hands to the next kernel).  The reads spin until the tags are there.
 __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, const __half *b, const __half *__restrict__ gamma,
                                                  const __half *__restrict__ awq, __half *__restrict__ resid_out, int G, uint32_t *xq,
-                                                 float2 *meta, int nsum, int slot) {
+                                                 float2 *meta, const uint2 *mail, int nsum, int slot, unsigned tag, int *err,
+                                                 unsigned limit_ms) {
     const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
     float sq = 0.0f;
 #pragma unroll 2
@@ -186,25 +190,37 @@ __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, c
         const bool live = grp < G;
         const int k = (live ? grp : g0) * 128 + hl * 8;
         const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
-        const uint4 rb = __ldcg(reinterpret_cast<const uint4 *>(b + k));
         const uint4 rg = *reinterpret_cast<const uint4 *>(gamma + k);
         uint4 ra = make_uint4(0, 0, 0, 0);
         if (awq) ra = *reinterpret_cast<const uint4 *>(awq + k);
         float v[8], fb[8], fg[8];
         unpack8(raw, v);
-        unpack8(rb, fb);
         unpack8(rg, fg);
-        if (nsum > 1) {
-#pragma unroll 2
-            for (int r = 1; r < nsum; r++) {
-                const uint4 rr = __ldcg(reinterpret_cast<const uint4 *>(b + (size_t)r * slot + k));
+        if (mail) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) fb[i] = 0.0f;
+            for (int r = 0; r < nsum; r += 2) {  // two slots' reads travel together
+                const bool two = r + 1 < nsum;
+                const uint4 *s0 = reinterpret_cast<const uint4 *>(mail + (size_t)r * slot + (k >> 1));
+                const uint4 *s1 = two ? reinterpret_cast<const uint4 *>(mail + (size_t)(r + 1) * slot + (k >> 1)) : s0;
+                uint4 a0 = ld_mail(s0), c0 = ld_mail(s0 + 1), a1 = ld_mail(s1), c1 = ld_mail(s1 + 1);
+                mail_settle(s0, a0, c0, tag, err, limit_ms);
+                mail_settle(s1, a1, c1, tag, err, limit_ms);
                 float fr[8];
-                unpack8(rr, fr);
+                unpack2(a0.x, fr[0], fr[1]); unpack2(a0.z, fr[2], fr[3]); unpack2(c0.x, fr[4], fr[5]); unpack2(c0.z, fr[6], fr[7]);
 #pragma unroll
                 for (int i = 0; i < 8; i++) fb[i] += fr[i];
+                if (two) {
+                    unpack2(a1.x, fr[0], fr[1]); unpack2(a1.z, fr[2], fr[3]); unpack2(c1.x, fr[4], fr[5]); unpack2(c1.z, fr[6], fr[7]);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) fb[i] += fr[i];
+                }
             }
 #pragma unroll
             for (int i = 0; i < 8; i++) fb[i] = __half2float(__float2half_rn(fb[i]));
+        } else {
+            const uint4 rb = __ldcg(reinterpret_cast<const uint4 *>(b + k));
+            unpack8(rb, fb);
         }
         unsigned hres[4];
 #pragma unroll
@@ -365,6 +381,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
     // Patience of every wait.  Tensor parallel: a rank may sit behind a peer whose launch came later (host jitter, a
     // graph being instantiated), and while its consumers wait for that peer its producer waits for them.
     const unsigned wait_ms = TP ? 5000u : (unsigned)(kWaitLimitNs / 1000000ull);
+    // tags of this launch's mailbox stores: launch number x 2 L + 2 layer + (o: 1, down: 2); never 0, never repeated
+    const unsigned xbase = TP ? (unsigned)ld_volatile(reinterpret_cast<const int *>(p.xepoch)) * (unsigned)(2 * p.L) : 0u;
     // words of layer l's descriptors -> desc[l & 1]; called by consumer threads one layer ahead (and for layer 0 at start)
     auto copy_desc = [&](int l, int t, int nthreads) {
         uint32_t *dst = desc + (l & 1) * kDescWords;
@@ -410,13 +428,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             }
         };
         auto arrive = [&](int q, int xout) {  // all lanes' output writes precede the arrival
-            if (TP && xout) {  // the outputs went to every rank: so does the arrival (counter 2 * layer + mailbox index)
-                __threadfence_system();
-                __syncwarp();
-                if (lane < p.world)
-                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.xbar[lane] + (q >> 2) * 2 + (xout - 1)), "r"(1u) : "memory");
-                return;
-            }
+            if (TP && xout) return;  // the outputs went to every rank with their tags: readers wait on those, not on a count
             __threadfence();
             __syncwarp();
             if (lane == 0) atomicAdd(p.bar + phase_barrier(q), 1u);
@@ -453,14 +465,19 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                     if (lane < 8 && n < ph.N) ph.y[n] = __float2half_rn((gv / (1.0f + expf(-gv))) * uv);
                 } else {
                     const int n = drb * 16 + lane;
-                    if (lane < 16 && n < ph.N) {
-                        const __half h = __float2half_rn(v * ri);
-                        if (TP && ph.xout) {  // this rank's partial sum: one NVLink store per rank (its own included)
-                            const size_t off = ((size_t)(ph.xout - 1) * p.world + p.rank) * p.xH + n;
-                            for (int r = 0; r < p.world; r++) p.xmail[r][off] = h;
-                        } else {
-                            ph.y[n] = h;
+                    const __half h = __float2half_rn(v * ri);
+                    if (TP && ph.xout) {
+                        // this rank's partial sums: two outputs and the tag per 8-byte store, one store per rank (its own included)
+                        const unsigned mine = (unsigned)__half_as_ushort(h);
+                        const unsigned next = __shfl_down_sync(0xffffffffu, mine, 1);
+                        if (lane < 16 && !(lane & 1) && n < ph.N) {  // N is a multiple of 16
+                            const unsigned tag = xbase + (unsigned)((done.q >> 2) * 2 + ((ph.xout - 1) & 1) + 1);
+                            const size_t off = ((size_t)(ph.xout - 1) * p.world + p.rank) * (size_t)(p.xH >> 1) + (size_t)(n >> 1);
+                            for (int r = 0; r < p.world; r++)
+                                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.xmail[r] + off), "r"(mine | (next << 16)), "r"(tag) : "memory");
                         }
+                    } else if (lane < 16 && n < ph.N) {
+                        ph.y[n] = h;
                     }
                 }
             }
@@ -516,16 +533,10 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             if (reinterpret_cast<int *>(misc)[30] == 0) dead = true;
         };
         constexpr bool tp = TP;
-        const unsigned xtarget = tp ? (ld_volatile(reinterpret_cast<const int *>(p.xepoch)) + 1u) * (unsigned)p.world * gridDim.x : 0u;
-        // barrier k of a row-split projection under tensor parallelism: counter xi of this rank, fed by all ranks
-        auto xrank_wait = [&](int k, int xi) {
-            if (tid == 0) {
-                const bool okw = dead ? false : xrank_poll(p.xbar[p.rank] + xi, xtarget, p.err, wait_ms);
-                reinterpret_cast<int *>(misc)[30] = okw ? 1 : 0;
-                if (p.trace && blockIdx.x == 0) p.trace[k + 1] = global_ns();
-            }
-            consumer_sync();
-            if (reinterpret_cast<int *>(misc)[30] == 0) dead = true;
+        // Tensor parallel: no barrier follows a row-split projection (the next phase's staging waits on the tags of
+        // the values it reads); CTA 0 still leaves its stamp so that the phase accounting keeps its seven columns.
+        auto xrank_wait = [&](int k, int) {
+            if (tid == 0 && p.trace && blockIdx.x == 0) p.trace[k + 1] = global_ns();
         };
         auto items_done = [&](int k) {  // every consumer thread has finished its items of the phase
             consumer_sync();
@@ -543,7 +554,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             const bool stamp = p.trace && fine >= 0 && blockIdx.x == 0 && tid == 0;
             if (stamp) p.trace[fine] = global_ns();
             if (ph.resid) {
-                float sq = mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, xq, meta, (TP && ph.xin) ? p.world : 1, p.xH);
+                // tensor parallel: gate/up reads this layer's o sums, QKV the previous layer's down sums
+                const bool from_mail = TP && ph.xin;
+                const uint2 *mail = from_mail ? p.xmail[p.rank] + (size_t)(ph.xin - 1) * p.world * (size_t)(p.xH >> 1) : nullptr;
+                const unsigned tag = xbase + (unsigned)((((q & 3) == 0 ? (q >> 2) - 1 : (q >> 2)) * 2) + ((ph.xin - 1) & 1) + 1);
+                float sq = mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, xq, meta, mail, p.world, p.xH >> 1, tag, p.err, wait_ms);
                 sq = warp_sum(sq);
                 if (lane == 0) misc[8 + warp] = sq;
                 consumer_sync();

@@ -15,8 +15,10 @@ struct MegaPhase {         // one projection of the token; 4 per layer in execut
     int nblk, G, N;
     int gate_up;           // tile rows 0-7 gate, 8-15 up of the same 8 outputs -> SiLU(gate) * up
     // Tensor parallel (MegaParams::world > 1).  xout = 1 + mailbox index: the outputs are this rank's partial sums of
-    // a row-split projection and go to slot `rank` of that mailbox on EVERY rank instead of y; the phase's barrier then
-    // spans all ranks.  xin = 1: resid points at a mailbox here, and b is the fp16-rounded sum of its `world` slots.
+    // a row-split projection and go to slot `rank` of that mailbox on EVERY rank instead of y, each pair of outputs in
+    // one 8-byte store together with a tag that names the launch and the layer.  xin = 1 + mailbox index: operand b is
+    // the fp16-rounded sum of that mailbox's `world` slots here; the reader spins on the tags, so no barrier stands
+    // between a row-split projection and the phase that consumes it.
     int xout, xin;
 };
 
@@ -50,9 +52,9 @@ struct MegaParams {
     // Tensor parallel: every rank runs this kernel on its shard, on its own GPU, in step with the others.
     int world, rank;            // world <= 1: single GPU, nothing below is read
     int xH;                     // mailbox slot length in halves (the hidden size)
-    __half *xmail[8];           // rank r's mailboxes [2][world][xH] as mapped here (peer memory; [rank] is local)
-    unsigned *xbar[8];          // rank r's cross-rank arrival counters [2 * L]; they only grow, one launch adds world * grid to each
-    unsigned *xepoch;           // local: launches completed so far (sets the counters' target)
+    uint2 *xmail[8];            // rank r's mailboxes [4][world][xH / 2] of {two fp16 outputs, tag} as mapped here (peer memory;
+                                // [rank] is local); layers alternate between mailboxes 0-1 and 2-3 (o, down)
+    unsigned *xepoch;           // local: launches completed so far (part of the tag)
 };
 
 // Shared-memory bytes the kernel needs for `nring` ring slots and `u_bytes` of phase scratch.

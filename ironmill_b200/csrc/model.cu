@@ -112,8 +112,8 @@ struct PeerAllreduce {
     unsigned char *base = nullptr;  // this rank's allocation: [flags: kXarMaxWorld u32][seq u32][pad to 256][buf: 2 x world x cap halves]
     size_t bytes = 0, cap = 0;      // cap: halves per vector
     unsigned char *peer[kXarMaxWorld] = {};  // every rank's allocation as mapped here (own included)
-    // appended for the tensor-parallel whole-token kernel: [mailboxes: 2 x world x hidden halves][2 L counters][launch count]
-    size_t mail_off = 0, bar_off = 0, epoch_off = 0;
+    // appended for the tensor-parallel whole-token kernel: [mailboxes: 4 x world x hidden/2 x {2 halves, tag}][launch count]
+    size_t mail_off = 0, epoch_off = 0;
 };
 struct XarArgs {
     unsigned *flags, *seq;             // local
@@ -662,12 +662,11 @@ static int mega_prepare(Model *m) {
         dn.tiles = Ly.down->tiles; dn.awq = Ly.down->awq; dn.nblk = Ly.down->nblk; dn.G = Ly.down->G; dn.N = Ly.down->N;
         dn.x = m->ffn_gate; dn.y = m->ffn_down;
         if (tp) {  // o and down are row-split: partial sums travel through the mailboxes, the next phase sums them
-            __half *mail = reinterpret_cast<__half *>(m->xar.base + m->xar.mail_off);
-            const size_t box = (size_t)m->world * c.hidden_size;
-            o.xout = 1;
-            gu.resid = mail; gu.xin = 1;
-            if (l > 0) { q.resid = mail + box; q.xin = 1; }
-            if (l + 1 < L) dn.xout = 2;  // the last layer's sum feeds the final norm outside the kernel
+            const int par = (l & 1) * 2;  // layers alternate between two pairs of mailboxes
+            o.xout = 1 + par;
+            gu.resid = m->ffn_down; gu.xin = 1 + par;        // resid stays non-null: it marks the norm phases
+            if (l > 0) { q.resid = m->ffn_down; q.xin = 1 + ((l - 1) & 1) * 2 + 1; }
+            if (l + 1 < L) dn.xout = 1 + par + 1;            // the last layer's sum feeds the final norm outside the kernel
         }
         ph[4 * l] = q; ph[4 * l + 1] = o; ph[4 * l + 2] = gu; ph[4 * l + 3] = dn;
         ml[l] = MegaLayer{Ly.q_norm, Ly.k_norm, Ly.kc, Ly.vc, Ly.ks, Ly.vs, Ly.krn};
@@ -704,10 +703,7 @@ static int mega_prepare(Model *m) {
     p.err = m->dev->err_flag;
     if (tp) {
         p.world = m->world; p.rank = m->rank; p.xH = c.hidden_size;
-        for (int r = 0; r < m->world; r++) {
-            p.xmail[r] = reinterpret_cast<__half *>(m->xar.peer[r] + m->xar.mail_off);
-            p.xbar[r] = reinterpret_cast<unsigned *>(m->xar.peer[r] + m->xar.bar_off);
-        }
+        for (int r = 0; r < m->world; r++) p.xmail[r] = reinterpret_cast<uint2 *>(m->xar.peer[r] + m->xar.mail_off);
         p.xepoch = reinterpret_cast<unsigned *>(m->xar.base + m->xar.epoch_off);
     }
     // phase stamps of CTA 0 (a store per grid barrier; read back by im_cuda_model_token_kernel_profile)
@@ -841,8 +837,7 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
         x.cap = (size_t)4 * m->cfg.hidden_size;  // up to four batch rows: the decode batches that run one matvec per projection
         x.bytes = 256 + (size_t)2 * m->world * x.cap * sizeof(__half);
         x.mail_off = (x.bytes + 255) & ~(size_t)255;
-        x.bar_off = (x.mail_off + (size_t)2 * m->world * m->cfg.hidden_size * sizeof(__half) + 255) & ~(size_t)255;
-        x.epoch_off = x.bar_off + (size_t)2 * m->cfg.num_layers * sizeof(unsigned);
+        x.epoch_off = (x.mail_off + (size_t)4 * m->world * (m->cfg.hidden_size / 2) * sizeof(uint2) + 255) & ~(size_t)255;
         x.bytes = x.epoch_off + 256;
         cudaIpcMemHandle_t mine{};
         unsigned char *xchg = nullptr;
