@@ -763,7 +763,7 @@ static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st
 
 int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st) {
     if (p.nkv <= 0 || p.nh % p.nkv != 0) return IM_ERR_BOUNDS;
-    const bool tp = p.world > 1;
+    const bool tp = p.tagged != 0;
     switch (p.nh / p.nkv) {
         case 1: return tp ? mega_launch_t<1, true>(p, dev, st) : mega_launch_t<1, false>(p, dev, st);
         case 2: return tp ? mega_launch_t<2, true>(p, dev, st) : mega_launch_t<2, false>(p, dev, st);

@@ -49,8 +49,11 @@ struct MegaParams {
     unsigned *bar;            // 7 * L arrival counters + 1 exit counter, zero between launches
     int *err;
     unsigned long long *trace;  // optional: CTA 0 stamps %globaltimer when it leaves each barrier (7L + 2 words)
-    // Tensor parallel: every rank runs this kernel on its shard, on its own GPU, in step with the others.
-    int world, rank;            // world <= 1: single GPU, nothing below is read
+    // Tagged hand-over of the o and down projections' outputs (MegaPhase::xout / xin).  Tensor parallel: every rank runs
+    // this kernel on its shard, on its own GPU, in step with the others, and the mailboxes are peer memory.  One GPU:
+    // world = 1, the mailboxes are local, and the only effect is that no grid barrier follows those two projections.
+    int tagged;                 // 0: plain outputs and a barrier after every projection; nothing below is read
+    int world, rank;
     int xH;                     // mailbox slot length in halves (the hidden size)
     uint2 *xmail[8];            // rank r's mailboxes [4][world][xH / 2] of {two fp16 outputs, tag} as mapped here (peer memory;
                                 // [rank] is local); layers alternate between mailboxes 0-1 and 2-3 (o, down)

@@ -625,6 +625,9 @@ static int mega_prepare(Model *m) {
     if (m->mega_mode == 0 || (env && env[0] == '0')) return IM_OK;
     const im_model_config &c = m->cfg;
     const bool tp = m->world > 1;
+    const char *tg = getenv("IM_MEGA_TAGGED");
+    // one GPU: opt-in only (measured slower there than the barrier: 64.0 against 60.0 us per layer at L8 shapes)
+    const bool tagged = tp || (tg && tg[0] == '1');
     if (tp && (!m->xar.ok || m->world > 8 || c.hidden_size % 128 != 0)) return IM_OK;  // needs the peer mapping of tp_init
     if (c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
     const int gq = m->nh_l / m->nkv_l;
@@ -661,12 +664,13 @@ static int mega_prepare(Model *m) {
         gu.x = m->hidden; gu.resid = m->ffn_down; gu.gamma = Ly.post_ln; gu.resid_out = m->residual; gu.y = m->ffn_gate; gu.gate_up = 1;
         dn.tiles = Ly.down->tiles; dn.awq = Ly.down->awq; dn.nblk = Ly.down->nblk; dn.G = Ly.down->G; dn.N = Ly.down->N;
         dn.x = m->ffn_gate; dn.y = m->ffn_down;
-        if (tp) {  // o and down are row-split: partial sums travel through the mailboxes, the next phase sums them
+        if (tagged) {  // o and down hand their outputs over through the tagged mailboxes (tensor parallel: partial sums of
+                       // the row-split projections, summed by the reader); no grid barrier follows them
             const int par = (l & 1) * 2;  // layers alternate between two pairs of mailboxes
             o.xout = 1 + par;
             gu.resid = m->ffn_down; gu.xin = 1 + par;        // resid stays non-null: it marks the norm phases
             if (l > 0) { q.resid = m->ffn_down; q.xin = 1 + ((l - 1) & 1) * 2 + 1; }
-            if (l + 1 < L) dn.xout = 1 + par + 1;            // the last layer's sum feeds the final norm outside the kernel
+            if (l + 1 < L) dn.xout = 1 + par + 1;            // the last layer's output feeds the final norm outside the kernel
         }
         ph[4 * l] = q; ph[4 * l + 1] = o; ph[4 * l + 2] = gu; ph[4 * l + 3] = dn;
         ml[l] = MegaLayer{Ly.q_norm, Ly.k_norm, Ly.kc, Ly.vc, Ly.ks, Ly.vs, Ly.krn};
@@ -702,9 +706,17 @@ static int mega_prepare(Model *m) {
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;
     if (tp) {
-        p.world = m->world; p.rank = m->rank; p.xH = c.hidden_size;
+        p.tagged = 1; p.world = m->world; p.rank = m->rank; p.xH = c.hidden_size;
         for (int r = 0; r < m->world; r++) p.xmail[r] = reinterpret_cast<uint2 *>(m->xar.peer[r] + m->xar.mail_off);
         p.xepoch = reinterpret_cast<unsigned *>(m->xar.base + m->xar.epoch_off);
+    } else if (tagged) {  // one GPU: local mailboxes (4 x hidden/2 pairs), then the launch count
+        const size_t mail_bytes = (size_t)4 * (c.hidden_size / 2) * sizeof(uint2);
+        unsigned char *loc = nullptr;
+        IM_TRY(m->alloc((void **)&loc, mail_bytes + 256));
+        IM_CUDA_CHECK(cudaMemset(loc, 0, mail_bytes + 256));
+        p.tagged = 1; p.world = 1; p.rank = 0; p.xH = c.hidden_size;
+        p.xmail[0] = reinterpret_cast<uint2 *>(loc);
+        p.xepoch = reinterpret_cast<unsigned *>(loc + mail_bytes);
     }
     // phase stamps of CTA 0 (a store per grid barrier; read back by im_cuda_model_token_kernel_profile)
     IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
