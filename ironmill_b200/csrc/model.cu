@@ -886,6 +886,48 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
         }
         x.ok = out == 1;
         (void)cudaGetLastError();
+        // Known-answer check of the mapping before anything depends on it: rank r contributes r + 1 in every element,
+        // three calls (both buffer parities, then the first again); every rank must read world (world + 1) / 2 everywhere.
+        // Any rank that does not sends everybody back to NCCL.
+        if (x.ok) {
+            const size_t n = (size_t)m->cfg.hidden_size;
+            std::vector<__half> hv(n, __float2half((float)(m->rank + 1)));
+            __half *tv = nullptr;
+            int good_kat = cudaMalloc((void **)&tv, n * sizeof(__half)) == cudaSuccess ? 1 : 0;
+            const float want = 0.5f * (float)m->world * (float)(m->world + 1);
+            for (int it = 0; it < 3; it++) {  // every rank launches all three, whatever it has seen so far
+                if (tv) cudaMemcpyAsync(tv, hv.data(), n * sizeof(__half), cudaMemcpyHostToDevice, m->stream);
+                if (tv && n <= x.cap && n % 8 == 0) {
+                    if (tp_allreduce(m, tv, n, m->stream) != IM_OK) good_kat = 0;
+                } else {
+                    good_kat = 0;
+                }
+                std::vector<__half> back(n);
+                if (!tv || cudaMemcpyAsync(back.data(), tv, n * sizeof(__half), cudaMemcpyDeviceToHost, m->stream) != cudaSuccess ||
+                    cudaStreamSynchronize(m->stream) != cudaSuccess)
+                    good_kat = 0;
+                for (size_t i = 0; good_kat && i < n; i++)
+                    if (__half2float(back[i]) != want) good_kat = 0;
+            }
+            int errw = 0;
+            cudaMemcpy(&errw, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost);
+            if (errw != 0) {
+                good_kat = 0;
+                cudaMemset(m->dev->err_flag, 0, sizeof(int));
+            }
+            if (tv) cudaFree(tv);
+            int all_kat = 0;
+            int *ag = nullptr;
+            if (cudaMalloc((void **)&ag, sizeof(int)) == cudaSuccess) {
+                cudaMemcpy(ag, &good_kat, sizeof(int), cudaMemcpyHostToDevice);
+                if (nccl()->AllReduce(ag, ag, 1, ncclInt, ncclMin, m->comm, m->stream) == ncclSuccess &&
+                    cudaStreamSynchronize(m->stream) == cudaSuccess)
+                    cudaMemcpy(&all_kat, ag, sizeof(int), cudaMemcpyDeviceToHost);
+                cudaFree(ag);
+            }
+            x.ok = all_kat == 1;
+            (void)cudaGetLastError();
+        }
         // The whole-token kernel exchanges its row-split partial sums through the same mapping; every rank must run it
         // or none (a rank on the per-kernel schedule would never feed the others' counters).
         if (x.ok) {
