@@ -307,14 +307,15 @@ def run_decode(args, rank, world):
             "timing": "CUDA events around a CUDA graph of launches rotating over 6 weight copies (702 MB > L2)"}
     if tk is not None:
         tk_ms, phases = tk
-        head_bytes = cfg.vocab_size * cfg.hidden_size * 2 + 2 * cfg.hidden_size * 2 + cfg.vocab_size * 2   # lm_head + embedding row + logits
+        head_bytes = (cfg.vocab_size // world) * cfg.hidden_size * 2 + 2 * cfg.hidden_size * 2 + (cfg.vocab_size // world) * 2   # this rank's lm_head rows + embedding row + logits
         tk_bytes = step_bytes - head_bytes
         roof = {"bound": "hbm", "kernel": "decode_token_kernel (all %d layers of one token: projections, RoPE + cache write, attention)" % cfg.num_hidden_layers,
                 "achieved": round(tk_bytes / (tk_ms * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(tk_bytes / (tk_ms * 1e-3) / 1e9 / peak, 4), "peak_source": peak_src,
                 "bytes_per_launch": tk_bytes, "us_per_launch": round(tk_ms * 1e3, 1),
-                "traffic": int(TOKEN_KERNEL_DRAM_BYTES_PER_LAYER * cfg.num_hidden_layers),
-                "traffic_note": "dram read+write per launch: ncu capture of an 8-layer model of the same shapes scaled by the layer count (profiles/)",
+                "traffic": int(TOKEN_KERNEL_DRAM_BYTES_PER_LAYER * cfg.num_hidden_layers) if world == 1 else None,
+                "traffic_note": ("dram read+write per launch: ncu capture of an 8-layer model of the same shapes scaled by the layer count (profiles/)"
+                                 if world == 1 else "no ncu capture of the tensor-parallel kernel (a multi-rank command is never profiled)"),
                 "timing": "CUDA events around 8 back-to-back launches on the engine's stream; every launch streams all weights (> L2)",
                 "phase_us_per_layer": {k: round(v, 2) for k, v in phases.items()},
                 "largest_projection_alone": proj}
@@ -332,7 +333,7 @@ def run_decode(args, rank, world):
         "config": {"workload": "llama3_8b_shape_int4_g128_awq_tq8_decode", "batch": B, "prompt_tokens": P,
                    "context_during_timing": [ctx0, ctx0 + K], "layers": cfg.num_hidden_layers, "hidden": 4096, "ffn": 14336, "vocab": 128256,
                    "parallelism": f"tp{world}" if world > 1 else "single",
-                   "allreduce": (("inside the whole-token kernel: partial sums stored to every rank's mailbox over NVLink, barrier across ranks"
+                   "allreduce": (("inside the whole-token kernel: partial sums stored to every rank's mailbox over NVLink with tags, summed by the consuming phase, no barrier"
                                   if (B == 1 and eng.token_kernel()) else "one-shot peer-memory kernel")
                                  if eng.tp_peer_allreduce() else "nccl") if world > 1 else None,
                    "l2_policy": "inputs larger than L2: every step streams this rank's %.2f GB of weights + KV" % (step_bytes / 1e9),

@@ -251,8 +251,10 @@ __device__ __forceinline__ void tq_attention_l2_prefetch(int tid, const AttnPara
 }
 
 // One (kv head, token, split) item on a 128-thread scope: positions [r0, r1) of the sequence against the GQ
-// query heads of the group.  cbk / cbv: the K (128) and V (256) codebooks in shared memory, filled by the caller.
-template <int GQ, class Scope>
+// query heads of the group.  cbk / cbv: the K (128) and V (256) codebooks in shared memory, filled by the caller,
+// each entry R times in a row (entry e for lane l at e * R + (l & (R - 1))): the gathers of a warp hit random entries,
+// and copies on neighbouring banks thin out the bank conflicts.
+template <int GQ, int R = 1, class Scope>
 __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> &sm, const float *cbk, const float *cbv, const AttnParams &p,
                                                   int kvh, int st, int split, int r0, int r1) {
     const int tid = sc.d, lane = tid & 31, warp = tid >> 5;
@@ -368,7 +370,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const uint32_t b0 = (w0 >> (8 * e)) & 0xffu, b1 = (w1 >> (8 * e)) & 0xffu;
-                    const float kc0 = cbk[b0 & 0x7fu], kc1 = cbk[b1 & 0x7fu];
+                    const float kc0 = cbk[(b0 & 0x7fu) * R + (lane & (R - 1))], kc1 = cbk[(b1 & 0x7fu) * R + (lane & (R - 1))];
                     const float sg0 = (b0 & 0x80u) ? 1.0f : -1.0f, sg1 = (b1 & 0x80u) ? 1.0f : -1.0f;
                     float qa[GP], qb[GP];  // this dimension's row: the rotated queries and S * q of the pass's heads (vector loads)
                     {
@@ -440,7 +442,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 #pragma unroll
         for (int g = 0; g < GQ; g++) o[g] *= sm.s_corr[g];
         for (int pp = 0; pp < nt; pp++) {
-            const float v = cbv[sm.tile[pp * kPitchB + tid]];
+            const float v = cbv[sm.tile[pp * kPitchB + tid] * R + (lane & (R - 1))];
 #pragma unroll
             for (int g = 0; g < GQ; g++) o[g] = fmaf(sm.sc[pp * GQ + g], v, o[g]);
         }
@@ -499,6 +501,14 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     const __half *src = tok + (is_q ? 0 : a.k_off) + h * kHd;
     const __half *w = is_q ? a.qw : a.kw;
     float x = __half2float(src[d]);
+    // the rotation's table entries are requested with the head's values, not after the norm's barrier
+    const int half_rot = a.rotary_dim / 2;
+    const int ri = d < half_rot ? d : d - half_rot;
+    float rc = 1.0f, rs = 0.0f;
+    if (d < a.rotary_dim) {
+        rc = __half2float(a.cosc[(size_t)pos_abs * (kHd / 2) + ri]);
+        rs = __half2float(a.sinc[(size_t)pos_abs * (kHd / 2) + ri]);
+    }
     if (a.with_norm) {
         float ss = warp_sum(x * x);
         if ((d & 31) == 0) red[d >> 5] = ss;
@@ -508,13 +518,10 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     }
     sh[d] = x;
     sc.sync();
-    const int half_rot = a.rotary_dim / 2;
     float y = x;
     if (d < a.rotary_dim) {
-        const int i = d < half_rot ? d : d - half_rot;
-        const float lo = sh[i], hi = sh[i + half_rot];
-        const float c = __half2float(a.cosc[(size_t)pos_abs * (kHd / 2) + i]), sn = __half2float(a.sinc[(size_t)pos_abs * (kHd / 2) + i]);
-        y = d < half_rot ? lo * c - hi * sn : lo * sn + hi * c;
+        const float lo = sh[ri], hi = sh[ri + half_rot];
+        y = d < half_rot ? lo * rc - hi * rs : lo * rs + hi * rc;
     }
     const __half yh = __float2half_rn(y);
     sc.sync();
