@@ -29,7 +29,6 @@ namespace im {
 namespace {
 
 constexpr int kGroups = kV2Consumers / 4;      // 128-thread groups of consumer warps
-constexpr int kCbCopies = 4;                    // copies of every codebook entry in the attention phase's tables
 constexpr int kRedFloats = kV2Consumers * 16;  // per ring slot: 16 row sums from each consumer warp
 constexpr int kStageBytes = kStageTiles * kTileBytes;
 constexpr int kPhaseWords = sizeof(MegaPhase) / 4, kLayerWords = sizeof(MegaLayer) / 4;
@@ -287,7 +286,7 @@ struct QjlCoop {
 template <int GQ>
 __device__ IM_MEGA_ITEM_INLINE void mega_attention_item(const GroupScope &gs, AttnSmem<GQ> &sm, const float *cbk, const float *cbv, const AttnParams &ap,
                                                  int kvh, int split, int r0, int r1) {
-    tq_attention_item<GQ, kCbCopies>(gs, sm, cbk, cbv, ap, kvh, 0, split, r0, r1);
+    tq_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, 0, split, r0, r1);
 }
 
 // Combine the splits of one query head and rotate back, by all 16 consumer warps.  Warp w takes splits w, w + 16, ...:
@@ -369,9 +368,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
     float *cbv = cbk + 128;
     float *bdk = cbv + 256;                          // suffix-minimum boundary tables of the encoder: K (127), V (255)
     float *bdv = bdk + 128;
-    float *cbk_r = bdv + 256;                        // the attention phase's copies: K [128][kCbCopies], V [256][kCbCopies]
-    float *cbv_r = cbk_r + 128 * kCbCopies;
-    float *misc = cbv_r + 256 * kCbCopies;           // [0] rms_inv, [8..23] reduction scratch, [30] wait result
+    float *misc = bdv + 256;                         // [0] rms_inv, [8..23] reduction scratch, [30] wait result
     // descriptors of the current and the next layer (5 phase blocks per layer: the four projections and the next
     // layer's QKV; plus the layer block), copied one layer ahead so that no phase starts with a global load
     uint32_t *desc = reinterpret_cast<uint32_t *>(misc + 32);   // [2][kDescWords]
@@ -406,10 +403,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         if (p.trace && blockIdx.x == 0) p.trace[0] = global_ns();
     }
     for (int i = tid; i < 128 + 256; i += kV2Threads) {
-        const float cv = i < 128 ? p.k_cb[i] : p.v_cb[i - 128];
-        cbk[i] = cv;
-#pragma unroll
-        for (int c = 0; c < kCbCopies; c++) cbk_r[i * kCbCopies + c] = cv;  // K copies, then V copies: one array
+        cbk[i] = i < 128 ? p.k_cb[i] : p.v_cb[i - 128];
         bdk[i] = i < 128 ? (i < p.k_levels - 1 ? p.k_bd[i] : INFINITY) : (i - 128 < p.v_levels - 1 ? p.v_bd[i - 128] : INFINITY);
     }
     __syncthreads();
@@ -681,7 +675,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 if (!dead)
                     for (int item = item0; item < p.nkv * used; item += gridDim.x * kGroups) {
                         const int kvh = item % p.nkv, split = item / p.nkv;
-                        mega_attention_item<GQ>(gs, sm, cbk_r, cbv_r, ap, kvh, split, split * chunk, min(split * chunk + chunk, seq_len));
+                        mega_attention_item<GQ>(gs, sm, cbk, cbv, ap, kvh, split, split * chunk, min(split * chunk + chunk, seq_len));
                     }
             }
             items_done(7 * l + 2);
@@ -719,7 +713,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 }
 
 size_t mega_smem_bytes(int nring, int u_bytes) {
-    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + ((2 + kCbCopies) * (128 + 256) + 32) * 4 + 2 * kDescWords * 4 + (size_t)u_bytes;
+    return (size_t)nring * (kStageBytes + kRedFloats * 4 + 16) + (2 * (128 + 256) + 32) * 4 + 2 * kDescWords * 4 + (size_t)u_bytes;
 }
 
 template <int GQ>

@@ -251,10 +251,8 @@ __device__ __forceinline__ void tq_attention_l2_prefetch(int tid, const AttnPara
 }
 
 // One (kv head, token, split) item on a 128-thread scope: positions [r0, r1) of the sequence against the GQ
-// query heads of the group.  cbk / cbv: the K (128) and V (256) codebooks in shared memory, filled by the caller,
-// each entry R times in a row (entry e for lane l at e * R + (l & (R - 1))): the gathers of a warp hit random entries,
-// and copies on neighbouring banks thin out the bank conflicts.
-template <int GQ, int R = 1, class Scope>
+// query heads of the group.  cbk / cbv: the K (128) and V (256) codebooks in shared memory, filled by the caller.
+template <int GQ, class Scope>
 __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> &sm, const float *cbk, const float *cbv, const AttnParams &p,
                                                   int kvh, int st, int split, int r0, int r1) {
     const int tid = sc.d, lane = tid & 31, warp = tid >> 5;
@@ -370,7 +368,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const uint32_t b0 = (w0 >> (8 * e)) & 0xffu, b1 = (w1 >> (8 * e)) & 0xffu;
-                    const float kc0 = cbk[(b0 & 0x7fu) * R + (lane & (R - 1))], kc1 = cbk[(b1 & 0x7fu) * R + (lane & (R - 1))];
+                    const float kc0 = cbk[b0 & 0x7fu], kc1 = cbk[b1 & 0x7fu];
                     const float sg0 = (b0 & 0x80u) ? 1.0f : -1.0f, sg1 = (b1 & 0x80u) ? 1.0f : -1.0f;
                     float qa[GP], qb[GP];  // this dimension's row: the rotated queries and S * q of the pass's heads (vector loads)
                     {
@@ -442,7 +440,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 #pragma unroll
         for (int g = 0; g < GQ; g++) o[g] *= sm.s_corr[g];
         for (int pp = 0; pp < nt; pp++) {
-            const float v = cbv[sm.tile[pp * kPitchB + tid] * R + (lane & (R - 1))];
+            const float v = cbv[sm.tile[pp * kPitchB + tid]];
 #pragma unroll
             for (int g = 0; g < GQ; g++) o[g] = fmaf(sm.sc[pp * GQ + g], v, o[g]);
         }
