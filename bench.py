@@ -50,7 +50,7 @@ METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes
 METRIC_ATTN = "TurboQuant INT8-KV decode attention HBM GB/s (32 Q / 8 KV heads, head_dim 128)"
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
 PROJ_DRAM_BYTES = 62467840 + 17920          # matvec_v2_kernel<gate+up+SiLU>, one launch
-TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = (970164992 + 28496384) / 8   # decode_token_kernel: capture of the 8-layer model at ~2k context
+TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = (972662016 + 38294528) / 8   # dram read + write of the 8-layer ncu capture (profiles/)
 
 
 def matvec_bytes(N, K, B=1, awq=True, bits=4):
