@@ -501,7 +501,7 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)H, st));
         nl += 2 + (m->world > 1 ? 1 : 0);
     }
-    const bool gemm = !mega && m->gemm_ok && m->world == 1 && MT >= kGemmMinTokens;
+    const bool gemm = !mega && m->gemm_ok && MT >= kGemmMinTokens;
     for (int l = 0; l < c.num_layers && gemm; l++) {
         // Dense contraction (prefill chunks, large decode batches): every projection is one tcgen05 GEMM; norms, SiLU
         // and the residual adds are separate element-wise launches (their bytes are a rounding error next to the GEMMs).
@@ -526,6 +526,8 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         IM_MARK(kCatAttn);
         IM_TRY(gemm_affine_tc(L.o, m->attn_out, m->ffn_down, MT, m->xs_scratch, st));
         IM_MARK(kCatOProj);
+        IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));  // tensor parallel: o is row-split
+        if (m->world > 1) IM_MARK(kCatComm);
         IM_TRY(im_cuda_fused_residual_rms_norm(m->hidden, m->ffn_down, L.post_ln, m->norm_out, m->residual, H, MT, eps, st));
         IM_MARK(kCatResNorm);
         IM_TRY(gemm_affine_tc(L.gate, m->norm_out, m->ffn_gate, MT, m->xs_scratch, st));
@@ -539,7 +541,9 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         IM_MARK(kCatFfn);
         IM_TRY(gemm_affine_tc(L.down, m->ffn_gate, m->ffn_down, MT, m->xs_scratch, st));
         IM_MARK(kCatDown);
-        nl += 11;
+        IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));  // tensor parallel: down is row-split
+        if (m->world > 1) IM_MARK(kCatComm);
+        nl += 11 + (m->world > 1 ? 2 : 0);
         if (l + 1 < c.num_layers) {
             Layer &Nx = m->layers[l + 1];
             IM_TRY(im_cuda_fused_residual_rms_norm(m->residual, m->ffn_down, Nx.input_ln, m->norm_out, m->hidden, H, MT, eps, st));
@@ -1344,7 +1348,7 @@ IM_EXPORT int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, in
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
     // 256-token chunks when the projections run as tensor-core GEMMs; the matvec kernels take at most 64 rows per call
-    const int chunk = (m->gemm_ok && m->world == 1) ? kPrefillChunk : 64;
+    const int chunk = m->gemm_ok ? kPrefillChunk : 64;
     for (int done = 0; done < n; done += chunk) {
         const int T = n - done < chunk ? n - done : chunk;
         memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);

@@ -38,10 +38,15 @@ def _worker(rank, world, port, ret):
         steps = (5, 17, 400, 3, 999, 12, 77, 250)   # batch-1 steps: the whole-token kernel with its cross-rank barriers when enabled
         for t in steps:
             outs.append(eng.decode_step(t))
+        eng.reset()
+        long_prompt = (np.arange(40, dtype=np.uint32) * 29 + 3) % 1000   # 16 tokens and more: the tensor-core GEMM with its all-reduces
+        outs.append(eng.prefill(long_prompt))
         if rank == 0:
             single = CudaInference(CudaConfig(max_seq_len=64, device=0))
             single.load_weights(DictProvider(cfg, tensors), tq_signs=tqc.signs, tq_qjl=tqc.qjl)
             refs = [single.prefill(prompt)] + [single.decode_step(t) for t in steps]
+            single.reset()
+            refs.append(single.prefill(long_prompt))
             err = max(float(np.abs(a - b).max()) for a, b in zip(outs, refs))
             ret[0] = err
             ret['peer'] = eng.tp_peer_allreduce()
