@@ -236,6 +236,9 @@ def run_decode(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL carries only set-up, the logits gather and prefill-size all-reduces here: in-switch reduction buys nothing, and
+        # every multi-GPU number of this repo was taken with it off (override by exporting NCCL_NVLS_ENABLE=1)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     dev = ops.Device(local)
     cfg = ModelConfig(**dict(L8, num_hidden_layers=args.layers))

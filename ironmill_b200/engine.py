@@ -8,6 +8,7 @@ argument meaning and error behaviour; every method is one call into the C ABI.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -158,6 +159,9 @@ class CudaInference:
 
     @_wrap
     def tp_init(self, unique_id: bytes) -> None:
+        """Joins the tensor-parallel group (every rank, same unique id).  NVLS is switched off unless the environment
+        says otherwise: the library's NCCL traffic is set-up, the logits gather and prefill-size all-reduces."""
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         check(lib().im_cuda_model_tp_init(self._model, unique_id))
 
     def tp_peer_allreduce(self) -> bool:
