@@ -105,7 +105,8 @@ struct HostAffine {  // one projection as handed to load_affine, already cut to 
 // Here every rank stores its vector into a slot of EVERY rank's receive buffer (plain stores to peer memory over
 // NVLink), raises a per-source sequence flag on every rank, waits (bounded) until all sources have raised theirs, and
 // sums the world's vectors from its own memory in rank order, in f32, rounding once.  Two buffer halves alternate:
-// a rank can only be one all-reduce ahead of the slowest one.  No multicast, no multimem: plain peer stores.
+// a rank can only be one all-reduce ahead of the slowest one.  Plain peer stores only: nothing goes through the
+// switch's reduction or replication units.
 constexpr int kXarMaxWorld = 8, kXarThreads = 512;
 struct PeerAllreduce {
     bool ok = false;
