@@ -106,3 +106,32 @@ def test_against_the_oracle_model_and_greedy_loop():
         t = int(orc.argmax(eng.decode_step(t)))
         assert t == int(toks[i][0]), (i, t, toks[:, 0])
     assert ms > 0
+
+
+def test_tagged_hand_over_variant_on_one_gpu():
+    # IM_MEGA_TAGGED=1 runs the tensor-parallel kernel with a world of one: the o / down outputs travel as tagged pairs
+    # through a (local) mailbox and the next phase spins on the tags instead of a grid barrier.  Same arithmetic as the
+    # default kernel (a separate compilation, so allow the last fp16 bit); 40 steps walk the launch counter and both
+    # mailbox parities.
+    cfg = _cfg(3, 512, 1024, 8, 2, 500)
+    tensors = synth_model(cfg, seed=11, awq=True, gamma_jitter=0.1)
+    tqc = orc.TqConstants(128, 8, seed=42)
+    plain = _engine(cfg, tensors, 96, True, tqc)
+    old = os.environ.get("IM_MEGA_TAGGED")
+    os.environ["IM_MEGA_TAGGED"] = "1"
+    try:
+        tagged = _engine(cfg, tensors, 96, True, tqc)
+    finally:
+        if old is None:
+            os.environ.pop("IM_MEGA_TAGGED", None)
+        else:
+            os.environ["IM_MEGA_TAGGED"] = old
+    assert plain.token_kernel() and tagged.token_kernel()
+    prompt = H.rng_for("mega-tagged").integers(0, cfg.vocab_size, 6).astype(np.uint32)
+    la, lb = plain.prefill(prompt), tagged.prefill(prompt)
+    assert np.array_equal(la, lb)
+    tok = int(la.argmax())
+    for _ in range(40):
+        la, lb = plain.decode_step(tok), tagged.decode_step(tok)
+        assert float(np.abs(la - lb).max()) <= 2e-3 and int(la.argmax()) == int(lb.argmax())
+        tok = int(la.argmax())
