@@ -508,7 +508,7 @@ def run_attention(args, rank, world):
 # ----------------------------------------------------------------------------- CPU arm (the oracle, timed)
 def cpu_matvec_baseline(seconds):
     from oracle import oracle as orc
-    threads = orc.max_threads()
+    threads = host_threads(orc)
     rng = np.random.default_rng(0)
     N = K = 4096
     w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
@@ -533,7 +533,7 @@ def cpu_decode_baseline(quick):
     cores on a bounded sample of one decode token: ONE Llama-3-8B-shaped layer (QKV, o, gate+up+SiLU, down at batch 1)
     plus 1/16 of the fp16 lm_head rows; a token is 32 such layers + the whole lm_head."""
     from oracle import oracle as orc
-    threads = orc.max_threads()
+    threads = host_threads(orc)
     rng = np.random.default_rng(0)
     mats = {}
     tq0 = time.perf_counter()
@@ -568,6 +568,16 @@ def cpu_decode_baseline(quick):
                       f"({lm_s * 1e3:.0f} ms), batch 1, OpenMP {threads} threads, {reps} repetition(s); attention and norms "
                       f"left out (under 1 % of the CPU time); quantize+pack of the layer took {quant_s:.1f} s",
             "layer_ms": round(layer_s * 1e3, 1), "lm_head_ms": round(lm_s * 1e3, 1), "quantize_layer_s": round(quant_s, 2)}
+
+
+def host_threads(orc):
+    """Threads for the CPU arm: all the cores this process may run on.  torchrun exports OMP_NUM_THREADS=1 to its workers,
+    which would otherwise make the oracle's OpenMP loops single-threaded there."""
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    return max(int(orc.max_threads()), avail)
 
 
 def run_reference(args, rank, world):
