@@ -277,6 +277,14 @@ typedef struct im_model_config {
     int tq_bits;              /* TurboQuant KV bits (0 = 8; only 8 is built) */
     uint64_t rotation_seed;   /* MetalConfig.rotation_seed (default 42) */
     int tp_world, tp_rank;    /* tensor parallel group (0/0 = single GPU) */
+    int prefill_chunk_size;   /* MetalConfig.prefill_chunk_size: tokens per prefill forward (0 = 256; at most 256) */
+    int decode_schedule;      /* batch-1 decode: 0 = the whole-token kernel whenever the model fits it, 1 = always the
+                                 graph of per-projection kernels, 2 = the whole-token kernel handing the o / down outputs on
+                                 as tagged pairs instead of grid barriers (what tensor-parallel ranks do; one GPU: a way to
+                                 run that code path) */
+    int tp_collective;        /* tensor parallel: 0 = the library's peer-memory exchange when every rank could map its
+                                 peers, 1 = NCCL all-reduce only */
+    int wait_limit_ms;        /* patience of the device-side bounded waits (0 = 400 ms, 5 s under tensor parallelism) */
 } im_model_config;
 
 int im_cuda_model_create(im_device *dev, const im_model_config *cfg, im_model **out);
@@ -323,13 +331,13 @@ size_t im_cuda_model_memory_bytes(const im_model *m);
  * packed codes + scales/zeros + AWQ vectors + fp16 lm_head rows + norm weights + batch * KV bytes. */
 size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch);
 /* 1 when the row-split projections of a tensor-parallel model are summed by the library's one-shot all-reduce over
- * peer memory (CUDA IPC + NVLink stores, set up by im_cuda_model_tp_init; IM_TP_PEER=0 disables it), 0 when NCCL's
+ * peer memory (CUDA IPC + NVLink stores, set up by im_cuda_model_tp_init; im_model_config.tp_collective = 1 keeps NCCL), 0 when NCCL's
  * all-reduce does it.  No counterpart in the reference (it has no tensor parallelism). */
 int im_cuda_model_tp_peer_allreduce(const im_model *m);
 /* 1 when batch-1 decode steps of this model run in the whole-token kernel (all layers in one cooperative launch), 0
  * when they run as a graph of per-projection kernels.  Under tensor parallelism the kernel of every rank exchanges the
  * partial sums of the row-split projections through peer memory and its barriers after those projections span all
- * ranks (IM_TP_MEGA=0 keeps tensor-parallel models on the per-kernel schedule; IM_MEGA=0 every model). */
+ * ranks (im_model_config.decode_schedule = 1 keeps the per-kernel schedule). */
 int im_cuda_model_token_kernel(const im_model *m);
 /* Number of kernel launches in one captured decode step. */
 int im_cuda_model_step_launches(const im_model *m);
@@ -338,10 +346,16 @@ int im_cuda_model_step_launches(const im_model *m);
  * ms_per_launch: average of `reps` back-to-back launches between two events on the model's stream;
  * phase_us_7 (optional, 7 floats): microseconds per layer in QKV, RoPE + cache write, attention, split reduction,
  * o, gate/up, down.  IM_ERR_STATE when the model does not use that kernel (batch > 1 only, tensor parallel,
- * non-INT4 weights, IM_MEGA=0). */
+ * non-INT4 weights, decode_schedule = 1). */
 int im_cuda_model_token_kernel_profile(im_model *m, int reps, float *ms_per_launch, float *phase_us_7);
-/* Development aid (no counterpart in the reference): the raw timer stamps behind the call above. */
-int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, int n);
+/* InferenceEngine::prefill_all_logits (crates/ironmill-inference/src/metal/pipeline.rs:38-70, the perplexity path):
+ * like im_cuda_model_prefill, but logits_out_host receives f32 [n_tokens, vocab], one row per prompt token. */
+int im_cuda_model_prefill_all_logits(im_model *m, const uint32_t *tokens_host, int n_tokens, float *logits_out_host);
+/* Host-side fault injection for tests of the error path (no counterpart in the reference).  Only for a model loaded
+ * with decode_schedule = 2 on one GPU: with missing_ranks = 1 the whole-token kernel also waits for the partial sums
+ * of a rank that does not exist, so its bounded wait runs out after wait_limit_ms, the kernel finishes, and the step
+ * returns IM_ERR_TIMEOUT; 0 restores normal operation.  Nothing faults or hangs: a wait gives up and sets a word. */
+int im_cuda_model_test_missing_ranks(im_model *m, int missing_ranks);
 /* Per-category GPU time of one eager decode step at the current position, which is not advanced
  * (MetalConfig.kernel_timing, crates/ironmill-inference/src/metal/pipeline.rs:353-422,1215-1234).
  * ms_by_category[11]: embed, qkv projection, rope, kv write, attention, o projection, residual+norm,

@@ -24,14 +24,6 @@ int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char *e = getenv("IM_PDL");
-        return !(e && e[0] == '0');
-    }();
-    return on;
-}
-
 int dev_malloc(Device *dev, void **ptr, size_t bytes) {
     *ptr = nullptr;
     if (bytes == 0) return IM_OK;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <atomic>
 #include <string>
 
 #include "../../include/ironmill_cuda.h"
@@ -51,6 +52,19 @@ struct Device {
     int *err_flag = nullptr;  // set by a kernel whose bounded wait ran out
 };
 constexpr int kSkMaxBlocks = 1 << 17;  // row blocks the counters cover (2M rows)
+
+// cudaFuncSetAttribute applies to the current device: remember per device ordinal (not per thread) whether a
+// kernel's attribute has been set.  Usage: static DeviceOnce once; if (once.first(dev->ordinal)) { set attributes }.
+struct DeviceOnce {
+    std::atomic<bool> done[64];
+    DeviceOnce() {
+        for (auto &d : done) d.store(false);
+    }
+    bool first(int ordinal) {
+        if (ordinal < 0 || ordinal >= 64) return true;  // outside the table: set every time
+        return !done[ordinal].exchange(true);
+    }
+};
 
 // Allocation bookkeeping shared by buffers, weights and models.
 int dev_malloc(Device *dev, void **ptr, size_t bytes);
@@ -105,8 +119,7 @@ int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, 
 // pdl_wait() (barrier set-up, streaming constant weights into shared memory) overlaps the predecessor's
 // tail; pdl_wait() returns once the predecessor has completed and its writes are visible.  Every kernel
 // launched through launch_k() must therefore call pdl_wait() before it reads anything a predecessor wrote
-// and before its first global write.  IM_PDL=0 in the environment turns the attribute off.
-bool pdl_enabled();
+// and before its first global write.
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
@@ -119,7 +132,7 @@ inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
@@ -191,6 +204,8 @@ int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len);
 struct TqPrep {
     const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
     int stride, k_off, v_off;
+    const __half *kv = nullptr;  // optional: K and V rows live in their own buffer [nseq*T, kv_stride]; k_off / v_off index it
+    int kv_stride = 0;
     const __half *qw, *kw, *cosc, *sinc;
     int nh, nkv, rotary_dim, with_norm, T, nseq, max_seq, base_pos;
     float eps;

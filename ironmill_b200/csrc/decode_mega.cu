@@ -167,81 +167,145 @@ __device__ __forceinline__ void mega_stage_plain(const __half *__restrict__ x, c
             float a[8];
             unpack8(ra, a);
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __fdividef(v[i], a[i]);  // x / s[k]; 2 ulp, far below the 16-bit rounding that follows
+            for (int i = 0; i < 8; i++) v[i] = __fdiv_rn(v[i], a[i]);  // f32(x) / f32(awq), as affine_matvec.metal:48-66
         }
         stage_chunk(v, live, grp, hl, xq, meta);
     }
 }
 
-// Residual + RMSNorm input: r = x + b, staged value r * gamma (/ awq); returns this thread's share of sum r^2.
-// resid_out: r rounded to fp16; each 8-element chunk is written by one CTA of the grid, from registers.
+// Residual + RMSNorm input, r = x + b, in the reference's two forms
+// (crates/ironmill-inference/src/metal/shaders/norm/superblock_fused_norm.metal:71-123 and norm/fused_residual_norm.metal:54-74):
+//   * the fused residual + norm + projection kernel multiplies the UNROUNDED vector: staged value r * gamma (/ awq), the
+//     row sums are scaled by rms_inv afterwards (xq_u / meta_u; only when want_u);
+//   * every other consumer reads norm_out, the fp16 copy f16(r * rms_inv * gamma): staged value that / awq (xq_r / meta_r;
+//     only when want_r), no scaling afterwards.
+// Pass 1 loads, forms r (kept in registers: at most kNormChunks chunks of 8 values per thread), writes this CTA's share
+// of resid_out = f16(r), stages the unrounded form and sums r^2; the CTA then agrees on rms_inv; pass 2 stages the
+// rounded form.  Returns rms_inv (also left in misc[0] for the producer warp).
 // mail != nullptr (tensor parallel): operand b is the sum of a mailbox's nsum slots (`slot` pairs apart, one per rank,
 // written over NVLink with `tag` beside every pair of values): f32 in rank order, rounded to fp16 (what the
 // stand-alone all-reduce hands to the next kernel).  The reads spin until the tags are there.
+// One 8-element chunk of the residual sum: r = x + b (b from memory or from the mailbox slots), the chunk's norm weights
+// and activation scales as loaded.
+__device__ __forceinline__ void norm_load(const __half *__restrict__ x, const __half *b, const __half *__restrict__ gamma,
+                                          const __half *__restrict__ awq, int k, const uint2 *mail, int nsum, int slot, unsigned tag, int *err,
+                                          unsigned limit_ms, float (&r)[8], uint4 &rgam, uint4 &rawq) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
+    rgam = *reinterpret_cast<const uint4 *>(gamma + k);
+    rawq = make_uint4(0, 0, 0, 0);
+    if (awq) rawq = *reinterpret_cast<const uint4 *>(awq + k);
+    float v[8], fb[8];
+    unpack8(raw, v);
+    if (mail) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) fb[i] = 0.0f;
+        for (int rk = 0; rk < nsum; rk += 2) {  // two slots' reads travel together
+            const bool two = rk + 1 < nsum;
+            const uint4 *s0 = reinterpret_cast<const uint4 *>(mail + (size_t)rk * slot + (k >> 1));
+            const uint4 *s1 = two ? reinterpret_cast<const uint4 *>(mail + (size_t)(rk + 1) * slot + (k >> 1)) : s0;
+            uint4 a0 = ld_mail(s0), c0 = ld_mail(s0 + 1), a1 = ld_mail(s1), c1 = ld_mail(s1 + 1);
+            mail_settle(s0, a0, c0, tag, err, limit_ms);
+            mail_settle(s1, a1, c1, tag, err, limit_ms);
+            float fr[8];
+            unpack2(a0.x, fr[0], fr[1]); unpack2(a0.z, fr[2], fr[3]); unpack2(c0.x, fr[4], fr[5]); unpack2(c0.z, fr[6], fr[7]);
+#pragma unroll
+            for (int i = 0; i < 8; i++) fb[i] += fr[i];
+            if (two) {
+                unpack2(a1.x, fr[0], fr[1]); unpack2(a1.z, fr[2], fr[3]); unpack2(c1.x, fr[4], fr[5]); unpack2(c1.z, fr[6], fr[7]);
+#pragma unroll
+                for (int i = 0; i < 8; i++) fb[i] += fr[i];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) fb[i] = __half2float(__float2half_rn(fb[i]));
+    } else {
+        const uint4 rb = __ldcg(reinterpret_cast<const uint4 *>(b + k));
+        unpack8(rb, fb);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) r[i] = v[i] + fb[i];
+}
+
 __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, const __half *b, const __half *__restrict__ gamma,
-                                                 const __half *__restrict__ awq, __half *__restrict__ resid_out, int G, uint32_t *xq,
-                                                 float2 *meta, const uint2 *mail, int nsum, int slot, unsigned tag, int *err,
+                                                 const __half *__restrict__ awq, __half *__restrict__ resid_out, int G, bool want_u,
+                                                 uint32_t *xq_u, float2 *meta_u, bool want_r, uint32_t *xq_r, float2 *meta_r, float eps,
+                                                 float *misc, const uint2 *mail, int nsum, int slot, unsigned tag, int *err,
                                                  unsigned limit_ms) {
     const int lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
     float sq = 0.0f;
-#pragma unroll 2
+    // the thread's first chunk stays in registers between the passes (hidden sizes up to 4096: its only chunk);
+    // further chunks are loaded again in pass 2
+    float r0[8];
+    uint4 rg0 = make_uint4(0, 0, 0, 0), ra0 = rg0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) r0[i] = 0.0f;
+#pragma unroll 1
     for (int g0 = warp * 2; g0 < G; g0 += kV2Consumers * 2) {
         const int grp = g0 + (lane >> 4);
         const bool live = grp < G;
         const int k = (live ? grp : g0) * 128 + hl * 8;
-        const uint4 raw = *reinterpret_cast<const uint4 *>(x + k);
-        const uint4 rg = *reinterpret_cast<const uint4 *>(gamma + k);
-        uint4 ra = make_uint4(0, 0, 0, 0);
-        if (awq) ra = *reinterpret_cast<const uint4 *>(awq + k);
-        float v[8], fb[8], fg[8];
-        unpack8(raw, v);
-        unpack8(rg, fg);
-        if (mail) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) fb[i] = 0.0f;
-            for (int r = 0; r < nsum; r += 2) {  // two slots' reads travel together
-                const bool two = r + 1 < nsum;
-                const uint4 *s0 = reinterpret_cast<const uint4 *>(mail + (size_t)r * slot + (k >> 1));
-                const uint4 *s1 = two ? reinterpret_cast<const uint4 *>(mail + (size_t)(r + 1) * slot + (k >> 1)) : s0;
-                uint4 a0 = ld_mail(s0), c0 = ld_mail(s0 + 1), a1 = ld_mail(s1), c1 = ld_mail(s1 + 1);
-                mail_settle(s0, a0, c0, tag, err, limit_ms);
-                mail_settle(s1, a1, c1, tag, err, limit_ms);
-                float fr[8];
-                unpack2(a0.x, fr[0], fr[1]); unpack2(a0.z, fr[2], fr[3]); unpack2(c0.x, fr[4], fr[5]); unpack2(c0.z, fr[6], fr[7]);
-#pragma unroll
-                for (int i = 0; i < 8; i++) fb[i] += fr[i];
-                if (two) {
-                    unpack2(a1.x, fr[0], fr[1]); unpack2(a1.z, fr[2], fr[3]); unpack2(c1.x, fr[4], fr[5]); unpack2(c1.z, fr[6], fr[7]);
-#pragma unroll
-                    for (int i = 0; i < 8; i++) fb[i] += fr[i];
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; i++) fb[i] = __half2float(__float2half_rn(fb[i]));
-        } else {
-            const uint4 rb = __ldcg(reinterpret_cast<const uint4 *>(b + k));
-            unpack8(rb, fb);
-        }
+        float r[8];
+        uint4 rg, ra;
+        norm_load(x, b, gamma, awq, k, mail, nsum, slot, tag, err, limit_ms, r, rg, ra);
         unsigned hres[4];
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
-            const float r0 = v[i] + fb[i], r1 = v[i + 1] + fb[i + 1];
-            if (live) sq += r0 * r0 + r1 * r1;
-            v[i] = r0 * fg[i];
-            v[i + 1] = r1 * fg[i + 1];
-            hres[i >> 1] = (unsigned)__half_as_ushort(__float2half_rn(r0)) | ((unsigned)__half_as_ushort(__float2half_rn(r1)) << 16);
+            if (live) sq += r[i] * r[i] + r[i + 1] * r[i + 1];
+            hres[i >> 1] = (unsigned)__half_as_ushort(__float2half_rn(r[i])) | ((unsigned)__half_as_ushort(__float2half_rn(r[i + 1])) << 16);
         }
         if (live && resid_out && (unsigned)(grp * 16 + hl) % gridDim.x == blockIdx.x)
             *reinterpret_cast<uint4 *>(resid_out + k) = make_uint4(hres[0], hres[1], hres[2], hres[3]);
-        if (awq) {
-            float a[8];
-            unpack8(ra, a);
+        if (g0 == warp * 2) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __fdividef(v[i], a[i]);
+            for (int i = 0; i < 8; i++) r0[i] = r[i];
+            rg0 = rg;
+            ra0 = ra;
         }
-        stage_chunk(v, live, grp, hl, xq, meta);
+        if (want_u) {
+            float v[8], fg[8], a[8];
+            unpack8(rg, fg);
+            if (awq) unpack8(ra, a);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                v[i] = r[i] * fg[i];
+                if (awq) v[i] = __fdiv_rn(v[i], a[i]);
+            }
+            stage_chunk(v, live, grp, hl, xq_u, meta_u);
+        }
     }
-    return sq;
+    sq = warp_sum(sq);
+    if (lane == 0) misc[8 + warp] = sq;
+    consumer_sync();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kV2Consumers; w++) tot += misc[8 + w];
+    const float ri = rsqrtf(tot / (float)(G * 128) + eps);
+    if (threadIdx.x == 0) misc[0] = ri;  // reaches the producer warp through the slot releases
+    if (want_r) {
+#pragma unroll 1
+        for (int g0 = warp * 2; g0 < G; g0 += kV2Consumers * 2) {
+            const int grp = g0 + (lane >> 4);
+            const bool live = grp < G;
+            float r[8];
+            uint4 rg = rg0, ra = ra0;
+            if (g0 == warp * 2) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) r[i] = r0[i];
+            } else {  // hidden sizes above 4096 (never with a mailbox: the engine keeps those on the per-kernel schedule)
+                norm_load(x, b, gamma, awq, (live ? grp : g0) * 128 + hl * 8, nullptr, 0, 0, 0u, err, limit_ms, r, rg, ra);
+            }
+            float v[8], fg[8], a[8];
+            unpack8(rg, fg);
+            if (awq) unpack8(ra, a);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                v[i] = __half2float(__float2half_rn(r[i] * ri * fg[i]));  // norm_out as the reference stores it
+                if (awq) v[i] = __fdiv_rn(v[i], a[i]);
+            }
+            stage_chunk(v, live, grp, hl, xq_r, meta_r);
+        }
+    }
+    return ri;
 }
 
 // The item phases run out of line: they are cold next to the projection loop, and a call boundary keeps their
@@ -380,7 +444,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
     const int NP = 4 * p.L;
     // Patience of every wait.  Tensor parallel: a rank may sit behind a peer whose launch came later (host jitter, a
     // graph being instantiated), and while its consumers wait for that peer its producer waits for them.
-    const unsigned wait_ms = TP ? 5000u : (unsigned)(kWaitLimitNs / 1000000ull);
+    const unsigned wait_ms = p.wait_ms ? p.wait_ms : (TP ? 5000u : (unsigned)(kWaitLimitNs / 1000000ull));
     // tags of this launch's mailbox stores: launch number x 2 L + 2 layer + (o: 1, down: 2); never 0, never repeated
     const unsigned xbase = TP ? (unsigned)ld_volatile(reinterpret_cast<const int *>(p.xepoch)) * (unsigned)(2 * p.L) : 0u;
     // words of layer l's descriptors -> desc[l & 1]; called by consumer threads one layer ahead (and for layer 0 at start)
@@ -436,12 +500,11 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         Cursor issue{0, StageIter(0, 0, 1), MegaPhase{}}, done{0, StageIter(0, 0, 1), MegaPhase{}};
         open(issue, 0);
         open(done, 0);
-        // phases in which this CTA has no tiles are passed at once
+        // Phases in which this CTA has no tiles are passed without an arrival from this warp: the CTA's consumers
+        // arrive for it once they have staged the phase's input (matvec_phase), so that nobody can overwrite a buffer
+        // they still read.
         auto skip_empty_done = [&]() {
-            while (done.q < NP && done.it.t >= done.it.t_end) {
-                arrive(done.q, done.ph.xout);
-                open(done, done.q + 1);
-            }
+            while (done.q < NP && done.it.t >= done.it.t_end) open(done, done.q + 1);
         };
         skip_empty_done();
         bool ok = true;
@@ -457,7 +520,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
 #pragma unroll
                     for (int w = 0; w < kV2Consumers; w++) v += buf[w * 16 + lane];
                 }
-                const float ri = ph.resid ? misc[0] : 1.0f;
+                // rows that multiplied the unrounded vector still need the norm's scale; norm_out carries it already
+                const float ri = (ph.resid && drb * 16 < ph.split_row) ? misc[0] : 1.0f;
                 const float vu = __shfl_down_sync(0xffffffffu, v, 8);  // lanes 0-7: the up row of the same output
                 if (ph.gate_up) {
                     const float gv = v * ri, uv = vu * ri;
@@ -516,8 +580,13 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         }
     } else {
         // =========================================================== consumers
+        // staged activations: the primary set for projections of up to g_max groups, and a second set of g_norm groups
+        // for the QKV phases of layers >= 1, whose K and V rows read the fp16 norm_out while the Q rows read the
+        // unrounded vector (mega_stage_norm)
         float2 *meta = reinterpret_cast<float2 *>(U);                                        // [g_max]
         uint32_t *xq = reinterpret_cast<uint32_t *>(U + (((size_t)p.g_max * 8 + 15) & ~(size_t)15));  // [G][2][32] words
+        float2 *meta2 = reinterpret_cast<float2 *>(xq + (size_t)p.g_max * 64);                 // [g_norm]
+        uint32_t *xq2 = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(meta2) + (((size_t)p.g_norm * 8 + 15) & ~(size_t)15));
         const int group = warp >> 2;
         const GroupScope gs{tid & 127, 128, 2 + group};
         bool dead = false;
@@ -558,18 +627,19 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 const bool from_mail = TP && ph.xin;
                 const uint2 *mail = from_mail ? p.xmail[p.rank] + (size_t)(ph.xin - 1) * p.world * (size_t)(p.xH >> 1) : nullptr;
                 const unsigned tag = xbase + (unsigned)((((q & 3) == 0 ? (q >> 2) - 1 : (q >> 2)) * 2) + ((ph.xin - 1) & 1) + 1);
-                float sq = mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, xq, meta, mail, p.world, p.xH >> 1, tag, p.err, wait_ms);
-                sq = warp_sum(sq);
-                if (lane == 0) misc[8 + warp] = sq;
-                consumer_sync();
-                float tot = 0.0f;
-#pragma unroll
-                for (int w = 0; w < kV2Consumers; w++) tot += misc[8 + w];
-                if (tid == 0) misc[0] = rsqrtf(tot / (float)(G * 128) + p.eps);  // reaches the producer through the slot release
+                // rows below split_row multiply the unrounded vector (primary set), the others norm_out (the second set, or
+                // the primary one when no row wants the unrounded vector)
+                const bool want_u = ph.split_row > 0, want_r = ph.split_row < ph.N;
+                mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, want_u, xq, meta, want_r, want_u ? xq2 : xq,
+                                want_u ? meta2 : meta, p.eps, misc, mail, p.world, p.xH >> 1, tag, p.err, wait_ms);
             } else {
                 mega_stage_plain(ph.x, ph.awq, G, xq, meta);
             }
             consumer_sync();
+            const Range r = cta_range(ph.nblk, G);
+            // A CTA without tiles in this phase arrives at its barrier here, after every consumer thread has read the
+            // phase's input (a CTA with tiles arrives from its producer warp, after its last stage was released).
+            if (r.t_begin >= r.t_end && tid == 0 && !(TP && ph.xout)) grid_arrive(p.bar, phase_barrier(q));
             if (q + 1 < NP) {  // the next projection's activation scales and norm weight: one pass through a 4.9 GB weight
                                // stream evicts them from L2 every token, so ask for them now, one 128-byte line per thread
                 const MegaPhase nx = *reinterpret_cast<const MegaPhase *>(desc + ((q >> 2) & 1) * kDescWords + ((q & 3) + 1) * kPhaseWords);
@@ -579,16 +649,23 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 }
             }
             if (stamp) p.trace[fine + 1] = global_ns();
-            const Range r = cta_range(ph.nblk, G);
             StageIter it(r.t_begin, r.t_end, G);
             int t0, n, rb, grp0;
             tm.reset();
+            const bool two_sets = ph.resid && ph.split_row > 0 && ph.split_row < ph.N;
+            bool on_second = false;
             while (it.next(t0, n, rb, grp0)) {
                 if (!dead && !mbar_wait_warp(&full[slot], par, p.err, wait_ms)) dead = true;
                 const unsigned char *st = ring + (size_t)slot * kStageBytes;
                 if (!dead && warp < n) {
                     const int tb = warp + kV2Consumers;
-                    tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq, meta, lane);
+                    const bool sec = two_sets && rb * 16 >= ph.split_row;  // this row block reads norm_out
+                    if (sec != on_second) {  // the cached activation fragments belong to the other set
+                        on_second = sec;
+                        tm.ga = tm.gb = -1;
+                    }
+                    tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, sec ? xq2 : xq,
+                            sec ? meta2 : meta, lane);
                 }
                 if (grp0 + n == G) {  // last stage of the row block: hand the partial sums to the producer warp
                     float *buf = red + slot * kRedFloats;
@@ -608,7 +685,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             if (stamp) p.trace[fine + 22] = global_ns();
         };
 
-        const int seq_len = p.pos[0] + 1;
+        const int seq_len = min(p.pos[0] + 1, p.max_seq);  // the host checks the position before every step; never read past the caches
         int chunk = (seq_len + p.splits - 1) / p.splits;
         chunk = (chunk + kTile - 1) / kTile * kTile;
         const int used = (seq_len + chunk - 1) / chunk;  // splits that hold positions (<= p.splits)
@@ -634,7 +711,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             // ---- (QK-norm,) RoPE, cache write, query rotation: one head per 128-thread group
             {
                 PrepArgs a;
-                a.qkv = p.qkv; a.stride = p.q_dim + 2 * p.kv_dim; a.k_off = p.q_dim; a.v_off = p.q_dim + p.kv_dim;
+                a.qkv = p.qkv; a.stride = p.q_dim + 2 * p.kv_dim; a.k_off = p.q_dim; a.v_off = p.q_dim + p.kv_dim; a.kv = nullptr; a.kv_stride = 0;
                 a.qw = ly.q_norm; a.kw = ly.k_norm; a.cosc = p.cosc; a.sinc = p.sinc;
                 a.nh = p.nh; a.nkv = p.nkv; a.rotary_dim = p.rotary_dim; a.with_norm = p.with_qk_norm; a.T = 1; a.max_seq = p.max_seq;
                 a.base_pos = seq_len - 1; a.eps = p.eps; a.pos_dev = nullptr; a.qrot = p.qrot; a.q_out = nullptr;  // the position was read once at the start
@@ -721,8 +798,8 @@ static constexpr int attn_bytes() {
     return kGroups * (int)sizeof(AttnSmem<GQ>);
 }
 
-int mega_u_bytes(int G_max, int gq) {
-    const int stage = ((G_max * 8 + 15) & ~15) + G_max * 2 * 32 * 4;
+int mega_u_bytes(int G_max, int G_norm, int gq) {
+    const int stage = ((G_max * 8 + 15) & ~15) + G_max * 2 * 32 * 4 + ((G_norm * 8 + 15) & ~15) + G_norm * 2 * 32 * 4;
     int attn = 0;
     switch (gq) {
         case 1: attn = attn_bytes<1>(); break;
@@ -742,11 +819,8 @@ static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st
     const size_t smem = mega_smem_bytes(p.nring, p.u_bytes);
     if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
     auto kern = decode_token_kernel<GQ, TP>;
-    static thread_local bool configured = false;
-    if (!configured) {
-        IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
-        configured = true;
-    }
+    static DeviceOnce once;  // per instantiation
+    if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(dev->sm_count);
     cfg.blockDim = dim3(kV2Threads);

@@ -321,11 +321,8 @@ int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     const size_t smem = 1024 + (size_t)kGStages * (kGM * kGK * 2 + TN * kGK * 2) + (2 * kGStages + 1) * 8 + 16;
     if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
     auto kern = gemm_int4_tc_kernel<TN>;
-    static thread_local bool configured = false;
-    if (!configured) {
-        IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    static DeviceOnce once;  // per instantiation
+    if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((p.N + kGM - 1) / kGM, (p.M + TN - 1) / TN);
     IM_CUDA_CHECK(launch_k(kern, grid, dim3(kGThreads), smem, st, p));
     return IM_OK;

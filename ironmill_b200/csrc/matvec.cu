@@ -484,11 +484,9 @@ static int launch_fast(const MatvecParams &p, const Device *dev, cudaStream_t st
     size_t smem = (size_t)NB * nchunks * (kXV * 32 * 16 + 32 * 8) + (size_t)(kWarps * RS * NB + kWarps + 1) * 4;
     if (smem > dev->smem_optin) return fail(IM_ERR_INVALID, "K=%d needs %zu bytes of shared memory per CTA (limit %zu)", p.K, smem, dev->smem_optin);
     auto kern = matvec_kernel<BITS, MODE, R, NB>;
-    static thread_local size_t configured = 0;  // per instantiation
-    if (smem > 48 * 1024 && smem > configured) {
+    static DeviceOnce once;  // per instantiation
+    if (smem > 48 * 1024 && once.first(dev->ordinal))
         IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
-        configured = dev->smem_optin;
-    }
     const int rows_per_tile = (kWarps / p.ksplit) * R;
     const int ntiles = (p.N + rows_per_tile - 1) / rows_per_tile;
     int ctas_per_sm = smem > 0 ? (int)((200 * 1024) / (smem + 1024)) : 8;

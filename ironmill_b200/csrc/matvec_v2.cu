@@ -353,11 +353,8 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     p.nring = nring;
     const size_t smem = fixed + (size_t)nring * per_slot;
     auto kern = matvec_v2_kernel<MODE, NB>;
-    static thread_local bool configured = false;
-    if (!configured) {
-        IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
-        configured = true;
-    }
+    static DeviceOnce once;  // per instantiation
+    if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
     const long long total = (long long)p.nblk * p.G;
     if (total > 0x7fffffffLL) return IM_ERR_BOUNDS;
     int grid = dev->sm_count;

@@ -13,6 +13,10 @@ struct MegaPhase {         // one projection of the token; 4 per layer in execut
     __half *resid_out;     // norm phases: a + b rounded to fp16 (must not alias x / resid)
     __half *y;             // outputs [N]
     int nblk, G, N;
+    // norm phases: rows below split_row multiply the unrounded normalised vector and are scaled by rms_inv afterwards
+    // (the reference's fused residual + norm + projection kernel: the next layer's Q rows); rows from split_row on
+    // multiply norm_out, its fp16 copy (K, V, gate, up)
+    int split_row;
     int gate_up;           // tile rows 0-7 gate, 8-15 up of the same 8 outputs -> SiLU(gate) * up
     // Tensor parallel (MegaParams::world > 1).  xout = 1 + mailbox index: the outputs are this rank's partial sums of
     // a row-split projection and go to slot `rank` of that mailbox on EVERY rank instead of y, each pair of outputs in
@@ -46,6 +50,7 @@ struct MegaParams {
     int nring;                // ring slots
     int u_bytes;              // shared-memory scratch shared by the phases
     int g_max;                // largest group count of any phase (sizes the activation staging area)
+    int g_norm;               // group count of the norm phases (hidden / 128): size of the second staging set
     unsigned *bar;            // 7 * L arrival counters + 1 exit counter, zero between launches
     int *err;
     unsigned long long *trace;  // optional: CTA 0 stamps %globaltimer when it leaves each barrier (7L + 2 words)
@@ -58,12 +63,13 @@ struct MegaParams {
     uint2 *xmail[8];            // rank r's mailboxes [4][world][xH / 2] of {two fp16 outputs, tag} as mapped here (peer memory;
                                 // [rank] is local); layers alternate between mailboxes 0-1 and 2-3 (o, down)
     unsigned *xepoch;           // local: launches completed so far (part of the tag)
+    unsigned wait_ms;           // patience of every bounded wait; 0 = the default (400 ms, 5 s with peers)
 };
 
 // Shared-memory bytes the kernel needs for `nring` ring slots and `u_bytes` of phase scratch.
 size_t mega_smem_bytes(int nring, int u_bytes);
-// Phase scratch for projections of up to G_max groups and GQ query heads per KV head.
-int mega_u_bytes(int G_max, int gq);
+// Phase scratch for projections of up to G_max groups (norm phases: G_norm) and GQ query heads per KV head.
+int mega_u_bytes(int G_max, int G_norm, int gq);
 // Cooperative launch; IM_ERR_BOUNDS if the shapes do not fit the kernel.
 int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st);
 

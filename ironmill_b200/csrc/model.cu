@@ -192,6 +192,7 @@ __global__ void __launch_bounds__(kXarThreads) peer_allreduce_kernel(const XarAr
 struct Layer {
     HostAffine hq, hk, hv;           // staged until finalize concatenates them
     AffineWeight *qkv = nullptr;     // rows [q | k | v] of this rank
+    AffineWeight q_rows{}, kv_rows{};  // non-owning views of qkv's Q rows and K | V rows (same device arrays)
     AffineWeight *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
     __half *input_ln = nullptr, *post_ln = nullptr, *q_norm = nullptr, *k_norm = nullptr;
     uint8_t *kc = nullptr, *vc = nullptr;
@@ -211,7 +212,7 @@ struct Model {
     __half *cosc = nullptr, *sinc = nullptr;
     // activations, MT = max tokens per forward
     int MT = 0;
-    __half *hidden = nullptr, *norm_out = nullptr, *residual = nullptr, *qkv = nullptr, *q_d = nullptr, *k_d = nullptr, *v_d = nullptr,
+    __half *hidden = nullptr, *norm_out = nullptr, *residual = nullptr, *qkv = nullptr, *q_d = nullptr, *k_d = nullptr,
            *attn_out = nullptr, *ffn_down = nullptr, *ffn_gate = nullptr, *ffn_up = nullptr, *xs_scratch = nullptr, *logits = nullptr,
            *logits_all = nullptr;
     bool gemm_ok = false;  // every projection is INT4 group-128: forwards of 16 tokens and more run the tensor-core GEMM
@@ -233,7 +234,11 @@ struct Model {
     // whole-token decode kernel (batch 1, single GPU): tables built by mega_prepare()
     bool mega_ready = false;
     MegaParams mega{};
-    int mega_mode = 1;  // 0: never use it (config / IM_MEGA=0)
+    bool mega_capacity2 = false;  // one GPU, tagged hand-over: mailboxes sized for one more (missing) rank (test hook)
+    uint2 *mega_phantom_mail = nullptr;
+    __half *logits_seq = nullptr;  // [prefill chunk, vocab_l] logits of every token (prefill_all_logits), allocated on first use
+    __half *logits_seq_all = nullptr;
+    __half *logits_seq_pin = nullptr;
 #if IM_HAVE_NCCL_H
     ncclComm_t comm = nullptr;
 #endif
@@ -432,6 +437,22 @@ static int make_weight(Model *m, const HostAffine &h, AffineWeight **out) {
     return IM_OK;
 }
 
+// Rows [row0, row0 + rows) of a weight as a weight of its own (non-owning; row0 a multiple of 16 so that the tiled
+// stream splits between row blocks).
+static AffineWeight row_view(const AffineWeight *w, int row0, int rows) {
+    AffineWeight v = *w;
+    v.N = rows;
+    v.codes = w->codes ? w->codes + (size_t)row0 * ((size_t)w->K * w->bits / 8) : nullptr;
+    v.sz = w->sz ? w->sz + (size_t)row0 * w->G : nullptr;
+    v.tiles = w->tiles ? w->tiles + (size_t)(row0 / 16) * w->G * 1088 : nullptr;
+    v.nblk = (rows + 15) / 16;
+    v.pair_tiles = nullptr;
+    v.pair_with = nullptr;
+    v.pair_nblk = 0;
+    v.bytes = 0;
+    return v;
+}
+
 static int tp_allreduce(Model *m, __half *buf, size_t count, cudaStream_t st) {
     if (m->world <= 1) return IM_OK;
 #if IM_HAVE_NCCL_H
@@ -483,7 +504,7 @@ struct Prof {
 
 // One forward pass over nseq sequences x T tokens each (decode: T = 1; prefill: nseq = 1).
 // Logits are produced for the last token of every sequence.
-static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches, Prof *prof = nullptr) {
+static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches, Prof *prof = nullptr, bool all_logits = false) {
     const im_model_config &c = m->cfg;
     const int H = c.hidden_size, hd = c.head_dim, MT = nseq * T;
     const float eps = c.rms_eps;
@@ -502,7 +523,9 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)H, st));
         nl += 2 + (m->world > 1 ? 1 : 0);
     }
-    const bool gemm = !mega && m->gemm_ok && MT >= kGemmMinTokens;
+    // More than one token per sequence is the reference's prefill form (its matmul kernels round x / awq and the
+    // dequantised weights to fp16: affine_matmul.metal:44-74), whatever the count; so are decode batches of 16 and more.
+    const bool gemm = !mega && m->gemm_ok && (T > 1 || MT >= kGemmMinTokens);
     for (int l = 0; l < c.num_layers && gemm; l++) {
         // Dense contraction (prefill chunks, large decode batches): every projection is one tcgen05 GEMM; norms, SiLU
         // and the residual adds are separate element-wise launches (their bytes are a rounding error next to the GEMMs).
@@ -557,16 +580,24 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
             IM_MARK(kCatResNorm);
         }
     }
+    // Launch-per-kernel schedule with the reference's decode-time rounding points (one token per sequence):
+    //   4-bit weights: Q of layers >= 1 comes out of the fused residual + norm + projection kernel (unrounded
+    //   normalised vector), K and V read norm_out (metal/attention.rs:616-702); gate/up read norm_out and keep their
+    //   f32 dot products for SiLU(g) * u (metal/ffn.rs:25-54).  Other widths have no fused kernels in the reference:
+    //   every projection reads the fp16 buffers, gate and up are rounded before the activation (ffn.rs:58-150).
     for (int l = 0; l < c.num_layers && !mega && !gemm; l++) {
         Layer &L = m->layers[l];
+        const bool fused4 = L.qkv->bits == 4 && L.gate->bits == 4 && L.up->bits == 4;
+        const int nmv = (MT + 3) / 4;
         if (l == 0) {
-            IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.qkv), m->norm_out, m->qkv, MT, st));
-            nl += (MT + 3) / 4;
+            IM_TRY(im_cuda_matvec_affine(static_cast<const im_affine_weight *>(&L.q_rows), m->norm_out, m->q_d, MT, st));
+            IM_TRY(im_cuda_matvec_affine(static_cast<const im_affine_weight *>(&L.kv_rows), m->norm_out, m->k_d, MT, st));
+            nl += 2 * nmv;
             IM_MARK(kCatQkv);
         }
         // (QK-norm +) RoPE, K/V cache write and query rotation in one launch, then split attention + reduce
         TqPrep a{};
-        a.qkv = m->qkv; a.stride = m->qkv_dim; a.k_off = m->q_dim; a.v_off = m->q_dim + m->kv_dim;
+        a.qkv = m->q_d; a.stride = m->q_dim; a.kv = m->k_d; a.kv_stride = 2 * m->kv_dim; a.k_off = 0; a.v_off = m->kv_dim;
         a.qw = L.q_norm; a.kw = L.k_norm; a.cosc = m->cosc; a.sinc = m->sinc;
         a.nh = m->nh_l; a.nkv = m->nkv_l; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd; a.with_norm = c.qk_norm ? 1 : 0;
         a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev;
@@ -582,26 +613,61 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         IM_MARK(kCatOProj);
         IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
         if (m->world > 1) IM_MARK(kCatComm);
-        // residual + RMSNorm folded into the gate/up projection (the projection reads the unrounded normalised vector)
-        IM_TRY(im_cuda_fused_residual_norm_ffn(static_cast<im_affine_weight *>(L.gate), static_cast<im_affine_weight *>(L.up), m->hidden,
-                                               m->ffn_down, L.post_ln, eps, m->ffn_gate, m->residual, m->norm_out, MT, st));
+        IM_TRY(im_cuda_fused_residual_rms_norm(m->hidden, m->ffn_down, L.post_ln, m->norm_out, m->residual, H, MT, eps, st));
+        IM_MARK(kCatResNorm);
+        if (fused4) {
+            IM_TRY(im_cuda_ffn_gate_up_act(static_cast<im_affine_weight *>(L.gate), static_cast<im_affine_weight *>(L.up), m->norm_out,
+                                           m->ffn_gate, MT, st));
+            nl += nmv;
+        } else {
+            IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.gate), m->norm_out, m->ffn_gate, MT, st));
+            IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.up), m->norm_out, m->ffn_up, MT, st));
+            const size_t n = (size_t)MT * m->I_l;
+            cudaError_t le = launch_k(silu_mul_kernel, dim3((unsigned)((n / 2 + 255) / 256)), dim3(256), 0, st, (const __half *)m->ffn_gate,
+                                      (const __half *)m->ffn_up, m->ffn_gate, n);
+            if (le != cudaSuccess) return fail(IM_ERR_CUDA, "launch failed: %s", cudaGetErrorString(le));
+            nl += 2 * nmv + 1;
+        }
         IM_MARK(kCatFfn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.down), m->ffn_gate, m->ffn_down, MT, st));
         IM_MARK(kCatDown);
         IM_TRY(tp_allreduce(m, m->ffn_down, (size_t)MT * H, st));
         if (m->world > 1) IM_MARK(kCatComm);
-        nl += 3 * ((MT + 3) / 4) + (m->world > 1 ? 2 : 0);
+        nl += 2 * nmv + 1 + (m->world > 1 ? 2 : 0);
         if (l + 1 < c.num_layers) {
             Layer &Nx = m->layers[l + 1];
-            IM_TRY(im_cuda_fused_residual_norm_matvec(static_cast<im_affine_weight *>(Nx.qkv), m->residual, m->ffn_down, Nx.input_ln, eps,
-                                                      m->qkv, m->hidden, m->norm_out, MT, st));
-            nl += (MT + 3) / 4;
+            if (Nx.qkv->bits == 4) {
+                IM_TRY(im_cuda_fused_residual_norm_matvec(static_cast<const im_affine_weight *>(&Nx.q_rows), m->residual, m->ffn_down, Nx.input_ln,
+                                                          eps, m->q_d, m->hidden, m->norm_out, MT, st));
+            } else {
+                IM_TRY(im_cuda_fused_residual_rms_norm(m->residual, m->ffn_down, Nx.input_ln, m->norm_out, m->hidden, H, MT, eps, st));
+                IM_TRY(im_cuda_matvec_affine(static_cast<const im_affine_weight *>(&Nx.q_rows), m->norm_out, m->q_d, MT, st));
+                nl++;
+            }
+            IM_TRY(im_cuda_matvec_affine(static_cast<const im_affine_weight *>(&Nx.kv_rows), m->norm_out, m->k_d, MT, st));
+            nl += 2 * nmv;
             IM_MARK(kCatQkv);
         } else {
             IM_TRY(im_cuda_residual_add(m->residual, m->ffn_down, m->hidden, (size_t)MT * H, st));
             nl++;
             IM_MARK(kCatResNorm);
         }
+    }
+    if (all_logits) {  // final norm + lm_head on every token of the (single) sequence: prefill_all_logits
+        IM_TRY(im_cuda_rms_norm(m->hidden, m->final_norm, m->norm_out, H, MT, eps, st));
+        for (int r = 0; r < MT; r += 64) {  // the fp16 matvec takes up to 64 rows per call
+            const int nb = MT - r < 64 ? MT - r : 64;
+            IM_TRY(im_cuda_matvec_f16(m->lm_head, m->norm_out + (size_t)r * H, m->logits_seq + (size_t)r * m->vocab_l, m->vocab_l, H, nb, st));
+        }
+        nl += 1 + (MT + 3) / 4;
+        if (m->world > 1) {
+#if IM_HAVE_NCCL_H
+            IM_NCCL_CHECK(nccl()->AllGather(m->logits_seq, m->logits_seq_all, (size_t)MT * m->vocab_l, ncclHalf, m->comm, st));
+            nl++;
+#endif
+        }
+        if (launches) *launches = nl;
+        return IM_OK;
     }
     // final norm + lm_head on the last token of each sequence
     for (int s = 0; s < nseq; s++) {
@@ -626,13 +692,11 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
 // has the tiled INT4 layout; anything else keeps the launch-per-kernel schedule of forward().
 static int mega_prepare(Model *m) {
     m->mega_ready = false;
-    const char *env = getenv("IM_MEGA");
-    if (m->mega_mode == 0 || (env && env[0] == '0')) return IM_OK;
     const im_model_config &c = m->cfg;
+    if (c.decode_schedule == 1) return IM_OK;
     const bool tp = m->world > 1;
-    const char *tg = getenv("IM_MEGA_TAGGED");
     // one GPU: opt-in only (measured slower there than the barrier: 64.0 against 60.0 us per layer at L8 shapes)
-    const bool tagged = tp || (tg && tg[0] == '1');
+    const bool tagged = tp || c.decode_schedule == 2;
     if (tp && (!m->xar.ok || m->world > 8 || c.hidden_size % 128 != 0)) return IM_OK;  // needs the peer mapping of tp_init
     if (c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
     const int gq = m->nh_l / m->nkv_l;
@@ -647,7 +711,10 @@ static int mega_prepare(Model *m) {
         if ((L.gate->awq != nullptr) != (L.up->awq != nullptr)) return IM_OK;
         IM_TRY(ensure_pair(L.gate, L.up, m->stream));
     }
-    const int u_bytes = mega_u_bytes(g_max, gq);
+    const int g_norm = c.hidden_size / 128;
+    if (c.hidden_size % 128 != 0) return IM_OK;
+    if (tagged && g_norm > 32) return IM_OK;  // the mailbox form of the norm staging keeps one chunk per thread (hidden <= 4096)
+    const int u_bytes = mega_u_bytes(g_max, g_norm, gq);
     if (u_bytes < 0) return IM_OK;
     int nring = 8;
     while (nring >= 3 && mega_smem_bytes(nring, u_bytes) + 1024 > m->dev->smem_optin) nring--;
@@ -663,6 +730,7 @@ static int mega_prepare(Model *m) {
             q.x = m->norm_out;
         } else {
             q.x = m->residual; q.resid = m->ffn_down; q.gamma = Ly.input_ln; q.resid_out = m->hidden;
+            q.split_row = m->q_dim;  // Q from the unrounded vector, K and V from norm_out (metal/attention.rs:616-702)
         }
         o.tiles = Ly.o->tiles; o.awq = Ly.o->awq; o.nblk = Ly.o->nblk; o.G = Ly.o->G; o.N = Ly.o->N; o.x = m->attn_out; o.y = m->ffn_down;
         gu.tiles = Ly.gate->pair_tiles; gu.awq = Ly.gate->awq; gu.nblk = Ly.gate->pair_nblk; gu.G = Ly.gate->G; gu.N = Ly.gate->N;
@@ -706,7 +774,7 @@ static int mega_prepare(Model *m) {
     p.attn_scale = c.attn_scale != 0.0f ? c.attn_scale : 1.0f / sqrtf((float)c.head_dim);
     p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)c.head_dim;
     p.max_seq = c.max_seq_len; p.rotary_dim = c.rotary_dim ? c.rotary_dim : c.head_dim; p.with_qk_norm = c.qk_norm ? 1 : 0;
-    p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max;
+    p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max; p.g_norm = g_norm;
     IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;
@@ -714,15 +782,21 @@ static int mega_prepare(Model *m) {
         p.tagged = 1; p.world = m->world; p.rank = m->rank; p.xH = c.hidden_size;
         for (int r = 0; r < m->world; r++) p.xmail[r] = reinterpret_cast<uint2 *>(m->xar.peer[r] + m->xar.mail_off);
         p.xepoch = reinterpret_cast<unsigned *>(m->xar.base + m->xar.epoch_off);
-    } else if (tagged) {  // one GPU: local mailboxes (4 x hidden/2 pairs), then the launch count
-        const size_t mail_bytes = (size_t)4 * (c.hidden_size / 2) * sizeof(uint2);
-        unsigned char *loc = nullptr;
+    } else if (tagged) {  // one GPU: local mailboxes (4 x hidden/2 pairs per rank slot), then the launch count
+        // sized for two rank slots: im_cuda_model_test_missing_ranks makes the kernel expect a second rank's sums
+        const size_t mail_bytes = (size_t)4 * 2 * (c.hidden_size / 2) * sizeof(uint2);
+        unsigned char *loc = nullptr, *phantom = nullptr;
         IM_TRY(m->alloc((void **)&loc, mail_bytes + 256));
+        IM_TRY(m->alloc((void **)&phantom, mail_bytes));
         IM_CUDA_CHECK(cudaMemset(loc, 0, mail_bytes + 256));
+        IM_CUDA_CHECK(cudaMemset(phantom, 0, mail_bytes));
         p.tagged = 1; p.world = 1; p.rank = 0; p.xH = c.hidden_size;
         p.xmail[0] = reinterpret_cast<uint2 *>(loc);
         p.xepoch = reinterpret_cast<unsigned *>(loc + mail_bytes);
+        m->mega_capacity2 = true;
+        m->mega_phantom_mail = reinterpret_cast<uint2 *>(phantom);
     }
+    p.wait_ms = c.wait_limit_ms > 0 ? (unsigned)c.wait_limit_ms : 0u;
     // phase stamps of CTA 0 (a store per grid barrier; read back by im_cuda_model_token_kernel_profile)
     IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
     IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
@@ -848,8 +922,7 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
     IM_NCCL_CHECK(nccl()->CommInitRank(&m->comm, m->world, id, m->rank));
     // Receive buffers of the one-shot all-reduce, mapped into every rank with CUDA IPC (handles exchanged through the
     // communicator just created).  Any failure here leaves the NCCL all-reduce in charge.
-    const char *env = getenv("IM_TP_PEER");
-    if (m->world <= kXarMaxWorld && !(env && env[0] == '0')) {
+    if (m->world <= kXarMaxWorld && m->cfg.tp_collective != 1) {
         PeerAllreduce &x = m->xar;
         x.cap = (size_t)4 * m->cfg.hidden_size;  // up to four batch rows: the decode batches that run one matvec per projection
         x.bytes = 256 + (size_t)2 * m->world * x.cap * sizeof(__half);
@@ -936,9 +1009,8 @@ IM_EXPORT int im_cuda_model_tp_init(im_model *m, const void *id_128_bytes) {
         // The whole-token kernel exchanges its row-split partial sums through the same mapping; every rank must run it
         // or none (a rank on the per-kernel schedule would never feed the others' counters).
         if (x.ok) {
-            const char *me = getenv("IM_TP_MEGA");
             int mine_ready = 0;
-            if (!(me && me[0] == '0') && mega_prepare(m) == IM_OK && m->mega_ready) mine_ready = 1;
+            if (mega_prepare(m) == IM_OK && m->mega_ready) mine_ready = 1;
             int all_ready = 0;
             int *ag = nullptr;
             if (cudaMalloc((void **)&ag, sizeof(int)) == cudaSuccess) {
@@ -982,6 +1054,10 @@ IM_EXPORT int im_cuda_model_create(im_device *dev, const im_model_config *cfg, i
     IM_REQUIRE(c.num_kv_heads % c.tp_world == 0 && c.intermediate_size % (c.tp_world * 128) == 0 && c.vocab_size % c.tp_world == 0,
                "tensor-parallel size %d must divide num_kv_heads, intermediate_size/128 and vocab_size", c.tp_world);
     IM_REQUIRE(c.rms_eps > 0.0f && c.rope_theta > 0.0, "rms_eps and rope_theta must be positive");
+    IM_REQUIRE(c.prefill_chunk_size >= 0 && c.prefill_chunk_size <= kPrefillChunk, "prefill_chunk_size must be in 0..%d", kPrefillChunk);
+    IM_REQUIRE(c.decode_schedule >= 0 && c.decode_schedule <= 2 && c.tp_collective >= 0 && c.tp_collective <= 1 && c.wait_limit_ms >= 0,
+               "bad decode_schedule / tp_collective / wait_limit_ms");
+    if (c.prefill_chunk_size == 0) c.prefill_chunk_size = kPrefillChunk;
     IM_CUDA_CHECK(cudaSetDevice(dev->ordinal));
     im_model *m = new im_model();
     m->dev = dev;
@@ -1028,6 +1104,7 @@ IM_EXPORT void im_cuda_model_free(im_model *m) {
     for (auto &a : m->allocs) dev_free(m->dev, a.first, a.second);
     if (m->tokens_pin) cudaFreeHost(m->tokens_pin);
     if (m->logits_pin) cudaFreeHost(m->logits_pin);
+    if (m->logits_seq_pin) cudaFreeHost(m->logits_seq_pin);
     if (m->err_pin) cudaFreeHost(m->err_pin);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
@@ -1147,6 +1224,8 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
             f.z16.insert(f.z16.end(), p->z16.begin(), p->z16.end());
         }
         IM_TRY(make_weight(m, f, &L.qkv));
+        L.q_rows = row_view(L.qkv, 0, m->q_dim);
+        L.kv_rows = row_view(L.qkv, m->q_dim, 2 * m->kv_dim);
         L.hq = HostAffine(); L.hk = HostAffine(); L.hv = HostAffine();
         // KV cache of this rank's heads (MetalKvCache, crates/ironmill-inference/src/metal/turboquant/cache.rs:104-354)
         const size_t rows = (size_t)c.max_batch * m->nkv_l * c.max_seq_len;
@@ -1181,8 +1260,7 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_TRY(m->alloc((void **)&m->residual, MT * H * 2));
     IM_TRY(m->alloc((void **)&m->qkv, MT * m->qkv_dim * 2));
     IM_TRY(m->alloc((void **)&m->q_d, MT * m->q_dim * 2));
-    IM_TRY(m->alloc((void **)&m->k_d, MT * m->kv_dim * 2));
-    IM_TRY(m->alloc((void **)&m->v_d, MT * m->kv_dim * 2));
+    IM_TRY(m->alloc((void **)&m->k_d, MT * 2 * m->kv_dim * 2));  // K | V rows of a token (launch-per-kernel schedule)
     IM_TRY(m->alloc((void **)&m->attn_out, MT * m->q_dim * 2));
     IM_TRY(m->alloc((void **)&m->qrot, MT * m->q_dim * 2 * sizeof(float)));
     IM_TRY(m->alloc((void **)&m->ffn_down, MT * H * 2));
@@ -1194,7 +1272,7 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
         if ((size_t)m->q_dim > kmax) kmax = (size_t)m->q_dim;
         IM_TRY(m->alloc((void **)&m->xs_scratch, MT * kmax * 2));
     }
-    m->gemm_ok = getenv("IM_GEMM") == nullptr || getenv("IM_GEMM")[0] != '0';
+    m->gemm_ok = true;
     for (Layer &L : m->layers)
         for (AffineWeight *w : {L.qkv, L.o, L.gate, L.up, L.down})
             if (!w || w->bits != 4 || w->group_size != 128 || w->K % 128 != 0 || w->N % 8 != 0) m->gemm_ok = false;
@@ -1306,14 +1384,20 @@ IM_EXPORT int im_cuda_model_token_kernel_profile(im_model *m, int reps, float *m
     IM_GUARD_END
 }
 
-// Development aid: the raw stamps (7L + 2 phase stamps, then 4 x 24 stamps inside the projections of layer 1).
-IM_EXPORT int im_cuda_model_debug_trace(im_model *m, unsigned long long *out, int n) {
+// Test hook of the error path: see the header.  The captured decode graphs hold the kernel's parameters by value, so
+// they are dropped and the next step captures again.
+IM_EXPORT int im_cuda_model_test_missing_ranks(im_model *m, int missing_ranks) {
     IM_GUARD_BEGIN
-    IM_REQUIRE(m && out && n >= 0, "bad argument");
-    if (!m->mega.trace) return fail(IM_ERR_STATE, "this model does not run the whole-token decode kernel");
-    const int have = 7 * m->cfg.num_layers + 2 + 96;
+    IM_REQUIRE(m && (missing_ranks == 0 || missing_ranks == 1), "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    if (!m->mega_ready || !m->mega_capacity2 || m->world != 1)
+        return fail(IM_ERR_STATE, "only for a single-GPU model loaded with decode_schedule = 2");
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
-    IM_CUDA_CHECK(cudaMemcpy(out, m->mega.trace, (size_t)(n < have ? n : have) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    m->mega.world = 1 + missing_ranks;
+    m->mega.xmail[1] = missing_ranks ? m->mega_phantom_mail : nullptr;  // where the stores "to the other rank" land
+    for (auto &g : m->graphs) cudaGraphExecDestroy(g.second);
+    m->graphs.clear();
     return IM_OK;
     IM_GUARD_END
 }
@@ -1349,7 +1433,7 @@ IM_EXPORT int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, in
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
     // 256-token chunks when the projections run as tensor-core GEMMs; the matvec kernels take at most 64 rows per call
-    const int chunk = m->gemm_ok ? kPrefillChunk : 64;
+    const int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
     for (int done = 0; done < n; done += chunk) {
         const int T = n - done < chunk ? n - done : chunk;
         memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
@@ -1365,6 +1449,46 @@ IM_EXPORT int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, in
     IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, st));
     IM_CUDA_CHECK(cudaStreamSynchronize(st));
     logits_to_host(m, m->logits_pin, 1, logits_out_host);
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_prefill_all_logits(im_model *m, const uint32_t *tokens_host, int n, float *logits_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && tokens_host && logits_out_host, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(n > 0, "prefill needs at least one token");
+    if (m->seq_pos + n > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->seq_pos, n, m->cfg.max_seq_len);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    cudaStream_t st = m->stream;
+    const int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
+    const size_t V = (size_t)m->cfg.vocab_size;
+    if (!m->logits_seq) {  // first use: a chunk's worth of logits on the device and in pinned host memory
+        IM_TRY(m->alloc((void **)&m->logits_seq, (size_t)kPrefillChunk * m->vocab_l * 2));
+        if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_seq_all, (size_t)kPrefillChunk * V * 2));
+        IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_seq_pin, (size_t)kPrefillChunk * V * 2));
+    }
+    for (int done = 0; done < n; done += chunk) {
+        const int T = n - done < chunk ? n - done : chunk;
+        memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
+        const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->seq_pos + T);
+        IM_TRY(forward(m, 1, T, splits, st, nullptr, nullptr, true));
+        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, 1, T);
+        IM_CUDA_CHECK(cudaGetLastError());
+        const __half *lg = m->world > 1 ? m->logits_seq_all : m->logits_seq;
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_seq_pin, lg, (size_t)T * V * 2, cudaMemcpyDeviceToHost, st));
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+        IM_CUDA_CHECK(cudaStreamSynchronize(st));
+        IM_TRY(step_error_check(m));
+        m->seq_pos += T;
+        // device layout [part][token][vocab_l] -> host rows [token][vocab]
+        const int vl = m->vocab_l;
+        for (int p = 0; p < m->world; p++)
+            for (int t = 0; t < T; t++)
+                widen(m->logits_seq_pin + ((size_t)p * T + t) * vl, logits_out_host + (size_t)(done + t) * V + (size_t)p * vl, vl);
+    }
     return IM_OK;
     IM_GUARD_END
 }

@@ -467,6 +467,8 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 struct PrepArgs {
     const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
     int stride, k_off, v_off;
+    const __half *kv;   // nullptr, or the buffer [nseq*T, kv_stride] that holds the K and V rows (k_off / v_off index it)
+    int kv_stride;
     const __half *qw, *kw, *cosc, *sinc;
     int nh, nkv, rotary_dim, with_norm, T, max_seq, base_pos;
     float eps;
@@ -487,16 +489,17 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     const int seq = st / a.T, t = st % a.T;
     const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
     const __half *tok = a.qkv + (size_t)st * a.stride;
+    const __half *tokkv = a.kv ? a.kv + (size_t)st * a.kv_stride : tok;
     const float sg = a.ktab.signs[d];  // requested together with the head's values, not after the RoPE
     if (slot >= a.nh + a.nkv) {  // value head
         const int h = slot - a.nh - a.nkv;
         const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(sc, __half2float(tok[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, (float *)nullptr, sg);
+        tq_encode_body(sc, __half2float(tokkv[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, (float *)nullptr, sg);
         return;
     }
     const bool is_q = slot < a.nh;
     const int h = is_q ? slot : slot - a.nh;
-    const __half *src = tok + (is_q ? 0 : a.k_off) + h * kHd;
+    const __half *src = (is_q ? tok : tokkv + a.k_off) + h * kHd;
     const __half *w = is_q ? a.qw : a.kw;
     float x = __half2float(src[d]);
     // the rotation's table entries are requested with the head's values, not after the norm's barrier

@@ -123,7 +123,8 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
     pdl_trigger();
     pdl_wait();
     const int seq = st / p.T, t = st % p.T;
-    const int seq_len = p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1;
+    // never past the end of the head's rows, whatever a device-side position says (the host can only check base_pos)
+    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1, p.max_seq);
     const int chunk = (seq_len + p.splits - 1) / p.splits;
     const int r0 = split * chunk, r1 = min(r0 + chunk, seq_len);
     cbk[tid] = p.k_cb[tid];
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
     __syncthreads();
 
     const int seq = st / p.T, tt = st % p.T;
-    const int seq_len = p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + tt + 1;
+    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + tt + 1, p.max_seq);  // see tq_attention_kernel
     const int chunk = (seq_len + p.splits - 1) / p.splits;
     const int c0 = split * chunk, c1 = min(c0 + chunk, seq_len);
     // this warp's run: whole tiles of the split's range
@@ -599,7 +600,7 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
     if (tq->hd != kHd) return fail(IM_ERR_INVALID, "the fused cache-write kernel is built for head_dim 128 (got %d)", tq->hd);
     if (a.nseq == 0 || a.T == 0) return IM_OK;
     PrepArgs k{};
-    k.qkv = a.qkv; k.stride = a.stride; k.k_off = a.k_off; k.v_off = a.v_off;
+    k.qkv = a.qkv; k.stride = a.stride; k.k_off = a.k_off; k.v_off = a.v_off; k.kv = a.kv; k.kv_stride = a.kv_stride;
     k.qw = a.qw; k.kw = a.kw; k.cosc = a.cosc; k.sinc = a.sinc;
     k.nh = a.nh; k.nkv = a.nkv; k.rotary_dim = a.rotary_dim ? a.rotary_dim : kHd; k.with_norm = a.with_norm;
     k.T = a.T; k.max_seq = a.max_seq; k.base_pos = a.base_pos; k.eps = a.eps; k.pos_dev = a.pos_dev;
@@ -637,14 +638,12 @@ int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uin
     p.nh = nh; p.nkv = nkv; p.max_seq = max_seq; p.base_pos = base_pos; p.T = T; p.splits = splits; p.pos_dev = pos_dev;
     dim3 grid(nkv, nseq * T, splits);
     const int gq = nh / nkv;
-    static const bool tc_on = [] { const char *e = getenv("IM_ATTN_TC"); return !(e && e[0] == '0'); }();
-    if (qrot && tc_on && (gq == 1 || gq == 2 || gq == 4) && nh % nkv == 0) {  // tensor-core kernel (needs the rotated queries)
-        static thread_local bool configured = false;
-        if (!configured) {  // the three instantiations share one function-pointer type: set them all once
+    if (qrot && (gq == 1 || gq == 2 || gq == 4) && nh % nkv == 0) {  // tensor-core kernel (needs the rotated queries)
+        static DeviceOnce once;
+        if (once.first(tq->dev->ordinal)) {  // the three instantiations share one function-pointer type: set them all once
             IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
             IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
             IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
-            configured = true;
         }
         auto kern = gq == 1 ? tq_attention_tc_kernel<1> : (gq == 2 ? tq_attention_tc_kernel<2> : tq_attention_tc_kernel<4>);
         int rc = IM_OK;

@@ -152,6 +152,79 @@ struct TileMath {
     }
 };
 
+// The same arithmetic on a STRIP: SG = 4 / NB consecutive tiles (groups grp0 .. grp0 + SG - 1) of one row block,
+// walked by one warp with ONE pair of accumulators.  An m16n8k32 product has eight B columns and a tile needs only
+// 2 NB of them (high and low activation bytes per batch row), so tile j of the strip puts its activations in columns
+// 2 NB j .. 2 NB j + 2 NB - 1 and zeros elsewhere: the accumulator then holds the integer dot products of SG different
+// (row, group) pairs side by side, every lane owns one of them (rows g and g + 8 of group grp0 + t / NB, batch row
+// t % NB), and the float fix-up runs once per strip with all 32 lanes busy instead of once per tile with 8 NB of them.
+// A lane feeds column g = lane >> 2: it reads its fragment of the staged activations for the one tile of the strip
+// whose columns it owns and a block of zeros for the others (an address select, no register copies).
+// acc0 / acc1: this lane's share of rows g / g + 8 (batch row t % NB); row_sums() folds the lanes of a row together.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+template <int NB>
+struct StripMath {
+    static constexpr int SG = 4 / NB;
+    float acc0, acc1;
+    __device__ __forceinline__ void reset() { acc0 = acc1 = 0.0f; }
+    // tiles: shared-memory address of the strip's first tile; ntiles (1 .. SG, warp-uniform) tiles are present;
+    // xq / meta: the staged activations (layout of v2_stage_x); zero32: 32 bytes of zeros in shared memory.
+    __device__ __forceinline__ void strip(uint32_t tiles, int grp0, int ntiles, uint32_t xq, const float2 *meta, uint32_t zero32, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+        const int jm = g / (2 * NB), col = g % (2 * NB);
+        const uint32_t xmine = xq + (uint32_t)(((((grp0 + jm) * 2 * NB + col) * 4 + t) * 8) * 4);
+        constexpr unsigned ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
+        int cal[4], cah[4];
+#pragma unroll
+        for (int j = 0; j < SG; j++) {
+            if (j < ntiles) {
+                const uint32_t tl = tiles + (uint32_t)(j * kTileBytes + lane * 16);
+                const uint4 a0 = lds128(tl), a1 = lds128(tl + 512);
+                const uint32_t xp = jm == j ? xmine : zero32;
+                const uint4 x0 = lds128(xp), x1 = lds128(xp + 16);
+                if (j == 0) {
+                    mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, x0.x, x0.z);
+                    mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, x0.y, x0.w);
+                } else {
+                    mma_u8s8(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, x0.x, x0.z);
+                    mma_u8s8(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, x0.y, x0.w);
+                }
+                mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, x1.x, x1.z);
+                mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, x1.y, x1.w);
+            }
+        }
+        const int jt = t / NB;
+        if (jt < ntiles) {
+            const float2 m = meta[(grp0 + jt) * NB + t % NB];
+            uint32_t s0, s1;
+            const uint32_t sza = tiles + (uint32_t)(jt * kTileBytes + kTileCodeBytes + g * 4);
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(s0) : "r"(sza));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(s1) : "r"(sza + 32));
+            const float2 sz0 = __half22float2(*reinterpret_cast<const __half2 *>(&s0)), sz1 = __half22float2(*reinterpret_cast<const __half2 *>(&s1));
+            const float f0 = (float)(cal[0] * 4096 + (cal[1] * 16 + (cah[0] * 256 + cah[1]))), f1 = (float)(cal[2] * 4096 + (cal[3] * 16 + (cah[2] * 256 + cah[3])));
+            acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
+            acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+        }
+    }
+    // Sums of rows g and g + 8 for batch row t % NB over the lanes that shared them; valid in every lane afterwards.
+    __device__ __forceinline__ void row_sums(float &r0, float &r1) const {
+        r0 = acc0;
+        r1 = acc1;
+        if (NB <= 2) {
+            r0 += __shfl_xor_sync(0xffffffffu, r0, 2);
+            r1 += __shfl_xor_sync(0xffffffffu, r1, 2);
+        }
+        if (NB == 1) {
+            r0 += __shfl_xor_sync(0xffffffffu, r0, 1);
+            r1 += __shfl_xor_sync(0xffffffffu, r1, 1);
+        }
+    }
+};
+
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kV2Consumers * 32) : "memory"); }
 
 __device__ __forceinline__ unsigned pack4s(int a, int b, int c, int d) {

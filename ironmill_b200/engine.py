@@ -47,6 +47,11 @@ class CudaConfig:
     tp_world: int = 1
     tp_rank: int = 0
     device: int = 0
+    # batch-1 decode schedule: "auto" (the whole-token kernel when the model fits it), "per_kernel" (graph of
+    # per-projection kernels), "tagged" (whole-token kernel with tagged hand-over of the o / down outputs on one GPU)
+    decode_schedule: str = "auto"
+    tp_collective: str = "auto"   # "auto" (peer-memory exchange when the ranks can map each other) or "nccl"
+    wait_limit_ms: int = 0        # patience of device-side bounded waits (0 = default)
 
     def with_max_seq_len(self, n: int) -> "CudaConfig":
         self.max_seq_len = n
@@ -70,7 +75,9 @@ class _CModelConfig(C.Structure):
                 ("num_kv_heads", C.c_int), ("head_dim", C.c_int), ("vocab_size", C.c_int), ("max_seq_len", C.c_int),
                 ("max_batch", C.c_int), ("rms_eps", C.c_float), ("attn_scale", C.c_float), ("embed_scale", C.c_float),
                 ("rope_theta", C.c_double), ("rotary_dim", C.c_int), ("qk_norm", C.c_int), ("tie_word_embeddings", C.c_int),
-                ("tq_bits", C.c_int), ("rotation_seed", C.c_uint64), ("tp_world", C.c_int), ("tp_rank", C.c_int)]
+                ("tq_bits", C.c_int), ("rotation_seed", C.c_uint64), ("tp_world", C.c_int), ("tp_rank", C.c_int),
+                ("prefill_chunk_size", C.c_int), ("decode_schedule", C.c_int), ("tp_collective", C.c_int),
+                ("wait_limit_ms", C.c_int)]
 
 
 @dataclass
@@ -117,7 +124,10 @@ class CudaInference:
                            mc.num_key_value_heads, mc.head_dim, mc.vocab_size, self.config.max_seq_len, self.config.max_batch,
                            mc.rms_norm_eps, mc.attn_scale, float(mc.extra.get("embed_scale", 0.0) or 0.0), mc.rope_theta,
                            int(mc.extra.get("rotary_dim", 0) or 0), int(mc.has_qk_norm), int(mc.tie_word_embeddings),
-                           self.config.n_bits, self.config.rotation_seed, self.config.tp_world, self.config.tp_rank)
+                           self.config.n_bits, self.config.rotation_seed, self.config.tp_world, self.config.tp_rank,
+                           int(self.config.prefill_chunk_size or 0),
+                           {"auto": 0, "per_kernel": 1, "tagged": 2}[self.config.decode_schedule],
+                           {"auto": 0, "nccl": 1}[self.config.tp_collective], int(self.config.wait_limit_ms))
         check(lib().im_cuda_model_create(self._dev, C.byref(cc), C.byref(self._model)))
         if tq_signs is not None:
             s = np.ascontiguousarray(tq_signs, dtype=np.float32)
@@ -190,6 +200,22 @@ class CudaInference:
         out = np.empty(self._mc.vocab_size, dtype=np.float32)
         check(lib().im_cuda_model_prefill(self._model, vp(toks), C.c_int(toks.size), vp(out)))
         return out
+
+    @_wrap
+    def prefill_all_logits(self, tokens) -> np.ndarray:
+        """InferenceEngine::prefill_all_logits (metal/pipeline.rs:38-70): logits [n_tokens, vocab], one row per token."""
+        self._need_model()
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.empty((toks.size, self._mc.vocab_size), dtype=np.float32)
+        check(lib().im_cuda_model_prefill_all_logits(self._model, vp(toks), C.c_int(toks.size), vp(out)))
+        return out
+
+    @_wrap
+    def test_missing_ranks(self, n: int) -> None:
+        """Host-side fault injection (tests of the error path; `decode_schedule="tagged"` on one GPU only): n = 1 makes
+        the whole-token kernel wait for a rank that does not exist until its bounded wait gives up; 0 undoes it."""
+        self._need_model()
+        check(lib().im_cuda_model_test_missing_ranks(self._model, C.c_int(n)))
 
     @_wrap
     def decode_step(self, token) -> np.ndarray:

@@ -1,8 +1,22 @@
 """CPU oracle of the whole decode step (test infrastructure): numpy glue over the oracle primitives,
 following the reference's schedule and its fp16 rounding points
 (crates/ironmill-inference/src/metal/pipeline.rs:424-1313; end-of-layer fusion
-crates/ironmill-inference/src/metal/attention.rs:616-702).  Weights are dequantised once to f32
-with w = (q - z) * s from the fp16 scale / zero point the GPU sees; dot products accumulate in f32."""
+crates/ironmill-inference/src/metal/attention.rs:616-702; FFN dispatch metal/ffn.rs:13-150; matvec / matmul
+choice metal/ops/mod.rs LinearKernelKind::for_token_count; attention split rule metal/attention.rs:394-413).
+Weights are dequantised once to f32 with w = (q - z) * s from the fp16 scale / zero point the GPU sees;
+dot products accumulate in f32.
+
+Rounding points of one token (token_count == 1, INT4 weights):
+  embedding -> hidden f16, norm_out f16; layer 0: Q, K, V = matvec(norm_out f16) -> f16;
+  layers >= 1: K, V = matvec(norm_out f16); Q comes from the previous layer's fused
+  residual + norm + projection kernel, which multiplies the UNROUNDED f32 normalised vector;
+  (QK-norm,) RoPE in place -> f16; cache write; attention (split in chunks of ceil(seq / splits) once the
+  sequence holds 256 positions, each split rotating its partial back) -> f16; o -> f16;
+  fused residual + norm -> residual f16, norm_out f16; gate/up read norm_out f16, their f32 dot products feed
+  SiLU(g) * u -> f16; down -> f16; residual + down -> hidden f16 (+ norm_out f16, next Q).
+token_count > 1 (prefill): every projection runs the matmul form f16(sum f16(x / awq) * f16((q - z) s)), gate and up
+are rounded to f16 before SiLU(g) * u, no projection is fused into a norm, attention is a single pass per token.
+INT8 weights never take the fused kernels (they exist for 4 bits only)."""
 import numpy as np
 
 from oracle import oracle as orc
@@ -87,17 +101,31 @@ def _deq(t):
 
 
 class OracleModel:
-    def __init__(self, cfg, tensors, tqc, max_seq, flip_rate=0.0):
+    """deviations: names of departures from the reference's rounding points, used to measure what each one costs
+    (every one of them is a legitimate "same arithmetic contract" choice an implementation could make):
+      kv_unrounded   K and V of layers >= 1 from the unrounded normalised vector (like Q)
+      ffn_unrounded  gate/up from the unrounded normalised vector
+      no_split       decode attention in a single pass whatever the length (one rotation back instead of one per split)
+      act_q16        projection inputs rounded to 16-bit integers per group of 128 (scale amax / 32639)
+      act_q24        the same with 24-bit integers (scale amax / 8355711)
+      sum_order      dot products summed as two halves of K (another f32 summation order)
+      prefill_matvec prefill projections in the matvec form (no f16 rounding of x / awq and of the weights)"""
+
+    def __init__(self, cfg, tensors, tqc, max_seq, flip_rate=0.0, deviations=()):
         """flip_rate > 0 flips the lowest fp16 bit of that fraction of the activations entering every layer:
         a stand-in for "another correct implementation" used to measure how far last-bit differences grow."""
         self.cfg, self.tq, self.max_seq = cfg, tqc, max_seq
         self.flip_rate, self._flip_rng = flip_rate, np.random.default_rng(12345)
+        self.dev = frozenset(deviations)
+        unknown = self.dev - {"kv_unrounded", "ffn_unrounded", "no_split", "act_q16", "act_q24", "sum_order", "prefill_matvec"}
+        assert not unknown, unknown
         g = lambda n: tensors[n].data.astype(np.float16)  # noqa: E731
         self.embed = g("model.embed_tokens.weight")
         self.lm = (self.embed if cfg.tie_word_embeddings else g("lm_head.weight")).astype(np.float32)
         self.final_norm = g("model.norm.weight")
         self.L = []
-        nkv, hd = cfg.num_key_value_heads, cfg.head_dim
+        nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        self.bits = tensors["model.layers.0.self_attn.q_proj.weight"].bit_width
         for i in range(cfg.num_hidden_layers):
             p = f"model.layers.{i}"
             d = {"in_ln": g(f"{p}.input_layernorm.weight"), "post_ln": g(f"{p}.post_attention_layernorm.weight")}
@@ -113,6 +141,7 @@ class OracleModel:
             d["vc"] = np.zeros((nkv, max_seq, hd), np.uint8)
             d["ks"], d["vs"], d["kr"] = (np.zeros((nkv, max_seq), np.float32) for _ in range(3))
             self.L.append(d)
+        self._w16 = {}
         self.cos, self.sin = orc.rope_table(hd, max_seq, cfg.rope_theta, cfg.extra.get("rotary_dim"))
         self.pos = 0
 
@@ -121,25 +150,65 @@ class OracleModel:
         v[self._flip_rng.random(v.shape) < self.flip_rate] ^= 1
         return v.view(np.float16)
 
-    @staticmethod
-    def _mv(w, awq, x16):
+    # ---- projections ------------------------------------------------------------------------------------------
+    def _round_act(self, x):
+        """The act_q16 / act_q24 deviations: x [T, K] f32 -> the values a block-integer staging would multiply."""
+        top = 32639.0 if "act_q16" in self.dev else 8355711.0 if "act_q24" in self.dev else None
+        if top is None or x.shape[-1] % 128:
+            return x
+        xg = x.reshape(x.shape[0], -1, 128)
+        amax = np.abs(xg).max(-1, keepdims=True)
+        safe = np.where(amax > 0, amax, np.float32(1.0))
+        xi = np.clip(np.rint(xg * (np.float32(top) / safe)), -top, top).astype(np.float32)
+        return (xi * (safe * np.float32(1.0 / top))).reshape(x.shape).astype(np.float32)
+
+    def _dot(self, x, w):
+        if "sum_order" in self.dev:
+            h = w.shape[1] // 2
+            return x[:, :h] @ w[:, :h].T + x[:, h:] @ w[:, h:].T
+        return x @ w.T
+
+    def _mv32(self, w, awq, x32):
+        """Matvec form on an f32 input: f32(x) / f32(awq) against f32 (q - z) s, f32 result (not yet rounded)."""
+        x = x32 if awq is None else x32 / awq
+        return self._dot(self._round_act(x.astype(np.float32)), w)
+
+    def _mv(self, w, awq, x16):
+        return self._mv32(w, awq, x16.astype(np.float32)).astype(np.float16)
+
+    def _mm(self, key, w, awq, x16):
+        """Matmul form (affine_matmul.metal:44-74,119-127): both operands rounded to f16, f32 accumulation."""
+        if "prefill_matvec" in self.dev:
+            return self._mv(w, awq, x16)
+        if key not in self._w16:
+            self._w16[key] = w.astype(np.float16).astype(np.float32)
         x = x16.astype(np.float32)
         if awq is not None:
-            x = x / awq
-        return (x @ w.T).astype(np.float16)
+            x = (x / awq).astype(np.float16).astype(np.float32)
+        return self._dot(x, self._w16[key]).astype(np.float16)
+
+    def _proj(self, li, name, w, awq, x16, decode):
+        return self._mv(w, awq, x16) if decode else self._mm((li, name), w, awq, x16)
 
     def forward(self, tokens):
         """tokens: T ids appended at the current position; returns f32 logits of the last one."""
         c, T = self.cfg, len(tokens)
         nh, nkv, hd, eps = c.num_attention_heads, c.num_key_value_heads, c.head_dim, np.float32(c.rms_norm_eps)
+        decode = T == 1
+        fused = decode and self.bits == 4          # the fused kernels exist for 4-bit weights and one token only
         norm_out, hidden = orc.embedding_norm(np.asarray(tokens, np.uint32), self.embed, self.L[0]["in_ln"], float(eps))
-        qkv = None
+        pre = None  # (q or qkv) computed by the previous layer's fused residual + norm + projection
         for li, d in enumerate(self.L):
-            if li == 0:
-                qkv = self._mv(d["qkv"], d["qkv_awq"], norm_out)
+            nq = nh * hd
+            if pre is not None and pre.shape[1] == d["qkv"].shape[0]:
+                qkv = pre
+            else:
+                qkv = self._proj(li, "qkv", d["qkv"], d["qkv_awq"], norm_out, decode)
+                if pre is not None:
+                    qkv = np.concatenate([pre, qkv[:, nq:]], 1)
             if self.flip_rate:
                 qkv, hidden = self._flip(qkv), self._flip(hidden)
-            q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+            q, k, v = qkv[:, :nq], qkv[:, nq:nq + nkv * hd], qkv[:, nq + nkv * hd:]
             if c.has_qk_norm:
                 q, k = orc.qk_norm_rope(q, k, d["qn"], d["kn"], self.cos, self.sin, nh, nkv, hd, self.pos, float(eps))
             else:
@@ -147,28 +216,39 @@ class OracleModel:
                 k = orc.rope(k, self.cos, self.sin, nkv, hd, self.pos)
             orc.tq_encode(k, self.tq, True, d["kc"], d["ks"], d["kr"], nkv, self.max_seq, self.pos)
             orc.tq_encode(np.ascontiguousarray(v), self.tq, False, d["vc"], d["vs"], None, nkv, self.max_seq, self.pos)
+            seq = self.pos + T
+            splits = 0
+            if decode and seq >= 256 and "no_split" not in self.dev:
+                splits = max(2, min(-(-seq // 256), 256))
             attn = orc.tq_attention(q, d["kc"], d["vc"], self.tq, d["ks"], d["vs"], d["kr"], c.attn_scale, nh, nkv,
-                                    self.max_seq, self.pos).reshape(T, nh * hd)
-            o = self._mv(d["o"], d["o_awq"], attn)
+                                    self.max_seq, self.pos, num_splits=splits).reshape(T, nh * hd)
+            o = self._proj(li, "o", d["o"], d["o_awq"], attn, decode)
             norm_out, residual = orc.fused_residual_rms_norm(hidden, o, d["post_ln"], float(eps))
-            x = norm_out.astype(np.float32)
-            if d["ffn_awq"] is not None:
-                x = x / d["ffn_awq"]
-            gt, up = x @ d["gate"].T, x @ d["up"].T
-            act = (gt / (np.float32(1.0) + np.exp(-gt))) * up
-            ffn = act.astype(np.float16)
-            down = self._mv(d["down"], d["down_awq"], ffn)
+            if fused:
+                if "ffn_unrounded" in self.dev:
+                    r = hidden.astype(np.float32) + o.astype(np.float32)
+                    ri = (np.float32(1.0) / np.sqrt((r * r).sum(-1, keepdims=True, dtype=np.float32) / np.float32(r.shape[-1]) + eps)).astype(np.float32)
+                    xg = r * d["post_ln"].astype(np.float32)
+                    gt, up = self._mv32(d["gate"], d["ffn_awq"], xg) * ri, self._mv32(d["up"], d["ffn_awq"], xg) * ri
+                else:
+                    x = norm_out.astype(np.float32)
+                    gt, up = self._mv32(d["gate"], d["ffn_awq"], x), self._mv32(d["up"], d["ffn_awq"], x)
+            else:
+                gt = self._proj(li, "gate", d["gate"], d["ffn_awq"], norm_out, decode).astype(np.float32)
+                up = self._proj(li, "up", d["up"], d["ffn_awq"], norm_out, decode).astype(np.float32)
+            ffn = ((gt / (np.float32(1.0) + np.exp(-gt))) * up).astype(np.float16)
+            down = self._proj(li, "down", d["down"], d["down_awq"], ffn, decode)
             r = residual.astype(np.float32) + down.astype(np.float32)
             hidden = r.astype(np.float16)
+            pre = None
             if li + 1 < len(self.L):
                 nx = self.L[li + 1]
                 rms_inv = (np.float32(1.0) / np.sqrt((r * r).sum(-1, keepdims=True, dtype=np.float32) / np.float32(r.shape[-1]) + eps)).astype(np.float32)
                 gam = nx["in_ln"].astype(np.float32)
                 norm_out = (r * rms_inv * gam).astype(np.float16)
-                xn = r * gam
-                if nx["qkv_awq"] is not None:
-                    xn = xn / nx["qkv_awq"]
-                qkv = ((xn @ nx["qkv"].T) * rms_inv).astype(np.float16)
+                if fused:
+                    rows = nx["qkv"].shape[0] if "kv_unrounded" in self.dev else nh * hd
+                    pre = (self._mv32(nx["qkv"][:rows], nx["qkv_awq"], r * gam) * rms_inv).astype(np.float16)
         last = orc.rms_norm(hidden[-1:], self.final_norm, float(eps))
         logits = (last.astype(np.float32) @ self.lm.T).astype(np.float16).astype(np.float32)
         self.pos += T

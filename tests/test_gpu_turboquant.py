@@ -146,6 +146,41 @@ def test_attention_full_context_property(tq, tqc):
         assert float((out[h] - ref).abs().max()) <= 2e-3 * float(ref.abs().max()) + 1e-3
 
 
+@pytest.mark.parametrize("ctx,nseq,nh,nkv", [(8192, 8, 32, 8), (1024, 32, 32, 8), (32768, 1, 4, 1), (131072, 1, 4, 1)])
+def test_decode_attention_long_context_and_batches_against_the_oracle(tq, tqc, ctx, nseq, nh, nkv):
+    """The attention benchmark's contexts and batches against the CPU oracle (single pass): 8k x batch 8 and 1k x batch 32
+    with 32 query / 8 KV heads; 32k and 128k for one KV head's four query heads (the oracle is O(context) per head)."""
+    max_seq = ctx
+    kc, ks, kr, vc, vs = _fill_cache(tq, tqc, nkv, max_seq, ctx, seed=ctx % 1000 + nseq, nseq=nseq)
+    q = H.make_x(nseq, nh * 128, seed=ctx % 977, name="q")
+    scale = 1.0 / np.sqrt(128.0)
+    out = tq.attention(_c(q), kc, vc, ks, vs, kr, scale, nh, nkv, max_seq, ctx - 1, nseq=nseq).cpu().numpy().reshape(nseq, nh, 128)
+    kcn, vcn, ksn, vsn, krn = (a.cpu().numpy() for a in (kc, vc, ks, vs, kr))
+    worst = 0.0
+    for s in range(nseq):
+        ref = orc.tq_attention(q[s:s + 1], kcn[s], vcn[s], tqc, ksn[s], vsn[s], krn[s], scale, nh, nkv, max_seq, ctx - 1, num_splits=0)
+        worst = max(worst, H.rel_err(out[s], ref.reshape(nh, 128)))
+    print(f"ctx {ctx} x {nseq} sequences: max error {worst:.2e} of the largest output")
+    assert worst <= 2e-3, worst
+
+
+def test_device_side_position_past_the_cache_is_clamped(tq, tqc):
+    """Positions can live in device memory (decode graphs): a value the host never saw must not make the kernels read
+    past a head's rows.  Position max_seq - 1 with two tokens: the second token's length is clamped to max_seq."""
+    nh, nkv, max_seq = 8, 2, 64
+    kc, ks, kr, vc, vs = _fill_cache(tq, tqc, nkv, max_seq, max_seq, seed=4)
+    q = H.make_x(2, nh * 128, seed=2, name="q")
+    pos = torch.tensor([max_seq - 1], dtype=torch.int32, device="cuda")
+    out = tq.attention(_c(q), kc, vc, ks, vs, kr, 0.0884, nh, nkv, max_seq, 0, pos_dev=pos).cpu().numpy().reshape(2, nh, 128)
+    ref = orc.tq_attention(q[0:1], kc[0].cpu().numpy(), vc[0].cpu().numpy(), tqc, ks[0].cpu().numpy(), vs[0].cpu().numpy(),
+                           kr[0].cpu().numpy(), 0.0884, nh, nkv, max_seq, max_seq - 1, num_splits=0)
+    # token 0 sees all max_seq positions; token 1 would see max_seq + 1 and is clamped to the same max_seq positions
+    q1 = orc.tq_attention(q[1:2], kc[0].cpu().numpy(), vc[0].cpu().numpy(), tqc, ks[0].cpu().numpy(), vs[0].cpu().numpy(),
+                          kr[0].cpu().numpy(), 0.0884, nh, nkv, max_seq, max_seq - 1, num_splits=0)
+    assert H.rel_err(out[0], ref.reshape(nh, 128)) <= 2e-3
+    assert np.isfinite(out).all() and H.rel_err(out[1], q1.reshape(nh, 128)) <= 2e-3
+
+
 def test_sequence_overflow_is_reported(tq):
     from ironmill_b200 import CudaSysError
     z8 = torch.zeros((1, 8, 16, 128), dtype=torch.uint8, device="cuda")
