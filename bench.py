@@ -42,10 +42,16 @@ GS = 128
 L8 = dict(architecture="llama", hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
           num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=8192, rms_norm_eps=1e-5,
           rope_theta=5e5, tie_word_embeddings=False)
+Q06 = dict(architecture="qwen3", hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
+           num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=8192, rms_norm_eps=1e-6,
+           rope_theta=1e6, tie_word_embeddings=False)
+MODELS = {"llama3_8b": (L8, True, "llama3_8b_shape_int4_g128_awq_tq8_decode"),      # (shape, AWQ scales, workload name)
+          "qwen3_0p6b": (Q06, False, "qwen3_0p6b_shape_int4_g128_tq8_decode")}
 # Llama-3-8B-shaped projections: (name, N, K, kind)
 L8_SHAPES = [("qkv", 6144, 4096, "plain"), ("o", 4096, 4096, "plain"),
              ("gate_up", 14336, 4096, "ffn"), ("down", 4096, 14336, "plain")]
 METRIC_DECODE = "decode tok/s (Llama-3-8B shape, INT4 g128 + AWQ weights, INT8 TurboQuant KV)"
+METRIC_DECODE_Q = "decode tok/s (Qwen3-0.6B shape, INT4 g128 weights, INT8 TurboQuant KV)"
 METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes, batch 1)"
 METRIC_ATTN = "TurboQuant INT8-KV decode attention HBM GB/s (32 Q / 8 KV heads, head_dim 128)"
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
@@ -117,7 +123,15 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s, no MEASURED_PEAKS.json beside this file)"
+
+
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s (burst) of the roofline: the cuBLAS figure in MEASURED_PEAKS.json, else 1590."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path)).get("bf16_tflops", 1590.0))
+    return 1590.0
 
 
 # ----------------------------------------------------------------------------- synthetic weights on the GPU
@@ -152,8 +166,8 @@ class SyntheticL8Provider:
     generator on the GPU, quantized by the library's GPU quantizer (bit-exact with the reference's CPU
     quantizer) and handed over as host arrays, like a bundle provider would."""
 
-    def __init__(self, cfg, dev, seed=1234):
-        self.cfg, self.dev, self.seed = cfg, dev, seed
+    def __init__(self, cfg, dev, seed=1234, awq=True):
+        self.cfg, self.dev, self.seed, self.awq = cfg, dev, seed, awq
 
     def config(self):
         return self.cfg
@@ -183,9 +197,10 @@ class SyntheticL8Provider:
         N, K, grp = shapes[key]
         layer = name.split(".")[2]
         ga = torch.Generator(device="cuda").manual_seed(self.seed * 104729 + zlib.crc32(f"{layer}.{grp}".encode()))
-        awq = (torch.rand(K, generator=ga, device="cuda") * 1.5 + 0.5).half()   # shared by projections with one input
+        awq = (torch.rand(K, generator=ga, device="cuda") * 1.5 + 0.5).half() if self.awq else None   # shared by projections with one input
         packed, s, z = gpu_quantized(self.dev, N, K, g, awq)
-        return WeightTensor(packed.cpu().numpy(), (N, K), "uint8", s.cpu().numpy(), z.cpu().numpy(), 4, GS, 1, awq.cpu().numpy())
+        return WeightTensor(packed.cpu().numpy(), (N, K), "uint8", s.cpu().numpy(), z.cpu().numpy(), 4, GS, 1,
+                            None if awq is None else awq.cpu().numpy())
 
 
 def time_dominant_kernel(dev, reps=5):
@@ -241,13 +256,14 @@ def run_decode(args, rank, world):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     dev = ops.Device(local)
-    cfg = ModelConfig(**dict(L8, num_hidden_layers=args.layers))
+    shape, with_awq, workload = MODELS[args.model]
+    cfg = ModelConfig(**dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"]))
     B, P, K, W = args.batch, args.prompt, args.steps, max(args.warmup, 3)
     e2e_steps = max(8, min(K, 64))
     max_seq = P + W + K + e2e_steps + 8
     eng = CudaInference(CudaConfig(max_seq_len=max_seq, max_batch=B, tp_world=world, tp_rank=rank, device=local))
     t0 = time.perf_counter()
-    eng.load_weights(SyntheticL8Provider(cfg, dev))
+    eng.load_weights(SyntheticL8Provider(cfg, dev, awq=with_awq))
     if world > 1:
         ids = [CudaInference.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
@@ -258,10 +274,12 @@ def run_decode(args, rank, world):
     logits = eng.prefill(prompt)
     prefill_s = time.perf_counter() - t0
     first = np.full(B, int(logits.argmax()), dtype=np.uint32)
-    if B > 1:   # lockstep batch: every sequence needs the prompt in its cache; replicate by decoding it again per step
+    if B > 1:   # every sequence of the batch gets the whole prompt in its own cache slot
         eng.reset()
-        for t in prompt[:min(P, 64)]:
-            eng.decode_step(np.full(B, t, dtype=np.uint32))
+        t0 = time.perf_counter()
+        for _ in range(B):
+            eng.add_sequence(prompt)
+        prefill_s = (time.perf_counter() - t0) / B
     toks, _ = eng.decode_greedy(first, W)
     sampler = ClockSampler(local)
     if rank == 0:
@@ -298,7 +316,7 @@ def run_decode(args, rank, world):
     launches = eng.step_launches()
     # dominant kernel: the whole-token decode kernel when the engine uses it (batch 1, one GPU), else the largest projection launch
     tk = eng.token_kernel_profile(8) if (B == 1 and eng.token_kernel()) else None   # every rank: the kernels of a tensor-parallel model wait on one another
-    dom_us, dom_bytes, _ = time_dominant_kernel(dev) if rank == 0 else (1.0, 0, 0)
+    dom_us, dom_bytes, _ = time_dominant_kernel(dev) if (rank == 0 and args.model == "llama3_8b") else (1.0, 0, 0)
     if rank != 0:
         return
     peak, peak_src = measured_peaks()
@@ -321,26 +339,27 @@ def run_decode(args, rank, world):
                                  if world == 1 else "no ncu capture of the tensor-parallel kernel (a multi-rank command is never profiled)"),
                 "timing": "CUDA events around 8 back-to-back launches on the engine's stream; every launch streams all weights (> L2)",
                 "phase_us_per_layer": {k: round(v, 2) for k, v in phases.items()},
-                "largest_projection_alone": proj}
-    else:
+                "largest_projection_alone": proj if args.model == "llama3_8b" else None}
+    elif args.model == "llama3_8b":
         roof = dict(proj, bound="hbm", peak=peak, unit="GB/s", peak_source=peak_src, traffic=PROJ_DRAM_BYTES,
                     traffic_note="dram read+write of this launch from the ncu capture under profiles/")
+    else:
+        roof = {"bound": "hbm", "kernel": "whole step (graph of per-projection kernels)", "achieved": round(step_gbs, 1), "peak": peak,
+                "unit": "GB/s", "frac": round(step_gbs / peak, 4), "peak_source": peak_src, "traffic": None}
     roof["whole_step"] = {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_gbs, 1),
                           "frac_of_hbm_roofline": round(step_gbs / peak, 4),
                           "roofline_tok_s": round(B * peak * 1e9 / step_bytes, 1)}
     out = {
-        "metric": METRIC_DECODE, "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "metric": METRIC_DECODE if args.model == "llama3_8b" else METRIC_DECODE_Q, "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u4 codes x i16 activations (f32 fix-up), f16 lm_head, u8 KV codebook indices",
         "data": "synthetic",
-        "config": {"workload": "llama3_8b_shape_int4_g128_awq_tq8_decode", "batch": B, "prompt_tokens": P,
-                   "context_during_timing": [ctx0, ctx0 + K], "layers": cfg.num_hidden_layers, "hidden": 4096, "ffn": 14336, "vocab": 128256,
-                   "parallelism": f"tp{world}" if world > 1 else "single",
-                   "allreduce": (("inside the whole-token kernel: partial sums stored to every rank's mailbox over NVLink with tags, summed by the consuming phase, no barrier"
-                                  if (B == 1 and eng.token_kernel()) else "one-shot peer-memory kernel")
-                                 if eng.tp_peer_allreduce() else "nccl") if world > 1 else None,
-                   "l2_policy": "inputs larger than L2: every step streams this rank's %.2f GB of weights + KV" % (step_bytes / 1e9),
-                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2)},
+        "config": decode_config(workload, cfg, B, P, world),
+        "run": {"context_during_timing": [ctx0, ctx0 + K],
+                "allreduce": (("inside the whole-token kernel: partial sums stored to every rank's mailbox over NVLink with tags, summed by the consuming phase, no barrier"
+                               if (B == 1 and eng.token_kernel()) else "one-shot peer-memory kernel")
+                              if eng.tp_peer_allreduce() else "nccl") if world > 1 else None,
+                "bytes_per_step_per_gpu": step_bytes, "load_s": round(load_s, 1), "prefill_s_per_sequence": round(prefill_s, 3)},
         "roofline": roof,
         "e2e": {"value": round(B * e2e_steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 2 * B * cfg.vocab_size, "steps": e2e_steps,
@@ -353,11 +372,83 @@ def run_decode(args, rank, world):
         "clocks": clocks,
     }
     if world == 1:
-        out["cpu_baseline"] = cpu_decode_baseline(quick=True)
+        out["cpu_baseline"] = cpu_decode_baseline(args.model, B, P, budget_s=20.0, min_steps=3)
     print(json.dumps(out))
 
 
+def decode_config(workload, cfg, B, P, world):
+    """The workload as both arms name it (the same keys and values in the GPU arm and in --impl reference)."""
+    return {"workload": workload, "batch": B, "prompt_tokens": P, "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+            "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size, "parallelism": f"tp{world}" if world > 1 else "single",
+            "l2_policy": "inputs larger than L2: every step streams all of the rank's weights and its KV cache"}
+
+
+def time_projection(dev, N, K, kind, B, bits, awq_on=True, reps=4):
+    """Microseconds per launch of one projection at batch B (CUDA events around a CUDA graph that rotates over enough
+    weight copies to exceed L2): batch <= 4 runs the matvec kernels (one launch), batch >= 16 the tcgen05 GEMM (gate and
+    up as two GEMMs + the SiLU kernel).  Returns (us, algorithmic bytes, flops, launches per call)."""
+    import torch
+
+    from ironmill_b200 import ops
+    nmat = 2 if kind == "ffn" else 1
+    wbytes = nmat * (N * K * bits // 8 + 4 * N * (K // GS))
+    ncopy = max(3, min(96, int(170e6 // wbytes) + 1))
+    g = torch.Generator(device="cuda").manual_seed(N + K + B)
+    awq = (torch.rand(K, generator=g, device="cuda") * 1.5 + 0.5).half() if awq_on else None
+    copies = []
+    for _ in range(ncopy):
+        mats = []
+        for _ in range(nmat):
+            w = (torch.randn((N, K), generator=g, device="cuda") * 0.02).half()
+            packed, sc, zp = ops.quantize_affine(w, GS, bits, awq)
+            mats.append(ops.AffineWeight(dev, packed, sc, zp, N, K, GS, bits, awq=awq))
+        copies.append(mats)
+    x = torch.randn((B, K), generator=g, device="cuda").half()
+    y = torch.empty((B, N), dtype=torch.float16, device="cuda")
+    y2 = torch.empty((B, N), dtype=torch.float16, device="cuda")
+    scratch = torch.empty((B, K), dtype=torch.float16, device="cuda")
+    gemm = B >= 16 and bits == 4
+
+    def call(i):
+        m = copies[i % ncopy]
+        if gemm:
+            ops.matmul_affine(m[0], x, out=y, scratch=scratch)
+            if kind == "ffn":
+                ops.matmul_affine(m[1], x, out=y2, scratch=scratch)
+                ops.silu_mul(y, y2, out=y)
+        elif kind == "ffn":
+            ops.ffn_gate_up_act(m[0], m[1], x, out=y)
+        else:
+            ops.matvec_affine(m[0], x, out=y)
+
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for i in range(min(ncopy, 3)):
+            call(i)
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            for i in range(ncopy):
+                call(i)
+        graph.replay()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(st)
+        st.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * ncopy)
+    nbytes = wbytes + B * K * 2 + B * N * 2 + (K * 2 if awq_on else 0)
+    del copies
+    torch.cuda.empty_cache()
+    return us, nbytes, 2.0 * nmat * B * N * K
+
+
 def run_matvec(args, rank, world):
+    """The single-kernel sweep: headline = the four INT4 g128 projection launches of one decoder layer at batch 1; `sweep`
+    lists every projection shape at batch 1 / 4 / 16 / 64, the shards a rank holds under 2 / 4 / 8-way tensor
+    parallelism (column split N / G for QKV and gate+up, row split K / G for o and down) and the INT8 form."""
     import torch
 
     from ironmill_b200 import ops
@@ -411,8 +502,27 @@ def run_matvec(args, rank, world):
         for name, N, K, kind in plain:
             ops.matvec_affine_host(copies[i % ncopies][name][0], xh[K])
     e2e_s = time.perf_counter() - w0
+    del copies
+    torch.cuda.empty_cache()
     dom_us, dom_bytes, _ = time_dominant_kernel(dev)
     peak, peak_src = measured_peaks()
+    tpeak = measured_tensor_peak()
+    sweep = []
+    cases = [(n, N, K, kind, B, 4, 1) for n, N, K, kind in L8_SHAPES for B in (1, 4, 16, 64)]
+    cases += [(n, N, K, kind, 1, 8, 1) for n, N, K, kind in L8_SHAPES]
+    for G in (2, 4, 8):   # what one of G ranks holds
+        cases += [(n, N // G if n in ("qkv", "gate_up") else N, K if n in ("qkv", "gate_up") else K // G, kind, 1, 4, G) for n, N, K, kind in L8_SHAPES]
+    if not args.sweep:
+        cases = []
+    for n, N, K, kind, B, bits, G in cases:
+        us, nb, fl = time_projection(dev, N, K, kind, B, bits)
+        row = {"shape": n, "N": N, "K": K, "batch": B, "bits": bits, "tp_shard_of": G, "us": round(us, 2),
+               "GBps": round(nb / us / 1e3, 1), "frac_hbm": round(nb / us / 1e3 / peak, 3)}
+        if B >= 16 and bits == 4:
+            row["TFLOPs"] = round(fl / us / 1e6, 1)
+            row["frac_tensor"] = round(fl / us / 1e6 / tpeak, 4)
+            row["kernel"] = "gemm_int4_tc_kernel (tcgen05)"
+        sweep.append(row)
     out = {"metric": METRIC_MATVEC, "value": round(step_bytes * steps / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": 1,
            "steps": steps, "warmup": args.warmup, "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "u4 codes x i16 activations, f32 fix-up", "data": "synthetic",
@@ -424,7 +534,7 @@ def run_matvec(args, rank, world):
                         "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_us, 3)},
            "e2e": {"value": round(sum(shape_bytes(*sh) for sh in plain) * 20 / e2e_s / 1e9, 3), "unit": "GB/s",
                    "h2d_bytes_per_step": sum(K * 2 for _, N, K, _ in plain), "d2h_bytes_per_step": sum(N * 2 for _, N, K, _ in plain)},
-           "gpu_launches": 4 * steps, "clocks": clocks, "cpu_baseline": cpu_matvec_baseline(3.0)}
+           "gpu_launches": 4 * steps, "clocks": clocks, "sweep": sweep, "cpu_baseline": cpu_matvec_baseline(3.0)}
     print(json.dumps(out))
 
 
@@ -528,46 +638,85 @@ def cpu_matvec_baseline(seconds):
             "quantize_ms": round(tq * 1e3, 1), "matvec_ms": round(tm * 1e3, 3)}
 
 
-def cpu_decode_baseline(quick):
-    """The CPU restatement of the reference's CPU path (affine quantize + dequantised matvec), timed on the host
-    cores on a bounded sample of one decode token: ONE Llama-3-8B-shaped layer (QKV, o, gate+up+SiLU, down at batch 1)
-    plus 1/16 of the fp16 lm_head rows; a token is 32 such layers + the whole lm_head."""
+def cpu_decode_baseline(model, B, P, budget_s, min_steps):
+    """The CPU restatement of the reference's path (the oracle, OpenMP on every core this process may use) running REAL
+    decode tokens of the named model at context P, batch 1 per token: per layer the fused QKV matvec, RoPE (with QK-norm
+    where the model has it), the TurboQuant write of K and V, TurboQuant attention over P cached positions, o,
+    residual + RMSNorm, gate/up + SiLU, down, residual add; then the final norm, the whole fp16 lm_head and the greedy
+    pick.  Bounded sample: the token runs all its layers over `sets` distinct sets of layer weights taken in turn
+    (every set is far larger than the CPU caches), caches hold random codes, and as many whole tokens are timed as fit
+    the budget (at least min_steps)."""
     from oracle import oracle as orc
+    shape, with_awq, _ = MODELS[model]
+    Hd, I, hd, nh, nkv, L, V = (shape[k] for k in ("hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
+                                                    "num_key_value_heads", "num_hidden_layers", "vocab_size"))
     threads = host_threads(orc)
     rng = np.random.default_rng(0)
-    mats = {}
+    sets, nsets = [], 2
+    max_seq = P + 64
     tq0 = time.perf_counter()
-    for name, N, K, kind in L8_SHAPES:
-        for j in range(2 if kind == "ffn" else 1):
-            w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
-            awq = rng.uniform(0.5, 2.0, K).astype(np.float16)
+    tqc = orc.TqConstants(hd, 8, seed=42)
+    for _ in range(nsets):
+        d = {}
+        for name, N, K in (("qkv", (nh + 2 * nkv) * hd, Hd), ("o", Hd, nh * hd), ("gate", I, Hd), ("up", I, Hd), ("down", Hd, I)):
+            w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02).astype(np.float16)
+            awq = rng.uniform(0.5, 2.0, K).astype(np.float16) if with_awq else None
             codes, sc, zp = orc.quantize_groups(w, GS, 4, awq=awq, threads=threads)
-            mats[(name, j)] = (orc.pack_int4(codes), orc.f32_to_f16(sc), orc.f32_to_f16(zp), awq)
+            d[name] = (orc.pack_int4(codes), orc.f32_to_f16(sc), orc.f32_to_f16(zp), awq, N, K)
+        d["kc"] = rng.integers(0, 256, (nkv, max_seq, hd), dtype=np.uint8)
+        d["vc"] = rng.integers(0, 256, (nkv, max_seq, hd), dtype=np.uint8)
+        d["ks"], d["vs"] = (rng.random((nkv, max_seq), dtype=np.float32) + 0.5 for _ in range(2))
+        d["kr"] = rng.random((nkv, max_seq), dtype=np.float32) * 0.1
+        d["g1"], d["g2"] = np.ones(Hd, np.float16), np.ones(Hd, np.float16)
+        d["qn"], d["kn"] = np.ones(hd, np.float16), np.ones(hd, np.float16)
+        sets.append(d)
     quant_s = time.perf_counter() - tq0
-    xs = {K: rng.standard_normal((1, K)).astype(np.float16) for K in (4096, 14336)}
-    lm_rows = 128256 // 16
-    lm = (rng.standard_normal((lm_rows, 4096)) * 0.02).astype(np.float16)
-    reps = 1 if quick else 3
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        for name, N, K, kind in L8_SHAPES:
-            if kind == "ffn":
-                g, u = mats[(name, 0)], mats[(name, 1)]
-                orc.ffn_gate_up_act(g[0], g[1], g[2], u[0], u[1], u[2], xs[K], N, K, GS, 4, awq=g[3], threads=threads)
+    lm = (rng.standard_normal((V, Hd), dtype=np.float32) * 0.02).astype(np.float16)
+    embed_row = (rng.standard_normal((1, Hd), dtype=np.float32) * 0.02).astype(np.float16)
+    cos, sin = orc.rope_table(hd, max_seq, shape["rope_theta"])
+    eps, scale = shape["rms_norm_eps"], 1.0 / np.sqrt(hd)
+    qk_norm = shape["architecture"] == "qwen3"
+
+    def mv(m, x):
+        return orc.matvec_affine(m[0], m[1], m[2], x, m[4], m[5], GS, 4, awq=m[3], threads=threads)
+
+    def token(pos):
+        hidden = embed_row
+        normed = orc.rms_norm(hidden, sets[0]["g1"], eps)
+        for l in range(L):
+            d = sets[l % nsets]
+            qkv = mv(d["qkv"], normed)
+            q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], np.ascontiguousarray(qkv[:, (nh + nkv) * hd:])
+            if qk_norm:
+                q, k = orc.qk_norm_rope(q, k, d["qn"], d["kn"], cos, sin, nh, nkv, hd, pos, eps)
             else:
-                m = mats[(name, 0)]
-                orc.matvec_affine(m[0], m[1], m[2], xs[K], N, K, GS, 4, awq=m[3], threads=threads)
-    layer_s = (time.perf_counter() - t0) / reps
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        orc.matvec_f16(lm, xs[4096], threads=threads)
-    lm_s = (time.perf_counter() - t0) / reps * 16
-    tok_s = 1.0 / (32 * layer_s + lm_s)
-    return {"value": round(tok_s, 4), "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"one layer's four projection calls ({layer_s * 1e3:.0f} ms) x32 + lm_head from 1/16 of its rows "
-                      f"({lm_s * 1e3:.0f} ms), batch 1, OpenMP {threads} threads, {reps} repetition(s); attention and norms "
-                      f"left out (under 1 % of the CPU time); quantize+pack of the layer took {quant_s:.1f} s",
-            "layer_ms": round(layer_s * 1e3, 1), "lm_head_ms": round(lm_s * 1e3, 1), "quantize_layer_s": round(quant_s, 2)}
+                q, k = orc.rope(q, cos, sin, nh, hd, pos), orc.rope(k, cos, sin, nkv, hd, pos)
+            orc.tq_encode(k, tqc, True, d["kc"], d["ks"], d["kr"], nkv, max_seq, pos)
+            orc.tq_encode(v, tqc, False, d["vc"], d["vs"], None, nkv, max_seq, pos)
+            attn = orc.tq_attention(q, d["kc"], d["vc"], tqc, d["ks"], d["vs"], d["kr"], scale, nh, nkv, max_seq, pos,
+                                    num_splits=max(2, min(-(-(pos + 1) // 256), 256)) if pos + 1 >= 256 else 0).reshape(1, nh * hd)
+            o = mv(d["o"], attn)
+            normed, resid = orc.fused_residual_rms_norm(hidden, o, d["g2"], eps)
+            g, u = d["gate"], d["up"]
+            act = orc.ffn_gate_up_act(g[0], g[1], g[2], u[0], u[1], u[2], normed, I, Hd, GS, 4, awq=g[3], threads=threads)
+            hidden = orc.residual_add(resid, mv(d["down"], act))
+            normed = orc.rms_norm(hidden, d["g1"], eps)
+        logits = orc.matvec_f16(lm, normed, threads=threads)
+        return orc.argmax(logits.astype(np.float32))
+
+    token(P)   # warm-up (page faults, OpenMP team)
+    times = []
+    while len(times) < min_steps or (sum(times) < budget_s and len(times) < 64):
+        t0 = time.perf_counter()
+        for b in range(B):
+            token(P + 1 + len(times) % 32)
+        times.append(time.perf_counter() - t0)
+    step_s = float(np.median(times))
+    return {"value": round(B / step_s, 4), "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{len(times)} whole decode step(s) of batch {B} at context {P} timed (median), every layer's projections, RoPE, TurboQuant write "
+                      f"and attention, norms, the full lm_head and the greedy pick; the {L} layers take {nsets} distinct weight sets in turn; "
+                      f"OpenMP {threads} threads; quantize+pack of the {nsets} sets took {quant_s:.1f} s",
+            "steps_timed": len(times), "ms_per_step": round(step_s * 1e3, 1), "quantize_s": round(quant_s, 2)}
 
 
 def host_threads(orc):
@@ -581,21 +730,34 @@ def host_threads(orc):
 
 
 def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU path as restated in oracle/ (kind "port": the reference itself is Rust + Metal
+    and cannot be built here), on the host cores of rank 0, on the same workload and config as the GPU arm.  `steps` is
+    the number of whole steps actually timed (bounded so that the run ends within a few minutes)."""
     if rank != 0:
         return
     t0 = time.perf_counter()
     if args.workload == "matvec":
         cb = cpu_matvec_baseline(8.0)
-        metric, unit, wl = METRIC_MATVEC, "GB/s", "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq"
-    else:
-        cb = cpu_decode_baseline(quick=False)
-        metric, unit, wl = METRIC_DECODE, "tok/s", "llama3_8b_shape_int4_g128_awq_tq8_decode"
-    out = {"impl": "reference", "metric": metric, "value": cb["value"], "unit": unit, "n_gpus": world, "steps": args.steps,
-           "warmup": args.warmup, "ms_per_step": round(1e3 / cb["value"], 2) if unit == "tok/s" else None,
+        out = {"impl": "reference", "metric": METRIC_MATVEC, "value": cb["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": cb["matvec_ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "f32", "data": "synthetic",
+               "config": {"workload": "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq", "shapes": [[n, N, K] for n, N, K, _ in L8_SHAPES]},
+               "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(out))
+        return
+    from ironmill_b200.bundle import ModelConfig
+    shape, _, workload = MODELS[args.model]
+    cfg = ModelConfig(**dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"]))
+    budget = 60.0 if args.steps >= 8 else 20.0
+    cb = cpu_decode_baseline(args.model, args.batch, args.prompt, budget_s=budget, min_steps=max(1, min(args.steps, 3)))
+    out = {"impl": "reference", "metric": METRIC_DECODE if args.model == "llama3_8b" else METRIC_DECODE_Q, "value": cb["value"],
+           "unit": "tok/s", "n_gpus": world, "steps": cb["steps_timed"], "warmup": 1, "ms_per_step": cb["ms_per_step"],
            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": wl, "batch": 1, "wall_s": round(time.perf_counter() - t0, 1)},
+           "config": decode_config(workload, cfg, args.batch, args.prompt, world),
+           "run": {"wall_s": round(time.perf_counter() - t0, 1), "steps_requested": args.steps,
+                   "note": "whole decode steps on the host cores of rank 0; the tensor-parallel layout does not apply to the CPU arm"},
            "cpu_baseline": cb,
-           "e2e": {"value": cb["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+           "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out))
 
 
@@ -608,7 +770,9 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "matvec", "attention"])
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the synthetic model (32 = the named workload; fewer only for profiler captures)")
+    ap.add_argument("--layers", type=int, default=0, help="decoder layers of the synthetic model (0 = the named model's; fewer only for profiler captures)")
+    ap.add_argument("--sweep", type=int, default=1, help="matvec workload: 1 = also time every shape at batch 1/4/16/64, INT8 and the tensor-parallel shards")
+    ap.add_argument("--model", default="llama3_8b", choices=sorted(MODELS), help="decode workload shape (the default is the headline configuration)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

@@ -190,7 +190,11 @@ int im_cuda_rope(void *qk_dev, const void *cos_dev, const void *sin_dev, int hea
  * uploaded to cos_dev / sin_dev [max_pos, head_dim/2].  rotary_dim 0 = head_dim. */
 int im_cuda_rope_table(int head_dim, int max_pos, double theta, int rotary_dim, void *cos_dev, void *sin_dev);
 
-/* ------------------------------------------------------------------ TurboQuant 8-bit KV cache
+/* silu_gate (crates/ironmill-inference/src/metal/shaders/activation/activation.metal:15): out = f16(SiLU(gate) * up)
+ * over n fp16 elements (n even), f32 inside; out may alias gate.  The prefill form of the FFN (metal/ffn.rs:58-150). */
+int im_cuda_silu_mul(const void *gate_dev, const void *up_dev, void *out_dev, size_t n, void *stream);
+
+/* ------------------------------------------------------------------ TurboQuant KV cache, 8 or 4 bits per element
  * Constants of MetalTurboQuantModel::new (crates/ironmill-inference/src/metal/turboquant/mod.rs:221-287):
  * rotation signs [hd] (+-1), QJL matrix [hd,hd] N(0,1), K codebook with 2^(bits-1) levels, V codebook with
  * 2^bits levels (lloyd_max_gaussian, crates/ironmill-inference/src/turboquant/codebook.rs:20-52). */
@@ -206,9 +210,10 @@ int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const float *sig
                       const float *v_bounds_host, im_tq **out);
 void im_cuda_tq_free(im_tq *tq);
 /* turboquant_cache_write (.../shaders/turboquant/turboquant.metal:52-170).  kv fp16 [nseq, T, nkv, hd];
- * cache u8 [nseq, nkv, max_seq, hd]; scale / r_norms f32 [nseq, nkv, max_seq]; write position of token t of
- * sequence s = (base_pos + pos_dev[s] + t) % max_seq (pos_dev may be NULL).  is_k selects the K form
- * (7-bit index | QJL sign, residual norm) or the V form (8-bit index). */
+ * cache u8 [nseq, nkv, max_seq, hd * n_bits / 8] (n_bits = 4: element 2i in the low nibble of byte i, 2i + 1 in the
+ * high one, .../src/shaders/turboquant_helpers.metal:24-77); scale / r_norms f32 [nseq, nkv, max_seq]; write position
+ * of token t of sequence s = (base_pos + pos_dev[s] + t) % max_seq (pos_dev may be NULL).  is_k selects the K form
+ * ((n_bits - 1)-bit index | QJL sign in the top bit, residual norm) or the V form (n_bits-bit index). */
 int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, void *cache_dev, float *scale_dev, float *r_norms_dev,
                       int nseq, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, void *stream);
 /* turboquant_attention in split mode + fused_sdpa_reduce (.../turboquant/turboquant.metal:202-462,
@@ -237,8 +242,10 @@ int im_cuda_tq_fused_attention(im_tq *tq, const void *qkv_dev, int qkv_stride, i
  * attention - an arena-owning server, a plugin whose host forbids allocation after start-up, code that runs between
  * another component's graph capture and replay.)  It allocates nothing and calls nothing that allocates: the split
  * partials go into a 4 MiB array inside the library image, which every GPU that loads the library keeps until the
- * process exits.  Same arguments and results as im_cuda_tq_attention.  Limits and rules:
- *  - nseq * T * nh * splits * 520 bytes must fit 4 MiB, otherwise IM_ERR_BOUNDS with the numbers in the message;
+ * process exits.  Same arguments, kernels and results as im_cuda_tq_attention.  Limits and rules:
+ *  - the split partials and the rotated queries, nseq * T * nh * (splits * 520 + 1024) bytes, must fit 4 MiB: with
+ *    num_splits = 0 the library lowers its own split count until they do, a count given by the caller is refused with
+ *    IM_ERR_BOUNDS and the numbers in the message;
  *  - the device of `tq` must be the current device;
  *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress); make that first call
  *    before any stream capture;
@@ -274,7 +281,7 @@ typedef struct im_model_config {
     int rotary_dim;           /* 0 = head_dim */
     int qk_norm;              /* 1: q_norm / k_norm weights present (Qwen3) */
     int tie_word_embeddings;  /* 1: lm_head = embedding table */
-    int tq_bits;              /* TurboQuant KV bits (0 = 8; only 8 is built) */
+    int tq_bits;              /* MetalConfig.n_bits: TurboQuant KV bits, 8 or 4 (0 = 8) */
     uint64_t rotation_seed;   /* MetalConfig.rotation_seed (default 42) */
     int tp_world, tp_rank;    /* tensor parallel group (0/0 = single GPU) */
     int prefill_chunk_size;   /* MetalConfig.prefill_chunk_size: tokens per prefill forward (0 = 256; at most 256) */
@@ -322,6 +329,17 @@ int im_cuda_model_decode_step(im_model *m, const uint32_t *tokens_host, int batc
  * [batch]; tokens_out_host u32 [n_steps, batch] (may be NULL); elapsed_ms_out = CUDA-event time of the loop. */
 int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tokens_host, int batch, int n_steps,
                                 uint32_t *tokens_out_host, float *elapsed_ms_out);
+/* BatchInferenceEngine (crates/ironmill-inference/src/engine.rs:121-131; the reference declares the trait and has no
+ * implementor): sequences that come and go, each in one of max_batch cache slots with its own position.
+ * seq_add prefills the prompt into a free slot and returns its id (logits_out_host, optional: f32 [vocab] of the last
+ * prompt token); seq_remove frees the slot; batch_decode_step appends tokens_host[i] to sequence seq_ids[i] for any
+ * subset of the live sequences, whatever their lengths, and returns f32 [n, vocab] in the same order.  The
+ * single-sequence calls above work on slot 0 and the lockstep form of decode_step on slots 0 .. batch - 1:
+ * use one interface or the other on a model.  im_cuda_model_reset frees every slot. */
+int im_cuda_model_seq_add(im_model *m, const uint32_t *tokens_host, int n_tokens, int *seq_id_out, float *logits_out_host);
+int im_cuda_model_seq_remove(im_model *m, int seq_id);
+int im_cuda_model_seq_position(const im_model *m, int seq_id);   /* tokens in the sequence's cache; -1: no such sequence */
+int im_cuda_model_batch_decode_step(im_model *m, const int *seq_ids, const uint32_t *tokens_host, int n, float *logits_out_host);
 int im_cuda_model_reset(im_model *m);
 int im_cuda_model_truncate(im_model *m, int pos);
 int im_cuda_model_seq_pos(const im_model *m);

@@ -129,6 +129,43 @@ def write_gpu_bundle(path: str, config: ModelConfig, tensors: dict, quantization
         json.dump(manifest, fh, indent=1)
 
 
+QUANTIZED_SUFFIXES = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+                      "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")
+
+
+def quantize_to_gpu_bundle(path: str, provider, bit_width: int = 4, group_size: int = 128, awq_scales: dict | None = None,
+                           min_elements: int = 0, device: int = 0) -> dict:
+    """The compile step of the reference (affine quantization pass + bundle writer,
+    crates/mil-rs/src/ir/passes/affine_quantize.rs:256-508, crates/ironmill-compile/src/weights/quantized.rs:852-1010,
+    crates/ironmill-compile/src/gpu/bundle.rs:52-356) with the quantizer running on the GPU: every linear projection of the
+    fp16 model behind `provider` is quantized and packed by the library's kernel (bit-exact with the reference's CPU
+    quantizer: same groups, f32 scale and zero point, low-nibble-first packing), everything else is written dense, and
+    the result is an ordinary `.ironml-gpu` directory.  awq_scales: optional {tensor name: fp16 [K]} per-input-channel
+    scales, applied as W * s before quantization and stored beside the tensor.  Returns the manifest.
+
+    No tile sidecar is written: the load-time repack into the kernels' tile stream is one pass of a GPU kernel over
+    weights that are already on the device, far cheaper than reading a second copy of them from disk."""
+    import torch
+
+    from . import ops
+    cfg: ModelConfig = provider.config()
+    out = {}
+    for name in provider.tensor_names():
+        t = provider.tensor(name)
+        quantize = (not t.quantized and name.endswith(QUANTIZED_SUFFIXES) and len(t.shape) == 2
+                    and int(np.prod(t.shape)) >= min_elements)
+        if not quantize:
+            out[name] = t
+            continue
+        N, K = t.shape
+        w = torch.from_numpy(np.ascontiguousarray(t.data, dtype=np.float16).reshape(N, K)).cuda(device)
+        awq = None if not awq_scales or name not in awq_scales else np.ascontiguousarray(awq_scales[name], dtype=np.float16)
+        packed, sc, zp = ops.quantize_affine(w, group_size, bit_width, None if awq is None else torch.from_numpy(awq).cuda(device))
+        out[name] = WeightTensor(packed.cpu().numpy(), (N, K), "uint8", sc.cpu().numpy(), zp.cpu().numpy(), bit_width, group_size, 1, awq)
+    write_gpu_bundle(path, cfg, out, {"method": "awq" if awq_scales else "affine", "n_bits": bit_width, "seed": 0, "min_elements": min_elements})
+    return json.load(open(os.path.join(path, "manifest.json")))
+
+
 class CudaBundleProvider:
     """WeightProvider over an `.ironml-gpu` directory: reads `manifest.json` up front and tensor files
     on demand (MetalBundleProvider, crates/ironmill-inference/src/metal/bundle.rs:22-92)."""

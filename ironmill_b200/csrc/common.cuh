@@ -210,6 +210,7 @@ struct TqPrep {
     int nh, nkv, rotary_dim, with_norm, T, nseq, max_seq, base_pos;
     float eps;
     const int *pos_dev;
+    const int *slot_map = nullptr;  // optional: sequence index -> cache slot
     float *qrot;    // out [nseq*T, nh, 2, hd]
     __half *q_out;  // optional out [nseq*T, nh, hd]
     uint8_t *kc, *vc;
@@ -218,7 +219,8 @@ struct TqPrep {
 int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st);
 int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,
                         const float *vs, const float *krn, float attn_scale, __half *out, int nseq, int nh, int nkv, int max_seq,
-                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot = nullptr);
+                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot = nullptr,
+                        const int *slot_map = nullptr);
 
 }  // namespace im
 

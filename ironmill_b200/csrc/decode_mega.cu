@@ -28,7 +28,20 @@ namespace im {
 
 namespace {
 
+// x / a for the AWQ scales: reciprocal, product and one Newton step on the remainder: the correctly rounded f32 quotient for
+// every operand that is not denormal (an IEEE division routine costs four times as much, 6 us per layer of staging time).
+__device__ __forceinline__ float div_awq(float x, float a) {
+    const float r = __frcp_rn(a);
+    const float q = x * r;
+    return fmaf(fmaf(-q, a, x), r, q);
+}
+
 constexpr int kGroups = kV2Consumers / 4;      // 128-thread groups of consumer warps
+// 16 consumer warps + the producer warp: five warps share one scheduler's register file, which caps the kernel at 96
+// registers per thread.  (Tried: a producer warp GROUP that hands registers to the consumers with setmaxnreg.  The pool
+// is what the CTA was launched with, 20 warps x 96, so the consumers reach 112 only if the producer drops to 24-32, and
+// a producer that small spills its whole stage walk: 97-101 us per layer against 84 without.)
+constexpr int kMegaThreads = kV2Threads;
 constexpr int kRedFloats = kV2Consumers * 16;  // per ring slot: 16 row sums from each consumer warp
 constexpr int kStageBytes = kStageTiles * kTileBytes;
 constexpr int kPhaseWords = sizeof(MegaPhase) / 4, kLayerWords = sizeof(MegaLayer) / 4;
@@ -103,41 +116,7 @@ __device__ __forceinline__ void mail_settle(const uint4 *src, uint4 &a, uint4 &c
     atomicExch(err, 2);
 }
 
-// ---- activation staging for one batch row (the NB = 1 case of matvec_v2.cu's v2_stage_x) ------------------
-// xq words: index ((grp*2 + col)*4 + t)*8 + j*2 + eo, col 0 = high bytes, 1 = low bytes; meta[grp] = (scale, sum).
-// resid_out (NORM only): a + b rounded to fp16; each 8-element chunk is written by one CTA of the grid, from the
-// registers that hold it anyway.
-// One 8-element chunk of a group (16 lanes per group): quantise to 16 bits, write the fragment words and the group's
-// (scale, sum).  v: the 8 values after norm weight and activation scale.
-__device__ __forceinline__ void stage_chunk(float (&v)[8], bool live, int grp, int hl, uint32_t *xq, float2 *meta) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    // 32639 = 127 * 256 + 127: both bytes of the split below stay inside a signed byte
-    const float sx = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f;
-    const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
-    int hi[8], lo[8], lsum = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        int xi = __float2int_rn(v[i] * inv);
-        xi = max(-32639, min(32639, xi));
-        lsum += xi;
-        hi[i] = (xi + 128) >> 8;
-        lo[i] = xi - hi[i] * 256;
-    }
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-    if (live) {
-        const int t = hl >> 2, j = hl & 3;
-        uint2 *dh = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 0) * 4 + t) * 4 + j) * 2);
-        uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 + 1) * 4 + t) * 4 + j) * 2);
-        *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
-        *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
-        if (hl == 0) meta[grp] = make_float2(sx * 0.0625f, (float)(lsum * 16));  // TileMath accumulates 16 x the integer dot product
-    }
-}
+// ---- activation staging for one batch row (stage_chunk24<1>, v2_device.cuh) ---------------------------------------
 __device__ __forceinline__ void unpack2(unsigned w, float &a, float &b) {  // two fp16 values of a word, no address taken
     a = __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
     b = __half2float(__ushort_as_half((unsigned short)(w >> 16)));
@@ -167,9 +146,9 @@ __device__ __forceinline__ void mega_stage_plain(const __half *__restrict__ x, c
             float a[8];
             unpack8(ra, a);
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __fdiv_rn(v[i], a[i]);  // f32(x) / f32(awq), as affine_matvec.metal:48-66
+            for (int i = 0; i < 8; i++) v[i] = div_awq(v[i], a[i]);  // f32(x) / f32(awq), as affine_matvec.metal:48-66
         }
-        stage_chunk(v, live, grp, hl, xq, meta);
+        stage_chunk24<1>(v, live, grp, 0, hl, xq, meta);
     }
 }
 
@@ -268,9 +247,9 @@ __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, c
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 v[i] = r[i] * fg[i];
-                if (awq) v[i] = __fdiv_rn(v[i], a[i]);
+                if (awq) v[i] = div_awq(v[i], a[i]);
             }
-            stage_chunk(v, live, grp, hl, xq_u, meta_u);
+            stage_chunk24<1>(v, live, grp, 0, hl, xq_u, meta_u);
         }
     }
     sq = warp_sum(sq);
@@ -300,9 +279,9 @@ __device__ __forceinline__ float mega_stage_norm(const __half *__restrict__ x, c
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 v[i] = __half2float(__float2half_rn(r[i] * ri * fg[i]));  // norm_out as the reference stores it
-                if (awq) v[i] = __fdiv_rn(v[i], a[i]);
+                if (awq) v[i] = div_awq(v[i], a[i]);
             }
-            stage_chunk(v, live, grp, hl, xq_r, meta_r);
+            stage_chunk24<1>(v, live, grp, 0, hl, xq_r, meta_r);
         }
     }
     return ri;
@@ -422,8 +401,9 @@ __device__ IM_MEGA_ITEM_INLINE void mega_reduce_head(const GroupScope &gs, int g
 
 // TP: the tensor-parallel variant (exchange of the row-split projections' partial sums between the ranks' kernels);
 // compiled apart so that the single-GPU kernel carries none of it.
-template <int GQ, bool TP>
-__global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaParams p) {
+// BITS: bits per cached element (8 or 4), a compile-time constant so that the cache-format branches of the shared bodies fold away.
+template <int GQ, bool TP, int BITS>
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const MegaParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int nring = p.nring;
     unsigned char *ring = smem;
@@ -456,7 +436,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         const uint32_t *src_ly = reinterpret_cast<const uint32_t *>(p.layers + l);
         for (int i = t; i < kLayerWords; i += nthreads) dst[5 * kPhaseWords + i] = src_ly[i];
     };
-    copy_desc(0, tid, kV2Threads);
+    copy_desc(0, tid, kMegaThreads);
 
     if (tid == 0) {
         for (int i = 0; i < nring; i++) {
@@ -466,8 +446,8 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (p.trace && blockIdx.x == 0) p.trace[0] = global_ns();
     }
-    for (int i = tid; i < 128 + 256; i += kV2Threads) {
-        cbk[i] = i < 128 ? p.k_cb[i] : p.v_cb[i - 128];
+    for (int i = tid; i < 128 + 256; i += kMegaThreads) {
+        cbk[i] = i < 128 ? (i < p.k_levels ? p.k_cb[i] : 0.0f) : (i - 128 < p.v_levels ? p.v_cb[i - 128] : 0.0f);
         bdk[i] = i < 128 ? (i < p.k_levels - 1 ? p.k_bd[i] : INFINITY) : (i - 128 < p.v_levels - 1 ? p.v_bd[i - 128] : INFINITY);
     }
     __syncthreads();
@@ -580,13 +560,13 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         }
     } else {
         // =========================================================== consumers
-        // staged activations: the primary set for projections of up to g_max groups, and a second set of g_norm groups
-        // for the QKV phases of layers >= 1, whose K and V rows read the fp16 norm_out while the Q rows read the
-        // unrounded vector (mega_stage_norm)
-        float2 *meta = reinterpret_cast<float2 *>(U);                                        // [g_max]
-        uint32_t *xq = reinterpret_cast<uint32_t *>(U + (((size_t)p.g_max * 8 + 15) & ~(size_t)15));  // [G][2][32] words
-        float2 *meta2 = reinterpret_cast<float2 *>(xq + (size_t)p.g_max * 64);                 // [g_norm]
-        uint32_t *xq2 = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(meta2) + (((size_t)p.g_norm * 8 + 15) & ~(size_t)15));
+        // staged activations of up to g_cap groups: two fix-up constants per group, then three byte planes of 32 words.
+        // The QKV phases of layers >= 1 stage a second set (their K and V rows read the fp16 norm_out while the Q rows read
+        // the unrounded vector, mega_stage_norm): it starts g_norm groups into the same arrays (g_cap >= 2 g_norm).
+        float2 *meta = reinterpret_cast<float2 *>(U);                                      // [g_cap][2]
+        uint32_t *xq = reinterpret_cast<uint32_t *>(U + (size_t)p.g_cap * 16);             // [g_cap][3][32] words
+        float2 *meta2 = meta + 2 * p.g_norm;
+        uint32_t *xq2 = xq + (size_t)p.g_norm * 96;
         const int group = warp >> 2;
         const GroupScope gs{tid & 127, 128, 2 + group};
         bool dead = false;
@@ -617,7 +597,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
         tm.reset();
 
         // One projection: stage the activations, then walk this CTA's stages of the phase.
-        auto matvec_phase = [&](int q, int fine) {  // fine >= 0: CTA 0 records 24 stamps at trace[fine..]
+        auto matvec_phase = [&](int q, int fine) __attribute__((always_inline)) {  // fine >= 0: CTA 0 records 24 stamps at trace[fine..]
             const MegaPhase ph = *reinterpret_cast<const MegaPhase *>(desc + ((q >> 2) & 1) * kDescWords + (q & 3) * kPhaseWords);
             const int G = ph.G;
             const bool stamp = p.trace && fine >= 0 && blockIdx.x == 0 && tid == 0;
@@ -669,11 +649,13 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 }
                 if (grp0 + n == G) {  // last stage of the row block: hand the partial sums to the producer warp
                     float *buf = red + slot * kRedFloats;
+                    float r0, r1;
+                    tm.row_sums(0, r0, r1);
                     if (t == 0) {
-                        buf[warp * 16 + g] = tm.acc0;
-                        buf[warp * 16 + g + 8] = tm.acc1;
+                        buf[warp * 16 + g] = r0;
+                        buf[warp * 16 + g + 8] = r1;
                     }
-                    tm.acc0 = tm.acc1 = 0.0f;
+                    tm.clear_sums();
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[slot]);
@@ -714,9 +696,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
                 a.qkv = p.qkv; a.stride = p.q_dim + 2 * p.kv_dim; a.k_off = p.q_dim; a.v_off = p.q_dim + p.kv_dim; a.kv = nullptr; a.kv_stride = 0;
                 a.qw = ly.q_norm; a.kw = ly.k_norm; a.cosc = p.cosc; a.sinc = p.sinc;
                 a.nh = p.nh; a.nkv = p.nkv; a.rotary_dim = p.rotary_dim; a.with_norm = p.with_qk_norm; a.T = 1; a.max_seq = p.max_seq;
-                a.base_pos = seq_len - 1; a.eps = p.eps; a.pos_dev = nullptr; a.qrot = p.qrot; a.q_out = nullptr;  // the position was read once at the start
-                a.ktab = EncodeTables{p.signs, cbk, bdk, p.qjl_t, p.k_levels, 1};
-                a.vtab = EncodeTables{p.signs, cbv, bdv, p.qjl_t, p.v_levels, 0};
+                a.base_pos = seq_len - 1; a.eps = p.eps; a.pos_dev = nullptr; a.slot_map = nullptr; a.qrot = p.qrot; a.q_out = nullptr;  // the position was read once at the start
+                a.ktab = EncodeTables{p.signs, cbk, bdk, p.qjl_t, p.k_levels, 1, BITS};
+                a.vtab = EncodeTables{p.signs, cbv, bdv, p.qjl_t, p.v_levels, 0, BITS};
                 a.kc = ly.kc; a.vc = ly.vc; a.ks = ly.ks; a.vs = ly.vs; a.krn = ly.krn;
                 float *sh = reinterpret_cast<float *>(U);
                 QjlCoop pj{sv, sh + 3 * kHd + 4};
@@ -737,7 +719,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) decode_token_kernel(const MegaP
             ap.q = nullptr; ap.kc = ly.kc; ap.vc = ly.vc; ap.ks = ly.ks; ap.vs = ly.vs; ap.krn = ly.krn;
             ap.signs = p.signs; ap.qjl = p.qjl_t; ap.k_cb = p.k_cb; ap.v_cb = p.v_cb; ap.qrot = p.qrot;
             ap.po = p.po; ap.pm = p.pm; ap.pl = p.pl; ap.attn_scale = p.attn_scale; ap.qjl_factor = p.qjl_factor;
-            ap.nh = p.nh; ap.nkv = p.nkv; ap.max_seq = p.max_seq; ap.base_pos = 0; ap.T = 1; ap.splits = p.splits; ap.pos_dev = p.pos;
+            ap.nh = p.nh; ap.nkv = p.nkv; ap.max_seq = p.max_seq; ap.base_pos = 0; ap.T = 1; ap.splits = p.splits; ap.pos_dev = p.pos; ap.slot_map = nullptr; ap.bits = BITS;
             const int item0 = blockIdx.x + gridDim.x * group;
             const bool have0 = !dead && item0 < p.nkv * used;
             if (have0) {
@@ -798,8 +780,10 @@ static constexpr int attn_bytes() {
     return kGroups * (int)sizeof(AttnSmem<GQ>);
 }
 
+int mega_g_cap(int G_max, int G_norm) { return G_max > 2 * G_norm ? G_max : 2 * G_norm; }
+
 int mega_u_bytes(int G_max, int G_norm, int gq) {
-    const int stage = ((G_max * 8 + 15) & ~15) + G_max * 2 * 32 * 4 + ((G_norm * 8 + 15) & ~15) + G_norm * 2 * 32 * 4;
+    const int stage = mega_g_cap(G_max, G_norm) * (16 + 3 * 32 * 4);
     int attn = 0;
     switch (gq) {
         case 1: attn = attn_bytes<1>(); break;
@@ -814,16 +798,16 @@ int mega_u_bytes(int G_max, int G_norm, int gq) {
     return (u + 15) & ~15;
 }
 
-template <int GQ, bool TP>
+template <int GQ, bool TP, int BITS>
 static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st) {
     const size_t smem = mega_smem_bytes(p.nring, p.u_bytes);
     if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
-    auto kern = decode_token_kernel<GQ, TP>;
+    auto kern = decode_token_kernel<GQ, TP, BITS>;
     static DeviceOnce once;  // per instantiation
     if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(dev->sm_count);
-    cfg.blockDim = dim3(kV2Threads);
+    cfg.blockDim = dim3(kMegaThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -838,11 +822,21 @@ static int mega_launch_t(const MegaParams &p, const Device *dev, cudaStream_t st
 int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st) {
     if (p.nkv <= 0 || p.nh % p.nkv != 0) return IM_ERR_BOUNDS;
     const bool tp = p.tagged != 0;
+    if (p.tq_bits == 4) {  // the 4-bit cache is built for the single-GPU (barrier) form of the kernel
+        if (tp) return IM_ERR_BOUNDS;
+        switch (p.nh / p.nkv) {
+            case 1: return mega_launch_t<1, false, 4>(p, dev, st);
+            case 2: return mega_launch_t<2, false, 4>(p, dev, st);
+            case 4: return mega_launch_t<4, false, 4>(p, dev, st);
+            case 8: return mega_launch_t<8, false, 4>(p, dev, st);
+            default: return IM_ERR_BOUNDS;
+        }
+    }
     switch (p.nh / p.nkv) {
-        case 1: return tp ? mega_launch_t<1, true>(p, dev, st) : mega_launch_t<1, false>(p, dev, st);
-        case 2: return tp ? mega_launch_t<2, true>(p, dev, st) : mega_launch_t<2, false>(p, dev, st);
-        case 4: return tp ? mega_launch_t<4, true>(p, dev, st) : mega_launch_t<4, false>(p, dev, st);
-        case 8: return tp ? mega_launch_t<8, true>(p, dev, st) : mega_launch_t<8, false>(p, dev, st);
+        case 1: return tp ? mega_launch_t<1, true, 8>(p, dev, st) : mega_launch_t<1, false, 8>(p, dev, st);
+        case 2: return tp ? mega_launch_t<2, true, 8>(p, dev, st) : mega_launch_t<2, false, 8>(p, dev, st);
+        case 4: return tp ? mega_launch_t<4, true, 8>(p, dev, st) : mega_launch_t<4, false, 8>(p, dev, st);
+        case 8: return tp ? mega_launch_t<8, true, 8>(p, dev, st) : mega_launch_t<8, false, 8>(p, dev, st);
         default: return IM_ERR_BOUNDS;
     }
 }

@@ -543,13 +543,18 @@ static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const Aff
     q.partial = w->dev->sk_partial; q.counters = w->dev->sk_counters; q.err = w->dev->err_flag;
     int done = 0;
     while (done < B) {
-        const int nb = B - done >= 4 ? 4 : (B - done >= 2 ? 2 : 1);
+        int nb = B - done >= 4 ? 4 : (B - done >= 2 ? 2 : 1);
         q.x = p.x + (size_t)done * p.K;
         q.b = p.b ? p.b + (size_t)done * p.K : nullptr;
         q.y = p.y + (size_t)done * p.N;
         q.residual_out = p.residual_out ? p.residual_out + (size_t)done * p.K : nullptr;
         q.normed_out = p.normed_out ? p.normed_out + (size_t)done * p.K : nullptr;
         int rc = v2_run(MODE, nb, q, w->dev, st);
+        // the staged activations of four (or two) batch rows may not fit beside the ring for a long K: fewer rows per launch
+        while (rc == IM_ERR_BOUNDS && nb > 1) {
+            nb /= 2;
+            rc = v2_run(MODE, nb, q, w->dev, st);
+        }
         if (rc != IM_OK) return rc;  // IM_ERR_BOUNDS on the first chunk: caller falls back
         done += nb;
     }
@@ -862,9 +867,6 @@ IM_EXPORT int im_cuda_matvec_f16(const void *w_dev, const void *x_dev, void *y_d
     return IM_OK;
     IM_GUARD_END
 }
-
-// Development aid (not part of the documented ABI): device buffer of 8 u64 that CTA 0 of the tiled matvec
-// fills with %globaltimer stamps (start, activations staged, first stage ready, second stage ready, loop end, end).
 
 // superblock_matmul_int4 (crates/ironmill-inference/src/metal/shaders/quantized/affine_matmul.metal:10-152) on the
 // tcgen05 tensor cores (gemm_tc.cu).  INT4 group-128 weights only.

@@ -29,9 +29,8 @@
 
 namespace im {
 
-// Activation staging.  xq words: index (((grp*2NB + col)*4 + t)*4 + j)*2 + eo, col = 2b (high bytes) or
-// 2b+1 (low bytes); the word holds elements (4t+j)*8 + {0,2,4,6} (eo = 0) or {1,3,5,7} (eo = 1) of the group.
-// meta[grp*NB + b] = (group scale, sum of the 128 integers).  Returns this thread's share of sum r^2.
+// Activation staging of batch row b (layout and rounding: stage_chunk24, v2_device.cuh).  Returns this thread's share
+// of sum r^2 (residual + norm modes).
 template <int MODE, int NB>
 __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *xq, float2 *meta, int nthreads_warps) {
     const int K = p.K, lane = threadIdx.x & 31, hl = lane & 15, warp = threadIdx.x >> 5;
@@ -71,37 +70,11 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const float2 fa = __half22float2(ha[i]);
-                v[2 * i] = v[2 * i] / fa.x;
-                v[2 * i + 1] = v[2 * i + 1] / fa.y;
+                v[2 * i] = __fdiv_rn(v[2 * i], fa.x);
+                v[2 * i + 1] = __fdiv_rn(v[2 * i + 1], fa.y);
             }
         }
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        // 32639 = 127 * 256 + 127: both bytes of the split below stay inside a signed byte
-        const float sx = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f;
-        const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
-        int hi[8], lo[8], lsum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            int xi = __float2int_rn(v[i] * inv);
-            xi = max(-32639, min(32639, xi));
-            lsum += xi;
-            hi[i] = (xi + 128) >> 8;
-            lo[i] = xi - hi[i] * 256;
-        }
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-        if (live) {
-            const int t = hl >> 2, j = hl & 3;
-            uint2 *dh = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 * NB + 2 * b) * 4 + t) * 4 + j) * 2);
-            uint2 *dl = reinterpret_cast<uint2 *>(xq + ((((size_t)grp * 2 * NB + 2 * b + 1) * 4 + t) * 4 + j) * 2);
-            *dh = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
-            *dl = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
-            if (hl == 0) meta[grp * NB + b] = make_float2(sx * 0.0625f, (float)(lsum * 16));  // TileMath accumulates 16 x the integer dot product
-        }
+        stage_chunk24<NB>(v, live, grp, b, hl, xq, meta);
     }
     return sq;
 }
@@ -118,9 +91,9 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     const int G = p.G, nring = p.nring;
     constexpr int stage_bytes = kStageTiles * kTileBytes;
     unsigned char *ring = smem;                                                        // nring * stage_bytes
-    uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);   // G * 2NB * 32 words
-    float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 2 * NB * 32);           // G * NB
-    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB);                     // nring * warps * 64 partial sums
+    uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);   // G * 3NB * 32 words
+    float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 3 * NB * 32);           // G * NB * 2
+    float *red = reinterpret_cast<float *>(meta + (size_t)G * NB * 2);                 // nring * warps * 64 partial sums
     float *misc = red + (size_t)nring * kV2Consumers * 64;                             // 16 floats: rms_inv per batch row, reduction scratch
     uint64_t *full = reinterpret_cast<uint64_t *>(misc + 32);
     uint64_t *empty = full + nring;
@@ -291,11 +264,17 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
         }
         if (grp0 + n == G || t0 + n == t_end) {  // last stage of this row block inside the CTA's range:
             float *buf = red + slot * (kV2Consumers * 64);  // hand the partial sums to the producer warp
-            if (t < NB) {
-                buf[warp * 64 + g * 4 + t] = tm.acc0;
-                buf[warp * 64 + (g + 8) * 4 + t] = tm.acc1;
+#pragma unroll
+            for (int cs = 0; cs < TileMath<NB>::kSets; cs++) {
+                float r0, r1;
+                tm.row_sums(cs, r0, r1);
+                const int bb = 2 * cs + (t >> 1);
+                if (!(t & 1) && bb < NB) {
+                    buf[warp * 64 + g * 4 + bb] = r0;
+                    buf[warp * 64 + (g + 8) * 4 + bb] = r1;
+                }
             }
-            tm.acc0 = tm.acc1 = 0.0f;
+            tm.clear_sums();
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
@@ -344,7 +323,7 @@ template <int MODE, int NB>
 static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     const size_t stage_bytes = (size_t)kStageTiles * kTileBytes;
     const size_t red_buf = (size_t)kV2Consumers * 64 * 4;  // one partial-sum buffer per ring slot
-    const size_t fixed = (size_t)p.G * 2 * NB * 32 * 4 + (size_t)p.G * NB * 8 + 32 * 4 + 64;
+    const size_t fixed = (size_t)p.G * 3 * NB * 32 * 4 + (size_t)p.G * NB * 16 + 32 * 4 + 64;
     const size_t per_slot = stage_bytes + 16 + red_buf;
     const size_t budget = dev->smem_optin > 8192 ? dev->smem_optin - 2048 : 0;
     if (fixed + 3 * per_slot > budget) return IM_ERR_BOUNDS;  // caller falls back to the first-generation kernel

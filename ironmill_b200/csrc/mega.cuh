@@ -44,13 +44,15 @@ struct MegaParams {
     const __half *cosc, *sinc;
     const float *signs, *qjl_t, *k_cb, *k_bd, *v_cb, *v_bd;
     int k_levels, v_levels;
+    int tq_bits;              // cache bits per element (8 or 4)
     float eps, attn_scale, qjl_factor;
     int max_seq, rotary_dim, with_qk_norm;
     int splits;               // attention items per KV head (capacity of the partial buffers)
     int nring;                // ring slots
     int u_bytes;              // shared-memory scratch shared by the phases
     int g_max;                // largest group count of any phase (sizes the activation staging area)
-    int g_norm;               // group count of the norm phases (hidden / 128): size of the second staging set
+    int g_norm;               // group count of the norm phases (hidden / 128): where the second staging set starts
+    int g_cap;                // groups the staging arrays hold: max(g_max, 2 g_norm)
     unsigned *bar;            // 7 * L arrival counters + 1 exit counter, zero between launches
     int *err;
     unsigned long long *trace;  // optional: CTA 0 stamps %globaltimer when it leaves each barrier (7L + 2 words)
@@ -70,6 +72,7 @@ struct MegaParams {
 size_t mega_smem_bytes(int nring, int u_bytes);
 // Phase scratch for projections of up to G_max groups (norm phases: G_norm) and GQ query heads per KV head.
 int mega_u_bytes(int G_max, int G_norm, int gq);
+int mega_g_cap(int G_max, int G_norm);
 // Cooperative launch; IM_ERR_BOUNDS if the shapes do not fit the kernel.
 int mega_launch(const MegaParams &p, const Device *dev, cudaStream_t st);
 

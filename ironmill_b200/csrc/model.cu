@@ -226,7 +226,13 @@ struct Model {
     int *err_pin = nullptr;  // the device's bounded-wait error word, copied back with every step
     cudaStream_t stream = nullptr;
     std::map<int, cudaGraphExec_t> graphs;
-    int seq_pos = 0;
+    // Cache slots (continuous batching): every sequence owns one of max_batch slots = its rows of every layer's caches
+    // and its position.  The single-sequence calls work on slot 0, the lockstep batch calls on slots 0 .. batch - 1.
+    std::vector<int> slot_pos;      // host copy of the positions
+    std::vector<char> slot_used;    // claimed by im_cuda_model_seq_add
+    int *slot_ident = nullptr;      // device: 0, 1, 2, ... (a one-sequence forward into slot s passes slot_ident + s)
+    int *slot_map = nullptr;        // device: slots of the sequences of the batch being decoded
+    int *slot_pin = nullptr;
     bool finalized = false;
     size_t bytes = 0;
     int launches_per_step = 0;
@@ -258,10 +264,10 @@ struct Model {
 static const int kPrefillChunk = 256;
 static const int kGemmMinTokens = 16;  // from here on the projections are dense contractions: tcgen05 GEMM instead of matvecs
 
-__global__ void advance_pos_kernel(int *pos, int n, int by) {
+__global__ void advance_pos_kernel(int *pos, const int *slot_map, int n, int by) {
     pdl_trigger();
     pdl_wait();
-    if ((int)threadIdx.x < n) pos[threadIdx.x] += by;
+    if ((int)threadIdx.x < n) pos[slot_map ? slot_map[threadIdx.x] : threadIdx.x] += by;
 }
 __global__ void set_pos_kernel(int *pos, int n, int v) {
     if ((int)threadIdx.x < n) pos[threadIdx.x] = v;
@@ -358,6 +364,21 @@ __global__ void silu_mul_kernel(const __half *__restrict__ gate, const __half *_
     const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(gate + i)), u = __half22float2(*reinterpret_cast<const __half2 *>(up + i));
     *reinterpret_cast<__half2 *>(out + i) = __floats2half2_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
 }
+
+}  // namespace im
+// silu_gate as an entry point of its own (the prefill form of the FFN: gate and up are rounded to fp16 first).
+// out may alias gate.  n even.
+IM_EXPORT int im_cuda_silu_mul(const void *gate_dev, const void *up_dev, void *out_dev, size_t n, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(gate_dev && up_dev && out_dev && n % 2 == 0, "bad argument");
+    if (n == 0) return IM_OK;
+    cudaError_t le = im::launch_k(im::silu_mul_kernel, dim3((unsigned)((n / 2 + 255) / 256)), dim3(256), 0, im::as_stream(stream),
+                                  static_cast<const __half *>(gate_dev), static_cast<const __half *>(up_dev), static_cast<__half *>(out_dev), n);
+    if (le != cudaSuccess) return im::fail(IM_ERR_CUDA, "launch failed: %s", cudaGetErrorString(le));
+    return IM_OK;
+    IM_GUARD_END
+}
+namespace im {
 
 static bool parse_layer_name(const char *name, int *layer, std::string *suffix) {
     const char *pfx = "model.layers.";
@@ -504,7 +525,9 @@ struct Prof {
 
 // One forward pass over nseq sequences x T tokens each (decode: T = 1; prefill: nseq = 1).
 // Logits are produced for the last token of every sequence.
-static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches, Prof *prof = nullptr, bool all_logits = false) {
+// slots: device array naming the cache slot of each of the nseq sequences (nullptr: slots 0 .. nseq - 1).
+static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches, Prof *prof = nullptr, bool all_logits = false,
+                   const int *slots = nullptr) {
     const im_model_config &c = m->cfg;
     const int H = c.hidden_size, hd = c.head_dim, MT = nseq * T;
     const float eps = c.rms_eps;
@@ -514,7 +537,7 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
                                   c.embed_scale != 0.0f ? c.embed_scale : 1.0f, st));
     nl++;
     IM_MARK(kCatEmbed);
-    const bool mega = MT == 1 && m->mega_ready && !prof;
+    const bool mega = MT == 1 && m->mega_ready && !prof && !slots;  // the whole-token kernel works on slot 0
     if (mega) {  // every layer in one persistent launch (decode_mega.cu); leaves the same buffers as the loop below
         int rc = mega_launch(m->mega, m->dev, st);
         if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "whole-token decode kernel: shapes do not fit");
@@ -539,13 +562,13 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         a.qkv = m->qkv; a.stride = m->qkv_dim; a.k_off = m->q_dim; a.v_off = m->q_dim + m->kv_dim;
         a.qw = L.q_norm; a.kw = L.k_norm; a.cosc = m->cosc; a.sinc = m->sinc;
         a.nh = m->nh_l; a.nkv = m->nkv_l; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd; a.with_norm = c.qk_norm ? 1 : 0;
-        a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev;
+        a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev; a.slot_map = slots;
         a.qrot = m->qrot; a.q_out = nullptr;
         a.kc = L.kc; a.vc = L.vc; a.ks = L.ks; a.vs = L.vs; a.krn = L.krn;
         IM_TRY(tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st));
         IM_MARK(kCatKvWrite);
         IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
-                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot));
+                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot, slots));
         nl += 3;
         IM_MARK(kCatAttn);
         IM_TRY(gemm_affine_tc(L.o, m->attn_out, m->ffn_down, MT, m->xs_scratch, st));
@@ -600,13 +623,13 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         a.qkv = m->q_d; a.stride = m->q_dim; a.kv = m->k_d; a.kv_stride = 2 * m->kv_dim; a.k_off = 0; a.v_off = m->kv_dim;
         a.qw = L.q_norm; a.kw = L.k_norm; a.cosc = m->cosc; a.sinc = m->sinc;
         a.nh = m->nh_l; a.nkv = m->nkv_l; a.rotary_dim = c.rotary_dim ? c.rotary_dim : hd; a.with_norm = c.qk_norm ? 1 : 0;
-        a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev;
+        a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev; a.slot_map = slots;
         a.qrot = m->qrot; a.q_out = nullptr;
         a.kc = L.kc; a.vc = L.vc; a.ks = L.ks; a.vs = L.vs; a.krn = L.krn;
         IM_TRY(tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st));
         IM_MARK(kCatKvWrite);
         IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
-                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot));
+                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot, slots));
         nl += 3;
         IM_MARK(kCatAttn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.o), m->attn_out, m->ffn_down, MT, st));
@@ -697,6 +720,7 @@ static int mega_prepare(Model *m) {
     const bool tp = m->world > 1;
     // one GPU: opt-in only (measured slower there than the barrier: 64.0 against 60.0 us per layer at L8 shapes)
     const bool tagged = tp || c.decode_schedule == 2;
+    if (tagged && c.tq_bits == 4) return IM_OK;  // 4-bit caches: the barrier form of the kernel only (tensor parallel: per-kernel schedule)
     if (tp && (!m->xar.ok || m->world > 8 || c.hidden_size % 128 != 0)) return IM_OK;  // needs the peer mapping of tp_init
     if (c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
     const int gq = m->nh_l / m->nkv_l;
@@ -769,12 +793,12 @@ static int mega_prepare(Model *m) {
     p.cosc = m->cosc; p.sinc = m->sinc;
     const Tq *tq = reinterpret_cast<const Tq *>(m->tq);
     p.signs = tq->signs; p.qjl_t = tq->qjl_t; p.k_cb = tq->k_cb; p.k_bd = tq->k_bd; p.v_cb = tq->v_cb; p.v_bd = tq->v_bd;
-    p.k_levels = tq->k_levels; p.v_levels = tq->v_levels;
+    p.k_levels = tq->k_levels; p.v_levels = tq->v_levels; p.tq_bits = tq->n_bits;
     p.eps = c.rms_eps;
     p.attn_scale = c.attn_scale != 0.0f ? c.attn_scale : 1.0f / sqrtf((float)c.head_dim);
     p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)c.head_dim;
     p.max_seq = c.max_seq_len; p.rotary_dim = c.rotary_dim ? c.rotary_dim : c.head_dim; p.with_qk_norm = c.qk_norm ? 1 : 0;
-    p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max; p.g_norm = g_norm;
+    p.nring = nring; p.u_bytes = u_bytes; p.g_max = g_max; p.g_norm = g_norm; p.g_cap = mega_g_cap(g_max, g_norm);
     IM_TRY(m->alloc((void **)&p.bar, (size_t)(7 * L + 1) * sizeof(unsigned)));
     IM_CUDA_CHECK(cudaMemset(p.bar, 0, (size_t)(7 * L + 1) * sizeof(unsigned)));
     p.err = m->dev->err_flag;
@@ -809,8 +833,11 @@ static int decode_splits(const Model *m, int batch) {
     return tq_auto_splits(m->dev, batch, 1, m->nkv_l, m->cfg.max_seq_len);
 }
 
-static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
-    auto it = m->graphs.find(batch);
+// mapped: the sequences of the batch live in the slots listed in m->slot_map (continuous batching); otherwise in slots 0 .. batch - 1.
+static int get_graph(Model *m, int batch, cudaGraphExec_t *out, bool mapped = false) {
+    const int key = batch + (mapped ? 1000 : 0);
+    const int *slots = mapped ? m->slot_map : nullptr;
+    auto it = m->graphs.find(key);
     if (it != m->graphs.end()) {
         *out = it->second;
         return IM_OK;
@@ -818,18 +845,18 @@ static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
     cudaStream_t st = m->stream;
     // one eager pass first: sets function attributes and warms NCCL outside the capture
     const int splits = decode_splits(m, batch);
-    IM_TRY(forward(m, batch, 1, splits, st, nullptr));
+    IM_TRY(forward(m, batch, 1, splits, st, nullptr, nullptr, false, slots));
     IM_CUDA_CHECK(cudaStreamSynchronize(st));
     cudaGraph_t g = nullptr;
     IM_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     int nl = 0;
-    int rc = forward(m, batch, 1, splits, st, &nl);
+    int rc = forward(m, batch, 1, splits, st, &nl, nullptr, false, slots);
     if (rc == IM_OK) {
         const __half *lg = m->world > 1 ? m->logits_all : m->logits;
         cudaError_t le = launch_k(argmax_kernel, dim3(kArgmaxCtas, batch), dim3(kArgmaxThreads), 0, st, lg, m->vocab_l, m->world, batch, m->tokens_dev,
                                   m->tok_hist, (const int *)m->step_dev, m->cfg.max_batch, m->cfg.max_seq_len, m->argmax_cand, m->argmax_counters);
         if (le == cudaSuccess) le = launch_k(bump_kernel, dim3(1), dim3(1), 0, st, m->step_dev);
-        if (le == cudaSuccess) le = launch_k(advance_pos_kernel, dim3(1), dim3(64), 0, st, m->pos_dev, batch, 1);
+        if (le == cudaSuccess) le = launch_k(advance_pos_kernel, dim3(1), dim3(64), 0, st, m->pos_dev, slots, batch, 1);
         if (le != cudaSuccess) rc = fail(IM_ERR_CUDA, "launch failed: %s", cudaGetErrorString(le));
         nl += 3;
     }
@@ -843,16 +870,9 @@ static int get_graph(Model *m, int batch, cudaGraphExec_t *out) {
     e = cudaGraphInstantiate(&ge, g, 0);
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return fail(IM_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
-    m->graphs[batch] = ge;
+    m->graphs[key] = ge;
     m->launches_per_step = nl;
     *out = ge;
-    return IM_OK;
-}
-
-static int set_positions(Model *m, int pos) {
-    set_pos_kernel<<<1, 64, 0, m->stream>>>(m->pos_dev, m->cfg.max_batch, pos);
-    IM_CUDA_CHECK(cudaGetLastError());
-    m->seq_pos = pos;
     return IM_OK;
 }
 
@@ -887,6 +907,62 @@ static int step_error_check(Model *m) {
     cudaMemset(m->dev->sk_counters, 0, (size_t)kSkMaxBlocks * sizeof(int));
     if (m->mega.bar) cudaMemset(m->mega.bar, 0, (size_t)(7 * m->cfg.num_layers + 1) * sizeof(unsigned));
     return fail(IM_ERR_TIMEOUT, "a device-side bounded wait ran out (code %d); the results of this step are invalid", code);
+}
+
+// Positions of every slot (reset, truncate of the single-sequence / lockstep interface).
+static int set_positions(Model *m, int pos) {
+    set_pos_kernel<<<1, 64, 0, m->stream>>>(m->pos_dev, m->cfg.max_batch, pos);
+    IM_CUDA_CHECK(cudaGetLastError());
+    for (int &p : m->slot_pos) p = pos;
+    return IM_OK;
+}
+__global__ void set_one_pos_kernel(int *pos, int slot, int v) { pos[slot] = v; }
+
+// Prefill of n tokens into cache slot `slot`, continuing at that slot's position.  last_logits (optional): f32 [vocab]
+// of the last token; all_logits (optional): f32 [n, vocab].
+static int prefill_slot(Model *m, int slot, const uint32_t *tokens_host, int n, float *last_logits, float *all_logits) {
+    if (m->slot_pos[slot] + n > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->slot_pos[slot], n, m->cfg.max_seq_len);
+    cudaStream_t st = m->stream;
+    // 256-token chunks when the projections run as tensor-core GEMMs; the matvec kernels take at most 64 rows per call
+    const int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
+    const size_t V = (size_t)m->cfg.vocab_size;
+    const int *slots = slot == 0 ? nullptr : m->slot_ident + slot;
+    if (all_logits && !m->logits_seq) {  // first use: a chunk's worth of logits on the device and in pinned host memory
+        IM_TRY(m->alloc((void **)&m->logits_seq, (size_t)kPrefillChunk * m->vocab_l * 2));
+        if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_seq_all, (size_t)kPrefillChunk * V * 2));
+        IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_seq_pin, (size_t)kPrefillChunk * V * 2));
+    }
+    for (int done = 0; done < n; done += chunk) {
+        const int T = n - done < chunk ? n - done : chunk;
+        memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
+        const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->slot_pos[slot] + T);
+        IM_TRY(forward(m, 1, T, splits, st, nullptr, nullptr, all_logits != nullptr, slots));
+        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, slots, 1, T);
+        IM_CUDA_CHECK(cudaGetLastError());
+        if (all_logits) {
+            const __half *lg = m->world > 1 ? m->logits_seq_all : m->logits_seq;
+            IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_seq_pin, lg, (size_t)T * V * 2, cudaMemcpyDeviceToHost, st));
+        }
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+        IM_CUDA_CHECK(cudaStreamSynchronize(st));  // tokens_pin is reused by the next chunk
+        IM_TRY(step_error_check(m));
+        m->slot_pos[slot] += T;
+        if (all_logits) {  // device layout [part][token][vocab_l] -> host rows [token][vocab]
+            const int vl = m->vocab_l;
+            for (int p = 0; p < m->world; p++)
+                for (int t = 0; t < T; t++)
+                    widen(m->logits_seq_pin + ((size_t)p * T + t) * vl, all_logits + (size_t)(done + t) * V + (size_t)p * vl, vl);
+        }
+    }
+    if (last_logits) {
+        const __half *lg = m->world > 1 ? m->logits_all : m->logits;
+        IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, V * 2, cudaMemcpyDeviceToHost, st));
+        IM_CUDA_CHECK(cudaStreamSynchronize(st));
+        logits_to_host(m, m->logits_pin, 1, last_logits);
+    }
+    return IM_OK;
 }
 
 }  // namespace im
@@ -1044,7 +1120,6 @@ IM_EXPORT int im_cuda_model_create(im_device *dev, const im_model_config *cfg, i
     // MetalConfig::validate (crates/ironmill-inference/src/metal/config.rs:364-384)
     IM_REQUIRE(c.max_seq_len > 0, "max_seq_len must be > 0");
     IM_REQUIRE(c.tq_bits == 4 || c.tq_bits == 8, "n_bits must be 4 or 8, got %d", c.tq_bits);
-    IM_REQUIRE(c.tq_bits == 8, "only the 8-bit TurboQuant cache is built (n_bits = %d)", c.tq_bits);
     IM_REQUIRE(c.num_layers > 0 && c.hidden_size > 0 && c.intermediate_size > 0 && c.num_heads > 0 && c.num_kv_heads > 0 &&
                    c.head_dim > 0 && c.vocab_size > 0, "model dimensions must be positive");
     IM_REQUIRE(c.head_dim == 128, "head_dim %d is not built (128 only)", c.head_dim);
@@ -1105,6 +1180,7 @@ IM_EXPORT void im_cuda_model_free(im_model *m) {
     if (m->tokens_pin) cudaFreeHost(m->tokens_pin);
     if (m->logits_pin) cudaFreeHost(m->logits_pin);
     if (m->logits_seq_pin) cudaFreeHost(m->logits_seq_pin);
+    if (m->slot_pin) cudaFreeHost(m->slot_pin);
     if (m->err_pin) cudaFreeHost(m->err_pin);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
@@ -1158,6 +1234,30 @@ IM_EXPORT int im_cuda_model_load_affine(im_model *m, const char *name, const voi
     const int H = c.hidden_size, hd = c.head_dim, r = m->rank;
     std::string suffix;
     int l = -1;
+    if (std::string(name) == "model.embed_tokens.weight" || std::string(name) == "lm_head.weight") {
+        // An affine-quantized embedding table or lm_head (the reference accepts both,
+        // crates/ironmill-inference/src/metal/weights.rs:305-420): dequantised here to the dense fp16 form the gather
+        // and the lm_head matvec read: f16((q - z) * s) from the fp16 parameters the GPU kernels see
+        // (crates/ironmill-core/src/dequant.rs:85-180,305-345), divided by the AWQ scale of its column if there is one.
+        IM_REQUIRE(N == c.vocab_size && K == H, "%s: expected shape [%d,%d], got [%d,%d]", name, c.vocab_size, H, N, K);
+        const int G = (K + group_size - 1) / group_size;
+        std::vector<__half> dense((size_t)N * K);
+        const uint8_t *q = static_cast<const uint8_t *>(qdata_host);
+        auto param = [&](const void *p, size_t i) -> float {
+            const float v = param_dtype == IM_DTYPE_F32 ? static_cast<const float *>(p)[i] : __half2float(static_cast<const __half *>(p)[i]);
+            return __half2float(__float2half_rn(v));
+        };
+        const __half *awq = static_cast<const __half *>(awq_f16_host);
+        for (size_t n = 0; n < (size_t)N; n++)
+            for (int k = 0; k < K; k++) {
+                const size_t e = n * K + k, pi = n * G + k / group_size;
+                const unsigned code = bit_width == 4 ? (q[e >> 1] >> (4 * (e & 1))) & 15u : q[e];
+                float v = __half2float(__float2half_rn(((float)code - param(zeros_host, pi)) * param(scales_host, pi)));
+                if (awq) v = v / __half2float(awq[k]);
+                dense[e] = __float2half_rn(v);
+            }
+        return im_cuda_model_load_dense(m, name, dense.data(), dense.size());
+    }
     if (!parse_layer_name(name, &l, &suffix) || l < 0 || l >= c.num_layers) return fail(IM_ERR_INVALID, "unknown quantized tensor '%s'", name);
     Layer &L = m->layers[l];
     HostAffine h;
@@ -1229,16 +1329,17 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
         L.hq = HostAffine(); L.hk = HostAffine(); L.hv = HostAffine();
         // KV cache of this rank's heads (MetalKvCache, crates/ironmill-inference/src/metal/turboquant/cache.rs:104-354)
         const size_t rows = (size_t)c.max_batch * m->nkv_l * c.max_seq_len;
-        IM_TRY(m->alloc((void **)&L.kc, rows * hd));
-        IM_TRY(m->alloc((void **)&L.vc, rows * hd));
+        const size_t rowb = (size_t)hd * c.tq_bits / 8;  // one byte per element, or two elements per byte (n_bits = 4)
+        IM_TRY(m->alloc((void **)&L.kc, rows * rowb));
+        IM_TRY(m->alloc((void **)&L.vc, rows * rowb));
         IM_TRY(m->alloc((void **)&L.ks, rows * 4));
         IM_TRY(m->alloc((void **)&L.vs, rows * 4));
         IM_TRY(m->alloc((void **)&L.krn, rows * 4));
         IM_CUDA_CHECK(cudaMemset(L.ks, 0, rows * 4));
         IM_CUDA_CHECK(cudaMemset(L.vs, 0, rows * 4));
         IM_CUDA_CHECK(cudaMemset(L.krn, 0, rows * 4));
-        IM_CUDA_CHECK(cudaMemset(L.kc, 0, rows * hd));
-        IM_CUDA_CHECK(cudaMemset(L.vc, 0, rows * hd));
+        IM_CUDA_CHECK(cudaMemset(L.kc, 0, rows * rowb));
+        IM_CUDA_CHECK(cudaMemset(L.vc, 0, rows * rowb));
     }
     // TurboQuant constants
     if (m->signs_host.empty()) {
@@ -1281,6 +1382,17 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_TRY(m->alloc((void **)&m->tokens_dev, MT * 4));
     IM_TRY(m->alloc((void **)&m->tok_hist, (size_t)c.max_seq_len * c.max_batch * 4));
     IM_TRY(m->alloc((void **)&m->pos_dev, 64 * 4));
+    IM_TRY(m->alloc((void **)&m->slot_ident, 64 * 4));
+    IM_TRY(m->alloc((void **)&m->slot_map, 64 * 4));
+    {
+        int ident[64];
+        for (int i = 0; i < 64; i++) ident[i] = i;
+        IM_CUDA_CHECK(cudaMemcpy(m->slot_ident, ident, sizeof(ident), cudaMemcpyHostToDevice));
+        IM_CUDA_CHECK(cudaMemcpy(m->slot_map, ident, sizeof(ident), cudaMemcpyHostToDevice));
+    }
+    IM_CUDA_CHECK(cudaMallocHost((void **)&m->slot_pin, 64 * sizeof(int)));
+    m->slot_pos.assign((size_t)c.max_batch, 0);
+    m->slot_used.assign((size_t)c.max_batch, 0);
     IM_TRY(m->alloc((void **)&m->step_dev, 4));
     IM_CUDA_CHECK(cudaMemset(m->pos_dev, 0, 64 * 4));
     IM_CUDA_CHECK(cudaMemset(m->step_dev, 0, 4));
@@ -1316,6 +1428,7 @@ IM_EXPORT int im_cuda_model_reset(im_model *m) {
     IM_REQUIRE(m, "bad argument");
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    for (char &u : m->slot_used) u = 0;
     return set_positions(m, 0);
     IM_GUARD_END
 }
@@ -1324,13 +1437,13 @@ IM_EXPORT int im_cuda_model_truncate(im_model *m, int pos) {
     IM_GUARD_BEGIN
     IM_REQUIRE(m, "bad argument");
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
-    if (pos < 0 || pos > m->seq_pos) return fail(IM_ERR_BOUNDS, "truncate_to(%d) is outside the current sequence of %d tokens", pos, m->seq_pos);
+    if (pos < 0 || pos > m->slot_pos[0]) return fail(IM_ERR_BOUNDS, "truncate_to(%d) is outside the current sequence of %d tokens", pos, m->slot_pos[0]);
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     return set_positions(m, pos);
     IM_GUARD_END
 }
 
-IM_EXPORT int im_cuda_model_seq_pos(const im_model *m) { return m ? m->seq_pos : 0; }
+IM_EXPORT int im_cuda_model_seq_pos(const im_model *m) { return m && !m->slot_pos.empty() ? m->slot_pos[0] : 0; }
 IM_EXPORT int im_cuda_model_max_seq_len(const im_model *m) { return m ? m->cfg.max_seq_len : 0; }
 IM_EXPORT size_t im_cuda_model_memory_bytes(const im_model *m) { return m ? m->bytes : 0; }
 // Timing of the whole-token decode kernel alone: `reps` launches back to back on the model's stream between two
@@ -1342,7 +1455,7 @@ IM_EXPORT int im_cuda_model_token_kernel_profile(im_model *m, int reps, float *m
     IM_REQUIRE(m && reps >= 1 && ms_per_launch, "bad argument");
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     if (!m->mega_ready) return fail(IM_ERR_STATE, "this model does not run the whole-token decode kernel");
-    if (m->seq_pos + 1 > m->cfg.max_seq_len) return fail(IM_ERR_BOUNDS, "no room for one more position");
+    if (m->slot_pos[0] + 1 > m->cfg.max_seq_len) return fail(IM_ERR_BOUNDS, "no room for one more position");
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
     const im_model_config &c = m->cfg;
@@ -1417,7 +1530,7 @@ IM_EXPORT size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch)
             b += (size_t)w->N * w->K * w->bits / 8 + (size_t)w->N * w->G * 4 + (w->awq ? (size_t)w->K * 2 : 0);
         }
         b += 2 * (size_t)c.hidden_size * 2;
-        b += (size_t)batch * m->nkv_l * ctx * (2 * c.head_dim + 12);
+        b += (size_t)batch * m->nkv_l * ctx * (2 * c.head_dim * c.tq_bits / 8 + 12);
     }
     b += (size_t)m->vocab_l * c.hidden_size * 2 + (size_t)c.hidden_size * 2;
     return b;
@@ -1428,28 +1541,8 @@ IM_EXPORT int im_cuda_model_prefill(im_model *m, const uint32_t *tokens_host, in
     IM_REQUIRE(m && tokens_host && logits_out_host, "bad argument");
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     IM_REQUIRE(n > 0, "prefill needs at least one token");
-    if (m->seq_pos + n > m->cfg.max_seq_len)
-        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->seq_pos, n, m->cfg.max_seq_len);
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
-    cudaStream_t st = m->stream;
-    // 256-token chunks when the projections run as tensor-core GEMMs; the matvec kernels take at most 64 rows per call
-    const int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
-    for (int done = 0; done < n; done += chunk) {
-        const int T = n - done < chunk ? n - done : chunk;
-        memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
-        IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
-        const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->seq_pos + T);
-        IM_TRY(forward(m, 1, T, splits, st, nullptr));
-        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, 1, T);
-        IM_CUDA_CHECK(cudaGetLastError());
-        IM_CUDA_CHECK(cudaStreamSynchronize(st));  // tokens_pin is reused by the next chunk
-        m->seq_pos += T;
-    }
-    const __half *lg = m->world > 1 ? m->logits_all : m->logits;
-    IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, (size_t)m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, st));
-    IM_CUDA_CHECK(cudaStreamSynchronize(st));
-    logits_to_host(m, m->logits_pin, 1, logits_out_host);
-    return IM_OK;
+    return prefill_slot(m, 0, tokens_host, n, logits_out_host, nullptr);
     IM_GUARD_END
 }
 
@@ -1458,37 +1551,80 @@ IM_EXPORT int im_cuda_model_prefill_all_logits(im_model *m, const uint32_t *toke
     IM_REQUIRE(m && tokens_host && logits_out_host, "bad argument");
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     IM_REQUIRE(n > 0, "prefill needs at least one token");
-    if (m->seq_pos + n > m->cfg.max_seq_len)
-        return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->seq_pos, n, m->cfg.max_seq_len);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    return prefill_slot(m, 0, tokens_host, n, nullptr, logits_out_host);
+    IM_GUARD_END
+}
+
+// ---- continuous batching: BatchInferenceEngine (crates/ironmill-inference/src/engine.rs:121-131) -------------------
+IM_EXPORT int im_cuda_model_seq_add(im_model *m, const uint32_t *tokens_host, int n, int *seq_id_out, float *logits_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && tokens_host && seq_id_out, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(n > 0, "a sequence needs at least one prompt token");
+    int slot = -1;
+    for (int s = 0; s < m->cfg.max_batch && slot < 0; s++)
+        if (!m->slot_used[s]) slot = s;
+    if (slot < 0) return fail(IM_ERR_BOUNDS, "all %d sequence slots are in use (max_batch)", m->cfg.max_batch);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    set_one_pos_kernel<<<1, 1, 0, m->stream>>>(m->pos_dev, slot, 0);
+    IM_CUDA_CHECK(cudaGetLastError());
+    m->slot_pos[slot] = 0;
+    int rc = prefill_slot(m, slot, tokens_host, n, logits_out_host, nullptr);
+    if (rc != IM_OK) return rc;
+    m->slot_used[slot] = 1;
+    *seq_id_out = slot;
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_seq_remove(im_model *m, int seq_id) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    if (seq_id < 0 || seq_id >= m->cfg.max_batch || !m->slot_used[seq_id]) return fail(IM_ERR_INVALID, "no sequence %d", seq_id);
+    m->slot_used[seq_id] = 0;   // the slot's cache rows are simply overwritten by the next tenant
+    m->slot_pos[seq_id] = 0;
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT int im_cuda_model_seq_position(const im_model *m, int seq_id) {
+    if (!m || seq_id < 0 || seq_id >= (int)m->slot_pos.size() || !m->slot_used[seq_id]) return -1;
+    return m->slot_pos[seq_id];
+}
+
+// One decode step for the listed sequences (any subset of the live ones, each at its own position): tokens_host[i] is
+// appended to sequence seq_ids[i]; logits_out_host f32 [n, vocab] in the same order.
+IM_EXPORT int im_cuda_model_batch_decode_step(im_model *m, const int *seq_ids, const uint32_t *tokens_host, int n, float *logits_out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && seq_ids && tokens_host && logits_out_host, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    IM_REQUIRE(n >= 1 && n <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", n, m->cfg.max_batch);
+    for (int i = 0; i < n; i++) {
+        const int s = seq_ids[i];
+        if (s < 0 || s >= m->cfg.max_batch || !m->slot_used[s]) return fail(IM_ERR_INVALID, "no sequence %d", s);
+        for (int j = 0; j < i; j++)
+            if (seq_ids[j] == s) return fail(IM_ERR_INVALID, "sequence %d listed twice", s);
+        if (m->slot_pos[s] + 1 > m->cfg.max_seq_len)
+            return fail(IM_ERR_BOUNDS, "sequence %d: position %d + 1 exceeds max_seq_len %d", s, m->slot_pos[s], m->cfg.max_seq_len);
+    }
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
-    const int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
-    const size_t V = (size_t)m->cfg.vocab_size;
-    if (!m->logits_seq) {  // first use: a chunk's worth of logits on the device and in pinned host memory
-        IM_TRY(m->alloc((void **)&m->logits_seq, (size_t)kPrefillChunk * m->vocab_l * 2));
-        if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_seq_all, (size_t)kPrefillChunk * V * 2));
-        IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_seq_pin, (size_t)kPrefillChunk * V * 2));
-    }
-    for (int done = 0; done < n; done += chunk) {
-        const int T = n - done < chunk ? n - done : chunk;
-        memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
-        IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
-        const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->seq_pos + T);
-        IM_TRY(forward(m, 1, T, splits, st, nullptr, nullptr, true));
-        advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, 1, T);
-        IM_CUDA_CHECK(cudaGetLastError());
-        const __half *lg = m->world > 1 ? m->logits_seq_all : m->logits_seq;
-        IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_seq_pin, lg, (size_t)T * V * 2, cudaMemcpyDeviceToHost, st));
-        IM_CUDA_CHECK(cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
-        IM_CUDA_CHECK(cudaStreamSynchronize(st));
-        IM_TRY(step_error_check(m));
-        m->seq_pos += T;
-        // device layout [part][token][vocab_l] -> host rows [token][vocab]
-        const int vl = m->vocab_l;
-        for (int p = 0; p < m->world; p++)
-            for (int t = 0; t < T; t++)
-                widen(m->logits_seq_pin + ((size_t)p * T + t) * vl, logits_out_host + (size_t)(done + t) * V + (size_t)p * vl, vl);
-    }
+    memcpy(m->slot_pin, seq_ids, (size_t)n * sizeof(int));
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->slot_map, m->slot_pin, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, st));
+    cudaGraphExec_t g = nullptr;
+    IM_TRY(get_graph(m, n, &g, true));
+    memcpy(m->tokens_pin, tokens_host, (size_t)n * 4);
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    IM_CUDA_CHECK(cudaGraphLaunch(g, st));
+    const __half *lg = m->world > 1 ? m->logits_all : m->logits;
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->logits_pin, lg, (size_t)n * m->cfg.vocab_size * 2, cudaMemcpyDeviceToHost, st));
+    IM_CUDA_CHECK(cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    IM_CUDA_CHECK(cudaStreamSynchronize(st));
+    IM_TRY(step_error_check(m));
+    for (int i = 0; i < n; i++) m->slot_pos[seq_ids[i]] += 1;
+    logits_to_host(m, m->logits_pin, n, logits_out_host);
     return IM_OK;
     IM_GUARD_END
 }
@@ -1498,8 +1634,10 @@ IM_EXPORT int im_cuda_model_decode_step(im_model *m, const uint32_t *tokens_host
     IM_REQUIRE(m && tokens_host && logits_out_host, "bad argument");
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     IM_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", batch, m->cfg.max_batch);
-    if (m->seq_pos + 1 > m->cfg.max_seq_len)
-        return fail(IM_ERR_BOUNDS, "sequence position %d + 1 exceeds max_seq_len %d", m->seq_pos, m->cfg.max_seq_len);
+    int far = 0;
+    for (int b = 0; b < batch; b++) far = m->slot_pos[b] > far ? m->slot_pos[b] : far;
+    if (far + 1 > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + 1 exceeds max_seq_len %d", far, m->cfg.max_seq_len);
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
     cudaGraphExec_t g = nullptr;
@@ -1512,7 +1650,7 @@ IM_EXPORT int im_cuda_model_decode_step(im_model *m, const uint32_t *tokens_host
     IM_CUDA_CHECK(cudaMemcpyAsync(m->err_pin, m->dev->err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
     IM_CUDA_CHECK(cudaStreamSynchronize(st));
     IM_TRY(step_error_check(m));
-    m->seq_pos += 1;
+    for (int b = 0; b < batch; b++) m->slot_pos[b] += 1;
     logits_to_host(m, m->logits_pin, batch, logits_out_host);
     return IM_OK;
     IM_GUARD_END
@@ -1525,8 +1663,10 @@ IM_EXPORT int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tok
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     IM_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", batch, m->cfg.max_batch);
     IM_REQUIRE(n_steps >= 0, "n_steps must be >= 0");
-    if (m->seq_pos + n_steps > m->cfg.max_seq_len)
-        return fail(IM_ERR_BOUNDS, "sequence position %d + %d steps exceeds max_seq_len %d", m->seq_pos, n_steps, m->cfg.max_seq_len);
+    int far = 0;
+    for (int b = 0; b < batch; b++) far = m->slot_pos[b] > far ? m->slot_pos[b] : far;
+    if (far + n_steps > m->cfg.max_seq_len)
+        return fail(IM_ERR_BOUNDS, "sequence position %d + %d steps exceeds max_seq_len %d", far, n_steps, m->cfg.max_seq_len);
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
     cudaGraphExec_t g = nullptr;
@@ -1555,7 +1695,7 @@ IM_EXPORT int im_cuda_model_decode_greedy(im_model *m, const uint32_t *first_tok
     cudaEventDestroy(e1);
     if (e != cudaSuccess) return fail(IM_ERR_CUDA, "decode loop failed: %s", cudaGetErrorString(e));
     IM_TRY(step_error_check(m));
-    m->seq_pos += n_steps;
+    for (int b = 0; b < batch; b++) m->slot_pos[b] += n_steps;
     if (elapsed_ms_out) *elapsed_ms_out = ms;
     if (tokens_out_host && n_steps > 0)
         IM_CUDA_CHECK(cudaMemcpy2D(tokens_out_host, (size_t)batch * 4, m->tok_hist, (size_t)m->cfg.max_batch * 4, (size_t)batch * 4, n_steps,
@@ -1569,7 +1709,8 @@ IM_EXPORT int im_cuda_model_profile_step(im_model *m, int batch, float *ms_by_ca
     IM_REQUIRE(m && ms_by_category && n_categories >= kCatCount, "bad argument (need %d categories)", (int)kCatCount);
     if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
     IM_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch, "batch %d outside 1..max_batch (%d)", batch, m->cfg.max_batch);
-    if (m->seq_pos + 1 > m->cfg.max_seq_len) return fail(IM_ERR_BOUNDS, "no room for one more position");
+    for (int b = 0; b < batch; b++)
+        if (m->slot_pos[b] + 1 > m->cfg.max_seq_len) return fail(IM_ERR_BOUNDS, "no room for one more position");
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     cudaStream_t st = m->stream;
     const int splits = decode_splits(m, batch);

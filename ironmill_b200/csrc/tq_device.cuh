@@ -76,7 +76,10 @@ __device__ __forceinline__ float hadamard_thread(const Scope &sc, float v, float
 struct EncodeTables {
     const float *signs, *cb, *bounds, *qjl_t;  // bounds = suffix minima; qjl_t = transposed QJL matrix [k][d]
     int n_levels, is_k;
+    int bits;  // cache bits per element: 8 (one byte each) or 4 (element 2i in the low nibble of byte i, 2i + 1 in the high one)
 };
+// bytes of one cached position (bytes_per_pos, crates/ironmill-inference/src/shaders/turboquant_helpers.metal:24-27)
+__host__ __device__ __forceinline__ int tq_row_bytes(int bits, int hd) { return bits == 4 ? hd / 2 : hd; }
 
 // The QJL projection of a 128-vector held in shared memory: thread d computes sum_k S^T[k][d] * vec[k], walking k
 // upwards.  `Direct` reads the thread's matrix column itself, 64 values in flight at a time; begin() may be called
@@ -188,9 +191,14 @@ __device__ __forceinline__ void tq_encode_body(const Scope &sc, float xin, const
         const float rs = tq_tree_sum(sc, __fmul_rn(r, r), red, hd);  // its barriers also publish res[]
         if (d == 0) *rnorm_out = __fsqrt_rn(fmaxf(rs, 1e-20f));
         const float proj = pj.template finish<true>(sc, res, d, hd);
-        if (proj >= 0.0f) byte |= 0x80u;
+        if (proj >= 0.0f) byte |= 1u << (tb.bits - 1);  // the QJL sign rides in the top bit of the storage unit
     }
-    cache_row[d] = (uint8_t)byte;
+    if (tb.bits == 4) {  // write_packed_elements (turboquant_helpers.metal:61-77): even thread writes the pair
+        const unsigned hi = __shfl_down_sync(0xffffffffu, byte, 1);
+        if (!(d & 1)) cache_row[d >> 1] = (uint8_t)((byte & 0xFu) | ((hi & 0xFu) << 4));
+    } else {
+        cache_row[d] = (uint8_t)byte;
+    }
     sc.sync();  // sh may be reused by the caller
 }
 
@@ -216,8 +224,18 @@ struct AttnParams {
     float *po, *pm, *pl;     // partials [nseq*T, nh, splits] x (hd | 1 | 1)
     float attn_scale, qjl_factor;
     int nh, nkv, max_seq, base_pos, T, splits;
-    const int *pos_dev;
+    const int *pos_dev;      // optional per-slot positions (added to base_pos)
+    const int *slot_map;     // optional: sequence index of this launch -> cache slot (nullptr: identity)
+    int bits;                // cache bits per element (8 or 4); rows hold tq_row_bytes(bits, hd) bytes
 };
+// Eight 4-bit elements of a cache word -> two words of one byte per element (the 8-bit layout the score and value
+// loops read).  K: the 3-bit index stays in bits 0-2, the QJL sign moves from bit 3 to bit 7; V: the byte is the index.
+__device__ __forceinline__ unsigned tq_spread4(unsigned x) {  // nibbles 0-3 of x (low 16 bits) -> bytes
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    return (x | (x << 4)) & 0x0F0F0F0Fu;
+}
+__device__ __forceinline__ unsigned tq_k_byte(unsigned b) { return (b & 0x07070707u) | ((b & 0x08080808u) << 4); }
+__device__ __forceinline__ int cache_slot(const int *slot_map, int seq) { return slot_map ? slot_map[seq] : seq; }
 
 __device__ __forceinline__ int qidx(int d) { return d + (d >> 5); }
 template <int GQ>
@@ -239,11 +257,12 @@ struct AttnSmem {  // per work item (128 threads)
 // issued before the barrier that publishes the query rotation and the new cache row, it turns the item's first cache
 // reads from HBM misses into L2 hits.
 __device__ __forceinline__ void tq_attention_l2_prefetch(int tid, const AttnParams &p, int kvh, int seq, int r0, int r1, int limit) {
-    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const size_t head_base = ((size_t)cache_slot(p.slot_map, seq) * p.nkv + kvh) * p.max_seq;
     const int nt = min(kTile, min(r1, limit) - r0);
-    if (tid < nt) {  // one 128-byte row of K and of V per thread
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kc + (head_base + r0 + tid) * kHd));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vc + (head_base + r0 + tid) * kHd));
+    const size_t rowb = (size_t)tq_row_bytes(p.bits, kHd);
+    if (tid < nt) {  // one row of K and of V per thread (a 128-byte line holds one 8-bit row or two 4-bit rows)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kc + (head_base + r0 + tid) * rowb));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vc + (head_base + r0 + tid) * rowb));
     } else if (tid >= 32 && tid < 35 && nt > 0) {  // the tile's scales: 32 floats = one line each
         const float *b = tid == 32 ? p.ks : (tid == 33 ? p.krn : p.vs);
         asm volatile("prefetch.global.L2 [%0];" ::"l"(b + head_base + r0));
@@ -273,7 +292,7 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
 
     // The K / V rows of a tile travel through registers: the first tile is requested before the queries are set
     // up, each further tile while its predecessor is being scored, so the cache latency overlaps other work.
-    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const size_t head_base = ((size_t)cache_slot(p.slot_map, seq) * p.nkv + kvh) * p.max_seq;
     const int pr = tid >> 2, part = tid & 3;  // loader: 32 rows x 128 bytes, 32 bytes per thread
     uint4 nk0, nk1, nv0, nv1;
     float n_ks = 0.0f, n_rw = 0.0f, n_vs = 0.0f;
@@ -281,12 +300,17 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         const int nt = min(kTile, r1 - ts);
         nk0 = nk1 = nv0 = nv1 = make_uint4(0, 0, 0, 0);
         if (pr < nt) {
-            const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
-            const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
-            nk0 = ldg_stream_v4(ksrc);
-            nk1 = ldg_stream_v4(ksrc + 1);
-            nv0 = ldg_stream_v4(vsrc);
-            nv1 = ldg_stream_v4(vsrc + 1);
+            if (p.bits == 4) {  // 64-byte rows: 16 bytes (32 elements) per thread, spread to bytes when stored
+                nk0 = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * (kHd / 2) + part * 16));
+                nv0 = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * (kHd / 2) + part * 16));
+            } else {
+                const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pr) * kHd + part * 32);
+                const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pr) * kHd + part * 32);
+                nk0 = ldg_stream_v4(ksrc);
+                nk1 = ldg_stream_v4(ksrc + 1);
+                nv0 = ldg_stream_v4(vsrc);
+                nv1 = ldg_stream_v4(vsrc + 1);
+            }
         }
         if (tid < kTile) {
             const bool ok = tid < nt;
@@ -342,7 +366,14 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         const int nt = min(kTile, r1 - ts);
         // ---- K goes to the tile buffer now, V waits in registers until the scores are done ----
         const uint4 v0 = nv0, v1 = nv1;
-        td[0] = nk0.x; td[1] = nk0.y; td[2] = nk0.z; td[3] = nk0.w; td[4] = nk1.x; td[5] = nk1.y; td[6] = nk1.z; td[7] = nk1.w;
+        if (p.bits == 4) {
+            td[0] = tq_k_byte(tq_spread4(nk0.x)); td[1] = tq_k_byte(tq_spread4(nk0.x >> 16));
+            td[2] = tq_k_byte(tq_spread4(nk0.y)); td[3] = tq_k_byte(tq_spread4(nk0.y >> 16));
+            td[4] = tq_k_byte(tq_spread4(nk0.z)); td[5] = tq_k_byte(tq_spread4(nk0.z >> 16));
+            td[6] = tq_k_byte(tq_spread4(nk0.w)); td[7] = tq_k_byte(tq_spread4(nk0.w >> 16));
+        } else {
+            td[0] = nk0.x; td[1] = nk0.y; td[2] = nk0.z; td[3] = nk0.w; td[4] = nk1.x; td[5] = nk1.y; td[6] = nk1.z; td[7] = nk1.w;
+        }
         if (tid < kTile) {
             sm.t_ks[tid] = n_ks;
             sm.t_rw[tid] = n_rw;
@@ -418,7 +449,12 @@ __device__ __forceinline__ void tq_attention_item(const Scope &sc, AttnSmem<GQ> 
         sc.sync();
 
         // ---- the V codes replace the K codes; online softmax: one warp per query head, lane = position ----
-        td[0] = v0.x; td[1] = v0.y; td[2] = v0.z; td[3] = v0.w; td[4] = v1.x; td[5] = v1.y; td[6] = v1.z; td[7] = v1.w;
+        if (p.bits == 4) {
+            td[0] = tq_spread4(v0.x); td[1] = tq_spread4(v0.x >> 16); td[2] = tq_spread4(v0.y); td[3] = tq_spread4(v0.y >> 16);
+            td[4] = tq_spread4(v0.z); td[5] = tq_spread4(v0.z >> 16); td[6] = tq_spread4(v0.w); td[7] = tq_spread4(v0.w >> 16);
+        } else {
+            td[0] = v0.x; td[1] = v0.y; td[2] = v0.z; td[3] = v0.w; td[4] = v1.x; td[5] = v1.y; td[6] = v1.z; td[7] = v1.w;
+        }
         for (int g = warp; g < GQ; g += kAttnThreads / 32) {
             const float s = sm.sc[lane * GQ + g];
             const float tm = warp_max(s);
@@ -473,6 +509,7 @@ struct PrepArgs {
     int nh, nkv, rotary_dim, with_norm, T, max_seq, base_pos;
     float eps;
     const int *pos_dev;
+    const int *slot_map;  // optional: sequence index -> cache slot (positions and cache rows are per slot)
     float *qrot;    // [nseq*T, nh, 2, hd]
     __half *q_out;  // optional dense roped q [nseq*T, nh, hd]
     EncodeTables ktab, vtab;
@@ -486,7 +523,7 @@ template <class Scope, class Proj>
 __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a, float *sh, int slot, int st, Proj &pj) {
     float *red = sh + 3 * kHd;
     const int d = sc.d;
-    const int seq = st / a.T, t = st % a.T;
+    const int seq = cache_slot(a.slot_map, st / a.T), t = st % a.T;  // from here on `seq` names the cache slot
     const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
     const __half *tok = a.qkv + (size_t)st * a.stride;
     const __half *tokkv = a.kv ? a.kv + (size_t)st * a.kv_stride : tok;
@@ -494,7 +531,7 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     if (slot >= a.nh + a.nkv) {  // value head
         const int h = slot - a.nh - a.nkv;
         const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(sc, __half2float(tokkv[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * kHd, a.vs + row, (float *)nullptr, sg);
+        tq_encode_body(sc, __half2float(tokkv[a.v_off + h * kHd + d]), a.vtab, sh, kHd, a.vc + row * tq_row_bytes(a.vtab.bits, kHd), a.vs + row, (float *)nullptr, sg);
         return;
     }
     const bool is_q = slot < a.nh;
@@ -528,7 +565,7 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     sc.sync();
     if (!is_q) {
         const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
-        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * kHd, a.ks + row, a.krn + row, sg, pj);
+        tq_encode_body(sc, __half2float(yh), a.ktab, sh, kHd, a.kc + row * tq_row_bytes(a.ktab.bits, kHd), a.ks + row, a.krn + row, sg, pj);
         return;
     }
     if (a.q_out) a.q_out[((size_t)st * a.nh + h) * kHd + d] = yh;

@@ -98,23 +98,28 @@ static void lloyd_max(int dim, int bits, std::vector<float> &levels, std::vector
 // ---------------------------------------------------------------- kernels: one CTA per work item
 // (the bodies live in tq_device.cuh, shared with the whole-token decode kernel)
 
-// grid (nkv, nseq*T), hd threads.
-__global__ void tq_encode_kernel(const __half *__restrict__ kv, const EncodeTables tb, uint8_t *__restrict__ cache,
+// grid (nseq*T, nkv), hd threads (tokens on x: a long prefill has more tokens than the y dimension holds).
+template <int BITS>
+__global__ void tq_encode_kernel(const __half *__restrict__ kv, const EncodeTables tb_in, uint8_t *__restrict__ cache,
                                  float *__restrict__ scale_buf, float *__restrict__ r_norms, int nkv, int hd, int max_seq, int base_pos,
                                  const int *__restrict__ pos_dev, int T) {
     extern __shared__ float sh[];
-    const int d = threadIdx.x, h = blockIdx.x, st = blockIdx.y;
+    const int d = threadIdx.x, h = blockIdx.y, st = blockIdx.x;
     const int seq = st / T, t = st % T;
     const int pos = (base_pos + (pos_dev ? pos_dev[seq] : 0) + t) % max_seq;
     const size_t row = ((size_t)seq * nkv + h) * max_seq + pos;
     const CtaScope sc{d, (int)blockDim.x};
-    tq_encode_body(sc, __half2float(kv[((size_t)st * nkv + h) * hd + d]), tb, sh, hd, cache + row * hd, scale_buf + row,
+    EncodeTables tb = tb_in;
+    tb.bits = BITS;  // a constant here: the packing branch of the body folds away
+    tq_encode_body(sc, __half2float(kv[((size_t)st * nkv + h) * hd + d]), tb, sh, hd, cache + row * tq_row_bytes(tb.bits, hd), scale_buf + row,
                    r_norms ? r_norms + row : nullptr);
 }
 
 // grid (nkv, nseq*T, splits), 128 threads.
-template <int GQ>
-__global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnParams p) {
+template <int GQ, int BITS>
+__global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnParams p_in) {
+    AttnParams p = p_in;
+    p.bits = BITS;  // a constant here: the cache-format branches of the body fold away
     __shared__ AttnSmem<GQ> sm;
     __shared__ float cbk[128];
     __shared__ float cbv[256];
@@ -124,27 +129,31 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
     pdl_wait();
     const int seq = st / p.T, t = st % p.T;
     // never past the end of the head's rows, whatever a device-side position says (the host can only check base_pos)
-    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1, p.max_seq);
+    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[cache_slot(p.slot_map, seq)] : 0) + t + 1, p.max_seq);
     const int chunk = (seq_len + p.splits - 1) / p.splits;
     const int r0 = split * chunk, r1 = min(r0 + chunk, seq_len);
-    cbk[tid] = p.k_cb[tid];
-    cbv[tid] = p.v_cb[tid];
-    cbv[tid + 128] = p.v_cb[tid + 128];
+    const int kl = 1 << (p.bits - 1), vl = 1 << p.bits;  // codebook sizes: K keeps one bit for the QJL sign
+    cbk[tid] = tid < kl ? p.k_cb[tid] : 0.0f;
+    cbv[tid] = tid < vl ? p.v_cb[tid] : 0.0f;
+    cbv[tid + 128] = tid + 128 < vl ? p.v_cb[tid + 128] : 0.0f;
     __syncthreads();
     const CtaScope sc{tid, kAttnThreads};
     tq_attention_item<GQ>(sc, sm, cbk, cbv, p, kvh, st, split, r0, r1);
 }
 
-// One launch between the QKV projection and the attention: grid (nh + 2 nkv, nseq*T), hd = 128 threads.
-__global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a) {
+// One launch between the QKV projection and the attention: grid (nseq*T, nh + 2 nkv), hd = 128 threads.
+template <int BITS>
+__global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a_in) {
     __shared__ float sh[3 * kHd + 4];
+    PrepArgs a = a_in;
+    a.ktab.bits = a.vtab.bits = BITS;
     pdl_trigger();
     pdl_wait();
     const CtaScope sc{(int)threadIdx.x, kHd};
-    tq_prep_item(sc, a, sh, blockIdx.x, blockIdx.y);
+    tq_prep_item(sc, a, sh, blockIdx.y, blockIdx.x);
 }
 
-// grid (nh, nseq*T), hd threads.
+// grid (nseq*T, nh), hd threads.
 __global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict__ po, const float *__restrict__ pm,
                                                         const float *__restrict__ pl, const float *__restrict__ signs,
                                                         __half *__restrict__ out, int nh, int splits) {
@@ -152,7 +161,7 @@ __global__ void __launch_bounds__(kHd) tq_reduce_kernel(const float *__restrict_
     pdl_trigger();
     pdl_wait();
     const CtaScope sc{(int)threadIdx.x, kHd};
-    tq_reduce_item(sc, x, po, pm, pl, signs, out, (size_t)blockIdx.y * nh + blockIdx.x, splits, splits);
+    tq_reduce_item(sc, x, po, pm, pl, signs, out, (size_t)blockIdx.x * nh + blockIdx.y, splits, splits);
 }
 
 
@@ -177,8 +186,10 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1,
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ unsigned lut_at(unsigned lane_base, unsigned w, int byte) {  // table word of byte `byte` of w for this lane
-    const unsigned b = __byte_perm(w, 0, 0x4440 + byte);
+// table word of element `idx` of cache word w for this lane: bytes (BITS = 8, idx 0-3) or nibbles (BITS = 4, idx 0-7)
+template <int BITS>
+__device__ __forceinline__ unsigned lut_at(unsigned lane_base, unsigned w, int idx) {
+    const unsigned b = BITS == 8 ? __byte_perm(w, 0, 0x4440 + idx) : ((w >> (4 * idx)) & 15u);
     unsigned v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(b * 128u + lane_base));
     return v;
@@ -188,8 +199,9 @@ __device__ __forceinline__ unsigned pack_h2(float a, float b) {
     return *reinterpret_cast<const unsigned *>(&h);
 }
 
-template <int GQ>
+template <int GQ, int BITS>
 __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const AttnParams p) {
+    constexpr int kRowB = BITS == 4 ? kHd / 2 : kHd;  // bytes of a cached row
     extern __shared__ __align__(16) unsigned char tc_smem[];
     unsigned *lutk = reinterpret_cast<unsigned *>(tc_smem);        // [256][32]: (centroid, sign) fp16 pair
     unsigned *lutv = lutk + 256 * 32;                               // [256][32]: (centroid, 0)
@@ -200,9 +212,10 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
     const int kvh = blockIdx.x, st = blockIdx.y, split = blockIdx.z;
     pdl_trigger();
     {   // tables (constants): before the dependency wait
-        const int b = tid;  // 256 threads, one byte value each
-        const __half2 ke = __floats2half2_rn(p.k_cb[b & 127], (b & 0x80) ? 1.0f : -1.0f);
-        const __half2 ve = __floats2half2_rn(p.v_cb[b], 0.0f);
+        const int b = tid;  // 256 threads, one stored value each (4-bit caches use the first 16 entries)
+        constexpr int kSign = 1 << (BITS - 1), kVals = 1 << BITS;
+        const __half2 ke = __floats2half2_rn(p.k_cb[b & (kSign - 1)], (b & kSign) ? 1.0f : -1.0f);
+        const __half2 ve = __floats2half2_rn(p.v_cb[b & (kVals - 1)], 0.0f);
         const unsigned ku = *reinterpret_cast<const unsigned *>(&ke), vu = *reinterpret_cast<const unsigned *>(&ve);
         uint4 *dk = reinterpret_cast<uint4 *>(lutk + b * 32), *dv = reinterpret_cast<uint4 *>(lutv + b * 32);
 #pragma unroll
@@ -215,14 +228,15 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
     __syncthreads();
 
     const int seq = st / p.T, tt = st % p.T;
-    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + tt + 1, p.max_seq);  // see tq_attention_kernel
+    const int slot = cache_slot(p.slot_map, seq);
+    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[slot] : 0) + tt + 1, p.max_seq);  // see tq_attention_kernel
     const int chunk = (seq_len + p.splits - 1) / p.splits;
     const int c0 = split * chunk, c1 = min(c0 + chunk, seq_len);
     // this warp's run: whole tiles of the split's range
     const int tiles = (max(c1 - c0, 0) + kTile - 1) / kTile, per = (tiles + kTcWarps - 1) / kTcWarps;
     const int r0 = c0 + warp * per * kTile, r1 = min(c1, r0 + per * kTile);
     const int h0 = kvh * GQ;
-    const size_t head_base = ((size_t)seq * p.nkv + kvh) * p.max_seq;
+    const size_t head_base = ((size_t)slot * p.nkv + kvh) * p.max_seq;
     const unsigned lk = (unsigned)__cvta_generic_to_shared(lutk) + lane * 4u, lv = (unsigned)__cvta_generic_to_shared(lutv) + lane * 4u;
 
     // B fragments of the score products: lane (n = g, t) holds dims 32 t + 4 j + {0..3} of column n: the rotated query
@@ -250,18 +264,19 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
 
     for (int ts = r0; ts < r1; ts += kTile) {
         const int nt = min(kTile, r1 - ts);
-        // ---- K rows g, g+8, g+16, g+24 of the tile: 32 bytes (dims 32t .. 32t+31) each ----
-        uint4 kq[4][2];
+        // ---- K rows g, g+8, g+16, g+24 of the tile: dims 32t .. 32t+31 each (32 bytes, or 16 bytes of nibbles) ----
+        uint4 kq[4][BITS == 8 ? 2 : 1];
         float ksv[4], rwv[4], vsv[4];
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int pos = g + 8 * r;
-            kq[r][0] = kq[r][1] = make_uint4(0, 0, 0, 0);
+            kq[r][0] = make_uint4(0, 0, 0, 0);
+            if (BITS == 8) kq[r][BITS == 8 ? 1 : 0] = make_uint4(0, 0, 0, 0);
             ksv[r] = rwv[r] = vsv[r] = 0.0f;
             if (pos < nt) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pos) * kHd + 32 * t);
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.kc + (head_base + ts + pos) * kRowB + (kRowB / 4) * t);
                 kq[r][0] = ldg_stream_v4(src);
-                kq[r][1] = ldg_stream_v4(src + 1);
+                if (BITS == 8) kq[r][BITS == 8 ? 1 : 0] = ldg_stream_v4(src + 1);
                 ksv[r] = p.ks[head_base + ts + pos];
                 rwv[r] = p.krn[head_base + ts + pos] * p.qjl_factor;
                 vsv[r] = p.vs[head_base + ts + pos];
@@ -275,10 +290,12 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
             const unsigned *wa = reinterpret_cast<const unsigned *>(&kq[2 * rb][0]);      // row g + 16 rb
             const unsigned *wb = reinterpret_cast<const unsigned *>(&kq[2 * rb + 1][0]);  // row g + 8 + 16 rb
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const unsigned a = wa[j], b = wb[j];
-                const unsigned la0 = lut_at(lk, a, 0), la1 = lut_at(lk, a, 1), la2 = lut_at(lk, a, 2), la3 = lut_at(lk, a, 3);
-                const unsigned lb0 = lut_at(lk, b, 0), lb1 = lut_at(lk, b, 1), lb2 = lut_at(lk, b, 2), lb3 = lut_at(lk, b, 3);
+            for (int j = 0; j < 8; j++) {  // dims 32 t + 4 j + {0..3}: word j (bytes), or half of word j / 2 (nibbles)
+                const unsigned a = BITS == 8 ? wa[j] : wa[j >> 1], b = BITS == 8 ? wb[j] : wb[j >> 1];
+                constexpr int e1 = 1, e2 = 2, e3 = 3;
+                const int e0 = BITS == 8 ? 0 : (j & 1) * 4;
+                const unsigned la0 = lut_at<BITS>(lk, a, e0), la1 = lut_at<BITS>(lk, a, e0 + e1), la2 = lut_at<BITS>(lk, a, e0 + e2), la3 = lut_at<BITS>(lk, a, e0 + e3);
+                const unsigned lb0 = lut_at<BITS>(lk, b, e0), lb1 = lut_at<BITS>(lk, b, e0 + e1), lb2 = lut_at<BITS>(lk, b, e0 + e2), lb3 = lut_at<BITS>(lk, b, e0 + e3);
                 // centroids in the low halves, signs in the high halves
                 mma_f16(c, __byte_perm(la0, la1, 0x5410), __byte_perm(lb0, lb1, 0x5410), __byte_perm(la2, la3, 0x5410),
                         __byte_perm(lb2, lb3, 0x5410), is_c ? bx[2 * j] : 0u, is_c ? bx[2 * j + 1] : 0u);
@@ -287,13 +304,21 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
             }
             sc[rb][0] = c[0]; sc[rb][1] = c[1]; sc[rb][2] = c[2]; sc[rb][3] = c[3];
         }
-        // ---- V rows 2t, 2t+1, 2t+8, 2t+9 (+16): 16 bytes (dims 16g .. 16g+15) each ----
+        // ---- V rows 2t, 2t+1, 2t+8, 2t+9 (+16): dims 16g .. 16g+15 each (16 bytes, or 8 bytes of nibbles in .x/.y) ----
         uint4 vq[8];
 #pragma unroll
         for (int r = 0; r < 8; r++) {
             const int pos = 2 * t + (r & 1) + 8 * ((r >> 1) & 1) + 16 * (r >> 2);
             vq[r] = make_uint4(0, 0, 0, 0);
-            if (pos < nt) vq[r] = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pos) * kHd + 16 * g));
+            if (pos < nt) {
+                if (BITS == 8) {
+                    vq[r] = ldg_stream_v4(reinterpret_cast<const uint4 *>(p.vc + (head_base + ts + pos) * kRowB + 16 * g));
+                } else {
+                    const uint2 v2 = __ldcs(reinterpret_cast<const uint2 *>(p.vc + (head_base + ts + pos) * kRowB + 8 * g));
+                    vq[r].x = v2.x;
+                    vq[r].y = v2.y;
+                }
+            }
         }
 
         // lanes t < 2 hold the centroid sums of heads 2t, 2t+1; lanes t + 2 the sign sums of the same heads
@@ -358,9 +383,9 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
             const unsigned *v3 = reinterpret_cast<const unsigned *>(&vq[4 * kb + 3]);  // + 9
 #pragma unroll
             for (int mb = 0; mb < 8; mb++) {  // rows g, g + 8 of the block: dims 16 g + 2 mb, + 1
-                const int w = mb >> 1, by = 2 * (mb & 1);
-                const unsigned e00 = lut_at(lv, v0[w], by), e01 = lut_at(lv, v1[w], by), e10 = lut_at(lv, v0[w], by + 1), e11 = lut_at(lv, v1[w], by + 1);
-                const unsigned f00 = lut_at(lv, v2[w], by), f01 = lut_at(lv, v3[w], by), f10 = lut_at(lv, v2[w], by + 1), f11 = lut_at(lv, v3[w], by + 1);
+                const int w = BITS == 8 ? mb >> 1 : mb >> 2, by = BITS == 8 ? 2 * (mb & 1) : 2 * (mb & 3);
+                const unsigned e00 = lut_at<BITS>(lv, v0[w], by), e01 = lut_at<BITS>(lv, v1[w], by), e10 = lut_at<BITS>(lv, v0[w], by + 1), e11 = lut_at<BITS>(lv, v1[w], by + 1);
+                const unsigned f00 = lut_at<BITS>(lv, v2[w], by), f01 = lut_at<BITS>(lv, v3[w], by), f10 = lut_at<BITS>(lv, v2[w], by + 1), f11 = lut_at<BITS>(lv, v3[w], by + 1);
                 mma_f16(o[mb], __byte_perm(e00, e01, 0x5410), __byte_perm(e10, e11, 0x5410), __byte_perm(f00, f01, 0x5410),
                         __byte_perm(f10, f11, 0x5410), b0, b1);
             }
@@ -412,14 +437,14 @@ __global__ void __launch_bounds__(kTcWarps * 32, 2) tq_attention_tc_kernel(const
 constexpr size_t kTcSmem = 2 * 256 * 32 * 4 + kTcWarps * 4 * 32 * 2 + kTcWarps * 4 * 130 * 4;
 
 // Rotated query and S * rotated query for every (token, head), computed once instead of once per split:
-// grid (nh, nseq*T), 128 threads.  q fp16 [nseq*T, nh, 128] -> qrot f32 [nseq*T, nh, 2, 128].
+// grid (nseq*T, nh), 128 threads.  q fp16 [nseq*T, nh, 128] -> qrot f32 [nseq*T, nh, 2, 128].
 __global__ void __launch_bounds__(kHd) tq_qrot_kernel(const __half *__restrict__ q, const float *__restrict__ signs,
                                                       const float *__restrict__ qjl_t, float *__restrict__ qrot, int nh) {
     __shared__ float sh[2 * kHd];
     pdl_trigger();
     pdl_wait();
     const int d = threadIdx.x;
-    const size_t hi = (size_t)blockIdx.y * nh + blockIdx.x;
+    const size_t hi = (size_t)blockIdx.x * nh + blockIdx.y;
     const CtaScope sc{d, kHd};
     const float rq = hadamard_thread(sc, __half2float(q[hi * kHd + d]), signs[d], sh + kHd, kHd);
     sh[d] = rq;
@@ -501,7 +526,7 @@ IM_EXPORT int im_cuda_tq_create(im_device *dev, int head_dim, int n_bits, const 
     IM_GUARD_BEGIN
     IM_REQUIRE(dev && out, "bad argument");
     *out = nullptr;
-    IM_REQUIRE(n_bits == 8, "only the 8-bit TurboQuant cache is built (n_bits = %d)", n_bits);
+    IM_REQUIRE(n_bits == 8 || n_bits == 4, "n_bits must be 4 or 8, got %d", n_bits);
     IM_REQUIRE(head_dim >= 32 && head_dim <= 1024 && (head_dim & (head_dim - 1)) == 0, "head_dim must be a power of two in 32..1024");
     IM_REQUIRE(signs_host && qjl_host, "signs and QJL matrix are required");
     IM_CUDA_CHECK(cudaSetDevice(dev->ordinal));
@@ -561,10 +586,11 @@ IM_EXPORT int im_cuda_tq_encode(const im_tq *tq, const void *kv_dev, int is_k, v
     IM_REQUIRE(!is_k || r_norms_dev, "the K cache needs a residual-norm buffer");
     IM_REQUIRE(nseq >= 0 && nkv > 0 && max_seq > 0 && base_pos >= 0 && T >= 0, "bad shape");
     if (nseq == 0 || T == 0) return IM_OK;
-    dim3 grid(nkv, nseq * T);
+    dim3 grid(nseq * T, nkv);
     const int hd = tq->hd;
-    EncodeTables tb{tq->signs, is_k ? tq->k_cb : tq->v_cb, is_k ? tq->k_bd : tq->v_bd, tq->qjl_t, is_k ? tq->k_levels : tq->v_levels, is_k};
-    tq_encode_kernel<<<grid, hd, 3 * hd * sizeof(float), as_stream(stream)>>>(
+    EncodeTables tb{tq->signs, is_k ? tq->k_cb : tq->v_cb, is_k ? tq->k_bd : tq->v_bd, tq->qjl_t, is_k ? tq->k_levels : tq->v_levels, is_k, tq->n_bits};
+    auto kern = tq->n_bits == 4 ? tq_encode_kernel<4> : tq_encode_kernel<8>;
+    kern<<<grid, hd, 3 * hd * sizeof(float), as_stream(stream)>>>(
         static_cast<const __half *>(kv_dev), tb, static_cast<uint8_t *>(cache_dev), scale_dev, r_norms_dev, nkv, hd, max_seq, base_pos, pos_dev, T);
     IM_CUDA_CHECK(cudaGetLastError());
     return IM_OK;
@@ -603,13 +629,13 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
     k.qkv = a.qkv; k.stride = a.stride; k.k_off = a.k_off; k.v_off = a.v_off; k.kv = a.kv; k.kv_stride = a.kv_stride;
     k.qw = a.qw; k.kw = a.kw; k.cosc = a.cosc; k.sinc = a.sinc;
     k.nh = a.nh; k.nkv = a.nkv; k.rotary_dim = a.rotary_dim ? a.rotary_dim : kHd; k.with_norm = a.with_norm;
-    k.T = a.T; k.max_seq = a.max_seq; k.base_pos = a.base_pos; k.eps = a.eps; k.pos_dev = a.pos_dev;
+    k.T = a.T; k.max_seq = a.max_seq; k.base_pos = a.base_pos; k.eps = a.eps; k.pos_dev = a.pos_dev; k.slot_map = a.slot_map;
     k.qrot = a.qrot; k.q_out = a.q_out;
-    k.ktab = EncodeTables{tq->signs, tq->k_cb, tq->k_bd, tq->qjl_t, tq->k_levels, 1};
-    k.vtab = EncodeTables{tq->signs, tq->v_cb, tq->v_bd, tq->qjl_t, tq->v_levels, 0};
+    k.ktab = EncodeTables{tq->signs, tq->k_cb, tq->k_bd, tq->qjl_t, tq->k_levels, 1, tq->n_bits};
+    k.vtab = EncodeTables{tq->signs, tq->v_cb, tq->v_bd, tq->qjl_t, tq->v_levels, 0, tq->n_bits};
     k.kc = a.kc; k.vc = a.vc; k.ks = a.ks; k.vs = a.vs; k.krn = a.krn;
-    dim3 grid(a.nh + 2 * a.nkv, a.nseq * a.T);
-    IM_CUDA_CHECK(launch_k(tq_qkv_prep_kernel, grid, dim3(kHd), 0, st, k));
+    dim3 grid(a.nseq * a.T, a.nh + 2 * a.nkv);
+    IM_CUDA_CHECK(launch_k(tq->n_bits == 4 ? tq_qkv_prep_kernel<4> : tq_qkv_prep_kernel<8>, grid, dim3(kHd), 0, st, k));
     return IM_OK;
 }
 
@@ -624,9 +650,11 @@ int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
 
 int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,
                         const float *vs, const float *krn, float attn_scale, __half *out, int nseq, int nh, int nkv, int max_seq,
-                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot) {
+                        int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot, const int *slot_map) {
     AttnParams p{};
     p.qrot = qrot;
+    p.slot_map = slot_map;
+    p.bits = tq->n_bits;
     p.q = q; p.kc = kc; p.vc = vc; p.ks = ks; p.vs = vs; p.krn = krn;
     p.signs = tq->signs; p.qjl = tq->qjl_t; p.k_cb = tq->k_cb; p.v_cb = tq->v_cb;
     const size_t rows = (size_t)nseq * T * nh * splits;
@@ -636,28 +664,36 @@ int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uin
     p.attn_scale = attn_scale;
     p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)tq->hd;
     p.nh = nh; p.nkv = nkv; p.max_seq = max_seq; p.base_pos = base_pos; p.T = T; p.splits = splits; p.pos_dev = pos_dev;
+    if ((long long)nseq * T > 65535) return fail(IM_ERR_BOUNDS, "attention takes at most 65535 (sequence, token) pairs per call, got %lld", (long long)nseq * T);
     dim3 grid(nkv, nseq * T, splits);
     const int gq = nh / nkv;
     if (qrot && (gq == 1 || gq == 2 || gq == 4) && nh % nkv == 0) {  // tensor-core kernel (needs the rotated queries)
         static DeviceOnce once;
-        if (once.first(tq->dev->ordinal)) {  // the three instantiations share one function-pointer type: set them all once
-            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
-            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
-            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+        if (once.first(tq->dev->ordinal)) {  // the instantiations share one function-pointer type: set them all once
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+            IM_CUDA_CHECK(cudaFuncSetAttribute(tq_attention_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
         }
-        auto kern = gq == 1 ? tq_attention_tc_kernel<1> : (gq == 2 ? tq_attention_tc_kernel<2> : tq_attention_tc_kernel<4>);
+        auto kern = tq->n_bits == 4 ? (gq == 1 ? tq_attention_tc_kernel<1, 4> : (gq == 2 ? tq_attention_tc_kernel<2, 4> : tq_attention_tc_kernel<4, 4>))
+                                    : (gq == 1 ? tq_attention_tc_kernel<1, 8> : (gq == 2 ? tq_attention_tc_kernel<2, 8> : tq_attention_tc_kernel<4, 8>));
         int rc = IM_OK;
         IM_CUDA_CHECK(launch_k(kern, grid, dim3(kTcWarps * 32), kTcSmem, st, p));
         if (rc != IM_OK) return rc;
     } else
-    switch (nh / nkv) {
-        case 1: IM_CUDA_CHECK(launch_k(tq_attention_kernel<1>, grid, dim3(kAttnThreads), 0, st, p)); break;
-        case 2: IM_CUDA_CHECK(launch_k(tq_attention_kernel<2>, grid, dim3(kAttnThreads), 0, st, p)); break;
-        case 4: IM_CUDA_CHECK(launch_k(tq_attention_kernel<4>, grid, dim3(kAttnThreads), 0, st, p)); break;
-        case 8: IM_CUDA_CHECK(launch_k(tq_attention_kernel<8>, grid, dim3(kAttnThreads), 0, st, p)); break;
-        default: return fail(IM_ERR_INVALID, "query heads per KV head must be 1, 2, 4 or 8 (got %d/%d)", nh, nkv);
+    {
+        const bool b4 = tq->n_bits == 4;
+        switch (nh / nkv) {
+            case 1: IM_CUDA_CHECK(launch_k(b4 ? tq_attention_kernel<1, 4> : tq_attention_kernel<1, 8>, grid, dim3(kAttnThreads), 0, st, p)); break;
+            case 2: IM_CUDA_CHECK(launch_k(b4 ? tq_attention_kernel<2, 4> : tq_attention_kernel<2, 8>, grid, dim3(kAttnThreads), 0, st, p)); break;
+            case 4: IM_CUDA_CHECK(launch_k(b4 ? tq_attention_kernel<4, 4> : tq_attention_kernel<4, 8>, grid, dim3(kAttnThreads), 0, st, p)); break;
+            case 8: IM_CUDA_CHECK(launch_k(b4 ? tq_attention_kernel<8, 4> : tq_attention_kernel<8, 8>, grid, dim3(kAttnThreads), 0, st, p)); break;
+            default: return fail(IM_ERR_INVALID, "query heads per KV head must be 1, 2, 4 or 8 (got %d/%d)", nh, nkv);
+        }
     }
-    dim3 rgrid(nh, nseq * T);
+    dim3 rgrid(nseq * T, nh);
     IM_CUDA_CHECK(launch_k(tq_reduce_kernel, rgrid, dim3(kHd), 0, st, (const float *)p.po, (const float *)p.pm, (const float *)p.pl,
                            (const float *)tq->signs, out, nh, splits));
     return IM_OK;
@@ -685,7 +721,7 @@ IM_EXPORT int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_c
     }
     // rotate the queries once (every split of a head would otherwise redo the rotation and the 128 x 128 projection)
     float *qrot = tq->scratch + tq_partial_bytes(nseq, T, nh, kHd, splits) / sizeof(float);
-    IM_CUDA_CHECK(launch_k(tq_qrot_kernel, dim3(nh, nseq * T), dim3(kHd), 0, as_stream(stream), static_cast<const __half *>(q_dev),
+    IM_CUDA_CHECK(launch_k(tq_qrot_kernel, dim3(nseq * T, nh), dim3(kHd), 0, as_stream(stream), static_cast<const __half *>(q_dev),
                            (const float *)tq->signs, (const float *)tq->qjl_t, qrot, nh));
     return tq_attention_launch(tq, tq->scratch, nullptr, static_cast<const uint8_t *>(k_cache_dev),
                                static_cast<const uint8_t *>(v_cache_dev), k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale,
@@ -763,16 +799,24 @@ IM_EXPORT int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, co
         IM_CUDA_CHECK(cudaGetSymbolAddress((void **)&ptr, g_static_attn_scratch));
         g_static_attn_ptr[cur] = ptr;
     }
-    const int splits = num_splits > 0 ? num_splits : tq_auto_splits(tq->dev, nseq, T, nkv, base_pos + T);
-    const size_t need = tq_partial_bytes(nseq, T, nh, kHd, splits);
+    // The array holds what im_cuda_tq_attention keeps in its allocated scratch: the split partials, then the rotated
+    // queries of the pre-pass (so both entry points run the same kernels).  A split count chosen here shrinks until
+    // the request fits; one given by the caller is taken as it is or refused.
+    int splits = num_splits > 0 ? num_splits : tq_auto_splits(tq->dev, nseq, T, nkv, base_pos + T);
+    while (num_splits <= 0 && splits > 1 && im_cuda_tq_scratch_bytes(nseq, T, nh, kHd, splits) > kStaticScratchFloats * sizeof(float)) splits--;
+    const size_t need = im_cuda_tq_scratch_bytes(nseq, T, nh, kHd, splits);
     if (need > kStaticScratchFloats * sizeof(float))
         return fail(IM_ERR_BOUNDS,
-                    "%d sequence(s) x %d token(s) x %d heads x %d splits need %zu bytes of split partials; the built-in scratch holds %zu "
-                    "(use fewer splits or im_cuda_tq_attention)",
+                    "%d sequence(s) x %d token(s) x %d heads x %d splits need %zu bytes of split partials and rotated queries; the built-in "
+                    "scratch holds %zu (use fewer splits or im_cuda_tq_attention)",
                     nseq, T, nh, splits, need, kStaticScratchFloats * sizeof(float));
     // Nothing has to start at zero: every split, empty ones included, writes its whole partial before the reduce reads it.
-    return tq_attention_launch(tq, g_static_attn_ptr[cur], static_cast<const __half *>(q_dev), static_cast<const uint8_t *>(k_cache_dev),
+    float *scratch = g_static_attn_ptr[cur];
+    float *qrot = scratch + tq_partial_bytes(nseq, T, nh, kHd, splits) / sizeof(float);
+    IM_CUDA_CHECK(launch_k(tq_qrot_kernel, dim3(nseq * T, nh), dim3(kHd), 0, as_stream(stream), static_cast<const __half *>(q_dev),
+                           (const float *)tq->signs, (const float *)tq->qjl_t, qrot, nh));
+    return tq_attention_launch(tq, scratch, nullptr, static_cast<const uint8_t *>(k_cache_dev),
                                static_cast<const uint8_t *>(v_cache_dev), k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale,
-                               static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream));
+                               static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, splits, as_stream(stream), qrot);
     IM_GUARD_END
 }

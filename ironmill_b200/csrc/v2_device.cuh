@@ -73,23 +73,65 @@ __device__ __forceinline__ void mma_u8s8_z(int (&c)[4], unsigned a0, unsigned a1
 }
 
 // The arithmetic of the consumer warps: two tiles (16 rows x 128 columns of 4-bit codes each) against the staged
-// activations of their groups, then the per-(row, group) float fix-up  s * sx * (sum_k xi_k q_k - z * sum_k xi_k)
-// (with meta = (sx / 16, 16 * sum_k xi_k): the integer dot product arrives multiplied by 16, see pair()).
-// Lane (g = lane >> 2, t = lane & 3) holds rows g and g + 8 of batch row t in acc0 / acc1.
+// activations of their groups, then the per-(row, group) float fix-up.
+//
+// Activations are staged once per CTA as 24-bit integers per group of 128 (xi = round(x * 8355711 / amax), so that all
+// three signed bytes of xi stay in [-127, 127]): the rounding is at the level of f32 arithmetic itself, the integer dot
+// products are exact.  A batch row occupies four B columns of the m16n8k32 product: high, middle, low byte and a zero
+// column; up to two batch rows share a product (eight columns), four batch rows take two.  In the accumulator, lane
+// (g = lane >> 2, t = lane & 3) holds rows g and g + 8 of columns 2t and 2t + 1: even t = (high, middle) bytes of batch
+// row t / 2, odd t = (low byte, zero).  Both kinds of lane run the same fix-up
+//     acc += s * m.x * (256 * v_first + v_second - z * m.y),     v = 16 * (low-nibble sum) + (high-nibble sum as 16 q)
+// with their own staged constants m = meta[(group * NB + batch row) * 2 + (t & 1)]:
+//     even: (sx * 16, sum(xi) / 16)     odd: (sx / 4096, 0)           (sx = amax / 8355711)
+// which add up to s * sx * (sum_k xi_k q_k - z * sum_k xi_k).  row_sums() folds the two lanes of a batch row together.
 // The activation fragments of a group stay in registers until the warp is handed another group: with K = 4096 a
 // stage is a whole row block, every warp sees the same two groups stage after stage, and the fragments are read
 // from shared memory once per projection.
+// Staged layout: xq words, index ((grp * 3 NB + 3 b + c) * 4 + t) * 8 + j * 2 + eo, byte plane c = 0 high, 1 middle, 2 low.
+constexpr int kActTop = 8355711;  // 0x7F7F7F: the largest staged magnitude
 template <int NB>
 struct TileMath {
-    uint4 xa0, xa1, xb0, xb1;  // B fragments of the groups ga / gb (words of columns 2b = high bytes, 2b + 1 = low bytes)
+    static constexpr int kSets = (NB + 1) / 2;  // column sets of up to two batch rows
+    uint4 xa0[kSets], xa1[kSets], xb0[kSets], xb1[kSets];  // B fragments of the groups ga / gb
     int ga, gb;
-    float acc0, acc1;
+    float acc0[kSets], acc1[kSets];
     __device__ __forceinline__ void reset() {  // new activations were staged
         ga = gb = -1;
-        acc0 = acc1 = 0.0f;
-        xa0 = xa1 = xb0 = xb1 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int s = 0; s < kSets; s++) {
+            acc0[s] = acc1[s] = 0.0f;
+            xa0[s] = xa1[s] = xb0[s] = xb1[s] = make_uint4(0, 0, 0, 0);
+        }
     }
-    // xq words: index ((grp*2NB + col)*4 + t)*8 ..; meta[grp*NB + b] = (scale, sum of the 128 integers)
+    __device__ __forceinline__ void clear_sums() {
+#pragma unroll
+        for (int s = 0; s < kSets; s++) acc0[s] = acc1[s] = 0.0f;
+    }
+    __device__ __forceinline__ void load_frag(const uint32_t *xq, int grp, int g, int t, uint4 (&x0)[kSets], uint4 (&x1)[kSets]) {
+#pragma unroll
+        for (int s = 0; s < kSets; s++) {
+            const int b = 2 * s + (g >> 2), c = g & 3;  // this lane's column: byte plane c of batch row b (c = 3: the zero column)
+            if (c < 3 && b < NB) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp * 3 * NB + 3 * b + c) * 4 + t) * 8);
+                x0[s] = xp[0];
+                x1[s] = xp[1];
+            }
+        }
+    }
+    __device__ __forceinline__ void fix_up(const int (&cl)[4], const int (&ch)[4], const unsigned char *tile, int grp, const float2 *meta,
+                                           int s, int g, int t) {
+        const int b = 2 * s + (t >> 1);
+        if (b < NB) {
+            const float2 m = meta[(grp * NB + b) * 2 + (t & 1)];
+            const __half2 *szp = reinterpret_cast<const __half2 *>(tile + kTileCodeBytes);
+            const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+            const float f0 = fmaf((float)(cl[0] * 16 + ch[0]), 256.0f, (float)(cl[1] * 16 + ch[1]));
+            const float f1 = fmaf((float)(cl[2] * 16 + ch[2]), 256.0f, (float)(cl[3] * 16 + ch[3]));
+            acc0[s] = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0[s]);
+            acc1[s] = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1[s]);
+        }
+    }
     __device__ __forceinline__ void pair(const unsigned char *tile_a, int grp_a, const unsigned char *tile_b, int grp_b, bool have_b,
                                          const uint32_t *xq, const float2 *meta, int lane) {
         const int g = lane >> 2, t = lane & 3;
@@ -102,134 +144,83 @@ struct TileMath {
         }
         if (grp_a != ga) {  // warp-uniform
             ga = grp_a;
-            if (g < 2 * NB) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_a * 2 * NB + g) * 4 + t) * 8);
-                xa0 = xp[0];
-                xa1 = xp[1];
-            }
+            load_frag(xq, grp_a, g, t, xa0, xa1);
         }
         if (have_b && grp_b != gb) {
             gb = grp_b;
-            if (g < 2 * NB) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xq + (((size_t)grp_b * 2 * NB + g) * 4 + t) * 8);
-                xb0 = xp[0];
-                xb1 = xp[1];
-            }
+            load_frag(xq, grp_b, g, t, xb0, xb1);
         }
         // Low and high nibbles go to separate accumulators: the low ones masked in place, the high ones masked in place
         // too (a byte 16 q, still a valid u8), so a word costs two logic operations and no shift.  The two chains are
         // independent; the fix-up adds them as 16 * low + high16, and the staged activation scale carries the 1/16.
         // B columns of a group: words (even positions, odd positions) of each 8-byte chunk: the low nibbles of a code
         // word are the even columns, the high nibbles the odd ones.
-        int cal[4], cah[4], cbl[4], cbh[4];
         constexpr unsigned ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
-        mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, xa0.x, xa0.z);
-        mma_u8s8_z(cbl, b0.x & ML, b1.x & ML, b0.y & ML, b1.y & ML, xb0.x, xb0.z);
-        mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, xa0.y, xa0.w);
-        mma_u8s8_z(cbh, b0.x & MH, b1.x & MH, b0.y & MH, b1.y & MH, xb0.y, xb0.w);
-        mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, xa1.x, xa1.z);
-        mma_u8s8(cbl, b0.z & ML, b1.z & ML, b0.w & ML, b1.w & ML, xb1.x, xb1.z);
-        mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, xa1.y, xa1.w);
-        mma_u8s8(cbh, b0.z & MH, b1.z & MH, b0.w & MH, b1.w & MH, xb1.y, xb1.w);
-        if (t < NB) {
-            {
-                const float2 m = meta[grp_a * NB + t];
-                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_a + kTileCodeBytes);
-                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)(cal[0] * 4096 + (cal[1] * 16 + (cah[0] * 256 + cah[1]))), f1 = (float)(cal[2] * 4096 + (cal[3] * 16 + (cah[2] * 256 + cah[3])));
-                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-            }
-            if (have_b) {
-                const float2 m = meta[grp_b * NB + t];
-                const __half2 *szp = reinterpret_cast<const __half2 *>(tile_b + kTileCodeBytes);
-                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
-                const float f0 = (float)(cbl[0] * 4096 + (cbl[1] * 16 + (cbh[0] * 256 + cbh[1]))), f1 = (float)(cbl[2] * 4096 + (cbl[3] * 16 + (cbh[2] * 256 + cbh[3])));
-                acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-                acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
-            }
-        }
-    }
-};
-
-// The same arithmetic on a STRIP: SG = 4 / NB consecutive tiles (groups grp0 .. grp0 + SG - 1) of one row block,
-// walked by one warp with ONE pair of accumulators.  An m16n8k32 product has eight B columns and a tile needs only
-// 2 NB of them (high and low activation bytes per batch row), so tile j of the strip puts its activations in columns
-// 2 NB j .. 2 NB j + 2 NB - 1 and zeros elsewhere: the accumulator then holds the integer dot products of SG different
-// (row, group) pairs side by side, every lane owns one of them (rows g and g + 8 of group grp0 + t / NB, batch row
-// t % NB), and the float fix-up runs once per strip with all 32 lanes busy instead of once per tile with 8 NB of them.
-// A lane feeds column g = lane >> 2: it reads its fragment of the staged activations for the one tile of the strip
-// whose columns it owns and a block of zeros for the others (an address select, no register copies).
-// acc0 / acc1: this lane's share of rows g / g + 8 (batch row t % NB); row_sums() folds the lanes of a row together.
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-template <int NB>
-struct StripMath {
-    static constexpr int SG = 4 / NB;
-    float acc0, acc1;
-    __device__ __forceinline__ void reset() { acc0 = acc1 = 0.0f; }
-    // tiles: shared-memory address of the strip's first tile; ntiles (1 .. SG, warp-uniform) tiles are present;
-    // xq / meta: the staged activations (layout of v2_stage_x); zero32: 32 bytes of zeros in shared memory.
-    __device__ __forceinline__ void strip(uint32_t tiles, int grp0, int ntiles, uint32_t xq, const float2 *meta, uint32_t zero32, int lane) {
-        const int g = lane >> 2, t = lane & 3;
-        const int jm = g / (2 * NB), col = g % (2 * NB);
-        const uint32_t xmine = xq + (uint32_t)(((((grp0 + jm) * 2 * NB + col) * 4 + t) * 8) * 4);
-        constexpr unsigned ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
-        int cal[4], cah[4];
 #pragma unroll
-        for (int j = 0; j < SG; j++) {
-            if (j < ntiles) {
-                const uint32_t tl = tiles + (uint32_t)(j * kTileBytes + lane * 16);
-                const uint4 a0 = lds128(tl), a1 = lds128(tl + 512);
-                const uint32_t xp = jm == j ? xmine : zero32;
-                const uint4 x0 = lds128(xp), x1 = lds128(xp + 16);
-                if (j == 0) {
-                    mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, x0.x, x0.z);
-                    mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, x0.y, x0.w);
-                } else {
-                    mma_u8s8(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, x0.x, x0.z);
-                    mma_u8s8(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, x0.y, x0.w);
-                }
-                mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, x1.x, x1.z);
-                mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, x1.y, x1.w);
-            }
-        }
-        const int jt = t / NB;
-        if (jt < ntiles) {
-            const float2 m = meta[(grp0 + jt) * NB + t % NB];
-            uint32_t s0, s1;
-            const uint32_t sza = tiles + (uint32_t)(jt * kTileBytes + kTileCodeBytes + g * 4);
-            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(s0) : "r"(sza));
-            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(s1) : "r"(sza + 32));
-            const float2 sz0 = __half22float2(*reinterpret_cast<const __half2 *>(&s0)), sz1 = __half22float2(*reinterpret_cast<const __half2 *>(&s1));
-            const float f0 = (float)(cal[0] * 4096 + (cal[1] * 16 + (cah[0] * 256 + cah[1]))), f1 = (float)(cal[2] * 4096 + (cal[3] * 16 + (cah[2] * 256 + cah[3])));
-            acc0 = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0), acc0);
-            acc1 = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1), acc1);
+        for (int s = 0; s < kSets; s++) {
+            int cal[4], cah[4], cbl[4], cbh[4];
+            mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, xa0[s].x, xa0[s].z);
+            mma_u8s8_z(cbl, b0.x & ML, b1.x & ML, b0.y & ML, b1.y & ML, xb0[s].x, xb0[s].z);
+            mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, xa0[s].y, xa0[s].w);
+            mma_u8s8_z(cbh, b0.x & MH, b1.x & MH, b0.y & MH, b1.y & MH, xb0[s].y, xb0[s].w);
+            mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, xa1[s].x, xa1[s].z);
+            mma_u8s8(cbl, b0.z & ML, b1.z & ML, b0.w & ML, b1.w & ML, xb1[s].x, xb1[s].z);
+            mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, xa1[s].y, xa1[s].w);
+            mma_u8s8(cbh, b0.z & MH, b1.z & MH, b0.w & MH, b1.w & MH, xb1[s].y, xb1[s].w);
+            fix_up(cal, cah, tile_a, grp_a, meta, s, g, t);
+            if (have_b) fix_up(cbl, cbh, tile_b, grp_b, meta, s, g, t);
         }
     }
-    // Sums of rows g and g + 8 for batch row t % NB over the lanes that shared them; valid in every lane afterwards.
-    __device__ __forceinline__ void row_sums(float &r0, float &r1) const {
-        r0 = acc0;
-        r1 = acc1;
-        if (NB <= 2) {
-            r0 += __shfl_xor_sync(0xffffffffu, r0, 2);
-            r1 += __shfl_xor_sync(0xffffffffu, r1, 2);
-        }
-        if (NB == 1) {
-            r0 += __shfl_xor_sync(0xffffffffu, r0, 1);
-            r1 += __shfl_xor_sync(0xffffffffu, r1, 1);
-        }
+    // Sums of rows g and g + 8 of batch row 2 s + t / 2, valid in both lanes of the pair afterwards.
+    __device__ __forceinline__ void row_sums(int s, float &r0, float &r1) const {
+        r0 = acc0[s] + __shfl_xor_sync(0xffffffffu, acc0[s], 1);
+        r1 = acc1[s] + __shfl_xor_sync(0xffffffffu, acc1[s], 1);
     }
 };
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kV2Consumers * 32) : "memory"); }
-
+// One 8-element chunk of a group of 128 activations (the group's 16 chunks sit in 16 consecutive lanes: hl = lane & 15):
+// round to 24-bit integers against the group's maximum, write the three byte planes in the fragment layout and, from
+// the chunk's first lane, the two fix-up constants of (group, batch row).  v: the values to multiply the weights with.
 __device__ __forceinline__ unsigned pack4s(int a, int b, int c, int d) {
     return (unsigned)(a & 0xff) | ((unsigned)(b & 0xff) << 8) | ((unsigned)(c & 0xff) << 16) | ((unsigned)(d & 0xff) << 24);
 }
+template <int NB>
+__device__ __forceinline__ void stage_chunk24(float (&v)[8], bool live, int grp, int b, int hl, uint32_t *xq, float2 *meta) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sx = amax > 0.0f ? amax * (1.0f / (float)kActTop) : 1.0f;
+    const float inv = amax > 0.0f ? (float)kActTop / amax : 0.0f;
+    int hi[8], mid[8], lo[8], lsum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        int xi = __float2int_rn(v[i] * inv);
+        xi = max(-kActTop, min(kActTop, xi));
+        lsum += xi;
+        lo[i] = ((xi + 128) & 0xff) - 128;  // signed low byte
+        const int r = (xi - lo[i]) >> 8;
+        mid[i] = ((r + 128) & 0xff) - 128;
+        hi[i] = (r - mid[i]) >> 8;
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (live) {
+        const int t = hl >> 2, j = hl & 3;
+        uint32_t *base = xq + ((((size_t)grp * 3 * NB + 3 * b) * 4 + t) * 4 + j) * 2;
+        *reinterpret_cast<uint2 *>(base) = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
+        *reinterpret_cast<uint2 *>(base + 32) = make_uint2(pack4s(mid[0], mid[2], mid[4], mid[6]), pack4s(mid[1], mid[3], mid[5], mid[7]));
+        *reinterpret_cast<uint2 *>(base + 64) = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
+        if (hl == 0) {
+            meta[(grp * NB + b) * 2] = make_float2(sx * 16.0f, (float)lsum * 0.0625f);
+            meta[(grp * NB + b) * 2 + 1] = make_float2(sx * (1.0f / 4096.0f), 0.0f);
+        }
+    }
+}
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kV2Consumers * 32) : "memory"); }
+
 
 struct StageIter {  // 32-bit and division-free in the loop: a 64-bit divide costs more than a tile
     int t, t_end, G, rb, grp;

@@ -90,6 +90,11 @@ class ModelInfo:
     max_seq_len: int
 
 
+def _argmax_last(logits: np.ndarray) -> int:
+    """Greedy pick: the LAST maximal index (crates/ironmill-inference/src/sampling.rs:331-339)."""
+    return int(logits.size - 1 - np.argmax(logits[::-1]))
+
+
 class Logits(np.ndarray):
     """Logits newtype: f32 vector of length vocab (crates/ironmill-inference/src/types.rs:155-187)."""
 
@@ -210,6 +215,47 @@ class CudaInference:
         check(lib().im_cuda_model_prefill_all_logits(self._model, vp(toks), C.c_int(toks.size), vp(out)))
         return out
 
+    # ---- BatchInferenceEngine (engine.rs:121-131) ------------------------------------------------
+    @_wrap
+    def add_sequence(self, tokens) -> int:
+        """Prefills the prompt into a free cache slot and returns the SequenceId.  The sequence's next token defaults to
+        the greedy pick of the prompt's last logits (batch_decode_step without arguments)."""
+        self._need_model()
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.empty(self._mc.vocab_size, dtype=np.float32)
+        sid = C.c_int(-1)
+        check(lib().im_cuda_model_seq_add(self._model, vp(toks), C.c_int(toks.size), C.byref(sid), vp(out)))
+        self._next = getattr(self, "_next", {})
+        self._next[sid.value] = int(_argmax_last(out))
+        return sid.value
+
+    @_wrap
+    def remove_sequence(self, seq_id: int) -> None:
+        self._need_model()
+        check(lib().im_cuda_model_seq_remove(self._model, C.c_int(seq_id)))
+        getattr(self, "_next", {}).pop(seq_id, None)
+
+    def sequence_position(self, seq_id: int) -> int:
+        return int(lib().im_cuda_model_seq_position(self._model, C.c_int(seq_id)))
+
+    @_wrap
+    def batch_decode_step(self, tokens: dict | None = None):
+        """One decode step for all active sequences (or for those named in `tokens`: {SequenceId: token}); returns
+        [(SequenceId, logits)].  Without `tokens` every active sequence continues greedily from its previous logits."""
+        self._need_model()
+        nxt = getattr(self, "_next", {})
+        feed = dict(tokens) if tokens is not None else dict(nxt)
+        if not feed:
+            return []
+        ids = np.ascontiguousarray(sorted(feed), dtype=np.int32)
+        toks = np.ascontiguousarray([feed[int(i)] for i in ids], dtype=np.uint32)
+        out = np.empty((ids.size, self._mc.vocab_size), dtype=np.float32)
+        check(lib().im_cuda_model_batch_decode_step(self._model, vp(ids), vp(toks), C.c_int(ids.size), vp(out)))
+        for i, sid in enumerate(ids):
+            nxt[int(sid)] = int(_argmax_last(out[i]))
+        self._next = nxt
+        return [(int(sid), out[i]) for i, sid in enumerate(ids)]
+
     @_wrap
     def test_missing_ranks(self, n: int) -> None:
         """Host-side fault injection (tests of the error path; `decode_schedule="tagged"` on one GPU only): n = 1 makes
@@ -241,6 +287,7 @@ class CudaInference:
     def reset(self) -> None:
         self._need_model()
         check(lib().im_cuda_model_reset(self._model))
+        self._next = {}
 
     def seq_pos(self) -> int:
         return int(lib().im_cuda_model_seq_pos(self._model)) if self._model else 0

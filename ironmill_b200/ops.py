@@ -170,11 +170,20 @@ def matvec_affine(w: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = N
     return y
 
 
-def matmul_affine(w: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Dense INT4 g128 GEMM on the tcgen05 tensor cores: y[M, N] = f16(x / awq) @ dequant(w)^T."""
+def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """silu_gate (crates/ironmill-inference/src/metal/shaders/activation/activation.metal): f16(SiLU(gate) * up), f32 inside."""
+    assert gate.is_cuda and gate.dtype == torch.float16 and gate.is_contiguous() and up.shape == gate.shape and up.is_contiguous()
+    y = out if out is not None else torch.empty_like(gate)
+    check(lib().im_cuda_silu_mul(vp(gate), vp(up), vp(y), C.c_size_t(gate.numel()), _stream()))
+    return y
+
+
+def matmul_affine(w: AffineWeight, x: torch.Tensor, out: torch.Tensor | None = None, scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Dense INT4 g128 GEMM on the tcgen05 tensor cores: y[M, N] = f16(x / awq) @ dequant(w)^T.  scratch: M * K halves."""
     M = _rows(x, w.K)
     y = out if out is not None else torch.empty((M, w.N), dtype=torch.float16, device=x.device)
-    scratch = torch.empty((M, w.K), dtype=torch.float16, device=x.device)
+    if scratch is None:
+        scratch = torch.empty((M, w.K), dtype=torch.float16, device=x.device)
     check(lib().im_cuda_matmul_affine(w.handle, vp(x), vp(y), C.c_int(M), vp(scratch), _stream()))
     return y
 

@@ -625,19 +625,26 @@ static float tree_sum(float *r, size_t hd) {
 }
 
 /* crates/ironmill-inference/src/metal/shaders/turboquant/turboquant.metal:52-170
- * (turboquant_cache_write), 8-bit storage.
- * kv [T, nkv, hd] fp16.  cache [nkv, max_seq, hd] u8, scale_buf / r_norms [nkv, max_seq] f32.
- * n_levels = 128 (K: 7-bit index | QJL sign in bit 7) or 256 (V).  hd must be a power of two. */
+ * (turboquant_cache_write) with the packing of src/shaders/turboquant_helpers.metal:24-77.
+ * kv [T, nkv, hd] fp16.  cache [nkv, max_seq, hd * n_bits / 8] u8, scale_buf / r_norms [nkv, max_seq] f32.
+ * n_bits = 8: one byte per element, n_levels = 128 (K: 7-bit index | QJL sign in bit 7) or 256 (V).
+ * n_bits = 4: two elements per byte (element 2i in the low nibble, 2i + 1 in the high one), n_levels = 8
+ * (K: 3-bit index | QJL sign in bit 3) or 16 (V).  hd must be a power of two. */
 EXPORT void orc_tq_encode(const uint16_t *kv, const float *signs, const float *codebook,
                           const float *boundaries, const float *qjl, int is_k, int n_bits,
                           uint8_t *cache, float *scale_buf, float *r_norms,
                           size_t nkv, size_t hd, size_t max_seq, size_t base_pos, size_t T) {
     size_t n_levels = is_k ? ((size_t)1 << (n_bits - 1)) : ((size_t)1 << n_bits);
     size_t nb = n_levels - 1;
+    /* one (token, head) per iteration, independent of the others (tokens of one call land on different positions:
+     * T <= max_seq is the caller's business, as in the reference's dispatch) */
+#pragma omp parallel
+    {
     float *x = (float *)malloc(sizeof(float) * hd);
     float *red = (float *)malloc(sizeof(float) * hd);
     float *res = (float *)malloc(sizeof(float) * hd);
     uint8_t *qv = (uint8_t *)malloc(hd);
+#pragma omp for collapse(2) schedule(static)
     for (size_t t = 0; t < T; t++)
         for (size_t h = 0; h < nkv; h++) {
             size_t pos = (base_pos + t) % max_seq;
@@ -667,9 +674,15 @@ EXPORT void orc_tq_encode(const uint16_t *kv, const float *signs, const float *c
                     if (proj >= 0.0f) qv[d] |= sign_mask;
                 }
             }
-            memcpy(cache + (h * max_seq + pos) * hd, qv, hd);
+            if (n_bits == 4) {   /* write_packed_elements, turboquant_helpers.metal:61-77 */
+                uint8_t *dst = cache + (h * max_seq + pos) * (hd / 2);
+                for (size_t d = 0; d < hd; d += 2) dst[d / 2] = (uint8_t)((qv[d] & 0xF) | ((d + 1 < hd ? qv[d + 1] & 0xF : 0) << 4));
+            } else {
+                memcpy(cache + (h * max_seq + pos) * hd, qv, hd);
+            }
         }
     free(x); free(red); free(res); free(qv);
+    }
 }
 
 /* crates/ironmill-inference/src/metal/shaders/turboquant/turboquant.metal:202-462
@@ -685,16 +698,23 @@ EXPORT void orc_tq_attention(const uint16_t *q, const uint8_t *kc, const uint8_t
                              uint16_t *out, size_t nh, size_t nkv, size_t hd, size_t max_seq,
                              size_t base_pos, size_t T, size_t num_splits) {
     const size_t TILE = 32;
+    const size_t bpp = n_bits == 4 ? hd / 2 : hd;   /* bytes_per_pos, turboquant_helpers.metal:24-27 */
+    const unsigned emask = n_bits == 4 ? 0xFu : 0xFFu, eshift = n_bits == 4 ? 4u : 0u;
+#define TQ_RAW(row, d) (n_bits == 4 ? (((row)[(d) >> 1] >> (eshift * ((d) & 1))) & emask) : (row)[d])  /* read_raw_element :36-46 */
+    size_t ns = num_splits ? num_splits : 1;
+    uint8_t sign_mask = (uint8_t)(1u << (n_bits - 1));
+    float qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)hd;
+    /* one (token, head) per iteration: the heads do not interact, so the threads change nothing in the results */
+#pragma omp parallel
+    {
     float *qr = (float *)malloc(sizeof(float) * hd);
     float *sq = (float *)malloc(sizeof(float) * hd);
     float *o = (float *)malloc(sizeof(float) * hd);
-    size_t ns = num_splits ? num_splits : 1;
     float *po = (float *)malloc(sizeof(float) * ns * hd);
     float *pm = (float *)malloc(sizeof(float) * ns);
     float *ps = (float *)malloc(sizeof(float) * ns);
     float scores[32];
-    uint8_t sign_mask = (uint8_t)(1u << (n_bits - 1));
-    float qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)hd;
+#pragma omp for collapse(2) schedule(dynamic)
     for (size_t t = 0; t < T; t++)
         for (size_t h = 0; h < nh; h++) {
             size_t seq_len = base_pos + t + 1;
@@ -725,10 +745,10 @@ EXPORT void orc_tq_attention(const uint16_t *q, const uint8_t *kc, const uint8_t
                         size_t ap = ts + p;
                         float kd = k_scale[kvh * max_seq + ap];
                         float w = k_rn[kvh * max_seq + ap] * qjl_factor * kd;
-                        const uint8_t *row = kc + (kvh * max_seq + ap) * hd;
+                        const uint8_t *row = kc + (kvh * max_seq + ap) * bpp;
                         float part = 0.0f;
                         for (size_t d = 0; d < hd; d++) {
-                            uint8_t raw = row[d];
+                            uint8_t raw = (uint8_t)TQ_RAW(row, d);
                             float kval = k_cb[raw & (sign_mask - 1)] * kd;
                             float sg = (raw & sign_mask) ? 1.0f : -1.0f;
                             part += qr[d] * kval + sq[d] * sg * w;
@@ -747,8 +767,8 @@ EXPORT void orc_tq_attention(const uint16_t *q, const uint8_t *kc, const uint8_t
                     for (size_t p = 0; p < nt; p++) {
                         size_t ap = ts + p;
                         float vd = v_scale[kvh * max_seq + ap];
-                        const uint8_t *row = vc + (kvh * max_seq + ap) * hd;
-                        for (size_t d = 0; d < hd; d++) o[d] += scores[p] * (v_cb[row[d]] * vd);
+                        const uint8_t *row = vc + (kvh * max_seq + ap) * bpp;
+                        for (size_t d = 0; d < hd; d++) o[d] += scores[p] * (v_cb[TQ_RAW(row, d)] * vd);
                     }
                 }
                 if (num_splits) {
@@ -777,6 +797,8 @@ EXPORT void orc_tq_attention(const uint16_t *q, const uint8_t *kc, const uint8_t
             }
         }
     free(qr); free(sq); free(o); free(po); free(pm); free(ps);
+    }
+#undef TQ_RAW
 }
 
 /* crates/ironmill-inference/src/sampling.rs:331-339 (argmax): last maximal index under

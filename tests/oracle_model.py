@@ -137,8 +137,8 @@ class OracleModel:
             d["gate"], d["ffn_awq"] = _deq(tensors[f"{p}.mlp.gate_proj.weight"])
             d["up"], _ = _deq(tensors[f"{p}.mlp.up_proj.weight"])
             d["down"], d["down_awq"] = _deq(tensors[f"{p}.mlp.down_proj.weight"])
-            d["kc"] = np.zeros((nkv, max_seq, hd), np.uint8)
-            d["vc"] = np.zeros((nkv, max_seq, hd), np.uint8)
+            d["kc"] = np.zeros((nkv, max_seq, hd * tqc.n_bits // 8), np.uint8)   # n_bits = 4: two elements per byte
+            d["vc"] = np.zeros((nkv, max_seq, hd * tqc.n_bits // 8), np.uint8)
             d["ks"], d["vs"], d["kr"] = (np.zeros((nkv, max_seq), np.float32) for _ in range(3))
             self.L.append(d)
         self._w16 = {}

@@ -224,3 +224,53 @@ def test_fused_attention_block_equals_separate_kernels(tq, tqc, with_norm, T, ba
     same = float((kc == kc2).float().mean())
     assert same >= 0.999, same   # a K value that differs in its last fp16 bit after RoPE can move a code
     assert torch.equal(vc, vc2) and torch.equal(vs, vs2)
+
+
+# ---------------------------------------------------------------------------------------------- 4-bit cache (n_bits = 4)
+@pytest.fixture(scope="module")
+def tqc4():
+    return orc.TqConstants(128, 4, seed=42)
+
+
+@pytest.fixture(scope="module")
+def tq4(dev, tqc4):
+    from ironmill_b200 import ops
+    return ops.TurboQuant(dev, 128, 4, tqc4.signs, tqc4.qjl, tqc4.k_levels, tqc4.k_bounds, tqc4.v_levels, tqc4.v_bounds)
+
+
+def _encode4(tq4, tqc4, kv, is_k, nkv, max_seq, base):
+    T = kv.size // (nkv * 128)
+    cache = np.zeros((nkv, max_seq, 64), dtype=np.uint8)
+    scale, rn = np.zeros((nkv, max_seq), np.float32), np.zeros((nkv, max_seq), np.float32)
+    orc.tq_encode(kv.reshape(T, nkv, 128), tqc4, is_k, cache, scale, rn, nkv, max_seq, base)
+    cd, sd, rd = _c(np.zeros((1, nkv, max_seq, 64), np.uint8)), _c(np.zeros((1, nkv, max_seq), np.float32)), _c(np.zeros((1, nkv, max_seq), np.float32))
+    tq4.encode(_c(kv), is_k, cd, sd, rd, nkv, max_seq, base)
+    return (cache, scale, rn), (cd.cpu().numpy()[0], sd.cpu().numpy()[0], rd.cpu().numpy()[0]), (cd, sd, rd)
+
+
+@pytest.mark.parametrize("is_k", [True, False])
+@pytest.mark.parametrize("T,base,max_seq", [(1, 0, 64), (5, 3, 64), (33, 60, 64)])
+def test_encode_4bit_bit_exact(tq4, tqc4, is_k, T, base, max_seq):
+    """3-bit index | QJL sign (K) or 4-bit index (V), two elements per byte, against the oracle: bytes and norms."""
+    kv = H.make_x(T, 8 * 128, seed=T + base, name="kv4")
+    (c, s, r), (gc, gs, gr), _ = _encode4(tq4, tqc4, kv, is_k, 8, max_seq, base)
+    assert (gc == c).all(), "packed cache bytes differ"
+    assert (gs.view(np.uint32) == s.view(np.uint32)).all()
+    if is_k:
+        assert (gr.view(np.uint32) == r.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 8), (8, 8), (16, 2)])
+@pytest.mark.parametrize("ctx", [1, 33, 257, 1024, 4097])
+def test_decode_attention_4bit(tq4, tqc4, nh, nkv, ctx):
+    """nh / nkv = 8 takes the f32 kernel (nibbles spread to bytes in shared memory), the others the tensor-core kernel."""
+    max_seq = ctx + 3
+    k, v = H.make_x(ctx, nkv * 128, ctx, "K4"), H.make_x(ctx, nkv * 128, ctx, "V4")
+    (kc, ks, kr), _, (kcd, ksd, krd) = _encode4(tq4, tqc4, k, True, nkv, max_seq, 0)
+    (vc, vs, _r), _, (vcd, vsd, _rd) = _encode4(tq4, tqc4, v, False, nkv, max_seq, 0)
+    q = H.make_x(1, nh * 128, seed=ctx, name="q4")
+    scale = 1.0 / np.sqrt(128.0)
+    ref = orc.tq_attention(q, kc, vc, tqc4, ks, vs, kr, scale, nh, nkv, max_seq, ctx - 1, num_splits=0)
+    for splits in (0, 3):
+        out = tq4.attention(_c(q), kcd, vcd, ksd, vsd, krd, scale, nh, nkv, max_seq, ctx - 1, num_splits=splits)
+        assert H.rel_err(out.cpu().numpy().reshape(ref.shape), ref) <= 2e-3, f"splits={splits}"
