@@ -28,10 +28,12 @@ namespace im {
 
 namespace {
 
-// x / a for the AWQ scales: reciprocal, product and one Newton step on the remainder: the correctly rounded f32 quotient for
-// every operand that is not denormal (an IEEE division routine costs four times as much, 6 us per layer of staging time).
+// x / a for the AWQ scales: approximate reciprocal, product and one Newton step on the remainder, which gives the correctly
+// rounded f32 quotient for operands that are not denormal.  (The IEEE division and reciprocal routines cost 6 to 10 us
+// per layer of staging time in this kernel: measured.)
 __device__ __forceinline__ float div_awq(float x, float a) {
-    const float r = __frcp_rn(a);
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));  // one instruction; the Newton step below repairs its last bits
     const float q = x * r;
     return fmaf(fmaf(-q, a, x), r, q);
 }
@@ -593,7 +595,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         };
 
         const int g = lane >> 2, t = lane & 3;
-        TileMath<1> tm;
+        TileMath<1, false> tm;
         tm.reset();
 
         // One projection: stage the activations, then walk this CTA's stages of the phase.
@@ -629,39 +631,45 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 }
             }
             if (stamp) p.trace[fine + 1] = global_ns();
-            StageIter it(r.t_begin, r.t_end, G);
-            int t0, n, rb, grp0;
             tm.reset();
             const bool two_sets = ph.resid && ph.split_row > 0 && ph.split_row < ph.N;
-            bool on_second = false;
-            while (it.next(t0, n, rb, grp0)) {
-                if (!dead && !mbar_wait_warp(&full[slot], par, p.err, wait_ms)) dead = true;
-                const unsigned char *st = ring + (size_t)slot * kStageBytes;
-                if (!dead && warp < n) {
-                    const int tb = warp + kV2Consumers;
-                    const bool sec = two_sets && rb * 16 >= ph.split_row;  // this row block reads norm_out
-                    if (sec != on_second) {  // the cached activation fragments belong to the other set
-                        on_second = sec;
-                        tm.ga = tm.gb = -1;
+#ifdef IM_DEV_TRACE
+            int sidx = 0;
+#endif
+            // This CTA's row blocks, each a run of stages of up to kStageTiles tiles (the same walk as the producer's StageIter,
+            // written as two plain loops: the iterator's arithmetic per stage cost 15 % of the loop's time).
+            const int rb_end = r.t_end / G;
+            for (int rb = r.t_begin / G; rb < rb_end; rb++) {
+                const bool sec = two_sets && rb * 16 >= ph.split_row;  // this row block reads norm_out
+                const uint32_t *xq_rb = sec ? xq2 : xq;
+                const float2 *meta_rb = sec ? meta2 : meta;
+                for (int grp0 = 0; grp0 < G; grp0 += kStageTiles) {
+                    const int n = min(kStageTiles, G - grp0);
+                    if (!dead && !mbar_wait_warp(&full[slot], par, p.err, wait_ms)) dead = true;
+#ifdef IM_DEV_TRACE
+                    if (stamp && sidx < 20) p.trace[fine + 2 + sidx++] = global_ns();  // the stage's data is here
+#endif
+                    const unsigned char *st = ring + (size_t)slot * kStageBytes;
+                    if (!dead && warp < n) {
+                        const int tb = warp + kV2Consumers;
+                        tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq_rb, meta_rb, lane);
                     }
-                    tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, sec ? xq2 : xq,
-                            sec ? meta2 : meta, lane);
-                }
-                if (grp0 + n == G) {  // last stage of the row block: hand the partial sums to the producer warp
-                    float *buf = red + slot * kRedFloats;
-                    float r0, r1;
-                    tm.row_sums(0, r0, r1);
-                    if (t == 0) {
-                        buf[warp * 16 + g] = r0;
-                        buf[warp * 16 + g + 8] = r1;
+                    if (grp0 + n == G) {  // last stage of the row block: hand the partial sums to the producer warp
+                        float *buf = red + slot * kRedFloats;
+                        float r0, r1;
+                        tm.row_sums(0, r0, r1);
+                        if (t == 0) {
+                            buf[warp * 16 + g] = r0;
+                            buf[warp * 16 + g + 8] = r1;
+                        }
+                        tm.clear_sums();
                     }
-                    tm.clear_sums();
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
-                if (++slot == nring) {
-                    slot = 0;
-                    par ^= 1;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
+                    if (++slot == nring) {
+                        slot = 0;
+                        par ^= 1;
+                    }
                 }
             }
             if (stamp) p.trace[fine + 22] = global_ns();

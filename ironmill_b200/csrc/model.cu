@@ -1515,6 +1515,17 @@ IM_EXPORT int im_cuda_model_test_missing_ranks(im_model *m, int missing_ranks) {
     IM_GUARD_END
 }
 
+#ifdef IM_DEV_TRACE
+// Development builds only (never declared in the header, never in the shipped library): the raw timer stamps of the
+// whole-token kernel's CTA 0.
+IM_EXPORT int im_cuda_model_dev_trace(im_model *m, unsigned long long *out, int n) {
+    const int have = 7 * m->cfg.num_layers + 2 + 96;
+    cudaStreamSynchronize(m->stream);
+    cudaMemcpy(out, m->mega.trace, (size_t)(n < have ? n : have) * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    return 0;
+}
+#endif
+
 // 1 when the row-split projections of a tensor-parallel model are summed by the one-shot peer-memory all-reduce,
 // 0 when NCCL does it (single GPU: 0).
 IM_EXPORT int im_cuda_model_tp_peer_allreduce(const im_model *m) { return m && m->xar.ok ? 1 : 0; }

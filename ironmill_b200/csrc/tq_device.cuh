@@ -231,6 +231,7 @@ struct AttnParams {
 // Eight 4-bit elements of a cache word -> two words of one byte per element (the 8-bit layout the score and value
 // loops read).  K: the 3-bit index stays in bits 0-2, the QJL sign moves from bit 3 to bit 7; V: the byte is the index.
 __device__ __forceinline__ unsigned tq_spread4(unsigned x) {  // nibbles 0-3 of x (low 16 bits) -> bytes
+    x &= 0xFFFFu;
     x = (x | (x << 8)) & 0x00FF00FFu;
     return (x | (x << 4)) & 0x0F0F0F0Fu;
 }

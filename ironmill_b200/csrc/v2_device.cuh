@@ -90,7 +90,9 @@ __device__ __forceinline__ void mma_u8s8_z(int (&c)[4], unsigned a0, unsigned a1
 // from shared memory once per projection.
 // Staged layout: xq words, index ((grp * 3 NB + 3 b + c) * 4 + t) * 8 + j * 2 + eo, byte plane c = 0 high, 1 middle, 2 low.
 constexpr int kActTop = 8355711;  // 0x7F7F7F: the largest staged magnitude
-template <int NB>
+// CACHE = false reads the fragments from shared memory for every pair of tiles instead (four 128-bit loads): 18 registers
+// fewer live across the stage loop, which is what the whole-token kernel, at its 96-register ceiling, needs more.
+template <int NB, bool CACHE = true>
 struct TileMath {
     static constexpr int kSets = (NB + 1) / 2;  // column sets of up to two batch rows
     uint4 xa0[kSets], xa1[kSets], xb0[kSets], xb1[kSets];  // B fragments of the groups ga / gb
@@ -142,14 +144,24 @@ struct TileMath {
             b0 = *reinterpret_cast<const uint4 *>(tile_b + lane * 16);
             b1 = *reinterpret_cast<const uint4 *>(tile_b + 512 + lane * 16);
         }
-        if (grp_a != ga) {  // warp-uniform
-            ga = grp_a;
-            load_frag(xq, grp_a, g, t, xa0, xa1);
+        uint4 la0[kSets], la1[kSets], lb0[kSets], lb1[kSets];  // CACHE = false: fragments that live for this pair only
+        if (CACHE) {
+            if (grp_a != ga) {  // warp-uniform
+                ga = grp_a;
+                load_frag(xq, grp_a, g, t, xa0, xa1);
+            }
+            if (have_b && grp_b != gb) {
+                gb = grp_b;
+                load_frag(xq, grp_b, g, t, xb0, xb1);
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < kSets; s++) la0[s] = la1[s] = lb0[s] = lb1[s] = make_uint4(0, 0, 0, 0);
+            load_frag(xq, grp_a, g, t, la0, la1);
+            if (have_b) load_frag(xq, grp_b, g, t, lb0, lb1);
         }
-        if (have_b && grp_b != gb) {
-            gb = grp_b;
-            load_frag(xq, grp_b, g, t, xb0, xb1);
-        }
+        const uint4 (&fa0)[kSets] = CACHE ? xa0 : la0, (&fa1)[kSets] = CACHE ? xa1 : la1;
+        const uint4 (&fb0)[kSets] = CACHE ? xb0 : lb0, (&fb1)[kSets] = CACHE ? xb1 : lb1;
         // Low and high nibbles go to separate accumulators: the low ones masked in place, the high ones masked in place
         // too (a byte 16 q, still a valid u8), so a word costs two logic operations and no shift.  The two chains are
         // independent; the fix-up adds them as 16 * low + high16, and the staged activation scale carries the 1/16.
@@ -159,14 +171,14 @@ struct TileMath {
 #pragma unroll
         for (int s = 0; s < kSets; s++) {
             int cal[4], cah[4], cbl[4], cbh[4];
-            mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, xa0[s].x, xa0[s].z);
-            mma_u8s8_z(cbl, b0.x & ML, b1.x & ML, b0.y & ML, b1.y & ML, xb0[s].x, xb0[s].z);
-            mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, xa0[s].y, xa0[s].w);
-            mma_u8s8_z(cbh, b0.x & MH, b1.x & MH, b0.y & MH, b1.y & MH, xb0[s].y, xb0[s].w);
-            mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, xa1[s].x, xa1[s].z);
-            mma_u8s8(cbl, b0.z & ML, b1.z & ML, b0.w & ML, b1.w & ML, xb1[s].x, xb1[s].z);
-            mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, xa1[s].y, xa1[s].w);
-            mma_u8s8(cbh, b0.z & MH, b1.z & MH, b0.w & MH, b1.w & MH, xb1[s].y, xb1[s].w);
+            mma_u8s8_z(cal, a0.x & ML, a1.x & ML, a0.y & ML, a1.y & ML, fa0[s].x, fa0[s].z);
+            mma_u8s8_z(cbl, b0.x & ML, b1.x & ML, b0.y & ML, b1.y & ML, fb0[s].x, fb0[s].z);
+            mma_u8s8_z(cah, a0.x & MH, a1.x & MH, a0.y & MH, a1.y & MH, fa0[s].y, fa0[s].w);
+            mma_u8s8_z(cbh, b0.x & MH, b1.x & MH, b0.y & MH, b1.y & MH, fb0[s].y, fb0[s].w);
+            mma_u8s8(cal, a0.z & ML, a1.z & ML, a0.w & ML, a1.w & ML, fa1[s].x, fa1[s].z);
+            mma_u8s8(cbl, b0.z & ML, b1.z & ML, b0.w & ML, b1.w & ML, fb1[s].x, fb1[s].z);
+            mma_u8s8(cah, a0.z & MH, a1.z & MH, a0.w & MH, a1.w & MH, fa1[s].y, fa1[s].w);
+            mma_u8s8(cbh, b0.z & MH, b1.z & MH, b0.w & MH, b1.w & MH, fb1[s].y, fb1[s].w);
             fix_up(cal, cah, tile_a, grp_a, meta, s, g, t);
             if (have_b) fix_up(cbl, cbh, tile_b, grp_b, meta, s, g, t);
         }
@@ -181,9 +193,6 @@ struct TileMath {
 // One 8-element chunk of a group of 128 activations (the group's 16 chunks sit in 16 consecutive lanes: hl = lane & 15):
 // round to 24-bit integers against the group's maximum, write the three byte planes in the fragment layout and, from
 // the chunk's first lane, the two fix-up constants of (group, batch row).  v: the values to multiply the weights with.
-__device__ __forceinline__ unsigned pack4s(int a, int b, int c, int d) {
-    return (unsigned)(a & 0xff) | ((unsigned)(b & 0xff) << 8) | ((unsigned)(c & 0xff) << 16) | ((unsigned)(d & 0xff) << 24);
-}
 template <int NB>
 __device__ __forceinline__ void stage_chunk24(float (&v)[8], bool live, int grp, int b, int hl, uint32_t *xq, float2 *meta) {
     float amax = 0.0f;
@@ -193,25 +202,29 @@ __device__ __forceinline__ void stage_chunk24(float (&v)[8], bool live, int grp,
     for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     const float sx = amax > 0.0f ? amax * (1.0f / (float)kActTop) : 1.0f;
     const float inv = amax > 0.0f ? (float)kActTop / amax : 0.0f;
-    int hi[8], mid[8], lo[8], lsum = 0;
+    // xi = hi * 65536 + mid * 256 + lo with signed digits: adding 0x808080 makes every digit a plain unsigned byte
+    // (digit + 128, no carries between them), and flipping bit 7 of each byte turns that into the digit's two's complement.
+    unsigned y[8];
+    int lsum = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         int xi = __float2int_rn(v[i] * inv);
         xi = max(-kActTop, min(kActTop, xi));
         lsum += xi;
-        lo[i] = ((xi + 128) & 0xff) - 128;  // signed low byte
-        const int r = (xi - lo[i]) >> 8;
-        mid[i] = ((r + 128) & 0xff) - 128;
-        hi[i] = (r - mid[i]) >> 8;
+        y[i] = (unsigned)(xi + 0x808080) ^ 0x808080u;  // bytes: low, middle, high digit
     }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
     if (live) {
         const int t = hl >> 2, j = hl & 3;
         uint32_t *base = xq + ((((size_t)grp * 3 * NB + 3 * b) * 4 + t) * 4 + j) * 2;
-        *reinterpret_cast<uint2 *>(base) = make_uint2(pack4s(hi[0], hi[2], hi[4], hi[6]), pack4s(hi[1], hi[3], hi[5], hi[7]));
-        *reinterpret_cast<uint2 *>(base + 32) = make_uint2(pack4s(mid[0], mid[2], mid[4], mid[6]), pack4s(mid[1], mid[3], mid[5], mid[7]));
-        *reinterpret_cast<uint2 *>(base + 64) = make_uint2(pack4s(lo[0], lo[2], lo[4], lo[6]), pack4s(lo[1], lo[3], lo[5], lo[7]));
+#pragma unroll
+        for (int c = 0; c < 3; c++) {  // staged plane c: 0 high, 1 middle, 2 low = byte 2 - c of y
+            const unsigned sel = (unsigned)(2 - c) | ((unsigned)(6 - c) << 4);
+            const unsigned e = __byte_perm(__byte_perm(y[0], y[2], sel), __byte_perm(y[4], y[6], sel), 0x5410);  // elements 0, 2, 4, 6
+            const unsigned o = __byte_perm(__byte_perm(y[1], y[3], sel), __byte_perm(y[5], y[7], sel), 0x5410);  // elements 1, 3, 5, 7
+            *reinterpret_cast<uint2 *>(base + 32 * c) = make_uint2(e, o);
+        }
         if (hl == 0) {
             meta[(grp * NB + b) * 2] = make_float2(sx * 16.0f, (float)lsum * 0.0625f);
             meta[(grp * NB + b) * 2 + 1] = make_float2(sx * (1.0f / 4096.0f), 0.0f);
