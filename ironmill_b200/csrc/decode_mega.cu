@@ -599,11 +599,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         tm.reset();
 
         // One projection: stage the activations, then walk this CTA's stages of the phase.
-        auto matvec_phase = [&](int q, int fine) __attribute__((always_inline)) {  // fine >= 0: CTA 0 records 24 stamps at trace[fine..]
+        auto matvec_phase = [&](int q) __attribute__((always_inline)) {
             const MegaPhase ph = *reinterpret_cast<const MegaPhase *>(desc + ((q >> 2) & 1) * kDescWords + (q & 3) * kPhaseWords);
             const int G = ph.G;
-            const bool stamp = p.trace && fine >= 0 && blockIdx.x == 0 && tid == 0;
-            if (stamp) p.trace[fine] = global_ns();
             if (ph.resid) {
                 // tensor parallel: gate/up reads this layer's o sums, QKV the previous layer's down sums
                 const bool from_mail = TP && ph.xin;
@@ -630,12 +628,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     if (nx.gamma) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.gamma + i * 64));
                 }
             }
-            if (stamp) p.trace[fine + 1] = global_ns();
             tm.reset();
             const bool two_sets = ph.resid && ph.split_row > 0 && ph.split_row < ph.N;
-#ifdef IM_DEV_TRACE
-            int sidx = 0;
-#endif
             // This CTA's row blocks, each a run of stages of up to kStageTiles tiles (the same walk as the producer's StageIter,
             // written as two plain loops: the iterator's arithmetic per stage cost 15 % of the loop's time).
             const int rb_end = r.t_end / G;
@@ -646,9 +640,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 for (int grp0 = 0; grp0 < G; grp0 += kStageTiles) {
                     const int n = min(kStageTiles, G - grp0);
                     if (!dead && !mbar_wait_warp(&full[slot], par, p.err, wait_ms)) dead = true;
-#ifdef IM_DEV_TRACE
-                    if (stamp && sidx < 20) p.trace[fine + 2 + sidx++] = global_ns();  // the stage's data is here
-#endif
                     const unsigned char *st = ring + (size_t)slot * kStageBytes;
                     if (!dead && warp < n) {
                         const int tb = warp + kV2Consumers;
@@ -672,7 +663,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     }
                 }
             }
-            if (stamp) p.trace[fine + 22] = global_ns();
         };
 
         const int seq_len = min(p.pos[0] + 1, p.max_seq);  // the host checks the position before every step; never read past the caches
@@ -687,7 +677,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             if (l > 0) {  // the previous layer's down projection
                 if (tp) xrank_wait(7 * l - 1, 2 * (l - 1) + 1); else grid_wait(7 * l - 1);
             }
-            matvec_phase(4 * l, l == 1 ? 7 * p.L + 2 : -1);
+            matvec_phase(4 * l);
             float sv[32];  // this thread's share of the projection matrix, on its way while the grid gathers
             if (blockIdx.x < n_heads) {
 #pragma unroll
@@ -756,11 +746,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
             items_done(7 * l + 3);
             grid_wait(7 * l + 3);
 
-            matvec_phase(4 * l + 1, l == 1 ? 7 * p.L + 2 + 24 : -1);  // o
+            matvec_phase(4 * l + 1);  // o
             if (tp) xrank_wait(7 * l + 4, 2 * l); else grid_wait(7 * l + 4);
-            matvec_phase(4 * l + 2, l == 1 ? 7 * p.L + 2 + 48 : -1);  // residual + norm -> gate/up + SiLU
+            matvec_phase(4 * l + 2);  // residual + norm -> gate/up + SiLU
             grid_wait(7 * l + 5);
-            matvec_phase(4 * l + 3, l == 1 ? 7 * p.L + 2 + 72 : -1);  // down
+            matvec_phase(4 * l + 3);  // down
         }
     }
 

@@ -258,11 +258,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
     while (it.next(t0, n, rb, grp0)) {
         if (!dead && !mbar_wait_warp(&full[slot], phase, p.err)) dead = true;
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
-#ifndef IM_DEV_NOMATH
         if (!dead && warp < n) {
-#else
-        if (false) {
-#endif
             const int tb = warp + kV2Consumers;
             tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq, meta, lane);
         }

@@ -822,8 +822,8 @@ static int mega_prepare(Model *m) {
     }
     p.wait_ms = c.wait_limit_ms > 0 ? (unsigned)c.wait_limit_ms : 0u;
     // phase stamps of CTA 0 (a store per grid barrier; read back by im_cuda_model_token_kernel_profile)
-    IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
-    IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2 + 96) * sizeof(unsigned long long)));
+    IM_TRY(m->alloc((void **)&p.trace, (size_t)(7 * L + 2) * sizeof(unsigned long long)));
+    IM_CUDA_CHECK(cudaMemset(p.trace, 0, (size_t)(7 * L + 2) * sizeof(unsigned long long)));
     IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
     m->mega_ready = true;
     return IM_OK;
@@ -1514,17 +1514,6 @@ IM_EXPORT int im_cuda_model_test_missing_ranks(im_model *m, int missing_ranks) {
     return IM_OK;
     IM_GUARD_END
 }
-
-#ifdef IM_DEV_TRACE
-// Development builds only (never declared in the header, never in the shipped library): the raw timer stamps of the
-// whole-token kernel's CTA 0.
-IM_EXPORT int im_cuda_model_dev_trace(im_model *m, unsigned long long *out, int n) {
-    const int have = 7 * m->cfg.num_layers + 2 + 96;
-    cudaStreamSynchronize(m->stream);
-    cudaMemcpy(out, m->mega.trace, (size_t)(n < have ? n : have) * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-    return 0;
-}
-#endif
 
 // 1 when the row-split projections of a tensor-parallel model are summed by the one-shot peer-memory all-reduce,
 // 0 when NCCL does it (single GPU: 0).
