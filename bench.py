@@ -352,7 +352,7 @@ def run_decode(args, rank, world):
     out = {
         "metric": METRIC_DECODE if args.model == "llama3_8b" else METRIC_DECODE_Q, "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "u4 codes x i16 activations (f32 fix-up), f16 lm_head, u8 KV codebook indices",
+        "dtype": "u4 codes x i24 activations (f32 fix-up), f16 lm_head, u8 KV codebook indices",
         "data": "synthetic",
         "config": decode_config(workload, cfg, B, P, world),
         "run": {"context_during_timing": [ctx0, ctx0 + K],
@@ -525,7 +525,7 @@ def run_matvec(args, rank, world):
         sweep.append(row)
     out = {"metric": METRIC_MATVEC, "value": round(step_bytes * steps / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": 1,
            "steps": steps, "warmup": args.warmup, "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak",
-           "vs_baseline": None, "dtype": "u4 codes x i16 activations, f32 fix-up", "data": "synthetic",
+           "vs_baseline": None, "dtype": "u4 codes x i24 activations, f32 fix-up", "data": "synthetic",
            "config": {"workload": "int4_g128_matvec_sweep_llama3_8b_shapes_b1_awq", "shapes": [[n, N, K] for n, N, K, _ in L8_SHAPES],
                       "l2_policy": f"rotation over {ncopies} weight copies ({ncopies * step_bytes >> 20} MiB) larger than L2"},
            "roofline": {"bound": "hbm", "kernel": "matvec_v2_kernel<gate+up+SiLU, batch 1> 4096->2x14336",
@@ -784,6 +784,10 @@ def main():
         run_attention(args, rank, world)
     else:
         run_decode(args, rank, world)
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        sys.stdout.flush()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -602,21 +602,24 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
         auto matvec_phase = [&](int q) __attribute__((always_inline)) {
             const MegaPhase ph = *reinterpret_cast<const MegaPhase *>(desc + ((q >> 2) & 1) * kDescWords + (q & 3) * kPhaseWords);
             const int G = ph.G;
+            const Range r = cta_range(ph.nblk, G);
             if (ph.resid) {
                 // tensor parallel: gate/up reads this layer's o sums, QKV the previous layer's down sums
                 const bool from_mail = TP && ph.xin;
                 const uint2 *mail = from_mail ? p.xmail[p.rank] + (size_t)(ph.xin - 1) * p.world * (size_t)(p.xH >> 1) : nullptr;
                 const unsigned tag = xbase + (unsigned)((((q & 3) == 0 ? (q >> 2) - 1 : (q >> 2)) * 2) + ((ph.xin - 1) & 1) + 1);
                 // rows below split_row multiply the unrounded vector (primary set), the others norm_out (the second set, or
-                // the primary one when no row wants the unrounded vector)
-                const bool want_u = ph.split_row > 0, want_r = ph.split_row < ph.N;
-                mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, want_u, xq, meta, want_r, want_u ? xq2 : xq,
-                                want_u ? meta2 : meta, p.eps, misc, mail, p.world, p.xH >> 1, tag, p.err, wait_ms);
+                // the primary one when no row of the phase wants the unrounded vector).  A CTA stages only the sets its own
+                // row blocks read: with whole row blocks per CTA almost every CTA of a QKV phase needs just one of them.
+                const bool phase_u = ph.split_row > 0;
+                const bool want_u = phase_u && r.t_begin < r.t_end && (r.t_begin / G) * 16 < ph.split_row;
+                const bool want_r = r.t_begin < r.t_end && (r.t_end / G) * 16 > ph.split_row;
+                mega_stage_norm(ph.x, ph.resid, ph.gamma, ph.awq, ph.resid_out, G, want_u, xq, meta, want_r, phase_u ? xq2 : xq,
+                                phase_u ? meta2 : meta, p.eps, misc, mail, p.world, p.xH >> 1, tag, p.err, wait_ms);
             } else {
                 mega_stage_plain(ph.x, ph.awq, G, xq, meta);
             }
             consumer_sync();
-            const Range r = cta_range(ph.nblk, G);
             // A CTA without tiles in this phase arrives at its barrier here, after every consumer thread has read the
             // phase's input (a CTA with tiles arrives from its producer warp, after its last stage was released).
             if (r.t_begin >= r.t_end && tid == 0 && !(TP && ph.xout)) grid_arrive(p.bar, phase_barrier(q));
