@@ -56,7 +56,7 @@ METRIC_MATVEC = "matvec HBM GB/s (INT4 g128 affine, Llama-3-8B projection shapes
 METRIC_ATTN = "TurboQuant INT8-KV decode attention HBM GB/s (32 Q / 8 KV heads, head_dim 128)"
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
 PROJ_DRAM_BYTES = 62467840 + 17920          # matvec_v2_kernel<gate+up+SiLU>, one launch
-TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = (972662016 + 38294528) / 8   # dram read + write of the 8-layer ncu capture (profiles/)
+TOKEN_KERNEL_DRAM_BYTES_PER_LAYER = (968957440 + 41039104) / 8   # dram read + write of the 8-layer ncu capture (profiles/decode_token_kernel_l8_shapes_ctx2k.md)
 
 
 def matvec_bytes(N, K, B=1, awq=True, bits=4):
@@ -423,7 +423,7 @@ def time_projection(dev, N, K, kind, B, bits, awq_on=True, reps=4):
 
     st = torch.cuda.Stream()
     with torch.cuda.stream(st):
-        for i in range(min(ncopy, 3)):
+        for i in range(ncopy):   # every copy once outside the capture: the paired gate/up tile stream is built on first use
             call(i)
         st.synchronize()
         graph = torch.cuda.CUDAGraph()

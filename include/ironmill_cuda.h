@@ -342,6 +342,11 @@ int im_cuda_model_seq_position(const im_model *m, int seq_id);   /* tokens in th
 int im_cuda_model_batch_decode_step(im_model *m, const int *seq_ids, const uint32_t *tokens_host, int n, float *logits_out_host);
 int im_cuda_model_reset(im_model *m);
 int im_cuda_model_truncate(im_model *m, int pos);
+/* Hidden state of the last step: the final RMSNorm output the lm_head consumed, fp16 widened to f32, `rows` rows of
+ * hidden_size (row i = sequence i of that step; row 0 for the single-sequence calls).  Replaces
+ * MetalInference::decode_step_with_hidden / last_hidden_state (ironmill-inference/src/metal/pipeline.rs:176-226), which
+ * read the same buffer (norm_out) for the draft head of speculative decoding: call it right after decode_step. */
+int im_cuda_model_last_hidden_state(im_model *m, int rows, float *out_host);
 int im_cuda_model_seq_pos(const im_model *m);
 int im_cuda_model_max_seq_len(const im_model *m);
 size_t im_cuda_model_memory_bytes(const im_model *m);

@@ -93,6 +93,7 @@ IM_EXPORT int im_cuda_device_open(int ordinal, im_device **out) {
     rc = im::dev_malloc(d, (void **)&d->sk_partial, (size_t)d->sm_count * 2 * 64 * sizeof(float));
     if (rc == IM_OK) rc = im::dev_malloc(d, (void **)&d->sk_counters, (size_t)im::kSkMaxBlocks * sizeof(int));
     if (rc == IM_OK) rc = im::dev_malloc(d, (void **)&d->err_flag, sizeof(int));
+    if (rc == IM_OK) rc = im::dev_malloc(d, (void **)&d->gemm_partial, im::kGemmPartialBytes);
     if (rc == IM_OK && (cudaMemset(d->sk_counters, 0, (size_t)im::kSkMaxBlocks * sizeof(int)) != cudaSuccess ||
                         cudaMemset(d->err_flag, 0, sizeof(int)) != cudaSuccess))
         rc = im::fail(IM_ERR_CUDA, "scratch initialisation failed");
@@ -110,6 +111,7 @@ IM_EXPORT void im_cuda_device_free(im_device *dev) {
     cudaFree(dev->sk_partial);
     cudaFree(dev->sk_counters);
     cudaFree(dev->err_flag);
+    cudaFree(dev->gemm_partial);
     delete dev;
 }
 

@@ -50,7 +50,11 @@ struct Device {
     float *sk_partial = nullptr;
     int *sk_counters = nullptr;
     int *err_flag = nullptr;  // set by a kernel whose bounded wait ran out
+    // f32 slices of a K-split tensor-core GEMM (gemm_tc.cu; few tokens against few row tiles).  One GEMM in flight per
+    // device handle at a time.
+    float *gemm_partial = nullptr;
 };
+constexpr size_t kGemmPartialBytes = (size_t)8 << 20;
 constexpr int kSkMaxBlocks = 1 << 17;  // row blocks the counters cover (2M rows)
 
 // cudaFuncSetAttribute applies to the current device: remember per device ordinal (not per thread) whether a
@@ -90,6 +94,9 @@ struct AffineWeight {
     size_t bytes = 0;
 };
 
+// bytes of one tile of the tile-major weight stream: 16 rows x 128 columns of codes + 16 (scale, zero) fp16 pairs
+inline size_t tile_bytes_of(int bits) { return bits == 4 ? 1088 : 2112; }
+
 struct V2Params {
     const uint8_t *tiles;  // [nblk][G][1088]: 1024 bytes of nibbles + 16 (scale, zero) pairs per tile
     const __half *awq, *x, *b, *gamma;
@@ -109,7 +116,8 @@ struct V2Params {
 int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __half *xs_scratch, cudaStream_t st);
 // Gate/up pair as one tile stream (matvec.cu); built on first use.
 int ensure_pair(const AffineWeight *gate, const AffineWeight *up, cudaStream_t st);
-int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st);
+int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st, int bits = 4);
+int v2_repack8(const uint8_t *codes, const __half2 *sz, int N, int K, int G, int nblk, uint8_t *tiles, cudaStream_t st);
 int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, const __half2 *sz1, int N, int K, int G, int nblk,
               int rows_per_blk, uint8_t *tiles, cudaStream_t st);
 

@@ -17,6 +17,8 @@
 // tcgen05.commit releases a stage when its eight MMAs have read it.  After the last group warps 0-3 read their 32
 // TMEM lanes each (tcgen05.ld 32x32b), convert and write fp16 outputs.  Every wait is bounded; a wait that runs
 // out sets the device error word, the kernel still frees its tensor memory and returns.
+#include <algorithm>
+
 #include "common.cuh"
 #include "v2_device.cuh"
 
@@ -70,6 +72,11 @@ struct GemmParams {
     __half *y;             // [M, N]
     int N, K, G, M;
     int *err;
+    // K split (few tokens, few row tiles): CTA z covers groups [z * gps, min(G, (z + 1) * gps)) and leaves its f32 sums in
+    // partial[z][m][n]; gemm_splitk_reduce_kernel adds the slices in z order and rounds once.  partial == nullptr: one
+    // CTA per tile covers every group and writes fp16 itself.
+    float *partial;
+    int gps;
 };
 
 // 8 nibbles of a word -> 8 fp16 values (q - z) * s in memory order.  c = 1024 + z, exact for integer z in
@@ -135,7 +142,8 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
     const uint32_t tmem_d = *tmem_slot;
     pdl_wait();
 
-    const int G = p.G;
+    const int g_begin = blockIdx.z * p.gps;
+    const int G = min(p.G, g_begin + p.gps) - g_begin;  // this CTA's groups (stages), >= 1 by construction of the grid
     bool ok = true;
     if (warp < kGWarpsA) {
         // ---------------------------------------------------------------- weights: dequantise into operand A
@@ -143,8 +151,8 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
         // codes of the next stage are requested before this stage is converted, so the memory latency is paid once.
         const int r = tid & 127, h = tid >> 7, n = n0 + r;
         const bool live = n < p.N;
-        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * (p.K / 2) + h * 32;
-        const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * G;
+        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * (p.K / 2) + (size_t)g_begin * 64 + h * 32;
+        const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * p.G + g_begin;
         const uint32_t row_off = (uint32_t)(h * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
         // register ring of the next kGAhead stages' codes: 32 bytes per stage in flight per thread, enough to cover the
         // memory latency at one stage per ~0.3 us
@@ -217,7 +225,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
         constexpr int kPer = TN / 8, kAhead = 2;
         const int c = t2 & 15, r0 = t2 >> 4;
         const uint32_t off0 = (uint32_t)((c >> 3) * (TN * 128) + r0 * 128 + (((c & 7) ^ r0) << 4));
-        const __half *src0 = p.xs + (size_t)c * 8;
+        const __half *src0 = p.xs + (size_t)g_begin * kGK + (size_t)c * 8;
         for (int it = 0; it < G + kAhead; it++) {
             // announce the stage whose copies have landed BEFORE waiting for a free slot for the next one: the other
             // order would make every MMA wait for its predecessor to retire
@@ -278,10 +286,19 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
                 uint32_t r[32];
                 tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
                 if (n < p.N) {
+                    if (p.partial) {
+                        float *dst = p.partial + (size_t)blockIdx.z * p.M * p.N + n;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int m = m0 + c0 + i;
-                        if (m < p.M) p.y[(size_t)m * p.N + n] = __float2half_rn(__uint_as_float(r[i]));
+                        for (int i = 0; i < 32; i++) {
+                            const int m = m0 + c0 + i;
+                            if (m < p.M) dst[(size_t)m * p.N] = __uint_as_float(r[i]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int m = m0 + c0 + i;
+                            if (m < p.M) p.y[(size_t)m * p.N + n] = __float2half_rn(__uint_as_float(r[i]));
+                        }
                     }
                 }
             }
@@ -315,6 +332,21 @@ __global__ void act_scale_kernel(const __half *__restrict__ x, const __half *__r
     *reinterpret_cast<uint4 *>(xs + i) = v;
 }
 
+// y[i] = f16(partial[0][i] + partial[1][i] + ...), slices added in order: one rounding, as the unsplit kernel's epilogue
+__global__ void gemm_splitk_reduce_kernel(const float *__restrict__ partial, __half *__restrict__ y, size_t n, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 a = *reinterpret_cast<const float4 *>(partial + i);
+    for (int z = 1; z < splits; z++) {
+        const float4 b = *reinterpret_cast<const float4 *>(partial + (size_t)z * n + i);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    const __half2 lo = __floats2half2_rn(a.x, a.y), hi = __floats2half2_rn(a.z, a.w);
+    *reinterpret_cast<uint2 *>(y + i) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+}
+
 template <int TN>
 int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     constexpr int kGStages = gemm_stages<TN>();
@@ -323,8 +355,13 @@ int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     auto kern = gemm_int4_tc_kernel<TN>;
     static DeviceOnce once;  // per instantiation
     if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((p.N + kGM - 1) / kGM, (p.M + TN - 1) / TN);
+    const int splits = (p.G + p.gps - 1) / p.gps;
+    dim3 grid((p.N + kGM - 1) / kGM, (p.M + TN - 1) / TN, splits);
     IM_CUDA_CHECK(launch_k(kern, grid, dim3(kGThreads), smem, st, p));
+    if (p.partial) {
+        const size_t n = (size_t)p.M * p.N;  // N is a multiple of 4 here (checked by the caller)
+        IM_CUDA_CHECK(launch_k(gemm_splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, (const float *)p.partial, p.y, n, splits));
+    }
     return IM_OK;
 }
 
@@ -336,7 +373,19 @@ int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __h
     if (w->bits != 4 || w->group_size != 128 || w->K % 128 != 0 || M < 1) return IM_ERR_BOUNDS;
     const size_t n = (size_t)M * w->K;
     IM_CUDA_CHECK(launch_k(act_scale_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, x, (const __half *)w->awq, xs_scratch, n, w->K));
-    GemmParams p{w->codes, w->sz, xs_scratch, y, w->N, w->K, w->G, M, w->dev->err_flag};
+    GemmParams p{w->codes, w->sz, xs_scratch, y, w->N, w->K, w->G, M, w->dev->err_flag, nullptr, w->G};
+    // Few tokens and few row tiles (decode batches of 16-64 against 4096-6144 rows: 32-48 CTAs of 32-112 sequential
+    // stages): split K so that the grid covers the GPU.  At least four groups per slice; the slices' f32 sums go through
+    // the device handle's scratch (one GEMM in flight per handle, like the tiled matvec).
+    if (M <= 64 && w->N % 4 == 0 && w->dev->gemm_partial) {
+        const int tiles = (w->N + kGM - 1) / kGM;
+        int splits = std::min(w->dev->sm_count / tiles, w->G / 4);
+        while (splits > 1 && (size_t)splits * M * w->N * sizeof(float) > kGemmPartialBytes) splits--;
+        if (splits > 1) {
+            p.gps = (w->G + splits - 1) / splits;
+            p.partial = w->dev->gemm_partial;
+        }
+    }
     // a 256-token tile shares every dequantised weight tile between twice as many tokens, but halves the CTA count:
     // worth it only once the grid still covers the GPU
     const long long ctas256 = (long long)((w->N + kGM - 1) / kGM) * ((M + 255) / 256);

@@ -528,6 +528,7 @@ int ensure_pair(const AffineWeight *gate_c, const AffineWeight *up, cudaStream_t
 template <int MODE>
 static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const AffineWeight *up, int B, cudaStream_t st) {
     V2Params q{};
+    if (w->bits != 4 && MODE != kPlain) return IM_ERR_BOUNDS;  // 8-bit tiles: the plain projection only
     if (MODE & 1) {
         if ((w->N + 7) / 8 > kSkMaxBlocks) return IM_ERR_BOUNDS;
         int rc = ensure_pair(w, up, st);
@@ -549,11 +550,11 @@ static int run_matvec_v2(const MatvecParams &p, const AffineWeight *w, const Aff
         q.y = p.y + (size_t)done * p.N;
         q.residual_out = p.residual_out ? p.residual_out + (size_t)done * p.K : nullptr;
         q.normed_out = p.normed_out ? p.normed_out + (size_t)done * p.K : nullptr;
-        int rc = v2_run(MODE, nb, q, w->dev, st);
+        int rc = v2_run(MODE, nb, q, w->dev, st, w->bits);
         // the staged activations of four (or two) batch rows may not fit beside the ring for a long K: fewer rows per launch
         while (rc == IM_ERR_BOUNDS && nb > 1) {
             nb /= 2;
-            rc = v2_run(MODE, nb, q, w->dev, st);
+            rc = v2_run(MODE, nb, q, w->dev, st, w->bits);
         }
         if (rc != IM_OK) return rc;  // IM_ERR_BOUNDS on the first chunk: caller falls back
         done += nb;
@@ -565,7 +566,7 @@ template <int MODE>
 static int run_matvec(MatvecParams p, const AffineWeight *w, int B, cudaStream_t st, const AffineWeight *up = nullptr) {
     const Device *dev = w->dev;
     const size_t xstride = (size_t)p.K, ystride = (size_t)p.N;
-    if (w->tiles && (MODE != kGateUpAct || (up && up->tiles))) {
+    if (w->tiles && (w->bits == 4 || MODE == kPlain) && (MODE != kGateUpAct || (up && up->tiles && up->bits == 4))) {
         const int rc = run_matvec_v2<MODE>(p, w, up, B, st);
         if (rc != IM_ERR_BOUNDS) return rc;  // shapes whose activations do not fit beside the ring use the kernel below
     }
@@ -676,13 +677,14 @@ static int weight_create_common(im_device *dev, const void *qdata, const void *s
     if (e == cudaSuccess && host_src) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return bail(fail(IM_ERR_CUDA, "weight repack failed: %s", cudaGetErrorString(e)));
     cleanup();
-    if (bit_width == 4 && group_size == kGroup && K % kGroup == 0 && (N + 15) / 16 <= kSkMaxBlocks) {
+    if ((bit_width == 4 || bit_width == 8) && group_size == kGroup && K % kGroup == 0 && (N + 15) / 16 <= kSkMaxBlocks) {
         // tile-major copy for the bulk-staged kernel
         w->nblk = (N + 15) / 16;
-        const size_t tb = (size_t)w->nblk * w->G * 1088;
+        const size_t tb = (size_t)w->nblk * w->G * tile_bytes_of(bit_width);
         if ((rc = dev_malloc(dev, (void **)&w->tiles, tb)) != IM_OK) return bail(rc);
         w->bytes += tb;
-        rc = v2_repack(w->codes, w->sz, nullptr, nullptr, N, K, w->G, w->nblk, 16, w->tiles, st);
+        rc = bit_width == 4 ? v2_repack(w->codes, w->sz, nullptr, nullptr, N, K, w->G, w->nblk, 16, w->tiles, st)
+                            : v2_repack8(w->codes, w->sz, N, K, w->G, w->nblk, w->tiles, st);
         if (rc == IM_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(IM_ERR_CUDA, "tile repack failed");
         if (rc != IM_OK) return bail(rc);
     }
@@ -715,7 +717,7 @@ IM_EXPORT void im_cuda_affine_weight_free(im_affine_weight *w) {
     im::dev_free(w->dev, w->codes, (code_bytes + 15) / 16 * 16);
     im::dev_free(w->dev, w->sz, (size_t)w->N * w->G * sizeof(__half2));
     im::dev_free(w->dev, w->awq, (size_t)w->K * sizeof(__half));
-    im::dev_free(w->dev, w->tiles, (size_t)w->nblk * w->G * 1088);
+    im::dev_free(w->dev, w->tiles, (size_t)w->nblk * w->G * im::tile_bytes_of(w->bits));
     im::dev_free(w->dev, w->pair_tiles, (size_t)w->pair_nblk * w->G * 1088);
     delete w;
 }

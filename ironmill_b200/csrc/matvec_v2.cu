@@ -16,8 +16,9 @@
 // consumers compute.  A consumer warp handles two tiles per stage: two 128-bit shared loads give
 // each thread the 8 nibble words of its two rows, three logic operations per word split them
 // into byte lanes, and four mma.sync m16n8k32 (u8 x s8 -> s32) multiply them with the
-// activations, which were block-quantised once per CTA to 16 bits per value (signed high byte
-// in one B column, signed low byte in the next; up to four batch rows share one instruction).
+// activations, which were block-quantised once per CTA to 24-bit integers per 128-group (three
+// signed byte planes in three B columns, the fourth column zero; two batch rows share one
+// instruction, four a pass over the tile: TileMath, v2_device.cuh).
 // Integer sums are exact inside a group; one float fix-up per tile applies
 //   s * sx * (sum_k xi_k q_k - z * sum_k xi_k).
 // Work is split stream-K fashion: every CTA gets the same number of tiles (+-1) out of the
@@ -85,11 +86,14 @@ __device__ __forceinline__ float v2_stage_x(const V2Params &p, int b, uint32_t *
 // Stage schedule (the producer lane and every consumer warp walk the same list): the CTA owns the
 // flattened tile range [t_begin, t_end); a stage is the next run of at most kStageTiles tiles that
 // stays inside one row block.
-template <int MODE, int NB>
+template <int MODE, int NB, int BITS>
 __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int G = p.G, nring = p.nring;
-    constexpr int stage_bytes = kStageTiles * kTileBytes;
+    using TG = TileGeom<BITS>;
+    using Iter = StageIterT<TG::kStageTiles>;
+    constexpr int kTileBytes = TG::kTileBytes;  // (shadows the 4-bit constants of the namespace on purpose)
+    constexpr int stage_bytes = TG::kStageTiles * kTileBytes;
     unsigned char *ring = smem;                                                        // nring * stage_bytes
     uint32_t *xq = reinterpret_cast<uint32_t *>(ring + (size_t)nring * stage_bytes);   // G * 3NB * 32 words
     float2 *meta = reinterpret_cast<float2 *>(xq + (size_t)G * 3 * NB * 32);           // G * NB * 2
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
                 }
             }
         };
-        StageIter issue(t_begin, t_end, G), done(t_begin, t_end, G);
+        Iter issue(t_begin, t_end, G), done(t_begin, t_end, G);
         int t0, n, rb0, grp0, dt0, dn, drb, dgrp;
         int slot = 0, phase = 0;  // slot of the stage being issued; phase = parity of the ring pass that last used it
         bool ok = true;
@@ -253,14 +257,18 @@ __global__ void __launch_bounds__(kV2Threads, 1) matvec_v2_kernel(const V2Params
 
     // A warp whose wait ran out stops computing but keeps every barrier of the schedule, so that
     // the other warps and the producer still run to the end; the host sees the error word.
-    StageIter it(t_begin, t_end, G);
+    Iter it(t_begin, t_end, G);
     int t0, n, rb, grp0, slot = 0, phase = 0;
     while (it.next(t0, n, rb, grp0)) {
         if (!dead && !mbar_wait_warp(&full[slot], phase, p.err)) dead = true;
         const unsigned char *st = ring + (size_t)slot * stage_bytes;
         if (!dead && warp < n) {
-            const int tb = warp + kV2Consumers;
-            tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq, meta, lane);
+            if (BITS == 4) {
+                const int tb = warp + kV2Consumers;
+                tm.pair(st + (size_t)warp * kTileBytes, grp0 + warp, st + (size_t)tb * kTileBytes, grp0 + tb, tb < n, xq, meta, lane);
+            } else {
+                tm.single8(st + (size_t)warp * kTileBytes, grp0 + warp, xq, meta, lane);
+            }
         }
         if (grp0 + n == G || t0 + n == t_end) {  // last stage of this row block inside the CTA's range:
             float *buf = red + slot * (kV2Consumers * 64);  // hand the partial sums to the producer warp
@@ -319,9 +327,38 @@ int v2_repack(const uint8_t *codes0, const __half2 *sz0, const uint8_t *codes1, 
     return IM_OK;
 }
 
-template <int MODE, int NB>
+// 8-bit codes: row-major [N][K] -> tiles of 2112 bytes in the plane order TileMath::single8 reads.  One thread per 16-byte
+// chunk: chunk i of a tile = plane (i >> 5) = 2 * (row half) + (column part), lane i & 31 = (g, t); its source is the 16
+// consecutive codes of row g + 8 * half at columns 32 t + 16 * part, split into (even, odd) bytes per 8 columns.
+__global__ void v2_repack8_kernel(const uint8_t *__restrict__ codes, const __half2 *__restrict__ sz, int N, int K, int G, int nblk,
+                                  uint8_t *__restrict__ tiles) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nchunks = (size_t)nblk * G * 128;
+    if (i >= nchunks) return;
+    const int lane = i & 31, part = (i >> 5) & 1, half = (i >> 6) & 1;
+    const size_t tile = i >> 7;
+    const int grp = (int)(tile % G), rb = (int)(tile / G);
+    const int g = lane >> 2, t = lane & 3, r = g + 8 * half, row = rb * 16 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < N) v = *reinterpret_cast<const uint4 *>(codes + (size_t)row * K + grp * 128 + 32 * t + 16 * part);
+    uint8_t *dst = tiles + tile * TileGeom<8>::kTileBytes;
+    *reinterpret_cast<uint4 *>(dst + (2 * half + part) * 512 + lane * 16) =
+        make_uint4(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531), __byte_perm(v.z, v.w, 0x6420), __byte_perm(v.z, v.w, 0x7531));
+    if (part == 0 && t == 0)
+        reinterpret_cast<__half2 *>(dst + TileGeom<8>::kCodeBytes)[r] =
+            row < N ? sz[(size_t)row * G + grp] : __halves2half2(__float2half(0.0f), __float2half(0.0f));
+}
+
+int v2_repack8(const uint8_t *codes, const __half2 *sz, int N, int K, int G, int nblk, uint8_t *tiles, cudaStream_t st) {
+    const size_t nchunks = (size_t)nblk * G * 128;
+    v2_repack8_kernel<<<(unsigned)((nchunks + 255) / 256), 256, 0, st>>>(codes, sz, N, K, G, nblk, tiles);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+}
+
+template <int MODE, int NB, int BITS = 4>
 static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
-    const size_t stage_bytes = (size_t)kStageTiles * kTileBytes;
+    const size_t stage_bytes = (size_t)TileGeom<BITS>::kStageTiles * TileGeom<BITS>::kTileBytes;
     const size_t red_buf = (size_t)kV2Consumers * 64 * 4;  // one partial-sum buffer per ring slot
     const size_t fixed = (size_t)p.G * 3 * NB * 32 * 4 + (size_t)p.G * NB * 16 + 32 * 4 + 64;
     const size_t per_slot = stage_bytes + 16 + red_buf;
@@ -331,7 +368,7 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
     if (nring > 8) nring = 8;
     p.nring = nring;
     const size_t smem = fixed + (size_t)nring * per_slot;
-    auto kern = matvec_v2_kernel<MODE, NB>;
+    auto kern = matvec_v2_kernel<MODE, NB, BITS>;
     static DeviceOnce once;  // per instantiation
     if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->smem_optin));
     const long long total = (long long)p.nblk * p.G;
@@ -344,7 +381,14 @@ static int v2_launch(V2Params p, const Device *dev, cudaStream_t st) {
 }
 
 // mode: bit 0 gate+up epilogue (paired tiles), bit 1 residual+norm prologue.  IM_ERR_BOUNDS if the shape does not fit.
-int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st) {
+int v2_run(int mode, int nb, const V2Params &p, const Device *dev, cudaStream_t st, int bits) {
+    if (bits == 8) {  // 8-bit codes: the plain projection only (the reference has no fused 8-bit kernels)
+        if (mode != 0) return IM_ERR_BOUNDS;
+        if (nb == 1) return v2_launch<0, 1, 8>(p, dev, st);
+        if (nb == 2) return v2_launch<0, 2, 8>(p, dev, st);
+        if (nb == 4) return v2_launch<0, 4, 8>(p, dev, st);
+        return fail(IM_ERR_INVALID, "unsupported v2 matvec batch %d", nb);
+    }
 #define V2_CASE(M, B) \
     if (mode == M && nb == B) return v2_launch<M, B>(p, dev, st);
     V2_CASE(0, 1) V2_CASE(0, 2) V2_CASE(0, 4) V2_CASE(1, 1) V2_CASE(1, 2) V2_CASE(1, 4) V2_CASE(2, 1) V2_CASE(2, 2) V2_CASE(2, 4) V2_CASE(3, 1) V2_CASE(3, 2) V2_CASE(3, 4)

@@ -465,7 +465,7 @@ static AffineWeight row_view(const AffineWeight *w, int row0, int rows) {
     v.N = rows;
     v.codes = w->codes ? w->codes + (size_t)row0 * ((size_t)w->K * w->bits / 8) : nullptr;
     v.sz = w->sz ? w->sz + (size_t)row0 * w->G : nullptr;
-    v.tiles = w->tiles ? w->tiles + (size_t)(row0 / 16) * w->G * 1088 : nullptr;
+    v.tiles = w->tiles ? w->tiles + (size_t)(row0 / 16) * w->G * tile_bytes_of(w->bits) : nullptr;
     v.nblk = (rows + 15) / 16;
     v.pair_tiles = nullptr;
     v.pair_with = nullptr;
@@ -1440,6 +1440,26 @@ IM_EXPORT int im_cuda_model_truncate(im_model *m, int pos) {
     if (pos < 0 || pos > m->slot_pos[0]) return fail(IM_ERR_BOUNDS, "truncate_to(%d) is outside the current sequence of %d tokens", pos, m->slot_pos[0]);
     IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
     return set_positions(m, pos);
+    IM_GUARD_END
+}
+
+// The final RMSNorm output the lm_head consumed in the last step (norm_out of
+// crates/ironmill-inference/src/metal/pipeline.rs:176-226, decode_step_with_hidden / last_hidden_state), fp16 widened
+// to f32: `rows` rows of hidden_size, one per sequence of that step in its order (row 0 for the single-sequence calls;
+// after prefill_all_logits: one row per token of the last chunk).
+IM_EXPORT int im_cuda_model_last_hidden_state(im_model *m, int rows, float *out_host) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(m && out_host, "bad argument");
+    if (!m->finalized) return fail(IM_ERR_STATE, "model not loaded");
+    const int cap = m->MT;
+    if (rows < 1 || rows > cap) return fail(IM_ERR_BOUNDS, "rows must be in 1..%d, got %d", cap, rows);
+    IM_CUDA_CHECK(cudaSetDevice(m->dev->ordinal));
+    const size_t n = (size_t)rows * m->cfg.hidden_size;
+    std::vector<__half> tmp(n);
+    IM_CUDA_CHECK(cudaMemcpyAsync(tmp.data(), m->norm_out, n * sizeof(__half), cudaMemcpyDeviceToHost, m->stream));
+    IM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
+    for (size_t i = 0; i < n; i++) out_host[i] = __half2float(tmp[i]);
+    return IM_OK;
     IM_GUARD_END
 }
 

@@ -10,6 +10,15 @@ constexpr int kV2Threads = (kV2Consumers + 1) * 32;
 constexpr int kTileCodeBytes = 1024;
 constexpr int kTileBytes = 1088;     // 1024 bytes of nibbles + 16 (scale, zero) fp16 pairs, contiguous
 constexpr int kStageTiles = 32;      // tiles per stage: two per consumer warp
+// 8-bit codes: a tile is 16 rows x 128 columns = 2048 bytes of codes + the same 16 (scale, zero) pairs; a stage holds one
+// tile per consumer warp (about the same bytes as a 4-bit stage).
+template <int BITS>
+struct TileGeom {
+    static constexpr int kCodeBytes = BITS == 4 ? im::kTileCodeBytes : 2048;
+    static constexpr int kTileBytes = kCodeBytes + 64;
+    static constexpr int kStageTiles = BITS == 4 ? im::kStageTiles : kV2Consumers;
+};
+static_assert(TileGeom<4>::kTileBytes == 1088 && TileGeom<8>::kTileBytes == 2112, "tile_bytes_of (common.cuh) states these sizes");
 constexpr unsigned long long kWaitLimitNs = 400ull * 1000 * 1000;  // bounded mbarrier waits: give up, flag, carry on without computing
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -183,6 +192,47 @@ struct TileMath {
             if (have_b) fix_up(cbl, cbh, tile_b, grp_b, meta, s, g, t);
         }
     }
+    // One tile of 8-bit codes.  Tile layout (v2_repack8_kernel): four 512-byte planes [row g | row g + 8][column chunks
+    // 0-1 | 2-3], 16 bytes per lane each = words (even columns of chunk j, odd columns of chunk j, even of j + 1, odd of
+    // j + 1): the codes are u8 operands as they lie, the B fragments are the ones the 4-bit tiles use (the even / odd
+    // split there comes from the nibble order).  The sums carry no factor 16, so the fix-up multiplies by it (exactly).
+    __device__ __forceinline__ void single8(const unsigned char *tile, int grp, const uint32_t *xq, const float2 *meta, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint4 a0 = *reinterpret_cast<const uint4 *>(tile + lane * 16);          // row g, chunks 0-1
+        const uint4 a1 = *reinterpret_cast<const uint4 *>(tile + 512 + lane * 16);    // row g, chunks 2-3
+        const uint4 c0 = *reinterpret_cast<const uint4 *>(tile + 1024 + lane * 16);   // row g + 8, chunks 0-1
+        const uint4 c1 = *reinterpret_cast<const uint4 *>(tile + 1536 + lane * 16);   // row g + 8, chunks 2-3
+        uint4 l0[kSets], l1[kSets];
+        if (CACHE) {
+            if (grp != ga) {
+                ga = grp;
+                load_frag(xq, grp, g, t, xa0, xa1);
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < kSets; s++) l0[s] = l1[s] = make_uint4(0, 0, 0, 0);
+            load_frag(xq, grp, g, t, l0, l1);
+        }
+        const uint4 (&f0)[kSets] = CACHE ? xa0 : l0, (&f1)[kSets] = CACHE ? xa1 : l1;
+#pragma unroll
+        for (int s = 0; s < kSets; s++) {
+            int ce[4], co[4];
+            mma_u8s8_z(ce, a0.x, c0.x, a0.z, c0.z, f0[s].x, f0[s].z);
+            mma_u8s8_z(co, a0.y, c0.y, a0.w, c0.w, f0[s].y, f0[s].w);
+            mma_u8s8(ce, a1.x, c1.x, a1.z, c1.z, f1[s].x, f1[s].z);
+            mma_u8s8(co, a1.y, c1.y, a1.w, c1.w, f1[s].y, f1[s].w);
+            const int b = 2 * s + (t >> 1);
+            if (b < NB) {
+                const float2 m = meta[(grp * NB + b) * 2 + (t & 1)];
+                const __half2 *szp = reinterpret_cast<const __half2 *>(tile + TileGeom<8>::kCodeBytes);
+                const float2 sz0 = __half22float2(szp[g]), sz1 = __half22float2(szp[g + 8]);
+                const float f0v = fmaf((float)(ce[0] + co[0]), 4096.0f, (float)(ce[1] + co[1]) * 16.0f);
+                const float f1v = fmaf((float)(ce[2] + co[2]), 4096.0f, (float)(ce[3] + co[3]) * 16.0f);
+                acc0[s] = fmaf(sz0.x * m.x, fmaf(-sz0.y, m.y, f0v), acc0[s]);
+                acc1[s] = fmaf(sz1.x * m.x, fmaf(-sz1.y, m.y, f1v), acc1[s]);
+            }
+        }
+    }
     // Sums of rows g and g + 8 of batch row 2 s + t / 2, valid in both lanes of the pair afterwards.
     __device__ __forceinline__ void row_sums(int s, float &r0, float &r1) const {
         r0 = acc0[s] + __shfl_xor_sync(0xffffffffu, acc0[s], 1);
@@ -235,12 +285,13 @@ __device__ __forceinline__ void stage_chunk24(float (&v)[8], bool live, int grp,
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kV2Consumers * 32) : "memory"); }
 
 
-struct StageIter {  // 32-bit and division-free in the loop: a 64-bit divide costs more than a tile
+template <int S>
+struct StageIterT {  // 32-bit and division-free in the loop: a 64-bit divide costs more than a tile
     int t, t_end, G, rb, grp;
-    __device__ StageIter(int t_begin, int t_end_, int G_) : t(t_begin), t_end(t_end_), G(G_), rb(t_begin / G_), grp(t_begin % G_) {}
+    __device__ StageIterT(int t_begin, int t_end_, int G_) : t(t_begin), t_end(t_end_), G(G_), rb(t_begin / G_), grp(t_begin % G_) {}
     __device__ bool next(int &t0, int &n, int &rb0, int &grp0) {
         if (t >= t_end) return false;
-        n = min(min(kStageTiles, G - grp), t_end - t);
+        n = min(min(S, G - grp), t_end - t);
         t0 = t;
         rb0 = rb;
         grp0 = grp;
@@ -253,5 +304,6 @@ struct StageIter {  // 32-bit and division-free in the loop: a 64-bit divide cos
         return true;
     }
 };
+using StageIter = StageIterT<kStageTiles>;
 
 }  // namespace im

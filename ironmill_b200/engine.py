@@ -215,6 +215,20 @@ class CudaInference:
         check(lib().im_cuda_model_prefill_all_logits(self._model, vp(toks), C.c_int(toks.size), vp(out)))
         return out
 
+    @_wrap
+    def last_hidden_state(self, rows: int = 1) -> np.ndarray:
+        """MetalInference::last_hidden_state (metal/pipeline.rs:198-226): the final RMSNorm output the lm_head consumed in
+        the last step, fp16 widened to f32; [hidden] for rows = 1, else [rows, hidden] (one row per sequence of the step)."""
+        self._need_model()
+        out = np.empty((rows, self._mc.hidden_size), dtype=np.float32)
+        check(lib().im_cuda_model_last_hidden_state(self._model, C.c_int(rows), vp(out)))
+        return out[0] if rows == 1 else out
+
+    def decode_step_with_hidden(self, token: int):
+        """MetalInference::decode_step_with_hidden (metal/pipeline.rs:176-196): (logits, final hidden state)."""
+        logits = self.decode_step(token)
+        return logits, self.last_hidden_state()
+
     # ---- BatchInferenceEngine (engine.rs:121-131) ------------------------------------------------
     @_wrap
     def add_sequence(self, tokens) -> int:

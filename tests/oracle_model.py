@@ -250,6 +250,7 @@ class OracleModel:
                     rows = nx["qkv"].shape[0] if "kv_unrounded" in self.dev else nh * hd
                     pre = (self._mv32(nx["qkv"][:rows], nx["qkv_awq"], r * gam) * rms_inv).astype(np.float16)
         last = orc.rms_norm(hidden[-1:], self.final_norm, float(eps))
+        self.last_hidden = last[0].astype(np.float32)  # norm_out after the final norm (metal/pipeline.rs:176-226)
         logits = (last.astype(np.float32) @ self.lm.T).astype(np.float16).astype(np.float32)
         self.pos += T
         return logits[0]

@@ -34,6 +34,13 @@ def test_shapes_and_token_tails(dev, N, K, M):
     _check(dev, H.QWeight(N, K, seed=N + M, name="g"), M)
 
 
+@pytest.mark.parametrize("N,K,M", [(512, 2048, 16), (512, 2048, 64), (384, 1792, 33), (1024, 14336, 16), (200, 1024, 7)])
+def test_k_split_for_few_tokens(dev, N, K, M):
+    # at most 64 tokens against few 128-row tiles: the grid is cut along K (four slices here; an uneven last slice at
+    # K = 1792 = 14 groups; ragged rows at N = 200), the f32 slices are added in order and rounded once
+    _check(dev, H.QWeight(N, K, awq=True, seed=N + K + M, name="gk"), M)
+
+
 def test_awq_and_ragged_rows(dev):
     # N not a multiple of the 128-row CTA tile: the last CTA's spare rows are masked
     _check(dev, H.QWeight(200, 512, awq=True, seed=3, name="ga"), 48)
@@ -54,7 +61,7 @@ def test_unusual_zero_points_take_the_f32_path(dev):
 
 
 def test_matches_the_matvec_kernel_rows(dev):
-    # the same weight through the decode matvec (16-bit integer activations) and the GEMM: both within their tolerance of the oracle
+    # the same weight through the decode matvec (24-bit integer activations) and the GEMM: both within their tolerance of the oracle
     from ironmill_b200 import ops
     qw = H.QWeight(512, 1024, awq=True, seed=11, name="gm")
     w = qw.gpu(dev)

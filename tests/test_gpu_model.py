@@ -279,6 +279,31 @@ def test_prefill_all_logits_rows_match_step_by_step_prefills():
         assert np.abs(allg[n - 1] - ref.forward(prompt[:n])).max() <= 5e-2
 
 
+def test_decode_step_with_hidden_returns_the_final_norm_output():
+    # MetalInference::decode_step_with_hidden (metal/pipeline.rs:176-226): logits and the vector the lm_head consumed.
+    # Both decode schedules; the hidden state against the oracle's (values of order 1: 2e-2 is ~5 fp16 ulps at 2-4),
+    # and logits recomputed from the returned hidden state with the fp16 lm_head must be the returned logits.
+    from ironmill_b200.engine import CudaConfig, CudaInference
+    cfg = _cfg("llama", 2, 256, 512, 4, 2, 333, 5e5, 1e-5)
+    tensors = synth_model(cfg, seed=18, awq=True)
+    tqc = orc.TqConstants(128, 8, seed=42)
+    prompt = H.rng_for("hid").integers(0, 333, 9).astype(np.uint32)
+    lm = tensors["lm_head.weight"].data.astype(np.float32)
+    for schedule in ("auto", "per_kernel"):
+        eng = CudaInference(CudaConfig(max_seq_len=64, decode_schedule=schedule))
+        eng.load_weights(DictProvider(cfg, tensors), tq_signs=tqc.signs, tq_qjl=tqc.qjl)
+        ref = OracleModel(cfg, tensors, tqc, 64)
+        eng.prefill(prompt)
+        ref.forward(prompt)
+        assert np.abs(eng.last_hidden_state() - ref.last_hidden).max() <= 2e-2
+        for tok in (7, 100, 45):
+            logits, hid = eng.decode_step_with_hidden(tok)
+            ref.forward(np.array([tok], dtype=np.uint32))
+            assert hid.shape == (256,) and np.abs(hid - ref.last_hidden).max() <= 2e-2, schedule
+            again = (hid @ lm.T).astype(np.float16).astype(np.float32)
+            assert np.abs(again - logits).max() <= 4e-3, schedule   # same fp16 inputs, another summation order
+
+
 def test_quantized_embedding_and_lm_head_load_as_dense():
     """A bundle may quantize model.embed_tokens.weight and lm_head.weight (crates/ironmill-inference/src/metal/weights.rs:305-420):
     the backend dequantises them at load.  Logits must equal those of the same model handed the dequantised fp16 tables."""
