@@ -260,6 +260,24 @@ int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, const void *
 size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);
 int im_cuda_tq_reserve_scratch(im_tq *tq, size_t bytes);
 
+/* ---- fp16 (unquantized) KV cache: the reference's path with TurboQuant off ----------------------------------------
+ * (ironmill-inference/src/metal/attention.rs:491-612).  head_dim must be 128.
+ * im_cuda_kv_scatter_f16 replaces kv_scatter (shaders/kv/kv_scatter.metal:20-42): proj fp16 [nseq*T, nkv, head_dim] is
+ * written to cache fp16 [slots, nkv, max_seq, head_dim] at position (base_pos + pos_dev[slot] + t) % max_seq of the
+ * token's sequence (slot_map_dev: optional sequence -> cache slot).
+ * im_cuda_sdpa_f16 replaces fused_sdpa (shaders/attention/fused_sdpa.metal:52-251), prefill_attention_v2
+ * (shaders/attention/attention.metal:571-750) and the pair fused_sdpa_split / fused_sdpa_reduce
+ * (shaders/attention/flash_decode.metal:25-215): out[t, h] = softmax(scale * q[t, h] . K^T) V over the positions
+ * 0 .. base_pos + pos_dev[seq] + t of the head's KV head (causal), fp16 in and out, f32 scores and sums.
+ * q, out fp16 [nseq*T, nh, head_dim].  num_splits = 0 lets the library choose (1 = single pass); more than one split
+ * needs scratch_dev of im_cuda_sdpa_f16_scratch_bytes(nseq, T, nh, splits) bytes. */
+int im_cuda_kv_scatter_f16(const void *proj_dev, void *cache_dev, int nseq, int T, int nkv, int head_dim, int max_seq, int base_pos,
+                           const int *pos_dev, const int *slot_map_dev, void *stream);
+size_t im_cuda_sdpa_f16_scratch_bytes(int nseq, int T, int nh, int splits);
+int im_cuda_sdpa_f16(im_device *dev, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev, void *out_dev, int nseq, int nh,
+                     int nkv, int head_dim, int max_seq, int base_pos, const int *pos_dev, int T, float scale, int num_splits,
+                     void *scratch_dev, size_t scratch_bytes, void *stream);
+
 /* ------------------------------------------------------------------ model-level engine
  * The CUDA counterpart of MetalInference behind the InferenceEngine trait
  * (crates/ironmill-inference/src/engine.rs:72-114; crates/ironmill-inference/src/metal/engine.rs:122-270,
@@ -281,7 +299,8 @@ typedef struct im_model_config {
     int rotary_dim;           /* 0 = head_dim */
     int qk_norm;              /* 1: q_norm / k_norm weights present (Qwen3) */
     int tie_word_embeddings;  /* 1: lm_head = embedding table */
-    int tq_bits;              /* MetalConfig.n_bits: TurboQuant KV bits, 8 or 4 (0 = 8) */
+    int tq_bits;              /* MetalConfig.n_bits: TurboQuant KV bits, 8 or 4 (0 = 8); 16 = MetalConfig.enable_turboquant
+                               * off: an unquantized fp16 KV cache (kv_scatter + fused_sdpa / FlashDecoding) */
     uint64_t rotation_seed;   /* MetalConfig.rotation_seed (default 42) */
     int tp_world, tp_rank;    /* tensor parallel group (0/0 = single GPU) */
     int prefill_chunk_size;   /* MetalConfig.prefill_chunk_size: tokens per prefill forward (0 = 256; at most 256) */

@@ -230,6 +230,26 @@ int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uin
                         int base_pos, const int *pos_dev, int T, int splits, cudaStream_t st, const float *qrot = nullptr,
                         const int *slot_map = nullptr);
 
+// ---- fp16 (unquantized) KV cache: kv_f16.cu ----
+struct Kv16Prep {
+    __half *qkv;  // [nseq*T, stride]: q | k | v of one token; the query heads are normed / rotated in place
+    int stride, k_off, v_off;
+    const __half *kv;  // nullptr, or the buffer [nseq*T, kv_stride] that holds the K and V rows (k_off / v_off index it)
+    int kv_stride;
+    const __half *qw, *kw, *cosc, *sinc;
+    int nh, nkv, rotary_dim, with_norm, T, nseq, max_seq, base_pos;
+    float eps;
+    const int *pos_dev;
+    const int *slot_map;  // optional: sequence index -> cache slot
+    __half *kc, *vc;      // [slots, nkv, max_seq, 128]
+};
+int kv16_prep_launch(const Kv16Prep &a, cudaStream_t st);
+size_t kv16_scratch_bytes(int tokens, int nh, int splits);
+int kv16_auto_splits(const Device *dev, int tokens, int nkv, int max_ctx);
+int kv16_attention_launch(const Device *dev, float *scratch, size_t scratch_bytes, const __half *q, int q_stride, const __half *kc, const __half *vc,
+                          float scale, __half *out, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, int splits,
+                          int ctx_hint, cudaStream_t st, const int *slot_map);
+
 }  // namespace im
 
 // The opaque handle types of the C ABI are thin tags over the internal structs.

@@ -1,0 +1,283 @@
+// Attention over an unquantized fp16 KV cache: the reference's path with TurboQuant switched off
+// (crates/ironmill-inference/src/metal/attention.rs:491-612):
+//   kv_scatter             shaders/kv/kv_scatter.metal:20-42            K / V projections -> cache [nkv, max_seq, hd]
+//   fused_sdpa             shaders/attention/fused_sdpa.metal:52-251    decode, short contexts
+//   prefill_attention_v2   shaders/attention/attention.metal:571-750    more than one token (causal)
+//   fused_sdpa_split + fused_sdpa_reduce   shaders/attention/flash_decode.metal:25-215   decode, long contexts
+// All of them compute softmax(scale * q . K^T) V with fp16 inputs, f32 scores / online softmax / accumulation and one
+// fp16 rounding of the output; they differ in tiling only.  Here one kernel covers them: a warp per query head walks
+// its share of the cached positions in tiles of 32 (lane = position for the scores, lane = four dimensions for the
+// weighted sum), the query heads of a KV head share a CTA (their K / V rows meet in L1), grid z splits the positions
+// of long contexts and a reduction kernel combines the splits exactly as fused_sdpa_reduce does.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace im {
+
+namespace {
+
+constexpr int kHd16 = 128;
+constexpr int kTile16 = 32;
+
+__device__ __forceinline__ int slot_of(const int *slot_map, int seq) { return slot_map ? slot_map[seq] : seq; }
+
+// (QK-norm,) RoPE, cache write.  One CTA of 128 threads per (token, head): query heads are rounded to fp16 in place
+// (the reference's q_proj buffer after fused_qk_norm_rope / rope), key heads are rounded and scattered, value heads are
+// scattered as they are.
+__global__ void __launch_bounds__(kHd16) kv16_prep_kernel(const Kv16Prep a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float sh[kHd16];
+    __shared__ float red[4];
+    const int st = blockIdx.x, slot = blockIdx.y, d = threadIdx.x;
+    const int seq = slot_of(a.slot_map, st / a.T), t = st % a.T;
+    const int pos_abs = a.base_pos + (a.pos_dev ? a.pos_dev[seq] : 0) + t;
+    __half *tok = a.qkv + (size_t)st * a.stride;
+    const __half *tokkv = a.kv ? a.kv + (size_t)st * a.kv_stride : tok;
+    if (slot >= a.nh + a.nkv) {  // value head
+        const int h = slot - a.nh - a.nkv;
+        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
+        a.vc[row * kHd16 + d] = tokkv[a.v_off + h * kHd16 + d];
+        return;
+    }
+    const bool is_q = slot < a.nh;
+    const int h = is_q ? slot : slot - a.nh;
+    const __half *src = (is_q ? tok : tokkv + a.k_off) + h * kHd16;
+    const __half *w = is_q ? a.qw : a.kw;
+    float x = __half2float(src[d]);
+    const int half_rot = a.rotary_dim / 2;
+    const int ri = d < half_rot ? d : d - half_rot;
+    float rc = 1.0f, rs = 0.0f;
+    if (d < a.rotary_dim) {
+        rc = __half2float(a.cosc[(size_t)pos_abs * (kHd16 / 2) + ri]);
+        rs = __half2float(a.sinc[(size_t)pos_abs * (kHd16 / 2) + ri]);
+    }
+    if (a.with_norm) {
+        const float ss = warp_sum(x * x);
+        if ((d & 31) == 0) red[d >> 5] = ss;
+        __syncthreads();
+        const float tot = red[0] + red[1] + red[2] + red[3];
+        x = x * rsqrtf(tot / (float)kHd16 + a.eps) * __half2float(w[d]);
+    }
+    sh[d] = x;
+    __syncthreads();
+    float y = x;
+    if (d < a.rotary_dim) {
+        const float lo = sh[ri], hi = sh[ri + half_rot];
+        y = d < half_rot ? lo * rc - hi * rs : lo * rs + hi * rc;
+    }
+    const __half yh = __float2half_rn(y);
+    if (is_q) {
+        tok[h * kHd16 + d] = yh;
+    } else {
+        const size_t row = ((size_t)seq * a.nkv + h) * a.max_seq + pos_abs % a.max_seq;
+        a.kc[row * kHd16 + d] = yh;
+    }
+}
+
+// kv_scatter alone (the reference's kernel): proj [nseq*T, nkv, hd] -> cache rows at the tokens' positions.
+__global__ void kv16_scatter_kernel(const __half *__restrict__ proj, __half *__restrict__ cache, int T, int nkv, int max_seq, int base_pos,
+                                    const int *__restrict__ pos_dev, const int *__restrict__ slot_map) {
+    const int st = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const int seq = slot_of(slot_map, st / T), t = st % T;
+    const int pos = (base_pos + (pos_dev ? pos_dev[seq] : 0) + t) % max_seq;
+    cache[(((size_t)seq * nkv + h) * max_seq + pos) * kHd16 + d] = proj[((size_t)st * nkv + h) * kHd16 + d];
+}
+
+struct Sdpa16 {
+    const __half *q;   // query of (token st, head h) at q + st * q_stride + h * hd
+    int q_stride;
+    const __half *kc, *vc;  // [slots, nkv, max_seq, hd]
+    __half *out;       // [nseq*T, nh, hd]
+    float *po, *pm, *pl;  // split partials [nseq*T*nh, splits] (x hd for po)
+    int nh, nkv, T, max_seq, base_pos, splits;
+    const int *pos_dev, *slot_map;
+    float scale;
+};
+
+// grid (nseq*T, nkv, splits), block GQ warps: warp w = query head kvh * GQ + w.
+template <int GQ>
+__global__ void __launch_bounds__(GQ * 32) sdpa16_kernel(const Sdpa16 p) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) float qs[GQ][kHd16];
+    const int st = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = kvh * GQ + warp;
+    const int seq = slot_of(p.slot_map, st / p.T), t = st % p.T;
+    // positions this token attends to: everything cached before it and itself (causal), never past the cache
+    const int seq_len = min(p.base_pos + (p.pos_dev ? p.pos_dev[seq] : 0) + t + 1, p.max_seq);
+    int chunk = (seq_len + p.splits - 1) / p.splits;
+    chunk = (chunk + kTile16 - 1) / kTile16 * kTile16;
+    const int r0 = split * chunk, r1 = min(r0 + chunk, seq_len);
+    {
+        const __half *qp = p.q + (size_t)st * p.q_stride + (size_t)head * kHd16;
+        const uint2 raw = *reinterpret_cast<const uint2 *>(qp + 4 * lane);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+        *reinterpret_cast<float4 *>(&qs[warp][4 * lane]) = make_float4(a.x, a.y, b.x, b.y);
+    }
+    __syncwarp();
+    const size_t cache_base = ((size_t)seq * p.nkv + kvh) * p.max_seq * kHd16;
+    float m = -INFINITY, l = 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int tile = r0; tile < r1; tile += kTile16) {
+        const int pos = tile + lane;
+        const bool live = pos < r1;
+        float s = -INFINITY;
+        {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(p.kc + cache_base + (size_t)(live ? pos : tile) * kHd16);
+            float dot = 0.0f;
+#pragma unroll 4
+            for (int i = 0; i < kHd16 / 8; i++) {
+                const uint4 raw = kr[i];
+                const float4 q0 = *reinterpret_cast<const float4 *>(&qs[warp][8 * i]), q1 = *reinterpret_cast<const float4 *>(&qs[warp][8 * i + 4]);
+                const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x)), k1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.z)), k3 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.w));
+                dot = fmaf(q0.x, k0.x, dot); dot = fmaf(q0.y, k0.y, dot); dot = fmaf(q0.z, k1.x, dot); dot = fmaf(q0.w, k1.y, dot);
+                dot = fmaf(q1.x, k2.x, dot); dot = fmaf(q1.y, k2.y, dot); dot = fmaf(q1.z, k3.x, dot); dot = fmaf(q1.w, k3.y, dot);
+            }
+            if (live) s = dot * p.scale;
+        }
+        float tmax = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+        if (tmax > m) {  // the reference rescales only when the maximum moves
+            const float corr = __expf(m - tmax);  // exp(-inf) = 0 on the first tile
+            l *= corr;
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[j] *= corr;
+            m = tmax;
+        }
+        const float wgt = live ? __expf(s - m) : 0.0f;
+        l += warp_sum(wgt);
+        const int n = min(kTile16, r1 - tile);
+        const __half *vr = p.vc + cache_base + (size_t)tile * kHd16 + 4 * lane;
+#pragma unroll 8
+        for (int j = 0; j < kTile16; j++) {
+            const float wj = __shfl_sync(0xffffffffu, wgt, j);
+            if (j < n) {
+                const uint2 raw = *reinterpret_cast<const uint2 *>(vr + (size_t)j * kHd16);
+                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                acc[0] = fmaf(wj, a.x, acc[0]); acc[1] = fmaf(wj, a.y, acc[1]); acc[2] = fmaf(wj, b.x, acc[2]); acc[3] = fmaf(wj, b.y, acc[3]);
+            }
+        }
+    }
+    const size_t hidx = (size_t)st * p.nh + head;
+    if (p.splits == 1) {
+        const float inv = 1.0f / fmaxf(l, 1e-10f);
+        const __half2 lo = __floats2half2_rn(acc[0] * inv, acc[1] * inv), hi = __floats2half2_rn(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2 *>(p.out + hidx * kHd16 + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+    } else {  // unnormalised partial of this split (an empty split leaves max = -inf, sum = 0)
+        const size_t pi = hidx * p.splits + split;
+        *reinterpret_cast<float4 *>(p.po + pi * kHd16 + 4 * lane) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (lane == 0) {
+            p.pm[pi] = m;
+            p.pl[pi] = l;
+        }
+    }
+}
+
+// fused_sdpa_reduce (flash_decode.metal:163-215): global max over the splits, rescale, normalise, fp16.
+__global__ void __launch_bounds__(kHd16) sdpa16_reduce_kernel(const float *__restrict__ po, const float *__restrict__ pm, const float *__restrict__ pl,
+                                                              __half *__restrict__ out, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t hidx = blockIdx.x;
+    const int d = threadIdx.x;
+    float gm = -INFINITY;
+    for (int s = 0; s < splits; s++) gm = fmaxf(gm, pm[hidx * splits + s]);
+    float acc = 0.0f, lsum = 0.0f;
+    for (int s = 0; s < splits; s++) {
+        const float mv = pm[hidx * splits + s];
+        const float corr = mv == -INFINITY ? 0.0f : __expf(mv - gm);
+        lsum += pl[hidx * splits + s] * corr;
+        acc += po[(hidx * splits + s) * kHd16 + d] * corr;
+    }
+    out[hidx * kHd16 + d] = __float2half_rn(acc / fmaxf(lsum, 1e-10f));
+}
+
+}  // namespace
+
+size_t kv16_scratch_bytes(int tokens, int nh, int splits) { return (size_t)tokens * nh * splits * (kHd16 + 2) * sizeof(float); }
+
+// Splits for a launch: one when the (token, KV head) pairs already fill the GPU or the context is short (the reference's
+// single-pass kernels), otherwise enough to give every SM two CTAs, at least 256 positions each.
+int kv16_auto_splits(const Device *dev, int tokens, int nkv, int max_ctx) {
+    const int ctas = tokens * nkv;
+    if (ctas >= dev->sm_count || max_ctx < 256) return 1;
+    int s = (2 * dev->sm_count + ctas - 1) / ctas;
+    s = std::min(s, (max_ctx + 255) / 256);
+    return std::max(1, std::min(s, 64));
+}
+
+int kv16_prep_launch(const Kv16Prep &a, cudaStream_t st) {
+    if (a.nseq * a.T == 0) return IM_OK;
+    IM_CUDA_CHECK(launch_k(kv16_prep_kernel, dim3(a.nseq * a.T, a.nh + 2 * a.nkv), dim3(kHd16), 0, st, a));
+    return IM_OK;
+}
+
+int kv16_attention_launch(const Device *dev, float *scratch, size_t scratch_bytes, const __half *q, int q_stride, const __half *kc, const __half *vc,
+                          float scale, __half *out, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, int splits,
+                          int ctx_hint, cudaStream_t st, const int *slot_map) {
+    const int tokens = nseq * T;
+    if (tokens == 0) return IM_OK;
+    if (nkv <= 0 || nh % nkv != 0) return fail(IM_ERR_INVALID, "nh must be a multiple of nkv");
+    const int gq = nh / nkv;
+    if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return fail(IM_ERR_INVALID, "fp16-KV attention is built for 1, 2, 4 or 8 query heads per KV head (got %d)", gq);
+    if (splits <= 0) splits = kv16_auto_splits(dev, tokens, nkv, ctx_hint > 0 ? ctx_hint : max_seq);
+    while (splits > 1 && kv16_scratch_bytes(tokens, nh, splits) > scratch_bytes) splits--;
+    Sdpa16 p{};
+    p.q = q; p.q_stride = q_stride; p.kc = kc; p.vc = vc; p.out = out;
+    p.po = scratch;
+    p.pm = scratch + (size_t)tokens * nh * splits * kHd16;
+    p.pl = p.pm + (size_t)tokens * nh * splits;
+    p.nh = nh; p.nkv = nkv; p.T = T; p.max_seq = max_seq; p.base_pos = base_pos; p.splits = splits;
+    p.pos_dev = pos_dev; p.slot_map = slot_map; p.scale = scale;
+    const dim3 grid(tokens, nkv, splits);
+    switch (gq) {
+    case 1: IM_CUDA_CHECK(launch_k(sdpa16_kernel<1>, grid, dim3(32), 0, st, p)); break;
+    case 2: IM_CUDA_CHECK(launch_k(sdpa16_kernel<2>, grid, dim3(64), 0, st, p)); break;
+    case 4: IM_CUDA_CHECK(launch_k(sdpa16_kernel<4>, grid, dim3(128), 0, st, p)); break;
+    default: IM_CUDA_CHECK(launch_k(sdpa16_kernel<8>, grid, dim3(256), 0, st, p)); break;
+    }
+    if (splits > 1)
+        IM_CUDA_CHECK(launch_k(sdpa16_reduce_kernel, dim3((unsigned)((size_t)tokens * nh)), dim3(kHd16), 0, st, (const float *)p.po, (const float *)p.pm,
+                               (const float *)p.pl, out, splits));
+    return IM_OK;
+}
+
+}  // namespace im
+
+// ---- C ABI ------------------------------------------------------------------------------------------------------
+IM_EXPORT int im_cuda_kv_scatter_f16(const void *proj_dev, void *cache_dev, int nseq, int T, int nkv, int head_dim, int max_seq, int base_pos,
+                                     const int *pos_dev, const int *slot_map_dev, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(proj_dev && cache_dev, "bad argument");
+    IM_REQUIRE(head_dim == im::kHd16, "the fp16-KV kernels are built for head_dim 128 (got %d)", head_dim);
+    IM_REQUIRE(nseq >= 0 && T >= 0 && nkv > 0 && max_seq > 0 && base_pos >= 0, "bad shape");
+    if (nseq * T == 0) return IM_OK;
+    im::kv16_scatter_kernel<<<dim3(nseq * T, nkv), im::kHd16, 0, im::as_stream(stream)>>>(static_cast<const __half *>(proj_dev), static_cast<__half *>(cache_dev), T,
+                                                                                       nkv, max_seq, base_pos, pos_dev, slot_map_dev);
+    IM_CUDA_CHECK(cudaGetLastError());
+    return IM_OK;
+    IM_GUARD_END
+}
+
+IM_EXPORT size_t im_cuda_sdpa_f16_scratch_bytes(int nseq, int T, int nh, int splits) { return im::kv16_scratch_bytes(nseq * T, nh, splits < 1 ? 1 : splits); }
+
+IM_EXPORT int im_cuda_sdpa_f16(im_device *dev, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev, void *out_dev, int nseq, int nh,
+                               int nkv, int head_dim, int max_seq, int base_pos, const int *pos_dev, int T, float scale, int num_splits,
+                               void *scratch_dev, size_t scratch_bytes, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(dev && q_dev && k_cache_dev && v_cache_dev && out_dev, "bad argument");
+    IM_REQUIRE(head_dim == im::kHd16, "the fp16-KV kernels are built for head_dim 128 (got %d)", head_dim);
+    IM_REQUIRE(nseq >= 0 && T >= 0 && max_seq > 0 && base_pos >= 0, "bad shape");
+    IM_REQUIRE(num_splits <= 1 || scratch_dev, "split attention needs a scratch buffer (im_cuda_sdpa_f16_scratch_bytes)");
+    if (!scratch_dev) num_splits = 1;
+    return im::kv16_attention_launch(dev, static_cast<float *>(scratch_dev), scratch_bytes, static_cast<const __half *>(q_dev), nh * head_dim,
+                                     static_cast<const __half *>(k_cache_dev), static_cast<const __half *>(v_cache_dev), scale,
+                                     static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, num_splits, base_pos + T,
+                                     im::as_stream(stream), nullptr);
+    IM_GUARD_END
+}

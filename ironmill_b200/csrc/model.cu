@@ -16,6 +16,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <new>
 #include <string>
@@ -237,6 +238,8 @@ struct Model {
     size_t bytes = 0;
     int launches_per_step = 0;
     float *scratch_ref = nullptr;
+    float *kv16_scratch = nullptr;  // split partials of the fp16-KV attention (tq_bits == 16)
+    size_t kv16_scratch_bytes = 0;
     // whole-token decode kernel (batch 1, single GPU): tables built by mega_prepare()
     bool mega_ready = false;
     MegaParams mega{};
@@ -526,6 +529,28 @@ struct Prof {
 // One forward pass over nseq sequences x T tokens each (decode: T = 1; prefill: nseq = 1).
 // Logits are produced for the last token of every sequence.
 // slots: device array naming the cache slot of each of the nseq sequences (nullptr: slots 0 .. nseq - 1).
+// (QK-norm +) RoPE, cache write and attention of one layer.  TurboQuant caches: the fused preparation (cache write
+// and query rotation), split attention, reduction.  fp16 cache (TurboQuant off): norm / RoPE in place, the K / V rows
+// scattered as fp16, one attention kernel over the fp16 rows (kv_f16.cu).  q_buf: the buffer a.qkv names, writable.
+// part 0: the preparation (cache write), part 1: the attention.
+static int attention_block(Model *m, int part, const TqPrep &a, __half *q_buf, Layer &L, int nseq, int T, float attn_scale, int attn_splits,
+                           const int *slots, cudaStream_t st) {
+    const im_model_config &c = m->cfg;
+    if (c.tq_bits == 16) {
+        Kv16Prep k{};
+        k.qkv = q_buf; k.stride = a.stride; k.k_off = a.k_off; k.v_off = a.v_off; k.kv = a.kv; k.kv_stride = a.kv_stride;
+        k.qw = a.qw; k.kw = a.kw; k.cosc = a.cosc; k.sinc = a.sinc; k.nh = a.nh; k.nkv = a.nkv; k.rotary_dim = a.rotary_dim;
+        k.with_norm = a.with_norm; k.T = T; k.nseq = nseq; k.max_seq = a.max_seq; k.base_pos = 0; k.eps = a.eps; k.pos_dev = a.pos_dev;
+        k.slot_map = slots; k.kc = reinterpret_cast<__half *>(L.kc); k.vc = reinterpret_cast<__half *>(L.vc);
+        if (part == 0) return kv16_prep_launch(k, st);
+        return kv16_attention_launch(m->dev, m->kv16_scratch, m->kv16_scratch_bytes, q_buf, a.stride, k.kc, k.vc, attn_scale, m->attn_out, nseq, a.nh,
+                                     a.nkv, c.max_seq_len, 0, m->pos_dev, T, 0, c.max_seq_len, st, slots);
+    }
+    if (part == 0) return tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st);
+    return tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale, m->attn_out,
+                               nseq, a.nh, a.nkv, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot, slots);
+}
+
 static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, int *launches, Prof *prof = nullptr, bool all_logits = false,
                    const int *slots = nullptr) {
     const im_model_config &c = m->cfg;
@@ -565,10 +590,9 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev; a.slot_map = slots;
         a.qrot = m->qrot; a.q_out = nullptr;
         a.kc = L.kc; a.vc = L.vc; a.ks = L.ks; a.vs = L.vs; a.krn = L.krn;
-        IM_TRY(tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st));
+        IM_TRY(attention_block(m, 0, a, m->qkv, L, nseq, T, attn_scale, attn_splits, slots, st));
         IM_MARK(kCatKvWrite);
-        IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
-                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot, slots));
+        IM_TRY(attention_block(m, 1, a, m->qkv, L, nseq, T, attn_scale, attn_splits, slots, st));
         nl += 3;
         IM_MARK(kCatAttn);
         IM_TRY(gemm_affine_tc(L.o, m->attn_out, m->ffn_down, MT, m->xs_scratch, st));
@@ -626,10 +650,9 @@ static int forward(Model *m, int nseq, int T, int attn_splits, cudaStream_t st, 
         a.T = T; a.nseq = nseq; a.max_seq = c.max_seq_len; a.base_pos = 0; a.eps = eps; a.pos_dev = m->pos_dev; a.slot_map = slots;
         a.qrot = m->qrot; a.q_out = nullptr;
         a.kc = L.kc; a.vc = L.vc; a.ks = L.ks; a.vs = L.vs; a.krn = L.krn;
-        IM_TRY(tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st));
+        IM_TRY(attention_block(m, 0, a, m->q_d, L, nseq, T, attn_scale, attn_splits, slots, st));
         IM_MARK(kCatKvWrite);
-        IM_TRY(tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale,
-                                   m->attn_out, nseq, m->nh_l, m->nkv_l, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot, slots));
+        IM_TRY(attention_block(m, 1, a, m->q_d, L, nseq, T, attn_scale, attn_splits, slots, st));
         nl += 3;
         IM_MARK(kCatAttn);
         IM_TRY(im_cuda_matvec_affine(static_cast<im_affine_weight *>(L.o), m->attn_out, m->ffn_down, MT, st));
@@ -720,6 +743,7 @@ static int mega_prepare(Model *m) {
     const bool tp = m->world > 1;
     // one GPU: opt-in only (measured slower there than the barrier: 64.0 against 60.0 us per layer at L8 shapes)
     const bool tagged = tp || c.decode_schedule == 2;
+    if (c.tq_bits == 16) return IM_OK;           // fp16 cache: the per-kernel schedule
     if (tagged && c.tq_bits == 4) return IM_OK;  // 4-bit caches: the barrier form of the kernel only (tensor parallel: per-kernel schedule)
     if (tp && (!m->xar.ok || m->world > 8 || c.hidden_size % 128 != 0)) return IM_OK;  // needs the peer mapping of tp_init
     if (c.head_dim != 128 || m->nkv_l <= 0 || m->nh_l % m->nkv_l != 0) return IM_OK;
@@ -1119,7 +1143,8 @@ IM_EXPORT int im_cuda_model_create(im_device *dev, const im_model_config *cfg, i
     if (c.tp_world == 0) c.tp_world = 1;
     // MetalConfig::validate (crates/ironmill-inference/src/metal/config.rs:364-384)
     IM_REQUIRE(c.max_seq_len > 0, "max_seq_len must be > 0");
-    IM_REQUIRE(c.tq_bits == 4 || c.tq_bits == 8, "n_bits must be 4 or 8, got %d", c.tq_bits);
+    IM_REQUIRE(c.tq_bits == 4 || c.tq_bits == 8 || c.tq_bits == 16, "n_bits must be 4 or 8 (TurboQuant) or 16 (fp16 KV cache, TurboQuant off), got %d",
+               c.tq_bits);
     IM_REQUIRE(c.num_layers > 0 && c.hidden_size > 0 && c.intermediate_size > 0 && c.num_heads > 0 && c.num_kv_heads > 0 &&
                    c.head_dim > 0 && c.vocab_size > 0, "model dimensions must be positive");
     IM_REQUIRE(c.head_dim == 128, "head_dim %d is not built (128 only)", c.head_dim);
@@ -1347,8 +1372,9 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
         m->qjl_host.resize((size_t)hd * hd);
         IM_TRY(im_cuda_tq_generate(hd, c.rotation_seed, m->signs_host.data(), m->qjl_host.data()));
     }
-    IM_TRY(im_cuda_tq_create(static_cast<im_device *>(m->dev), hd, c.tq_bits, m->signs_host.data(), m->qjl_host.data(), nullptr, nullptr, nullptr,
-                             nullptr, &m->tq));
+    // (an fp16 cache keeps the handle for its scratch bookkeeping only: none of its tables is read)
+    IM_TRY(im_cuda_tq_create(static_cast<im_device *>(m->dev), hd, c.tq_bits == 16 ? 8 : c.tq_bits, m->signs_host.data(), m->qjl_host.data(), nullptr,
+                             nullptr, nullptr, nullptr, &m->tq));
     // RoPE tables
     IM_TRY(m->alloc((void **)&m->cosc, (size_t)c.max_seq_len * (hd / 2) * 2));
     IM_TRY(m->alloc((void **)&m->sinc, (size_t)c.max_seq_len * (hd / 2) * 2));
@@ -1412,6 +1438,13 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     for (int t = 1; t <= kPrefillChunk; t++) {
         const size_t s = im_cuda_tq_scratch_bytes(1, t, m->nh_l, hd, tq_auto_splits(m->dev, 1, t, m->nkv_l, c.max_seq_len));
         if (s > need) need = s;
+    }
+    if (c.tq_bits == 16) {
+        size_t n16 = 0;
+        for (int b = 1; b <= c.max_batch; b++) n16 = std::max(n16, kv16_scratch_bytes(b, m->nh_l, kv16_auto_splits(m->dev, b, m->nkv_l, c.max_seq_len)));
+        for (int t = 1; t <= kPrefillChunk; t++) n16 = std::max(n16, kv16_scratch_bytes(t, m->nh_l, kv16_auto_splits(m->dev, t, m->nkv_l, c.max_seq_len)));
+        IM_TRY(m->alloc((void **)&m->kv16_scratch, n16));
+        m->kv16_scratch_bytes = n16;
     }
     IM_TRY(im_cuda_tq_reserve_scratch(m->tq, need));
     m->scratch_ref = reinterpret_cast<Tq *>(m->tq)->scratch;
@@ -1550,7 +1583,7 @@ IM_EXPORT size_t im_cuda_model_step_bytes(const im_model *m, int ctx, int batch)
             b += (size_t)w->N * w->K * w->bits / 8 + (size_t)w->N * w->G * 4 + (w->awq ? (size_t)w->K * 2 : 0);
         }
         b += 2 * (size_t)c.hidden_size * 2;
-        b += (size_t)batch * m->nkv_l * ctx * (2 * c.head_dim * c.tq_bits / 8 + 12);
+        b += (size_t)batch * m->nkv_l * ctx * (2 * c.head_dim * c.tq_bits / 8 + (c.tq_bits == 16 ? 0 : 12));
     }
     b += (size_t)m->vocab_l * c.hidden_size * 2 + (size_t)c.hidden_size * 2;
     return b;

@@ -61,13 +61,16 @@ class CudaConfig:
         self.enable_turboquant, self.n_bits = True, bits
         return self
 
+    def without_turboquant(self) -> "CudaConfig":
+        """fp16 KV cache (MetalConfig.enable_turboquant = false: kv_scatter + fused_sdpa / FlashDecoding)."""
+        self.enable_turboquant = False
+        return self
+
     def validate(self) -> None:
         if self.max_seq_len == 0:
             raise InferenceError("Runtime", "max_seq_len must be > 0")
         if self.n_bits not in (4, 8):
             raise InferenceError("Runtime", f"n_bits must be 4 or 8, got {self.n_bits}")
-        if not self.enable_turboquant:
-            raise InferenceError("Runtime", "the CUDA backend keeps its KV cache in TurboQuant form only")
 
 
 class _CModelConfig(C.Structure):
@@ -129,7 +132,8 @@ class CudaInference:
                            mc.num_key_value_heads, mc.head_dim, mc.vocab_size, self.config.max_seq_len, self.config.max_batch,
                            mc.rms_norm_eps, mc.attn_scale, float(mc.extra.get("embed_scale", 0.0) or 0.0), mc.rope_theta,
                            int(mc.extra.get("rotary_dim", 0) or 0), int(mc.has_qk_norm), int(mc.tie_word_embeddings),
-                           self.config.n_bits, self.config.rotation_seed, self.config.tp_world, self.config.tp_rank,
+                           self.config.n_bits if self.config.enable_turboquant else 16, self.config.rotation_seed, self.config.tp_world,
+                           self.config.tp_rank,
                            int(self.config.prefill_chunk_size or 0),
                            {"auto": 0, "per_kernel": 1, "tagged": 2}[self.config.decode_schedule],
                            {"auto": 0, "nccl": 1}[self.config.tp_collective], int(self.config.wait_limit_ms))

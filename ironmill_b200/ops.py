@@ -371,3 +371,23 @@ def tq_attention_static(tq: "TurboQuant", q, k_cache, v_cache, k_scale, v_scale,
                                             C.c_float(attn_scale), vp(out), C.c_int(nseq), C.c_int(nh), C.c_int(nkv), C.c_int(max_seq),
                                             C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_int(num_splits), _stream()))
     return out
+
+
+def kv_scatter_f16(proj, cache, nseq, T, nkv, max_seq, base_pos, pos_dev=None):
+    """kv_scatter (shaders/kv/kv_scatter.metal:20-42): proj fp16 [nseq*T, nkv, 128] -> cache fp16 [nseq, nkv, max_seq, 128]."""
+    check(lib().im_cuda_kv_scatter_f16(vp(proj), vp(cache), C.c_int(nseq), C.c_int(T), C.c_int(nkv), C.c_int(128), C.c_int(max_seq),
+                                       C.c_int(base_pos), vp(pos_dev), None, _stream()))
+
+
+def sdpa_f16(dev: "Device", q, k_cache, v_cache, scale, nh, nkv, max_seq, base_pos, nseq=1, pos_dev=None, num_splits=0):
+    """fp16-KV attention (fused_sdpa / prefill_attention_v2 / fused_sdpa_split + reduce): q fp16 [nseq*T, nh, 128]."""
+    T = _h16(q).numel() // (nseq * nh * 128)
+    out = torch.empty_like(q)
+    splits = num_splits if num_splits > 0 else 64
+    nbytes = int(lib().im_cuda_sdpa_f16_scratch_bytes(C.c_int(nseq), C.c_int(T), C.c_int(nh), C.c_int(splits)))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    check(lib().im_cuda_sdpa_f16(dev.handle, vp(q), vp(k_cache), vp(v_cache), vp(out), C.c_int(nseq), C.c_int(nh), C.c_int(nkv), C.c_int(128),
+                                 C.c_int(max_seq), C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_float(scale), C.c_int(num_splits),
+                                 vp(scratch), C.c_size_t(nbytes), _stream()))
+    return out
+

@@ -809,3 +809,87 @@ EXPORT uint32_t orc_argmax(const float *logits, size_t n) {
         if (!(logits[i] < logits[best])) best = i;
     return (uint32_t)best;
 }
+
+/* Attention over an fp16 (unquantized) KV cache: the reference's path with TurboQuant off.
+ *   num_splits == 0: crates/ironmill-inference/src/metal/shaders/attention/fused_sdpa.metal:52-251 (fused_sdpa; the
+ *                    prefill kernel attention.metal:571-750, prefill_attention_v2, is the same arithmetic): tiles of
+ *                    SDPA_BC = 32 positions, f32 dot products of fp16 q and K scaled by `scale`, online softmax that
+ *                    rescales only when the running maximum moves, O += w * V for w > 0, O / max(sum, 1e-10) -> fp16.
+ *   num_splits  > 0: .../flash_decode.metal:25-151 (fused_sdpa_split: chunk = ceil(seq_len / num_splits), tiles of
+ *                    SPLIT_BC = 8, max_hint = -inf as ops/attention_ops.rs:396-399 passes it, unnormalised partials)
+ *                    and :163-215 (fused_sdpa_reduce: global max, rescale, normalise).
+ * q [T, nh, hd] fp16; caches [nkv, max_seq, hd] fp16; out [T, nh, hd] fp16; token t attends to positions
+ * 0 .. base_pos + t (causal, the reference's causal_limit = seq_len - token_count + q_pos + 1). */
+EXPORT void orc_sdpa_f16(const uint16_t *q, const uint16_t *kc, const uint16_t *vc, float scale, uint16_t *out,
+                         size_t nh, size_t nkv, size_t hd, size_t max_seq, size_t base_pos, size_t T, size_t num_splits) {
+    const size_t gq = nh / nkv;
+    const size_t ns = num_splits ? num_splits : 1;
+    const size_t bc = num_splits ? 8 : 32;
+#pragma omp parallel
+    {
+    float *qf = (float *)malloc(hd * sizeof(float)), *o = (float *)malloc(hd * sizeof(float));
+    float *po = (float *)malloc(ns * hd * sizeof(float)), *pm = (float *)malloc(ns * sizeof(float)), *ps = (float *)malloc(ns * sizeof(float));
+    float s_tile[32];
+#pragma omp for collapse(2) schedule(dynamic)
+    for (size_t t = 0; t < T; t++)
+        for (size_t h = 0; h < nh; h++) {
+            const size_t kvh = h / gq, seq_len = base_pos + t + 1;
+            const uint16_t *K = kc + kvh * max_seq * hd, *V = vc + kvh * max_seq * hd;
+            for (size_t d = 0; d < hd; d++) qf[d] = h2f(q[(t * nh + h) * hd + d]);
+            const size_t chunk = (seq_len + ns - 1) / ns;
+            for (size_t s = 0; s < ns; s++) {
+                const size_t k0 = s * chunk, k1 = k0 + chunk < seq_len ? k0 + chunk : seq_len;
+                float m = -INFINITY, l = 0.0f;
+                for (size_t d = 0; d < hd; d++) o[d] = 0.0f;
+                for (size_t p0 = k0; p0 < k1; p0 += bc) {
+                    const size_t n = p0 + bc < k1 ? bc : k1 - p0;
+                    float tile_max = -INFINITY;
+                    for (size_t p = 0; p < n; p++) {
+                        float dot = 0.0f;
+                        for (size_t d = 0; d < hd; d++) dot += qf[d] * h2f(K[(p0 + p) * hd + d]);
+                        s_tile[p] = dot * scale;
+                        if (s_tile[p] > tile_max) tile_max = s_tile[p];
+                    }
+                    const float new_max = m > tile_max ? m : tile_max;
+                    if (new_max > m) {
+                        const float corr = expf(m - new_max);
+                        l *= corr;
+                        for (size_t d = 0; d < hd; d++) o[d] *= corr;
+                        m = new_max;
+                    }
+                    float tile_sum = 0.0f;
+                    for (size_t p = 0; p < n; p++) {
+                        s_tile[p] = expf(s_tile[p] - m);
+                        tile_sum += s_tile[p];
+                    }
+                    l += tile_sum;
+                    for (size_t p = 0; p < n; p++)
+                        if (s_tile[p] > 0.0f)
+                            for (size_t d = 0; d < hd; d++) o[d] += s_tile[p] * h2f(V[(p0 + p) * hd + d]);
+                }
+                if (!num_splits) {
+                    const float denom = fmaxf(l, 1e-10f);
+                    for (size_t d = 0; d < hd; d++) out[(t * nh + h) * hd + d] = f2h(o[d] / denom);
+                } else {
+                    pm[s] = k0 < k1 ? m : -INFINITY;
+                    ps[s] = l;
+                    for (size_t d = 0; d < hd; d++) po[s * hd + d] = o[d];
+                }
+            }
+            if (num_splits) {
+                float gm = -INFINITY;
+                for (size_t s = 0; s < ns; s++) if (pm[s] > gm) gm = pm[s];
+                float csum = 0.0f;
+                for (size_t d = 0; d < hd; d++) o[d] = 0.0f;
+                for (size_t s = 0; s < ns; s++) {
+                    const float corr = expf(pm[s] - gm);
+                    csum += ps[s] * corr;
+                    for (size_t d = 0; d < hd; d++) o[d] += po[s * hd + d] * corr;
+                }
+                const float denom = fmaxf(csum, 1e-10f);
+                for (size_t d = 0; d < hd; d++) out[(t * nh + h) * hd + d] = f2h(o[d] / denom);
+            }
+        }
+    free(qf); free(o); free(po); free(pm); free(ps);
+    }
+}

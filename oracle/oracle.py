@@ -340,6 +340,17 @@ def tq_attention(q, k_cache, v_cache, tq: TqConstants, k_scale, v_scale, k_rnorm
     return out
 
 
+def sdpa_f16(q, k_cache, v_cache, scale, nh, nkv, hd, max_seq, base_pos, num_splits=0):
+    """fp16-KV attention (fused_sdpa / prefill_attention_v2; num_splits > 0: fused_sdpa_split + fused_sdpa_reduce).
+    q [T, nh, hd], caches [nkv, max_seq, hd] fp16 -> [T, nh, hd] fp16."""
+    q = _h(q)
+    T = q.size // (nh * hd)
+    out = np.zeros((T, nh, hd), dtype=np.float16)
+    lib().orc_sdpa_f16(_p(q), _p(_h(k_cache)), _p(_h(v_cache)), C.c_float(scale), _p(out), C.c_size_t(nh), C.c_size_t(nkv),
+                       C.c_size_t(hd), C.c_size_t(max_seq), C.c_size_t(base_pos), C.c_size_t(T), C.c_size_t(num_splits))
+    return out
+
+
 def argmax(logits):
     logits = _f(np.asarray(logits, dtype=np.float32))
     return int(lib().orc_argmax(_p(logits), C.c_size_t(logits.size)))

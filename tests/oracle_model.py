@@ -111,10 +111,11 @@ class OracleModel:
       sum_order      dot products summed as two halves of K (another f32 summation order)
       prefill_matvec prefill projections in the matvec form (no f16 rounding of x / awq and of the weights)"""
 
-    def __init__(self, cfg, tensors, tqc, max_seq, flip_rate=0.0, deviations=()):
+    def __init__(self, cfg, tensors, tqc, max_seq, flip_rate=0.0, deviations=(), kv_f16=False):
         """flip_rate > 0 flips the lowest fp16 bit of that fraction of the activations entering every layer:
         a stand-in for "another correct implementation" used to measure how far last-bit differences grow."""
         self.cfg, self.tq, self.max_seq = cfg, tqc, max_seq
+        self.kv_f16 = kv_f16  # TurboQuant off: fp16 K / V rows in the cache (metal/attention.rs:491-612)
         self.flip_rate, self._flip_rng = flip_rate, np.random.default_rng(12345)
         self.dev = frozenset(deviations)
         unknown = self.dev - {"kv_unrounded", "ffn_unrounded", "no_split", "act_q16", "act_q24", "sum_order", "prefill_matvec"}
@@ -137,9 +138,12 @@ class OracleModel:
             d["gate"], d["ffn_awq"] = _deq(tensors[f"{p}.mlp.gate_proj.weight"])
             d["up"], _ = _deq(tensors[f"{p}.mlp.up_proj.weight"])
             d["down"], d["down_awq"] = _deq(tensors[f"{p}.mlp.down_proj.weight"])
-            d["kc"] = np.zeros((nkv, max_seq, hd * tqc.n_bits // 8), np.uint8)   # n_bits = 4: two elements per byte
-            d["vc"] = np.zeros((nkv, max_seq, hd * tqc.n_bits // 8), np.uint8)
-            d["ks"], d["vs"], d["kr"] = (np.zeros((nkv, max_seq), np.float32) for _ in range(3))
+            if kv_f16:
+                d["k16"], d["v16"] = np.zeros((nkv, max_seq, hd), np.float16), np.zeros((nkv, max_seq, hd), np.float16)
+            else:
+                d["kc"] = np.zeros((nkv, max_seq, hd * tqc.n_bits // 8), np.uint8)   # n_bits = 4: two elements per byte
+                d["vc"] = np.zeros((nkv, max_seq, hd * tqc.n_bits // 8), np.uint8)
+                d["ks"], d["vs"], d["kr"] = (np.zeros((nkv, max_seq), np.float32) for _ in range(3))
             self.L.append(d)
         self._w16 = {}
         self.cos, self.sin = orc.rope_table(hd, max_seq, cfg.rope_theta, cfg.extra.get("rotary_dim"))
@@ -214,14 +218,23 @@ class OracleModel:
             else:
                 q = orc.rope(q, self.cos, self.sin, nh, hd, self.pos)
                 k = orc.rope(k, self.cos, self.sin, nkv, hd, self.pos)
-            orc.tq_encode(k, self.tq, True, d["kc"], d["ks"], d["kr"], nkv, self.max_seq, self.pos)
-            orc.tq_encode(np.ascontiguousarray(v), self.tq, False, d["vc"], d["vs"], None, nkv, self.max_seq, self.pos)
             seq = self.pos + T
             splits = 0
             if decode and seq >= 256 and "no_split" not in self.dev:
                 splits = max(2, min(-(-seq // 256), 256))
-            attn = orc.tq_attention(q, d["kc"], d["vc"], self.tq, d["ks"], d["vs"], d["kr"], c.attn_scale, nh, nkv,
-                                    self.max_seq, self.pos, num_splits=splits).reshape(T, nh * hd)
+            if self.kv_f16:  # kv_scatter (shaders/kv/kv_scatter.metal:20-42), then fused_sdpa / prefill_attention_v2 / the split pair
+                kk = np.asarray(k, np.float16).reshape(T, nkv, hd)
+                vv = np.asarray(v, np.float16).reshape(T, nkv, hd)
+                for t in range(T):
+                    d["k16"][:, self.pos + t] = kk[t]
+                    d["v16"][:, self.pos + t] = vv[t]
+                attn = orc.sdpa_f16(q, d["k16"], d["v16"], c.attn_scale, nh, nkv, hd, self.max_seq, self.pos,
+                                    num_splits=splits).reshape(T, nh * hd)
+            else:
+                orc.tq_encode(k, self.tq, True, d["kc"], d["ks"], d["kr"], nkv, self.max_seq, self.pos)
+                orc.tq_encode(np.ascontiguousarray(v), self.tq, False, d["vc"], d["vs"], None, nkv, self.max_seq, self.pos)
+                attn = orc.tq_attention(q, d["kc"], d["vc"], self.tq, d["ks"], d["vs"], d["kr"], c.attn_scale, nh, nkv,
+                                        self.max_seq, self.pos, num_splits=splits).reshape(T, nh * hd)
             o = self._proj(li, "o", d["o"], d["o_awq"], attn, decode)
             norm_out, residual = orc.fused_residual_rms_norm(hidden, o, d["post_ln"], float(eps))
             if fused:
