@@ -549,24 +549,32 @@ def run_attention(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = ops.Device(local)
-    nh, nkv, hd, ctx, B = 32, 8, 128, args.prompt, args.batch
+    nh, nkv, hd, ctx, B, bits = 32, 8, 128, args.prompt, args.batch, args.kv_bits
     signs, qjl = ops.tq_generate(hd, 42)
-    tq = ops.TurboQuant(dev, hd, 8, signs, qjl)
-    kv_bytes = B * nkv * ctx * (2 * hd + 12)
+    tq = ops.TurboQuant(dev, hd, bits, signs, qjl) if bits != 16 else None
+    kv_bytes = B * nkv * ctx * (2 * hd * bits // 8 + (12 if bits != 16 else 0))
     ncopy = max(2, int(400e6 // kv_bytes) + 1)
     g = torch.Generator(device="cuda").manual_seed(3)
     caches = []
     for _ in range(ncopy):
-        kc = torch.randint(0, 256, (B, nkv, ctx, hd), generator=g, device="cuda", dtype=torch.uint8)
-        vc = torch.randint(0, 256, (B, nkv, ctx, hd), generator=g, device="cuda", dtype=torch.uint8)
+        if bits == 16:   # fp16 rows (TurboQuant off)
+            caches.append(((torch.randn((B, nkv, ctx, hd), generator=g, device="cuda") * 0.5).half(),
+                           torch.randn((B, nkv, ctx, hd), generator=g, device="cuda").half()))
+            continue
+        kc = torch.randint(0, 256, (B, nkv, ctx, hd * bits // 8), generator=g, device="cuda", dtype=torch.uint8)
+        vc = torch.randint(0, 256, (B, nkv, ctx, hd * bits // 8), generator=g, device="cuda", dtype=torch.uint8)
         ks = torch.rand((B, nkv, ctx), generator=g, device="cuda") + 0.5
         vs = torch.rand((B, nkv, ctx), generator=g, device="cuda") + 0.5
         kr = torch.rand((B, nkv, ctx), generator=g, device="cuda") * 0.1
         caches.append((kc, vc, ks, vs, kr))
     q = torch.randn((B, nh, hd), generator=g, device="cuda").half()
     scale = 1.0 / np.sqrt(hd)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
 
     def step(i):
+        if bits == 16:
+            k16, v16 = caches[i % ncopy]
+            return ops.sdpa_f16(dev, q, k16, v16, scale, nh, nkv, ctx, 0, nseq=B, pos_dev=pos)
         kc, vc, ks, vs, kr = caches[i % ncopy]
         return tq.attention(q, kc, vc, ks, vs, kr, scale, nh, nkv, ctx, ctx - 1, nseq=B)
 
@@ -601,12 +609,15 @@ def run_attention(args, rank, world):
         step(i).cpu()
         q.copy_(qh, non_blocking=False)
     e2e_s = time.perf_counter() - w0
-    out = {"metric": METRIC_ATTN, "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+    metric = METRIC_ATTN if bits == 8 else METRIC_ATTN.replace("TurboQuant INT8-KV", "TurboQuant INT4-KV" if bits == 4 else "fp16-KV")
+    out = {"metric": metric, "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
            "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "u8 codebook indices, f32 accumulation", "data": "synthetic",
-           "config": {"workload": "turboquant_int8_kv_decode_attention", "context": ctx, "batch": B, "q_heads": nh, "kv_heads": nkv,
+           "dtype": "u8 codebook indices, f32 accumulation" if bits != 16 else "f16 rows, f32 accumulation", "data": "synthetic",
+           "config": {"workload": {8: "turboquant_int8_kv_decode_attention", 4: "turboquant_int4_kv_decode_attention",
+                                   16: "fp16_kv_decode_attention"}[bits], "context": ctx, "batch": B, "q_heads": nh, "kv_heads": nkv,
                       "l2_policy": f"rotation over {ncopy} cache copies ({ncopy * kv_bytes >> 20} MiB) larger than L2"},
-           "roofline": {"bound": "hbm", "kernel": "tq_attention_kernel<4> + tq_reduce_kernel", "achieved": round(gbs, 1), "peak": peak,
+           "roofline": {"bound": "hbm", "kernel": "tq_attention_tc_kernel<4> + tq_reduce_kernel" if bits != 16 else "sdpa16_kernel<4> + sdpa16_reduce_kernel",
+                        "achieved": round(gbs, 1), "peak": peak,
                         "unit": "GB/s", "frac": round(gbs / peak, 4), "peak_source": peak_src, "bytes_per_launch": kv_bytes,
                         "us_per_launch": round(ms / steps * 1e3, 2), "traffic": None},
            "e2e": {"value": round(kv_bytes * 8 / e2e_s / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": B * nh * hd * 2,
@@ -772,6 +783,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="decoder layers of the synthetic model (0 = the named model's; fewer only for profiler captures)")
     ap.add_argument("--sweep", type=int, default=1, help="matvec workload: 1 = also time every shape at batch 1/4/16/64, INT8 and the tensor-parallel shards")
+    ap.add_argument("--kv-bits", type=int, default=8, choices=[4, 8, 16], help="attention workload: TurboQuant bits, or 16 = fp16 KV cache")
     ap.add_argument("--model", default="llama3_8b", choices=sorted(MODELS), help="decode workload shape (the default is the headline configuration)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))

@@ -104,8 +104,10 @@ __device__ __forceinline__ uint4 dequant8_slow(uint32_t w, float z, float s) {  
 
 // ring depth by token tile: 96 KB per stage at TN = 256 leaves room for two, 64 KB at TN = 128 for three (deeper rings
 // measured no faster: the weight warps, not the pipeline depth, set the pace)
+// (few tokens: the stages are small, and a deeper ring with more activation copies in flight hides the L2 latency that
+// otherwise paces a CTA at one stage per trip)
 template <int TN>
-constexpr int gemm_stages() { return TN >= 256 ? 2 : 3; }
+constexpr int gemm_stages() { return TN >= 256 ? 2 : TN >= 128 ? 3 : TN >= 64 ? 4 : 5; }
 
 template <int TN>
 __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p) {
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
         // 128 threads: thread = (16-byte chunk c of the 256-byte row segment, row r0 of every group of eight rows), so its
         // swizzled destination is one constant plus 1024 bytes per step and its source one pointer plus 8 rows per step.
         const int t2 = tid - kGWarpsA * 32;
-        constexpr int kPer = TN / 8, kAhead = 2;
+        constexpr int kPer = TN / 8, kAhead = kGStages > 3 ? kGStages - 1 : 2;
         const int c = t2 & 15, r0 = t2 >> 4;
         const uint32_t off0 = (uint32_t)((c >> 3) * (TN * 128) + r0 * 128 + (((c & 7) ^ r0) << 4));
         const __half *src0 = p.xs + (size_t)g_begin * kGK + (size_t)c * 8;

@@ -277,7 +277,8 @@ IM_EXPORT int im_cuda_sdpa_f16(im_device *dev, const void *q_dev, const void *k_
     if (!scratch_dev) num_splits = 1;
     return im::kv16_attention_launch(dev, static_cast<float *>(scratch_dev), scratch_bytes, static_cast<const __half *>(q_dev), nh * head_dim,
                                      static_cast<const __half *>(k_cache_dev), static_cast<const __half *>(v_cache_dev), scale,
-                                     static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, num_splits, base_pos + T,
+                                     static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, num_splits,
+                                     pos_dev ? max_seq : base_pos + T,  // positions on the device: the cache length bounds the context
                                      im::as_stream(stream), nullptr);
     IM_GUARD_END
 }
