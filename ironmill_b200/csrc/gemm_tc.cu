@@ -92,6 +92,27 @@ __device__ __forceinline__ uint4 dequant8_fast(uint32_t w, __half2 c, __half2 s)
     const uint32_t cc = *reinterpret_cast<uint32_t *>(&v26), d = *reinterpret_cast<uint32_t *>(&v37);
     return make_uint4(__byte_perm(a, b, 0x5410), __byte_perm(cc, d, 0x5410), __byte_perm(a, b, 0x7632), __byte_perm(cc, d, 0x7632));
 }
+// 8-bit codes: the 8 bytes of two words -> 8 fp16 values (q - z) * s in memory order.  0x6400 | q is 1024 + q for q < 1024.
+__device__ __forceinline__ uint4 dequant8b_fast(uint32_t w0, uint32_t w1, __half2 c, __half2 s) {
+    uint32_t h[4] = {__byte_perm(w0, 0x64u, 0x4140), __byte_perm(w0, 0x64u, 0x4342), __byte_perm(w1, 0x64u, 0x4140), __byte_perm(w1, 0x64u, 0x4342)};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h[i]), c), s);
+        o[i] = *reinterpret_cast<const uint32_t *>(&v);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+__device__ __forceinline__ uint4 dequant8b_slow(uint32_t w0, uint32_t w1, float z, float s) {
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t w = i < 2 ? w0 : w1;
+        const float lo = ((float)((w >> (16 * (i & 1))) & 255u) - z) * s, hi = ((float)((w >> (16 * (i & 1) + 8)) & 255u) - z) * s;
+        o[i] = (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
 __device__ __forceinline__ uint4 dequant8_slow(uint32_t w, float z, float s) {  // any zero point: f32, one rounding
     uint32_t o[4];
 #pragma unroll
@@ -104,14 +125,16 @@ __device__ __forceinline__ uint4 dequant8_slow(uint32_t w, float z, float s) {  
 
 // ring depth by token tile: 96 KB per stage at TN = 256 leaves room for two, 64 KB at TN = 128 for three (deeper rings
 // measured no faster: the weight warps, not the pipeline depth, set the pace)
-// (few tokens: the stages are small, and a deeper ring with more activation copies in flight hides the L2 latency that
-// otherwise paces a CTA at one stage per trip)
+// (also for the small token tiles: five stages with four activation copies in flight at 32 tokens, four with three at
+// 64, measured 20-60 % slower than three stages with two in flight on 16-64 tokens)
 template <int TN>
-constexpr int gemm_stages() { return TN >= 256 ? 2 : TN >= 128 ? 3 : TN >= 64 ? 4 : 5; }
+constexpr int gemm_stages() { return TN >= 256 ? 2 : 3; }
 
-template <int TN>
+template <int TN, int BITS>
 __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p) {
     constexpr int kGStages = gemm_stages<TN>();
+    constexpr int kCodeVec = BITS == 4 ? 2 : 4;      // 16-byte vectors of codes per thread and stage (64 columns)
+    constexpr int kAheadA = BITS == 4 ? kGAhead : 2;  // stages of codes in flight in registers (32 registers either way)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of every operand buffer: the swizzle is a function of the address bits
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -153,38 +176,40 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
         // codes of the next stage are requested before this stage is converted, so the memory latency is paid once.
         const int r = tid & 127, h = tid >> 7, n = n0 + r;
         const bool live = n < p.N;
-        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * (p.K / 2) + (size_t)g_begin * 64 + h * 32;
+        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * ((size_t)p.K * BITS / 8) + (size_t)g_begin * (16 * BITS) + h * (8 * BITS);
         const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * p.G + g_begin;
         const uint32_t row_off = (uint32_t)(h * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
-        // register ring of the next kGAhead stages' codes: 32 bytes per stage in flight per thread, enough to cover the
-        // memory latency at one stage per ~0.3 us
-        uint4 wb[kGAhead][2];
-        __half2 szb[kGAhead];
+        // register ring of the next kAheadA stages' codes: 32 (4-bit) or 64 (8-bit) bytes per stage in flight per thread,
+        // enough to cover the memory latency at one stage per ~0.3 us
+        uint4 wb[kAheadA][kCodeVec];
+        __half2 szb[kAheadA];
 #pragma unroll
-        for (int u = 0; u < kGAhead; u++) {
-            wb[u][0] = wb[u][1] = make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < kAheadA; u++) {
+#pragma unroll
+            for (int v = 0; v < kCodeVec; v++) wb[u][v] = make_uint4(0, 0, 0, 0);
             szb[u] = __floats2half2_rn(0.0f, 0.0f);
             if (live && u < G) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)u * 64);
-                wb[u][0] = ldg_stream_v4(src);
-                wb[u][1] = ldg_stream_v4(src + 1);
+                const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)u * (16 * BITS));
+#pragma unroll
+                for (int v = 0; v < kCodeVec; v++) wb[u][v] = ldg_stream_v4(src + v);
                 szb[u] = szrow[u];
             }
         }
-        for (int kt0 = 0; kt0 < G; kt0 += kGAhead) {
+        for (int kt0 = 0; kt0 < G; kt0 += kAheadA) {
 #pragma unroll
-            for (int u = 0; u < kGAhead; u++) {
+            for (int u = 0; u < kAheadA; u++) {
                 const int kt = kt0 + u;
                 if (kt < G) {  // warp-uniform
                     const int s = kt % kGStages, use = kt / kGStages;
-                    const uint32_t w0 = wb[u][0].x, w1 = wb[u][0].y, w2 = wb[u][0].z, w3 = wb[u][0].w;
-                    const uint32_t w4 = wb[u][1].x, w5 = wb[u][1].y, w6 = wb[u][1].z, w7 = wb[u][1].w;
+                    uint4 cw[kCodeVec];
+#pragma unroll
+                    for (int v = 0; v < kCodeVec; v++) cw[v] = wb[u][v];
                     const __half2 szc = szb[u];
-                    if (live && kt + kGAhead < G) {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)(kt + kGAhead) * 64);
-                        wb[u][0] = ldg_stream_v4(src);
-                        wb[u][1] = ldg_stream_v4(src + 1);
-                        szb[u] = szrow[kt + kGAhead];
+                    if (live && kt + kAheadA < G) {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)(kt + kAheadA) * (16 * BITS));
+#pragma unroll
+                        for (int v = 0; v < kCodeVec; v++) wb[u][v] = ldg_stream_v4(src + v);
+                        szb[u] = szrow[kt + kAheadA];
                     }
                     // convert into registers first: only the eight stores wait for the slot to be free
                     const float zf = __high2float(szc), sf = __low2float(szc);
@@ -194,11 +219,23 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
                     // needs it.  Rows past N carry zero codes and a zero scale, which dequantise to zero.
                     if (__builtin_expect(fast, 1)) {
                         const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szc));
-                        v0 = dequant8_fast(w0, c2, s2); v1 = dequant8_fast(w1, c2, s2); v2 = dequant8_fast(w2, c2, s2); v3 = dequant8_fast(w3, c2, s2);
-                        v4 = dequant8_fast(w4, c2, s2); v5 = dequant8_fast(w5, c2, s2); v6 = dequant8_fast(w6, c2, s2); v7 = dequant8_fast(w7, c2, s2);
+                        if (BITS == 4) {
+                            v0 = dequant8_fast(cw[0].x, c2, s2); v1 = dequant8_fast(cw[0].y, c2, s2); v2 = dequant8_fast(cw[0].z, c2, s2); v3 = dequant8_fast(cw[0].w, c2, s2);
+                            v4 = dequant8_fast(cw[1].x, c2, s2); v5 = dequant8_fast(cw[1].y, c2, s2); v6 = dequant8_fast(cw[1].z, c2, s2); v7 = dequant8_fast(cw[1].w, c2, s2);
+                        } else {
+                            v0 = dequant8b_fast(cw[0].x, cw[0].y, c2, s2); v1 = dequant8b_fast(cw[0].z, cw[0].w, c2, s2);
+                            v2 = dequant8b_fast(cw[1].x, cw[1].y, c2, s2); v3 = dequant8b_fast(cw[1].z, cw[1].w, c2, s2);
+                            v4 = dequant8b_fast(cw[kCodeVec - 2].x, cw[kCodeVec - 2].y, c2, s2); v5 = dequant8b_fast(cw[kCodeVec - 2].z, cw[kCodeVec - 2].w, c2, s2);
+                            v6 = dequant8b_fast(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, c2, s2); v7 = dequant8b_fast(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, c2, s2);
+                        }
+                    } else if (BITS == 4) {
+                        v0 = dequant8_slow(cw[0].x, zf, sf); v1 = dequant8_slow(cw[0].y, zf, sf); v2 = dequant8_slow(cw[0].z, zf, sf); v3 = dequant8_slow(cw[0].w, zf, sf);
+                        v4 = dequant8_slow(cw[1].x, zf, sf); v5 = dequant8_slow(cw[1].y, zf, sf); v6 = dequant8_slow(cw[1].z, zf, sf); v7 = dequant8_slow(cw[1].w, zf, sf);
                     } else {
-                        v0 = dequant8_slow(w0, zf, sf); v1 = dequant8_slow(w1, zf, sf); v2 = dequant8_slow(w2, zf, sf); v3 = dequant8_slow(w3, zf, sf);
-                        v4 = dequant8_slow(w4, zf, sf); v5 = dequant8_slow(w5, zf, sf); v6 = dequant8_slow(w6, zf, sf); v7 = dequant8_slow(w7, zf, sf);
+                        v0 = dequant8b_slow(cw[0].x, cw[0].y, zf, sf); v1 = dequant8b_slow(cw[0].z, cw[0].w, zf, sf);
+                        v2 = dequant8b_slow(cw[1].x, cw[1].y, zf, sf); v3 = dequant8b_slow(cw[1].z, cw[1].w, zf, sf);
+                        v4 = dequant8b_slow(cw[kCodeVec - 2].x, cw[kCodeVec - 2].y, zf, sf); v5 = dequant8b_slow(cw[kCodeVec - 2].z, cw[kCodeVec - 2].w, zf, sf);
+                        v6 = dequant8b_slow(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, zf, sf); v7 = dequant8b_slow(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, zf, sf);
                     }
                     if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
                     unsigned char *dst = As + (size_t)s * kABytes + row_off;
@@ -224,7 +261,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
         // 128 threads: thread = (16-byte chunk c of the 256-byte row segment, row r0 of every group of eight rows), so its
         // swizzled destination is one constant plus 1024 bytes per step and its source one pointer plus 8 rows per step.
         const int t2 = tid - kGWarpsA * 32;
-        constexpr int kPer = TN / 8, kAhead = kGStages > 3 ? kGStages - 1 : 2;
+        constexpr int kPer = TN / 8, kAhead = 2;
         const int c = t2 & 15, r0 = t2 >> 4;
         const uint32_t off0 = (uint32_t)((c >> 3) * (TN * 128) + r0 * 128 + (((c & 7) ^ r0) << 4));
         const __half *src0 = p.xs + (size_t)g_begin * kGK + (size_t)c * 8;
@@ -349,12 +386,12 @@ __global__ void gemm_splitk_reduce_kernel(const float *__restrict__ partial, __h
     *reinterpret_cast<uint2 *>(y + i) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
 }
 
-template <int TN>
+template <int TN, int BITS>
 int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     constexpr int kGStages = gemm_stages<TN>();
     const size_t smem = 1024 + (size_t)kGStages * (kGM * kGK * 2 + TN * kGK * 2) + (2 * kGStages + 1) * 8 + 16;
     if (smem > dev->smem_optin) return IM_ERR_BOUNDS;
-    auto kern = gemm_int4_tc_kernel<TN>;
+    auto kern = gemm_int4_tc_kernel<TN, BITS>;
     static DeviceOnce once;  // per instantiation
     if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int splits = (p.G + p.gps - 1) / p.gps;
@@ -372,7 +409,7 @@ int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
 // Y[M, N] = f16(X / awq) * dequant(W)^T for M tokens.  xs_scratch: M * K halves.  IM_ERR_BOUNDS when the weight is not
 // INT4 group-128 with K a multiple of 128 (the caller falls back to the matvec kernels).
 int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __half *xs_scratch, cudaStream_t st) {
-    if (w->bits != 4 || w->group_size != 128 || w->K % 128 != 0 || M < 1) return IM_ERR_BOUNDS;
+    if ((w->bits != 4 && w->bits != 8) || w->group_size != 128 || w->K % 128 != 0 || M < 1) return IM_ERR_BOUNDS;
     const size_t n = (size_t)M * w->K;
     IM_CUDA_CHECK(launch_k(act_scale_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, x, (const __half *)w->awq, xs_scratch, n, w->K));
     GemmParams p{w->codes, w->sz, xs_scratch, y, w->N, w->K, w->G, M, w->dev->err_flag, nullptr, w->G};
@@ -391,10 +428,16 @@ int gemm_affine_tc(const AffineWeight *w, const __half *x, __half *y, int M, __h
     // a 256-token tile shares every dequantised weight tile between twice as many tokens, but halves the CTA count:
     // worth it only once the grid still covers the GPU
     const long long ctas256 = (long long)((w->N + kGM - 1) / kGM) * ((M + 255) / 256);
-    if (M > 128 && ctas256 >= w->dev->sm_count) return gemm_launch<256>(p, w->dev, st);
-    if (M > 64) return gemm_launch<128>(p, w->dev, st);
-    if (M > 32) return gemm_launch<64>(p, w->dev, st);
-    return gemm_launch<32>(p, w->dev, st);
+    if (w->bits == 8) {  // superblock_matmul_int8 (affine_matmul.metal:155-290): the same kernel, byte codes
+        if (M > 128 && ctas256 >= w->dev->sm_count) return gemm_launch<256, 8>(p, w->dev, st);
+        if (M > 64) return gemm_launch<128, 8>(p, w->dev, st);
+        if (M > 32) return gemm_launch<64, 8>(p, w->dev, st);
+        return gemm_launch<32, 8>(p, w->dev, st);
+    }
+    if (M > 128 && ctas256 >= w->dev->sm_count) return gemm_launch<256, 4>(p, w->dev, st);
+    if (M > 64) return gemm_launch<128, 4>(p, w->dev, st);
+    if (M > 32) return gemm_launch<64, 4>(p, w->dev, st);
+    return gemm_launch<32, 4>(p, w->dev, st);
 }
 
 }  // namespace im

@@ -96,11 +96,18 @@ struct Sdpa16 {
     float scale;
 };
 
-// grid (nseq*T, nkv, splits), block GQ warps: warp w = query head kvh * GQ + w.
+// grid (nseq*T, nkv, splits), block GQ warps: warp w = query head kvh * GQ + w.  The CTA brings each tile of 32 K rows
+// and 32 V rows into shared memory once (16-byte asynchronous copies, two tiles in flight) for all of its query heads;
+// K rows sit 272 bytes apart so that a lane reading its own row with 128-bit loads meets no bank conflict.
+constexpr int kKRow16 = 272, kVRow16 = 256;
+
 template <int GQ>
 __global__ void __launch_bounds__(GQ * 32) sdpa16_kernel(const Sdpa16 p) {
     pdl_trigger();
     pdl_wait();
+    constexpr int NT = GQ * 32;
+    __shared__ __align__(16) unsigned char ksm[2][kTile16 * kKRow16];
+    __shared__ __align__(16) unsigned char vsm[2][kTile16 * kVRow16];
     __shared__ __align__(16) float qs[GQ][kHd16];
     const int st = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -117,16 +124,33 @@ __global__ void __launch_bounds__(GQ * 32) sdpa16_kernel(const Sdpa16 p) {
         const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
         *reinterpret_cast<float4 *>(&qs[warp][4 * lane]) = make_float4(a.x, a.y, b.x, b.y);
     }
-    __syncwarp();
     const size_t cache_base = ((size_t)seq * p.nkv + kvh) * p.max_seq * kHd16;
+    auto load_tile = [&](int buf, int tile) {  // rows past the split's end repeat its last row (their weights are zero)
+        for (int c = threadIdx.x; c < kTile16 * 16; c += NT) {
+            const int row = c >> 4, ch = c & 15;
+            const size_t src = cache_base + (size_t)min(tile + row, r1 - 1) * kHd16 + ch * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(&ksm[buf][row * kKRow16 + ch * 16])), "l"(p.kc + src) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(&vsm[buf][row * kVRow16 + ch * 16])), "l"(p.vc + src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     float m = -INFINITY, l = 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int tile = r0; tile < r1; tile += kTile16) {
-        const int pos = tile + lane;
-        const bool live = pos < r1;
+    const int ntiles = r1 > r0 ? (r1 - r0 + kTile16 - 1) / kTile16 : 0;
+    if (ntiles > 0) load_tile(0, r0);
+    for (int it = 0; it < ntiles; it++) {
+        const int tile = r0 + it * kTile16, buf = it & 1;
+        if (it + 1 < ntiles) {
+            load_tile(buf ^ 1, tile + kTile16);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // the tile (and, the first time, the queries) is visible to every warp
+        const bool live = tile + lane < r1;
         float s = -INFINITY;
         {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(p.kc + cache_base + (size_t)(live ? pos : tile) * kHd16);
+            const uint4 *kr = reinterpret_cast<const uint4 *>(&ksm[buf][lane * kKRow16]);
             float dot = 0.0f;
 #pragma unroll 4
             for (int i = 0; i < kHd16 / 8; i++) {
@@ -151,17 +175,15 @@ __global__ void __launch_bounds__(GQ * 32) sdpa16_kernel(const Sdpa16 p) {
         }
         const float wgt = live ? __expf(s - m) : 0.0f;
         l += warp_sum(wgt);
-        const int n = min(kTile16, r1 - tile);
-        const __half *vr = p.vc + cache_base + (size_t)tile * kHd16 + 4 * lane;
+        const unsigned char *vr = &vsm[buf][8 * lane];
 #pragma unroll 8
-        for (int j = 0; j < kTile16; j++) {
+        for (int j = 0; j < kTile16; j++) {  // rows past the end carry weight zero
             const float wj = __shfl_sync(0xffffffffu, wgt, j);
-            if (j < n) {
-                const uint2 raw = *reinterpret_cast<const uint2 *>(vr + (size_t)j * kHd16);
-                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-                acc[0] = fmaf(wj, a.x, acc[0]); acc[1] = fmaf(wj, a.y, acc[1]); acc[2] = fmaf(wj, b.x, acc[2]); acc[3] = fmaf(wj, b.y, acc[3]);
-            }
+            const uint2 raw = *reinterpret_cast<const uint2 *>(vr + j * kVRow16);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+            acc[0] = fmaf(wj, a.x, acc[0]); acc[1] = fmaf(wj, a.y, acc[1]); acc[2] = fmaf(wj, b.x, acc[2]); acc[3] = fmaf(wj, b.y, acc[3]);
         }
+        __syncthreads();  // every warp is done with this buffer before the copies of the tile after next land in it
     }
     const size_t hidx = (size_t)st * p.nh + head;
     if (p.splits == 1) {

@@ -216,7 +216,7 @@ struct Model {
     __half *hidden = nullptr, *norm_out = nullptr, *residual = nullptr, *qkv = nullptr, *q_d = nullptr, *k_d = nullptr,
            *attn_out = nullptr, *ffn_down = nullptr, *ffn_gate = nullptr, *ffn_up = nullptr, *xs_scratch = nullptr, *logits = nullptr,
            *logits_all = nullptr;
-    bool gemm_ok = false;  // every projection is INT4 group-128: forwards of 16 tokens and more run the tensor-core GEMM
+    bool gemm_ok = false;  // every projection is INT4 or INT8 group-128: forwards of 16 tokens and more run the tensor-core GEMM
     float *qrot = nullptr;  // [MT, nh_l, 2, hd] rotated queries
     uint32_t *tokens_dev = nullptr, *tok_hist = nullptr;
     int *pos_dev = nullptr, *step_dev = nullptr;
@@ -1402,7 +1402,7 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     m->gemm_ok = true;
     for (Layer &L : m->layers)
         for (AffineWeight *w : {L.qkv, L.o, L.gate, L.up, L.down})
-            if (!w || w->bits != 4 || w->group_size != 128 || w->K % 128 != 0 || w->N % 8 != 0) m->gemm_ok = false;
+            if (!w || (w->bits != 4 && w->bits != 8) || w->group_size != 128 || w->K % 128 != 0 || w->N % 8 != 0) m->gemm_ok = false;
     IM_TRY(m->alloc((void **)&m->logits, (size_t)c.max_batch * m->vocab_l * 2));
     if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_all, (size_t)c.max_batch * c.vocab_size * 2));
     IM_TRY(m->alloc((void **)&m->tokens_dev, MT * 4));

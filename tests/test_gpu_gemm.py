@@ -41,6 +41,17 @@ def test_k_split_for_few_tokens(dev, N, K, M):
     _check(dev, H.QWeight(N, K, awq=True, seed=N + K + M, name="gk"), M)
 
 
+@pytest.mark.parametrize("N,K,M", [(256, 512, 32), (384, 1024, 70), (1024, 1024, 129), (512, 2048, 16), (200, 512, 300)])
+def test_int8_weights(dev, N, K, M):
+    # superblock_matmul_int8 (affine_matmul.metal:155-290): byte codes through the same tensor-core kernel
+    qw = H.QWeight(N, K, bits=8, awq=True, seed=N + K + M, name="g8")
+    from ironmill_b200 import ops
+    x = (H.rng_for("gemm-x8", M).standard_normal((M, K))).astype(np.float16)
+    y = ops.matmul_affine(qw.gpu(dev), torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = orc.matmul_affine(qw.packed, qw.scales_f16, qw.zps_f16, x, N, K, 128, 8, awq=qw.awq, threads=8)
+    assert H.rel_err(y, ref) <= TOL, (N, K, M)
+
+
 def test_awq_and_ragged_rows(dev):
     # N not a multiple of the 128-row CTA tile: the last CTA's spare rows are masked
     _check(dev, H.QWeight(200, 512, awq=True, seed=3, name="ga"), 48)
