@@ -509,6 +509,7 @@ def run_matvec(args, rank, world):
     tpeak = measured_tensor_peak()
     sweep = []
     cases = [(n, N, K, kind, B, 4, 1) for n, N, K, kind in L8_SHAPES for B in (1, 4, 16, 64)]
+    cases += [(n, N, K, kind, B, 4, 1) for n, N, K, kind in L8_SHAPES for B in (256, 2048)]   # prefill chunks: the tensor-core GEMM
     cases += [(n, N, K, kind, 1, 8, 1) for n, N, K, kind in L8_SHAPES]
     for G in (2, 4, 8):   # what one of G ranks holds
         cases += [(n, N // G if n in ("qkv", "gate_up") else N, K if n in ("qkv", "gate_up") else K // G, kind, 1, 4, G) for n, N, K, kind in L8_SHAPES]

@@ -303,7 +303,8 @@ typedef struct im_model_config {
                                * off: an unquantized fp16 KV cache (kv_scatter + fused_sdpa / FlashDecoding) */
     uint64_t rotation_seed;   /* MetalConfig.rotation_seed (default 42) */
     int tp_world, tp_rank;    /* tensor parallel group (0/0 = single GPU) */
-    int prefill_chunk_size;   /* MetalConfig.prefill_chunk_size: tokens per prefill forward (0 = 256; at most 256) */
+    int prefill_chunk_size;   /* MetalConfig.prefill_chunk_size: tokens per prefill forward (0 = 2048, the most; never more
+                               * than max_seq_len; the activation buffers are sized for it) */
     int decode_schedule;      /* batch-1 decode: 0 = the whole-token kernel whenever the model fits it, 1 = always the
                                  graph of per-projection kernels, 2 = the whole-token kernel handing the o / down outputs on
                                  as tagged pairs instead of grid barriers (what tensor-parallel ranks do; one GPU: a way to

@@ -12,11 +12,15 @@
 //     dequantisation is fused into the operand load, HBM carries 4 bits per weight.  The codes of the next stage
 //     are requested before the current one is converted;
 //   * B: the activations, already divided by the AWQ scales and rounded to fp16 (act_scale_kernel), brought in by
-//     two warps with 16-byte cp.async copies into the same layout, two stages in flight.
-// A three-stage ring decouples the producers from the tensor core: full barriers count the ten producer warps,
-// tcgen05.commit releases a stage when its eight MMAs have read it.  After the last group warps 0-3 read their 32
+//     the copy engine: one thread issues two cp.async.bulk.tensor copies per stage (boxes of 64 columns x TN token
+//     rows of a 2-D tensor map with the 128-byte swizzle; rows past the last token come back as zeros), completion
+//     counted in bytes on the stage's full barrier.  The map covers this GPU's own buffer; no multicast.
+// A ring of stages decouples the producers from the tensor core: full barriers count the eight weight warps and the
+// announcement of the activation bytes, tcgen05.commit releases a stage when its eight MMAs have read it.  After the last group warps 0-3 read their 32
 // TMEM lanes each (tcgen05.ld 32x32b), convert and write fp16 outputs.  Every wait is bounded; a wait that runs
 // out sets the device error word, the kernel still frees its tensor memory and returns.
+#include <cuda.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -29,7 +33,7 @@ namespace {
 constexpr int kGM = 128;       // weight rows per CTA = UMMA M
 constexpr int kGK = 128;       // columns per stage = one quantisation group = two 64-column swizzle atoms
 constexpr int kGAhead = 4;      // stages of packed codes a weight thread keeps in flight in registers
-constexpr int kGWarpsA = 8, kGWarpsB = 4;       // warps 0-7: weights (0-3 also the epilogue), 8-11: activations, 12: tensor memory + MMA issue
+constexpr int kGWarpsA = 16, kGWarpsB = 1;      // warps 0-15: weights (0-3 also the epilogue), 16: activation copies, 17: tensor memory + MMA issue
 constexpr int kGThreads = (kGWarpsA + kGWarpsB + 1) * 32;
 constexpr int kGMmaWarp = kGWarpsA + kGWarpsB;
 
@@ -63,6 +67,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// One tile of the activation matrix: box {64 columns, TN rows} of a 2-D tensor map (fp16, 128-byte swizzle), landing in
+// the K-major operand layout the MMA descriptors name; rows past the last token are filled with zeros.  Completion is
+// counted in bytes on the stage's full barrier.  x is a multiple of 64 columns (128 bytes): the 16-byte rule holds.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
 }
 
 struct GemmParams {
@@ -131,10 +144,10 @@ template <int TN>
 constexpr int gemm_stages() { return TN >= 256 ? 2 : 3; }
 
 template <int TN, int BITS>
-__global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b) {
     constexpr int kGStages = gemm_stages<TN>();
-    constexpr int kCodeVec = BITS == 4 ? 2 : 4;      // 16-byte vectors of codes per thread and stage (64 columns)
-    constexpr int kAheadA = BITS == 4 ? kGAhead : 2;  // stages of codes in flight in registers (32 registers either way)
+    constexpr int kCodeVec = BITS == 4 ? 1 : 2;      // 16-byte vectors of codes per thread and stage (32 columns)
+    constexpr int kAheadA = BITS == 4 ? kGAhead : 2;  // stages of codes in flight in registers (16 registers either way)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of every operand buffer: the swizzle is a function of the address bits
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
     pdl_trigger();
     if (tid == 0) {
         for (int i = 0; i < kGStages; i++) {
-            mbar_init(&full[i], kGWarpsA + kGWarpsB);
+            mbar_init(&full[i], kGWarpsA + 1);  // the weight warps + the thread that announces the activation bytes
             mbar_init(&empty[i], 1);
         }
         mbar_init(accum, 1);
@@ -172,14 +185,17 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
     bool ok = true;
     if (warp < kGWarpsA) {
         // ---------------------------------------------------------------- weights: dequantise into operand A
-        // thread = (row r, half h of the group): 64 columns = 32 bytes of codes per stage, one swizzle atom.  The
-        // codes of the next stage are requested before this stage is converted, so the memory latency is paid once.
-        const int r = tid & 127, h = tid >> 7, n = n0 + r;
+        // thread = (row r, quarter q of the group): 32 columns = 16 (4-bit) or 32 (8-bit) bytes of codes per stage, four
+        // 16-byte chunks of one swizzle atom.  The codes of the next stages are requested before this stage is converted,
+        // so the memory latency is paid once.  Sixteen such warps: four per scheduler to cover each other's dependent
+        // chains (eight measured 43 % issue utilisation).
+        const int r = tid & 127, q = tid >> 7, n = n0 + r;
         const bool live = n < p.N;
-        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * ((size_t)p.K * BITS / 8) + (size_t)g_begin * (16 * BITS) + h * (8 * BITS);
+        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * ((size_t)p.K * BITS / 8) + (size_t)g_begin * (16 * BITS) + q * (4 * BITS);
         const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * p.G + g_begin;
-        const uint32_t row_off = (uint32_t)(h * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
-        // register ring of the next kAheadA stages' codes: 32 (4-bit) or 64 (8-bit) bytes per stage in flight per thread,
+        const uint32_t row_off = (uint32_t)((q >> 1) * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
+        const int c0 = 4 * (q & 1);  // first 16-byte chunk of this thread inside the atom's 128-byte row
+        // register ring of the next kAheadA stages' codes: 16 (4-bit) or 32 (8-bit) bytes per stage in flight per thread,
         // enough to cover the memory latency at one stage per ~0.3 us
         uint4 wb[kAheadA][kCodeVec];
         __half2 szb[kAheadA];
@@ -214,81 +230,52 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
                     // convert into registers first: only the eight stores wait for the slot to be free
                     const float zf = __high2float(szc), sf = __low2float(szc);
                     const bool fast = zf == rintf(zf) && zf >= -1024.0f && zf <= 1023.0f;
-                    uint4 v0, v1, v2, v3, v4, v5, v6, v7;
+                    uint4 v0, v1, v2, v3;
                     // Two real branches (not a select): the f32 path costs three times the packed one and almost no group
                     // needs it.  Rows past N carry zero codes and a zero scale, which dequantise to zero.
                     if (__builtin_expect(fast, 1)) {
                         const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szc));
                         if (BITS == 4) {
                             v0 = dequant8_fast(cw[0].x, c2, s2); v1 = dequant8_fast(cw[0].y, c2, s2); v2 = dequant8_fast(cw[0].z, c2, s2); v3 = dequant8_fast(cw[0].w, c2, s2);
-                            v4 = dequant8_fast(cw[1].x, c2, s2); v5 = dequant8_fast(cw[1].y, c2, s2); v6 = dequant8_fast(cw[1].z, c2, s2); v7 = dequant8_fast(cw[1].w, c2, s2);
                         } else {
                             v0 = dequant8b_fast(cw[0].x, cw[0].y, c2, s2); v1 = dequant8b_fast(cw[0].z, cw[0].w, c2, s2);
-                            v2 = dequant8b_fast(cw[1].x, cw[1].y, c2, s2); v3 = dequant8b_fast(cw[1].z, cw[1].w, c2, s2);
-                            v4 = dequant8b_fast(cw[kCodeVec - 2].x, cw[kCodeVec - 2].y, c2, s2); v5 = dequant8b_fast(cw[kCodeVec - 2].z, cw[kCodeVec - 2].w, c2, s2);
-                            v6 = dequant8b_fast(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, c2, s2); v7 = dequant8b_fast(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, c2, s2);
+                            v2 = dequant8b_fast(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, c2, s2); v3 = dequant8b_fast(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, c2, s2);
                         }
                     } else if (BITS == 4) {
                         v0 = dequant8_slow(cw[0].x, zf, sf); v1 = dequant8_slow(cw[0].y, zf, sf); v2 = dequant8_slow(cw[0].z, zf, sf); v3 = dequant8_slow(cw[0].w, zf, sf);
-                        v4 = dequant8_slow(cw[1].x, zf, sf); v5 = dequant8_slow(cw[1].y, zf, sf); v6 = dequant8_slow(cw[1].z, zf, sf); v7 = dequant8_slow(cw[1].w, zf, sf);
                     } else {
                         v0 = dequant8b_slow(cw[0].x, cw[0].y, zf, sf); v1 = dequant8b_slow(cw[0].z, cw[0].w, zf, sf);
-                        v2 = dequant8b_slow(cw[1].x, cw[1].y, zf, sf); v3 = dequant8b_slow(cw[1].z, cw[1].w, zf, sf);
-                        v4 = dequant8b_slow(cw[kCodeVec - 2].x, cw[kCodeVec - 2].y, zf, sf); v5 = dequant8b_slow(cw[kCodeVec - 2].z, cw[kCodeVec - 2].w, zf, sf);
-                        v6 = dequant8b_slow(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, zf, sf); v7 = dequant8b_slow(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, zf, sf);
+                        v2 = dequant8b_slow(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, zf, sf); v3 = dequant8b_slow(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, zf, sf);
                     }
                     if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
                     unsigned char *dst = As + (size_t)s * kABytes + row_off;
-                    const int x = r & 7;  // chunk c = columns 64h + 8c .. + 7 of the group, stored at chunk c ^ (row & 7)
-                    *reinterpret_cast<uint4 *>(dst + ((0 ^ x) << 4)) = v0;
-                    *reinterpret_cast<uint4 *>(dst + ((1 ^ x) << 4)) = v1;
-                    *reinterpret_cast<uint4 *>(dst + ((2 ^ x) << 4)) = v2;
-                    *reinterpret_cast<uint4 *>(dst + ((3 ^ x) << 4)) = v3;
-                    *reinterpret_cast<uint4 *>(dst + ((4 ^ x) << 4)) = v4;
-                    *reinterpret_cast<uint4 *>(dst + ((5 ^ x) << 4)) = v5;
-                    *reinterpret_cast<uint4 *>(dst + ((6 ^ x) << 4)) = v6;
-                    *reinterpret_cast<uint4 *>(dst + ((7 ^ x) << 4)) = v7;
+                    const int x = r & 7;  // chunk c = columns 8c .. 8c + 7 of the atom's 64, stored at chunk c ^ (row & 7)
+                    *reinterpret_cast<uint4 *>(dst + (((c0 + 0) ^ x) << 4)) = v0;
+                    *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ x) << 4)) = v1;
+                    *reinterpret_cast<uint4 *>(dst + (((c0 + 2) ^ x) << 4)) = v2;
+                    *reinterpret_cast<uint4 *>(dst + (((c0 + 3) ^ x) << 4)) = v3;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full[s]);
                 }
             }
         }
-    } else if (warp < kGMmaWarp) {
-        // ---------------------------------------------------------------- activations: cp.async into operand B
-        // 64 threads keep two stages of 16-byte asynchronous copies in flight; a stage is announced once its group of
-        // copies has landed (rows past the last token are zero-filled by a copy of source size 0).
-        // 128 threads: thread = (16-byte chunk c of the 256-byte row segment, row r0 of every group of eight rows), so its
-        // swizzled destination is one constant plus 1024 bytes per step and its source one pointer plus 8 rows per step.
-        const int t2 = tid - kGWarpsA * 32;
-        constexpr int kPer = TN / 8, kAhead = 2;
-        const int c = t2 & 15, r0 = t2 >> 4;
-        const uint32_t off0 = (uint32_t)((c >> 3) * (TN * 128) + r0 * 128 + (((c & 7) ^ r0) << 4));
-        const __half *src0 = p.xs + (size_t)g_begin * kGK + (size_t)c * 8;
-        for (int it = 0; it < G + kAhead; it++) {
-            // announce the stage whose copies have landed BEFORE waiting for a free slot for the next one: the other
-            // order would make every MMA wait for its predecessor to retire
-            if (it >= kAhead) {
-                asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full[(it - kAhead) % kGStages]);
+    } else if (warp == kGWarpsA) {
+        // ---------------------------------------------------------------- activations: TMA into operand B
+        // One thread per stage: wait for the slot, announce the bytes on the stage's full barrier and issue the two
+        // tensor copies (columns 0-63 and 64-127 of the group, TN token rows each; a tensor map over this GPU's own
+        // activation buffer, no multicast).  The copy engine does the swizzle and the zero fill of rows past M.
+        for (int it = 0; it < G; it++) {
+            const int s = it % kGStages, use = it / kGStages;
+            if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
+            if (lane == 0 && ok) {
+                unsigned char *dst = Bs + (size_t)s * kBBytes;
+                const int x = (g_begin + it) * kGK;
+                mbar_expect_tx(&full[s], (uint32_t)kBBytes);
+                tma_load_2d(dst, &tmap_b, x, m0, &full[s]);
+                tma_load_2d(dst + TN * 128, &tmap_b, x + 64, m0, &full[s]);
             }
-            if (it < G) {
-                const int s = it % kGStages, use = it / kGStages;
-                if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
-                const uint32_t d0 = smem_u32(Bs + (size_t)s * kBBytes) + off0;
-                const __half *sk = src0 + (size_t)it * kGK;
-#pragma unroll 8
-                for (int i = 0; i < kPer; i++) {
-                    const int m = m0 + r0 + 8 * i;
-                    const bool in = m < p.M;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d0 + (uint32_t)i * 1024u), "l"(sk + (size_t)(in ? m : 0) * p.K),
-                                 "r"(in ? 16 : 0)
-                                 : "memory");
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            __syncwarp();
         }
     } else {
         // ---------------------------------------------------------------- one thread issues the MMAs
@@ -386,6 +373,19 @@ __global__ void gemm_splitk_reduce_kernel(const float *__restrict__ partial, __h
     *reinterpret_cast<uint2 *>(y + i) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
+typedef CUresult (*TmapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TmapEncodeFn tmap_encode_fn() {
+    static TmapEncodeFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<TmapEncodeFn>(f);
+    }();
+    return fn;
+}
+
 template <int TN, int BITS>
 int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     constexpr int kGStages = gemm_stages<TN>();
@@ -394,9 +394,20 @@ int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     auto kern = gemm_int4_tc_kernel<TN, BITS>;
     static DeviceOnce once;  // per instantiation
     if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // activations [M, K] fp16 row-major as a 2-D tensor: inner dimension K, boxes of 64 columns x TN rows, 128-byte swizzle
+    TmapEncodeFn enc = tmap_encode_fn();
+    if (!enc) return fail(IM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    alignas(64) CUtensorMap tmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)p.K * sizeof(__half)};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)TN};
+    const cuuint32_t estride[2] = {1u, 1u};
+    const CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(p.xs), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(IM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for activations [%d, %d]", (int)cr, p.M, p.K);
     const int splits = (p.G + p.gps - 1) / p.gps;
     dim3 grid((p.N + kGM - 1) / kGM, (p.M + TN - 1) / TN, splits);
-    IM_CUDA_CHECK(launch_k(kern, grid, dim3(kGThreads), smem, st, p));
+    IM_CUDA_CHECK(launch_k(kern, grid, dim3(kGThreads), smem, st, p, tmap));
     if (p.partial) {
         const size_t n = (size_t)p.M * p.N;  // N is a multiple of 4 here (checked by the caller)
         IM_CUDA_CHECK(launch_k(gemm_splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, (const float *)p.partial, p.y, n, splits));

@@ -881,7 +881,7 @@ IM_EXPORT int im_cuda_matmul_affine(const im_affine_weight *w, const void *x_dev
     IM_CUDA_CHECK(cudaSetDevice(w->dev->ordinal));
     const int rc = gemm_affine_tc(w, static_cast<const __half *>(x_dev), static_cast<__half *>(y_dev), M, static_cast<__half *>(scratch_dev),
                                   as_stream(stream));
-    if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "the tensor-core GEMM takes INT4 group-128 weights with K a multiple of 128");
+    if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "the tensor-core GEMM takes INT4 or INT8 group-128 weights with K a multiple of 128");
     return rc;
     IM_GUARD_END
 }

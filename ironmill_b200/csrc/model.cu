@@ -264,7 +264,11 @@ struct Model {
     }
 };
 
-static const int kPrefillChunk = 256;
+// Tokens per prefill forward: the tensor-core GEMMs fill the GPU from about a thousand tokens on (a 256-token chunk is
+// 32-112 CTAs per projection), so the default is the largest chunk; the activation buffers are sized for the configured
+// chunk (at most max_seq_len).  prefill_all_logits keeps 256-token chunks: it holds a chunk's logits for every token.
+static const int kPrefillChunk = 2048;
+static const int kAllLogitsChunk = 256;
 static const int kGemmMinTokens = 16;  // from here on the projections are dense contractions: tcgen05 GEMM instead of matvecs
 
 __global__ void advance_pos_kernel(int *pos, const int *slot_map, int n, int by) {
@@ -949,13 +953,14 @@ static int prefill_slot(Model *m, int slot, const uint32_t *tokens_host, int n, 
         return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", m->slot_pos[slot], n, m->cfg.max_seq_len);
     cudaStream_t st = m->stream;
     // 256-token chunks when the projections run as tensor-core GEMMs; the matvec kernels take at most 64 rows per call
-    const int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
+    int chunk = m->gemm_ok ? m->cfg.prefill_chunk_size : (m->cfg.prefill_chunk_size < 64 ? m->cfg.prefill_chunk_size : 64);
+    if (all_logits && chunk > kAllLogitsChunk) chunk = kAllLogitsChunk;
     const size_t V = (size_t)m->cfg.vocab_size;
     const int *slots = slot == 0 ? nullptr : m->slot_ident + slot;
     if (all_logits && !m->logits_seq) {  // first use: a chunk's worth of logits on the device and in pinned host memory
-        IM_TRY(m->alloc((void **)&m->logits_seq, (size_t)kPrefillChunk * m->vocab_l * 2));
-        if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_seq_all, (size_t)kPrefillChunk * V * 2));
-        IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_seq_pin, (size_t)kPrefillChunk * V * 2));
+        IM_TRY(m->alloc((void **)&m->logits_seq, (size_t)kAllLogitsChunk * m->vocab_l * 2));
+        if (m->world > 1) IM_TRY(m->alloc((void **)&m->logits_seq_all, (size_t)kAllLogitsChunk * V * 2));
+        IM_CUDA_CHECK(cudaMallocHost((void **)&m->logits_seq_pin, (size_t)kAllLogitsChunk * V * 2));
     }
     for (int done = 0; done < n; done += chunk) {
         const int T = n - done < chunk ? n - done : chunk;
@@ -1158,6 +1163,7 @@ IM_EXPORT int im_cuda_model_create(im_device *dev, const im_model_config *cfg, i
     IM_REQUIRE(c.decode_schedule >= 0 && c.decode_schedule <= 2 && c.tp_collective >= 0 && c.tp_collective <= 1 && c.wait_limit_ms >= 0,
                "bad decode_schedule / tp_collective / wait_limit_ms");
     if (c.prefill_chunk_size == 0) c.prefill_chunk_size = kPrefillChunk;
+    if (c.prefill_chunk_size > c.max_seq_len) c.prefill_chunk_size = c.max_seq_len;  // no prompt is longer than the cache
     IM_CUDA_CHECK(cudaSetDevice(dev->ordinal));
     im_model *m = new im_model();
     m->dev = dev;
@@ -1380,7 +1386,7 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
     IM_TRY(m->alloc((void **)&m->sinc, (size_t)c.max_seq_len * (hd / 2) * 2));
     IM_TRY(im_cuda_rope_table(hd, c.max_seq_len, c.rope_theta, c.rotary_dim, m->cosc, m->sinc));
     // activations
-    m->MT = c.max_batch > kPrefillChunk ? c.max_batch : kPrefillChunk;
+    m->MT = std::max(std::max(c.max_batch, c.prefill_chunk_size), kAllLogitsChunk < c.max_seq_len ? kAllLogitsChunk : c.max_seq_len);
     const size_t MT = m->MT;
     IM_TRY(m->alloc((void **)&m->hidden, MT * H * 2));
     IM_TRY(m->alloc((void **)&m->norm_out, MT * H * 2));
@@ -1435,14 +1441,14 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
         const size_t s = im_cuda_tq_scratch_bytes(b, 1, m->nh_l, hd, decode_splits(m, b));
         if (s > need) need = s;
     }
-    for (int t = 1; t <= kPrefillChunk; t++) {
+    for (int t = 1; t <= m->MT; t++) {
         const size_t s = im_cuda_tq_scratch_bytes(1, t, m->nh_l, hd, tq_auto_splits(m->dev, 1, t, m->nkv_l, c.max_seq_len));
         if (s > need) need = s;
     }
     if (c.tq_bits == 16) {
         size_t n16 = 0;
         for (int b = 1; b <= c.max_batch; b++) n16 = std::max(n16, kv16_scratch_bytes(b, m->nh_l, kv16_auto_splits(m->dev, b, m->nkv_l, c.max_seq_len)));
-        for (int t = 1; t <= kPrefillChunk; t++) n16 = std::max(n16, kv16_scratch_bytes(t, m->nh_l, kv16_auto_splits(m->dev, t, m->nkv_l, c.max_seq_len)));
+        for (int t = 1; t <= m->MT; t++) n16 = std::max(n16, kv16_scratch_bytes(t, m->nh_l, kv16_auto_splits(m->dev, t, m->nkv_l, c.max_seq_len)));
         IM_TRY(m->alloc((void **)&m->kv16_scratch, n16));
         m->kv16_scratch_bytes = n16;
     }

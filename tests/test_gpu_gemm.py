@@ -52,6 +52,11 @@ def test_int8_weights(dev, N, K, M):
     assert H.rel_err(y, ref) <= TOL, (N, K, M)
 
 
+def test_many_token_tiles_of_256(dev):
+    # 19 token tiles x 8 row tiles: the 256-token tile (chosen once the grid covers the GPU), a ragged last token tile
+    _check(dev, H.QWeight(1024, 512, awq=True, seed=77, name="gt"), 4700)
+
+
 def test_awq_and_ragged_rows(dev):
     # N not a multiple of the 128-row CTA tile: the last CTA's spare rows are masked
     _check(dev, H.QWeight(200, 512, awq=True, seed=3, name="ga"), 48)
