@@ -255,6 +255,14 @@ int im_cuda_tq_attention_static(const im_tq *tq, const void *q_dev, const void *
                                 const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,
                                 void *out_dev, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T,
                                 int num_splits, void *stream);
+/* Prefill form for one sequence (T tokens at positions base_pos .. base_pos + T - 1, rows already in the cache, the
+ * reference's turboquant_attention with token_count > 1, turboquant.metal:202-462): the cached rows are dequantised once
+ * into dq_dev (im_cuda_tq_prefill_scratch_bytes(nkv, max_seq) bytes) and scored by a causal tensor-core pass.  Caches of
+ * one sequence: [nkv, max_seq, ...].  Same results as im_cuda_tq_attention within its tolerance. */
+size_t im_cuda_tq_prefill_scratch_bytes(int nkv, int max_seq);
+int im_cuda_tq_prefill_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev, const float *k_scale_dev,
+                                 const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale, void *out_dev, int nh, int nkv,
+                                 int max_seq, int base_pos, int T, void *dq_dev, void *stream);
 /* Scratch im_cuda_tq_attention needs for a launch: split partials (nseq*T*nh*splits*(head_dim+2) floats) plus the
  * rotated queries of its pre-pass (nseq*T*nh*2*head_dim floats).  The handle grows its scratch on demand. */
 size_t im_cuda_tq_scratch_bytes(int nseq, int T, int nh, int head_dim, int splits);

@@ -34,7 +34,7 @@ _lib = None
 _VOIDP_RESTYPE = ("im_cuda_buffer_ptr",)
 _SIZE_RESTYPE = ("im_cuda_device_allocated_bytes", "im_cuda_buffer_length", "im_cuda_affine_weight_bytes",
                  "im_cuda_model_memory_bytes", "im_cuda_model_step_bytes", "im_cuda_tq_scratch_bytes",
-                 "im_cuda_sdpa_f16_scratch_bytes")
+                 "im_cuda_sdpa_f16_scratch_bytes", "im_cuda_tq_prefill_scratch_bytes")
 _VOID_RESTYPE = ("im_cuda_device_free", "im_cuda_buffer_free", "im_cuda_affine_weight_free", "im_cuda_model_free",
                  "im_cuda_tq_free", "im_cuda_tp_free")
 

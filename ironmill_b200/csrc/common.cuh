@@ -208,6 +208,12 @@ struct Tq {
 };
 
 int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len);
+int tq_reduce_launch(const Tq *tq, const float *po, const float *pm, const float *pl, __half *out, int tokens, int nh, int splits, cudaStream_t st);
+// Prefill chunks of one sequence: dequantise the cached rows once, causal flash attention on the tensor cores (tq_prefill.cu).
+size_t tq_prefill_scratch_bytes(int nkv, int max_seq);
+int tq_prefill_attention_launch(const Tq *tq, float *partials, void *dq, const float *qrot, const uint8_t *kc, const uint8_t *vc, const float *ks,
+                                const float *vs, const float *krn, float attn_scale, __half *out, int slot, int nh, int nkv, int max_seq,
+                                const int *pos_dev, int T, int ctx_end, cudaStream_t st, int base_pos = 0);
 // Inputs of the fused RoPE + cache write + query rotation launch (turboquant.cu).
 struct TqPrep {
     const __half *qkv;  // [nseq*T, stride]: q | k | v of one token

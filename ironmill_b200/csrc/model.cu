@@ -238,6 +238,8 @@ struct Model {
     size_t bytes = 0;
     int launches_per_step = 0;
     float *scratch_ref = nullptr;
+    void *pf_dq = nullptr;          // dequantised K' / V' rows of one sequence for prefill chunks (tq_prefill.cu)
+    int prefill_slot_id = -1, prefill_ctx_end = 0;  // set around a prefill chunk's forward: the slot and its positions after the chunk
     float *kv16_scratch = nullptr;  // split partials of the fp16-KV attention (tq_bits == 16)
     size_t kv16_scratch_bytes = 0;
     // whole-token decode kernel (batch 1, single GPU): tables built by mega_prepare()
@@ -551,6 +553,12 @@ static int attention_block(Model *m, int part, const TqPrep &a, __half *q_buf, L
                                      a.nkv, c.max_seq_len, 0, m->pos_dev, T, 0, c.max_seq_len, st, slots);
     }
     if (part == 0) return tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st);
+    if (nseq == 1 && T >= 16 && m->pf_dq && m->prefill_slot_id >= 0) {  // a prefill chunk: dequantise once, flash attention
+        const int rc = tq_prefill_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, m->pf_dq, m->qrot, L.kc, L.vc, L.ks, L.vs, L.krn,
+                                                   attn_scale, m->attn_out, m->prefill_slot_id, a.nh, a.nkv, c.max_seq_len, m->pos_dev, T,
+                                                   m->prefill_ctx_end, st);
+        if (rc != IM_ERR_BOUNDS) return rc;  // head groupings it does not take: the per-token kernel below
+    }
     return tq_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, nullptr, L.kc, L.vc, L.ks, L.vs, L.krn, attn_scale, m->attn_out,
                                nseq, a.nh, a.nkv, c.max_seq_len, 0, m->pos_dev, T, attn_splits, st, m->qrot, slots);
 }
@@ -967,7 +975,11 @@ static int prefill_slot(Model *m, int slot, const uint32_t *tokens_host, int n, 
         memcpy(m->tokens_pin, tokens_host + done, (size_t)T * 4);
         IM_CUDA_CHECK(cudaMemcpyAsync(m->tokens_dev, m->tokens_pin, (size_t)T * 4, cudaMemcpyHostToDevice, st));
         const int splits = tq_auto_splits(m->dev, 1, T, m->nkv_l, m->slot_pos[slot] + T);
-        IM_TRY(forward(m, 1, T, splits, st, nullptr, nullptr, all_logits != nullptr, slots));
+        m->prefill_slot_id = slot;
+        m->prefill_ctx_end = m->slot_pos[slot] + T;
+        const int frc = forward(m, 1, T, splits, st, nullptr, nullptr, all_logits != nullptr, slots);
+        m->prefill_slot_id = -1;
+        IM_TRY(frc);
         advance_pos_kernel<<<1, 64, 0, st>>>(m->pos_dev, slots, 1, T);
         IM_CUDA_CHECK(cudaGetLastError());
         if (all_logits) {
@@ -1452,6 +1464,8 @@ IM_EXPORT int im_cuda_model_finalize(im_model *m) {
         IM_TRY(m->alloc((void **)&m->kv16_scratch, n16));
         m->kv16_scratch_bytes = n16;
     }
+    if (c.tq_bits != 16 && tq_prefill_scratch_bytes(m->nkv_l, c.max_seq_len) <= ((size_t)2 << 30))  // (longer caches: the per-token kernel)
+        IM_TRY(m->alloc(&m->pf_dq, tq_prefill_scratch_bytes(m->nkv_l, c.max_seq_len)));
     IM_TRY(im_cuda_tq_reserve_scratch(m->tq, need));
     m->scratch_ref = reinterpret_cast<Tq *>(m->tq)->scratch;
     m->bytes += need + reinterpret_cast<Tq *>(m->tq)->const_bytes;

@@ -639,6 +639,12 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
     return IM_OK;
 }
 
+// Combination of split partials (normalise, rotate back, fp16) for `tokens` x nh heads: shared with tq_prefill.cu.
+int tq_reduce_launch(const Tq *tq, const float *po, const float *pm, const float *pl, __half *out, int tokens, int nh, int splits, cudaStream_t st) {
+    IM_CUDA_CHECK(launch_k(tq_reduce_kernel, dim3(tokens, nh), dim3(kHd), 0, st, po, pm, pl, (const float *)tq->signs, out, nh, splits));
+    return IM_OK;
+}
+
 int tq_auto_splits(const Device *dev, int nseq, int T, int nkv, int seq_len) {
     const int ctas = nseq * T * nkv;
     int s = (2 * dev->sm_count + ctas - 1) / ctas;                // two 8-warp CTAs per SM
@@ -699,6 +705,37 @@ int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uin
     return IM_OK;
 }
 }  // namespace im
+
+IM_EXPORT size_t im_cuda_tq_prefill_scratch_bytes(int nkv, int max_seq) { return im::tq_prefill_scratch_bytes(nkv, max_seq); }
+
+// Prefill form of im_cuda_tq_attention for one sequence (cache slot 0): T tokens at positions base_pos .. base_pos + T - 1,
+// whose rows are already in the cache; the cached rows are dequantised once into dq_dev and a causal flash-attention
+// pass runs over them on the tensor cores (tq_prefill.cu).  Same arithmetic contract and tolerance as im_cuda_tq_attention.
+IM_EXPORT int im_cuda_tq_prefill_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev, const float *k_scale_dev,
+                                           const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale, void *out_dev, int nh, int nkv,
+                                           int max_seq, int base_pos, int T, void *dq_dev, void *stream) {
+    IM_GUARD_BEGIN
+    IM_REQUIRE(tq && q_dev && k_cache_dev && v_cache_dev && k_scale_dev && v_scale_dev && k_rnorm_dev && out_dev && dq_dev, "bad argument");
+    IM_REQUIRE(tq->hd == kHd, "the attention kernel is built for head_dim 128 (got %d)", tq->hd);
+    IM_REQUIRE(nkv > 0 && nh % nkv == 0, "nh must be a multiple of nkv");
+    IM_REQUIRE(T >= 0 && max_seq > 0 && base_pos >= 0, "bad shape");
+    if (T == 0) return IM_OK;
+    if (base_pos + T > max_seq) return fail(IM_ERR_BOUNDS, "sequence position %d + %d tokens exceeds max_seq_len %d", base_pos, T, max_seq);
+    const size_t need = im_cuda_tq_scratch_bytes(1, T, nh, kHd, 1);
+    if (need > tq->scratch_bytes) {
+        int rc = im_cuda_tq_reserve_scratch(tq, need);
+        if (rc != IM_OK) return rc;
+    }
+    float *qrot = tq->scratch + tq_partial_bytes(1, T, nh, kHd, 1) / sizeof(float);
+    IM_CUDA_CHECK(launch_k(tq_qrot_kernel, dim3(T, nh), dim3(kHd), 0, as_stream(stream), static_cast<const __half *>(q_dev), (const float *)tq->signs,
+                           (const float *)tq->qjl_t, qrot, nh));
+    const int rc = tq_prefill_attention_launch(tq, tq->scratch, dq_dev, qrot, static_cast<const uint8_t *>(k_cache_dev), static_cast<const uint8_t *>(v_cache_dev),
+                                               k_scale_dev, v_scale_dev, k_rnorm_dev, attn_scale, static_cast<__half *>(out_dev), 0, nh, nkv, max_seq, nullptr, T,
+                                               base_pos + T, as_stream(stream), base_pos);
+    if (rc == IM_ERR_BOUNDS) return fail(IM_ERR_INVALID, "query heads per KV head must be 1, 2, 4 or 8 (got %d/%d)", nh, nkv);
+    return rc;
+    IM_GUARD_END
+}
 
 IM_EXPORT int im_cuda_tq_attention(im_tq *tq, const void *q_dev, const void *k_cache_dev, const void *v_cache_dev,
                                    const float *k_scale_dev, const float *v_scale_dev, const float *k_rnorm_dev, float attn_scale,

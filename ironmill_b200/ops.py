@@ -323,6 +323,16 @@ class TurboQuant:
                                          C.c_int(base_pos), vp(pos_dev), C.c_int(T), C.c_int(num_splits), _stream()))
         return out
 
+    def prefill_attention(self, q, k_cache, v_cache, k_scale, v_scale, k_rnorm, attn_scale, nh, nkv, max_seq, base_pos):
+        """T tokens of one sequence at positions base_pos .. (rows already cached): dequantise once + causal tensor-core pass."""
+        T = _h16(q).numel() // (nh * self.head_dim)
+        out = torch.empty_like(q)
+        dq = torch.empty(int(lib().im_cuda_tq_prefill_scratch_bytes(C.c_int(nkv), C.c_int(max_seq))), dtype=torch.uint8, device=q.device)
+        check(lib().im_cuda_tq_prefill_attention(self.handle, vp(q), vp(k_cache), vp(v_cache), vp(k_scale), vp(v_scale), vp(k_rnorm),
+                                                 C.c_float(attn_scale), vp(out), C.c_int(nh), C.c_int(nkv), C.c_int(max_seq), C.c_int(base_pos),
+                                                 C.c_int(T), vp(dq), _stream()))
+        return out
+
     def free(self):
         if self.handle:
             lib().im_cuda_tq_free(self.handle)

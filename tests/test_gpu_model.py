@@ -280,6 +280,24 @@ def test_prefill_all_logits_rows_match_step_by_step_prefills():
         assert np.abs(allg[n - 1] - ref.forward(prompt[:n])).max() <= 5e-2
 
 
+@pytest.mark.parametrize("nh,nkv,n_bits", [(8, 2, 8), (4, 4, 8), (8, 1, 8), (8, 2, 4)])
+def test_prefill_chunks_after_a_cached_prefix_match_the_oracle(nh, nkv, n_bits):
+    # Chunks of 16 tokens and more take the dequantise-once flash-attention path (tq_prefill.cu); fewer, the per-token
+    # kernel.  A prompt fed in pieces (40 + 33 + 7 + 100 tokens: the later pieces attend to a cached prefix; 7 < 16) must
+    # give the oracle's logits after every piece; 1, 2, 4 and 8 query heads per KV head; 8- and 4-bit caches.
+    cfg = _cfg("llama", 2, 128 * nh // 2, 512, nh, nkv, 333, 5e5, 1e-5)
+    tensors = synth_model(cfg, seed=40 + nh + nkv, awq=True)
+    eng, ref = _engines(cfg, tensors, 256, n_bits=n_bits)
+    prompt = H.rng_for("pf").integers(0, 333, 180).astype(np.uint32)
+    done = 0
+    for n in (40, 33, 7, 100):
+        a, b = eng.prefill(prompt[done:done + n]), ref.forward(prompt[done:done + n])
+        done += n
+        assert np.abs(a - b).max() <= 5e-2, (n, float(np.abs(a - b).max()))
+    a, b = eng.decode_step(5), ref.forward([5])
+    assert np.abs(a - b).max() <= 5e-2
+
+
 def test_decode_step_with_hidden_returns_the_final_norm_output():
     # MetalInference::decode_step_with_hidden (metal/pipeline.rs:176-226): logits and the vector the lm_head consumed.
     # Both decode schedules; the hidden state against the oracle's (values of order 1: 2e-2 is ~5 fp16 ulps at 2-4),

@@ -262,6 +262,37 @@ def test_encode_4bit_bit_exact(tq4, tqc4, is_k, T, base, max_seq):
 
 
 @pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 8), (8, 8), (16, 2)])
+@pytest.mark.parametrize("base,T", [(0, 16), (0, 100), (37, 50), (300, 257), (1000, 24)])
+def test_prefill_flash_attention_against_the_oracle(tq, tqc, nh, nkv, base, T):
+    """The prefill form (cached rows dequantised once, causal tensor-core pass: tq_prefill.cu) against the oracle's
+    per-token turboquant_attention, and against the per-token CUDA kernel; 4, 2, 1 and 8 query heads per KV head."""
+    max_seq = base + T + 5
+    kc, ks, kr, vc, vs = _fill_cache(tq, tqc, nkv, max_seq, base + T, seed=base + T)
+    q = H.make_x(T, nh * 128, seed=T, name="qp")
+    ref = orc.tq_attention(q, kc[0].cpu().numpy(), vc[0].cpu().numpy(), tqc, ks[0].cpu().numpy(), vs[0].cpu().numpy(), kr[0].cpu().numpy(),
+                           0.0884, nh, nkv, max_seq, base)
+    out = tq.prefill_attention(_c(q), kc, vc, ks, vs, kr, 0.0884, nh, nkv, max_seq, base).cpu().numpy().reshape(ref.shape)
+    tok = tq.attention(_c(q), kc, vc, ks, vs, kr, 0.0884, nh, nkv, max_seq, base).cpu().numpy().reshape(ref.shape)
+    e_new, e_tok = H.rel_err(out, ref), H.rel_err(tok, ref)
+    print(f"prefill attention nh {nh} nkv {nkv} base {base} T {T}: flash {e_new:.2e}, per-token kernel {e_tok:.2e}")
+    assert e_new <= 2e-3, (e_new, e_tok)
+
+
+@pytest.mark.parametrize("base,T", [(0, 40), (130, 70)])
+def test_prefill_flash_attention_4bit(tq4, tqc4, base, T):
+    nh, nkv = 16, 4
+    max_seq = base + T + 3
+    n = base + T
+    k, v = H.make_x(n, nkv * 128, n, "K4p"), H.make_x(n, nkv * 128, n, "V4p")
+    (kc, ks, kr), _, (kcd, ksd, krd) = _encode4(tq4, tqc4, k, True, nkv, max_seq, 0)
+    (vc, vs, _r), _, (vcd, vsd, _rd) = _encode4(tq4, tqc4, v, False, nkv, max_seq, 0)
+    q = H.make_x(T, nh * 128, seed=T, name="q4p")
+    ref = orc.tq_attention(q, kc, vc, tqc4, ks, vs, kr, 0.0884, nh, nkv, max_seq, base)
+    out = tq4.prefill_attention(_c(q), kcd, vcd, ksd, vsd, krd, 0.0884, nh, nkv, max_seq, base).cpu().numpy().reshape(ref.shape)
+    assert H.rel_err(out, ref) <= 2e-3
+
+
+@pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 8), (8, 8), (16, 2)])
 @pytest.mark.parametrize("ctx", [1, 33, 257, 1024, 4097])
 def test_decode_attention_4bit(tq4, tqc4, nh, nkv, ctx):
     """nh / nkv = 8 takes the f32 kernel (nibbles spread to bytes in shared memory), the others the tensor-core kernel."""
