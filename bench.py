@@ -340,11 +340,12 @@ def run_decode(args, rank, world):
                 "timing": "CUDA events around 8 back-to-back launches on the engine's stream; every launch streams all weights (> L2)",
                 "phase_us_per_layer": {k: round(v, 2) for k, v in phases.items()},
                 "largest_projection_alone": proj if args.model == "llama3_8b" else None}
-    elif args.model == "llama3_8b":
+    elif args.model == "llama3_8b" and B < 16:
         roof = dict(proj, bound="hbm", peak=peak, unit="GB/s", peak_source=peak_src, traffic=PROJ_DRAM_BYTES,
                     traffic_note="dram read+write of this launch from the ncu capture under profiles/")
     else:
-        roof = {"bound": "hbm", "kernel": "whole step (graph of per-projection kernels)", "achieved": round(step_gbs, 1), "peak": peak,
+        roof = {"bound": "hbm", "kernel": "whole step (graph of per-projection kernels; from 16 rows on the projections are tcgen05 GEMMs)",
+                "achieved": round(step_gbs, 1), "peak": peak,
                 "unit": "GB/s", "frac": round(step_gbs / peak, 4), "peak_source": peak_src, "traffic": None}
     roof["whole_step"] = {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_gbs, 1),
                           "frac_of_hbm_roofline": round(step_gbs / peak, 4),
