@@ -140,14 +140,106 @@ __device__ __forceinline__ uint4 dequant8_slow(uint32_t w, float z, float s) {  
 // measured no faster: the weight warps, not the pipeline depth, set the pace)
 // (also for the small token tiles: five stages with four activation copies in flight at 32 tokens, four with three at
 // 64, measured 20-60 % slower than three stages with two in flight on 16-64 tokens)
+// Two 256-token tiles per dequantised weight stage (512 tokens per CTA, all of tensor memory) were built and measured at
+// 2048 tokens: 2.5 us per pair of products = the 136 KB of operands a CTA then pulls per group at ~54 GB/s per SM, i.e.
+// the L2 -> SM bandwidth bounds the activation supply, not the weight warps: +5-11 % where the CTAs formed one wave
+// (o, down), -17 % where they did not (qkv); not kept.  Halving the activation bytes per product needs CTA pairs
+// (cta_group::2) that share one activation tile.
 template <int TN>
 constexpr int gemm_stages() { return TN >= 256 ? 2 : 3; }
+
+// The weight warps' work for one CTA: dequantise the groups [g_begin, g_begin + G) of rows n0 .. n0 + 127 into the A ring
+// (STAGES slots of 32 KB), one stage per group; full barriers are arrived at once per warp and stage, empty barriers
+// are waited on before a slot is reused.
+template <int BITS, int STAGES>
+__device__ __forceinline__ void gemm_weight_warps(const GemmParams &p, unsigned char *As, uint64_t *full, uint64_t *empty, int g_begin, int G, int n0,
+                                                  bool &ok) {
+    constexpr int kGStages = STAGES;
+    constexpr int kABytes = kGM * kGK * 2;
+    constexpr int kCodeVec = BITS == 4 ? 1 : 2;      // 16-byte vectors of codes per thread and stage (32 columns)
+    constexpr int kAheadA = BITS == 4 ? kGAhead : 2;  // stages of codes in flight in registers (16 registers either way)
+    const int tid = threadIdx.x, lane = tid & 31;
+    // ---------------------------------------------------------------- weights: dequantise into operand A
+    // thread = (row r, quarter q of the group): 32 columns = 16 (4-bit) or 32 (8-bit) bytes of codes per stage, four
+    // 16-byte chunks of one swizzle atom.  The codes of the next stages are requested before this stage is converted,
+    // so the memory latency is paid once.  Sixteen such warps: four per scheduler to cover each other's dependent
+    // chains (eight measured 43 % issue utilisation).
+    const int r = tid & 127, q = tid >> 7, n = n0 + r;
+    const bool live = n < p.N;
+    const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * ((size_t)p.K * BITS / 8) + (size_t)g_begin * (16 * BITS) + q * (4 * BITS);
+    const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * p.G + g_begin;
+    const uint32_t row_off = (uint32_t)((q >> 1) * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
+    const int c0 = 4 * (q & 1);  // first 16-byte chunk of this thread inside the atom's 128-byte row
+    // register ring of the next kAheadA stages' codes: 16 (4-bit) or 32 (8-bit) bytes per stage in flight per thread,
+    // enough to cover the memory latency at one stage per ~0.3 us
+    uint4 wb[kAheadA][kCodeVec];
+    __half2 szb[kAheadA];
+#pragma unroll
+    for (int u = 0; u < kAheadA; u++) {
+#pragma unroll
+        for (int v = 0; v < kCodeVec; v++) wb[u][v] = make_uint4(0, 0, 0, 0);
+        szb[u] = __floats2half2_rn(0.0f, 0.0f);
+        if (live && u < G) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)u * (16 * BITS));
+#pragma unroll
+            for (int v = 0; v < kCodeVec; v++) wb[u][v] = ldg_stream_v4(src + v);
+            szb[u] = szrow[u];
+        }
+    }
+    for (int kt0 = 0; kt0 < G; kt0 += kAheadA) {
+#pragma unroll
+        for (int u = 0; u < kAheadA; u++) {
+            const int kt = kt0 + u;
+            if (kt < G) {  // warp-uniform
+                const int s = kt % kGStages, use = kt / kGStages;
+                uint4 cw[kCodeVec];
+#pragma unroll
+                for (int v = 0; v < kCodeVec; v++) cw[v] = wb[u][v];
+                const __half2 szc = szb[u];
+                if (live && kt + kAheadA < G) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)(kt + kAheadA) * (16 * BITS));
+#pragma unroll
+                    for (int v = 0; v < kCodeVec; v++) wb[u][v] = ldg_stream_v4(src + v);
+                    szb[u] = szrow[kt + kAheadA];
+                }
+                // convert into registers first: only the eight stores wait for the slot to be free
+                const float zf = __high2float(szc), sf = __low2float(szc);
+                const bool fast = zf == rintf(zf) && zf >= -1024.0f && zf <= 1023.0f;
+                uint4 v0, v1, v2, v3;
+                // Two real branches (not a select): the f32 path costs three times the packed one and almost no group
+                // needs it.  Rows past N carry zero codes and a zero scale, which dequantise to zero.
+                if (__builtin_expect(fast, 1)) {
+                    const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szc));
+                    if (BITS == 4) {
+                        v0 = dequant8_fast(cw[0].x, c2, s2); v1 = dequant8_fast(cw[0].y, c2, s2); v2 = dequant8_fast(cw[0].z, c2, s2); v3 = dequant8_fast(cw[0].w, c2, s2);
+                    } else {
+                        v0 = dequant8b_fast(cw[0].x, cw[0].y, c2, s2); v1 = dequant8b_fast(cw[0].z, cw[0].w, c2, s2);
+                        v2 = dequant8b_fast(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, c2, s2); v3 = dequant8b_fast(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, c2, s2);
+                    }
+                } else if (BITS == 4) {
+                    v0 = dequant8_slow(cw[0].x, zf, sf); v1 = dequant8_slow(cw[0].y, zf, sf); v2 = dequant8_slow(cw[0].z, zf, sf); v3 = dequant8_slow(cw[0].w, zf, sf);
+                } else {
+                    v0 = dequant8b_slow(cw[0].x, cw[0].y, zf, sf); v1 = dequant8b_slow(cw[0].z, cw[0].w, zf, sf);
+                    v2 = dequant8b_slow(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, zf, sf); v3 = dequant8b_slow(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, zf, sf);
+                }
+                if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
+                unsigned char *dst = As + (size_t)s * kABytes + row_off;
+                const int x = r & 7;  // chunk c = columns 8c .. 8c + 7 of the atom's 64, stored at chunk c ^ (row & 7)
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 0) ^ x) << 4)) = v0;
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ x) << 4)) = v1;
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 2) ^ x) << 4)) = v2;
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 3) ^ x) << 4)) = v3;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+            }
+        }
+    }
+}
 
 template <int TN, int BITS>
 __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b) {
     constexpr int kGStages = gemm_stages<TN>();
-    constexpr int kCodeVec = BITS == 4 ? 1 : 2;      // 16-byte vectors of codes per thread and stage (32 columns)
-    constexpr int kAheadA = BITS == 4 ? kGAhead : 2;  // stages of codes in flight in registers (16 registers either way)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of every operand buffer: the swizzle is a function of the address bits
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -184,82 +276,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_int4_tc_kernel(const GemmPa
     const int G = min(p.G, g_begin + p.gps) - g_begin;  // this CTA's groups (stages), >= 1 by construction of the grid
     bool ok = true;
     if (warp < kGWarpsA) {
-        // ---------------------------------------------------------------- weights: dequantise into operand A
-        // thread = (row r, quarter q of the group): 32 columns = 16 (4-bit) or 32 (8-bit) bytes of codes per stage, four
-        // 16-byte chunks of one swizzle atom.  The codes of the next stages are requested before this stage is converted,
-        // so the memory latency is paid once.  Sixteen such warps: four per scheduler to cover each other's dependent
-        // chains (eight measured 43 % issue utilisation).
-        const int r = tid & 127, q = tid >> 7, n = n0 + r;
-        const bool live = n < p.N;
-        const uint8_t *crow = p.codes + (size_t)(live ? n : 0) * ((size_t)p.K * BITS / 8) + (size_t)g_begin * (16 * BITS) + q * (4 * BITS);
-        const __half2 *szrow = p.sz + (size_t)(live ? n : 0) * p.G + g_begin;
-        const uint32_t row_off = (uint32_t)((q >> 1) * (kGM * 128) + (r >> 3) * 1024 + (r & 7) * 128);
-        const int c0 = 4 * (q & 1);  // first 16-byte chunk of this thread inside the atom's 128-byte row
-        // register ring of the next kAheadA stages' codes: 16 (4-bit) or 32 (8-bit) bytes per stage in flight per thread,
-        // enough to cover the memory latency at one stage per ~0.3 us
-        uint4 wb[kAheadA][kCodeVec];
-        __half2 szb[kAheadA];
-#pragma unroll
-        for (int u = 0; u < kAheadA; u++) {
-#pragma unroll
-            for (int v = 0; v < kCodeVec; v++) wb[u][v] = make_uint4(0, 0, 0, 0);
-            szb[u] = __floats2half2_rn(0.0f, 0.0f);
-            if (live && u < G) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)u * (16 * BITS));
-#pragma unroll
-                for (int v = 0; v < kCodeVec; v++) wb[u][v] = ldg_stream_v4(src + v);
-                szb[u] = szrow[u];
-            }
-        }
-        for (int kt0 = 0; kt0 < G; kt0 += kAheadA) {
-#pragma unroll
-            for (int u = 0; u < kAheadA; u++) {
-                const int kt = kt0 + u;
-                if (kt < G) {  // warp-uniform
-                    const int s = kt % kGStages, use = kt / kGStages;
-                    uint4 cw[kCodeVec];
-#pragma unroll
-                    for (int v = 0; v < kCodeVec; v++) cw[v] = wb[u][v];
-                    const __half2 szc = szb[u];
-                    if (live && kt + kAheadA < G) {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(crow + (size_t)(kt + kAheadA) * (16 * BITS));
-#pragma unroll
-                        for (int v = 0; v < kCodeVec; v++) wb[u][v] = ldg_stream_v4(src + v);
-                        szb[u] = szrow[kt + kAheadA];
-                    }
-                    // convert into registers first: only the eight stores wait for the slot to be free
-                    const float zf = __high2float(szc), sf = __low2float(szc);
-                    const bool fast = zf == rintf(zf) && zf >= -1024.0f && zf <= 1023.0f;
-                    uint4 v0, v1, v2, v3;
-                    // Two real branches (not a select): the f32 path costs three times the packed one and almost no group
-                    // needs it.  Rows past N carry zero codes and a zero scale, which dequantise to zero.
-                    if (__builtin_expect(fast, 1)) {
-                        const __half2 c2 = __float2half2_rn(1024.0f + zf), s2 = __half2half2(__low2half(szc));
-                        if (BITS == 4) {
-                            v0 = dequant8_fast(cw[0].x, c2, s2); v1 = dequant8_fast(cw[0].y, c2, s2); v2 = dequant8_fast(cw[0].z, c2, s2); v3 = dequant8_fast(cw[0].w, c2, s2);
-                        } else {
-                            v0 = dequant8b_fast(cw[0].x, cw[0].y, c2, s2); v1 = dequant8b_fast(cw[0].z, cw[0].w, c2, s2);
-                            v2 = dequant8b_fast(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, c2, s2); v3 = dequant8b_fast(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, c2, s2);
-                        }
-                    } else if (BITS == 4) {
-                        v0 = dequant8_slow(cw[0].x, zf, sf); v1 = dequant8_slow(cw[0].y, zf, sf); v2 = dequant8_slow(cw[0].z, zf, sf); v3 = dequant8_slow(cw[0].w, zf, sf);
-                    } else {
-                        v0 = dequant8b_slow(cw[0].x, cw[0].y, zf, sf); v1 = dequant8b_slow(cw[0].z, cw[0].w, zf, sf);
-                        v2 = dequant8b_slow(cw[kCodeVec - 1].x, cw[kCodeVec - 1].y, zf, sf); v3 = dequant8b_slow(cw[kCodeVec - 1].z, cw[kCodeVec - 1].w, zf, sf);
-                    }
-                    if (ok && use > 0 && !mbar_wait_warp(&empty[s], (use - 1) & 1, p.err)) ok = false;
-                    unsigned char *dst = As + (size_t)s * kABytes + row_off;
-                    const int x = r & 7;  // chunk c = columns 8c .. 8c + 7 of the atom's 64, stored at chunk c ^ (row & 7)
-                    *reinterpret_cast<uint4 *>(dst + (((c0 + 0) ^ x) << 4)) = v0;
-                    *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ x) << 4)) = v1;
-                    *reinterpret_cast<uint4 *>(dst + (((c0 + 2) ^ x) << 4)) = v2;
-                    *reinterpret_cast<uint4 *>(dst + (((c0 + 3) ^ x) << 4)) = v3;
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full[s]);
-                }
-            }
-        }
+        gemm_weight_warps<BITS, kGStages>(p, As, full, empty, g_begin, G, n0, ok);
     } else if (warp == kGWarpsA) {
         // ---------------------------------------------------------------- activations: TMA into operand B
         // One thread per stage: wait for the slot, announce the bytes on the stage's full barrier and issue the two
@@ -386,6 +403,20 @@ static TmapEncodeFn tmap_encode_fn() {
     return fn;
 }
 
+// activations [M, K] fp16 row-major as a 2-D tensor: inner dimension K, boxes of 64 columns x `rows` rows, 128-byte swizzle
+static int make_act_tmap(const GemmParams &p, int rows, CUtensorMap *tmap) {
+    TmapEncodeFn enc = tmap_encode_fn();
+    if (!enc) return fail(IM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)p.K * sizeof(__half)};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)rows};
+    const cuuint32_t estride[2] = {1u, 1u};
+    const CUresult cr = enc(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(p.xs), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(IM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for activations [%d, %d]", (int)cr, p.M, p.K);
+    return IM_OK;
+}
+
 template <int TN, int BITS>
 int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     constexpr int kGStages = gemm_stages<TN>();
@@ -394,17 +425,8 @@ int gemm_launch(const GemmParams &p, const Device *dev, cudaStream_t st) {
     auto kern = gemm_int4_tc_kernel<TN, BITS>;
     static DeviceOnce once;  // per instantiation
     if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    // activations [M, K] fp16 row-major as a 2-D tensor: inner dimension K, boxes of 64 columns x TN rows, 128-byte swizzle
-    TmapEncodeFn enc = tmap_encode_fn();
-    if (!enc) return fail(IM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     alignas(64) CUtensorMap tmap;
-    const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
-    const cuuint64_t gstride[1] = {(cuuint64_t)p.K * sizeof(__half)};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)TN};
-    const cuuint32_t estride[2] = {1u, 1u};
-    const CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(p.xs), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) return fail(IM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for activations [%d, %d]", (int)cr, p.M, p.K);
+    if (const int trc = make_act_tmap(p, TN, &tmap); trc != IM_OK) return trc;
     const int splits = (p.G + p.gps - 1) / p.gps;
     dim3 grid((p.N + kGM - 1) / kGM, (p.M + TN - 1) / TN, splits);
     IM_CUDA_CHECK(launch_k(kern, grid, dim3(kGThreads), smem, st, p, tmap));

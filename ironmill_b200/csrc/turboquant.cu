@@ -142,6 +142,9 @@ __global__ void __launch_bounds__(kAttnThreads) tq_attention_kernel(const AttnPa
 }
 
 // One launch between the QKV projection and the attention: grid (nseq*T, nh + 2 nkv), hd = 128 threads.
+// (Tried for prefill chunks: 16 tokens per CTA with the QJL matrix held in 64 KB of shared memory instead of 64 KB read
+// from L2 per (token, head): three resident CTAs per SM do not hide the per-token chain of block barriers; 2048-token
+// prefill 71 -> 81 ms.  Sixteen small CTAs per SM, as here, do.)
 template <int BITS>
 __global__ void __launch_bounds__(kHd) tq_qkv_prep_kernel(const PrepArgs a_in) {
     __shared__ float sh[3 * kHd + 4];
@@ -634,7 +637,8 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
     k.ktab = EncodeTables{tq->signs, tq->k_cb, tq->k_bd, tq->qjl_t, tq->k_levels, 1, tq->n_bits};
     k.vtab = EncodeTables{tq->signs, tq->v_cb, tq->v_bd, tq->qjl_t, tq->v_levels, 0, tq->n_bits};
     k.kc = a.kc; k.vc = a.vc; k.ks = a.ks; k.vs = a.vs; k.krn = a.krn;
-    dim3 grid(a.nseq * a.T, a.nh + 2 * a.nkv);
+    const int tokens = a.nseq * a.T;
+    dim3 grid(tokens, a.nh + 2 * a.nkv);
     IM_CUDA_CHECK(launch_k(tq->n_bits == 4 ? tq_qkv_prep_kernel<4> : tq_qkv_prep_kernel<8>, grid, dim3(kHd), 0, st, k));
     return IM_OK;
 }
