@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(GQ * 32, GQ == 8 ? 1 : 2) tq_prefill_attention
     unsigned char *vt = kt + 2 * kPfN * kKRowB;                // [2][32][272]
     float *sc = reinterpret_cast<float *>(vt + 2 * kPfN * kVRowB);  // [2][3][32]: ks, r_norm * qjl_factor, vs of the tile's positions
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int tb = blockIdx.x, kvh = blockIdx.y;
+    const int tb = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;  // the latest tokens attend to the most positions: longest CTAs first
     pdl_trigger();
     pdl_wait();
     const int P = p.base_pos + (p.pos_dev ? p.pos_dev[p.slot] : 0);
