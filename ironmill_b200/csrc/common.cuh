@@ -213,7 +213,8 @@ int tq_reduce_launch(const Tq *tq, const float *po, const float *pm, const float
 size_t tq_prefill_scratch_bytes(int nkv, int max_seq);
 int tq_prefill_attention_launch(const Tq *tq, float *partials, void *dq, const float *qrot, const uint8_t *kc, const uint8_t *vc, const float *ks,
                                 const float *vs, const float *krn, float attn_scale, __half *out, int slot, int nh, int nkv, int max_seq,
-                                const int *pos_dev, int T, int ctx_end, cudaStream_t st, int base_pos = 0);
+                                const int *pos_dev, int T, int ctx_end, cudaStream_t st, int base_pos = 0, bool project_queries = true);
+bool tq_prefill_takes(int nh, int nkv);  // head groupings the prefill pass is built for
 // Inputs of the fused RoPE + cache write + query rotation launch (turboquant.cu).
 struct TqPrep {
     const __half *qkv;  // [nseq*T, stride]: q | k | v of one token
@@ -229,6 +230,7 @@ struct TqPrep {
     __half *q_out;  // optional out [nseq*T, nh, hd]
     uint8_t *kc, *vc;
     float *ks, *vs, *krn;
+    int no_q_proj = 0;  // query heads: leave S * (rotated query) to the consumer (the prefill attention pass projects it itself)
 };
 int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st);
 int tq_attention_launch(const Tq *tq, float *scratch, const __half *q, const uint8_t *kc, const uint8_t *vc, const float *ks,

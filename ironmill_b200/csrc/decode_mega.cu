@@ -700,7 +700,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                 a.base_pos = seq_len - 1; a.eps = p.eps; a.pos_dev = nullptr; a.slot_map = nullptr; a.qrot = p.qrot; a.q_out = nullptr;  // the position was read once at the start
                 a.ktab = EncodeTables{p.signs, cbk, bdk, p.qjl_t, p.k_levels, 1, BITS};
                 a.vtab = EncodeTables{p.signs, cbv, bdv, p.qjl_t, p.v_levels, 0, BITS};
-                a.kc = ly.kc; a.vc = ly.vc; a.ks = ly.ks; a.vs = ly.vs; a.krn = ly.krn;
+                a.kc = ly.kc; a.vc = ly.vc; a.ks = ly.ks; a.vs = ly.vs; a.krn = ly.krn; a.no_q_proj = 0;
                 float *sh = reinterpret_cast<float *>(U);
                 QjlCoop pj{sv, sh + 3 * kHd + 4};
                 if (!dead)

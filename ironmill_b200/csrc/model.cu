@@ -552,8 +552,14 @@ static int attention_block(Model *m, int part, const TqPrep &a, __half *q_buf, L
         return kv16_attention_launch(m->dev, m->kv16_scratch, m->kv16_scratch_bytes, q_buf, a.stride, k.kc, k.vc, attn_scale, m->attn_out, nseq, a.nh,
                                      a.nkv, c.max_seq_len, 0, m->pos_dev, T, 0, c.max_seq_len, st, slots);
     }
-    if (part == 0) return tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), a, st);
-    if (nseq == 1 && T >= 16 && m->pf_dq && m->prefill_slot_id >= 0) {  // a prefill chunk: dequantise once, flash attention
+    // a prefill chunk of one sequence: dequantise the cached rows once, causal tensor-core pass (which also projects the queries)
+    const bool flash = nseq == 1 && T >= 16 && m->pf_dq && m->prefill_slot_id >= 0 && tq_prefill_takes(a.nh, a.nkv);
+    if (part == 0) {
+        TqPrep b = a;
+        b.no_q_proj = flash ? 1 : 0;
+        return tq_prep_launch(reinterpret_cast<const Tq *>(m->tq), b, st);
+    }
+    if (flash) {
         const int rc = tq_prefill_attention_launch(reinterpret_cast<const Tq *>(m->tq), m->scratch_ref, m->pf_dq, m->qrot, L.kc, L.vc, L.ks, L.vs, L.krn,
                                                    attn_scale, m->attn_out, m->prefill_slot_id, a.nh, a.nkv, c.max_seq_len, m->pos_dev, T,
                                                    m->prefill_ctx_end, st);

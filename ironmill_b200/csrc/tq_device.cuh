@@ -516,6 +516,7 @@ struct PrepArgs {
     EncodeTables ktab, vtab;
     uint8_t *kc, *vc;
     float *ks, *vs, *krn;
+    int no_q_proj;  // query heads: skip the QJL projection (its consumer computes it)
 };
 
 // One head (slot in [0, nh + 2 nkv)) of token st on a 128-thread scope.  sh: 3*128 + 4 floats.  pj: the QJL
@@ -575,6 +576,7 @@ __device__ __forceinline__ void tq_prep_item(const Scope &sc, const PrepArgs &a,
     float *dst = a.qrot + ((size_t)st * a.nh + h) * 2 * kHd;
     dst[d] = rq;
     sc.sync();
+    if (a.no_q_proj) return;
     pj.begin(d, kHd);
     const float acc = pj.template finish<false>(sc, sh, d, kHd);
     dst[kHd + d] = acc;

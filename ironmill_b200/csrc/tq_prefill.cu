@@ -86,7 +86,8 @@ __device__ __forceinline__ unsigned pack2h(float a, float b) {
 }
 
 struct PrefillParams {
-    const float *qrot;         // [T, nh, 2, 128]: rotated query, S * rotated query
+    const float *qrot;         // [T, nh, 2, 128]: rotated query, S * rotated query (the second half is not read when qjl_t is given)
+    const float *qjl_t;        // optional: the transposed QJL matrix [k][d] f32; the kernel then projects the rotated queries itself
     const __half *kd, *vd;     // [nkv][npos][256], [nkv][npos][128]
     const float *ks, *vs, *krn;  // cache side arrays [slots, nkv, max_seq]
     float *po, *pm, *pl;       // partials, one split: [T * nh] x (128 | 1 | 1)
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(GQ * 32, GQ == 8 ? 1 : 2) tq_prefill_attention
         const int r = i >> 5, c8 = i & 31;  // 8 values per item
         const int tok = tb * kPfTok + r / GQ, h = kvh * GQ + r % GQ;
         uint4 v = make_uint4(0, 0, 0, 0);
+        if (p.qjl_t && c8 >= 16) continue;  // S q~ is computed below
         if (tok < p.T) {
             const float *src = p.qrot + ((size_t)tok * p.nh + h) * 256 + 8 * c8;
             const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
@@ -152,6 +154,39 @@ __global__ void __launch_bounds__(GQ * 32, GQ == 8 ? 1 : 2) tq_prefill_attention
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
+    const unsigned qs_a = (unsigned)__cvta_generic_to_shared(qs + (warp * 16 + (lane & 15)) * kKRowB + (lane >> 4) * 16);
+    if (p.qjl_t) {
+        // S q~ for this block's rows on the tensor cores: [16 rows x 128] x S^T [128 x 128] per warp, the matrix as fp16 in
+        // the (still empty) tile buffers, rows of 272 bytes.  The per-(token, head) launch that otherwise does this reads
+        // the 64 KB matrix from L2 once per row: a sixth of a 2048-token prefill.  fp16 operands like every other product
+        // of this kernel; the result is rounded to fp16 as the score products read it.
+        unsigned char *stm = kt;  // 128 rows x 272 bytes <= the K' and V' tile buffers together
+        for (int i = tid; i < kHd * 16; i += NT) {
+            const int k = i >> 4, c = i & 15;
+            const float4 a = *reinterpret_cast<const float4 *>(p.qjl_t + k * kHd + 8 * c), b = *reinterpret_cast<const float4 *>(p.qjl_t + k * kHd + 8 * c + 4);
+            *reinterpret_cast<uint4 *>(stm + k * kVRowB + 16 * c) = make_uint4(pack2h(a.x, a.y), pack2h(a.z, a.w), pack2h(b.x, b.y), pack2h(b.z, b.w));
+        }
+        __syncthreads();
+        const unsigned st_a = (unsigned)__cvta_generic_to_shared(stm + (lane & 15) * kVRowB + (lane >> 4) * 16);
+#pragma unroll 1
+        for (int nd = 0; nd < 16; nd += 2) {
+            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                unsigned a[4], b[4];
+                ldsm_x4(a, qs_a + kk * 32);
+                ldsm_x4_t(b, st_a + kk * 16 * kVRowB + nd * 16);
+                mma16816(c0, a[0], a[1], a[2], a[3], b[0], b[1]);
+                mma16816(c1, a[0], a[1], a[2], a[3], b[2], b[3]);
+            }
+            unsigned char *r0p = qs + (warp * 16 + g) * kKRowB + 256 + (8 * nd + 2 * t) * 2, *r1p = r0p + 8 * kKRowB;
+            *reinterpret_cast<unsigned *>(r0p) = pack2h(c0[0], c0[1]);
+            *reinterpret_cast<unsigned *>(r1p) = pack2h(c0[2], c0[3]);
+            *reinterpret_cast<unsigned *>(r0p + 16) = pack2h(c1[0], c1[1]);
+            *reinterpret_cast<unsigned *>(r1p + 16) = pack2h(c1[2], c1[3]);
+        }
+        __syncthreads();  // the matrix is no longer needed: the tile copies may overwrite it
+    }
     // this thread's two score rows: g and g + 8 of the warp's 16
     const int row0 = warp * 16 + g, row1 = row0 + 8;
     const int tok0 = tb * kPfTok + row0 / GQ, tok1 = tb * kPfTok + row1 / GQ;
@@ -160,7 +195,6 @@ __global__ void __launch_bounds__(GQ * 32, GQ == 8 ? 1 : 2) tq_prefill_attention
     float o[16][4];
 #pragma unroll
     for (int i = 0; i < 16; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    const unsigned qs_a = (unsigned)__cvta_generic_to_shared(qs + (warp * 16 + (lane & 15)) * kKRowB + (lane >> 4) * 16);
 
     if (ntiles > 0) load_tile(0, 0);
     for (int it = 0; it < ntiles; it++) {
@@ -290,6 +324,12 @@ int pf_launch(const PrefillParams &p, const Device *dev, cudaStream_t st) {
 
 }  // namespace
 
+bool tq_prefill_takes(int nh, int nkv) {
+    if (nkv <= 0 || nh % nkv != 0) return false;
+    const int gq = nh / nkv;
+    return gq == 1 || gq == 2 || gq == 4 || gq == 8;
+}
+
 size_t tq_prefill_scratch_bytes(int nkv, int max_seq) { return (size_t)nkv * max_seq * (256 + 128) * sizeof(__half); }
 
 // One sequence's prefill chunk: T tokens whose rows are already in the cache at positions pos_dev[slot] .. + T - 1;
@@ -297,7 +337,7 @@ size_t tq_prefill_scratch_bytes(int nkv, int max_seq) { return (size_t)nkv * max
 // floats; dq: tq_prefill_scratch_bytes(nkv, max_seq).  IM_ERR_BOUNDS when the head grouping is not 1, 2, 4 or 8.
 int tq_prefill_attention_launch(const Tq *tq, float *partials, void *dq, const float *qrot, const uint8_t *kc, const uint8_t *vc, const float *ks,
                                 const float *vs, const float *krn, float attn_scale, __half *out, int slot, int nh, int nkv, int max_seq,
-                                const int *pos_dev, int T, int ctx_end, cudaStream_t st, int base_pos) {
+                                const int *pos_dev, int T, int ctx_end, cudaStream_t st, int base_pos, bool project_queries) {
     if (nkv <= 0 || nh % nkv != 0 || T <= 0) return IM_ERR_BOUNDS;
     const int gq = nh / nkv;
     if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return IM_ERR_BOUNDS;
@@ -311,7 +351,7 @@ int tq_prefill_attention_launch(const Tq *tq, float *partials, void *dq, const f
         IM_CUDA_CHECK(launch_k(tq_dequant_rows_kernel<8>, dgrid, dim3(256), 0, st, kc, vc, (const float *)tq->k_cb, (const float *)tq->v_cb, kd, vd, slot, nkv,
                                max_seq, npos));
     PrefillParams p{};
-    p.qrot = qrot; p.kd = kd; p.vd = vd; p.ks = ks; p.vs = vs; p.krn = krn;
+    p.qrot = qrot; p.qjl_t = project_queries ? tq->qjl_t : nullptr; p.kd = kd; p.vd = vd; p.ks = ks; p.vs = vs; p.krn = krn;
     const size_t rows = (size_t)T * nh;
     p.po = partials; p.pm = partials + rows * kHd; p.pl = p.pm + rows;
     p.pos_dev = pos_dev; p.attn_scale = attn_scale; p.qjl_factor = sqrtf(2.0f / 3.14159265f) / (float)tq->hd;

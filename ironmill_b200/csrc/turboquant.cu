@@ -633,7 +633,7 @@ int tq_prep_launch(const Tq *tq, const TqPrep &a, cudaStream_t st) {
     k.qw = a.qw; k.kw = a.kw; k.cosc = a.cosc; k.sinc = a.sinc;
     k.nh = a.nh; k.nkv = a.nkv; k.rotary_dim = a.rotary_dim ? a.rotary_dim : kHd; k.with_norm = a.with_norm;
     k.T = a.T; k.max_seq = a.max_seq; k.base_pos = a.base_pos; k.eps = a.eps; k.pos_dev = a.pos_dev; k.slot_map = a.slot_map;
-    k.qrot = a.qrot; k.q_out = a.q_out;
+    k.qrot = a.qrot; k.q_out = a.q_out; k.no_q_proj = a.no_q_proj;
     k.ktab = EncodeTables{tq->signs, tq->k_cb, tq->k_bd, tq->qjl_t, tq->k_levels, 1, tq->n_bits};
     k.vtab = EncodeTables{tq->signs, tq->v_cb, tq->v_bd, tq->qjl_t, tq->v_levels, 0, tq->n_bits};
     k.kc = a.kc; k.vc = a.vc; k.ks = a.ks; k.vs = a.vs; k.krn = a.krn;
