@@ -256,7 +256,7 @@ size_t kv16_scratch_bytes(int tokens, int nh, int splits);
 int kv16_auto_splits(const Device *dev, int tokens, int nkv, int max_ctx);
 int kv16_attention_launch(const Device *dev, float *scratch, size_t scratch_bytes, const __half *q, int q_stride, const __half *kc, const __half *vc,
                           float scale, __half *out, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, int splits,
-                          int ctx_hint, cudaStream_t st, const int *slot_map);
+                          int ctx_hint, cudaStream_t st, const int *slot_map, int prefill_slot = -1);  // prefill_slot >= 0: one sequence in that cache slot
 
 }  // namespace im
 

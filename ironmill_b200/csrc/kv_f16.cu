@@ -7,8 +7,9 @@
 // All of them compute softmax(scale * q . K^T) V with fp16 inputs, f32 scores / online softmax / accumulation and one
 // fp16 rounding of the output; they differ in tiling only.  Here one kernel covers them: a warp per query head walks
 // its share of the cached positions in tiles of 32 (lane = position for the scores, lane = four dimensions for the
-// weighted sum), the query heads of a KV head share a CTA (their K / V rows meet in L1), grid z splits the positions
-// of long contexts and a reduction kernel combines the splits exactly as fused_sdpa_reduce does.
+// weighted sum), the query heads of a KV head share a CTA (their K / V tiles are staged once in shared memory), grid z
+// splits the positions of long contexts and a reduction kernel combines the splits exactly as fused_sdpa_reduce does.
+// Prefill chunks of one sequence (16 tokens and more) take a causal tensor-core pass instead (sdpa16_prefill_kernel).
 #include <algorithm>
 
 #include "common.cuh"
@@ -200,6 +201,169 @@ __global__ void __launch_bounds__(GQ * 32) sdpa16_kernel(const Sdpa16 p) {
     }
 }
 
+// ---- prefill chunks of one sequence (prefill_attention_v2, attention.metal:571-750): causal flash attention on the
+// tensor cores.  A CTA owns 16 consecutive tokens of one KV head = 16 * GQ score rows (row = token * GQ + head), one warp
+// per 16 rows (mma.sync m16n8k16, operands by ldmatrix); K / V tiles of 32 cached rows by 16-byte cp.async into
+// shared-memory rows 272 bytes apart, two tiles in flight.  fp16 operands (the cache and the queries are fp16 already; the
+// softmax weights are rounded to fp16 for the second product), f32 scores, sums and outputs.
+constexpr int kPf16Tok = 16, kPf16N = 32, kPf16Row = 272;
+__device__ __forceinline__ void mma16816_f(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ unsigned pack_h2f(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const unsigned *>(&h);
+}
+
+// grid (ceil(T / 16), nkv); block GQ warps; one sequence (cache slot `slot`), T tokens at positions P .. P + T - 1.
+template <int GQ>
+__global__ void __launch_bounds__(GQ * 32, GQ == 8 ? 1 : 2) sdpa16_prefill_kernel(const Sdpa16 p, int slot) {
+    constexpr int M = kPf16Tok * GQ, NT = GQ * 32;
+    extern __shared__ __align__(16) unsigned char pf16_smem[];
+    unsigned char *qs = pf16_smem;                      // [M][272]
+    unsigned char *kt = qs + M * kPf16Row;              // [2][32][272]
+    unsigned char *vt = kt + 2 * kPf16N * kPf16Row;     // [2][32][272]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int tb = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;  // longest (latest) token blocks first
+    pdl_trigger();
+    pdl_wait();
+    const int P = p.base_pos + (p.pos_dev ? p.pos_dev[slot] : 0);
+    for (int i = tid; i < M * 16; i += NT) {
+        const int r = i >> 4, c = i & 15;
+        const int tok = tb * kPf16Tok + r / GQ, h = kvh * GQ + r % GQ;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok < p.T) v = *reinterpret_cast<const uint4 *>(p.q + (size_t)tok * p.q_stride + (size_t)h * kHd16 + 8 * c);
+        *reinterpret_cast<uint4 *>(qs + r * kPf16Row + 16 * c) = v;
+    }
+    const int last_tok = min(tb * kPf16Tok + kPf16Tok - 1, p.T - 1);
+    const int n_end = min(P + last_tok + 1, p.max_seq);
+    const int ntiles = (n_end + kPf16N - 1) / kPf16N;
+    const size_t cache_base = ((size_t)slot * p.nkv + kvh) * p.max_seq * kHd16;
+    auto load_tile = [&](int buf, int tile) {
+        const int p0 = tile * kPf16N;
+        for (int i = tid; i < kPf16N * 16; i += NT) {
+            const int r = i >> 4, c = i & 15;
+            const size_t src = cache_base + (size_t)min(p0 + r, n_end - 1) * kHd16 + 8 * c;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(kt + (buf * kPf16N + r) * kPf16Row + 16 * c)), "l"(p.kc + src) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(vt + (buf * kPf16N + r) * kPf16Row + 16 * c)), "l"(p.vc + src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int row0 = warp * 16 + g, row1 = row0 + 8;
+    const int tok0 = tb * kPf16Tok + row0 / GQ, tok1 = tb * kPf16Tok + row1 / GQ;
+    const int lim0 = tok0 < p.T ? P + tok0 : -1, lim1 = tok1 < p.T ? P + tok1 : -1;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const unsigned qs_a = (unsigned)__cvta_generic_to_shared(qs + (warp * 16 + (lane & 15)) * kPf16Row + (lane >> 4) * 16);
+    if (ntiles > 0) load_tile(0, 0);
+    for (int it = 0; it < ntiles; it++) {
+        const int buf = it & 1, p0 = it * kPf16N;
+        if (it + 1 < ntiles) {
+            load_tile(buf ^ 1, it + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        float sc[4][4];
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f;
+        const unsigned kt_a = (unsigned)__cvta_generic_to_shared(kt + (buf * kPf16N + (lane & 7) + 8 * (lane >> 4)) * kPf16Row + ((lane >> 3) & 1) * 16);
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+            unsigned a[4], b01[4], b23[4];
+            ldsm4(a, qs_a + kk * 32);
+            ldsm4(b01, kt_a + kk * 32);
+            ldsm4(b23, kt_a + 16 * kPf16Row + kk * 32);
+            mma16816_f(sc[0], a[0], a[1], a[2], a[3], b01[0], b01[1]);
+            mma16816_f(sc[1], a[0], a[1], a[2], a[3], b01[2], b01[3]);
+            mma16816_f(sc[2], a[0], a[1], a[2], a[3], b23[0], b23[1]);
+            mma16816_f(sc[3], a[0], a[1], a[2], a[3], b23[2], b23[3]);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int pos = p0 + 8 * nb + 2 * t + (e & 1);
+                const int lim = (e < 2) ? lim0 : lim1;
+                sc[nb][e] = (pos <= lim && pos < n_end) ? sc[nb][e] * p.scale : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], sc[nb][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            corr[r] = m_new == -INFINITY ? 1.0f : __expf(m_run[r] - m_new);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        unsigned pa[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                w[e] = sc[nb][e] == -INFINITY ? 0.0f : __expf(sc[nb][e] - m_run[e >> 1]);
+                l_run[e >> 1] += w[e];
+            }
+            pa[nb >> 1][(nb & 1) * 2 + 0] = pack_h2f(w[0], w[1]);
+            pa[nb >> 1][(nb & 1) * 2 + 1] = pack_h2f(w[2], w[3]);
+        }
+#pragma unroll
+        for (int kb = 0; kb < 2; kb++) {
+            const unsigned vt_a = (unsigned)__cvta_generic_to_shared(vt + (buf * kPf16N + 16 * kb + (lane & 15)) * kPf16Row + (lane >> 4) * 16);
+#pragma unroll
+            for (int nd = 0; nd < 16; nd += 2) {
+                unsigned b[4];
+                ldsm4_t(b, vt_a + nd * 16);
+                mma16816_f(o[nd], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b[0], b[1]);
+                mma16816_f(o[nd + 1], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+        const int row = r == 0 ? row0 : row1, tok = r == 0 ? tok0 : tok1;
+        if (tok < p.T) {
+            const float inv = 1.0f / fmaxf(l_run[r], 1e-10f);
+            __half *dst = p.out + ((size_t)tok * p.nh + kvh * GQ + row % GQ) * kHd16;
+#pragma unroll
+            for (int nd = 0; nd < 16; nd++) *reinterpret_cast<unsigned *>(dst + 8 * nd + 2 * t) = pack_h2f(o[nd][2 * r] * inv, o[nd][2 * r + 1] * inv);
+        }
+    }
+}
+
+template <int GQ>
+static int sdpa16_prefill_launch(const Sdpa16 &p, int slot, const Device *dev, cudaStream_t st) {
+    constexpr size_t smem = (size_t)kPf16Tok * GQ * kPf16Row + 4 * kPf16N * kPf16Row;
+    auto kern = sdpa16_prefill_kernel<GQ>;
+    static DeviceOnce once;
+    if (once.first(dev->ordinal)) IM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    IM_CUDA_CHECK(launch_k(kern, dim3((p.T + kPf16Tok - 1) / kPf16Tok, p.nkv), dim3(GQ * 32), smem, st, p, slot));
+    return IM_OK;
+}
+
 // fused_sdpa_reduce (flash_decode.metal:163-215): global max over the splits, rescale, normalise, fp16.
 __global__ void __launch_bounds__(kHd16) sdpa16_reduce_kernel(const float *__restrict__ po, const float *__restrict__ pm, const float *__restrict__ pl,
                                                               __half *__restrict__ out, int splits) {
@@ -241,12 +405,23 @@ int kv16_prep_launch(const Kv16Prep &a, cudaStream_t st) {
 
 int kv16_attention_launch(const Device *dev, float *scratch, size_t scratch_bytes, const __half *q, int q_stride, const __half *kc, const __half *vc,
                           float scale, __half *out, int nseq, int nh, int nkv, int max_seq, int base_pos, const int *pos_dev, int T, int splits,
-                          int ctx_hint, cudaStream_t st, const int *slot_map) {
+                          int ctx_hint, cudaStream_t st, const int *slot_map, int prefill_slot) {
     const int tokens = nseq * T;
     if (tokens == 0) return IM_OK;
     if (nkv <= 0 || nh % nkv != 0) return fail(IM_ERR_INVALID, "nh must be a multiple of nkv");
     const int gq = nh / nkv;
     if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return fail(IM_ERR_INVALID, "fp16-KV attention is built for 1, 2, 4 or 8 query heads per KV head (got %d)", gq);
+    if (nseq == 1 && T >= 16 && prefill_slot >= 0) {  // a prefill chunk of one sequence (cache slot known to the host): the tensor-core pass
+        Sdpa16 f{};
+        f.q = q; f.q_stride = q_stride; f.kc = kc; f.vc = vc; f.out = out; f.nh = nh; f.nkv = nkv; f.T = T; f.max_seq = max_seq;
+        f.base_pos = base_pos; f.pos_dev = pos_dev; f.scale = scale; f.splits = 1;
+        switch (gq) {
+        case 1: return sdpa16_prefill_launch<1>(f, prefill_slot, dev, st);
+        case 2: return sdpa16_prefill_launch<2>(f, prefill_slot, dev, st);
+        case 4: return sdpa16_prefill_launch<4>(f, prefill_slot, dev, st);
+        default: return sdpa16_prefill_launch<8>(f, prefill_slot, dev, st);
+        }
+    }
     if (splits <= 0) splits = kv16_auto_splits(dev, tokens, nkv, ctx_hint > 0 ? ctx_hint : max_seq);
     while (splits > 1 && kv16_scratch_bytes(tokens, nh, splits) > scratch_bytes) splits--;
     Sdpa16 p{};
@@ -301,6 +476,6 @@ IM_EXPORT int im_cuda_sdpa_f16(im_device *dev, const void *q_dev, const void *k_
                                      static_cast<const __half *>(k_cache_dev), static_cast<const __half *>(v_cache_dev), scale,
                                      static_cast<__half *>(out_dev), nseq, nh, nkv, max_seq, base_pos, pos_dev, T, num_splits,
                                      pos_dev ? max_seq : base_pos + T,  // positions on the device: the cache length bounds the context
-                                     im::as_stream(stream), nullptr);
+                                     im::as_stream(stream), nullptr, nseq == 1 ? 0 : -1);
     IM_GUARD_END
 }

@@ -550,7 +550,7 @@ static int attention_block(Model *m, int part, const TqPrep &a, __half *q_buf, L
         k.slot_map = slots; k.kc = reinterpret_cast<__half *>(L.kc); k.vc = reinterpret_cast<__half *>(L.vc);
         if (part == 0) return kv16_prep_launch(k, st);
         return kv16_attention_launch(m->dev, m->kv16_scratch, m->kv16_scratch_bytes, q_buf, a.stride, k.kc, k.vc, attn_scale, m->attn_out, nseq, a.nh,
-                                     a.nkv, c.max_seq_len, 0, m->pos_dev, T, 0, c.max_seq_len, st, slots);
+                                     a.nkv, c.max_seq_len, 0, m->pos_dev, T, 0, c.max_seq_len, st, slots, nseq == 1 ? m->prefill_slot_id : -1);
     }
     // a prefill chunk of one sequence: dequantise the cached rows once, causal tensor-core pass (which also projects the queries)
     const bool flash = nseq == 1 && T >= 16 && m->pf_dq && m->prefill_slot_id >= 0 && tq_prefill_takes(a.nh, a.nkv);

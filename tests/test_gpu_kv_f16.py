@@ -62,6 +62,20 @@ def test_prefill_is_causal_and_batched_sequences_use_their_own_positions(dev):
         assert H.rel_err(outb[i:i + 1], refi) <= TOL, i
 
 
+@pytest.mark.parametrize("nh,nkv", [(4, 4), (4, 2), (8, 2), (8, 1)])
+@pytest.mark.parametrize("base,T", [(0, 16), (0, 130), (77, 50), (500, 300)])
+def test_prefill_tensor_core_pass_matches_the_oracle(dev, nh, nkv, base, T):
+    # chunks of 16 tokens and more of one sequence: the causal tensor-core pass (sdpa16_prefill_kernel); 1, 2, 4 and 8
+    # query heads per KV head; cached prefixes of 0, 77 and 500 positions
+    from ironmill_b200 import ops
+    max_seq = base + T + 7
+    k, v = _caches(nkv, max_seq, base + T + nh)
+    q = H.rng_for("kv16-qpf", T).standard_normal((T, nh, 128)).astype(np.float16)
+    out = ops.sdpa_f16(dev, torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), 0.0884, nh, nkv, max_seq, base).cpu().numpy()
+    ref = orc.sdpa_f16(q, k, v, 0.0884, nh, nkv, 128, max_seq, base)
+    assert H.rel_err(out, ref) <= TOL, (nh, nkv, base, T)
+
+
 def test_kv_scatter_writes_the_rows_of_the_new_tokens(dev):
     from ironmill_b200 import ops
     nkv, max_seq, T = 2, 64, 5
